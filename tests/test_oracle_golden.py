@@ -88,7 +88,7 @@ def test_forward_against_reference(name, oracle_c):
     # bf16 / f16 reference forward: normalised max-rel 1e-2, with the weight codes formed
     # the way the forward forms them for that dtype (cast first).  With fp32 codes a few
     # codes per thousand differ and single outputs move by several percent, so that
-    # pairing is only held to 0.2.
+    # pairing is not held to an output tolerance; only the share of differing codes is.
     for dt, tdt in (("bf16", torch.bfloat16), ("f16", torch.float16)):
         xd = x.to(tdt).float().numpy()
         rr = O.bitlinear_forward(xd, w.numpy(), dt, weight_mode="cast_first")
@@ -96,7 +96,7 @@ def test_forward_against_reference(name, oracle_c):
         yl = O.bitlinear_forward_float(xd, w.numpy(), dt)
         assert norm_err(yl, z[f"y_{dt}"]) < 1e-2, dt
         r32 = O.bitlinear_forward(xd, w.numpy(), dt)
-        assert norm_err(r32["y"], z[f"y_{dt}"]) < 0.2, dt
+        assert (r32["codes"] != rr["codes"]).mean() < 0.01, dt
 
 
 @pytest.mark.parametrize("name", gi.I2S_CASES)
