@@ -135,7 +135,7 @@ def test_packers_against_reference():
     w = z["w"]
     codes, s = O.ternarize_absmean(w)
     assert np.array_equal(codes, t)
-    assert abs(float(s) - float(z["sglkernel_scale"])) <= 1e-9
+    assert ulp_dist(s, z["sglkernel_scale"]) <= 1  # torch's summation order
     assert np.array_equal(O.pack_i2s(t), z["sglkernel_simd"])
     assert np.array_equal(O.pack_i2s(t), z["core_blocked"])
     assert np.array_equal(O.pack_seq_lsb(t), z["sglkernel_scalar"])
