@@ -1,0 +1,143 @@
+/*
+ * wf_b200 — C ABI of the B200 (sm_100a) ternary BitLinear library.
+ *
+ * Every entry point returns 0 on success or a WF_E_* code; wf_last_error()
+ * gives the message of the calling thread's last failure.  Nothing throws and
+ * nothing exits.  All pointers are device pointers unless a comment says
+ * "host".  The caller owns every buffer; the library allocates nothing.
+ * `stream` is a cudaStream_t passed as void* (NULL = the default stream).
+ * Calls are asynchronous on that stream.  There is no CPU fallback: on a machine
+ * without an sm_100 device every compute entry point fails with WF_E_DEVICE.
+ *
+ * Each declaration cites the interface of the reference project that it
+ * replaces (paths inside that project).
+ */
+#ifndef WF_B200_H
+#define WF_B200_H
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+/* ---- status codes ---- */
+#define WF_OK 0
+#define WF_E_ARG 1       /* bad argument: null pointer, size, alignment, unsupported dtype */
+#define WF_E_DEVICE 2    /* no usable sm_100 device / CUDA runtime error */
+#define WF_E_SCRATCH 3   /* scratch buffer too small */
+#define WF_E_LIMIT 4     /* size beyond a documented maximum */
+
+/* ---- element types of activations / weights / outputs ---- */
+#define WF_F32 0
+#define WF_F16 1
+#define WF_BF16 2
+#define WF_I8 3 /* activations already quantized to int8 */
+
+/* ---- layouts of packed 2-bit weights (code = w + 1, 4 per byte, row-major [N, K/4]) ---- */
+#define WF_LAYOUT_WF16 0    /* this library's layout: per 32-bit word, byte b bit-pair j = weight 16*word + 4*j + b; K % 64 == 0 */
+#define WF_LAYOUT_I2S 1     /* 128-weight blocks of 32 bytes: byte j bits 7:6,5:4,3:2,1:0 = weights j, j+32, j+64, j+96; K % 128 == 0 */
+#define WF_LAYOUT_SEQ_LSB 2 /* byte j = weights 4j..4j+3 at shifts 0,2,4,6 (conversion source only) */
+#define WF_LAYOUT_SEQ_MSB 3 /* byte j = weights 4j..4j+3 at shifts 6,4,2,0 (conversion source only) */
+#define WF_LAYOUT_HF 4      /* [N/4, K] bytes: byte (r,c) = rows r, r+N/4, r+2N/4, r+3N/4 at shifts 0,2,4,6 (conversion source only) */
+
+/* ---- ternarization modes of wf_pack_ternary ---- */
+#define WF_PACK_FP32 0      /* scale = mean|w| in fp32, codes = clamp(rint(w / scale)) */
+#define WF_PACK_CAST_BF16 1 /* cast to bf16 first, every intermediate rounded to bf16 */
+#define WF_PACK_CAST_F16 2  /* cast to f16 first, every intermediate rounded to f16 */
+
+/* ---- activation quantization modes of wf_act_quant_i8 ---- */
+#define WF_ACT_PER_TOKEN 0  /* per row absmax, arithmetic in the element type of x */
+#define WF_ACT_PER_TENSOR 1 /* one absmax for the whole tensor, fp32, scale = max/127 returned */
+
+/* ---- launch flags of the contraction entry points ---- */
+#define WF_FLAG_PDL 1u /* launch with programmatic stream serialization: the kernel streams its
+                          first weights before it waits for the previous kernel of the stream */
+
+int wf_version(void);
+const char* wf_last_error(void);
+
+/* Returns WF_OK when the current CUDA device can run this library (compute capability 10.x). */
+int wf_device_check(void);
+
+/*
+ * Absmean ternarization + 2-bit packing of a weight matrix into WF_LAYOUT_WF16.
+ * Replaces: ternary_weight_quantization_no_scale (packages/training/src/wrinklefree/quantization/weight_quant.py:35-56),
+ *           BitLinear.weight_quant for the cast-first modes (packages/training/src/wrinklefree/models/bitlinear.py:46-64,103),
+ *           pack_ternary_sglkernel (packages/inference/scripts/convert_to_sglkernel.py:51-123).
+ * w: [N, K] row-major with row stride ldw elements, type w_dtype (WF_F32/WF_F16/WF_BF16).
+ * codes_out: [N, K/4] bytes.  scale_out: 2 floats: [0] the dequantization multiplier
+ * (mean|w| for WF_PACK_FP32; the rounded 1/scale of the forward for the cast-first
+ * modes), [1] the quantization multiplier actually used.  K % 64 == 0.
+ * scratch: at least wf_pack_scratch_bytes(N, K) bytes of device memory, 16-byte aligned.
+ * The sum of |w| is carried in fp64 in a fixed order: results are deterministic.
+ */
+size_t wf_pack_scratch_bytes(int64_t N, int64_t K);
+int wf_pack_ternary(const void* w, int w_dtype, int64_t N, int64_t K, int64_t ldw, int mode, float eps,
+                    uint8_t* codes_out, float* scale_out, void* scratch, size_t scratch_bytes, void* stream);
+
+/*
+ * Layout conversion of already-ternary packed weights into dst_layout (WF16 or I2S).
+ * Replaces the Python packing loops: _pack_ternary_weights (packages/inference/src/wrinklefree_inference/cache/bitnet_converter.py:26-77),
+ * repack_hf_weights / pack_weights (packages/inference/src/wrinklefree_inference/kernels/native.py:181-241),
+ * pack_ternary_weights (packages/inference/src/wrinklefree_inference/kernels/bitnet_patch.py:81-112).
+ * N, K are the logical weight dimensions; src holds N*K/4 bytes in src_layout.
+ */
+int wf_repack(const uint8_t* src, int src_layout, uint8_t* dst, int dst_layout, int64_t N, int64_t K, void* stream);
+
+/* Packs int8 ternary values {-1,0,1} [N,K] into `layout` (WF16 or I2S); unpacks the other way. */
+int wf_pack_codes(const int8_t* ternary, uint8_t* dst, int layout, int64_t N, int64_t K, void* stream);
+int wf_unpack_codes(const uint8_t* src, int layout, int8_t* ternary, int64_t N, int64_t K, void* stream);
+
+/*
+ * Activation quantization to int8.
+ * Replaces: BitLinear.activation_quant (packages/training/src/wrinklefree/models/bitlinear.py:66-84) for WF_ACT_PER_TOKEN,
+ *           quantize_activations_i8 / bitnet_quantize_activations_cpu
+ *           (packages/inference/extern/sglang-bitnet/sgl-kernel/csrc/bitnet/bitnet_gemv.cpp:880-1135,
+ *            .../csrc/cpu/torch_extension_cpu.cpp:409-427) for WF_ACT_PER_TENSOR.
+ * x: [M, K] row stride ldx elements.  q: [M, K] int8 contiguous.
+ * WF_ACT_PER_TOKEN: scale[m] = the multiplier rnd(rnd(1/max(absmax,eps))*127) in the arithmetic of x's type
+ *   (the value the reference divides by to dequantize); rowsum[m] (nullable) = sum_k q[m,k].
+ * WF_ACT_PER_TENSOR: x must be WF_F32; scale[0] = max/127 (max < 1e-6 counts as 1); rowsum as above.
+ *   Rounding is to nearest even everywhere.
+ */
+int wf_act_quant_i8(const void* x, int x_dtype, int64_t M, int64_t K, int64_t ldx, int mode, float eps, int8_t* q,
+                    float* scale, int32_t* rowsum, void* stream);
+
+/*
+ * y[m, n] = (float(acc[m,n]) * inv_sx[m]) * s_w (+ bias[n]),  acc[m,n] = sum_k q[m,k] * w[n,k]  (int32, exact).
+ *
+ * wf_bitlinear_decode: fused per-token activation quantization + contraction for small token counts
+ * (decode); any M is accepted, the weights are re-read once per group of tokens that fits in shared memory.
+ * wf_bitlinear_prefill: the tensor-core (tcgen05) contraction for large token counts; needs
+ * workspace of wf_prefill_workspace_bytes(M, K) bytes when x is not WF_I8.
+ *
+ * Replace: BitLinear.forward at lambda = 1 (packages/training/src/wrinklefree/models/bitlinear.py:86-113),
+ *          bitnet_gemv_cpu / bitnet_gemm_cpu (packages/inference/extern/sglang-bitnet/sgl-kernel/csrc/cpu/torch_extension_cpu.cpp:331-407),
+ *          bitnet_vec_dot_i2_i8 / bitnet_gemm_i2_i8 (.../csrc/bitnet/bitnet_gemv.cpp:325-874),
+ *          BitNetLinearMethod.apply (packages/inference/extern/sglang-bitnet/python/sglang/srt/layers/quantization/bitnet.py:205-255).
+ *
+ * x: [M, K] of x_dtype, row stride ldx elements.  With WF_I8, x is int8 [M, K]; x_scale (nullable, [M])
+ *    holds the per-token multipliers (inv_sx = 1/x_scale[m], 1 when null) and x_rowsum is ignored.
+ *    Otherwise x_scale must be null and inv_sx[m] = 1/scale[m] with scale as in wf_act_quant_i8 per token.
+ * codes: [N, K/4] in `layout` (WF16 or I2S).
+ * w_scale: device pointer to s_w (nullable: then s_w = w_scale_host).
+ * bias: nullable, [N] of bias_dtype.   y: [M, N] of y_dtype, row stride ldy elements.
+ * acc_out: nullable, int32 [M, N] contiguous: the raw integer accumulators, for bit-exact checks.
+ */
+int wf_bitlinear_decode(const void* x, int x_dtype, int64_t ldx, const float* x_scale, const uint8_t* codes,
+                        int layout, const float* w_scale, float w_scale_host, const void* bias, int bias_dtype,
+                        void* y, int y_dtype, int64_t ldy, int32_t* acc_out, int64_t M, int64_t N, int64_t K,
+                        float eps, unsigned flags, void* stream);
+
+size_t wf_prefill_workspace_bytes(int64_t M, int64_t K);
+int wf_bitlinear_prefill(const void* x, int x_dtype, int64_t ldx, const float* x_scale, const uint8_t* codes,
+                         int layout, const float* w_scale, float w_scale_host, const void* bias, int bias_dtype,
+                         void* y, int y_dtype, int64_t ldy, int32_t* acc_out, int64_t M, int64_t N, int64_t K,
+                         float eps, void* workspace, size_t workspace_bytes, unsigned flags, void* stream);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* WF_B200_H */

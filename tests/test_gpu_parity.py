@@ -1,0 +1,344 @@
+"""GPU parity tests: every CUDA entry point, called through the C ABI, against the CPU
+oracle and the golden vectors produced by the reference.  Integer results (codes, int8
+activations, int32 accumulators) must be bit-exact; fp32 outputs follow the stated
+operation order and must equal the oracle's exactly; outputs are additionally held to
+the reference forward within max|a-b|/max|b| <= 1e-5 (fp32) and 1e-2 (bf16 / f16)."""
+import os
+
+import numpy as np
+import pytest
+import torch
+
+import inputs as gi
+from oracle import bitlinear_oracle as O
+
+pytestmark = pytest.mark.gpu
+GOLD = os.path.join(os.path.dirname(__file__), "golden")
+DEV = "cuda:0"
+TDT = {"f32": torch.float32, "bf16": torch.bfloat16, "f16": torch.float16}
+
+
+def load(name):
+    z = np.load(os.path.join(GOLD, f"{name}.npz"))
+    x, w = gi.make_inputs(name)
+    assert gi.sha(x.numpy(), w.numpy()) == str(z["input_sha"])
+    return z, x, w
+
+
+def norm_err(a, b):
+    return float(np.abs(a - b).max() / max(np.abs(b).max(), 1e-30))
+
+
+def test_library_is_loaded_and_device_ok(wf):
+    assert wf.check_kernel_available()
+    assert wf._lib.lib().wf_version() >= 100
+
+
+# ---------------------------------------------------------------- weights
+@pytest.mark.parametrize("name", list(gi.CASES))
+def test_pack_fp32_codes_and_scale(wf, name):
+    z, x, w = load(name)
+    n, k = w.shape
+    codes, scale = wf.pack_ternary(w.to(DEV))
+    got = wf.unpack_codes(codes, n, k).cpu().numpy()
+    assert np.array_equal(got, z["codes"])  # identical to the reference's own codes
+    assert np.array_equal(codes.cpu().numpy(), O.pack_wf16(z["codes"]))  # and to the oracle's packed bytes
+    s = scale.cpu().numpy()
+    assert s[0] == O.absmean_scale(w.numpy()) and s[1] == s[0]
+    # deterministic: a second run gives the same bytes and scale
+    codes2, scale2 = wf.pack_ternary(w.to(DEV))
+    assert torch.equal(codes, codes2) and torch.equal(scale, scale2)
+
+
+@pytest.mark.parametrize("name", list(gi.CASES))
+@pytest.mark.parametrize("dt", ["bf16", "f16"])
+def test_pack_cast_first(wf, name, dt):
+    z, x, w = load(name)
+    n, k = w.shape
+    codes, scale = wf.pack_ternary(w.to(DEV), mode=TDT[dt])
+    assert np.array_equal(wf.unpack_codes(codes, n, k).cpu().numpy(), z[f"codes_fwd_{dt}"])
+    assert scale.cpu().numpy()[0] == z[f"dequant_fwd_{dt}"]
+    # a weight stored in the low-precision type gives the same result
+    codes2, scale2 = wf.pack_ternary(w.to(DEV).to(TDT[dt]), mode=TDT[dt])
+    assert torch.equal(codes, codes2) and torch.equal(scale, scale2)
+
+
+def test_pack_edge_cases(wf):
+    # all-zero weights -> all-zero codes, scale = eps (test_quantization.py:81-87)
+    codes, scale = wf.pack_ternary(torch.zeros(8, 64, device=DEV))
+    assert (wf.unpack_codes(codes, 8, 64) == 0).all() and scale[0].item() == np.float32(1e-5)
+    # extreme magnitudes stay ternary and finite
+    g = torch.Generator().manual_seed(3)
+    for mag in (1e-8, 1e6):
+        w = torch.randn(16, 128, generator=g) * mag
+        codes, scale = wf.pack_ternary(w.to(DEV))
+        ref, s = O.ternarize_absmean(w.numpy())
+        assert np.array_equal(wf.unpack_codes(codes, 16, 128).cpu().numpy(), ref) and scale[0].item() == s
+    # strided rows
+    w = torch.randn(16, 256, generator=g) * 0.02
+    wide = torch.zeros(16, 320)
+    wide[:, :256] = w
+    c1, s1 = wf.pack_ternary(w.to(DEV))
+    c2, s2 = wf.pack_ternary(wide.to(DEV)[:, :256])
+    assert torch.equal(c1, c2) and torch.equal(s1, s2)
+    with pytest.raises(RuntimeError):
+        wf.pack_ternary(torch.zeros(4, 48, device=DEV))  # K % 64 != 0
+
+
+def test_layout_conversions(wf):
+    z = np.load(os.path.join(GOLD, "packers.npz"))
+    t = z["ternary"]
+    n, k = t.shape
+    L = wf._lib
+    want_wf16, want_i2s = O.pack_wf16(t), O.pack_i2s(t)
+    tt = torch.from_numpy(t).to(DEV)
+    assert np.array_equal(wf.pack_codes(tt, L.LAYOUT_WF16).cpu().numpy(), want_wf16)
+    assert np.array_equal(wf.pack_codes(tt, L.LAYOUT_I2S).cpu().numpy(), want_i2s)
+    assert np.array_equal(want_i2s, z["sglkernel_simd"])  # the reference packer's own bytes
+    srcs = {L.LAYOUT_I2S: z["sglkernel_simd"], L.LAYOUT_SEQ_LSB: z["native_seq_lsb"],
+            L.LAYOUT_SEQ_MSB: z["quantize_to_bitnet_msb"], L.LAYOUT_HF: O.pack_hf(t), L.LAYOUT_WF16: want_wf16}
+    for lay, src in srcs.items():
+        s = torch.from_numpy(np.ascontiguousarray(src)).to(DEV)
+        assert np.array_equal(wf.repack(s, lay, n, k, L.LAYOUT_WF16).cpu().numpy(), want_wf16), lay
+        assert np.array_equal(wf.repack(s, lay, n, k, L.LAYOUT_I2S).cpu().numpy(), want_i2s), lay
+        assert np.array_equal(wf.unpack_codes(s, n, k, lay).cpu().numpy(), t), lay
+    # the HF bytes the reference's unpacker was pinned on
+    hf = torch.from_numpy(z["hf_bytes"]).to(DEV)
+    assert np.array_equal(wf.unpack_codes(hf, 16, 256, L.LAYOUT_HF).cpu().numpy(), z["hf_unpacked"])
+
+
+# ---------------------------------------------------------------- activations
+@pytest.mark.parametrize("name", list(gi.CASES))
+@pytest.mark.parametrize("dt", ["f32", "bf16", "f16"])
+def test_act_quant_per_token(wf, name, dt):
+    z, x, w = load(name)
+    q, s, rs = wf.act_quant_i8(x.to(TDT[dt]).to(DEV), want_rowsum=True)
+    assert np.array_equal(q.cpu().numpy(), z[f"q_{dt}"])
+    assert np.array_equal(s.cpu().numpy(), z[f"act_scale_{dt}"])
+    assert np.array_equal(rs.cpu().numpy(), z[f"q_{dt}"].astype(np.int32).sum(1))
+
+
+@pytest.mark.parametrize("name", gi.I2S_CASES)
+def test_act_quant_per_tensor(wf, name):
+    z, x, w = load(name)
+    q, s = wf.quantize_activations_i8(x.to(DEV))
+    assert np.array_equal(q.cpu().numpy(), z["i2s_q_tensor"])
+    assert s.cpu().numpy()[0] == z["i2s_act_scale"]
+    q0, s0 = wf.quantize_activations_i8(torch.zeros(2, 64, device=DEV))
+    assert not q0.any() and s0.item() == np.float32(1.0 / 127.0)
+
+
+def test_act_quant_edge_cases(wf):
+    g = torch.Generator().manual_seed(4)
+    x = torch.randn(7, 256, generator=g)
+    x[2] = 0  # all-zero token: absmax clamps to eps
+    x[3] *= 1000.0
+    x[4] *= 1e-6
+    for dt in ("f32", "bf16"):
+        xd = x.to(TDT[dt])
+        q, s = wf.act_quant_i8(xd.to(DEV))
+        qo, so = O.act_quant_per_token(xd.float().numpy(), dt)
+        assert np.array_equal(q.cpu().numpy(), qo) and np.array_equal(s.cpu().numpy(), so)
+
+
+# ---------------------------------------------------------------- contraction
+@pytest.mark.parametrize("name", list(gi.CASES))
+@pytest.mark.parametrize("dt", ["f32", "bf16", "f16"])
+def test_decode_against_golden(wf, name, dt):
+    z, x, w = load(name)
+    codes, scale = wf.pack_ternary(w.to(DEV))
+    xd = x.to(TDT[dt])
+    y, acc = wf.bitlinear(xd.to(DEV), codes, scale, out_dtype=torch.float32, want_acc=True)
+    acc_o = O.int_gemm(z[f"q_{dt}"], z["codes"])
+    assert np.array_equal(acc.cpu().numpy(), acc_o)  # int32 accumulators: bit-exact
+    y_o = O.rescale(acc_o, z[f"act_scale_{dt}"], O.absmean_scale(w.numpy()))
+    assert np.array_equal(y.cpu().numpy(), y_o)  # same fp32 operation order -> identical
+    if dt == "f32":
+        assert norm_err(y.cpu().numpy(), z["y_f32"]) < 1e-5
+        yb = wf.bitlinear(xd.to(DEV), codes, scale, bias=torch.from_numpy(z["bias"]).to(DEV))
+        assert norm_err(yb.cpu().numpy(), z["y_bias_f32"]) < 1e-5
+    else:
+        # against the low-precision reference forward the weights are packed the way that forward forms them
+        codes_c, scale_c = wf.pack_ternary(w.to(DEV), mode=TDT[dt])
+        yc = wf.bitlinear(xd.to(DEV), codes_c, scale_c)
+        assert yc.dtype == TDT[dt]
+        assert norm_err(yc.float().cpu().numpy(), z[f"y_{dt}"]) < 1e-2
+
+
+SHAPES = [  # (M, K, N)
+    (1, 64, 16), (2, 128, 24), (3, 192, 40), (4, 576, 100), (5, 640, 16), (7, 1024, 33), (8, 2560, 64), (9, 512, 48),
+    (16, 576, 1536), (17, 1088, 80), (33, 2560, 96), (64, 2560, 160), (64, 6912, 64), (70, 640, 32), (1, 6912, 2560),
+    (4, 2560, 6912), (1, 4096, 14336), (130, 256, 48),
+]
+
+
+@pytest.mark.parametrize("m,k,n", SHAPES)
+def test_decode_random_shapes_bit_exact(wf, oracle_c, m, k, n):
+    rng = np.random.default_rng(m * 100003 + k * 17 + n)
+    t = rng.integers(-1, 2, size=(n, k)).astype(np.int8)
+    x = torch.from_numpy(rng.standard_normal((m, k)).astype(np.float32))
+    x = gi.with_outliers(x, seed=m + k + n)
+    L = wf._lib
+    for dt in ("bf16", "f32"):
+        xd = x.to(TDT[dt])
+        q, s = oracle_c.act_quant(xd.float().numpy(), {"f32": 0, "bf16": 1}[dt])
+        acc_o = oracle_c.int_gemm(q, t)
+        y_o = oracle_c.rescale(acc_o, s, 0.0173)
+        for lay in ((L.LAYOUT_WF16, L.LAYOUT_I2S) if k % 128 == 0 else (L.LAYOUT_WF16,)):
+            codes = wf.pack_codes(torch.from_numpy(t).to(DEV), lay)
+            y, acc = wf.bitlinear(xd.to(DEV), codes, 0.0173, layout=lay, out_dtype=torch.float32, want_acc=True,
+                                  path="decode")
+            assert np.array_equal(acc.cpu().numpy(), acc_o), (dt, lay)
+            assert np.array_equal(y.cpu().numpy(), y_o), (dt, lay)
+
+
+def test_decode_extreme_codes_and_activations(wf):
+    """All 81 four-code combinations against activations pinned at -128 and 127."""
+    k = 64
+    combos = np.array([[a, b, c, d] for a in (-1, 0, 1) for b in (-1, 0, 1) for c in (-1, 0, 1) for d in (-1, 0, 1)], np.int8)
+    t = np.tile(combos, (1, k // 4))  # [81, 64]
+    q = np.empty((4, k), np.int8)
+    q[0], q[1] = 127, -128
+    q[2] = np.where(np.arange(k) % 2 == 0, 127, -128)
+    q[3] = np.where(np.arange(k) % 3 == 0, -128, 127)
+    codes = wf.pack_codes(torch.from_numpy(t).to(DEV))
+    y, acc = wf.bitlinear(torch.from_numpy(q).to(DEV), codes, 1.0, want_acc=True)
+    assert np.array_equal(acc.cpu().numpy(), O.int_gemm(q, t))
+    assert np.array_equal(y.cpu().numpy(), O.int_gemm(q, t).astype(np.float32))
+
+
+def test_int8_input_with_scales_and_strides(wf):
+    rng = np.random.default_rng(9)
+    m, k, n = 6, 384, 50
+    t = rng.integers(-1, 2, size=(n, k)).astype(np.int8)
+    q = rng.integers(-128, 128, size=(m, k)).astype(np.int8)
+    s = (rng.random(m).astype(np.float32) + 0.5) * 40
+    codes = wf.pack_codes(torch.from_numpy(t).to(DEV))
+    wide = torch.zeros(m, k + 64, dtype=torch.int8, device=DEV)
+    wide[:, :k] = torch.from_numpy(q).to(DEV)
+    out = torch.empty(m, n + 14, device=DEV)[:, :n]
+    ws = torch.tensor([0.021], device=DEV)
+    y, acc = wf.bitlinear(wide[:, :k], codes, ws, x_scale=torch.from_numpy(s).to(DEV), want_acc=True, out=None)
+    acc_o = O.int_gemm(q, t)
+    assert np.array_equal(acc.cpu().numpy(), acc_o)
+    assert np.array_equal(y.cpu().numpy(), O.rescale(acc_o, s, np.float32(0.021)))
+
+
+def test_prefill_entry_point_bit_exact(wf, oracle_c):
+    rng = np.random.default_rng(21)
+    for (m, k, n) in ((128, 256, 64), (200, 576, 144), (512, 2560, 256)):
+        t = rng.integers(-1, 2, size=(n, k)).astype(np.int8)
+        x = torch.from_numpy(rng.standard_normal((m, k)).astype(np.float32)).bfloat16()
+        q, s = oracle_c.act_quant(x.float().numpy(), 1)
+        acc_o = oracle_c.int_gemm(q, t)
+        codes = wf.pack_codes(torch.from_numpy(t).to(DEV))
+        y, acc = wf.bitlinear(x.to(DEV), codes, 0.02, out_dtype=torch.float32, want_acc=True, path="prefill")
+        assert np.array_equal(acc.cpu().numpy(), acc_o)
+        assert np.array_equal(y.cpu().numpy(), oracle_c.rescale(acc_o, s, 0.02))
+
+
+# ---------------------------------------------------------------- operator API and modules
+@pytest.mark.parametrize("name", gi.I2S_CASES)
+def test_operator_api_matches_reference_kernel(wf, name):
+    z, x, w = load(name)
+    m, k, n, _ = gi.CASES[name]
+    packed = torch.from_numpy(O.pack_i2s(z["codes"])).to(DEV)
+    q, s = wf.quantize_activations_i8(x.to(DEV))
+    out = wf.bitnet_gemm(packed, q, float(z["w_scale_torch"]))
+    assert out.dtype == torch.float32 and tuple(out.shape) == (m, n)
+    assert np.array_equal(out.cpu().numpy(), z["i2s_gemm"])  # the compiled reference kernel's own output
+    v = wf.bitnet_gemv(packed, q[0], float(z["w_scale_torch"]))
+    assert np.array_equal(v.cpu().numpy(), z["i2s_gemv_row0"])
+    with pytest.raises(ValueError):
+        wf.bitnet_gemv(packed[:, :16], q[0, :64], 1.0)  # K % 128 != 0, as the reference rejects
+
+
+@pytest.mark.parametrize("dt", ["f32", "bf16", "f16"])
+def test_bitlinear_module_drop_in(wf, dt):
+    z, x, w = load("c1")
+    layer = wf.BitLinear(576, 1536, bias=False).to(DEV)
+    with torch.no_grad():
+        layer.weight.copy_(w.to(DEV))
+        y = layer(x.to(TDT[dt]).to(DEV).reshape(2, 8, 576))
+    assert y.dtype == TDT[dt] and tuple(y.shape) == (2, 8, 1536)
+    tol = 1e-5 if dt == "f32" else 1e-2
+    assert norm_err(y.float().cpu().numpy().reshape(16, 1536), z[f"y_{dt}"]) < tol
+    # weight update invalidates the packed copy
+    with torch.no_grad():
+        layer.weight.mul_(2.0)
+        y2 = layer(x.to(TDT[dt]).to(DEV))
+    assert norm_err(y2.float().cpu().numpy(), 2 * z[f"y_{dt}"]) < max(tol, 4e-3 if dt != "f32" else 0)
+    with pytest.raises(RuntimeError):
+        with torch.no_grad():
+            layer(x)  # CPU tensor: no fallback
+
+
+def test_bitlinear_module_training_formula_on_gpu(wf):
+    z, x, w = load("k192")
+    layer = wf.BitLinear(192, 80).to(DEV)
+    with torch.no_grad():
+        layer.weight.copy_(w.to(DEV))
+    xg = x.to(DEV).requires_grad_(True)
+    y = layer(xg)  # gradient needed -> straight-through formula
+    y.sum().backward()
+    assert xg.grad is not None and layer.weight.grad is not None
+    assert norm_err(y.detach().cpu().numpy(), z["y_f32"]) < 1e-5
+    with torch.no_grad():
+        y_fast = layer(x.to(DEV))
+    assert norm_err(y_fast.cpu().numpy(), y.detach().cpu().numpy()) < 1e-5
+
+
+def test_linear_methods(wf):
+    z, x, w = load("k512")
+    m, k, n, _ = gi.CASES["k512"]
+    packed = torch.from_numpy(O.pack_i2s(z["codes"])).to(DEV)
+    scale = torch.tensor([float(z["w_scale_torch"])], device=DEV)
+    method = wf.BitNetConfig().get_quant_method(None, "")
+    layer = torch.nn.Module()
+    method.create_weights(layer, k, [n], k, n, torch.bfloat16)
+    assert tuple(layer.qweight.shape) == (n, k // 4) and layer.qweight.pack_factor == 4
+    layer = layer.to(DEV)
+    layer.qweight.data.copy_(packed)
+    layer.scale.data.copy_(scale)
+    method.process_weights_after_loading(layer)
+    out = method.apply(layer, x.to(DEV))
+    assert out.dtype == torch.float32
+    assert norm_err(out.cpu().numpy(), z["y_f32"]) < 1e-5
+    # the reference's own per-tensor arithmetic, as its apply() composes it
+    pt = wf.BitNetLinearMethod(wf.BitNetConfig(act_quant="per_tensor")).apply(layer, x.to(DEV))
+    assert norm_err(pt.cpu().numpy(), z["i2s_gemm"] * z["i2s_act_scale"]) < 1e-6
+    with pytest.raises(ValueError):
+        method.create_weights(torch.nn.Module(), 576, [64], 576, 64, torch.bfloat16)  # K % 128 != 0
+    fp = wf.PackedBitNetLinearMethod().apply(packed, scale, x.to(DEV).bfloat16(), n, k)
+    assert fp.dtype == torch.bfloat16 and norm_err(fp.float().cpu().numpy(), z["y_f32"]) < 2e-2
+    nat = wf.BitNetLinearNative(k, n, packed, scale)(x.to(DEV))
+    assert norm_err(nat.cpu().numpy(), z["y_f32"]) < 1e-5
+
+
+# ---------------------------------------------------------------- BASELINE sizes: properties
+@pytest.mark.parametrize("n,k", [(2560, 2560), (6912, 2560), (2560, 6912)])
+@pytest.mark.parametrize("m", [1, 4, 16, 64])
+def test_full_size_sweep_properties(wf, oracle_c, n, k, m):
+    g = torch.Generator().manual_seed(1000 * (n // 1000) + m)
+    w = torch.randn(n, k, generator=g) * 0.02
+    x = gi.with_outliers(torch.randn(m, k, generator=g), seed=m).bfloat16()
+    codes, scale = wf.pack_ternary(w.to(DEV))
+    zero_frac = float((wf.unpack_codes(codes, n, k) == 0).float().mean())
+    assert 0.29 < zero_frac < 0.33  # about 31 % zeros for absmean-ternarized Gaussians
+    y, acc = wf.bitlinear(x.to(DEV), codes, scale, out_dtype=torch.float32, want_acc=True)
+    # a slice of rows against the oracle, bit-exact
+    rows = slice(0, n, max(1, n // 64))
+    t, s_w = O.ternarize_absmean(w.numpy()[rows])
+    q, s = oracle_c.act_quant(x.float().numpy(), 1)
+    t_rows = wf.unpack_codes(codes, n, k).cpu().numpy()[rows]
+    assert np.array_equal(acc.cpu().numpy()[:, rows], oracle_c.int_gemm(q, t_rows))
+    # checksum over all rows: sum_n acc[m, n] = q[m] . (sum_n codes[n])
+    colsum = wf.unpack_codes(codes, n, k).to(torch.int64).sum(0).cpu().numpy()
+    assert np.array_equal(acc.to(torch.int64).sum(1).cpu().numpy(), q.astype(np.int64) @ colsum)
+    # linearity in the weights' sign: negated codes negate the accumulators
+    neg = wf.pack_codes(-wf.unpack_codes(codes, n, k))
+    _, acc_neg = wf.bitlinear(x.to(DEV), neg, scale, out_dtype=torch.float32, want_acc=True)
+    assert torch.equal(acc_neg, -acc)
+    # determinism
+    y2 = wf.bitlinear(x.to(DEV), codes, scale, out_dtype=torch.float32)
+    assert torch.equal(y, y2)

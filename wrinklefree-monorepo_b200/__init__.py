@@ -1,0 +1,30 @@
+"""wf_b200: B200-native (sm_100a) ternary BitLinear — packed 2-bit absmean weights,
+per-token int8 activations, int32 accumulation, fp32 rescale — behind the
+reference's module and operator interfaces.  CUDA only; no CPU fallback."""
+from . import _lib  # noqa: F401
+from .bitlinear import BitLinear, BitLinearNoActivationQuant, convert_linear_to_bitlinear  # noqa: F401
+from .lambda_warmup import (  # noqa: F401
+    LambdaWarmup,
+    get_current_lambda,
+    get_global_lambda_warmup,
+    set_global_lambda_warmup,
+)
+from .linear_method import (  # noqa: F401
+    BitNetConfig,
+    BitNetLinearMethod,
+    BitNetLinearNative,
+    PackedBitNetLinearMethod,
+)
+from .ops import (  # noqa: F401
+    QK_I2_S,
+    act_quant_i8,
+    bitlinear,
+    bitnet_gemm,
+    bitnet_gemv,
+    check_kernel_available,
+    pack_codes,
+    pack_ternary,
+    quantize_activations_i8,
+    repack,
+    unpack_codes,
+)

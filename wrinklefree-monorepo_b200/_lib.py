@@ -1,0 +1,68 @@
+"""ctypes binding of libwf_b200.so (the C ABI declared in include/wf_b200.h).
+
+There is no fallback: if the library has not been built, or a call fails, a
+RuntimeError is raised with the library's own message.
+"""
+from __future__ import annotations
+
+import ctypes as C
+import os
+
+HERE = os.path.dirname(os.path.abspath(__file__))
+LIB_PATH = os.path.join(HERE, "libwf_b200.so")
+
+# constants of include/wf_b200.h
+WF_F32, WF_F16, WF_BF16, WF_I8 = 0, 1, 2, 3
+LAYOUT_WF16, LAYOUT_I2S, LAYOUT_SEQ_LSB, LAYOUT_SEQ_MSB, LAYOUT_HF = 0, 1, 2, 3, 4
+PACK_FP32, PACK_CAST_BF16, PACK_CAST_F16 = 0, 1, 2
+ACT_PER_TOKEN, ACT_PER_TENSOR = 0, 1
+FLAG_PDL = 1
+
+_i64, _int, _f32, _p, _sz, _u32 = C.c_int64, C.c_int, C.c_float, C.c_void_p, C.c_size_t, C.c_uint
+
+_SIGNATURES = {
+    "wf_version": (_int, []),
+    "wf_last_error": (C.c_char_p, []),
+    "wf_device_check": (_int, []),
+    "wf_pack_scratch_bytes": (_sz, [_i64, _i64]),
+    "wf_pack_ternary": (_int, [_p, _int, _i64, _i64, _i64, _int, _f32, _p, _p, _p, _sz, _p]),
+    "wf_repack": (_int, [_p, _int, _p, _int, _i64, _i64, _p]),
+    "wf_pack_codes": (_int, [_p, _p, _int, _i64, _i64, _p]),
+    "wf_unpack_codes": (_int, [_p, _int, _p, _i64, _i64, _p]),
+    "wf_act_quant_i8": (_int, [_p, _int, _i64, _i64, _i64, _int, _f32, _p, _p, _p, _p]),
+    "wf_bitlinear_decode": (_int, [_p, _int, _i64, _p, _p, _int, _p, _f32, _p, _int, _p, _int, _i64, _p, _i64, _i64, _i64,
+                                   _f32, _u32, _p]),
+    "wf_prefill_workspace_bytes": (_sz, [_i64, _i64]),
+    "wf_bitlinear_prefill": (_int, [_p, _int, _i64, _p, _p, _int, _p, _f32, _p, _int, _p, _int, _i64, _p, _i64, _i64, _i64,
+                                    _f32, _p, _sz, _u32, _p]),
+}
+
+_lib = None
+
+
+def exported_symbols():
+    """Names every build of the library must export (checked by the CPU tests)."""
+    return sorted(_SIGNATURES)
+
+
+def lib():
+    global _lib
+    if _lib is None:
+        if not os.path.exists(LIB_PATH):
+            raise RuntimeError(
+                f"{LIB_PATH} is missing: build it with `python __graft_entry__.py build` "
+                "(there is no CPU or PyTorch fallback for these operators)"
+            )
+        handle = C.CDLL(LIB_PATH)
+        for name, (res, args) in _SIGNATURES.items():
+            fn = getattr(handle, name)
+            fn.restype = res
+            fn.argtypes = args
+        _lib = handle
+    return _lib
+
+
+def check(rc: int, what: str) -> None:
+    if rc != 0:
+        msg = lib().wf_last_error().decode("utf-8", "replace")
+        raise RuntimeError(f"{what} failed (code {rc}): {msg}")

@@ -1,0 +1,116 @@
+"""Drop-in replacement of the reference's BitLinear module
+(wrinklefree/models/bitlinear.py:12-192): same class names, constructor,
+methods, parameters and state_dict.
+
+Inference (no gradient needed, lambda == 1, CUDA input) runs on the packed
+weights through the C ABI: the weight is absmean-ternarized and packed once per
+weight version and input dtype, and every forward is one fused
+quantize-and-contract kernel.  Whenever a gradient is required or the lambda
+warm-up is active, the module evaluates the straight-through-estimator formula
+of the reference with torch operators, because that formula *is* the training
+definition; it is not an accelerated path and the CUDA kernels never route
+through it.
+"""
+from __future__ import annotations
+
+from typing import Optional
+
+import torch
+import torch.nn as nn
+import torch.nn.functional as F
+
+from . import ops
+from .lambda_warmup import get_current_lambda
+
+
+class BitLinear(nn.Linear):
+    """1.58-bit weights (absmean ternary) x 8-bit per-token activations."""
+
+    def __init__(self, in_features: int, out_features: int, bias: bool = False, eps: float = 1e-5):
+        super().__init__(in_features, out_features, bias=bias)
+        self.eps = eps
+        self._packed = {}  # x dtype -> (weight version, data_ptr, codes, scale)
+
+    # ---- the reference's two quantizers, as differentiable-free torch formulas ----
+    def weight_quant(self, w: torch.Tensor) -> torch.Tensor:
+        scale = 1.0 / w.abs().mean().clamp(min=self.eps)
+        return (w * scale).round().clamp(-1, 1) / scale
+
+    def activation_quant(self, x: torch.Tensor) -> torch.Tensor:
+        scale = 127.0 / x.abs().max(dim=-1, keepdim=True).values.clamp(min=self.eps)
+        return (x * scale).round().clamp(-128, 127) / scale
+
+    # ---- packed weights ----
+    def packed_weight(self, dtype: torch.dtype = torch.float32):
+        """(codes uint8 [N, K/4], scale float32 [2]) for inputs of `dtype`, rebuilt when the
+        weight tensor changes (in-place update or reassignment)."""
+        key = (self.weight._version, self.weight.data_ptr(), self.weight.device)
+        hit = self._packed.get(dtype)
+        if hit is None or hit[0] != key:
+            codes, scale = ops.pack_ternary(self.weight.detach(), mode=dtype, eps=self.eps)
+            hit = (key, codes, scale)
+            self._packed[dtype] = hit
+        return hit[1], hit[2]
+
+    def _fast_path(self, x: torch.Tensor, lam: float) -> bool:
+        if lam != 1.0:
+            return False
+        if torch.is_grad_enabled() and (x.requires_grad or self.weight.requires_grad
+                                        or (self.bias is not None and self.bias.requires_grad)):
+            return False
+        return True
+
+    def forward(self, x: torch.Tensor) -> torch.Tensor:
+        lam = get_current_lambda()
+        if self._fast_path(x, lam):
+            if not x.is_cuda:
+                raise RuntimeError("BitLinear inference runs on the CUDA kernels only; got a CPU tensor "
+                                   "(there is no CPU fallback)")
+            if x.dtype not in (torch.float32, torch.bfloat16, torch.float16):
+                raise TypeError(f"BitLinear: unsupported input dtype {x.dtype}")
+            codes, scale = self.packed_weight(x.dtype)
+            return ops.bitlinear(x, codes, scale, bias=self.bias, out_dtype=x.dtype, eps=self.eps)
+        # training definition (straight-through estimator with lambda mixing)
+        w = self.weight.to(x.dtype)
+        w_quant = w + lam * (self.weight_quant(w) - w).detach()
+        x_quant = x + lam * (self.activation_quant(x) - x).detach()
+        bias = self.bias.to(x.dtype) if self.bias is not None else None
+        return F.linear(x_quant, w_quant, bias)
+
+
+class BitLinearNoActivationQuant(nn.Linear):
+    """Weight-only variant (wrinklefree/models/bitlinear.py:116-151); torch formula only."""
+
+    def __init__(self, in_features: int, out_features: int, bias: bool = False, eps: float = 1e-5):
+        super().__init__(in_features, out_features, bias=bias)
+        self.eps = eps
+
+    def weight_quant(self, w: torch.Tensor) -> torch.Tensor:
+        scale = 1.0 / w.abs().mean().clamp(min=self.eps)
+        return (w * scale).round().clamp(-1, 1) / scale
+
+    def forward(self, x: torch.Tensor) -> torch.Tensor:
+        lam = get_current_lambda()
+        w = self.weight.to(x.dtype)
+        w_quant = w + lam * (self.weight_quant(w) - w).detach()
+        bias = self.bias.to(x.dtype) if self.bias is not None else None
+        return F.linear(x, w_quant, bias)
+
+
+def convert_linear_to_bitlinear(module: nn.Module, exclude_names: Optional[list] = None) -> nn.Module:
+    """Replace every nn.Linear below `module` by a BitLinear holding the same parameters
+    (wrinklefree/models/bitlinear.py:154-192)."""
+    exclude_names = exclude_names or []
+    for name, child in module.named_children():
+        if name in exclude_names:
+            continue
+        if isinstance(child, nn.Linear) and not isinstance(child, BitLinear):
+            new = BitLinear(child.in_features, child.out_features, bias=child.bias is not None)
+            new = new.to(device=child.weight.device, dtype=child.weight.dtype)
+            new.weight.data.copy_(child.weight.data)
+            if child.bias is not None:
+                new.bias.data.copy_(child.bias.data)
+            setattr(module, name, new)
+        else:
+            convert_linear_to_bitlinear(child, exclude_names)
+    return module

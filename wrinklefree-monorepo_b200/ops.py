@@ -1,0 +1,245 @@
+"""Tensor-level wrappers over the C ABI, plus the operator API of the reference's
+sgl_kernel.quantization.bitnet module under the same names.
+
+All tensors must live on a CUDA device of compute capability 10.x; the current
+torch stream is used.  Nothing here computes on the CPU.
+"""
+from __future__ import annotations
+
+from typing import Optional, Tuple
+
+import torch
+
+from . import _lib as L
+
+QK_I2_S = 128  # block size of the I2_S layout (sgl_kernel/quantization/bitnet.py:14)
+
+_DT = {torch.float32: L.WF_F32, torch.float16: L.WF_F16, torch.bfloat16: L.WF_BF16, torch.int8: L.WF_I8}
+_PACK_MODE = {torch.float32: L.PACK_FP32, torch.bfloat16: L.PACK_CAST_BF16, torch.float16: L.PACK_CAST_F16}
+DECODE_MAX_TOKENS = 64  # token counts above this go to the prefill entry point
+
+
+def _stream() -> int:
+    return torch.cuda.current_stream().cuda_stream
+
+
+def _need_cuda(*ts):
+    for t in ts:
+        if t is not None and not t.is_cuda:
+            raise RuntimeError("wf_b200 operators need CUDA tensors (there is no CPU path)")
+
+
+def _ptr(t: Optional[torch.Tensor]):
+    return None if t is None else t.data_ptr()
+
+
+def check_kernel_available() -> bool:
+    """True when the compiled library is loadable and the current device is sm_100
+    (name kept from sgl_kernel/quantization/bitnet.py:39-45)."""
+    try:
+        return torch.cuda.is_available() and L.lib().wf_device_check() == 0
+    except (RuntimeError, OSError):
+        return False
+
+
+# --------------------------------------------------------------------------
+# weights
+# --------------------------------------------------------------------------
+
+
+def pack_ternary(weight: torch.Tensor, mode: torch.dtype = torch.float32, eps: float = 1e-5
+                 ) -> Tuple[torch.Tensor, torch.Tensor]:
+    """Absmean-ternarize `weight` [N, K] and pack it 2 bits per weight (WF16 layout).
+
+    mode torch.float32: scale = mean|w| in fp32, codes = clamp(round(w / scale)) as
+    ternary_weight_quantization_no_scale (wrinklefree/quantization/weight_quant.py:35-56).
+    mode torch.bfloat16 / torch.float16: the cast-first arithmetic that BitLinear.forward
+    applies when its input has that dtype (wrinklefree/models/bitlinear.py:103-107).
+    Returns (codes uint8 [N, K/4], scale float32 [2]): scale[0] is the dequantization
+    multiplier, scale[1] the quantization multiplier.
+    """
+    _need_cuda(weight)
+    if weight.dim() != 2:
+        raise ValueError("pack_ternary expects a 2-D weight")
+    if weight.stride(1) != 1:
+        weight = weight.contiguous()
+    n, k = weight.shape
+    lib = L.lib()
+    codes = torch.empty((n, k // 4), dtype=torch.uint8, device=weight.device)
+    scale = torch.empty(2, dtype=torch.float32, device=weight.device)
+    nbytes = lib.wf_pack_scratch_bytes(n, k)
+    scratch = torch.empty(max(nbytes, 8), dtype=torch.uint8, device=weight.device)
+    with torch.cuda.device(weight.device):
+        L.check(lib.wf_pack_ternary(weight.data_ptr(), _DT[weight.dtype], n, k, weight.stride(0), _PACK_MODE[mode], eps,
+                                    codes.data_ptr(), scale.data_ptr(), scratch.data_ptr(), scratch.numel(), _stream()),
+                "wf_pack_ternary")
+    return codes, scale
+
+
+def repack(src: torch.Tensor, src_layout: int, n: int, k: int, dst_layout: int = L.LAYOUT_WF16) -> torch.Tensor:
+    """Convert packed ternary weights between layouts on the GPU (constants L.LAYOUT_*)."""
+    _need_cuda(src)
+    src = src.contiguous()
+    if src.numel() != n * k // 4:
+        raise ValueError(f"packed tensor has {src.numel()} bytes, expected {n * k // 4}")
+    dst = torch.empty((n, k // 4), dtype=torch.uint8, device=src.device)
+    with torch.cuda.device(src.device):
+        L.check(L.lib().wf_repack(src.data_ptr(), src_layout, dst.data_ptr(), dst_layout, n, k, _stream()), "wf_repack")
+    return dst
+
+
+def pack_codes(ternary: torch.Tensor, layout: int = L.LAYOUT_WF16) -> torch.Tensor:
+    """Pack int8 values in {-1, 0, 1} [N, K] into a kernel layout."""
+    _need_cuda(ternary)
+    t = ternary.to(torch.int8).contiguous()
+    n, k = t.shape
+    dst = torch.empty((n, k // 4), dtype=torch.uint8, device=t.device)
+    with torch.cuda.device(t.device):
+        L.check(L.lib().wf_pack_codes(t.data_ptr(), dst.data_ptr(), layout, n, k, _stream()), "wf_pack_codes")
+    return dst
+
+
+def unpack_codes(packed: torch.Tensor, n: int, k: int, layout: int = L.LAYOUT_WF16) -> torch.Tensor:
+    _need_cuda(packed)
+    packed = packed.contiguous()
+    out = torch.empty((n, k), dtype=torch.int8, device=packed.device)
+    with torch.cuda.device(packed.device):
+        L.check(L.lib().wf_unpack_codes(packed.data_ptr(), layout, out.data_ptr(), n, k, _stream()), "wf_unpack_codes")
+    return out
+
+
+# --------------------------------------------------------------------------
+# activations
+# --------------------------------------------------------------------------
+
+
+def act_quant_i8(x: torch.Tensor, per_tensor: bool = False, eps: float = 1e-5, want_rowsum: bool = False):
+    """int8 activation quantization.  Per token (default) follows BitLinear.activation_quant
+    in the arithmetic of x.dtype; per_tensor follows bitnet_quantize_activations_cpu (fp32).
+    Returns (q int8 same shape, scale fp32 [M] or [1][, rowsum int32 [M]])."""
+    _need_cuda(x)
+    k = x.shape[-1]
+    x2 = x.reshape(-1, k)
+    if x2.stride(1) != 1:
+        x2 = x2.contiguous()
+    m = x2.shape[0]
+    q = torch.empty((m, k), dtype=torch.int8, device=x.device)
+    scale = torch.empty(1 if per_tensor else m, dtype=torch.float32, device=x.device)
+    rowsum = torch.empty(m, dtype=torch.int32, device=x.device) if want_rowsum else None
+    with torch.cuda.device(x.device):
+        L.check(L.lib().wf_act_quant_i8(x2.data_ptr(), _DT[x2.dtype], m, k, x2.stride(0),
+                                        L.ACT_PER_TENSOR if per_tensor else L.ACT_PER_TOKEN, eps, q.data_ptr(),
+                                        scale.data_ptr(), _ptr(rowsum), _stream()), "wf_act_quant_i8")
+    q = q.reshape(x.shape)
+    return (q, scale, rowsum) if want_rowsum else (q, scale)
+
+
+# --------------------------------------------------------------------------
+# the contraction
+# --------------------------------------------------------------------------
+
+_workspaces = {}
+
+
+def _workspace(device, nbytes: int) -> torch.Tensor:
+    ws = _workspaces.get(device)
+    if ws is None or ws.numel() < nbytes:
+        ws = torch.empty(max(nbytes, 1 << 20), dtype=torch.uint8, device=device)
+        _workspaces[device] = ws
+    return ws
+
+
+def bitlinear(x: torch.Tensor, codes: torch.Tensor, w_scale, bias: Optional[torch.Tensor] = None,
+              out_dtype: Optional[torch.dtype] = None, layout: int = L.LAYOUT_WF16, x_scale: Optional[torch.Tensor] = None,
+              eps: float = 1e-5, want_acc: bool = False, pdl: bool = False, path: str = "auto",
+              out: Optional[torch.Tensor] = None):
+    """y = BitLinear(x) on packed weights: per-token int8 quantization of x (fused for small
+    token counts), exact int32 contraction with the ternary codes, fp32 rescale
+    ``(float(acc) * (1/s_x[m])) * s_w`` and optional bias.
+
+    x: [..., K] float32/float16/bfloat16, or int8 (already quantized; x_scale [M] optional).
+    codes: uint8 [N, K/4] in `layout`.  w_scale: device tensor (first element used) or float.
+    path: "auto" (decode kernel up to 64 tokens, prefill above), "decode" or "prefill".
+    Returns y [..., N] (and the int32 accumulators [M, N] when want_acc).
+    """
+    _need_cuda(x, codes, bias, x_scale)
+    k = x.shape[-1]
+    n = codes.shape[0]
+    if codes.dtype != torch.uint8 or codes.dim() != 2 or codes.shape[1] * 4 != k:
+        raise ValueError(f"codes must be uint8 [N, K/4] with K={k}, got {tuple(codes.shape)} {codes.dtype}")
+    x2 = x.reshape(-1, k)
+    if x2.stride(1) != 1:
+        x2 = x2.contiguous()
+    m = x2.shape[0]
+    if out_dtype is None:
+        out_dtype = torch.float32 if x.dtype == torch.int8 else x.dtype
+    y = out if out is not None else torch.empty((m, n), dtype=out_dtype, device=x.device)
+    acc = torch.empty((m, n), dtype=torch.int32, device=x.device) if want_acc else None
+    if isinstance(w_scale, torch.Tensor):
+        ws_ptr, ws_host = w_scale.data_ptr(), 0.0
+        if w_scale.dtype != torch.float32 or not w_scale.is_cuda:
+            raise ValueError("w_scale tensor must be float32 on the GPU")
+    else:
+        ws_ptr, ws_host = None, float(w_scale)
+    if not codes.is_contiguous():
+        codes = codes.contiguous()
+    lib = L.lib()
+    flags = L.FLAG_PDL if pdl else 0
+    use_prefill = path == "prefill" or (path == "auto" and m > DECODE_MAX_TOKENS)
+    with torch.cuda.device(x.device):
+        if m == 0:
+            pass
+        elif use_prefill:
+            nbytes = lib.wf_prefill_workspace_bytes(m, k) if x2.dtype != torch.int8 else 0
+            ws = _workspace(x.device, nbytes) if nbytes else None
+            L.check(lib.wf_bitlinear_prefill(x2.data_ptr(), _DT[x2.dtype], x2.stride(0), _ptr(x_scale), codes.data_ptr(),
+                                             layout, ws_ptr, ws_host, _ptr(bias), _DT[bias.dtype] if bias is not None else 0,
+                                             y.data_ptr(), _DT[y.dtype], y.stride(0), _ptr(acc), m, n, k, eps,
+                                             _ptr(ws), ws.numel() if ws is not None else 0, flags, _stream()),
+                    "wf_bitlinear_prefill")
+        else:
+            L.check(lib.wf_bitlinear_decode(x2.data_ptr(), _DT[x2.dtype], x2.stride(0), _ptr(x_scale), codes.data_ptr(),
+                                            layout, ws_ptr, ws_host, _ptr(bias), _DT[bias.dtype] if bias is not None else 0,
+                                            y.data_ptr(), _DT[y.dtype], y.stride(0), _ptr(acc), m, n, k, eps, flags,
+                                            _stream()), "wf_bitlinear_decode")
+    y = y.reshape(*x.shape[:-1], n)
+    return (y, acc) if want_acc else y
+
+
+# --------------------------------------------------------------------------
+# operator API of sgl_kernel.quantization.bitnet (same names, same argument meaning)
+# --------------------------------------------------------------------------
+
+
+def bitnet_gemv(packed_weights: torch.Tensor, activations: torch.Tensor, scale: float) -> torch.Tensor:
+    """y = scale * (W @ x): packed I2_S weights [out, in/4] uint8, int8 activations [in] -> float32 [out]
+    (sgl_kernel/quantization/bitnet.py:73-111)."""
+    in_features = packed_weights.shape[1] * 4
+    if in_features % QK_I2_S != 0:
+        raise ValueError(f"bitnet_gemv: in_features ({in_features}) must be multiple of {QK_I2_S}")
+    if activations.shape[0] != in_features:
+        raise ValueError(f"bitnet_gemv: activations.shape[0] ({activations.shape[0]}) != in_features ({in_features})")
+    return bitlinear(activations.reshape(1, -1), packed_weights, float(scale), layout=L.LAYOUT_I2S,
+                     out_dtype=torch.float32, path="decode").reshape(-1)
+
+
+def bitnet_gemm(packed_weights: torch.Tensor, activations: torch.Tensor, scale: float) -> torch.Tensor:
+    """Y = scale * (X @ W^T): int8 activations [batch, in] -> float32 [batch, out]
+    (sgl_kernel/quantization/bitnet.py:114-152)."""
+    in_features = packed_weights.shape[1] * 4
+    if in_features % QK_I2_S != 0:
+        raise ValueError(f"bitnet_gemm: in_features ({in_features}) must be multiple of {QK_I2_S}")
+    return bitlinear(activations, packed_weights, float(scale), layout=L.LAYOUT_I2S, out_dtype=torch.float32)
+
+
+def quantize_activations_i8(activations: torch.Tensor) -> Tuple[torch.Tensor, torch.Tensor]:
+    """Per-tensor absmax int8 quantization; returns (int8 tensor, scale tensor [1])
+    (sgl_kernel/quantization/bitnet.py:155-179)."""
+    q, s = act_quant_i8(activations.float(), per_tensor=True)
+    return q, s
+
+
+def auto_tune_tiles(M: int, N: int, K: int) -> Tuple[int, int, int]:
+    """Kept for API compatibility (sgl_kernel/quantization/bitnet.py:182-203); the GPU kernels
+    pick their own tiling, the returned values are the reference's CPU heuristics."""
+    return min(M, 64), min(N, 64), min(K, QK_I2_S * 2)
