@@ -1,0 +1,347 @@
+"""Benchmark of the ternary BitLinear hot path on B200.
+
+python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference]
+
+Workload ("decode_gemv_sweep"): the decode GEMV sweep at BitNet-2B-like shapes — projections
+(N x K) 2560x2560, 6912x2560, 2560x6912, token batches M in {1, 4, 16, 64}, weights
+N(0, 0.02) absmean-ternarized and packed 2 bits per weight, activations bf16 N(0,1) with
+0.1 % outliers at +-20.  One step is one pass of the fused quantize-and-contract kernel over
+a stack of independent layers of every (shape, M) pair; the stack holds more distinct packed
+weights (~0.5 GB) than the L2 cache, so every launch streams its weights from HBM.
+`value` is algorithmic GB/s (packed codes + scale + bf16 x + bf16 y per launch) over the whole
+step with inputs resident in HBM; `e2e` is the same with the step's activations copied in from
+pinned host memory and its outputs copied back inside the timed region.
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import statistics
+import subprocess
+import sys
+import threading
+import time
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+if ROOT not in sys.path:
+    sys.path.insert(0, ROOT)
+sys.path.insert(0, os.path.join(ROOT, "tests", "golden"))
+
+SHAPES = [(2560, 2560), (6912, 2560), (2560, 6912)]  # (N, K)
+BATCHES = [1, 4, 16, 64]
+LAYERS = {(2560, 2560): 96, (6912, 2560): 40, (2560, 6912): 40}  # distinct weight matrices per shape
+METRIC = "ternary_decode_gemv_GBps"
+
+
+def algorithmic_bytes(m: int, n: int, k: int) -> int:
+    """Packed codes + fp32 weight scale + bf16 activations read once + bf16 outputs."""
+    return n * k // 4 + 4 + 2 * m * k + 2 * m * n
+
+
+def reference_bytes(m: int, n: int, k: int) -> int:
+    """The reference's own accounting (scripts/benchmark_kernels.py:61-66): int8 x, fp32 y."""
+    return n * k // 4 + m * k + 4 * m * n
+
+
+def measured_peaks():
+    path = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.exists(path):
+        with open(path) as f:
+            return json.load(f), "measured"
+    return {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0}, "fallback"
+
+
+class ClockSampler(threading.Thread):
+    """Samples SM clocks and throttle reasons with nvidia-smi while the timed region runs."""
+
+    Q = ("clocks.sm,clocks.max.sm,clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
+         "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, index: int):
+        super().__init__(daemon=True)
+        self.index, self.samples, self.stop_flag, self.proc = index, [], False, None
+
+    def run(self):
+        try:
+            self.proc = subprocess.Popen(["nvidia-smi", f"--id={self.index}", f"--query-gpu={self.Q}",
+                                          "--format=csv,noheader,nounits", "-lms", "100"], stdout=subprocess.PIPE, text=True)
+            for line in self.proc.stdout:
+                if self.stop_flag:
+                    break
+                self.samples.append([c.strip() for c in line.split(",")])
+        except OSError:
+            pass
+
+    def finish(self):
+        self.stop_flag = True
+        if self.proc is not None:
+            self.proc.terminate()
+        sm = [float(s[0]) for s in self.samples if s and s[0].replace(".", "").isdigit()]
+        mx = [float(s[1]) for s in self.samples if len(s) > 1 and s[1].replace(".", "").isdigit()]
+        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+        reasons = sorted({names[i] for s in self.samples if len(s) >= 6 for i in range(4) if s[2 + i].startswith("Active")})
+        return {"sm_mhz": statistics.median(sm) if sm else None, "sm_max_mhz": max(mx) if mx else None,
+                "reasons": reasons, "samples": len(sm)}
+
+
+# ------------------------------------------------------------------ workload construction
+def build_workload(wf, torch, device, rank: int, world: int, layers_scale: float = 1.0):
+    """Packs the layer stacks on the device.  Returns a list of groups, one per (shape, M):
+    dict(n, k, m, layers=[(codes, scale)], x=[L, M, K] bf16, y=[L, M, N] bf16)."""
+    import inputs as gi
+
+    groups = []
+    stacks = {}
+    for si, (n, k) in enumerate(SHAPES):
+        nl = max(2, int(LAYERS[(n, k)] * layers_scale))
+        g = torch.Generator(device="cpu").manual_seed(1000 * si + 17 * rank)
+        lay = []
+        # one latent matrix per layer, generated on the device for speed (seeded), packed, then dropped
+        gd = torch.Generator(device=device).manual_seed(1000 * si + 17 * rank)
+        for _ in range(nl):
+            w = torch.randn(n, k, generator=gd, device=device, dtype=torch.float32) * 0.02
+            lay.append(wf.pack_ternary(w))
+            del w
+        stacks[(n, k)] = lay
+        for m in BATCHES:
+            x = torch.randn(nl, m, k, generator=g, dtype=torch.float32)
+            x = gi.with_outliers(x, seed=1000 * si + m).to(torch.bfloat16)
+            groups.append(dict(n=n, k=k, m=m, layers=lay, x_host=x.pin_memory(), x=x.to(device),
+                               y=torch.empty(nl, m, n, dtype=torch.bfloat16, device=device)))
+    return groups
+
+
+def run_step(wf, groups, pdl: bool):
+    launches = 0
+    for g in groups:
+        x, y = g["x"], g["y"]
+        for li, (codes, scale) in enumerate(g["layers"]):
+            wf.bitlinear(x[li], codes, scale, out=y[li], pdl=pdl, path="decode")
+            launches += 1
+    return launches
+
+
+def step_bytes(groups, fn=algorithmic_bytes) -> int:
+    return sum(fn(g["m"], g["n"], g["k"]) * len(g["layers"]) for g in groups)
+
+
+def capture(torch, fn):
+    """Warm up on a side stream, then capture `fn` into a CUDA graph."""
+    s = torch.cuda.Stream()
+    s.wait_stream(torch.cuda.current_stream())
+    with torch.cuda.stream(s):
+        fn()
+    torch.cuda.current_stream().wait_stream(s)
+    torch.cuda.synchronize()
+    graph = torch.cuda.CUDAGraph()
+    with torch.cuda.graph(graph):
+        fn()
+    return graph
+
+
+# ------------------------------------------------------------------ CPU reference arm
+def cpu_reference_run(steps: int, warmup: int, nl: int = 2):
+    """Times the reference's own CPU kernel (bitnet_gemm_i2_i8 compiled from its sources, behind
+    oracle/_ref) on a bounded sample of the sweep; falls back to the C port of the oracle."""
+    import numpy as np
+
+    from oracle import bitlinear_oracle as O
+    from oracle.clib import load_oracle, load_reference
+
+    ref = load_reference()
+    kind = "reference" if ref is not None else "port"
+    port = load_oracle()
+    cores = ref.num_threads() if ref is not None else port.num_threads()
+    rng = np.random.default_rng(0)
+    # nl layers per shape in the sample, rotated so the weights do not stay in the cores' L1/L2
+    work = []
+    for (n, k) in SHAPES:
+        mats = []
+        for _ in range(nl):
+            t = rng.integers(-1, 2, size=(n, k)).astype(np.int8)
+            mats.append(O.pack_i2s(t) if ref is not None else port.pack_wf16(t))
+        for m in BATCHES:
+            q = rng.integers(-127, 128, size=(m, k)).astype(np.int8)
+            work.append((n, k, m, mats, q))
+
+    def one_step():
+        for (n, k, m, mats, q) in work:
+            for p in mats:
+                if ref is not None:
+                    ref.gemm(p, q, 0.02)
+                else:
+                    port.gemm_wf16(q, p)
+
+    bytes_step = sum(algorithmic_bytes(m, n, k) * nl for (n, k, m, _, _) in work)
+    for _ in range(warmup):
+        one_step()
+    t0 = time.perf_counter()
+    for _ in range(steps):
+        one_step()
+    dt = (time.perf_counter() - t0) / steps
+    sample = (f"{nl} layers per shape x 3 shapes x M in {BATCHES}, int8 activations already quantized, "
+              f"{steps} steps of {dt * 1e3:.1f} ms; kernel: " +
+              ("bitnet_gemm_i2_i8 (AVX-%s build of the reference's bitnet_gemv.cpp, OpenMP)" % ref.flavour.replace("avx", "")
+               if ref is not None else "scalar C port of the oracle (OpenMP)"))
+    return dict(value=bytes_step / dt / 1e9, unit="GB/s", cores=cores, kind=kind, sample=sample), steps, warmup, dt
+
+
+# ------------------------------------------------------------------ main
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=20)
+    ap.add_argument("--warmup", type=int, default=5)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--layers-scale", type=float, default=1.0, help="scale the layer stacks (profiling on a small case)")
+    ap.add_argument("--no-pdl", action="store_true")
+    ap.add_argument("--no-cpu-baseline", action="store_true")
+    args = ap.parse_args()
+    rank = int(os.environ.get("RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+    warmup = max(args.warmup, 3)
+    config = {"workload": "decode_gemv_sweep", "shapes_NxK": ["%dx%d" % s for s in SHAPES], "batches_M": BATCHES,
+              "layers_per_shape": [LAYERS[s] for s in SHAPES], "activations": "bf16 N(0,1) + 0.1% outliers at +-20",
+              "weights": "N(0,0.02) absmean-ternarized, 2 bits/weight", "l2": "inputs larger than L2 (distinct weights per launch)"}
+
+    if args.impl == "reference":
+        if rank != 0:
+            return
+        cb, steps, wu, dt = cpu_reference_run(args.steps, warmup)
+        line = {"impl": "reference", "metric": METRIC, "value": cb["value"], "unit": "GB/s", "n_gpus": args.gpus,
+                "steps": steps, "warmup": wu, "ms_per_step": dt * 1e3, "higher_is_better": True, "scaling": "weak",
+                "vs_baseline": None, "dtype": "u8xs8->s32", "data": "synthetic", "config": config, "cpu_baseline": cb,
+                "e2e": {"value": cb["value"], "unit": "GB/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+                "gpu_launches": 0}
+        print(json.dumps(line))
+        return
+
+    import torch
+
+    from __graft_entry__ import load_package
+
+    wf = load_package()
+    torch.cuda.set_device(local_rank)
+    device = torch.device("cuda", local_rank)
+    if not wf.check_kernel_available():
+        raise RuntimeError("wf_b200 library / sm_100 device unavailable: " + wf._lib.lib().wf_last_error().decode())
+    dist = None
+    if world > 1:
+        import torch.distributed as dist
+
+        dist.init_process_group("nccl", device_id=device)
+
+    groups = build_workload(wf, torch, device, rank, world, args.layers_scale)
+    pdl = not args.no_pdl
+    try:
+        graph = capture(torch, lambda: run_step(wf, groups, pdl))
+    except RuntimeError as e:  # programmatic dependent launch not capturable here: plain edges
+        if not pdl:
+            raise
+        print(f"[bench] capture with programmatic dependent launch failed ({e}); retrying without", file=sys.stderr)
+        pdl = False
+        torch.cuda.synchronize()
+        graph = capture(torch, lambda: run_step(wf, groups, pdl))
+    launches = sum(len(g["layers"]) for g in groups)
+    total_bytes = step_bytes(groups)
+
+    def barrier():
+        if dist is not None:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    # ---- device-resident timing
+    for _ in range(warmup):
+        graph.replay()
+    barrier()
+    sampler = ClockSampler(local_rank)
+    if rank == 0:
+        sampler.start()
+        time.sleep(0.3)
+    ev0, ev1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    ev0.record()
+    for _ in range(args.steps):
+        graph.replay()
+    ev1.record()
+    barrier()
+    ms = ev0.elapsed_time(ev1) / args.steps
+    clocks = sampler.finish() if rank == 0 else None
+
+    # ---- end to end: pinned host activations in, outputs back to pinned host memory, every step
+    h2d = sum(g["x_host"].numel() * 2 for g in groups)
+    d2h = sum(g["y"].numel() * 2 for g in groups)
+    y_host = [torch.empty(g["y"].shape, dtype=torch.bfloat16).pin_memory() for g in groups]
+
+    def e2e_step():
+        for g in groups:
+            g["x"].copy_(g["x_host"], non_blocking=True)
+        graph.replay()
+        for g, yh in zip(groups, y_host):
+            yh.copy_(g["y"], non_blocking=True)
+
+    for _ in range(3):
+        e2e_step()
+    barrier()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for _ in range(args.steps):
+        e2e_step()
+    e1.record()
+    barrier()
+    ms_e2e = e0.elapsed_time(e1) / args.steps
+
+    if dist is not None:
+        t = torch.tensor([ms, ms_e2e], device=device)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        ms, ms_e2e = t.tolist()
+    if rank != 0:
+        if dist is not None:
+            dist.destroy_process_group()
+        return
+
+    peaks, peak_kind = measured_peaks()
+    value = world * total_bytes / (ms * 1e-3) / 1e9
+    per_launch_bytes = total_bytes / launches
+    per_launch_us = ms * 1e3 / launches
+    achieved = per_launch_bytes / (per_launch_us * 1e-6) / 1e9
+    # per (shape, M) breakdown, each group timed alone over its own layer stack
+    breakdown = []
+    for g in groups:
+        gg = [g]
+        gr = capture(torch, lambda: run_step(wf, gg, pdl))
+        for _ in range(3):
+            gr.replay()
+        torch.cuda.synchronize()
+        a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        a.record()
+        reps = 10
+        for _ in range(reps):
+            gr.replay()
+        b.record()
+        torch.cuda.synchronize()
+        us = a.elapsed_time(b) * 1e3 / reps / len(g["layers"])
+        by = algorithmic_bytes(g["m"], g["n"], g["k"])
+        breakdown.append({"N": g["n"], "K": g["k"], "M": g["m"], "us_per_launch": round(us, 3),
+                          "GBps": round(by / us / 1e3, 1), "frac_hbm": round(by / us / 1e3 / peaks["hbm_gbs"], 4),
+                          "GBps_reference_accounting": round(reference_bytes(g["m"], g["n"], g["k"]) / us / 1e3, 1)})
+    line = {"metric": METRIC, "value": value, "unit": "GB/s", "n_gpus": world, "steps": args.steps, "warmup": warmup,
+            "ms_per_step": ms, "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "u8xs8->s32",
+            "data": "synthetic", "config": dict(config, pdl=pdl, graph=True, parallelism="replicas" if world > 1 else "single"),
+            "roofline": {"bound": "hbm", "achieved": achieved, "peak": peaks["hbm_gbs"], "unit": "GB/s",
+                         "frac": achieved / peaks["hbm_gbs"], "traffic": None, "peak_kind": peak_kind + " copy bandwidth",
+                         "kernel": "decode_kernel", "bytes_per_launch": per_launch_bytes, "us_per_launch": per_launch_us},
+            "e2e": {"value": world * total_bytes / (ms_e2e * 1e-3) / 1e9, "unit": "GB/s", "h2d_bytes_per_step": h2d,
+                    "d2h_bytes_per_step": d2h, "ms_per_step": ms_e2e},
+            "gpu_launches": launches * args.steps, "clocks": clocks, "breakdown": breakdown}
+    if not args.no_cpu_baseline and world == 1:
+        cb, _, _, _ = cpu_reference_run(3, 1)
+        line["cpu_baseline"] = cb
+    print(json.dumps(line))
+    if dist is not None:
+        dist.destroy_process_group()
+
+
+if __name__ == "__main__":
+    main()
