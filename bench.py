@@ -6,8 +6,10 @@ Workload ("decode_gemv_sweep"): the decode GEMV sweep at BitNet-2B-like shapes â
 (N x K) 2560x2560, 6912x2560, 2560x6912, token batches M in {1, 4, 16, 64}, weights
 N(0, 0.02) absmean-ternarized and packed 2 bits per weight, activations bf16 N(0,1) with
 0.1 % outliers at +-20.  One step is one pass of the fused quantize-and-contract kernel over
-a stack of independent layers of every (shape, M) pair; the stack holds more distinct packed
-weights (~0.5 GB) than the L2 cache, so every launch streams its weights from HBM.
+a stack of independent layers of every (shape, M) pair (one grouped, persistent launch per
+pair); the stacks hold more distinct packed weights (~0.5 GB) than the L2 cache, so every
+launch streams its weights from HBM.  The per-pair breakdown also times the same stack as one
+launch per layer, chained with programmatic dependent launch (the latency-bound form).
 `value` is algorithmic GB/s (packed codes + scale + bf16 x + bf16 y per launch) over the whole
 step with inputs resident in HBM; `e2e` is the same with the step's activations copied in from
 pinned host memory and its outputs copied back inside the timed region.
@@ -107,12 +109,22 @@ def build_workload(wf, torch, device, rank: int, world: int, layers_scale: float
         for m in BATCHES:
             x = torch.randn(nl, m, k, generator=g, dtype=torch.float32)
             x = gi.with_outliers(x, seed=1000 * si + m).to(torch.bfloat16)
-            groups.append(dict(n=n, k=k, m=m, layers=lay, x_host=x.pin_memory(), x=x.to(device),
-                               y=torch.empty(nl, m, n, dtype=torch.bfloat16, device=device)))
+            xd = x.to(device)
+            y = torch.empty(nl, m, n, dtype=torch.bfloat16, device=device)
+            grp = wf.DecodeGroup([dict(x=xd[li], codes=c, w_scale=s, out=y[li]) for li, (c, s) in enumerate(lay)])
+            groups.append(dict(n=n, k=k, m=m, layers=lay, x_host=x.pin_memory(), x=xd, y=y, group=grp))
     return groups
 
 
 def run_step(wf, groups, pdl: bool):
+    """One pass over the sweep: every (shape, M) layer stack is one grouped launch."""
+    for g in groups:
+        g["group"].run(pdl=pdl)
+    return len(groups)
+
+
+def run_step_single(wf, groups, pdl: bool):
+    """The same pass as one launch per layer (the dependent-chain form of a decoder)."""
     launches = 0
     for g in groups:
         x, y = g["x"], g["y"]
@@ -244,7 +256,7 @@ def main():
         pdl = False
         torch.cuda.synchronize()
         graph = capture(torch, lambda: run_step(wf, groups, pdl))
-    launches = sum(len(g["layers"]) for g in groups)
+    launches = len(groups)
     total_bytes = step_bytes(groups)
 
     def barrier():
@@ -322,10 +334,23 @@ def main():
         b.record()
         torch.cuda.synchronize()
         us = a.elapsed_time(b) * 1e3 / reps / len(g["layers"])
+        # the same stack as one launch per layer, chained with programmatic dependent launch
+        gs = capture(torch, lambda: run_step_single(wf, gg, pdl))
+        for _ in range(3):
+            gs.replay()
+        torch.cuda.synchronize()
+        a.record()
+        for _ in range(reps):
+            gs.replay()
+        b.record()
+        torch.cuda.synchronize()
+        us_single = a.elapsed_time(b) * 1e3 / reps / len(g["layers"])
         by = algorithmic_bytes(g["m"], g["n"], g["k"])
-        breakdown.append({"N": g["n"], "K": g["k"], "M": g["m"], "us_per_launch": round(us, 3),
-                          "GBps": round(by / us / 1e3, 1), "frac_hbm": round(by / us / 1e3 / peaks["hbm_gbs"], 4),
-                          "GBps_reference_accounting": round(reference_bytes(g["m"], g["n"], g["k"]) / us / 1e3, 1)})
+        breakdown.append({"N": g["n"], "K": g["k"], "M": g["m"], "layers": len(g["layers"]),
+                          "us_per_layer_grouped": round(us, 3), "GBps": round(by / us / 1e3, 1),
+                          "frac_hbm": round(by / us / 1e3 / peaks["hbm_gbs"], 4),
+                          "GBps_reference_accounting": round(reference_bytes(g["m"], g["n"], g["k"]) / us / 1e3, 1),
+                          "us_per_launch_single_chain": round(us_single, 3)})
     line = {"metric": METRIC, "value": value, "unit": "GB/s", "n_gpus": world, "steps": args.steps, "warmup": warmup,
             "ms_per_step": ms, "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "u8xs8->s32",
             "data": "synthetic", "config": dict(config, pdl=pdl, graph=True, parallelism="replicas" if world > 1 else "single"),

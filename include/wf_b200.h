@@ -131,6 +131,43 @@ int wf_bitlinear_decode(const void* x, int x_dtype, int64_t ldx, const float* x_
                         void* y, int y_dtype, int64_t ldy, int32_t* acc_out, int64_t M, int64_t N, int64_t K,
                         float eps, unsigned flags, void* stream);
 
+/*
+ * Grouped form of wf_bitlinear_decode: P independent problems (for example the q/k/v or gate/up
+ * projections of one layer, or a stack of layers) run as ONE persistent kernel, so that weight
+ * streaming of one problem overlaps everything else of the others.  Replaces the per-projection loops of
+ * bitnet_qkv_forward_cpu / bitnet_mlp_forward_cpu
+ * (packages/inference/extern/sglang-bitnet/sgl-kernel/csrc/cpu/bitnet_fused_layer.cpp:150-375).
+ *
+ * Fields have the meaning of the wf_bitlinear_decode arguments of the same name.  All problems of a group
+ * share x_dtype.  The fields starting with an underscore are filled by wf_bitlinear_decode_plan.
+ * Use: fill a host array, call wf_bitlinear_decode_plan on it, copy it unchanged to device memory
+ * (it must stay there while the kernel runs; it may be reused for any number of launches), then call
+ * wf_bitlinear_decode_grouped with both copies.
+ */
+typedef struct wf_problem {
+    const void* x;
+    const float* x_scale;
+    const uint8_t* codes;
+    const float* w_scale;
+    const void* bias;
+    void* y;
+    int32_t* acc_out;
+    int64_t ldx, ldy;
+    int32_t M, N, K;
+    int32_t x_dtype, y_dtype, bias_dtype, layout;
+    float w_scale_host, eps;
+    int32_t _item_begin, _row_items, _chunks, _reserved;
+} wf_problem;
+
+int wf_bitlinear_decode_plan(wf_problem* host_problems, int P);
+int wf_bitlinear_decode_grouped(const wf_problem* dev_problems, const wf_problem* host_problems, int P, unsigned flags,
+                                void* stream);
+
+/* Last device-side status of the decode kernels on the current device: 0, or WF_E_LIMIT when a bounded
+ * wait inside a kernel ran out (the kernel then finished without hanging; its outputs are invalid).
+ * Synchronizes the device. */
+int wf_device_status(void);
+
 size_t wf_prefill_workspace_bytes(int64_t M, int64_t K);
 int wf_bitlinear_prefill(const void* x, int x_dtype, int64_t ldx, const float* x_scale, const uint8_t* codes,
                          int layout, const float* w_scale, float w_scale_host, const void* bias, int bias_dtype,

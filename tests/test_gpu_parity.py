@@ -342,3 +342,45 @@ def test_full_size_sweep_properties(wf, oracle_c, n, k, m):
     # determinism
     y2 = wf.bitlinear(x.to(DEV), codes, scale, out_dtype=torch.float32)
     assert torch.equal(y, y2)
+
+
+# ---------------------------------------------------------------- grouped launches
+def test_grouped_decode_matches_single_calls(wf, oracle_c):
+    """q/k/v-like and mixed-shape groups: one persistent launch, results identical to the oracle."""
+    rng = np.random.default_rng(77)
+    specs = [(3, 256, 96), (3, 256, 32), (3, 256, 32), (5, 576, 100), (1, 2560, 2560), (8, 640, 48), (2, 128, 16)]
+    probs, want = [], []
+    for (m, k, n) in specs:
+        t = rng.integers(-1, 2, size=(n, k)).astype(np.int8)
+        x = torch.from_numpy(rng.standard_normal((m, k)).astype(np.float32)).bfloat16()
+        q, s = oracle_c.act_quant(x.float().numpy(), 1)
+        acc = oracle_c.int_gemm(q, t)
+        want.append((acc, oracle_c.rescale(acc, s, 0.02)))
+        probs.append(dict(x=x.to(DEV), codes=wf.pack_codes(torch.from_numpy(t).to(DEV)), w_scale=0.02,
+                          out_dtype=torch.float32, want_acc=True))
+    grp = wf.DecodeGroup(probs)
+    for rep in range(2):  # the descriptor array is reusable
+        outs = grp.run(pdl=bool(rep))
+        for y, acc, (acc_o, y_o) in zip(outs, grp.accs, want):
+            assert np.array_equal(acc.cpu().numpy(), acc_o)
+            assert np.array_equal(y.cpu().numpy(), y_o)
+    wf.device_status()
+
+
+def test_grouped_large_stack(wf, oracle_c):
+    """A stack of layers larger than one wave of CTAs, M > token tile (several passes)."""
+    rng = np.random.default_rng(78)
+    probs, want = [], []
+    for i in range(12):
+        m, k, n = (20 if i % 2 else 1), 1024, 1000 + 16 * i
+        t = rng.integers(-1, 2, size=(n, k)).astype(np.int8)
+        x = torch.from_numpy(rng.standard_normal((m, k)).astype(np.float32))
+        q, s = oracle_c.act_quant(x.numpy(), 0)
+        acc = oracle_c.int_gemm(q, t)
+        want.append(acc)
+        probs.append(dict(x=x.to(DEV), codes=wf.pack_codes(torch.from_numpy(t).to(DEV)), w_scale=1.0, want_acc=True))
+    grp = wf.DecodeGroup(probs)
+    grp.run()
+    for acc, acc_o in zip(grp.accs, want):
+        assert np.array_equal(acc.cpu().numpy(), acc_o)
+    wf.device_status()

@@ -17,6 +17,8 @@ from .linear_method import (  # noqa: F401
 )
 from .ops import (  # noqa: F401
     QK_I2_S,
+    DecodeGroup,
+    device_status,
     act_quant_i8,
     bitlinear,
     bitnet_gemm,

@@ -20,6 +20,18 @@ FLAG_PDL = 1
 
 _i64, _int, _f32, _p, _sz, _u32 = C.c_int64, C.c_int, C.c_float, C.c_void_p, C.c_size_t, C.c_uint
 
+
+
+class Problem(C.Structure):
+    """Mirror of `wf_problem` (include/wf_b200.h)."""
+
+    _fields_ = [("x", _p), ("x_scale", _p), ("codes", _p), ("w_scale", _p), ("bias", _p), ("y", _p), ("acc_out", _p),
+                ("ldx", _i64), ("ldy", _i64), ("M", C.c_int32), ("N", C.c_int32), ("K", C.c_int32),
+                ("x_dtype", C.c_int32), ("y_dtype", C.c_int32), ("bias_dtype", C.c_int32), ("layout", C.c_int32),
+                ("w_scale_host", _f32), ("eps", _f32),
+                ("_item_begin", C.c_int32), ("_row_items", C.c_int32), ("_chunks", C.c_int32), ("_reserved", C.c_int32)]
+
+
 _SIGNATURES = {
     "wf_version": (_int, []),
     "wf_last_error": (C.c_char_p, []),
@@ -32,6 +44,9 @@ _SIGNATURES = {
     "wf_act_quant_i8": (_int, [_p, _int, _i64, _i64, _i64, _int, _f32, _p, _p, _p, _p]),
     "wf_bitlinear_decode": (_int, [_p, _int, _i64, _p, _p, _int, _p, _f32, _p, _int, _p, _int, _i64, _p, _i64, _i64, _i64,
                                    _f32, _u32, _p]),
+    "wf_bitlinear_decode_plan": (_int, [_p, _int]),
+    "wf_bitlinear_decode_grouped": (_int, [_p, _p, _int, _u32, _p]),
+    "wf_device_status": (_int, []),
     "wf_prefill_workspace_bytes": (_sz, [_i64, _i64]),
     "wf_bitlinear_prefill": (_int, [_p, _int, _i64, _p, _p, _int, _p, _f32, _p, _int, _p, _int, _i64, _p, _i64, _i64, _i64,
                                     _f32, _p, _sz, _u32, _p]),

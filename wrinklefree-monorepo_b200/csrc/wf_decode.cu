@@ -1,13 +1,20 @@
 // Fused per-token activation quantization + ternary contraction for small token
-// counts (decode).  HBM-bound: the packed weights are streamed once with 128-bit
-// loads, expanded in registers and contracted on the int8 tensor path against
-// activations quantized into shared memory by the same CTA.
+// counts (decode).  HBM-bound: a persistent kernel streams the packed weights
+// once through a ring of shared-memory stages filled by bulk asynchronous copies
+// (one elected producer thread, mbarrier completion), expands them in registers
+// and contracts them on the int8 tensor path against activations that the same
+// CTA quantized into shared memory.
 //
-// Work decomposition.  A "unit" is 16 weight rows x 512 weights of K (one warp:
-// each lane holds 2 x 16 bytes of two rows).  A CTA of 8 warps owns RG row
-// tiles (RG in {1,2,4,8}) and splits K over 8/RG warps per tile; partial sums
-// meet in a shared-memory int32 tile.  Tokens are processed in groups of
-// MT = 8*NT per CTA (grid.y).
+// Work list.  Every problem (one linear layer applied to M tokens) is cut into
+// items of 16*RI weight rows over the whole of K; tokens beyond MT = 8*NT per
+// pass form further passes ("chunks") over the same rows.  The items of all
+// problems of a launch form one list that is split into contiguous ranges, one
+// per CTA, so a CTA quantizes the activations of a problem once and then only
+// streams weights.
+//
+// Inside an item a "unit" is 16 rows x 512 weights of K, handled by one warp:
+// each lane reads 2 x 16 bytes of rows g and g+8 from the stage.  K is split
+// over 8/RI warps per row tile; partial sums meet in a shared-memory int32 tile.
 //
 // Expansion.  In both kernel layouts, (word >> 2p) & 0x03030303 yields four
 // weights that are consecutive in K, i.e. the partner of one 32-bit word of int8
@@ -18,33 +25,67 @@
 // token's sum of activations is subtracted once, in integers, in the epilogue.
 // With FOURACC the shift is skipped: the four bit positions accumulate into four
 // accumulators scaled by 1, 4, 16, 64 and are combined exactly at the end.
+//
+// Every wait on an mbarrier is bounded: when the bound is hit the CTA records
+// WF_E_LIMIT in a device status word, stops waiting anywhere and runs to its end.
 #include "wf_common.cuh"
 
 namespace wf {
 
-constexpr int DEC_THREADS = 256;
+constexpr int DEC_CONSUMERS = 256;               // 8 consumer warps
+constexpr int DEC_THREADS = DEC_CONSUMERS + 32;  // + 1 producer warp
 constexpr int TOK_STRIDE = 576;  // bytes of shared memory per (k-block, token): 512 + 64 skew (conflict-free 128-bit reads)
+constexpr int MAX_STAGES = 8;
+constexpr unsigned SPIN_LIMIT = 1u << 20;
 
-struct DecodeParams {
-    const void* x;
-    int64_t ldx;
-    const float* x_scale;  // WF_I8 input only (nullable)
-    const uint8_t* codes;
-    const float* w_scale;
-    float w_scale_host;
-    const void* bias;
-    int bias_dtype;
-    void* y;
-    int y_dtype;
-    int64_t ldy;
-    int32_t* acc_out;
-    int M, N, K;
-    int KB;   // number of 512-wide k-blocks (K rounded up)
-    int RG;   // row tiles per CTA
-    int MTA;  // token rows allocated in shared memory per k-block
-    int layout;
-    float eps;
+__device__ int g_decode_status = 0;
+
+struct DecodeCfg {
+    int P;            // problems
+    int total_items;
+    int RI;           // row tiles (16 rows) per item
+    int KBmax;        // k-blocks (512) of the largest K
+    int MTA;          // token rows allocated per k-block in shared memory
+    int stages;
+    int stage_bytes;  // bytes per stage (16*RI rows at the pitch of the largest K)
+    int act_off, stage_off;  // byte offsets inside dynamic shared memory
 };
+
+__device__ __forceinline__ uint32_t smem_u32(const void* p) { return static_cast<uint32_t>(__cvta_generic_to_shared(p)); }
+
+__device__ __forceinline__ void mbar_init(uint64_t* bar, unsigned count) {
+    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;\n" ::"r"(smem_u32(bar)), "r"(count));
+}
+__device__ __forceinline__ void mbar_arrive(uint64_t* bar) {
+    asm volatile("{\n .reg .b64 st;\n mbarrier.arrive.shared::cta.b64 st, [%0];\n}\n" ::"r"(smem_u32(bar)) : "memory");
+}
+__device__ __forceinline__ void mbar_expect_tx(uint64_t* bar, unsigned bytes) {
+    asm volatile("{\n .reg .b64 st;\n mbarrier.arrive.expect_tx.shared::cta.b64 st, [%0], %1;\n}\n" ::"r"(smem_u32(bar)), "r"(bytes)
+                 : "memory");
+}
+// Bounded wait.  Returns false (and poisons the CTA) when the bound is hit.
+__device__ __forceinline__ bool mbar_wait(uint64_t* bar, unsigned parity, volatile int* poisoned) {
+    if (*poisoned) return false;
+    const uint32_t a = smem_u32(bar);
+    for (unsigned it = 0; it < SPIN_LIMIT; ++it) {
+        unsigned ok;
+        asm volatile("{\n .reg .pred p;\n mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n selp.u32 %0, 1, 0, p;\n}\n"
+                     : "=r"(ok)
+                     : "r"(a), "r"(parity)
+                     : "memory");
+        if (ok) return true;
+        if ((it & 1023) == 1023 && *poisoned) return false;
+    }
+    *poisoned = 1;
+    atomicExch(&g_decode_status, WF_E_LIMIT);
+    return false;
+}
+__device__ __forceinline__ void bulk_copy_g2s(void* dst, const void* src, unsigned bytes, uint64_t* bar) {
+    asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];\n" ::"r"(smem_u32(dst)),
+                 "l"(src), "r"(bytes), "r"(smem_u32(bar))
+                 : "memory");
+}
+__device__ __forceinline__ void consumer_sync() { asm volatile("bar.sync 1, %0;\n" ::"n"(DEC_CONSUMERS) : "memory"); }
 
 __device__ __forceinline__ void mma_u8s8(int (&d)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3, uint32_t b0,
                                          uint32_t b1) {
@@ -52,14 +93,6 @@ __device__ __forceinline__ void mma_u8s8(int (&d)[4], uint32_t a0, uint32_t a1, 
         "mma.sync.aligned.m16n8k32.row.col.s32.u8.s8.s32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};\n"
         : "+r"(d[0]), "+r"(d[1]), "+r"(d[2]), "+r"(d[3])
         : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
-}
-
-__device__ __forceinline__ uint4 ldg_stream(const uint8_t* p) {
-    uint4 v;
-    asm volatile("ld.global.nc.L1::no_allocate.v4.u32 {%0,%1,%2,%3}, [%4];\n"
-                 : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w)
-                 : "l"(p));
-    return v;
 }
 
 // Byte offset, inside the 512-byte region of one (k-block, token), of the 32-bit activation word
@@ -79,20 +112,27 @@ __device__ __forceinline__ int act_slot_of_k(int layout, int kl) {
     return act_slot(byte >> 6, (byte >> 4) & 3, (byte >> 2) & 3, 3 - grp);
 }
 
-// ---- the quantization prologue: x -> int8 in fragment order, per-token multiplier and sum ----
+__host__ __device__ __forceinline__ int row_pitch(int K) { return ((K / 4 + 127) / 128) * 128 + 64; }
+
+// ---- the quantization stage: x -> int8 in fragment order, per-token multiplier and sum ----
+// Executed by the 256 consumer threads together whenever the CTA moves to another (problem, token pass).
 template <int XDT>
-__device__ __forceinline__ void quantize_tokens(const DecodeParams& p, int m0, int m_valid, uint8_t* s_act, float* s_inv,
+__device__ __forceinline__ void quantize_tokens(const wf_problem& p, int MTA, int m0, int m_valid, uint8_t* s_act, float* s_inv,
                                                 int* s_rowsum, unsigned* s_maxbits) {
     const int tid = threadIdx.x;
-    const int Kp = p.KB * 512;
+    const int KB = (p.K + 511) >> 9, Kp = KB * 512;
+    for (int i = tid; i < m_valid; i += DEC_CONSUMERS) {
+        s_rowsum[i] = 0;
+        s_maxbits[i] = 0;
+    }
+    consumer_sync();
     // threads per token: all 256 for one token down to one warp per token for 8 or more
-    int tpt = DEC_THREADS;
-    while (tpt > 32 && DEC_THREADS / tpt < m_valid) tpt >>= 1;
-    const int par = DEC_THREADS / tpt;  // tokens handled concurrently
+    int tpt = DEC_CONSUMERS;
+    while (tpt > 32 && DEC_CONSUMERS / tpt < m_valid) tpt >>= 1;
+    const int par = DEC_CONSUMERS / tpt;  // tokens handled concurrently
     const int sub = tid / tpt, lane_in = tid % tpt;
 
     if constexpr (XDT == WF_I8) {
-        // already int8: copy into fragment order, sum rows
         for (int tb = 0; tb < m_valid; tb += par) {
             int tok = tb + sub;
             int sum = 0;
@@ -106,7 +146,7 @@ __device__ __forceinline__ void quantize_tokens(const DecodeParams& p, int m0, i
                     for (int j = 0; j < 4; ++j) {
                         sum += __dp4a(static_cast<int>(w[j]), 0x01010101, 0);
                         int kb = (k + 4 * j) >> 9, kl = (k + 4 * j) & 511;
-                        *reinterpret_cast<uint32_t*>(s_act + (kb * p.MTA + tok) * TOK_STRIDE + act_slot_of_k(p.layout, kl)) = w[j];
+                        *reinterpret_cast<uint32_t*>(s_act + (kb * MTA + tok) * TOK_STRIDE + act_slot_of_k(p.layout, kl)) = w[j];
                     }
                 }
             }
@@ -115,7 +155,6 @@ __device__ __forceinline__ void quantize_tokens(const DecodeParams& p, int m0, i
             if (tok < m_valid && (tid & 31) == 0) atomicAdd(&s_rowsum[tok], sum);
         }
         if (tid < m_valid) s_inv[tid] = p.x_scale ? __frcp_rn(p.x_scale[m0 + tid]) : 1.0f;
-        return;
     } else {
         // pass 1: absmax per token
         for (int tb = 0; tb < m_valid; tb += par) {
@@ -133,7 +172,7 @@ __device__ __forceinline__ void quantize_tokens(const DecodeParams& p, int m0, i
             for (int o = 16; o > 0; o >>= 1) mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, o));
             if (tok < m_valid && (tid & 31) == 0) atomicMax(&s_maxbits[tok], __float_as_uint(mx));
         }
-        __syncthreads();
+        consumer_sync();
         // pass 2: quantize, scatter, sum
         for (int tb = 0; tb < m_valid; tb += par) {
             int tok = tb + sub;
@@ -155,7 +194,7 @@ __device__ __forceinline__ void quantize_tokens(const DecodeParams& p, int m0, i
                         }
                     }
                     int kb = k >> 9, kl = k & 511;
-                    uint8_t* base = s_act + (kb * p.MTA + tok) * TOK_STRIDE;
+                    uint8_t* base = s_act + (kb * MTA + tok) * TOK_STRIDE;
                     *reinterpret_cast<uint32_t*>(base + act_slot_of_k(p.layout, kl)) = w0;
                     *reinterpret_cast<uint32_t*>(base + act_slot_of_k(p.layout, kl + 4)) = w1;
                 }
@@ -165,30 +204,20 @@ __device__ __forceinline__ void quantize_tokens(const DecodeParams& p, int m0, i
             if (tok < m_valid && (tid & 31) == 0) atomicAdd(&s_rowsum[tok], sum);
         }
     }
+    consumer_sync();
 }
 
-struct UnitRegs {
-    uint4 r0[2], r1[2];  // [h]: 16 bytes of row g and of row g+8
-};
-
-__device__ __forceinline__ void load_unit(const DecodeParams& p, int kb, int row0, int row1, int t, UnitRegs& u) {
-    const int64_t rb = p.K >> 2;  // bytes per packed row
-#pragma unroll
-    for (int h = 0; h < 2; ++h) {
-        int64_t off = static_cast<int64_t>(kb) * 128 + h * 64 + t * 16;
-        bool kin = off < rb;
-        u.r0[h] = (kin && row0 < p.N) ? ldg_stream(p.codes + row0 * rb + off) : make_uint4(0, 0, 0, 0);
-        u.r1[h] = (kin && row1 < p.N) ? ldg_stream(p.codes + row1 * rb + off) : make_uint4(0, 0, 0, 0);
-    }
-}
-
+// One unit: 16 rows x 512 weights from the stage (rows g and g+8 of the tile, 2 x 16 bytes each per lane)
+// against the activations of one k-block.
 template <int NT, bool FOURACC>
-__device__ __forceinline__ void compute_unit(const UnitRegs& u, const uint8_t* s_act_kb, int MTA, int m_valid, int g, int t,
-                                             int (&acc)[NT][FOURACC ? 4 : 1][4]) {
+__device__ __forceinline__ void compute_unit(const uint8_t* w_r0, const uint8_t* w_r1, const uint8_t* s_act_kb, int m_valid, int g,
+                                             int t, int (&acc)[NT][FOURACC ? 4 : 1][4]) {
 #pragma unroll
     for (int h = 0; h < 2; ++h) {
-        const uint32_t wa[4] = {u.r0[h].x, u.r0[h].y, u.r0[h].z, u.r0[h].w};
-        const uint32_t wb[4] = {u.r1[h].x, u.r1[h].y, u.r1[h].z, u.r1[h].w};
+        const uint4 ra = *reinterpret_cast<const uint4*>(w_r0 + h * 64 + t * 16);
+        const uint4 rb = *reinterpret_cast<const uint4*>(w_r1 + h * 64 + t * 16);
+        const uint32_t wa[4] = {ra.x, ra.y, ra.z, ra.w};
+        const uint32_t wb[4] = {rb.x, rb.y, rb.z, rb.w};
 #pragma unroll
         for (int pp = 0; pp < 4; ++pp) {
             uint32_t a0[4], a1[4];
@@ -215,150 +244,320 @@ __device__ __forceinline__ void compute_unit(const UnitRegs& u, const uint8_t* s
     }
 }
 
+// item index -> (problem, token pass, row item)
+__device__ __forceinline__ void locate_item(const wf_problem* __restrict__ probs, int P, int item, int& pi, int& chunk, int& ritem) {
+    int lo = 0, hi = P - 1;
+    while (lo < hi) {  // last problem whose _item_begin <= item
+        int mid = (lo + hi + 1) >> 1;
+        if (probs[mid]._item_begin <= item) lo = mid; else hi = mid - 1;
+    }
+    pi = lo;
+    int local = item - probs[lo]._item_begin;
+    chunk = local / probs[lo]._row_items;
+    ritem = local % probs[lo]._row_items;
+}
+
 template <int XDT, int NT, bool FOURACC>
-__global__ void __launch_bounds__(DEC_THREADS) decode_kernel(const DecodeParams p) {
-    extern __shared__ __align__(16) uint8_t smem[];
+__global__ void __launch_bounds__(DEC_THREADS, 1)
+    decode_kernel(const wf_problem* __restrict__ dev_problems, const __grid_constant__ wf_problem single, const DecodeCfg cfg) {
+    extern __shared__ __align__(128) uint8_t smem[];
     constexpr int MT = NT * 8;
-    // shared memory: [MT] multipliers, [MT] row sums, [MT] absmax bits, [RG][16][MT] partial sums, activations
-    float* s_inv = reinterpret_cast<float*>(smem);
-    int* s_rowsum = reinterpret_cast<int*>(smem + MT * 4);
-    unsigned* s_maxbits = reinterpret_cast<unsigned*>(smem + MT * 8);
-    int* s_red = reinterpret_cast<int*>(smem + MT * 12);
-    uint8_t* s_act = smem + MT * 12 + p.RG * 16 * MT * 4;
+    uint64_t* full = reinterpret_cast<uint64_t*>(smem);
+    uint64_t* empty = full + MAX_STAGES;
+    volatile int* poisoned = reinterpret_cast<volatile int*>(smem + 128);
+    float* s_inv = reinterpret_cast<float*>(smem + 256);
+    int* s_rowsum = reinterpret_cast<int*>(smem + 256 + MT * 4);
+    unsigned* s_maxbits = reinterpret_cast<unsigned*>(smem + 256 + MT * 8);
+    int* s_red = reinterpret_cast<int*>(smem + 256 + MT * 12);  // two buffers of RI*16*MT
+    uint8_t* s_act = smem + cfg.act_off;
+    uint8_t* s_stage = smem + cfg.stage_off;
+    const wf_problem* probs = dev_problems ? dev_problems : &single;
 
     // let the next kernel of the stream start its own weight streaming as early as possible
     asm volatile("griddepcontrol.launch_dependents;\n" ::: "memory");
 
-    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31, g = lane >> 2, t = lane & 3;
-    const int rt_local = warp % p.RG, ks = warp / p.RG, KS = 8 / p.RG;
-    const int rt = blockIdx.x * p.RG + rt_local;
-    const int row0 = rt * 16 + g, row1 = row0 + 8;
-    const int m0 = blockIdx.y * MT;
-    const int m_valid = min(MT, p.M - m0);
-
-    // weights do not depend on the previous kernel: issue the first unit's loads now
-    UnitRegs cur, nxt;
-    int kb = ks;
-    if (kb < p.KB) load_unit(p, kb, row0, row1, t, cur);
-
-    for (int i = tid; i < MT; i += DEC_THREADS) {
-        s_rowsum[i] = 0;
-        s_maxbits[i] = 0;
-        s_inv[i] = 0.f;
+    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    const int red_size = cfg.RI * 16 * MT;
+    if (tid == 0) {
+        for (int s = 0; s < cfg.stages; ++s) {
+            mbar_init(&full[s], 1);
+            mbar_init(&empty[s], DEC_CONSUMERS / 32);
+        }
+        *poisoned = 0;
+        asm volatile("fence.mbarrier_init.release.cluster;\n" ::: "memory");
     }
-    for (int i = tid; i < p.RG * 16 * MT; i += DEC_THREADS) s_red[i] = 0;
+    for (int i = tid; i < 2 * red_size; i += DEC_THREADS) s_red[i] = 0;
     __syncthreads();
 
+    const int beg = static_cast<int>(static_cast<int64_t>(blockIdx.x) * cfg.total_items / gridDim.x);
+    const int end = static_cast<int>(static_cast<int64_t>(blockIdx.x + 1) * cfg.total_items / gridDim.x);
+    const int rows_item = cfg.RI * 16;
+
+    if (warp == DEC_CONSUMERS / 32) {
+        // ---------------- producer: weights do not depend on the previous kernel, stream them right away
+        for (int it = beg, n = 0; it < end; ++it, ++n) {
+            const int stage = n % cfg.stages;
+            if (n >= cfg.stages) mbar_wait(&empty[stage], ((n / cfg.stages) - 1) & 1, poisoned);
+            int pi, chunk, ritem;
+            locate_item(probs, cfg.P, it, pi, chunk, ritem);
+            const wf_problem& p = probs[pi];
+            const int r0 = ritem * rows_item;
+            const int nrows = min(rows_item, p.N - r0);
+            const unsigned rowbytes = static_cast<unsigned>(p.K >> 2);
+            const int pitch = row_pitch(p.K);
+            if (lane == 0) mbar_expect_tx(&full[stage], static_cast<unsigned>(nrows) * rowbytes);
+            __syncwarp();
+            uint8_t* dst = s_stage + static_cast<size_t>(stage) * cfg.stage_bytes;
+            const uint8_t* src = p.codes + static_cast<int64_t>(r0) * rowbytes;
+            for (int r = lane; r < nrows; r += 32)
+                bulk_copy_g2s(dst + r * pitch, src + static_cast<int64_t>(r) * rowbytes, rowbytes, &full[stage]);
+        }
+        return;
+    }
+
+    // ---------------- consumers
+    const int g = lane >> 2, t = lane & 3;
+    const int rt_local = warp % cfg.RI, ks = warp / cfg.RI, KS = (DEC_CONSUMERS / 32) / cfg.RI;
+    int cur_p = -1, cur_chunk = -1, m0 = 0, m_valid = 0;
     // x may be produced by the previous kernel of the stream
     asm volatile("griddepcontrol.wait;\n" ::: "memory");
-    quantize_tokens<XDT>(p, m0, m_valid, s_act, s_inv, s_rowsum, s_maxbits);
-    __syncthreads();
 
-    int acc[NT][FOURACC ? 4 : 1][4];
-#pragma unroll
-    for (int a = 0; a < NT; ++a)
-#pragma unroll
-        for (int b = 0; b < (FOURACC ? 4 : 1); ++b)
-#pragma unroll
-            for (int c = 0; c < 4; ++c) acc[a][b][c] = 0;
+    for (int it = beg, n = 0; it < end; ++it, ++n) {
+        int pi, chunk, ritem;
+        locate_item(probs, cfg.P, it, pi, chunk, ritem);
+        const wf_problem& p = probs[pi];
+        if (pi != cur_p || chunk != cur_chunk) {
+            consumer_sync();  // nobody still reads the multipliers / sums of the previous pass
+            cur_p = pi;
+            cur_chunk = chunk;
+            m0 = chunk * MT;
+            m_valid = min(MT, p.M - m0);
+            quantize_tokens<XDT>(p, cfg.MTA, m0, m_valid, s_act, s_inv, s_rowsum, s_maxbits);
+        }
+        const int stage = n % cfg.stages;
+        mbar_wait(&full[stage], (n / cfg.stages) & 1, poisoned);
 
+        int acc[NT][FOURACC ? 4 : 1][4];
+#pragma unroll
+        for (int a = 0; a < NT; ++a)
+#pragma unroll
+            for (int b = 0; b < (FOURACC ? 4 : 1); ++b)
+#pragma unroll
+                for (int c = 0; c < 4; ++c) acc[a][b][c] = 0;
+
+        const int KB = (p.K + 511) >> 9;
+        const int pitch = row_pitch(p.K);
+        const uint8_t* w_r0 = s_stage + static_cast<size_t>(stage) * cfg.stage_bytes + (rt_local * 16 + g) * pitch;
+        const uint8_t* w_r1 = w_r0 + 8 * pitch;
 #pragma unroll 1
-    for (; kb < p.KB; kb += KS) {
-        const int kn = kb + KS;
-        if (kn < p.KB) load_unit(p, kn, row0, row1, t, nxt);
-        compute_unit<NT, FOURACC>(cur, s_act + kb * p.MTA * TOK_STRIDE, p.MTA, m_valid, g, t, acc);
-        if (kn < p.KB) cur = nxt;
-    }
+        for (int kb = ks; kb < KB; kb += KS)
+            compute_unit<NT, FOURACC>(w_r0 + kb * 128, w_r1 + kb * 128, s_act + kb * cfg.MTA * TOK_STRIDE, m_valid, g, t, acc);
+        __syncwarp();
+        if (lane == 0) mbar_arrive(&empty[stage]);  // this warp no longer reads the stage
 
-    // fold the partial sums of the K-splits: lane holds rows g, g+8 x tokens 2t, 2t+1 of every token tile
+        // fold the partial sums of the K-splits: lane holds rows g, g+8 x tokens 2t, 2t+1 of every token tile
+        int* red = s_red + (n & 1) * red_size + rt_local * 16 * MT;
 #pragma unroll
-    for (int nt = 0; nt < NT; ++nt) {
-        int v[4];
+        for (int nt = 0; nt < NT; ++nt) {
+            int v[4];
 #pragma unroll
-        for (int c = 0; c < 4; ++c) {
-            if constexpr (FOURACC)
-                v[c] = acc[nt][0][c] + (acc[nt][1][c] >> 2) + (acc[nt][2][c] >> 4) + (acc[nt][3][c] >> 6);
-            else
-                v[c] = acc[nt][0][c];
+            for (int c = 0; c < 4; ++c) {
+                if constexpr (FOURACC)
+                    v[c] = acc[nt][0][c] + (acc[nt][1][c] >> 2) + (acc[nt][2][c] >> 4) + (acc[nt][3][c] >> 6);
+                else
+                    v[c] = acc[nt][0][c];
+            }
+            const int tk = nt * 8 + 2 * t;
+            atomicAdd(&red[g * MT + tk], v[0]);
+            atomicAdd(&red[g * MT + tk + 1], v[1]);
+            atomicAdd(&red[(g + 8) * MT + tk], v[2]);
+            atomicAdd(&red[(g + 8) * MT + tk + 1], v[3]);
         }
-        int* base = s_red + rt_local * 16 * MT;
-        const int tk = nt * 8 + 2 * t;
-        if (KS == 1) {
-            base[g * MT + tk] = v[0];
-            base[g * MT + tk + 1] = v[1];
-            base[(g + 8) * MT + tk] = v[2];
-            base[(g + 8) * MT + tk + 1] = v[3];
-        } else {
-            atomicAdd(&base[g * MT + tk], v[0]);
-            atomicAdd(&base[g * MT + tk + 1], v[1]);
-            atomicAdd(&base[(g + 8) * MT + tk], v[2]);
-            atomicAdd(&base[(g + 8) * MT + tk + 1], v[3]);
-        }
-    }
-    __syncthreads();
+        consumer_sync();
 
-    // epilogue: integer correction, fp32 rescale in the stated order, bias, store
-    const float s_w = p.w_scale ? __ldg(p.w_scale) : p.w_scale_host;
-    const int rows_cta = p.RG * 16;
-    for (int idx = tid; idx < rows_cta * m_valid; idx += DEC_THREADS) {
-        const int tok = idx / rows_cta, r = idx % rows_cta;
-        const int n = blockIdx.x * rows_cta + r;
-        if (n >= p.N) continue;
-        const int a = s_red[(r >> 4) * 16 * MT + (r & 15) * MT + tok] - s_rowsum[tok];
-        float v = rescale(a, s_inv[tok], s_w);
-        if (p.bias) v = __fadd_rn(v, load1_rt(p.bias, p.bias_dtype, n));
-        const int64_t m = m0 + tok;
-        store1_rt(p.y, p.y_dtype, m * p.ldy + n, v);
-        if (p.acc_out) p.acc_out[m * p.N + n] = a;
+        // epilogue: integer correction, fp32 rescale in the stated order, bias, store; clears the tile
+        const float s_w = p.w_scale ? __ldg(p.w_scale) : p.w_scale_host;
+        int* redb = s_red + (n & 1) * red_size;
+        const int r0 = ritem * rows_item;
+        for (int idx = tid; idx < rows_item * m_valid; idx += DEC_CONSUMERS) {
+            const int tok = idx / rows_item, r = idx % rows_item;
+            const int cell = (r >> 4) * 16 * MT + (r & 15) * MT + tok;
+            const int raw = redb[cell];
+            redb[cell] = 0;
+            const int nrow = r0 + r;
+            if (nrow >= p.N) continue;
+            const int a = raw - s_rowsum[tok];
+            float v = rescale(a, s_inv[tok], s_w);
+            if (p.bias) v = __fadd_rn(v, load1_rt(p.bias, p.bias_dtype, nrow));
+            const int64_t m = m0 + tok;
+            store1_rt(p.y, p.y_dtype, m * p.ldy + nrow, v);
+            if (p.acc_out) p.acc_out[m * p.N + nrow] = a;
+        }
     }
 }
 
+// ------------------------------------------------------------------ host side
+struct GroupPlan {
+    int NT, RI, KBmax, MTA, stages, stage_bytes, act_off, stage_off, total_items, grid;
+    size_t smem;
+};
+
+constexpr size_t SMEM_MAX = 227 * 1024;
+
+static int num_sms() {
+    static thread_local int cached = 0;
+    if (!cached) {
+        int dev = 0, n = 0;
+        if (cudaGetDevice(&dev) != cudaSuccess || cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || n <= 0)
+            n = 148;
+        cached = n;
+    }
+    return cached;
+}
+
+static size_t fixed_bytes(int NT, int RI) {
+    const int MT = NT * 8;
+    size_t b = 256 + static_cast<size_t>(MT) * 12 + 2u * RI * 16 * MT * 4;
+    return (b + 127) / 128 * 128;
+}
+
+// Chooses the token tile, the item size and the ring depth for a group, and fills the item fields.
+static int plan_group(wf_problem* probs, int P, GroupPlan& g, bool write_fields) {
+    int Kmax = 0, Mmax = 0;
+    for (int i = 0; i < P; ++i) {
+        Kmax = probs[i].K > Kmax ? probs[i].K : Kmax;
+        Mmax = probs[i].M > Mmax ? probs[i].M : Mmax;
+    }
+    const int sms = num_sms();
+    const int pitch = row_pitch(Kmax);
+    g.KBmax = (Kmax + 511) / 512;
+    // token tile: as many tokens as fit beside three 16-row stages
+    int NT = Mmax <= 8 ? 1 : (Mmax <= 16 ? 2 : (Mmax <= 32 ? 4 : 8));
+    for (;; NT >>= 1) {
+        const int mta = Mmax < NT * 8 ? Mmax : NT * 8;
+        const size_t need = fixed_bytes(NT, 1) + static_cast<size_t>(g.KBmax) * mta * TOK_STRIDE + 3u * 16 * pitch;
+        if (need <= SMEM_MAX || NT == 1) break;
+    }
+    g.NT = NT;
+    const int MT = NT * 8;
+    g.MTA = Mmax < MT ? Mmax : MT;
+    const size_t act = (static_cast<size_t>(g.KBmax) * g.MTA * TOK_STRIDE + 127) / 128 * 128;
+    // item size: about 32 KB per stage, smaller while there are too few items to keep every SM busy
+    int RI = 8;
+    while (RI > 1 && 16 * RI * pitch > 32 * 1024) RI >>= 1;
+    auto count_items = [&](int ri) {
+        long long t = 0;
+        for (int i = 0; i < P; ++i)
+            t += static_cast<long long>((probs[i].N + 16 * ri - 1) / (16 * ri)) * ((probs[i].M + MT - 1) / MT);
+        return t;
+    };
+    while (RI > 1 && count_items(RI) < 4LL * sms) RI >>= 1;
+    while (RI > 1 && fixed_bytes(NT, RI) + act + 2u * 16 * RI * pitch > SMEM_MAX) RI >>= 1;
+    g.RI = RI;
+    g.stage_bytes = 16 * RI * pitch;
+    g.act_off = static_cast<int>(fixed_bytes(NT, RI));
+    g.stage_off = g.act_off + static_cast<int>(act);
+    if (static_cast<size_t>(g.stage_off) + 2u * g.stage_bytes > SMEM_MAX)
+        return fail(WF_E_LIMIT, "wf_bitlinear_decode: K=%d needs more shared memory than one SM has", Kmax);
+    const long long total = count_items(RI);
+    if (total > 0x7fffffffLL) return fail(WF_E_LIMIT, "wf_bitlinear_decode: too many work items");
+    g.total_items = static_cast<int>(total);
+    g.grid = g.total_items <= 2 * sms ? g.total_items : sms;
+    const int per_cta = (g.total_items + g.grid - 1) / g.grid;
+    int stages = static_cast<int>((SMEM_MAX - g.stage_off) / g.stage_bytes);
+    if (stages > MAX_STAGES) stages = MAX_STAGES;
+    if (stages > per_cta + 1) stages = per_cta + 1 > 2 ? per_cta + 1 : 2;
+    g.stages = stages;
+    g.smem = static_cast<size_t>(g.stage_off) + static_cast<size_t>(stages) * g.stage_bytes;
+    if (write_fields) {
+        int begin = 0;
+        for (int i = 0; i < P; ++i) {
+            probs[i]._item_begin = begin;
+            probs[i]._row_items = (probs[i].N + 16 * RI - 1) / (16 * RI);
+            probs[i]._chunks = (probs[i].M + MT - 1) / MT;
+            probs[i]._reserved = 0;
+            begin += probs[i]._row_items * probs[i]._chunks;
+        }
+    }
+    return WF_OK;
+}
+
 template <int XDT, int NT, bool FOURACC>
-static int launch_decode(const DecodeParams& p, size_t smem, dim3 grid, unsigned flags, cudaStream_t st) {
+static int launch_decode(const wf_problem* dev, const wf_problem& single, const DecodeCfg& cfg, const GroupPlan& g, unsigned flags,
+                         cudaStream_t st) {
     auto kern = decode_kernel<XDT, NT, FOURACC>;
     static thread_local size_t configured = 0;  // per instantiation
-    if (smem > 48 * 1024 && smem > configured) {
-        WF_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem)));
-        configured = smem;
+    if (g.smem > 48 * 1024 && g.smem > configured) {
+        WF_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(SMEM_MAX)));
+        configured = SMEM_MAX;
     }
-    cudaLaunchConfig_t cfg = {};
-    cfg.gridDim = grid;
-    cfg.blockDim = dim3(DEC_THREADS);
-    cfg.dynamicSmemBytes = smem;
-    cfg.stream = st;
+    cudaLaunchConfig_t lc = {};
+    lc.gridDim = dim3(g.grid);
+    lc.blockDim = dim3(DEC_THREADS);
+    lc.dynamicSmemBytes = g.smem;
+    lc.stream = st;
     cudaLaunchAttribute attr[1];
     if (flags & WF_FLAG_PDL) {
         attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
         attr[0].val.programmaticStreamSerializationAllowed = 1;
-        cfg.attrs = attr;
-        cfg.numAttrs = 1;
+        lc.attrs = attr;
+        lc.numAttrs = 1;
     }
-    WF_CUDA(cudaLaunchKernelEx(&cfg, kern, p));
+    WF_CUDA(cudaLaunchKernelEx(&lc, kern, dev, single, cfg));
     return WF_OK;
 }
 
 template <int XDT>
-static int dispatch_nt(const DecodeParams& p, int NT, size_t smem, dim3 grid, unsigned flags, cudaStream_t st) {
-    switch (NT) {
-        case 1: return launch_decode<XDT, 1, true>(p, smem, grid, flags, st);
-        case 2: return launch_decode<XDT, 2, true>(p, smem, grid, flags, st);
-        case 4: return launch_decode<XDT, 4, false>(p, smem, grid, flags, st);
-        default: return launch_decode<XDT, 8, false>(p, smem, grid, flags, st);
+static int dispatch_nt(const wf_problem* dev, const wf_problem& single, const DecodeCfg& cfg, const GroupPlan& g, unsigned flags,
+                       cudaStream_t st) {
+    switch (g.NT) {
+        case 1: return launch_decode<XDT, 1, true>(dev, single, cfg, g, flags, st);
+        case 2: return launch_decode<XDT, 2, true>(dev, single, cfg, g, flags, st);
+        case 4: return launch_decode<XDT, 4, false>(dev, single, cfg, g, flags, st);
+        default: return launch_decode<XDT, 8, false>(dev, single, cfg, g, flags, st);
     }
 }
 
-constexpr size_t DEC_SMEM_BUDGET = 200 * 1024;
+static int check_problem(const char* who, const wf_problem& q);
 
-static size_t decode_smem(int NT, int RG, int KB, int MTA) {
-    const int MT = NT * 8;
-    return static_cast<size_t>(MT) * 12 + static_cast<size_t>(RG) * 16 * MT * 4 + static_cast<size_t>(KB) * MTA * TOK_STRIDE;
+static int run_group(const char* who, const wf_problem* dev, wf_problem* host, int P, bool planned, unsigned flags, void* stream) {
+    for (int i = 0; i < P; ++i) {
+        if (int rc = check_problem(who, host[i])) return rc;
+        WF_REQUIRE(host[i].x_dtype == host[0].x_dtype, "%s: all problems of a group must share x_dtype", who);
+    }
+    if (int rc = require_device()) return rc;
+    GroupPlan g;
+    if (planned) {
+        // the caller's copy on the device was planned earlier: recompute and compare
+        if (int rc = plan_group(host, P, g, false)) return rc;
+        int begin = 0;
+        for (int i = 0; i < P; ++i) {
+            const int MT = g.NT * 8;
+            const int ri = (host[i].N + 16 * g.RI - 1) / (16 * g.RI), ch = (host[i].M + MT - 1) / MT;
+            WF_REQUIRE(host[i]._item_begin == begin && host[i]._row_items == ri && host[i]._chunks == ch,
+                       "%s: problem %d was not prepared by wf_bitlinear_decode_plan (or was changed afterwards)", who, i);
+            begin += ri * ch;
+        }
+    } else {
+        if (int rc = plan_group(host, P, g, true)) return rc;
+    }
+    DecodeCfg cfg;
+    cfg.P = P; cfg.total_items = g.total_items; cfg.RI = g.RI; cfg.KBmax = g.KBmax; cfg.MTA = g.MTA; cfg.stages = g.stages;
+    cfg.stage_bytes = g.stage_bytes; cfg.act_off = g.act_off; cfg.stage_off = g.stage_off;
+    cudaStream_t st = static_cast<cudaStream_t>(stream);
+    switch (host[0].x_dtype) {
+        case WF_F32: return dispatch_nt<WF_F32>(dev, host[0], cfg, g, flags, st);
+        case WF_BF16: return dispatch_nt<WF_BF16>(dev, host[0], cfg, g, flags, st);
+        case WF_F16: return dispatch_nt<WF_F16>(dev, host[0], cfg, g, flags, st);
+        default: return dispatch_nt<WF_I8>(dev, host[0], cfg, g, flags, st);
+    }
 }
 
 }  // namespace wf
 
 using namespace wf;
 
-// Shared argument validation of the two contraction entry points.
+// Shared argument validation of the contraction entry points.
 int wf_check_linear_args(const char* who, const void* x, int x_dtype, int64_t ldx, const float* x_scale, const uint8_t* codes,
                          int layout, const void* bias, int bias_dtype, void* y, int y_dtype, int64_t ldy, int64_t M, int64_t N,
                          int64_t K) {
@@ -381,6 +580,11 @@ int wf_check_linear_args(const char* who, const void* x, int x_dtype, int64_t ld
     return WF_OK;
 }
 
+static int wf::check_problem(const char* who, const wf_problem& q) {
+    return wf_check_linear_args(who, q.x, q.x_dtype, q.ldx, q.x_scale, q.codes, q.layout, q.bias, q.bias_dtype, q.y, q.y_dtype,
+                                q.ldy, q.M, q.N, q.K);
+}
+
 extern "C" int wf_bitlinear_decode(const void* x, int x_dtype, int64_t ldx, const float* x_scale, const uint8_t* codes,
                                    int layout, const float* w_scale, float w_scale_host, const void* bias, int bias_dtype,
                                    void* y, int y_dtype, int64_t ldy, int32_t* acc_out, int64_t M, int64_t N, int64_t K,
@@ -388,35 +592,38 @@ extern "C" int wf_bitlinear_decode(const void* x, int x_dtype, int64_t ldx, cons
     if (int rc = wf_check_linear_args("wf_bitlinear_decode", x, x_dtype, ldx, x_scale, codes, layout, bias, bias_dtype, y,
                                       y_dtype, ldy, M, N, K))
         return rc;
+    wf_problem p = {};
+    p.x = x; p.x_scale = x_scale; p.codes = codes; p.w_scale = w_scale; p.bias = bias; p.y = y; p.acc_out = acc_out;
+    p.ldx = ldx; p.ldy = ldy; p.M = static_cast<int>(M); p.N = static_cast<int>(N); p.K = static_cast<int>(K);
+    p.x_dtype = x_dtype; p.y_dtype = y_dtype; p.bias_dtype = bias_dtype; p.layout = layout;
+    p.w_scale_host = w_scale_host; p.eps = eps;
+    return run_group("wf_bitlinear_decode", nullptr, &p, 1, false, flags, stream);
+}
+
+extern "C" int wf_bitlinear_decode_plan(wf_problem* host_problems, int P) {
+    WF_REQUIRE(host_problems && P > 0, "wf_bitlinear_decode_plan: empty group");
+    for (int i = 0; i < P; ++i)
+        if (int rc = check_problem("wf_bitlinear_decode_plan", host_problems[i])) return rc;
     if (int rc = require_device()) return rc;
+    GroupPlan g;
+    return plan_group(host_problems, P, g, true);
+}
 
-    DecodeParams p;
-    p.x = x; p.ldx = ldx; p.x_scale = x_scale; p.codes = codes; p.w_scale = w_scale; p.w_scale_host = w_scale_host;
-    p.bias = bias; p.bias_dtype = bias_dtype; p.y = y; p.y_dtype = y_dtype; p.ldy = ldy; p.acc_out = acc_out;
-    p.M = static_cast<int>(M); p.N = static_cast<int>(N); p.K = static_cast<int>(K);
-    p.KB = static_cast<int>((K + 511) / 512);
-    p.layout = layout; p.eps = eps;
+extern "C" int wf_bitlinear_decode_grouped(const wf_problem* dev_problems, const wf_problem* host_problems, int P, unsigned flags,
+                                           void* stream) {
+    WF_REQUIRE(dev_problems && host_problems && P > 0, "wf_bitlinear_decode_grouped: empty group");
+    return run_group("wf_bitlinear_decode_grouped", dev_problems, const_cast<wf_problem*>(host_problems), P, true, flags, stream);
+}
 
-    const int row_tiles = static_cast<int>((N + 15) / 16);
-    int RG = row_tiles <= 320 ? 1 : (row_tiles <= 640 ? 2 : (row_tiles <= 1280 ? 4 : 8));
-    while (RG < 8 && 8 / RG > p.KB && row_tiles >= 2 * RG) RG <<= 1;  // few k-blocks: give idle warps more rows
-    p.RG = RG;
-
-    // tokens per CTA: as many as fit in shared memory, in multiples of 8 up to 64
-    int NT = M <= 8 ? 1 : (M <= 16 ? 2 : (M <= 32 ? 4 : 8));
-    while (NT > 1 && decode_smem(NT, RG, p.KB, static_cast<int>(M < NT * 8 ? M : NT * 8)) > DEC_SMEM_BUDGET) NT >>= 1;
-    const int MT = NT * 8;
-    p.MTA = static_cast<int>(M < MT ? M : MT);
-    const size_t smem = decode_smem(NT, RG, p.KB, p.MTA);
-    if (smem > 227 * 1024) return fail(WF_E_LIMIT, "wf_bitlinear_decode: K=%lld needs %zu bytes of shared memory", (long long)K, smem);
-
-    dim3 grid((row_tiles + RG - 1) / RG, static_cast<unsigned>((M + MT - 1) / MT));
-    if (grid.y > 65535) return fail(WF_E_LIMIT, "wf_bitlinear_decode: too many token groups (%u); use wf_bitlinear_prefill", grid.y);
-    cudaStream_t st = static_cast<cudaStream_t>(stream);
-    switch (x_dtype) {
-        case WF_F32: return dispatch_nt<WF_F32>(p, NT, smem, grid, flags, st);
-        case WF_BF16: return dispatch_nt<WF_BF16>(p, NT, smem, grid, flags, st);
-        case WF_F16: return dispatch_nt<WF_F16>(p, NT, smem, grid, flags, st);
-        default: return dispatch_nt<WF_I8>(p, NT, smem, grid, flags, st);
+extern "C" int wf_device_status(void) {
+    if (int rc = require_device()) return rc;
+    WF_CUDA(cudaDeviceSynchronize());
+    int v = 0;
+    WF_CUDA(cudaMemcpyFromSymbol(&v, g_decode_status, sizeof(int)));
+    if (v) {
+        int zero = 0;
+        WF_CUDA(cudaMemcpyToSymbol(g_decode_status, &zero, sizeof(int)));
+        return fail(v, "a bounded wait inside a decode kernel ran out; the outputs of that launch are invalid");
     }
+    return WF_OK;
 }

@@ -206,6 +206,75 @@ def bitlinear(x: torch.Tensor, codes: torch.Tensor, w_scale, bias: Optional[torc
     return (y, acc) if want_acc else y
 
 
+class DecodeGroup:
+    """Several independent BitLinear problems run as one persistent kernel (q/k/v, gate/up, or a
+    stack of layers).  Build once, `run()` any number of times; the tensors given at construction
+    are read / written in place on every run.
+
+    problems: iterable of dicts with keys x, codes, w_scale and optionally bias, out, out_dtype,
+    layout, x_scale, eps, want_acc.  All x must share a dtype.
+    """
+
+    def __init__(self, problems):
+        import ctypes as C
+
+        problems = list(problems)
+        if not problems:
+            raise ValueError("empty group")
+        self._keep = []
+        self.outputs, self.accs = [], []
+        arr = (L.Problem * len(problems))()
+        dev = problems[0]["x"].device
+        for i, pr in enumerate(problems):
+            x, codes, w_scale = pr["x"], pr["codes"], pr["w_scale"]
+            bias, x_scale = pr.get("bias"), pr.get("x_scale")
+            _need_cuda(x, codes, bias, x_scale)
+            k = x.shape[-1]
+            x2 = x.reshape(-1, k)
+            if x2.stride(1) != 1 or not codes.is_contiguous():
+                raise ValueError("DecodeGroup needs x with unit inner stride and contiguous codes")
+            m, n = x2.shape[0], codes.shape[0]
+            out_dtype = pr.get("out_dtype") or (torch.float32 if x.dtype == torch.int8 else x.dtype)
+            y = pr.get("out")
+            if y is None:
+                y = torch.empty((m, n), dtype=out_dtype, device=dev)
+            acc = torch.empty((m, n), dtype=torch.int32, device=dev) if pr.get("want_acc") else None
+            q = arr[i]
+            q.x, q.x_scale, q.codes = x2.data_ptr(), _ptr(x_scale), codes.data_ptr()
+            if isinstance(w_scale, torch.Tensor):
+                q.w_scale, q.w_scale_host = w_scale.data_ptr(), 0.0
+            else:
+                q.w_scale, q.w_scale_host = None, float(w_scale)
+            q.bias, q.y, q.acc_out = _ptr(bias), y.data_ptr(), _ptr(acc)
+            q.ldx, q.ldy, q.M, q.N, q.K = x2.stride(0), y.stride(0), m, n, k
+            q.x_dtype, q.y_dtype = _DT[x2.dtype], _DT[y.dtype]
+            q.bias_dtype = _DT[bias.dtype] if bias is not None else 0
+            q.layout, q.eps = pr.get("layout", L.LAYOUT_WF16), pr.get("eps", 1e-5)
+            self._keep += [x2, codes, w_scale, bias, x_scale, y, acc]
+            self.outputs.append(y.reshape(*x.shape[:-1], n))
+            self.accs.append(acc)
+        self.device = dev
+        self._host = arr
+        with torch.cuda.device(dev):
+            L.check(L.lib().wf_bitlinear_decode_plan(C.addressof(arr), len(problems)), "wf_bitlinear_decode_plan")
+        raw = bytes(arr)
+        self._dev = torch.frombuffer(bytearray(raw), dtype=torch.uint8).to(dev)
+        self.count = len(problems)
+
+    def run(self, pdl: bool = False):
+        import ctypes as C
+
+        with torch.cuda.device(self.device):
+            L.check(L.lib().wf_bitlinear_decode_grouped(self._dev.data_ptr(), C.addressof(self._host), self.count,
+                                                        L.FLAG_PDL if pdl else 0, _stream()), "wf_bitlinear_decode_grouped")
+        return self.outputs
+
+
+def device_status() -> None:
+    """Raises when a bounded wait inside a decode kernel ran out since the last check."""
+    L.check(L.lib().wf_device_status(), "wf_device_status")
+
+
 # --------------------------------------------------------------------------
 # operator API of sgl_kernel.quantization.bitnet (same names, same argument meaning)
 # --------------------------------------------------------------------------
