@@ -384,3 +384,31 @@ def test_grouped_large_stack(wf, oracle_c):
     for acc, acc_o in zip(grp.accs, want):
         assert np.array_equal(acc.cpu().numpy(), acc_o)
     wf.device_status()
+
+
+@pytest.mark.parametrize("m,dt", [(1, "bf16"), (4, "f32"), (16, "bf16"), (40, "bf16")])
+def test_grouped_throughput_mode_equals_single_calls(wf, oracle_c, m, dt):
+    """Groups with thousands of 16-row items take the form of the kernel in which every warp consumes
+    its own items; accumulators and outputs must equal those of single calls (and the oracle's)."""
+    L = wf._lib
+    rng = np.random.default_rng(500 + m)
+    shapes = [(4000, 1024), (6912, 2560), (2560, 6912), (3000, 576), (5000, 640), (6000, 1024), (6912, 1280), (4096, 2048)]
+    probs, singles = [], []
+    for i, (n, k) in enumerate(shapes):
+        lay = L.LAYOUT_I2S if (i % 2 and k % 128 == 0) else L.LAYOUT_WF16
+        t = torch.from_numpy(rng.integers(-1, 2, size=(n, k)).astype(np.int8)).to(DEV)
+        codes = wf.pack_codes(t, lay)
+        x = gi.with_outliers(torch.from_numpy(rng.standard_normal((m, k)).astype(np.float32)), seed=i).to(TDT[dt]).to(DEV)
+        bias = torch.from_numpy(rng.standard_normal(n).astype(np.float32)).to(DEV) if i % 3 == 0 else None
+        probs.append(dict(x=x, codes=codes, w_scale=0.0173, bias=bias, layout=lay, out_dtype=torch.float32, want_acc=True))
+        singles.append(wf.bitlinear(x, codes, 0.0173, bias=bias, layout=lay, out_dtype=torch.float32, want_acc=True,
+                                    path="decode"))
+        if i == 0:  # one of them against the CPU oracle directly
+            q, s = oracle_c.act_quant(x.float().cpu().numpy(), {"f32": 0, "bf16": 1}[dt])
+            assert np.array_equal(singles[0][1].cpu().numpy(), oracle_c.int_gemm(q, t.cpu().numpy()))
+    grp = wf.DecodeGroup(probs)
+    outs = grp.run()
+    for (y1, a1), y2, a2 in zip(singles, outs, grp.accs):
+        assert torch.equal(a1, a2)
+        assert torch.equal(y1, y2)
+    wf.device_status()

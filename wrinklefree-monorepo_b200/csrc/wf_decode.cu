@@ -35,7 +35,7 @@ namespace wf {
 constexpr int DEC_CONSUMERS = 256;               // 8 consumer warps
 constexpr int DEC_THREADS = DEC_CONSUMERS + 32;  // + 1 producer warp
 constexpr int TOK_STRIDE = 576;  // bytes of shared memory per (k-block, token): 512 + 64 skew (conflict-free 128-bit reads)
-constexpr int MAX_STAGES = 8;
+constexpr int MAX_STAGES = 16;
 constexpr unsigned SPIN_LIMIT = 1u << 20;
 
 __device__ int g_decode_status = 0;
@@ -49,6 +49,7 @@ struct DecodeCfg {
     int stages;
     int stage_bytes;  // bytes per stage (16*RI rows at the pitch of the largest K)
     int act_off, stage_off;  // byte offsets inside dynamic shared memory
+    int decoupled;    // 1: every consumer warp owns whole 16-row items (RI == 1); 0: the 8 warps share each item
 };
 
 __device__ __forceinline__ uint32_t smem_u32(const void* p) { return static_cast<uint32_t>(__cvta_generic_to_shared(p)); }
@@ -264,11 +265,11 @@ __global__ void __launch_bounds__(DEC_THREADS, 1)
     constexpr int MT = NT * 8;
     uint64_t* full = reinterpret_cast<uint64_t*>(smem);
     uint64_t* empty = full + MAX_STAGES;
-    volatile int* poisoned = reinterpret_cast<volatile int*>(smem + 128);
-    float* s_inv = reinterpret_cast<float*>(smem + 256);
-    int* s_rowsum = reinterpret_cast<int*>(smem + 256 + MT * 4);
-    unsigned* s_maxbits = reinterpret_cast<unsigned*>(smem + 256 + MT * 8);
-    int* s_red = reinterpret_cast<int*>(smem + 256 + MT * 12);  // two buffers of RI*16*MT
+    volatile int* poisoned = reinterpret_cast<volatile int*>(smem + 256);
+    float* s_inv = reinterpret_cast<float*>(smem + 384);
+    int* s_rowsum = reinterpret_cast<int*>(smem + 384 + MT * 4);
+    unsigned* s_maxbits = reinterpret_cast<unsigned*>(smem + 384 + MT * 8);
+    int* s_red = reinterpret_cast<int*>(smem + 384 + MT * 12);  // two buffers of RI*16*MT
     uint8_t* s_act = smem + cfg.act_off;
     uint8_t* s_stage = smem + cfg.stage_off;
     const wf_problem* probs = dev_problems ? dev_problems : &single;
@@ -281,7 +282,7 @@ __global__ void __launch_bounds__(DEC_THREADS, 1)
     if (tid == 0) {
         for (int s = 0; s < cfg.stages; ++s) {
             mbar_init(&full[s], 1);
-            mbar_init(&empty[s], DEC_CONSUMERS / 32);
+            mbar_init(&empty[s], cfg.decoupled ? 1 : DEC_CONSUMERS / 32);
         }
         *poisoned = 0;
         asm volatile("fence.mbarrier_init.release.cluster;\n" ::: "memory");
@@ -321,6 +322,69 @@ __global__ void __launch_bounds__(DEC_THREADS, 1)
     int cur_p = -1, cur_chunk = -1, m0 = 0, m_valid = 0;
     // x may be produced by the previous kernel of the stream
     asm volatile("griddepcontrol.wait;\n" ::: "memory");
+
+    if (cfg.decoupled) {
+        // Every warp consumes whole items (16 rows over all of K) on its own: no CTA-wide barrier and no shared
+        // atomics except where the CTA moves on to another (problem, token pass).
+        int it = beg;
+        while (it < end) {
+            int pi, chunk, ritem;
+            locate_item(probs, cfg.P, it, pi, chunk, ritem);
+            const wf_problem& p = probs[pi];
+            const int seg_end = min(end, p._item_begin + (chunk + 1) * p._row_items);
+            consumer_sync();  // every warp is done with the previous pass
+            m0 = chunk * MT;
+            m_valid = min(MT, p.M - m0);
+            quantize_tokens<XDT>(p, cfg.MTA, m0, m_valid, s_act, s_inv, s_rowsum, s_maxbits);
+            const int KB = (p.K + 511) >> 9;
+            const int pitch = row_pitch(p.K);
+            const float s_w = p.w_scale ? __ldg(p.w_scale) : p.w_scale_host;
+            int j = it + ((warp - (it - beg)) & 7);  // first item of this warp in the segment: (j - beg) % 8 == warp
+            for (; j < seg_end; j += 8) {
+                const int n = j - beg, stage = n % cfg.stages;
+                mbar_wait(&full[stage], (n / cfg.stages) & 1, poisoned);
+                int acc[NT][FOURACC ? 4 : 1][4];
+#pragma unroll
+                for (int a = 0; a < NT; ++a)
+#pragma unroll
+                    for (int b = 0; b < (FOURACC ? 4 : 1); ++b)
+#pragma unroll
+                        for (int c = 0; c < 4; ++c) acc[a][b][c] = 0;
+                const uint8_t* w_r0 = s_stage + static_cast<size_t>(stage) * cfg.stage_bytes + g * pitch;
+                const uint8_t* w_r1 = w_r0 + 8 * pitch;
+#pragma unroll 1
+                for (int kb = 0; kb < KB; ++kb)
+                    compute_unit<NT, FOURACC>(w_r0 + kb * 128, w_r1 + kb * 128, s_act + kb * cfg.MTA * TOK_STRIDE, m_valid, g, t, acc);
+                __syncwarp();
+                if (lane == 0) mbar_arrive(&empty[stage]);
+                // epilogue straight from the accumulators: lane holds rows g, g+8 x tokens 2t, 2t+1 of every token tile
+                const int row_a = (ritem + (j - it)) * 16 + g, row_b = row_a + 8;
+#pragma unroll
+                for (int nt = 0; nt < NT; ++nt) {
+#pragma unroll
+                    for (int c = 0; c < 4; ++c) {
+                        int v;
+                        if constexpr (FOURACC)
+                            v = acc[nt][0][c] + (acc[nt][1][c] >> 2) + (acc[nt][2][c] >> 4) + (acc[nt][3][c] >> 6);
+                        else
+                            v = acc[nt][0][c];
+                        const int tok = nt * 8 + 2 * t + (c & 1);
+                        const int nrow = (c & 2) ? row_b : row_a;
+                        if (tok < m_valid && nrow < p.N) {
+                            const int a = v - s_rowsum[tok];
+                            float out = rescale(a, s_inv[tok], s_w);
+                            if (p.bias) out = __fadd_rn(out, load1_rt(p.bias, p.bias_dtype, nrow));
+                            const int64_t m = m0 + tok;
+                            store1_rt(p.y, p.y_dtype, m * p.ldy + nrow, out);
+                            if (p.acc_out) p.acc_out[m * p.N + nrow] = a;
+                        }
+                    }
+                }
+            }
+            it = seg_end;
+        }
+        return;
+    }
 
     for (int it = beg, n = 0; it < end; ++it, ++n) {
         int pi, chunk, ritem;
@@ -398,7 +462,7 @@ __global__ void __launch_bounds__(DEC_THREADS, 1)
 
 // ------------------------------------------------------------------ host side
 struct GroupPlan {
-    int NT, RI, KBmax, MTA, stages, stage_bytes, act_off, stage_off, total_items, grid;
+    int NT, RI, KBmax, MTA, stages, stage_bytes, act_off, stage_off, total_items, grid, decoupled;
     size_t smem;
 };
 
@@ -415,9 +479,15 @@ static int num_sms() {
     return cached;
 }
 
+static long long count_items16(const wf_problem* probs, int P, int MT) {
+    long long t = 0;
+    for (int i = 0; i < P; ++i) t += static_cast<long long>((probs[i].N + 15) / 16) * ((probs[i].M + MT - 1) / MT);
+    return t;
+}
+
 static size_t fixed_bytes(int NT, int RI) {
     const int MT = NT * 8;
-    size_t b = 256 + static_cast<size_t>(MT) * 12 + 2u * RI * 16 * MT * 4;
+    size_t b = 384 + static_cast<size_t>(MT) * 12 + 2u * RI * 16 * MT * 4;
     return (b + 127) / 128 * 128;
 }
 
@@ -442,8 +512,11 @@ static int plan_group(wf_problem* probs, int P, GroupPlan& g, bool write_fields)
     const int MT = NT * 8;
     g.MTA = Mmax < MT ? Mmax : MT;
     const size_t act = (static_cast<size_t>(g.KBmax) * g.MTA * TOK_STRIDE + 127) / 128 * 128;
+    // Enough 16-row items to give every consumer warp of every SM several of them: the warps work on their
+    // own items.  Otherwise (a single small layer) the 8 warps of a CTA share each item and split K.
+    g.decoupled = count_items16(probs, P, MT) >= 16LL * sms && fixed_bytes(NT, 1) + act + 4u * 16 * pitch <= SMEM_MAX;
     // item size: about 32 KB per stage, smaller while there are too few items to keep every SM busy
-    int RI = 8;
+    int RI = g.decoupled ? 1 : 8;
     while (RI > 1 && 16 * RI * pitch > 32 * 1024) RI >>= 1;
     auto count_items = [&](int ri) {
         long long t = 0;
@@ -467,6 +540,8 @@ static int plan_group(wf_problem* probs, int P, GroupPlan& g, bool write_fields)
     int stages = static_cast<int>((SMEM_MAX - g.stage_off) / g.stage_bytes);
     if (stages > MAX_STAGES) stages = MAX_STAGES;
     if (stages > per_cta + 1) stages = per_cta + 1 > 2 ? per_cta + 1 : 2;
+    if (g.decoupled && static_cast<size_t>(stages) * g.stage_bytes > 160 * 1024)  // bytes in flight per SM: enough is enough
+        stages = static_cast<int>(160 * 1024 / g.stage_bytes) > 4 ? static_cast<int>(160 * 1024 / g.stage_bytes) : 4;
     g.stages = stages;
     g.smem = static_cast<size_t>(g.stage_off) + static_cast<size_t>(stages) * g.stage_bytes;
     if (write_fields) {
@@ -543,7 +618,7 @@ static int run_group(const char* who, const wf_problem* dev, wf_problem* host, i
     }
     DecodeCfg cfg;
     cfg.P = P; cfg.total_items = g.total_items; cfg.RI = g.RI; cfg.KBmax = g.KBmax; cfg.MTA = g.MTA; cfg.stages = g.stages;
-    cfg.stage_bytes = g.stage_bytes; cfg.act_off = g.act_off; cfg.stage_off = g.stage_off;
+    cfg.stage_bytes = g.stage_bytes; cfg.act_off = g.act_off; cfg.stage_off = g.stage_off; cfg.decoupled = g.decoupled;
     cudaStream_t st = static_cast<cudaStream_t>(stream);
     switch (host[0].x_dtype) {
         case WF_F32: return dispatch_nt<WF_F32>(dev, host[0], cfg, g, flags, st);
