@@ -325,7 +325,8 @@ __global__ void __launch_bounds__(DEC_THREADS, 1)
 
     if (cfg.decoupled) {
         // Every warp consumes whole items (16 rows over all of K) on its own: no CTA-wide barrier and no shared
-        // atomics except where the CTA moves on to another (problem, token pass).
+        // atomics except where the CTA moves on to another (problem, token pass).  With fewer than 8 stages only
+        // that many warps consume.
         int it = beg;
         while (it < end) {
             int pi, chunk, ritem;
@@ -339,8 +340,10 @@ __global__ void __launch_bounds__(DEC_THREADS, 1)
             const int KB = (p.K + 511) >> 9;
             const int pitch = row_pitch(p.K);
             const float s_w = p.w_scale ? __ldg(p.w_scale) : p.w_scale_host;
-            int j = it + ((warp - (it - beg)) & 7);  // first item of this warp in the segment: (j - beg) % 8 == warp
-            for (; j < seg_end; j += 8) {
+            // A stage is always consumed by the same warp, (stage % 8), so that the rounds of a stage are waited
+            // for in order (a parity wait cannot tell round r from round r + 2).
+            for (int j = it; j < seg_end; ++j) {
+                if ((((j - beg) % cfg.stages) & 7) != warp) continue;
                 const int n = j - beg, stage = n % cfg.stages;
                 mbar_wait(&full[stage], (n / cfg.stages) & 1, poisoned);
                 int acc[NT][FOURACC ? 4 : 1][4];
@@ -539,9 +542,8 @@ static int plan_group(wf_problem* probs, int P, GroupPlan& g, bool write_fields)
     const int per_cta = (g.total_items + g.grid - 1) / g.grid;
     int stages = static_cast<int>((SMEM_MAX - g.stage_off) / g.stage_bytes);
     if (stages > MAX_STAGES) stages = MAX_STAGES;
-    if (stages > per_cta + 1) stages = per_cta + 1 > 2 ? per_cta + 1 : 2;
-    if (g.decoupled && static_cast<size_t>(stages) * g.stage_bytes > 160 * 1024)  // bytes in flight per SM: enough is enough
-        stages = static_cast<int>(160 * 1024 / g.stage_bytes) > 4 ? static_cast<int>(160 * 1024 / g.stage_bytes) : 4;
+    if (!g.decoupled && stages > per_cta + 1) stages = per_cta + 1 > 2 ? per_cta + 1 : 2;
+    if (g.decoupled) stages = stages >= 16 ? 16 : (stages >= 8 ? 8 : stages);  // one owning warp per stage
     g.stages = stages;
     g.smem = static_cast<size_t>(g.stage_off) + static_cast<size_t>(stages) * g.stage_bytes;
     if (write_fields) {
