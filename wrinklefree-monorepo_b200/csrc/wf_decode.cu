@@ -296,22 +296,36 @@ __global__ void __launch_bounds__(DEC_THREADS, 1)
 
     if (warp == DEC_CONSUMERS / 32) {
         // ---------------- producer: weights do not depend on the previous kernel, stream them right away
+        // The item list is walked incrementally: one search at the start, then only counters.
+        int pi, chunk, ritem;
+        locate_item(probs, cfg.P, beg, pi, chunk, ritem);
+        const uint8_t* codes = probs[pi].codes;
+        int N = probs[pi].N, row_items = probs[pi]._row_items, chunks = probs[pi]._chunks;
+        unsigned rowbytes = static_cast<unsigned>(probs[pi].K >> 2);
+        int pitch = row_pitch(probs[pi].K);
         for (int it = beg, n = 0; it < end; ++it, ++n) {
             const int stage = n % cfg.stages;
             if (n >= cfg.stages) mbar_wait(&empty[stage], ((n / cfg.stages) - 1) & 1, poisoned);
-            int pi, chunk, ritem;
-            locate_item(probs, cfg.P, it, pi, chunk, ritem);
-            const wf_problem& p = probs[pi];
             const int r0 = ritem * rows_item;
-            const int nrows = min(rows_item, p.N - r0);
-            const unsigned rowbytes = static_cast<unsigned>(p.K >> 2);
-            const int pitch = row_pitch(p.K);
+            const int nrows = min(rows_item, N - r0);
             if (lane == 0) mbar_expect_tx(&full[stage], static_cast<unsigned>(nrows) * rowbytes);
             __syncwarp();
             uint8_t* dst = s_stage + static_cast<size_t>(stage) * cfg.stage_bytes;
-            const uint8_t* src = p.codes + static_cast<int64_t>(r0) * rowbytes;
+            const uint8_t* src = codes + static_cast<int64_t>(r0) * rowbytes;
             for (int r = lane; r < nrows; r += 32)
                 bulk_copy_g2s(dst + r * pitch, src + static_cast<int64_t>(r) * rowbytes, rowbytes, &full[stage]);
+            if (++ritem == row_items) {
+                ritem = 0;
+                if (++chunk == chunks) {
+                    chunk = 0;
+                    if (++pi < cfg.P) {
+                        codes = probs[pi].codes;
+                        N = probs[pi].N; row_items = probs[pi]._row_items; chunks = probs[pi]._chunks;
+                        rowbytes = static_cast<unsigned>(probs[pi].K >> 2);
+                        pitch = row_pitch(probs[pi].K);
+                    }
+                }
+            }
         }
         return;
     }
