@@ -14,7 +14,7 @@
 //
 // Inside an item a "unit" is 16 rows x 512 weights of K, handled by one warp:
 // each lane reads 2 x 16 bytes of rows g and g+8 from the stage.  K is split
-// over 8/RI warps per row tile; partial sums meet in a shared-memory int32 tile.
+// over 16/RI warps per row tile; partial sums meet in a shared-memory int32 tile.
 //
 // Expansion.  In both kernel layouts, (word >> 2p) & 0x03030303 yields four
 // weights that are consecutive in K, i.e. the partner of one 32-bit word of int8
@@ -32,7 +32,8 @@
 
 namespace wf {
 
-constexpr int DEC_CONSUMERS = 256;               // 8 consumer warps
+constexpr int DEC_CONSUMERS = 512;               // 16 consumer warps
+constexpr int NW = DEC_CONSUMERS / 32;
 constexpr int DEC_THREADS = DEC_CONSUMERS + 32;  // + 1 producer warp
 constexpr int TOK_STRIDE = 576;  // bytes of shared memory per (k-block, token): 512 + 64 skew (conflict-free 128-bit reads)
 constexpr int MAX_STAGES = 16;
@@ -49,7 +50,7 @@ struct DecodeCfg {
     int stages;
     int stage_bytes;  // bytes per stage (16*RI rows at the pitch of the largest K)
     int act_off, stage_off;  // byte offsets inside dynamic shared memory
-    int decoupled;    // 1: every consumer warp owns whole 16-row items (RI == 1); 0: the 8 warps share each item
+    int decoupled;    // 1: every consumer warp owns whole 16-row items (RI == 1); 0: the 16 warps share each item
 };
 
 __device__ __forceinline__ uint32_t smem_u32(const void* p) { return static_cast<uint32_t>(__cvta_generic_to_shared(p)); }
@@ -332,7 +333,7 @@ __global__ void __launch_bounds__(DEC_THREADS, 1)
 
     // ---------------- consumers
     const int g = lane >> 2, t = lane & 3;
-    const int rt_local = warp % cfg.RI, ks = warp / cfg.RI, KS = (DEC_CONSUMERS / 32) / cfg.RI;
+    const int rt_local = warp % cfg.RI, ks = warp / cfg.RI, KS = NW / cfg.RI;
     int cur_p = -1, cur_chunk = -1, m0 = 0, m_valid = 0;
     // x may be produced by the previous kernel of the stream
     asm volatile("griddepcontrol.wait;\n" ::: "memory");
@@ -354,12 +355,21 @@ __global__ void __launch_bounds__(DEC_THREADS, 1)
             const int KB = (p.K + 511) >> 9;
             const int pitch = row_pitch(p.K);
             const float s_w = p.w_scale ? __ldg(p.w_scale) : p.w_scale_host;
-            // A stage is always consumed by the same warp, (stage % 8), so that the rounds of a stage are waited
+            // the fields of the problem that the epilogue needs, read once per pass
+            void* const y = p.y;
+            const void* const bias = p.bias;
+            int32_t* const acc_out = p.acc_out;
+            const int64_t ldy = p.ldy;
+            const int N = p.N, y_dtype = p.y_dtype, bias_dtype = p.bias_dtype;
+            // A stage is always consumed by the same warp (stage == warp), so that the rounds of a stage are waited
             // for in order (a parity wait cannot tell round r from round r + 2).
-            for (int j = it; j < seg_end; ++j) {
-                if ((((j - beg) % cfg.stages) & 7) != warp) continue;
-                const int n = j - beg, stage = n % cfg.stages;
-                mbar_wait(&full[stage], (n / cfg.stages) & 1, poisoned);
+            const int S = cfg.stages;
+            int n = it - beg;
+            n += (warp - n % S + S) % S;  // first local item index >= it - beg with n % S == warp
+            if (warp >= S) n = seg_end - beg;  // more warps than stages: the rest only help to quantize
+            for (; n < seg_end - beg; n += S) {
+                const int j = n + beg, stage = warp;
+                mbar_wait(&full[stage], (n / S) & 1, poisoned);
                 int acc[NT][FOURACC ? 4 : 1][4];
 #pragma unroll
                 for (int a = 0; a < NT; ++a)
@@ -387,13 +397,13 @@ __global__ void __launch_bounds__(DEC_THREADS, 1)
                             v = acc[nt][0][c];
                         const int tok = nt * 8 + 2 * t + (c & 1);
                         const int nrow = (c & 2) ? row_b : row_a;
-                        if (tok < m_valid && nrow < p.N) {
+                        if (tok < m_valid && nrow < N) {
                             const int a = v - s_rowsum[tok];
                             float out = rescale(a, s_inv[tok], s_w);
-                            if (p.bias) out = __fadd_rn(out, load1_rt(p.bias, p.bias_dtype, nrow));
+                            if (bias) out = __fadd_rn(out, load1_rt(bias, bias_dtype, nrow));
                             const int64_t m = m0 + tok;
-                            store1_rt(p.y, p.y_dtype, m * p.ldy + nrow, out);
-                            if (p.acc_out) p.acc_out[m * p.N + nrow] = a;
+                            store1_rt(y, y_dtype, m * ldy + nrow, out);
+                            if (acc_out) acc_out[m * N + nrow] = a;
                         }
                     }
                 }
@@ -530,8 +540,8 @@ static int plan_group(wf_problem* probs, int P, GroupPlan& g, bool write_fields)
     g.MTA = Mmax < MT ? Mmax : MT;
     const size_t act = (static_cast<size_t>(g.KBmax) * g.MTA * TOK_STRIDE + 127) / 128 * 128;
     // Enough 16-row items to give every consumer warp of every SM several of them: the warps work on their
-    // own items.  Otherwise (a single small layer) the 8 warps of a CTA share each item and split K.
-    g.decoupled = count_items16(probs, P, MT) >= 16LL * sms && fixed_bytes(NT, 1) + act + 4u * 16 * pitch <= SMEM_MAX;
+    // own items.  Otherwise (a single small layer) the 16 warps of a CTA share each item and split K.
+    g.decoupled = count_items16(probs, P, MT) >= 32LL * sms && fixed_bytes(NT, 1) + act + 4u * 16 * pitch <= SMEM_MAX;
     // item size: about 32 KB per stage, smaller while there are too few items to keep every SM busy
     int RI = g.decoupled ? 1 : 8;
     while (RI > 1 && 16 * RI * pitch > 32 * 1024) RI >>= 1;
@@ -557,7 +567,7 @@ static int plan_group(wf_problem* probs, int P, GroupPlan& g, bool write_fields)
     int stages = static_cast<int>((SMEM_MAX - g.stage_off) / g.stage_bytes);
     if (stages > MAX_STAGES) stages = MAX_STAGES;
     if (!g.decoupled && stages > per_cta + 1) stages = per_cta + 1 > 2 ? per_cta + 1 : 2;
-    if (g.decoupled) stages = stages >= 16 ? 16 : (stages >= 8 ? 8 : stages);  // one owning warp per stage
+    if (g.decoupled && stages > NW) stages = NW;  // one owning warp per stage
     g.stages = stages;
     g.smem = static_cast<size_t>(g.stage_off) + static_cast<size_t>(stages) * g.stage_bytes;
     if (write_fields) {
