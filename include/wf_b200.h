@@ -140,11 +140,17 @@ int wf_bitlinear_decode(const void* x, int x_dtype, int64_t ldx, const float* x_
  *
  * Fields have the meaning of the wf_bitlinear_decode arguments of the same name.  All problems of a group
  * share x_dtype.  The fields starting with an underscore are filled by wf_bitlinear_decode_plan.
+ * The struct is 384 bytes and both copies must start on a 64-byte boundary (it embeds TMA descriptors).
  * Use: fill a host array, call wf_bitlinear_decode_plan on it, copy it unchanged to device memory
  * (it must stay there while the kernel runs; it may be reused for any number of launches), then call
  * wf_bitlinear_decode_grouped with both copies.
  */
-typedef struct wf_problem {
+#if defined(__GNUC__) || defined(__clang__) || defined(__CUDACC__)
+#define WF_ALIGN64 __attribute__((aligned(64)))
+#else
+#define WF_ALIGN64 __declspec(align(64))
+#endif
+typedef struct WF_ALIGN64 wf_problem {
     const void* x;
     const float* x_scale;
     const uint8_t* codes;
@@ -156,7 +162,9 @@ typedef struct wf_problem {
     int32_t M, N, K;
     int32_t x_dtype, y_dtype, bias_dtype, layout;
     float w_scale_host, eps;
-    int32_t _item_begin, _row_items, _chunks, _reserved;
+    int32_t _item_begin, _row_items, _chunks, _kb_full, _tail_bytes; /* 128 bytes up to here */
+    uint64_t _tmap_main[16]; /* TMA descriptor: [K/512 blocks][N rows][128 bytes] view of codes */
+    uint64_t _tmap_tail[16]; /* TMA descriptor of the last, partial 128-byte column block (if any) */
 } wf_problem;
 
 int wf_bitlinear_decode_plan(wf_problem* host_problems, int P);

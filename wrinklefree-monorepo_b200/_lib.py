@@ -29,7 +29,18 @@ class Problem(C.Structure):
                 ("ldx", _i64), ("ldy", _i64), ("M", C.c_int32), ("N", C.c_int32), ("K", C.c_int32),
                 ("x_dtype", C.c_int32), ("y_dtype", C.c_int32), ("bias_dtype", C.c_int32), ("layout", C.c_int32),
                 ("w_scale_host", _f32), ("eps", _f32),
-                ("_item_begin", C.c_int32), ("_row_items", C.c_int32), ("_chunks", C.c_int32), ("_reserved", C.c_int32)]
+                ("_item_begin", C.c_int32), ("_row_items", C.c_int32), ("_chunks", C.c_int32), ("_kb_full", C.c_int32),
+                ("_tail_bytes", C.c_int32), ("_tmap_main", C.c_uint64 * 16), ("_tmap_tail", C.c_uint64 * 16)]
+
+
+assert C.sizeof(Problem) == 384
+
+
+def aligned_problem_array(n: int):
+    """A ctypes array of n Problem structs starting on a 64-byte boundary (returns array, keep-alive buffer)."""
+    raw = (C.c_char * (n * C.sizeof(Problem) + 64))()
+    addr = (C.addressof(raw) + 63) // 64 * 64
+    return (Problem * n).from_address(addr), raw
 
 
 _SIGNATURES = {

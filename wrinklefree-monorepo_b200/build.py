@@ -44,7 +44,7 @@ def build_library(force: bool = False, verbose: bool = False) -> str:
             print(out)
         if p.returncode != 0:
             raise RuntimeError(f"nvcc failed on {src}:\n{out}")
-    cmd = [nvcc, "-shared", "-o", LIB, *objs, "-ccbin", "/usr/bin/g++", "-lcuda"]
+    cmd = [nvcc, "-shared", "-o", LIB, *objs, "-ccbin", "/usr/bin/g++"]
     r = subprocess.run(cmd, capture_output=True, text=True)
     if r.returncode != 0:
         raise RuntimeError("link failed:\n" + r.stdout + r.stderr)

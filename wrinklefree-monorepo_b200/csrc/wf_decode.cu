@@ -1,7 +1,8 @@
 // Fused per-token activation quantization + ternary contraction for small token
 // counts (decode).  HBM-bound: a persistent kernel streams the packed weights
-// once through a ring of shared-memory stages filled by bulk asynchronous copies
-// (one elected producer thread, mbarrier completion), expands them in registers
+// once through a ring of shared-memory stages filled by tiled TMA copies (one
+// elected producer thread, mbarrier completion; one request brings the
+// [k-blocks][16 rows][128 bytes] box of a whole row tile), expands them in registers
 // and contracts them on the int8 tensor path against activations that the same
 // CTA quantized into shared memory.
 //
@@ -12,8 +13,9 @@
 // per CTA, so a CTA quantizes the activations of a problem once and then only
 // streams weights.
 //
-// Inside an item a "unit" is 16 rows x 512 weights of K, handled by one warp:
-// each lane reads 2 x 16 bytes of rows g and g+8 from the stage.  K is split
+// Inside an item a "unit" is 16 rows x 512 weights of K (a 2 KB tile of the
+// stage: 16 rows of 128 bytes), handled by one warp: each lane reads 2 x 16 bytes
+// of rows g and g+8.  K is split
 // over 16/RI warps per row tile; partial sums meet in a shared-memory int32 tile.
 //
 // Expansion.  In both kernel layouts, (word >> 2p) & 0x03030303 yields four
@@ -28,10 +30,13 @@
 //
 // Every wait on an mbarrier is bounded: when the bound is hit the CTA records
 // WF_E_LIMIT in a device status word, stops waiting anywhere and runs to its end.
+#include <cuda.h>
+
 #include "wf_common.cuh"
 
 namespace wf {
 
+constexpr int TILE_BYTES = 2048;  // one unit of packed weights in a stage: 16 rows x 128 bytes
 constexpr int DEC_CONSUMERS = 512;               // 16 consumer warps
 constexpr int NW = DEC_CONSUMERS / 32;
 constexpr int DEC_THREADS = DEC_CONSUMERS + 32;  // + 1 producer warp
@@ -87,6 +92,18 @@ __device__ __forceinline__ void bulk_copy_g2s(void* dst, const void* src, unsign
                  "l"(src), "r"(bytes), "r"(smem_u32(bar))
                  : "memory");
 }
+__device__ __forceinline__ void tma_load_3d(void* dst, const void* tmap, int c0, int c1, int c2, uint64_t* bar) {
+    asm volatile("cp.async.bulk.tensor.3d.shared::cluster.global.tile.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3, %4}], [%5];\n" ::"r"(
+                     smem_u32(dst)),
+                 "l"(reinterpret_cast<uint64_t>(tmap)), "r"(c0), "r"(c1), "r"(c2), "r"(smem_u32(bar))
+                 : "memory");
+}
+__device__ __forceinline__ void tma_load_2d(void* dst, const void* tmap, int c0, int c1, uint64_t* bar) {
+    asm volatile("cp.async.bulk.tensor.2d.shared::cluster.global.tile.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];\n" ::"r"(
+                     smem_u32(dst)),
+                 "l"(reinterpret_cast<uint64_t>(tmap)), "r"(c0), "r"(c1), "r"(smem_u32(bar))
+                 : "memory");
+}
 __device__ __forceinline__ void consumer_sync() { asm volatile("bar.sync 1, %0;\n" ::"n"(DEC_CONSUMERS) : "memory"); }
 
 __device__ __forceinline__ void mma_u8s8(int (&d)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3, uint32_t b0,
@@ -114,7 +131,6 @@ __device__ __forceinline__ int act_slot_of_k(int layout, int kl) {
     return act_slot(byte >> 6, (byte >> 4) & 3, (byte >> 2) & 3, 3 - grp);
 }
 
-__host__ __device__ __forceinline__ int row_pitch(int K) { return ((K / 4 + 127) / 128) * 128 + 64; }
 
 // ---- the quantization stage: x -> int8 in fragment order, per-token multiplier and sum ----
 // Executed by the 256 consumer threads together whenever the CTA moves to another (problem, token pass).
@@ -300,30 +316,37 @@ __global__ void __launch_bounds__(DEC_THREADS, 1)
         // The item list is walked incrementally: one search at the start, then only counters.
         int pi, chunk, ritem;
         locate_item(probs, cfg.P, beg, pi, chunk, ritem);
-        const uint8_t* codes = probs[pi].codes;
-        int N = probs[pi].N, row_items = probs[pi]._row_items, chunks = probs[pi]._chunks;
-        unsigned rowbytes = static_cast<unsigned>(probs[pi].K >> 2);
-        int pitch = row_pitch(probs[pi].K);
-        for (int it = beg, n = 0; it < end; ++it, ++n) {
-            const int stage = n % cfg.stages;
-            if (n >= cfg.stages) mbar_wait(&empty[stage], ((n / cfg.stages) - 1) & 1, poisoned);
-            const int r0 = ritem * rows_item;
-            const int nrows = min(rows_item, N - r0);
-            if (lane == 0) mbar_expect_tx(&full[stage], static_cast<unsigned>(nrows) * rowbytes);
-            __syncwarp();
-            uint8_t* dst = s_stage + static_cast<size_t>(stage) * cfg.stage_bytes;
-            const uint8_t* src = codes + static_cast<int64_t>(r0) * rowbytes;
-            for (int r = lane; r < nrows; r += 32)
-                bulk_copy_g2s(dst + r * pitch, src + static_cast<int64_t>(r) * rowbytes, rowbytes, &full[stage]);
-            if (++ritem == row_items) {
-                ritem = 0;
-                if (++chunk == chunks) {
-                    chunk = 0;
-                    if (++pi < cfg.P) {
-                        codes = probs[pi].codes;
-                        N = probs[pi].N; row_items = probs[pi]._row_items; chunks = probs[pi]._chunks;
-                        rowbytes = static_cast<unsigned>(probs[pi].K >> 2);
-                        pitch = row_pitch(probs[pi].K);
+        // Only one lane works: a whole 16-row tile over all of K is one TMA request (plus one for a K tail).
+        if (lane == 0) {
+            const wf_problem* p = &probs[pi];
+            int N = p->N, row_items = p->_row_items, chunks = p->_chunks, kbf = p->_kb_full, tail = p->_tail_bytes;
+            int KB = (p->K + 511) >> 9;
+            for (int it = beg, n = 0; it < end; ++it, ++n) {
+                const int stage = n % cfg.stages;
+                if (n >= cfg.stages) mbar_wait(&empty[stage], ((n / cfg.stages) - 1) & 1, poisoned);
+                const int r0 = ritem * rows_item;
+                int tiles = (N - r0 + 15) >> 4;
+                tiles = tiles < cfg.RI ? tiles : cfg.RI;
+                mbar_expect_tx(&full[stage], static_cast<unsigned>(tiles * KB) * TILE_BYTES);
+                uint8_t* dst = s_stage + static_cast<size_t>(stage) * cfg.stage_bytes;
+                for (int rt = 0; rt < tiles; ++rt, dst += KB * TILE_BYTES) {
+                    if (kbf > 0) {
+                        tma_load_3d(dst, p->_tmap_main, 0, r0 + rt * 16, 0, &full[stage]);
+                        if (tail) tma_load_2d(dst + kbf * TILE_BYTES, p->_tmap_tail, 0, r0 + rt * 16, &full[stage]);
+                    } else {  // plain 2-D view: one request per 128-byte column block
+                        for (int kb = 0; kb < KB; ++kb)
+                            tma_load_2d(dst + kb * TILE_BYTES, p->_tmap_tail, kb * 128, r0 + rt * 16, &full[stage]);
+                    }
+                }
+                if (++ritem == row_items) {
+                    ritem = 0;
+                    if (++chunk == chunks) {
+                        chunk = 0;
+                        if (++pi < cfg.P) {
+                            p = &probs[pi];
+                            N = p->N; row_items = p->_row_items; chunks = p->_chunks; kbf = p->_kb_full; tail = p->_tail_bytes;
+                            KB = (p->K + 511) >> 9;
+                        }
                     }
                 }
             }
@@ -353,7 +376,6 @@ __global__ void __launch_bounds__(DEC_THREADS, 1)
             m_valid = min(MT, p.M - m0);
             quantize_tokens<XDT>(p, cfg.MTA, m0, m_valid, s_act, s_inv, s_rowsum, s_maxbits);
             const int KB = (p.K + 511) >> 9;
-            const int pitch = row_pitch(p.K);
             const float s_w = p.w_scale ? __ldg(p.w_scale) : p.w_scale_host;
             // the fields of the problem that the epilogue needs, read once per pass
             void* const y = p.y;
@@ -377,11 +399,11 @@ __global__ void __launch_bounds__(DEC_THREADS, 1)
                     for (int b = 0; b < (FOURACC ? 4 : 1); ++b)
 #pragma unroll
                         for (int c = 0; c < 4; ++c) acc[a][b][c] = 0;
-                const uint8_t* w_r0 = s_stage + static_cast<size_t>(stage) * cfg.stage_bytes + g * pitch;
-                const uint8_t* w_r1 = w_r0 + 8 * pitch;
+                const uint8_t* w_r0 = s_stage + static_cast<size_t>(stage) * cfg.stage_bytes + g * 128;
 #pragma unroll 1
                 for (int kb = 0; kb < KB; ++kb)
-                    compute_unit<NT, FOURACC>(w_r0 + kb * 128, w_r1 + kb * 128, s_act + kb * cfg.MTA * TOK_STRIDE, m_valid, g, t, acc);
+                    compute_unit<NT, FOURACC>(w_r0 + kb * TILE_BYTES, w_r0 + kb * TILE_BYTES + 1024,
+                                              s_act + kb * cfg.MTA * TOK_STRIDE, m_valid, g, t, acc);
                 __syncwarp();
                 if (lane == 0) mbar_arrive(&empty[stage]);
                 // epilogue straight from the accumulators: lane holds rows g, g+8 x tokens 2t, 2t+1 of every token tile
@@ -437,12 +459,11 @@ __global__ void __launch_bounds__(DEC_THREADS, 1)
                 for (int c = 0; c < 4; ++c) acc[a][b][c] = 0;
 
         const int KB = (p.K + 511) >> 9;
-        const int pitch = row_pitch(p.K);
-        const uint8_t* w_r0 = s_stage + static_cast<size_t>(stage) * cfg.stage_bytes + (rt_local * 16 + g) * pitch;
-        const uint8_t* w_r1 = w_r0 + 8 * pitch;
+        const uint8_t* w_r0 = s_stage + static_cast<size_t>(stage) * cfg.stage_bytes + rt_local * KB * TILE_BYTES + g * 128;
 #pragma unroll 1
         for (int kb = ks; kb < KB; kb += KS)
-            compute_unit<NT, FOURACC>(w_r0 + kb * 128, w_r1 + kb * 128, s_act + kb * cfg.MTA * TOK_STRIDE, m_valid, g, t, acc);
+            compute_unit<NT, FOURACC>(w_r0 + kb * TILE_BYTES, w_r0 + kb * TILE_BYTES + 1024, s_act + kb * cfg.MTA * TOK_STRIDE,
+                                      m_valid, g, t, acc);
         __syncwarp();
         if (lane == 0) mbar_arrive(&empty[stage]);  // this warp no longer reads the stage
 
@@ -518,6 +539,70 @@ static size_t fixed_bytes(int NT, int RI) {
     return (b + 127) / 128 * 128;
 }
 
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*, const cuuint64_t*,
+                                  const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
+                                  CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+static EncodeTiledFn encode_fn() {
+    static EncodeTiledFn fn = nullptr;
+    if (!fn) {
+        void* p = nullptr;
+        cudaDriverEntryPointQueryResult q;
+        if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &q) == cudaSuccess &&
+            q == cudaDriverEntryPointSuccess)
+            fn = reinterpret_cast<EncodeTiledFn>(p);
+    }
+    return fn;
+}
+
+// TMA descriptors of the packed weights of one problem.  Main: the full 128-byte column blocks as a 3-D tensor
+// [block][row][128 bytes], so that one box [all blocks][16 rows][128] lands in the stage as consecutive 2 KB tiles.
+// Tail: the last, partial column block as a 2-D tensor whose missing bytes are filled with zeros.  When the 3-D
+// view is refused, the plain 2-D view [row][K/4 bytes] is used with one request per column block.
+static int encode_maps(wf_problem& q) {
+    EncodeTiledFn enc = encode_fn();
+    if (!enc) return fail(WF_E_DEVICE, "cuTensorMapEncodeTiled is not available in this driver");
+    const cuuint64_t rowbytes = static_cast<cuuint64_t>(q.K) / 4;
+    const int kbf = static_cast<int>(rowbytes / 128), tail = static_cast<int>(rowbytes % 128);
+    const cuuint32_t ones[3] = {1, 1, 1};
+    void* base = const_cast<uint8_t*>(q.codes);
+    CUresult r = CUDA_SUCCESS;
+    if (kbf > 0) {
+        const cuuint64_t dims[3] = {128, static_cast<cuuint64_t>(q.N), static_cast<cuuint64_t>(kbf)};
+        const cuuint64_t strides[2] = {rowbytes, 128};
+        const cuuint32_t box[3] = {128, 16, static_cast<cuuint32_t>(kbf)};
+        r = enc(reinterpret_cast<CUtensorMap*>(q._tmap_main), CU_TENSOR_MAP_DATA_TYPE_UINT8, 3, base, dims, strides, box, ones,
+                CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_NONE, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    }
+    if (kbf > 0 && kbf <= 256 && r == CUDA_SUCCESS) {
+        q._kb_full = kbf;
+        q._tail_bytes = tail;
+        if (tail) {
+            const cuuint64_t dims[2] = {static_cast<cuuint64_t>(tail), static_cast<cuuint64_t>(q.N)};
+            const cuuint64_t strides[1] = {rowbytes};
+            const cuuint32_t box[2] = {128, 16};
+            r = enc(reinterpret_cast<CUtensorMap*>(q._tmap_tail), CU_TENSOR_MAP_DATA_TYPE_UINT8, 2,
+                    static_cast<uint8_t*>(base) + static_cast<size_t>(kbf) * 128, dims, strides, box, ones,
+                    CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_NONE, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                    CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+            if (r != CUDA_SUCCESS) return fail(WF_E_DEVICE, "cuTensorMapEncodeTiled (tail block) failed with %d", (int)r);
+        }
+        return WF_OK;
+    }
+    // plain 2-D view
+    const cuuint64_t dims[2] = {rowbytes, static_cast<cuuint64_t>(q.N)};
+    const cuuint64_t strides[1] = {rowbytes};
+    const cuuint32_t box[2] = {128, 16};
+    r = enc(reinterpret_cast<CUtensorMap*>(q._tmap_tail), CU_TENSOR_MAP_DATA_TYPE_UINT8, 2, base, dims, strides, box, ones,
+            CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_NONE, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+            CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    if (r != CUDA_SUCCESS) return fail(WF_E_DEVICE, "cuTensorMapEncodeTiled failed with %d", (int)r);
+    q._kb_full = 0;
+    q._tail_bytes = static_cast<int>(rowbytes);
+    return WF_OK;
+}
+
 // Chooses the token tile, the item size and the ring depth for a group, and fills the item fields.
 static int plan_group(wf_problem* probs, int P, GroupPlan& g, bool write_fields) {
     int Kmax = 0, Mmax = 0;
@@ -526,8 +611,8 @@ static int plan_group(wf_problem* probs, int P, GroupPlan& g, bool write_fields)
         Mmax = probs[i].M > Mmax ? probs[i].M : Mmax;
     }
     const int sms = num_sms();
-    const int pitch = row_pitch(Kmax);
     g.KBmax = (Kmax + 511) / 512;
+    const int pitch = g.KBmax * 128;  // stage bytes per weight row
     // token tile: as many tokens as fit beside three 16-row stages
     int NT = Mmax <= 8 ? 1 : (Mmax <= 16 ? 2 : (Mmax <= 32 ? 4 : 8));
     for (;; NT >>= 1) {
@@ -576,8 +661,8 @@ static int plan_group(wf_problem* probs, int P, GroupPlan& g, bool write_fields)
             probs[i]._item_begin = begin;
             probs[i]._row_items = (probs[i].N + 16 * RI - 1) / (16 * RI);
             probs[i]._chunks = (probs[i].M + MT - 1) / MT;
-            probs[i]._reserved = 0;
             begin += probs[i]._row_items * probs[i]._chunks;
+            if (int rc = encode_maps(probs[i])) return rc;
         }
     }
     return WF_OK;

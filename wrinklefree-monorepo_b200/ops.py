@@ -223,7 +223,7 @@ class DecodeGroup:
             raise ValueError("empty group")
         self._keep = []
         self.outputs, self.accs = [], []
-        arr = (L.Problem * len(problems))()
+        arr, self._raw = L.aligned_problem_array(len(problems))
         dev = problems[0]["x"].device
         for i, pr in enumerate(problems):
             x, codes, w_scale = pr["x"], pr["codes"], pr["w_scale"]
