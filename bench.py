@@ -208,6 +208,8 @@ def main():
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--layers-scale", type=float, default=1.0, help="scale the layer stacks (profiling on a small case)")
     ap.add_argument("--no-pdl", action="store_true")
+    ap.add_argument("--only-m", type=int, default=0, help="restrict the sweep to one token batch (profiling)")
+    ap.add_argument("--only-shape", type=int, default=-1, help="restrict the sweep to one shape index (profiling)")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     args = ap.parse_args()
     rank = int(os.environ.get("RANK", "0"))
@@ -245,6 +247,11 @@ def main():
 
         dist.init_process_group("nccl", device_id=device)
 
+    global SHAPES, BATCHES
+    if args.only_m:
+        BATCHES = [args.only_m]
+    if args.only_shape >= 0:
+        SHAPES = [SHAPES[args.only_shape]]
     groups = build_workload(wf, torch, device, rank, world, args.layers_scale)
     pdl = not args.no_pdl
     try:
