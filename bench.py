@@ -247,11 +247,10 @@ def main():
 
         dist.init_process_group("nccl", device_id=device)
 
-    global SHAPES, BATCHES
     if args.only_m:
-        BATCHES = [args.only_m]
+        BATCHES[:] = [args.only_m]
     if args.only_shape >= 0:
-        SHAPES = [SHAPES[args.only_shape]]
+        SHAPES[:] = [SHAPES[args.only_shape]]
     groups = build_workload(wf, torch, device, rank, world, args.layers_scale)
     pdl = not args.no_pdl
     try:
