@@ -225,15 +225,21 @@ __device__ __forceinline__ void quantize_tokens(const wf_problem& p, int MTA, in
     consumer_sync();
 }
 
+__device__ __forceinline__ uint4 lds128(uint32_t addr) {
+    uint4 v;
+    asm volatile("ld.shared.v4.u32 {%0,%1,%2,%3}, [%4];\n" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "r"(addr));
+    return v;
+}
+
 // One unit: 16 rows x 512 weights from the stage (rows g and g+8 of the tile, 2 x 16 bytes each per lane)
 // against the activations of one k-block.
 template <int NT, bool FOURACC>
-__device__ __forceinline__ void compute_unit(const uint8_t* w_r0, const uint8_t* w_r1, const uint8_t* s_act_kb, int m_valid, int g,
-                                             int t, int (&acc)[NT][FOURACC ? 4 : 1][4]) {
+__device__ __forceinline__ void compute_unit(uint32_t w_r0, uint32_t w_r1, uint32_t s_act_kb, int m_valid, int g, int t,
+                                             int (&acc)[NT][FOURACC ? 4 : 1][4]) {
 #pragma unroll
     for (int h = 0; h < 2; ++h) {
-        const uint4 ra = *reinterpret_cast<const uint4*>(w_r0 + h * 64 + t * 16);
-        const uint4 rb = *reinterpret_cast<const uint4*>(w_r1 + h * 64 + t * 16);
+        const uint4 ra = lds128(w_r0 + h * 64 + t * 16);
+        const uint4 rb = lds128(w_r1 + h * 64 + t * 16);
         const uint32_t wa[4] = {ra.x, ra.y, ra.z, ra.w};
         const uint32_t wb[4] = {rb.x, rb.y, rb.z, rb.w};
 #pragma unroll
@@ -253,8 +259,7 @@ __device__ __forceinline__ void compute_unit(const uint8_t* w_r0, const uint8_t*
             for (int nt = 0; nt < NT; ++nt) {
                 const int tok = nt * 8 + g;
                 uint4 bw = make_uint4(0, 0, 0, 0);
-                if (tok < m_valid)
-                    bw = *reinterpret_cast<const uint4*>(s_act_kb + tok * TOK_STRIDE + ((h * 4 + pp) * 4 + t) * 16);
+                if (tok < m_valid) bw = lds128(s_act_kb + tok * TOK_STRIDE + ((h * 4 + pp) * 4 + t) * 16);
                 mma_u8s8(acc[nt][FOURACC ? pp : 0], a0[0], a1[0], a0[1], a1[1], bw.x, bw.y);
                 mma_u8s8(acc[nt][FOURACC ? pp : 0], a0[2], a1[2], a0[3], a1[3], bw.z, bw.w);
             }
@@ -299,7 +304,7 @@ __global__ void __launch_bounds__(DEC_THREADS, 1)
     if (tid == 0) {
         for (int s = 0; s < cfg.stages; ++s) {
             mbar_init(&full[s], 1);
-            mbar_init(&empty[s], cfg.decoupled ? 1 : DEC_CONSUMERS / 32);
+            mbar_init(&empty[s], NW);
         }
         *poisoned = 0;
         asm volatile("fence.mbarrier_init.release.cluster;\n" ::: "memory");
@@ -361,80 +366,6 @@ __global__ void __launch_bounds__(DEC_THREADS, 1)
     // x may be produced by the previous kernel of the stream
     asm volatile("griddepcontrol.wait;\n" ::: "memory");
 
-    if (cfg.decoupled) {
-        // Every warp consumes whole items (16 rows over all of K) on its own: no CTA-wide barrier and no shared
-        // atomics except where the CTA moves on to another (problem, token pass).  With fewer than 8 stages only
-        // that many warps consume.
-        int it = beg;
-        while (it < end) {
-            int pi, chunk, ritem;
-            locate_item(probs, cfg.P, it, pi, chunk, ritem);
-            const wf_problem& p = probs[pi];
-            const int seg_end = min(end, p._item_begin + (chunk + 1) * p._row_items);
-            consumer_sync();  // every warp is done with the previous pass
-            m0 = chunk * MT;
-            m_valid = min(MT, p.M - m0);
-            quantize_tokens<XDT>(p, cfg.MTA, m0, m_valid, s_act, s_inv, s_rowsum, s_maxbits);
-            const int KB = (p.K + 511) >> 9;
-            const float s_w = p.w_scale ? __ldg(p.w_scale) : p.w_scale_host;
-            // the fields of the problem that the epilogue needs, read once per pass
-            void* const y = p.y;
-            const void* const bias = p.bias;
-            int32_t* const acc_out = p.acc_out;
-            const int64_t ldy = p.ldy;
-            const int N = p.N, y_dtype = p.y_dtype, bias_dtype = p.bias_dtype;
-            // A stage is always consumed by the same warp (stage == warp), so that the rounds of a stage are waited
-            // for in order (a parity wait cannot tell round r from round r + 2).
-            const int S = cfg.stages;
-            int n = it - beg;
-            n += (warp - n % S + S) % S;  // first local item index >= it - beg with n % S == warp
-            if (warp >= S) n = seg_end - beg;  // more warps than stages: the rest only help to quantize
-            for (; n < seg_end - beg; n += S) {
-                const int j = n + beg, stage = warp;
-                mbar_wait(&full[stage], (n / S) & 1, poisoned);
-                int acc[NT][FOURACC ? 4 : 1][4];
-#pragma unroll
-                for (int a = 0; a < NT; ++a)
-#pragma unroll
-                    for (int b = 0; b < (FOURACC ? 4 : 1); ++b)
-#pragma unroll
-                        for (int c = 0; c < 4; ++c) acc[a][b][c] = 0;
-                const uint8_t* w_r0 = s_stage + static_cast<size_t>(stage) * cfg.stage_bytes + g * 128;
-#pragma unroll 1
-                for (int kb = 0; kb < KB; ++kb)
-                    compute_unit<NT, FOURACC>(w_r0 + kb * TILE_BYTES, w_r0 + kb * TILE_BYTES + 1024,
-                                              s_act + kb * cfg.MTA * TOK_STRIDE, m_valid, g, t, acc);
-                __syncwarp();
-                if (lane == 0) mbar_arrive(&empty[stage]);
-                // epilogue straight from the accumulators: lane holds rows g, g+8 x tokens 2t, 2t+1 of every token tile
-                const int row_a = (ritem + (j - it)) * 16 + g, row_b = row_a + 8;
-#pragma unroll
-                for (int nt = 0; nt < NT; ++nt) {
-#pragma unroll
-                    for (int c = 0; c < 4; ++c) {
-                        int v;
-                        if constexpr (FOURACC)
-                            v = acc[nt][0][c] + (acc[nt][1][c] >> 2) + (acc[nt][2][c] >> 4) + (acc[nt][3][c] >> 6);
-                        else
-                            v = acc[nt][0][c];
-                        const int tok = nt * 8 + 2 * t + (c & 1);
-                        const int nrow = (c & 2) ? row_b : row_a;
-                        if (tok < m_valid && nrow < N) {
-                            const int a = v - s_rowsum[tok];
-                            float out = rescale(a, s_inv[tok], s_w);
-                            if (bias) out = __fadd_rn(out, load1_rt(bias, bias_dtype, nrow));
-                            const int64_t m = m0 + tok;
-                            store1_rt(y, y_dtype, m * ldy + nrow, out);
-                            if (acc_out) acc_out[m * N + nrow] = a;
-                        }
-                    }
-                }
-            }
-            it = seg_end;
-        }
-        return;
-    }
-
     for (int it = beg, n = 0; it < end; ++it, ++n) {
         int pi, chunk, ritem;
         locate_item(probs, cfg.P, it, pi, chunk, ritem);
@@ -459,10 +390,11 @@ __global__ void __launch_bounds__(DEC_THREADS, 1)
                 for (int c = 0; c < 4; ++c) acc[a][b][c] = 0;
 
         const int KB = (p.K + 511) >> 9;
-        const uint8_t* w_r0 = s_stage + static_cast<size_t>(stage) * cfg.stage_bytes + rt_local * KB * TILE_BYTES + g * 128;
+        const uint32_t w_r0 = smem_u32(s_stage) + stage * cfg.stage_bytes + rt_local * KB * TILE_BYTES + g * 128;
+        const uint32_t act0 = smem_u32(s_act);
 #pragma unroll 1
         for (int kb = ks; kb < KB; kb += KS)
-            compute_unit<NT, FOURACC>(w_r0 + kb * TILE_BYTES, w_r0 + kb * TILE_BYTES + 1024, s_act + kb * cfg.MTA * TOK_STRIDE,
+            compute_unit<NT, FOURACC>(w_r0 + kb * TILE_BYTES, w_r0 + kb * TILE_BYTES + 1024, act0 + kb * cfg.MTA * TOK_STRIDE,
                                       m_valid, g, t, acc);
         __syncwarp();
         if (lane == 0) mbar_arrive(&empty[stage]);  // this warp no longer reads the stage
@@ -505,6 +437,154 @@ __global__ void __launch_bounds__(DEC_THREADS, 1)
             store1_rt(p.y, p.y_dtype, m * p.ldy + nrow, v);
             if (p.acc_out) p.acc_out[m * p.N + nrow] = a;
         }
+    }
+}
+
+// ---- streaming form: every warp owns one stage and is its own producer ------------------------------
+// Used when a launch has thousands of 16-row items.  Warp w consumes the items w, w + S, w + 2S, ... of
+// the CTA's range (S = stages <= 16 warps); as soon as its MMA loop has read the stage it issues the TMA
+// request of its next item itself, so no thread serialises the requests of the CTA and no "empty"
+// barrier exists.  The CTA only synchronises where it moves to another (problem, token pass).
+struct ItemCursor {  // walks the item list in strides
+    int pi, chunk, ritem, row_items, chunks;
+};
+
+__device__ __forceinline__ void cursor_advance(ItemCursor& c, const wf_problem* __restrict__ probs, int P, int by) {
+    c.ritem += by;
+    while (c.ritem >= c.row_items) {
+        c.ritem -= c.row_items;
+        if (++c.chunk == c.chunks) {
+            c.chunk = 0;
+            if (++c.pi >= P) return;
+            c.row_items = probs[c.pi]._row_items;
+            c.chunks = probs[c.pi]._chunks;
+        }
+    }
+}
+
+__device__ __forceinline__ void issue_item(const wf_problem* p, int ritem, uint8_t* dst, uint64_t* bar) {
+    const int KB = (p->K + 511) >> 9, kbf = p->_kb_full;
+    mbar_expect_tx(bar, static_cast<unsigned>(KB) * TILE_BYTES);
+    if (kbf > 0) {
+        tma_load_3d(dst, p->_tmap_main, 0, ritem * 16, 0, bar);
+        if (p->_tail_bytes) tma_load_2d(dst + kbf * TILE_BYTES, p->_tmap_tail, 0, ritem * 16, bar);
+    } else {
+        for (int kb = 0; kb < KB; ++kb) tma_load_2d(dst + kb * TILE_BYTES, p->_tmap_tail, kb * 128, ritem * 16, bar);
+    }
+}
+
+template <int XDT, int NT, bool FOURACC>
+__global__ void __launch_bounds__(DEC_CONSUMERS, 1)
+    decode_stream_kernel(const wf_problem* __restrict__ dev_problems, const __grid_constant__ wf_problem single, const DecodeCfg cfg) {
+    extern __shared__ __align__(128) uint8_t smem[];
+    constexpr int MT = NT * 8;
+    uint64_t* full = reinterpret_cast<uint64_t*>(smem);
+    volatile int* poisoned = reinterpret_cast<volatile int*>(smem + 256);
+    float* s_inv = reinterpret_cast<float*>(smem + 384);
+    int* s_rowsum = reinterpret_cast<int*>(smem + 384 + MT * 4);
+    unsigned* s_maxbits = reinterpret_cast<unsigned*>(smem + 384 + MT * 8);
+    uint8_t* s_act = smem + cfg.act_off;
+    uint8_t* s_stage = smem + cfg.stage_off;
+    const wf_problem* probs = dev_problems ? dev_problems : &single;
+
+    asm volatile("griddepcontrol.launch_dependents;\n" ::: "memory");
+    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31, g = lane >> 2, t = lane & 3;
+    const int S = cfg.stages;
+    if (tid == 0) {
+        for (int s = 0; s < S; ++s) mbar_init(&full[s], 1);
+        *poisoned = 0;
+        asm volatile("fence.mbarrier_init.release.cluster;\n" ::: "memory");
+    }
+    __syncthreads();
+
+    const int beg = static_cast<int>(static_cast<int64_t>(blockIdx.x) * cfg.total_items / gridDim.x);
+    const int end = static_cast<int>(static_cast<int64_t>(blockIdx.x + 1) * cfg.total_items / gridDim.x);
+    uint8_t* my_stage = s_stage + static_cast<size_t>(warp) * cfg.stage_bytes;
+    const uint32_t w_r0 = smem_u32(my_stage) + g * 128;
+    const uint32_t act0 = smem_u32(s_act);
+
+    // cursor of the next item this warp will request; the first request goes out before anything else
+    ItemCursor nx;
+    int nx_item = beg + warp;
+    unsigned loads = 0;  // completed + pending requests of this warp (parity of the wait)
+    if (warp < S && nx_item < end) {
+        locate_item(probs, cfg.P, nx_item, nx.pi, nx.chunk, nx.ritem);
+        nx.row_items = probs[nx.pi]._row_items;
+        nx.chunks = probs[nx.pi]._chunks;
+        if (lane == 0) issue_item(&probs[nx.pi], nx.ritem, my_stage, &full[warp]);
+    }
+
+    // x may be produced by the previous kernel of the stream
+    asm volatile("griddepcontrol.wait;\n" ::: "memory");
+
+    int it = beg;
+    while (it < end) {
+        int pi, chunk, ritem;
+        locate_item(probs, cfg.P, it, pi, chunk, ritem);
+        const wf_problem& p = probs[pi];
+        const int seg_end = min(end, p._item_begin + (chunk + 1) * p._row_items);
+        consumer_sync();  // every warp is done with the previous pass
+        const int m0 = chunk * MT, m_valid = min(MT, p.M - m0);
+        quantize_tokens<XDT>(p, cfg.MTA, m0, m_valid, s_act, s_inv, s_rowsum, s_maxbits);
+        const int KB = (p.K + 511) >> 9;
+        const float s_w = p.w_scale ? __ldg(p.w_scale) : p.w_scale_host;
+        void* const y = p.y;
+        const void* const bias = p.bias;
+        int32_t* const acc_out = p.acc_out;
+        const int64_t ldy = p.ldy;
+        const int N = p.N, y_dtype = p.y_dtype, bias_dtype = p.bias_dtype;
+        if (warp < S) {
+            int j = it + ((warp - (it - beg)) % S + S) % S;  // first item of this warp in the pass
+            for (; j < seg_end; j += S) {
+                mbar_wait(&full[warp], loads & 1, poisoned);
+                ++loads;
+                int acc[NT][FOURACC ? 4 : 1][4];
+#pragma unroll
+                for (int a = 0; a < NT; ++a)
+#pragma unroll
+                    for (int b = 0; b < (FOURACC ? 4 : 1); ++b)
+#pragma unroll
+                        for (int c = 0; c < 4; ++c) acc[a][b][c] = 0;
+#pragma unroll 1
+                for (int kb = 0; kb < KB; ++kb)
+                    compute_unit<NT, FOURACC>(w_r0 + kb * TILE_BYTES, w_r0 + kb * TILE_BYTES + 1024,
+                                              act0 + kb * cfg.MTA * TOK_STRIDE, m_valid, g, t, acc);
+                // the stage has been read: request this warp's next item (it may belong to a later pass)
+                __syncwarp();
+                nx_item += S;
+                if (nx_item < end) {
+                    cursor_advance(nx, probs, cfg.P, S);
+                    if (lane == 0) {
+                        asm volatile("fence.proxy.async.shared::cta;\n" ::: "memory");
+                        issue_item(&probs[nx.pi], nx.ritem, my_stage, &full[warp]);
+                    }
+                }
+                // epilogue straight from the accumulators: lane holds rows g, g+8 x tokens 2t, 2t+1 of every token tile
+                const int row_a = (ritem + (j - it)) * 16 + g, row_b = row_a + 8;
+#pragma unroll
+                for (int nt = 0; nt < NT; ++nt) {
+#pragma unroll
+                    for (int c = 0; c < 4; ++c) {
+                        int v;
+                        if constexpr (FOURACC)
+                            v = acc[nt][0][c] + (acc[nt][1][c] >> 2) + (acc[nt][2][c] >> 4) + (acc[nt][3][c] >> 6);
+                        else
+                            v = acc[nt][0][c];
+                        const int tok = nt * 8 + 2 * t + (c & 1);
+                        const int nrow = (c & 2) ? row_b : row_a;
+                        if (tok < m_valid && nrow < N) {
+                            const int a = v - s_rowsum[tok];
+                            float out = rescale(a, s_inv[tok], s_w);
+                            if (bias) out = __fadd_rn(out, load1_rt(bias, bias_dtype, nrow));
+                            const int64_t m = m0 + tok;
+                            store1_rt(y, y_dtype, m * ldy + nrow, out);
+                            if (acc_out) acc_out[m * N + nrow] = a;
+                        }
+                    }
+                }
+            }
+        }
+        it = seg_end;
     }
 }
 
@@ -671,15 +751,15 @@ static int plan_group(wf_problem* probs, int P, GroupPlan& g, bool write_fields)
 template <int XDT, int NT, bool FOURACC>
 static int launch_decode(const wf_problem* dev, const wf_problem& single, const DecodeCfg& cfg, const GroupPlan& g, unsigned flags,
                          cudaStream_t st) {
-    auto kern = decode_kernel<XDT, NT, FOURACC>;
-    static thread_local size_t configured = 0;  // per instantiation
-    if (g.smem > 48 * 1024 && g.smem > configured) {
+    auto kern = g.decoupled ? decode_stream_kernel<XDT, NT, FOURACC> : decode_kernel<XDT, NT, FOURACC>;
+    static thread_local bool configured[2] = {false, false};  // per instantiation
+    if (!configured[g.decoupled]) {
         WF_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(SMEM_MAX)));
-        configured = SMEM_MAX;
+        configured[g.decoupled] = true;
     }
     cudaLaunchConfig_t lc = {};
     lc.gridDim = dim3(g.grid);
-    lc.blockDim = dim3(DEC_THREADS);
+    lc.blockDim = dim3(g.decoupled ? DEC_CONSUMERS : DEC_THREADS);
     lc.dynamicSmemBytes = g.smem;
     lc.stream = st;
     cudaLaunchAttribute attr[1];
