@@ -480,10 +480,10 @@ __global__ void __launch_bounds__(DEC_CONSUMERS, 1)
     constexpr int MT = NT * 8;
     uint64_t* full = reinterpret_cast<uint64_t*>(smem);
     volatile int* poisoned = reinterpret_cast<volatile int*>(smem + 256);
-    float* s_inv = reinterpret_cast<float*>(smem + 384);
-    int* s_rowsum = reinterpret_cast<int*>(smem + 384 + MT * 4);
-    unsigned* s_maxbits = reinterpret_cast<unsigned*>(smem + 384 + MT * 8);
-    uint8_t* s_act = smem + cfg.act_off;
+    float* s_inv = reinterpret_cast<float*>(smem + 384);                    // [2][MT]
+    int* s_rowsum = reinterpret_cast<int*>(smem + 384 + MT * 8);            // [2][MT]
+    unsigned* s_maxbits = reinterpret_cast<unsigned*>(smem + 384 + MT * 16);  // [2][MT]
+    uint8_t* s_act = smem + cfg.act_off;                                    // [2][KBmax * MTA * TOK_STRIDE]
     uint8_t* s_stage = smem + cfg.stage_off;
     const wf_problem* probs = dev_problems ? dev_problems : &single;
 
@@ -501,7 +501,6 @@ __global__ void __launch_bounds__(DEC_CONSUMERS, 1)
     const int end = static_cast<int>(static_cast<int64_t>(blockIdx.x + 1) * cfg.total_items / gridDim.x);
     uint8_t* my_stage = s_stage + static_cast<size_t>(warp) * cfg.stage_bytes;
     const uint32_t w_r0 = smem_u32(my_stage) + g * 128;
-    const uint32_t act0 = smem_u32(s_act);
 
     // cursor of the next item this warp will request; the first request goes out before anything else
     ItemCursor nx;
@@ -517,15 +516,34 @@ __global__ void __launch_bounds__(DEC_CONSUMERS, 1)
     // x may be produced by the previous kernel of the stream
     asm volatile("griddepcontrol.wait;\n" ::: "memory");
 
-    int it = beg;
-    while (it < end) {
+    // Two activation buffers: the first two passes of the CTA's range are quantized up front, so that a CTA
+    // whose range crosses from one problem into the next does not stop streaming there.  Later passes (rare:
+    // problems much smaller than a CTA's share) reuse the buffers behind a CTA-wide barrier.
+    const int act_bytes = cfg.KBmax * cfg.MTA * TOK_STRIDE;
+    int seg = 0, it = beg, pre_it = beg;
+    for (int sgi = 0; sgi < 2 && pre_it < end; ++sgi) {
+        int pi, chunk, ritem;
+        locate_item(probs, cfg.P, pre_it, pi, chunk, ritem);
+        const wf_problem& p = probs[pi];
+        quantize_tokens<XDT>(p, cfg.MTA, chunk * MT, min(MT, p.M - chunk * MT), s_act + sgi * act_bytes, s_inv + sgi * MT,
+                             s_rowsum + sgi * MT, s_maxbits + sgi * MT);
+        pre_it = min(end, p._item_begin + (chunk + 1) * p._row_items);
+    }
+    for (; it < end; ++seg) {
         int pi, chunk, ritem;
         locate_item(probs, cfg.P, it, pi, chunk, ritem);
         const wf_problem& p = probs[pi];
         const int seg_end = min(end, p._item_begin + (chunk + 1) * p._row_items);
-        consumer_sync();  // every warp is done with the previous pass
         const int m0 = chunk * MT, m_valid = min(MT, p.M - m0);
-        quantize_tokens<XDT>(p, cfg.MTA, m0, m_valid, s_act, s_inv, s_rowsum, s_maxbits);
+        const int buf = seg & 1;
+        if (seg >= 2) {
+            consumer_sync();  // every warp is done with the pass that used this buffer
+            quantize_tokens<XDT>(p, cfg.MTA, m0, m_valid, s_act + buf * act_bytes, s_inv + buf * MT, s_rowsum + buf * MT,
+                                 s_maxbits + buf * MT);
+        }
+        const uint32_t act0 = smem_u32(s_act + buf * act_bytes);
+        const float* const inv_p = s_inv + buf * MT;
+        const int* const rowsum_p = s_rowsum + buf * MT;
         const int KB = (p.K + 511) >> 9;
         const float s_w = p.w_scale ? __ldg(p.w_scale) : p.w_scale_host;
         void* const y = p.y;
@@ -573,8 +591,8 @@ __global__ void __launch_bounds__(DEC_CONSUMERS, 1)
                         const int tok = nt * 8 + 2 * t + (c & 1);
                         const int nrow = (c & 2) ? row_b : row_a;
                         if (tok < m_valid && nrow < N) {
-                            const int a = v - s_rowsum[tok];
-                            float out = rescale(a, s_inv[tok], s_w);
+                            const int a = v - rowsum_p[tok];
+                            float out = rescale(a, inv_p[tok], s_w);
                             if (bias) out = __fadd_rn(out, load1_rt(bias, bias_dtype, nrow));
                             const int64_t m = m0 + tok;
                             store1_rt(y, y_dtype, m * ldy + nrow, out);
@@ -706,7 +724,7 @@ static int plan_group(wf_problem* probs, int P, GroupPlan& g, bool write_fields)
     const size_t act = (static_cast<size_t>(g.KBmax) * g.MTA * TOK_STRIDE + 127) / 128 * 128;
     // Enough 16-row items to give every consumer warp of every SM several of them: the warps work on their
     // own items.  Otherwise (a single small layer) the 16 warps of a CTA share each item and split K.
-    g.decoupled = count_items16(probs, P, MT) >= 32LL * sms && fixed_bytes(NT, 1) + act + 4u * 16 * pitch <= SMEM_MAX;
+    g.decoupled = count_items16(probs, P, MT) >= 32LL * sms && fixed_bytes(NT, 1) + 2 * act + 6u * 16 * pitch <= SMEM_MAX;
     // item size: about 32 KB per stage, smaller while there are too few items to keep every SM busy
     int RI = g.decoupled ? 1 : 8;
     while (RI > 1 && 16 * RI * pitch > 32 * 1024) RI >>= 1;
@@ -721,7 +739,7 @@ static int plan_group(wf_problem* probs, int P, GroupPlan& g, bool write_fields)
     g.RI = RI;
     g.stage_bytes = 16 * RI * pitch;
     g.act_off = static_cast<int>(fixed_bytes(NT, RI));
-    g.stage_off = g.act_off + static_cast<int>(act);
+    g.stage_off = g.act_off + static_cast<int>(g.decoupled ? 2 * act : act);
     if (static_cast<size_t>(g.stage_off) + 2u * g.stage_bytes > SMEM_MAX)
         return fail(WF_E_LIMIT, "wf_bitlinear_decode: K=%d needs more shared memory than one SM has", Kmax);
     const long long total = count_items(RI);
