@@ -104,7 +104,10 @@ __device__ __forceinline__ void tma_load_2d(void* dst, const void* tmap, int c0,
                  "l"(reinterpret_cast<uint64_t>(tmap)), "r"(c0), "r"(c1), "r"(smem_u32(bar))
                  : "memory");
 }
-__device__ __forceinline__ void consumer_sync() { asm volatile("bar.sync 1, %0;\n" ::"n"(DEC_CONSUMERS) : "memory"); }
+template <int NTHREADS = DEC_CONSUMERS>
+__device__ __forceinline__ void consumer_sync() {
+    asm volatile("bar.sync 1, %0;\n" ::"n"(NTHREADS) : "memory");
+}
 
 __device__ __forceinline__ void mma_u8s8(int (&d)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3, uint32_t b0,
                                          uint32_t b1) {
@@ -134,20 +137,20 @@ __device__ __forceinline__ int act_slot_of_k(int layout, int kl) {
 
 // ---- the quantization stage: x -> int8 in fragment order, per-token multiplier and sum ----
 // Executed by the 256 consumer threads together whenever the CTA moves to another (problem, token pass).
-template <int XDT>
+template <int XDT, int NTHREADS = DEC_CONSUMERS>
 __device__ __forceinline__ void quantize_tokens(const wf_problem& p, int MTA, int m0, int m_valid, uint8_t* s_act, float* s_inv,
                                                 int* s_rowsum, unsigned* s_maxbits) {
     const int tid = threadIdx.x;
     const int KB = (p.K + 511) >> 9, Kp = KB * 512;
-    for (int i = tid; i < m_valid; i += DEC_CONSUMERS) {
+    for (int i = tid; i < m_valid; i += NTHREADS) {
         s_rowsum[i] = 0;
         s_maxbits[i] = 0;
     }
-    consumer_sync();
+    consumer_sync<NTHREADS>();
     // threads per token: all 256 for one token down to one warp per token for 8 or more
-    int tpt = DEC_CONSUMERS;
-    while (tpt > 32 && DEC_CONSUMERS / tpt < m_valid) tpt >>= 1;
-    const int par = DEC_CONSUMERS / tpt;  // tokens handled concurrently
+    int tpt = NTHREADS;
+    while (tpt > 32 && NTHREADS / tpt < m_valid) tpt >>= 1;
+    const int par = NTHREADS / tpt;  // tokens handled concurrently
     const int sub = tid / tpt, lane_in = tid % tpt;
 
     if constexpr (XDT == WF_I8) {
@@ -190,7 +193,7 @@ __device__ __forceinline__ void quantize_tokens(const wf_problem& p, int MTA, in
             for (int o = 16; o > 0; o >>= 1) mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, o));
             if (tok < m_valid && (tid & 31) == 0) atomicMax(&s_maxbits[tok], __float_as_uint(mx));
         }
-        consumer_sync();
+        consumer_sync<NTHREADS>();
         // pass 2: quantize, scatter, sum
         for (int tb = 0; tb < m_valid; tb += par) {
             int tok = tb + sub;
@@ -222,7 +225,7 @@ __device__ __forceinline__ void quantize_tokens(const wf_problem& p, int MTA, in
             if (tok < m_valid && (tid & 31) == 0) atomicAdd(&s_rowsum[tok], sum);
         }
     }
-    consumer_sync();
+    consumer_sync<NTHREADS>();
 }
 
 __device__ __forceinline__ uint4 lds128(uint32_t addr) {
@@ -441,8 +444,10 @@ __global__ void __launch_bounds__(DEC_THREADS, 1)
 }
 
 // ---- streaming form: every warp owns one stage and is its own producer ------------------------------
-// Used when a launch has thousands of 16-row items.  Warp w consumes the items w, w + S, w + 2S, ... of
-// the CTA's range (S = stages <= 16 warps); as soon as its MMA loop has read the stage it issues the TMA
+// Used when a launch has thousands of 16-row items.  CTAs are half-size (8 warps, at most half of an SM's
+// shared memory) so that two are resident per SM: the prologue and the tail of one overlap the streaming of
+// the other, also across launches chained with programmatic dependent launch.  Warp w consumes the items
+// w, w + S, w + 2S, ... of the CTA's range (S = stages <= 8 warps); as soon as its MMA loop has read the stage it issues the TMA
 // request of its next item itself, so no thread serialises the requests of the CTA and no "empty"
 // barrier exists.  The CTA only synchronises where it moves to another (problem, token pass).
 struct ItemCursor {  // walks the item list in strides
@@ -473,8 +478,11 @@ __device__ __forceinline__ void issue_item(const wf_problem* p, int ritem, uint8
     }
 }
 
+constexpr int STREAM_THREADS = 256;  // 8 warps; two such CTAs share an SM
+constexpr int SW = STREAM_THREADS / 32;
+
 template <int XDT, int NT, bool FOURACC>
-__global__ void __launch_bounds__(DEC_CONSUMERS, 1)
+__global__ void __launch_bounds__(STREAM_THREADS, 2)
     decode_stream_kernel(const wf_problem* __restrict__ dev_problems, const __grid_constant__ wf_problem single, const DecodeCfg cfg) {
     extern __shared__ __align__(128) uint8_t smem[];
     constexpr int MT = NT * 8;
@@ -525,7 +533,7 @@ __global__ void __launch_bounds__(DEC_CONSUMERS, 1)
         int pi, chunk, ritem;
         locate_item(probs, cfg.P, pre_it, pi, chunk, ritem);
         const wf_problem& p = probs[pi];
-        quantize_tokens<XDT>(p, cfg.MTA, chunk * MT, min(MT, p.M - chunk * MT), s_act + sgi * act_bytes, s_inv + sgi * MT,
+        quantize_tokens<XDT, STREAM_THREADS>(p, cfg.MTA, chunk * MT, min(MT, p.M - chunk * MT), s_act + sgi * act_bytes, s_inv + sgi * MT,
                              s_rowsum + sgi * MT, s_maxbits + sgi * MT);
         pre_it = min(end, p._item_begin + (chunk + 1) * p._row_items);
     }
@@ -537,8 +545,8 @@ __global__ void __launch_bounds__(DEC_CONSUMERS, 1)
         const int m0 = chunk * MT, m_valid = min(MT, p.M - m0);
         const int buf = seg & 1;
         if (seg >= 2) {
-            consumer_sync();  // every warp is done with the pass that used this buffer
-            quantize_tokens<XDT>(p, cfg.MTA, m0, m_valid, s_act + buf * act_bytes, s_inv + buf * MT, s_rowsum + buf * MT,
+            consumer_sync<STREAM_THREADS>();  // every warp is done with the pass that used this buffer
+            quantize_tokens<XDT, STREAM_THREADS>(p, cfg.MTA, m0, m_valid, s_act + buf * act_bytes, s_inv + buf * MT, s_rowsum + buf * MT,
                                  s_maxbits + buf * MT);
         }
         const uint32_t act0 = smem_u32(s_act + buf * act_bytes);
@@ -613,6 +621,7 @@ struct GroupPlan {
 };
 
 constexpr size_t SMEM_MAX = 227 * 1024;
+constexpr size_t SMEM_STREAM_MAX = 113 * 1024;  // two streaming CTAs per SM
 
 static int num_sms() {
     static thread_local int cached = 0;
@@ -724,7 +733,7 @@ static int plan_group(wf_problem* probs, int P, GroupPlan& g, bool write_fields)
     const size_t act = (static_cast<size_t>(g.KBmax) * g.MTA * TOK_STRIDE + 127) / 128 * 128;
     // Enough 16-row items to give every consumer warp of every SM several of them: the warps work on their
     // own items.  Otherwise (a single small layer) the 16 warps of a CTA share each item and split K.
-    g.decoupled = count_items16(probs, P, MT) >= 32LL * sms && fixed_bytes(NT, 1) + 2 * act + 6u * 16 * pitch <= SMEM_MAX;
+    g.decoupled = count_items16(probs, P, MT) >= 32LL * sms && fixed_bytes(NT, 1) + 2 * act + 3u * 16 * pitch <= SMEM_STREAM_MAX;
     // item size: about 32 KB per stage, smaller while there are too few items to keep every SM busy
     int RI = g.decoupled ? 1 : 8;
     while (RI > 1 && 16 * RI * pitch > 32 * 1024) RI >>= 1;
@@ -745,12 +754,12 @@ static int plan_group(wf_problem* probs, int P, GroupPlan& g, bool write_fields)
     const long long total = count_items(RI);
     if (total > 0x7fffffffLL) return fail(WF_E_LIMIT, "wf_bitlinear_decode: too many work items");
     g.total_items = static_cast<int>(total);
-    g.grid = g.total_items <= 2 * sms ? g.total_items : sms;
+    g.grid = g.decoupled ? 2 * sms : (g.total_items <= 2 * sms ? g.total_items : sms);
     const int per_cta = (g.total_items + g.grid - 1) / g.grid;
-    int stages = static_cast<int>((SMEM_MAX - g.stage_off) / g.stage_bytes);
+    int stages = static_cast<int>(((g.decoupled ? SMEM_STREAM_MAX : SMEM_MAX) - g.stage_off) / g.stage_bytes);
     if (stages > MAX_STAGES) stages = MAX_STAGES;
     if (!g.decoupled && stages > per_cta + 1) stages = per_cta + 1 > 2 ? per_cta + 1 : 2;
-    if (g.decoupled && stages > NW) stages = NW;  // one owning warp per stage
+    if (g.decoupled && stages > SW) stages = SW;  // one owning warp per stage
     g.stages = stages;
     g.smem = static_cast<size_t>(g.stage_off) + static_cast<size_t>(stages) * g.stage_bytes;
     if (write_fields) {
@@ -777,7 +786,7 @@ static int launch_decode(const wf_problem* dev, const wf_problem& single, const 
     }
     cudaLaunchConfig_t lc = {};
     lc.gridDim = dim3(g.grid);
-    lc.blockDim = dim3(g.decoupled ? DEC_CONSUMERS : DEC_THREADS);
+    lc.blockDim = dim3(g.decoupled ? STREAM_THREADS : DEC_THREADS);
     lc.dynamicSmemBytes = g.smem;
     lc.stream = st;
     cudaLaunchAttribute attr[1];
