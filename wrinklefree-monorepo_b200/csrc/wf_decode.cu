@@ -55,6 +55,7 @@ struct DecodeCfg {
     int stages;
     int stage_bytes;  // bytes per stage (16*RI rows at the pitch of the largest K)
     int act_off, stage_off;  // byte offsets inside dynamic shared memory
+    int cpp;          // streaming form: CTAs per problem when ranges are aligned to problems (0: contiguous split)
     int decoupled;    // 1: every consumer warp owns whole 16-row items (RI == 1); 0: the 16 warps share each item
 };
 
@@ -505,8 +506,20 @@ __global__ void __launch_bounds__(STREAM_THREADS, 2)
     }
     __syncthreads();
 
-    const int beg = static_cast<int>(static_cast<int64_t>(blockIdx.x) * cfg.total_items / gridDim.x);
-    const int end = static_cast<int>(static_cast<int64_t>(blockIdx.x + 1) * cfg.total_items / gridDim.x);
+    // The CTA's range of items: an even share of one problem when the grid divides well over the problems
+    // (one quantization per CTA, no pass boundary inside a range), else an even share of the whole list.
+    int beg, end;
+    if (cfg.cpp > 0) {
+        const int pi = blockIdx.x / cfg.cpp, sub = blockIdx.x % cfg.cpp;
+        if (pi >= cfg.P) return;
+        const int ib = probs[pi]._item_begin, cnt = probs[pi]._row_items * probs[pi]._chunks;
+        beg = ib + static_cast<int>(static_cast<int64_t>(sub) * cnt / cfg.cpp);
+        end = ib + static_cast<int>(static_cast<int64_t>(sub + 1) * cnt / cfg.cpp);
+        if (beg >= end) return;
+    } else {
+        beg = static_cast<int>(static_cast<int64_t>(blockIdx.x) * cfg.total_items / gridDim.x);
+        end = static_cast<int>(static_cast<int64_t>(blockIdx.x + 1) * cfg.total_items / gridDim.x);
+    }
     uint8_t* my_stage = s_stage + static_cast<size_t>(warp) * cfg.stage_bytes;
     const uint32_t w_r0 = smem_u32(my_stage) + g * 128;
 
@@ -616,7 +629,7 @@ __global__ void __launch_bounds__(STREAM_THREADS, 2)
 
 // ------------------------------------------------------------------ host side
 struct GroupPlan {
-    int NT, RI, KBmax, MTA, stages, stage_bytes, act_off, stage_off, total_items, grid, decoupled;
+    int NT, RI, KBmax, MTA, stages, stage_bytes, act_off, stage_off, total_items, grid, decoupled, cpp;
     size_t smem;
 };
 
@@ -755,6 +768,11 @@ static int plan_group(wf_problem* probs, int P, GroupPlan& g, bool write_fields)
     if (total > 0x7fffffffLL) return fail(WF_E_LIMIT, "wf_bitlinear_decode: too many work items");
     g.total_items = static_cast<int>(total);
     g.grid = g.decoupled ? 2 * sms : (g.total_items <= 2 * sms ? g.total_items : sms);
+    g.cpp = 0;
+    if (g.decoupled && P <= g.grid) {
+        const int cpp = g.grid / P;
+        if (cpp * P * 10 >= g.grid * 9) g.cpp = cpp;  // at most a tenth of the CTAs left without work
+    }
     const int per_cta = (g.total_items + g.grid - 1) / g.grid;
     int stages = static_cast<int>(((g.decoupled ? SMEM_STREAM_MAX : SMEM_MAX) - g.stage_off) / g.stage_bytes);
     if (stages > MAX_STAGES) stages = MAX_STAGES;
@@ -836,7 +854,7 @@ static int run_group(const char* who, const wf_problem* dev, wf_problem* host, i
     }
     DecodeCfg cfg;
     cfg.P = P; cfg.total_items = g.total_items; cfg.RI = g.RI; cfg.KBmax = g.KBmax; cfg.MTA = g.MTA; cfg.stages = g.stages;
-    cfg.stage_bytes = g.stage_bytes; cfg.act_off = g.act_off; cfg.stage_off = g.stage_off; cfg.decoupled = g.decoupled;
+    cfg.stage_bytes = g.stage_bytes; cfg.act_off = g.act_off; cfg.stage_off = g.stage_off; cfg.decoupled = g.decoupled; cfg.cpp = g.cpp;
     cudaStream_t st = static_cast<cudaStream_t>(stream);
     switch (host[0].x_dtype) {
         case WF_F32: return dispatch_nt<WF_F32>(dev, host[0], cfg, g, flags, st);
