@@ -55,6 +55,7 @@ struct DecodeCfg {
     int stages;
     int stage_bytes;  // bytes per stage (16*RI rows at the pitch of the largest K)
     int act_off, stage_off;  // byte offsets inside dynamic shared memory
+    int nbuf;         // streaming form: activation buffers (2 when they are small, else 1)
     int cpp;          // streaming form: CTAs per problem when ranges are aligned to problems (0: contiguous split)
     int decoupled;    // 1: every consumer warp owns whole 16-row items (RI == 1); 0: the 16 warps share each item
 };
@@ -542,7 +543,8 @@ __global__ void __launch_bounds__(STREAM_THREADS, 2)
     // problems much smaller than a CTA's share) reuse the buffers behind a CTA-wide barrier.
     const int act_bytes = cfg.KBmax * cfg.MTA * TOK_STRIDE;
     int seg = 0, it = beg, pre_it = beg;
-    for (int sgi = 0; sgi < 2 && pre_it < end; ++sgi) {
+    const int nbuf = cfg.nbuf;
+    for (int sgi = 0; sgi < nbuf && pre_it < end; ++sgi) {
         int pi, chunk, ritem;
         locate_item(probs, cfg.P, pre_it, pi, chunk, ritem);
         const wf_problem& p = probs[pi];
@@ -556,8 +558,8 @@ __global__ void __launch_bounds__(STREAM_THREADS, 2)
         const wf_problem& p = probs[pi];
         const int seg_end = min(end, p._item_begin + (chunk + 1) * p._row_items);
         const int m0 = chunk * MT, m_valid = min(MT, p.M - m0);
-        const int buf = seg & 1;
-        if (seg >= 2) {
+        const int buf = seg % nbuf;
+        if (seg >= nbuf) {
             consumer_sync<STREAM_THREADS>();  // every warp is done with the pass that used this buffer
             quantize_tokens<XDT, STREAM_THREADS>(p, cfg.MTA, m0, m_valid, s_act + buf * act_bytes, s_inv + buf * MT, s_rowsum + buf * MT,
                                  s_maxbits + buf * MT);
@@ -629,7 +631,7 @@ __global__ void __launch_bounds__(STREAM_THREADS, 2)
 
 // ------------------------------------------------------------------ host side
 struct GroupPlan {
-    int NT, RI, KBmax, MTA, stages, stage_bytes, act_off, stage_off, total_items, grid, decoupled, cpp;
+    int NT, RI, KBmax, MTA, stages, stage_bytes, act_off, stage_off, total_items, grid, decoupled, cpp, nbuf;
     size_t smem;
 };
 
@@ -746,7 +748,8 @@ static int plan_group(wf_problem* probs, int P, GroupPlan& g, bool write_fields)
     const size_t act = (static_cast<size_t>(g.KBmax) * g.MTA * TOK_STRIDE + 127) / 128 * 128;
     // Enough 16-row items to give every consumer warp of every SM several of them: the warps work on their
     // own items.  Otherwise (a single small layer) the 16 warps of a CTA share each item and split K.
-    g.decoupled = count_items16(probs, P, MT) >= 32LL * sms && fixed_bytes(NT, 1) + 2 * act + 3u * 16 * pitch <= SMEM_STREAM_MAX;
+    g.decoupled = count_items16(probs, P, MT) >= 32LL * sms && fixed_bytes(NT, 1) + act + 4u * 16 * pitch <= SMEM_STREAM_MAX;
+    g.nbuf = (g.decoupled && fixed_bytes(NT, 1) + 2 * act + 6u * 16 * pitch <= SMEM_STREAM_MAX) ? 2 : 1;
     // item size: about 32 KB per stage, smaller while there are too few items to keep every SM busy
     int RI = g.decoupled ? 1 : 8;
     while (RI > 1 && 16 * RI * pitch > 32 * 1024) RI >>= 1;
@@ -761,7 +764,7 @@ static int plan_group(wf_problem* probs, int P, GroupPlan& g, bool write_fields)
     g.RI = RI;
     g.stage_bytes = 16 * RI * pitch;
     g.act_off = static_cast<int>(fixed_bytes(NT, RI));
-    g.stage_off = g.act_off + static_cast<int>(g.decoupled ? 2 * act : act);
+    g.stage_off = g.act_off + static_cast<int>(g.nbuf * act);
     if (static_cast<size_t>(g.stage_off) + 2u * g.stage_bytes > SMEM_MAX)
         return fail(WF_E_LIMIT, "wf_bitlinear_decode: K=%d needs more shared memory than one SM has", Kmax);
     const long long total = count_items(RI);
@@ -854,7 +857,7 @@ static int run_group(const char* who, const wf_problem* dev, wf_problem* host, i
     }
     DecodeCfg cfg;
     cfg.P = P; cfg.total_items = g.total_items; cfg.RI = g.RI; cfg.KBmax = g.KBmax; cfg.MTA = g.MTA; cfg.stages = g.stages;
-    cfg.stage_bytes = g.stage_bytes; cfg.act_off = g.act_off; cfg.stage_off = g.stage_off; cfg.decoupled = g.decoupled; cfg.cpp = g.cpp;
+    cfg.stage_bytes = g.stage_bytes; cfg.act_off = g.act_off; cfg.stage_off = g.stage_off; cfg.decoupled = g.decoupled; cfg.cpp = g.cpp; cfg.nbuf = g.nbuf;
     cudaStream_t st = static_cast<cudaStream_t>(stream);
     switch (host[0].x_dtype) {
         case WF_F32: return dispatch_nt<WF_F32>(dev, host[0], cfg, g, flags, st);
