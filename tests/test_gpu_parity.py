@@ -225,16 +225,40 @@ def test_int8_input_with_scales_and_strides(wf):
 
 
 def test_prefill_entry_point_bit_exact(wf, oracle_c):
+    """The tensor-core contraction: partial token / row / K tiles, both layouts, float and int8 input, bias."""
+    L = wf._lib
     rng = np.random.default_rng(21)
-    for (m, k, n) in ((128, 256, 64), (200, 576, 144), (512, 2560, 256)):
+    for (m, k, n) in ((128, 256, 64), (200, 576, 144), (512, 2560, 256), (300, 1024, 700), (129, 128, 257)):
         t = rng.integers(-1, 2, size=(n, k)).astype(np.int8)
         x = torch.from_numpy(rng.standard_normal((m, k)).astype(np.float32)).bfloat16()
+        bias = torch.from_numpy(rng.standard_normal(n).astype(np.float32))
         q, s = oracle_c.act_quant(x.float().numpy(), 1)
         acc_o = oracle_c.int_gemm(q, t)
-        codes = wf.pack_codes(torch.from_numpy(t).to(DEV))
-        y, acc = wf.bitlinear(x.to(DEV), codes, 0.02, out_dtype=torch.float32, want_acc=True, path="prefill")
-        assert np.array_equal(acc.cpu().numpy(), acc_o)
-        assert np.array_equal(y.cpu().numpy(), oracle_c.rescale(acc_o, s, 0.02))
+        for lay in ((L.LAYOUT_WF16, L.LAYOUT_I2S) if k % 128 == 0 else (L.LAYOUT_WF16,)):
+            codes = wf.pack_codes(torch.from_numpy(t).to(DEV), lay)
+            y, acc = wf.bitlinear(x.to(DEV), codes, 0.02, layout=lay, out_dtype=torch.float32, want_acc=True, path="prefill")
+            assert np.array_equal(acc.cpu().numpy(), acc_o), (m, k, n, lay)
+            assert np.array_equal(y.cpu().numpy(), oracle_c.rescale(acc_o, s, 0.02))
+        yb = wf.bitlinear(x.to(DEV), codes, 0.02, bias=bias.to(DEV), layout=lay, out_dtype=torch.float32, path="prefill")
+        assert np.array_equal(yb.cpu().numpy(), oracle_c.rescale(acc_o, s, 0.02, bias.numpy()))
+        # already-quantized input with per-token multipliers
+        yq, accq = wf.bitlinear(torch.from_numpy(q).to(DEV), codes, 0.02, layout=lay, x_scale=torch.from_numpy(s).to(DEV),
+                                want_acc=True, path="prefill")
+        assert np.array_equal(accq.cpu().numpy(), acc_o) and np.array_equal(yq.cpu().numpy(), oracle_c.rescale(acc_o, s, 0.02))
+    wf.device_status()
+
+
+@pytest.mark.parametrize("n,k", [(2560, 2560), (6912, 2560), (2560, 6912)])
+def test_prefill_full_size_against_decode_path(wf, n, k):
+    """BASELINE prefill shapes at M = 512: the tensor-core path and the decode path agree bit for bit."""
+    g = torch.Generator().manual_seed(n + k)
+    w = torch.randn(n, k, generator=g) * 0.02
+    x = gi.with_outliers(torch.randn(512, k, generator=g), seed=3).bfloat16().to(DEV)
+    codes, scale = wf.pack_ternary(w.to(DEV))
+    y1, a1 = wf.bitlinear(x, codes, scale, want_acc=True, path="prefill")
+    y2, a2 = wf.bitlinear(x, codes, scale, want_acc=True, path="decode")
+    assert torch.equal(a1, a2) and torch.equal(y1, y2)
+    wf.device_status()
 
 
 # ---------------------------------------------------------------- operator API and modules

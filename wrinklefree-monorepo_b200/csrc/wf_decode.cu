@@ -35,6 +35,12 @@
 #include "wf_common.cuh"
 
 namespace wf {
+__device__ int g_decode_status = 0;
+}
+#define WF_STATUS_WORD ::wf::g_decode_status
+#include "wf_async.cuh"
+
+namespace wf {
 
 constexpr int TILE_BYTES = 2048;  // one unit of packed weights in a stage: 16 rows x 128 bytes
 constexpr int DEC_CONSUMERS = 512;               // 16 consumer warps
@@ -42,9 +48,6 @@ constexpr int NW = DEC_CONSUMERS / 32;
 constexpr int DEC_THREADS = DEC_CONSUMERS + 32;  // + 1 producer warp
 constexpr int TOK_STRIDE = 576;  // bytes of shared memory per (k-block, token): 512 + 64 skew (conflict-free 128-bit reads)
 constexpr int MAX_STAGES = 16;
-constexpr unsigned SPIN_LIMIT = 1u << 20;
-
-__device__ int g_decode_status = 0;
 
 struct DecodeCfg {
     int P;            // problems
@@ -60,52 +63,6 @@ struct DecodeCfg {
     int decoupled;    // 1: every consumer warp owns whole 16-row items (RI == 1); 0: the 16 warps share each item
 };
 
-__device__ __forceinline__ uint32_t smem_u32(const void* p) { return static_cast<uint32_t>(__cvta_generic_to_shared(p)); }
-
-__device__ __forceinline__ void mbar_init(uint64_t* bar, unsigned count) {
-    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;\n" ::"r"(smem_u32(bar)), "r"(count));
-}
-__device__ __forceinline__ void mbar_arrive(uint64_t* bar) {
-    asm volatile("{\n .reg .b64 st;\n mbarrier.arrive.shared::cta.b64 st, [%0];\n}\n" ::"r"(smem_u32(bar)) : "memory");
-}
-__device__ __forceinline__ void mbar_expect_tx(uint64_t* bar, unsigned bytes) {
-    asm volatile("{\n .reg .b64 st;\n mbarrier.arrive.expect_tx.shared::cta.b64 st, [%0], %1;\n}\n" ::"r"(smem_u32(bar)), "r"(bytes)
-                 : "memory");
-}
-// Bounded wait.  Returns false (and poisons the CTA) when the bound is hit.
-__device__ __forceinline__ bool mbar_wait(uint64_t* bar, unsigned parity, volatile int* poisoned) {
-    if (*poisoned) return false;
-    const uint32_t a = smem_u32(bar);
-    for (unsigned it = 0; it < SPIN_LIMIT; ++it) {
-        unsigned ok;
-        asm volatile("{\n .reg .pred p;\n mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n selp.u32 %0, 1, 0, p;\n}\n"
-                     : "=r"(ok)
-                     : "r"(a), "r"(parity)
-                     : "memory");
-        if (ok) return true;
-        if ((it & 1023) == 1023 && *poisoned) return false;
-    }
-    *poisoned = 1;
-    atomicExch(&g_decode_status, WF_E_LIMIT);
-    return false;
-}
-__device__ __forceinline__ void bulk_copy_g2s(void* dst, const void* src, unsigned bytes, uint64_t* bar) {
-    asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];\n" ::"r"(smem_u32(dst)),
-                 "l"(src), "r"(bytes), "r"(smem_u32(bar))
-                 : "memory");
-}
-__device__ __forceinline__ void tma_load_3d(void* dst, const void* tmap, int c0, int c1, int c2, uint64_t* bar) {
-    asm volatile("cp.async.bulk.tensor.3d.shared::cluster.global.tile.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3, %4}], [%5];\n" ::"r"(
-                     smem_u32(dst)),
-                 "l"(reinterpret_cast<uint64_t>(tmap)), "r"(c0), "r"(c1), "r"(c2), "r"(smem_u32(bar))
-                 : "memory");
-}
-__device__ __forceinline__ void tma_load_2d(void* dst, const void* tmap, int c0, int c1, uint64_t* bar) {
-    asm volatile("cp.async.bulk.tensor.2d.shared::cluster.global.tile.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];\n" ::"r"(
-                     smem_u32(dst)),
-                 "l"(reinterpret_cast<uint64_t>(tmap)), "r"(c0), "r"(c1), "r"(smem_u32(bar))
-                 : "memory");
-}
 template <int NTHREADS = DEC_CONSUMERS>
 __device__ __forceinline__ void consumer_sync() {
     asm volatile("bar.sync 1, %0;\n" ::"n"(NTHREADS) : "memory");
@@ -929,10 +886,14 @@ extern "C" int wf_bitlinear_decode_grouped(const wf_problem* dev_problems, const
     return run_group("wf_bitlinear_decode_grouped", dev_problems, const_cast<wf_problem*>(host_problems), P, true, flags, stream);
 }
 
+extern "C" int wf_prefill_status_fetch(int* out);
+
 extern "C" int wf_device_status(void) {
     if (int rc = require_device()) return rc;
     WF_CUDA(cudaDeviceSynchronize());
-    int v = 0;
+    int v = 0, v2 = 0;
+    if (int rc = wf_prefill_status_fetch(&v2)) return rc;
+    if (v2) return fail(v2, "a bounded wait inside the prefill kernel ran out; the outputs of that launch are invalid");
     WF_CUDA(cudaMemcpyFromSymbol(&v, g_decode_status, sizeof(int)));
     if (v) {
         int zero = 0;

@@ -1,42 +1,369 @@
-// Contraction for large token counts (prefill): stand-alone activation
-// quantization into the caller's workspace, then the integer contraction.
+// Contraction for large token counts (prefill): a dense int8 GEMM on the
+// 5th-generation tensor cores.
+//
+//   acc[tok, n] = sum_k q[tok, k] * code[n, k]      (u8 codes = w + 1, s8 activations, s32 accumulate in TMEM)
+//   y[tok, n]   = (float(acc - rowsum[tok]) * inv_sx[tok]) * s_w + bias[n]
+//
+// One CTA computes a tile of 128 tokens x 256 weight rows.  Per 128-wide block of K:
+//   * warp 0 (one lane) issues two TMA loads: the int8 activation tile (128 tokens x 128 bytes,
+//     128-byte swizzle, the MMA's A operand) and the PACKED weight tile (256 rows x 32 bytes);
+//   * warps 2-5 expand the packed tile to int8 (one mask + shift per four weights) and store it
+//     K-major with the 128-byte swizzle pattern, as the MMA's B operand;
+//   * warp 1 (one lane) issues four tcgen05.mma.kind::i8 (M=128, N=256, K=32) into the TMEM accumulator
+//     and commits them to the barrier that frees the stage.
+// After the last block, warps 2-5 read the accumulator with tcgen05.ld (lane = token), apply the integer
+// correction and the fp32 rescale, and store y.  Every mbarrier wait is bounded.
+#include <cuda.h>
+
 #include "wf_common.cuh"
+
+namespace wf {
+__device__ int g_prefill_status = 0;
+}
+#define WF_STATUS_WORD ::wf::g_prefill_status
+#include "wf_async.cuh"
 
 int wf_check_linear_args(const char* who, const void* x, int x_dtype, int64_t ldx, const float* x_scale, const uint8_t* codes,
                          int layout, const void* bias, int bias_dtype, void* y, int y_dtype, int64_t ldy, int64_t M, int64_t N,
                          int64_t K);
 
-using namespace wf;
+namespace wf {
+
+constexpr int PF_BM = 128;      // tokens per tile (TMEM lanes)
+constexpr int PF_BN = 256;      // weight rows per tile (TMEM columns)
+constexpr int PF_BK = 128;      // K per stage
+constexpr int PF_STAGES = 3;
+constexpr int PF_THREADS = 192; // warp 0 TMA, warp 1 MMA, warps 2-5 expand + epilogue
+constexpr int PF_A_BYTES = PF_BM * PF_BK;        // 16 KB
+constexpr int PF_P_BYTES = PF_BN * PF_BK / 4;    // 8 KB packed
+constexpr int PF_B_BYTES = PF_BN * PF_BK;        // 32 KB expanded
+constexpr int PF_STAGE_BYTES = PF_A_BYTES + PF_P_BYTES + PF_B_BYTES;
+constexpr size_t PF_SMEM = 1024 /*align slack*/ + PF_STAGES * PF_STAGE_BYTES + 256 /*barriers*/;
+
+struct PrefillParams {
+    const float* x_scale;   // [M] per-token multipliers (nullable: 1)
+    const int32_t* rowsum;  // [M]
+    const float* w_scale;
+    float w_scale_host;
+    const void* bias;
+    int bias_dtype;
+    void* y;
+    int y_dtype;
+    int64_t ldy;
+    int32_t* acc_out;
+    int M, N, K, layout;
+};
+
+__device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory"); }
+__device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;\n" ::: "memory"); }
+
+__device__ __forceinline__ void tc_commit(uint64_t* bar) {
+    asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];\n" ::"r"(smem_u32(bar)) : "memory");
+}
+
+// K-major operand tile with 128-byte swizzle: rows of 128 bytes, 8-row groups 1024 bytes apart.
+__device__ __forceinline__ uint64_t smem_desc_sw128(uint32_t addr) {
+    uint64_t d = 0;
+    d |= static_cast<uint64_t>((addr & 0x3FFFF) >> 4);  // start address
+    d |= static_cast<uint64_t>(1024 >> 4) << 32;        // stride between 8-row groups
+    d |= static_cast<uint64_t>(1) << 46;                // descriptor version of sm_100
+    d |= static_cast<uint64_t>(2) << 61;                // SWIZZLE_128B
+    return d;
+}
+
+__device__ __forceinline__ void mma_i8(uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc, uint32_t idesc, uint32_t accumulate) {
+    asm volatile(
+        "{\n .reg .pred p;\n setp.ne.b32 p, %4, 0;\n"
+        " tcgen05.mma.cta_group::1.kind::i8 [%0], %1, %2, %3, {%5, %5, %5, %5}, p;\n}\n" ::"r"(d_tmem),
+        "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate), "r"(0u)
+        : "memory");
+}
+
+__device__ __forceinline__ void tmem_ld32(uint32_t addr, uint32_t (&v)[32]) {
+    asm volatile(
+        "tcgen05.ld.sync.aligned.32x32b.x32.b32 {%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,%16,%17,%18,%19,%20,%21,%22,"
+        "%23,%24,%25,%26,%27,%28,%29,%30,%31}, [%32];\n"
+        : "=r"(v[0]), "=r"(v[1]), "=r"(v[2]), "=r"(v[3]), "=r"(v[4]), "=r"(v[5]), "=r"(v[6]), "=r"(v[7]), "=r"(v[8]), "=r"(v[9]),
+          "=r"(v[10]), "=r"(v[11]), "=r"(v[12]), "=r"(v[13]), "=r"(v[14]), "=r"(v[15]), "=r"(v[16]), "=r"(v[17]), "=r"(v[18]),
+          "=r"(v[19]), "=r"(v[20]), "=r"(v[21]), "=r"(v[22]), "=r"(v[23]), "=r"(v[24]), "=r"(v[25]), "=r"(v[26]), "=r"(v[27]),
+          "=r"(v[28]), "=r"(v[29]), "=r"(v[30]), "=r"(v[31])
+        : "r"(addr));
+    asm volatile("tcgen05.wait::ld.sync.aligned;\n" ::: "memory");
+}
+
+__device__ __forceinline__ void sts128(uint32_t addr, uint32_t a, uint32_t b, uint32_t c, uint32_t d) {
+    asm volatile("st.shared.v4.u32 [%0], {%1,%2,%3,%4};\n" ::"r"(addr), "r"(a), "r"(b), "r"(c), "r"(d) : "memory");
+}
+__device__ __forceinline__ uint4 lds128p(uint32_t addr) {
+    uint4 v;
+    asm volatile("ld.shared.v4.u32 {%0,%1,%2,%3}, [%4];\n" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "r"(addr));
+    return v;
+}
+
+// Expands the 32 packed bytes of one weight row (128 weights) into 128 int8 bytes stored as row `r` of a
+// K-major tile with 128-byte swizzle (16-byte chunk c of the row lands at chunk c ^ (r & 7)).
+__device__ __forceinline__ void expand_row(uint32_t packed_addr, uint32_t tile_addr, int r, int layout) {
+    const uint4 p0 = lds128p(packed_addr), p1 = lds128p(packed_addr + 16);
+    const uint32_t w[8] = {p0.x, p0.y, p0.z, p0.w, p1.x, p1.y, p1.z, p1.w};
+    const uint32_t row = tile_addr + r * 128;
+    const uint32_t m = 0x03030303u;
+    const int x = r & 7;
+    if (layout == WF_LAYOUT_WF16) {
+        // word c holds weights 16c..16c+15: bit pair j of byte b = weight 16c + 4j + b
+#pragma unroll
+        for (int c = 0; c < 8; ++c)
+            sts128(row + ((c ^ x) << 4), w[c] & m, (w[c] >> 2) & m, (w[c] >> 4) & m, (w[c] >> 6) & m);
+    } else {
+        // I2_S: byte j bits 7:6, 5:4, 3:2, 1:0 = weights j, j+32, j+64, j+96; chunk c covers weights 16c..16c+15
+#pragma unroll
+        for (int c = 0; c < 8; ++c) {
+            const int sh = 6 - 2 * (c >> 1), wb = 4 * (c & 1);
+            sts128(row + ((c ^ x) << 4), (w[wb] >> sh) & m, (w[wb + 1] >> sh) & m, (w[wb + 2] >> sh) & m, (w[wb + 3] >> sh) & m);
+        }
+    }
+}
+
+__global__ void __launch_bounds__(PF_THREADS, 1)
+    prefill_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_p, const PrefillParams p) {
+    extern __shared__ uint8_t smem_raw[];
+    // operand tiles need 1024-byte alignment for the 128-byte swizzle
+    uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~static_cast<uintptr_t>(1023));
+    uint8_t* bars = smem + PF_STAGES * PF_STAGE_BYTES;
+    uint64_t* tma_full = reinterpret_cast<uint64_t*>(bars);           // [S] TMA bytes landed
+    uint64_t* b_full = tma_full + PF_STAGES;                          // [S] expansion written
+    uint64_t* mma_done = b_full + PF_STAGES;                          // [S] MMAs of the stage retired
+    uint64_t* acc_full = mma_done + PF_STAGES;                        // accumulator complete
+    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(acc_full + 1);
+    volatile int* poisoned = reinterpret_cast<volatile int*>(tmem_slot + 1);
+
+    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    const int m0 = blockIdx.y * PF_BM, n0 = blockIdx.x * PF_BN;
+    const int kblocks = (p.K + PF_BK - 1) / PF_BK;
+
+    if (tid == 0) {
+        for (int s = 0; s < PF_STAGES; ++s) {
+            mbar_init(&tma_full[s], 1);
+            mbar_init(&b_full[s], 4);  // one arrival per expansion warp
+            mbar_init(&mma_done[s], 1);
+        }
+        mbar_init(acc_full, 1);
+        *poisoned = 0;
+        asm volatile("fence.mbarrier_init.release.cluster;\n" ::: "memory");
+    }
+    if (warp == 1) {  // TMEM: 256 columns of 128 lanes hold the 128 x 256 int32 accumulator
+        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;\n" ::"r"(smem_u32(tmem_slot)), "r"(PF_BN));
+        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;\n" ::);
+    }
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    const uint32_t tmem_base = *tmem_slot;
+
+    if (warp == 0) {
+        if (lane == 0) {
+            for (int kb = 0; kb < kblocks; ++kb) {
+                const int s = kb % PF_STAGES;
+                if (kb >= PF_STAGES) mbar_wait(&mma_done[s], ((kb / PF_STAGES) - 1) & 1, poisoned);
+                uint8_t* st = smem + s * PF_STAGE_BYTES;
+                mbar_expect_tx(&tma_full[s], PF_A_BYTES + PF_P_BYTES);
+                tma_load_2d(st, &tmap_a, kb * PF_BK, m0, &tma_full[s]);
+                tma_load_2d(st + PF_A_BYTES, &tmap_p, kb * (PF_BK / 4), n0, &tma_full[s]);
+            }
+        }
+    } else if (warp == 1) {
+        if (lane == 0) {
+            // instruction descriptor: D = s32, A = signed 8-bit, B = unsigned 8-bit, both K-major, N = 256, M = 128
+            const uint32_t idesc = (2u << 4) | (1u << 7) | (0u << 10) | (static_cast<uint32_t>(PF_BN >> 3) << 17) |
+                                   (static_cast<uint32_t>(PF_BM >> 4) << 24);
+            for (int kb = 0; kb < kblocks; ++kb) {
+                const int s = kb % PF_STAGES;
+                const unsigned par = (kb / PF_STAGES) & 1;
+                mbar_wait(&tma_full[s], par, poisoned);
+                mbar_wait(&b_full[s], par, poisoned);
+                tc_fence_after();
+                const uint32_t a_addr = smem_u32(smem + s * PF_STAGE_BYTES);
+                const uint32_t b_addr = a_addr + PF_A_BYTES + PF_P_BYTES;
+                const uint64_t a_desc = smem_desc_sw128(a_addr), b_desc = smem_desc_sw128(b_addr);
+#pragma unroll
+                for (int k = 0; k < PF_BK / 32; ++k)  // 32 bytes of K per MMA: advance the start address by 2 x 16 bytes
+                    mma_i8(tmem_base, a_desc + 2 * k, b_desc + 2 * k, idesc, (kb | k) ? 1u : 0u);
+                tc_commit(&mma_done[s]);
+            }
+            tc_commit(acc_full);
+        }
+    } else {
+        // ---- expansion: 128 threads, two weight rows each per K block
+        const int et = tid - 64;  // 0..127
+        for (int kb = 0; kb < kblocks; ++kb) {
+            const int s = kb % PF_STAGES;
+            mbar_wait(&tma_full[s], (kb / PF_STAGES) & 1, poisoned);
+            const uint32_t packed = smem_u32(smem + s * PF_STAGE_BYTES + PF_A_BYTES);
+            const uint32_t tile = packed + PF_P_BYTES;
+            expand_row(packed + et * 32, tile, et, p.layout);
+            expand_row(packed + (et + 128) * 32, tile, et + 128, p.layout);
+            asm volatile("fence.proxy.async.shared::cta;\n" ::: "memory");  // generic writes -> visible to the tensor core
+            __syncwarp();
+            if (lane == 0) mbar_arrive(&b_full[s]);
+        }
+        // ---- epilogue: this warp owns TMEM lanes 32 * (warp % 4) .. + 31, lane = token
+        mbar_wait(acc_full, 0, poisoned);
+        tc_fence_after();
+        const int lane_grp = (warp & 3) * 32;
+        const int tok = m0 + lane_grp + lane;
+        const bool tok_ok = tok < p.M;
+        const float s_w = p.w_scale ? __ldg(p.w_scale) : p.w_scale_host;
+        const float inv = tok_ok ? (p.x_scale ? __frcp_rn(p.x_scale[tok]) : 1.0f) : 0.f;
+        const int rs = tok_ok ? p.rowsum[tok] : 0;
+        for (int c0 = 0; c0 < PF_BN; c0 += 32) {
+            uint32_t v[32];
+            tmem_ld32(tmem_base + (static_cast<uint32_t>(lane_grp) << 16) + c0, v);
+            if (!tok_ok) continue;
+#pragma unroll
+            for (int j = 0; j < 32; ++j) {
+                const int n = n0 + c0 + j;
+                if (n < p.N) {
+                    const int a = static_cast<int>(v[j]) - rs;
+                    float out = rescale(a, inv, s_w);
+                    if (p.bias) out = __fadd_rn(out, load1_rt(p.bias, p.bias_dtype, n));
+                    store1_rt(p.y, p.y_dtype, static_cast<int64_t>(tok) * p.ldy + n, out);
+                    if (p.acc_out) p.acc_out[static_cast<int64_t>(tok) * p.N + n] = a;
+                }
+            }
+        }
+    }
+    tc_fence_before();
+    __syncthreads();
+    if (warp == 1) {
+        tc_fence_after();
+        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;\n" ::"r"(tmem_base), "r"(PF_BN));
+    }
+}
+
+// row sums of an int8 matrix (for activations that arrive already quantized)
+__global__ void rowsum_i8_kernel(const int8_t* __restrict__ q, int64_t ldq, int K, int32_t* __restrict__ rowsum) {
+    const int64_t m = blockIdx.x;
+    int s = 0;
+    for (int k = threadIdx.x * 16; k < K; k += blockDim.x * 16) {
+        const uint4 v = __ldg(reinterpret_cast<const uint4*>(q + m * ldq + k));
+        s += __dp4a(static_cast<int>(v.x), 0x01010101, 0) + __dp4a(static_cast<int>(v.y), 0x01010101, 0) +
+             __dp4a(static_cast<int>(v.z), 0x01010101, 0) + __dp4a(static_cast<int>(v.w), 0x01010101, 0);
+    }
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) s += __shfl_xor_sync(0xffffffffu, s, o);
+    __shared__ int sh[8];
+    if ((threadIdx.x & 31) == 0) sh[threadIdx.x >> 5] = s;
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        int t = 0;
+        for (int i = 0; i < (blockDim.x >> 5); ++i) t += sh[i];
+        rowsum[m] = t;
+    }
+}
+
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*, const cuuint64_t*,
+                                  const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
+                                  CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+static EncodeTiledFn pf_encode_fn() {
+    static EncodeTiledFn fn = nullptr;
+    if (!fn) {
+        void* ptr = nullptr;
+        cudaDriverEntryPointQueryResult q;
+        if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &ptr, cudaEnableDefault, &q) == cudaSuccess &&
+            q == cudaDriverEntryPointSuccess)
+            fn = reinterpret_cast<EncodeTiledFn>(ptr);
+    }
+    return fn;
+}
 
 static size_t align_up(size_t v, size_t a) { return (v + a - 1) / a * a; }
 
+}  // namespace wf
+
+using namespace wf;
+
+extern "C" int wf_prefill_status_fetch(int* out) {
+    WF_CUDA(cudaMemcpyFromSymbol(out, g_prefill_status, sizeof(int)));
+    if (*out) {
+        int zero = 0;
+        WF_CUDA(cudaMemcpyToSymbol(g_prefill_status, &zero, sizeof(int)));
+    }
+    return WF_OK;
+}
+
+// workspace: int8 activations [M, K] | multipliers [M] | row sums [M]
 extern "C" size_t wf_prefill_workspace_bytes(int64_t M, int64_t K) {
     if (M <= 0 || K <= 0) return 0;
-    return align_up(static_cast<size_t>(M) * K, 256) + align_up(static_cast<size_t>(M) * 4, 256);
+    return align_up(static_cast<size_t>(M) * K, 256) + 2 * align_up(static_cast<size_t>(M) * 4, 256);
 }
 
 extern "C" int wf_bitlinear_prefill(const void* x, int x_dtype, int64_t ldx, const float* x_scale, const uint8_t* codes,
                                     int layout, const float* w_scale, float w_scale_host, const void* bias, int bias_dtype,
                                     void* y, int y_dtype, int64_t ldy, int32_t* acc_out, int64_t M, int64_t N, int64_t K,
                                     float eps, void* workspace, size_t workspace_bytes, unsigned flags, void* stream) {
+    (void)flags;
     if (int rc = wf_check_linear_args("wf_bitlinear_prefill", x, x_dtype, ldx, x_scale, codes, layout, bias, bias_dtype, y,
                                       y_dtype, ldy, M, N, K))
         return rc;
-    const int8_t* q = static_cast<const int8_t*>(x);
-    const float* qs = x_scale;
-    int64_t ldq = ldx;
+    WF_REQUIRE(workspace && reinterpret_cast<uintptr_t>(workspace) % 256 == 0, "wf_bitlinear_prefill: workspace must be 256-byte aligned");
+    if (workspace_bytes < wf_prefill_workspace_bytes(M, K))
+        return fail(WF_E_SCRATCH, "wf_bitlinear_prefill: workspace of %zu bytes, need %zu", workspace_bytes,
+                    wf_prefill_workspace_bytes(M, K));
+    if (int rc = require_device()) return rc;
+    cudaStream_t st = static_cast<cudaStream_t>(stream);
+    uint8_t* ws = static_cast<uint8_t*>(workspace);
+    int8_t* wq = reinterpret_cast<int8_t*>(ws);
+    float* wscale = reinterpret_cast<float*>(ws + align_up(static_cast<size_t>(M) * K, 256));
+    int32_t* wsum = reinterpret_cast<int32_t*>(ws + align_up(static_cast<size_t>(M) * K, 256) + align_up(static_cast<size_t>(M) * 4, 256));
+
+    const int8_t* q = nullptr;
+    const float* qs = nullptr;
+    int64_t ldq = K;
     if (x_dtype != WF_I8) {
-        WF_REQUIRE(workspace && reinterpret_cast<uintptr_t>(workspace) % 256 == 0, "wf_bitlinear_prefill: workspace must be 256-byte aligned");
-        if (workspace_bytes < wf_prefill_workspace_bytes(M, K))
-            return fail(WF_E_SCRATCH, "wf_bitlinear_prefill: workspace of %zu bytes, need %zu", workspace_bytes,
-                        wf_prefill_workspace_bytes(M, K));
-        int8_t* wq = static_cast<int8_t*>(workspace);
-        float* ws = reinterpret_cast<float*>(static_cast<uint8_t*>(workspace) + align_up(static_cast<size_t>(M) * K, 256));
-        if (int rc = wf_act_quant_i8(x, x_dtype, M, K, ldx, WF_ACT_PER_TOKEN, eps, wq, ws, nullptr, stream)) return rc;
+        if (int rc = wf_act_quant_i8(x, x_dtype, M, K, ldx, WF_ACT_PER_TOKEN, eps, wq, wscale, wsum, stream)) return rc;
         q = wq;
-        qs = ws;
-        ldq = K;
+        qs = wscale;
+    } else {
+        q = static_cast<const int8_t*>(x);
+        qs = x_scale;
+        ldq = ldx;
+        rowsum_i8_kernel<<<static_cast<unsigned>(M), 128, 0, st>>>(q, ldq, static_cast<int>(K), wsum);
+        WF_CUDA(cudaGetLastError());
     }
-    return wf_bitlinear_decode(q, WF_I8, ldq, qs, codes, layout, w_scale, w_scale_host, bias, bias_dtype, y, y_dtype, ldy,
-                               acc_out, M, N, K, eps, flags, stream);
+
+    EncodeTiledFn enc = pf_encode_fn();
+    if (!enc) return fail(WF_E_DEVICE, "cuTensorMapEncodeTiled is not available in this driver");
+    alignas(64) CUtensorMap tmap_a, tmap_p;
+    const cuuint32_t ones[2] = {1, 1};
+    {
+        const cuuint64_t dims[2] = {static_cast<cuuint64_t>(K), static_cast<cuuint64_t>(M)};
+        const cuuint64_t strides[1] = {static_cast<cuuint64_t>(ldq)};
+        const cuuint32_t box[2] = {PF_BK, PF_BM};
+        CUresult r = enc(&tmap_a, CU_TENSOR_MAP_DATA_TYPE_UINT8, 2, const_cast<int8_t*>(q), dims, strides, box, ones,
+                         CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                         CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+        if (r != CUDA_SUCCESS) return fail(WF_E_DEVICE, "cuTensorMapEncodeTiled (activations) failed with %d", (int)r);
+    }
+    {
+        const cuuint64_t dims[2] = {static_cast<cuuint64_t>(K / 4), static_cast<cuuint64_t>(N)};
+        const cuuint64_t strides[1] = {static_cast<cuuint64_t>(K / 4)};
+        const cuuint32_t box[2] = {PF_BK / 4, PF_BN};
+        CUresult r = enc(&tmap_p, CU_TENSOR_MAP_DATA_TYPE_UINT8, 2, const_cast<uint8_t*>(codes), dims, strides, box, ones,
+                         CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_NONE, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                         CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+        if (r != CUDA_SUCCESS) return fail(WF_E_DEVICE, "cuTensorMapEncodeTiled (packed weights) failed with %d", (int)r);
+    }
+    PrefillParams pp;
+    pp.x_scale = qs; pp.rowsum = wsum; pp.w_scale = w_scale; pp.w_scale_host = w_scale_host; pp.bias = bias;
+    pp.bias_dtype = bias_dtype; pp.y = y; pp.y_dtype = y_dtype; pp.ldy = ldy; pp.acc_out = acc_out;
+    pp.M = static_cast<int>(M); pp.N = static_cast<int>(N); pp.K = static_cast<int>(K); pp.layout = layout;
+    static thread_local bool configured = false;
+    if (!configured) {
+        WF_CUDA(cudaFuncSetAttribute(prefill_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(PF_SMEM)));
+        configured = true;
+    }
+    dim3 grid(static_cast<unsigned>((N + PF_BN - 1) / PF_BN), static_cast<unsigned>((M + PF_BM - 1) / PF_BM));
+    prefill_kernel<<<grid, PF_THREADS, PF_SMEM, st>>>(tmap_a, tmap_p, pp);
+    WF_CUDA(cudaGetLastError());
+    return WF_OK;
 }

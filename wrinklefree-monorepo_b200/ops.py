@@ -190,8 +190,8 @@ def bitlinear(x: torch.Tensor, codes: torch.Tensor, w_scale, bias: Optional[torc
         if m == 0:
             pass
         elif use_prefill:
-            nbytes = lib.wf_prefill_workspace_bytes(m, k) if x2.dtype != torch.int8 else 0
-            ws = _workspace(x.device, nbytes) if nbytes else None
+            nbytes = lib.wf_prefill_workspace_bytes(m, k)
+            ws = _workspace(x.device, nbytes)
             L.check(lib.wf_bitlinear_prefill(x2.data_ptr(), _DT[x2.dtype], x2.stride(0), _ptr(x_scale), codes.data_ptr(),
                                              layout, ws_ptr, ws_host, _ptr(bias), _DT[bias.dtype] if bias is not None else 0,
                                              y.data_ptr(), _DT[y.dtype], y.stride(0), _ptr(acc), m, n, k, eps,
