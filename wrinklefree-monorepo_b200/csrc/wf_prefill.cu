@@ -214,20 +214,51 @@ __global__ void __launch_bounds__(PF_THREADS, 1)
         const float s_w = p.w_scale ? __ldg(p.w_scale) : p.w_scale_host;
         const float inv = tok_ok ? (p.x_scale ? __frcp_rn(p.x_scale[tok]) : 1.0f) : 0.f;
         const int rs = tok_ok ? p.rowsum[tok] : 0;
+        const bool vec_ok = (p.ldy * (p.y_dtype == WF_F32 ? 4 : 2)) % 16 == 0 && reinterpret_cast<uintptr_t>(p.y) % 16 == 0;
         for (int c0 = 0; c0 < PF_BN; c0 += 32) {
             uint32_t v[32];
             tmem_ld32(tmem_base + (static_cast<uint32_t>(lane_grp) << 16) + c0, v);
             if (!tok_ok) continue;
+            const int nb = n0 + c0;
+            float o[32];
 #pragma unroll
             for (int j = 0; j < 32; ++j) {
-                const int n = n0 + c0 + j;
-                if (n < p.N) {
-                    const int a = static_cast<int>(v[j]) - rs;
-                    float out = rescale(a, inv, s_w);
-                    if (p.bias) out = __fadd_rn(out, load1_rt(p.bias, p.bias_dtype, n));
-                    store1_rt(p.y, p.y_dtype, static_cast<int64_t>(tok) * p.ldy + n, out);
-                    if (p.acc_out) p.acc_out[static_cast<int64_t>(tok) * p.N + n] = a;
+                const int a = static_cast<int>(v[j]) - rs;
+                o[j] = rescale(a, inv, s_w);
+                if (p.bias && nb + j < p.N) o[j] = __fadd_rn(o[j], load1_rt(p.bias, p.bias_dtype, nb + j));
+                v[j] = static_cast<uint32_t>(a);
+            }
+            if (vec_ok && nb + 32 <= p.N) {
+                // 32 consecutive outputs of one token: 128-bit stores
+                if (p.y_dtype == WF_F32) {
+                    float4* dst = reinterpret_cast<float4*>(static_cast<float*>(p.y) + static_cast<int64_t>(tok) * p.ldy + nb);
+#pragma unroll
+                    for (int j = 0; j < 8; ++j) dst[j] = make_float4(o[4 * j], o[4 * j + 1], o[4 * j + 2], o[4 * j + 3]);
+                } else {
+                    uint32_t h[16];
+#pragma unroll
+                    for (int j = 0; j < 16; ++j) {
+                        if (p.y_dtype == WF_BF16) {
+                            __nv_bfloat162 t2 = __floats2bfloat162_rn(o[2 * j], o[2 * j + 1]);
+                            h[j] = *reinterpret_cast<uint32_t*>(&t2);
+                        } else {
+                            __half2 t2 = __floats2half2_rn(o[2 * j], o[2 * j + 1]);
+                            h[j] = *reinterpret_cast<uint32_t*>(&t2);
+                        }
+                    }
+                    uint4* dst = reinterpret_cast<uint4*>(static_cast<uint16_t*>(p.y) + static_cast<int64_t>(tok) * p.ldy + nb);
+#pragma unroll
+                    for (int j = 0; j < 4; ++j) dst[j] = make_uint4(h[4 * j], h[4 * j + 1], h[4 * j + 2], h[4 * j + 3]);
                 }
+            } else {
+#pragma unroll
+                for (int j = 0; j < 32; ++j)
+                    if (nb + j < p.N) store1_rt(p.y, p.y_dtype, static_cast<int64_t>(tok) * p.ldy + nb + j, o[j]);
+            }
+            if (p.acc_out) {
+#pragma unroll
+                for (int j = 0; j < 32; ++j)
+                    if (nb + j < p.N) p.acc_out[static_cast<int64_t>(tok) * p.N + nb + j] = static_cast<int>(v[j]);
             }
         }
     }
