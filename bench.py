@@ -199,6 +199,39 @@ def cpu_reference_run(steps: int, warmup: int, nl: int = 2):
     return dict(value=bytes_step / dt / 1e9, unit="GB/s", cores=cores, kind=kind, sample=sample), steps, warmup, dt
 
 
+# ------------------------------------------------------------------ prefill GEMM (secondary figures of the same line)
+PREFILL_M = [512, 2048, 8192]
+
+
+def prefill_section(wf, torch, device, peaks):
+    """int8 x ternary GEMM on tcgen05 at the sweep's shapes: TOPS = 2*M*N*K / time, for the whole operator
+    (activation quantization + contraction) with bf16 activations resident in HBM."""
+    out = []
+    gd = torch.Generator(device=device).manual_seed(4242)
+    for (n, k) in [(2560, 2560), (6912, 2560), (2560, 6912)]:
+        codes, scale = wf.pack_ternary(torch.randn(n, k, generator=gd, device=device) * 0.02)
+        for m in PREFILL_M:
+            x = torch.randn(m, k, generator=gd, device=device).to(torch.bfloat16)
+            y = torch.empty(m, n, dtype=torch.bfloat16, device=device)
+            graph = capture(torch, lambda: wf.bitlinear(x, codes, scale, out=y, path="prefill"))
+            for _ in range(3):
+                graph.replay()
+            torch.cuda.synchronize()
+            a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            reps = 10
+            a.record()
+            for _ in range(reps):
+                graph.replay()
+            b.record()
+            torch.cuda.synchronize()
+            us = a.elapsed_time(b) * 1e3 / reps
+            tops = 2.0 * m * n * k / us / 1e6
+            out.append({"N": n, "K": k, "M": m, "us": round(us, 2), "TOPS": round(tops, 1),
+                        "frac_of_2x_measured_bf16": round(tops / (2 * peaks["bf16_tflops"]), 4),
+                        "frac_of_nominal_int8_4500": round(tops / 4500.0, 4)})
+    return out
+
+
 # ------------------------------------------------------------------ main
 def main():
     ap = argparse.ArgumentParser()
@@ -366,6 +399,8 @@ def main():
             "e2e": {"value": world * total_bytes / (ms_e2e * 1e-3) / 1e9, "unit": "GB/s", "h2d_bytes_per_step": h2d,
                     "d2h_bytes_per_step": d2h, "ms_per_step": ms_e2e},
             "gpu_launches": launches * args.steps, "clocks": clocks, "breakdown": breakdown}
+    if not args.only_m and args.only_shape < 0:
+        line["prefill_gemm"] = prefill_section(wf, torch, device, peaks)
     if not args.no_cpu_baseline and world == 1:
         cb, _, _, _ = cpu_reference_run(3, 1)
         line["cpu_baseline"] = cb
