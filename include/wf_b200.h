@@ -78,6 +78,23 @@ int wf_pack_ternary(const void* w, int w_dtype, int64_t N, int64_t K, int64_t ld
                     uint8_t* codes_out, float* scale_out, void* scratch, size_t scratch_bytes, void* stream);
 
 /*
+ * wf_pack_ternary for callers that must not allocate: same arguments without the scratch pair.
+ * This entry point has no counterpart in the reference.  It is for hosts where device allocation is
+ * off-limits at the point of packing (a serving process whose memory pool owns the GPU and forbids
+ * cudaMalloc in layer code, or a latency-critical thread that cannot take an allocation's implicit device
+ * synchronisation).  The scratch is a fixed array inside the library image on every GPU that loads it
+ * (wf_pack_noalloc_scratch_bytes() = 9472 bytes, held until exit); the call allocates and frees nothing.
+ * Limit: N * K <= WF_PACK_NOALLOC_MAX_WEIGHTS, larger matrices are refused with WF_E_LIMIT.
+ * The first call on a device resolves the array's device address: make it outside any stream capture.
+ * All calls on a device share the array, so calls that overlap on the GPU race; every launch overwrites
+ * what it reads, nothing needs clearing between calls.  Results are identical to wf_pack_ternary's.
+ */
+#define WF_PACK_NOALLOC_MAX_WEIGHTS ((int64_t)1 << 28)
+size_t wf_pack_noalloc_scratch_bytes(void);
+int wf_pack_ternary_noalloc(const void* w, int w_dtype, int64_t N, int64_t K, int64_t ldw, int mode, float eps,
+                            uint8_t* codes_out, float* scale_out, void* stream);
+
+/*
  * Layout conversion of already-ternary packed weights into dst_layout (WF16 or I2S).
  * Replaces the Python packing loops: _pack_ternary_weights (packages/inference/src/wrinklefree_inference/cache/bitnet_converter.py:26-77),
  * repack_hf_weights / pack_weights (packages/inference/src/wrinklefree_inference/kernels/native.py:181-241),

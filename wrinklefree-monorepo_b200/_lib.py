@@ -49,6 +49,8 @@ _SIGNATURES = {
     "wf_device_check": (_int, []),
     "wf_pack_scratch_bytes": (_sz, [_i64, _i64]),
     "wf_pack_ternary": (_int, [_p, _int, _i64, _i64, _i64, _int, _f32, _p, _p, _p, _sz, _p]),
+    "wf_pack_noalloc_scratch_bytes": (_sz, []),
+    "wf_pack_ternary_noalloc": (_int, [_p, _int, _i64, _i64, _i64, _int, _f32, _p, _p, _p]),
     "wf_repack": (_int, [_p, _int, _p, _int, _i64, _i64, _p]),
     "wf_pack_codes": (_int, [_p, _p, _int, _i64, _i64, _p]),
     "wf_unpack_codes": (_int, [_p, _int, _p, _i64, _i64, _p]),

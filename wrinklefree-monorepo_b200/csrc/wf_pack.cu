@@ -293,3 +293,76 @@ int wf_unpack_codes(const uint8_t* src, int layout, int8_t* ternary, int64_t N, 
     return WF_OK;
 }
 }
+
+// ---------------------------------------------------------------------------------------------
+// Allocation-free variant of wf_pack_ternary.
+//
+// Some hosts of this library may not allocate device memory at the point where they pack weights:
+// a serving process whose own pool has claimed the GPU and forbids cudaMalloc inside layer code,
+// or a latency-critical thread that cannot afford the implicit device synchronisation of an
+// allocation.  wf_pack_ternary needs a small scratch buffer (the per-block partial sums of |w|);
+// here that scratch is a fixed array that lives in the library image on every GPU that loads it
+// (WF_PACK_NOALLOC_SCRATCH_BYTES, held until the process exits).  Nothing is allocated or freed by
+// this entry point, neither through the CUDA runtime nor through any other library.
+//
+// The first call on a device looks up the device address of the array (the host-side symbol is
+// only a handle, not an address a kernel may use); make that first call outside any stream capture.
+// All calls on a device share the one array: two calls whose kernels overlap on the GPU (different
+// streams) race on it.  Every launch overwrites the part of the array it later reads, so nothing
+// has to be cleared between calls.
+// ---------------------------------------------------------------------------------------------
+namespace wf {
+
+constexpr int NOALLOC_MAX_PARTIALS = 148 * 8;  // the largest grid launch_pack ever uses
+static __device__ __align__(256) double g_pack_noalloc_scratch[NOALLOC_MAX_PARTIALS];
+
+constexpr int NOALLOC_MAX_DEVICES = 64;
+static double* g_noalloc_ptr[NOALLOC_MAX_DEVICES] = {};  // device address of the array, per device
+
+// Set-up, once per device, with that device current.
+static int noalloc_scratch(double** out) {
+    int dev = -1;
+    WF_CUDA(cudaGetDevice(&dev));
+    if (dev < 0 || dev >= NOALLOC_MAX_DEVICES) return fail(WF_E_LIMIT, "wf_pack_ternary_noalloc: device index %d not supported", dev);
+    if (!g_noalloc_ptr[dev]) {
+        double* ptr = nullptr;
+        cudaError_t e = cudaGetSymbolAddress(reinterpret_cast<void**>(&ptr), g_pack_noalloc_scratch);
+        if (e != cudaSuccess) return cuda_fail(e, "cudaGetSymbolAddress(g_pack_noalloc_scratch)");
+        if (!ptr) return fail(WF_E_DEVICE, "wf_pack_ternary_noalloc: no device address for the scratch array");
+        g_noalloc_ptr[dev] = ptr;
+    }
+    *out = g_noalloc_ptr[dev];
+    return WF_OK;
+}
+
+}  // namespace wf
+
+extern "C" size_t wf_pack_noalloc_scratch_bytes(void) { return sizeof(double) * wf::NOALLOC_MAX_PARTIALS; }
+
+extern "C" int wf_pack_ternary_noalloc(const void* w, int w_dtype, int64_t N, int64_t K, int64_t ldw, int mode, float eps,
+                                       uint8_t* codes_out, float* scale_out, void* stream) {
+    WF_REQUIRE(w && codes_out && scale_out, "wf_pack_ternary_noalloc: null pointer");
+    WF_REQUIRE(N > 0 && K > 0 && K % 64 == 0, "wf_pack_ternary_noalloc: need N > 0 and K a positive multiple of 64 (N=%lld K=%lld)",
+               (long long)N, (long long)K);
+    if (N > WF_PACK_NOALLOC_MAX_WEIGHTS / K)
+        return fail(WF_E_LIMIT, "wf_pack_ternary_noalloc: %lld x %lld weights exceed the maximum of %lld for the allocation-free "
+                                "entry point; use wf_pack_ternary with caller scratch",
+                    (long long)N, (long long)K, (long long)WF_PACK_NOALLOC_MAX_WEIGHTS);
+    WF_REQUIRE(is_float_dtype(w_dtype), "wf_pack_ternary_noalloc: unsupported weight dtype %d", w_dtype);
+    WF_REQUIRE(mode >= WF_PACK_FP32 && mode <= WF_PACK_CAST_F16, "wf_pack_ternary_noalloc: unknown mode %d", mode);
+    WF_REQUIRE(ldw >= K && (ldw * dtype_size(w_dtype)) % 16 == 0, "wf_pack_ternary_noalloc: row stride must cover K and keep rows 16-byte aligned");
+    WF_REQUIRE(reinterpret_cast<uintptr_t>(w) % 16 == 0 && reinterpret_cast<uintptr_t>(codes_out) % 16 == 0,
+               "wf_pack_ternary_noalloc: w and codes_out must be 16-byte aligned");
+    if (wf_pack_scratch_bytes(N, K) > wf_pack_noalloc_scratch_bytes())
+        return fail(WF_E_LIMIT, "wf_pack_ternary_noalloc: this matrix needs %zu bytes of scratch, the fixed array holds %zu",
+                    wf_pack_scratch_bytes(N, K), wf_pack_noalloc_scratch_bytes());
+    if (int rc = require_device()) return rc;
+    double* partial = nullptr;
+    if (int rc = noalloc_scratch(&partial)) return rc;
+    cudaStream_t st = static_cast<cudaStream_t>(stream);
+    switch (w_dtype) {
+        case WF_F32: return launch_pack<WF_F32>(w, N, K, ldw, mode, eps, codes_out, scale_out, partial, st);
+        case WF_BF16: return launch_pack<WF_BF16>(w, N, K, ldw, mode, eps, codes_out, scale_out, partial, st);
+        default: return launch_pack<WF_F16>(w, N, K, ldw, mode, eps, codes_out, scale_out, partial, st);
+    }
+}
