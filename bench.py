@@ -203,14 +203,14 @@ def cpu_reference_run(steps: int, warmup: int, nl: int = 2):
 PREFILL_M = [512, 2048, 8192]
 
 
-def prefill_section(wf, torch, device, peaks):
+def prefill_section(wf, torch, device, peaks, shapes=None, ms=None):
     """int8 x ternary GEMM on tcgen05 at the sweep's shapes: TOPS = 2*M*N*K / time, for the whole operator
     (activation quantization + contraction) with bf16 activations resident in HBM."""
     out = []
     gd = torch.Generator(device=device).manual_seed(4242)
-    for (n, k) in [(2560, 2560), (6912, 2560), (2560, 6912)]:
+    for (n, k) in (shapes or [(2560, 2560), (6912, 2560), (2560, 6912)]):
         codes, scale = wf.pack_ternary(torch.randn(n, k, generator=gd, device=device) * 0.02)
-        for m in PREFILL_M:
+        for m in (ms or PREFILL_M):
             x = torch.randn(m, k, generator=gd, device=device).to(torch.bfloat16)
             y = torch.empty(m, n, dtype=torch.bfloat16, device=device)
             graph = capture(torch, lambda: wf.bitlinear(x, codes, scale, out=y, path="prefill"))
@@ -241,6 +241,7 @@ def main():
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--layers-scale", type=float, default=1.0, help="scale the layer stacks (profiling on a small case)")
     ap.add_argument("--no-pdl", action="store_true")
+    ap.add_argument("--prefill-only", action="store_true", help="run only the prefill GEMM section (profiling)")
     ap.add_argument("--only-m", type=int, default=0, help="restrict the sweep to one token batch (profiling)")
     ap.add_argument("--only-shape", type=int, default=-1, help="restrict the sweep to one shape index (profiling)")
     ap.add_argument("--no-cpu-baseline", action="store_true")
@@ -280,6 +281,12 @@ def main():
 
         dist.init_process_group("nccl", device_id=device)
 
+    if args.prefill_only:
+        peaks, _ = measured_peaks()
+        res = prefill_section(wf, torch, device, peaks, [SHAPES[args.only_shape]] if args.only_shape >= 0 else None,
+                              [args.only_m] if args.only_m else None)
+        print(json.dumps({"prefill_gemm": res}))
+        return
     if args.only_m:
         BATCHES[:] = [args.only_m]
     if args.only_shape >= 0:
