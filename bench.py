@@ -34,6 +34,7 @@ SHAPES = [(2560, 2560), (6912, 2560), (2560, 6912)]  # (N, K)
 BATCHES = [1, 4, 16, 64]
 LAYERS = {(2560, 2560): 96, (6912, 2560): 40, (2560, 6912): 40}  # distinct weight matrices per shape
 METRIC = "ternary_decode_gemv_GBps"
+NCU_TRAFFIC_RATIO = 162.28 / 158.27  # dram bytes / algorithmic bytes, profiles/decode_stream_kernel_m1_2560x2560.md
 
 
 def algorithmic_bytes(m: int, n: int, k: int) -> int:
@@ -90,29 +91,46 @@ class ClockSampler(threading.Thread):
 # ------------------------------------------------------------------ workload construction
 def build_workload(wf, torch, device, rank: int, world: int, layers_scale: float = 1.0):
     """Packs the layer stacks on the device.  Returns a list of groups, one per (shape, M):
-    dict(n, k, m, layers=[(codes, scale)], x=[L, M, K] bf16, y=[L, M, N] bf16)."""
+    dict(n, k, m, layers, x=[L, M, K'] bf16, y=[L, M, N'] bf16, group, reduce).
+
+    With more than one rank the sweep is tensor-parallel the way the reference shards these projections:
+    the 2560x2560 and 6912x2560 (q / gate / up like) matrices are column-parallel (rows split, no exchange),
+    2560x6912 (down like) is row-parallel (K split at multiples of 64, one all-reduce of the partial outputs).
+    Every rank builds the same full matrices (same seeds), ternarizes them whole and keeps its shard."""
     import inputs as gi
 
+    if world > 1:
+        from wrinklefree_monorepo_b200 import tp
+
     groups = []
-    stacks = {}
     for si, (n, k) in enumerate(SHAPES):
         nl = max(2, int(LAYERS[(n, k)] * layers_scale))
-        g = torch.Generator(device="cpu").manual_seed(1000 * si + 17 * rank)
+        row_parallel = world > 1 and k > n
+        g = torch.Generator(device="cpu").manual_seed(1000 * si)
+        gd = torch.Generator(device=device).manual_seed(1000 * si)
         lay = []
-        # one latent matrix per layer, generated on the device for speed (seeded), packed, then dropped
-        gd = torch.Generator(device=device).manual_seed(1000 * si + 17 * rank)
+        n_loc, k_lo, k_hi = n, 0, k
+        if world > 1 and not row_parallel:
+            r_lo, r_hi = tp.shard_bounds(n, world, 16)[rank]
+            n_loc = r_hi - r_lo
+        if row_parallel:
+            k_lo, k_hi = tp.shard_bounds(k, world, 64)[rank]
         for _ in range(nl):
             w = torch.randn(n, k, generator=gd, device=device, dtype=torch.float32) * 0.02
-            lay.append(wf.pack_ternary(w))
+            codes, scale = wf.pack_ternary(w)  # one per-tensor scale for the whole matrix, then shard
             del w
-        stacks[(n, k)] = lay
+            if world > 1 and not row_parallel:
+                codes = tp.shard_codes_rows(codes, r_lo, r_hi)
+            elif row_parallel:
+                codes = tp.shard_codes_k(codes, k_lo, k_hi)
+            lay.append((codes, scale))
         for m in BATCHES:
             x = torch.randn(nl, m, k, generator=g, dtype=torch.float32)
-            x = gi.with_outliers(x, seed=1000 * si + m).to(torch.bfloat16)
+            x = gi.with_outliers(x, seed=1000 * si + m).to(torch.bfloat16)[..., k_lo:k_hi].contiguous()
             xd = x.to(device)
-            y = torch.empty(nl, m, n, dtype=torch.bfloat16, device=device)
+            y = torch.empty(nl, m, n_loc, dtype=torch.bfloat16, device=device)
             grp = wf.DecodeGroup([dict(x=xd[li], codes=c, w_scale=s, out=y[li]) for li, (c, s) in enumerate(lay)])
-            groups.append(dict(n=n, k=k, m=m, layers=lay, x_host=x.pin_memory(), x=xd, y=y, group=grp))
+            groups.append(dict(n=n, k=k, m=m, layers=lay, x_host=x.pin_memory(), x=xd, y=y, group=grp, reduce=row_parallel))
     return groups
 
 
@@ -120,6 +138,10 @@ def run_step(wf, groups, pdl: bool):
     """One pass over the sweep: every (shape, M) layer stack is one grouped launch."""
     for g in groups:
         g["group"].run(pdl=pdl)
+        if g["reduce"]:  # row-parallel stack: sum the partial outputs of all ranks (the path's only exchange)
+            import torch.distributed as dist
+
+            dist.all_reduce(g["y"])
     return len(groups)
 
 
@@ -259,7 +281,7 @@ def main():
             return
         cb, steps, wu, dt = cpu_reference_run(args.steps, warmup)
         line = {"impl": "reference", "metric": METRIC, "value": cb["value"], "unit": "GB/s", "n_gpus": args.gpus,
-                "steps": steps, "warmup": wu, "ms_per_step": dt * 1e3, "higher_is_better": True, "scaling": "weak",
+                "steps": steps, "warmup": wu, "ms_per_step": dt * 1e3, "higher_is_better": True, "scaling": "strong",
                 "vs_baseline": None, "dtype": "u8xs8->s32", "data": "synthetic", "config": config, "cpu_baseline": cb,
                 "e2e": {"value": cb["value"], "unit": "GB/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
                 "gpu_launches": 0}
@@ -360,8 +382,10 @@ def main():
         return
 
     peaks, peak_kind = measured_peaks()
-    value = world * total_bytes / (ms * 1e-3) / 1e9
-    per_launch_bytes = total_bytes / launches
+    # the whole (unsharded) sweep's algorithmic bytes over the slowest rank's time
+    full_bytes = sum(algorithmic_bytes(g["m"], g["n"], g["k"]) * len(g["layers"]) for g in groups)
+    value = full_bytes / (ms * 1e-3) / 1e9
+    per_launch_bytes = total_bytes / launches / world  # what one rank's kernel moves
     per_launch_us = ms * 1e3 / launches
     achieved = per_launch_bytes / (per_launch_us * 1e-6) / 1e9
     # per (shape, M) breakdown, each group timed alone over its own layer stack
@@ -398,12 +422,14 @@ def main():
                           "GBps_reference_accounting": round(reference_bytes(g["m"], g["n"], g["k"]) / us / 1e3, 1),
                           "us_per_launch_single_chain": round(us_single, 3)})
     line = {"metric": METRIC, "value": value, "unit": "GB/s", "n_gpus": world, "steps": args.steps, "warmup": warmup,
-            "ms_per_step": ms, "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "u8xs8->s32",
-            "data": "synthetic", "config": dict(config, pdl=pdl, graph=True, parallelism="replicas" if world > 1 else "single"),
+            "ms_per_step": ms, "higher_is_better": True, "scaling": "strong", "vs_baseline": None, "dtype": "u8xs8->s32",
+            "data": "synthetic", "config": dict(config, pdl=pdl, graph=True, parallelism=f"tp{world}" if world > 1 else "single"),
             "roofline": {"bound": "hbm", "achieved": achieved, "peak": peaks["hbm_gbs"], "unit": "GB/s",
-                         "frac": achieved / peaks["hbm_gbs"], "traffic": None, "peak_kind": peak_kind + " copy bandwidth",
+                         "frac": achieved / peaks["hbm_gbs"], "traffic": per_launch_bytes * NCU_TRAFFIC_RATIO,
+                         "traffic_source": "ncu capture of the M=1 2560x2560 group (162.3 MB DRAM for 158.27 MB algorithmic), scaled",
+                         "peak_kind": peak_kind + " copy bandwidth",
                          "kernel": "decode_kernel", "bytes_per_launch": per_launch_bytes, "us_per_launch": per_launch_us},
-            "e2e": {"value": world * total_bytes / (ms_e2e * 1e-3) / 1e9, "unit": "GB/s", "h2d_bytes_per_step": h2d,
+            "e2e": {"value": full_bytes / (ms_e2e * 1e-3) / 1e9, "unit": "GB/s", "h2d_bytes_per_step": h2d,
                     "d2h_bytes_per_step": d2h, "ms_per_step": ms_e2e},
             "gpu_launches": launches * args.steps, "clocks": clocks, "breakdown": breakdown}
     if not args.only_m and args.only_shape < 0:

@@ -1,0 +1,64 @@
+"""Tensor-parallel BitLinear on two GPUs over NCCL (skipped with fewer than two devices).  Each rank is a child
+process; the CUDA kernels run on its own GPU.  Column-parallel shards reproduce the single-GPU result exactly;
+row-parallel partial sums are checked per shard bit for bit against the oracle, the reduced output within the
+normalised tolerance."""
+import os
+import sys
+
+import numpy as np
+import pytest
+import torch
+import torch.distributed as dist
+import torch.multiprocessing as mp
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+pytestmark = pytest.mark.gpu
+
+
+def _worker(rank, world, port, results):
+    sys.path.insert(0, ROOT)
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port), NCCL_NVLS_ENABLE="0")
+    torch.cuda.set_device(rank)
+    dev = torch.device("cuda", rank)
+    dist.init_process_group("nccl", rank=rank, world_size=world, device_id=dev)
+    try:
+        from __graft_entry__ import load_package
+        from oracle import bitlinear_oracle as O
+
+        wf = load_package()
+        from wrinklefree_monorepo_b200 import tp
+
+        g = torch.Generator().manual_seed(0)
+        n, k, m = 512, 1344, 6  # K = 21 units of 64: uneven split
+        w = torch.randn(n, k, generator=g) * 0.02
+        x = torch.randn(m, k, generator=g).bfloat16()
+        codes, scale = wf.pack_ternary(w.to(dev))
+        full = wf.bitlinear(x.to(dev), codes, scale, out_dtype=torch.float32)
+
+        col = tp.ColumnParallelBitLinear(codes, scale, k, n, gather_output=True)
+        y = col(x.to(dev), out_dtype=torch.float32)
+        assert torch.equal(y, full)
+
+        row = tp.RowParallelBitLinear(codes, scale, k, n, input_is_parallel=False, reduce_dtype=torch.float32)
+        lo, hi = row.bounds[rank]
+        # this shard's integer accumulators against the oracle on the same slice
+        _, acc = wf.bitlinear(x.to(dev)[:, lo:hi].contiguous(), row.codes, scale, want_acc=True)
+        t = O.unpack_wf16(codes.cpu().numpy())[:, lo:hi]
+        q, _ = O.act_quant_per_token(x.float().numpy()[:, lo:hi], "bf16")
+        assert np.array_equal(acc.cpu().numpy(), O.int_gemm(q, t))
+        y = row(x.to(dev), out_dtype=torch.float32)
+        err = float((y - full).abs().max() / full.abs().max())
+        assert err < 2e-2, err
+        wf.device_status()
+        results[rank] = "ok"
+    finally:
+        dist.destroy_process_group()
+
+
+def test_tp2_nccl():
+    if torch.cuda.device_count() < 2:
+        pytest.skip("needs two GPUs")
+    mgr = mp.Manager()
+    results = mgr.dict()
+    mp.spawn(_worker, args=(2, 29650 + os.getpid() % 300, results), nprocs=2, join=True)
+    assert dict(results) == {0: "ok", 1: "ok"}
