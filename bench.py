@@ -254,6 +254,57 @@ def prefill_section(wf, torch, device, peaks, shapes=None, ms=None):
     return out
 
 
+# ------------------------------------------------------------------ decoder tokens/s (secondary figures)
+def decoder_section(wf, torch, device, world, full: bool):
+    """Greedy decode tokens/s of random-init ternary decoders on the BitLinear kernels (CUDA-graphed step):
+    Llama-3-8B shape at a 2048-token context for batch 1 and 32 (256 with --decoder-full), tensor-parallel over
+    the ranks; on one GPU also the SmolLM2-135M shape (batch 32, 512-token prompt, 128 steps)."""
+    from wrinklefree_monorepo_b200.decoder import LLAMA3_8B, SMOLLM2_135M, TernaryDecoder
+
+    out = []
+
+    def timed(model, steps):
+        model.graph.replay()
+        torch.cuda.synchronize()
+        a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        a.record()
+        for _ in range(steps):
+            model.graph.replay()
+            model.tok.copy_(model.next_tok)
+        b.record()
+        torch.cuda.synchronize()
+        return a.elapsed_time(b) / steps
+
+    for batch in ([1, 32, 256] if full else [1, 32]):
+        model = TernaryDecoder(LLAMA3_8B, batch, 2048, device, seed=7)
+        for L in model.layers:  # a context of 2048 random tokens' keys and values
+            L["kc"].normal_()
+            L["vc"].normal_()
+        model.pos.fill_(2047)
+        model.capture(masked=False)
+        ms = timed(model, 16)
+        by = model.weight_bytes_per_step()
+        out.append({"model": "llama3-8b-shape", "tp": world, "batch": batch, "context": 2048, "ms_per_step": round(ms, 3),
+                    "tok_s": round(batch / ms * 1e3, 1), "GB_per_step_per_rank": round(by / 1e9, 3),
+                    "GBps_per_rank": round(by / ms / 1e6, 1)})
+        del model
+        torch.cuda.empty_cache()
+    if world == 1:
+        model = TernaryDecoder(SMOLLM2_135M, 32, 640, device, seed=8)
+        g = torch.Generator().manual_seed(9)
+        ids = torch.randint(0, SMOLLM2_135M.vocab, (32, 512), generator=g).to(device)
+        torch.cuda.synchronize()
+        t0 = time.perf_counter()
+        model.prefill(ids)
+        torch.cuda.synchronize()
+        t_prefill = time.perf_counter() - t0
+        model.capture(masked=True)
+        ms = timed(model, 128)
+        out.append({"model": "smollm2-135m-shape", "tp": 1, "batch": 32, "prompt": 512, "decode_steps": 128,
+                    "prefill_ms": round(t_prefill * 1e3, 1), "ms_per_step": round(ms, 3), "tok_s": round(32 / ms * 1e3, 1)})
+    return out
+
+
 # ------------------------------------------------------------------ main
 def main():
     ap = argparse.ArgumentParser()
@@ -264,6 +315,8 @@ def main():
     ap.add_argument("--layers-scale", type=float, default=1.0, help="scale the layer stacks (profiling on a small case)")
     ap.add_argument("--no-pdl", action="store_true")
     ap.add_argument("--prefill-only", action="store_true", help="run only the prefill GEMM section (profiling)")
+    ap.add_argument("--no-decoder", action="store_true", help="skip the decoder tokens/s section")
+    ap.add_argument("--decoder-full", action="store_true", help="also batch 256 of the 8B shape")
     ap.add_argument("--only-m", type=int, default=0, help="restrict the sweep to one token batch (profiling)")
     ap.add_argument("--only-shape", type=int, default=-1, help="restrict the sweep to one shape index (profiling)")
     ap.add_argument("--no-cpu-baseline", action="store_true")
@@ -301,7 +354,9 @@ def main():
     if world > 1:
         import torch.distributed as dist
 
-        dist.init_process_group("nccl", device_id=device)
+        import datetime
+
+        dist.init_process_group("nccl", device_id=device, timeout=datetime.timedelta(seconds=90))
 
     if args.prefill_only:
         peaks, _ = measured_peaks()
@@ -376,11 +431,6 @@ def main():
         t = torch.tensor([ms, ms_e2e], device=device)
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
         ms, ms_e2e = t.tolist()
-    if rank != 0:
-        if dist is not None:
-            dist.destroy_process_group()
-        return
-
     peaks, peak_kind = measured_peaks()
     # the whole (unsharded) sweep's algorithmic bytes over the slowest rank's time
     full_bytes = sum(algorithmic_bytes(g["m"], g["n"], g["k"]) * len(g["layers"]) for g in groups)
@@ -388,7 +438,8 @@ def main():
     per_launch_bytes = total_bytes / launches / world  # what one rank's kernel moves
     per_launch_us = ms * 1e3 / launches
     achieved = per_launch_bytes / (per_launch_us * 1e-6) / 1e9
-    # per (shape, M) breakdown, each group timed alone over its own layer stack
+    # per (shape, M) breakdown, each group timed alone over its own layer stack (every rank takes part: the
+    # row-parallel groups contain the all-reduce)
     breakdown = []
     for g in groups:
         gg = [g]
@@ -421,6 +472,19 @@ def main():
                           "frac_hbm": round(by / us / 1e3 / peaks["hbm_gbs"], 4),
                           "GBps_reference_accounting": round(reference_bytes(g["m"], g["n"], g["k"]) / us / 1e3, 1),
                           "us_per_launch_single_chain": round(us_single, 3)})
+    decoder = None
+    if not args.no_decoder and not args.only_m and args.only_shape < 0:
+        for g in groups:  # free the sweep's buffers first
+            g.clear()
+        torch.cuda.empty_cache()
+        try:
+            decoder = decoder_section(wf, torch, device, world, args.decoder_full)
+        except Exception as e:  # the main line must survive a failure of this secondary section
+            decoder = [{"error": repr(e)[:300]}]
+    if rank != 0:
+        if dist is not None:
+            dist.destroy_process_group()
+        return
     line = {"metric": METRIC, "value": value, "unit": "GB/s", "n_gpus": world, "steps": args.steps, "warmup": warmup,
             "ms_per_step": ms, "higher_is_better": True, "scaling": "strong", "vs_baseline": None, "dtype": "u8xs8->s32",
             "data": "synthetic", "config": dict(config, pdl=pdl, graph=True, parallelism=f"tp{world}" if world > 1 else "single"),
@@ -432,6 +496,8 @@ def main():
             "e2e": {"value": full_bytes / (ms_e2e * 1e-3) / 1e9, "unit": "GB/s", "h2d_bytes_per_step": h2d,
                     "d2h_bytes_per_step": d2h, "ms_per_step": ms_e2e},
             "gpu_launches": launches * args.steps, "clocks": clocks, "breakdown": breakdown}
+    if decoder is not None:
+        line["decode_tok_s"] = decoder
     if not args.only_m and args.only_shape < 0:
         line["prefill_gemm"] = prefill_section(wf, torch, device, peaks)
     if not args.no_cpu_baseline and world == 1:

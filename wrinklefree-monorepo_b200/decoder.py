@@ -1,0 +1,218 @@
+"""A minimal LLaMA-style ternary decoder used to measure decode tokens/s on the BitLinear kernels.
+
+Skeleton after the reference's model (wrinklefree/models/attention.py:126-218, ffn.py:43-87, llama.py:81-238):
+RMSNorm -> q/k/v BitLinear -> RoPE -> GQA attention -> o BitLinear -> residual -> RMSNorm -> gate/up BitLinear ->
+act(gate) * up -> down BitLinear -> residual; bf16 embedding and lm_head.  Unlike the reference it keeps a bf16
+KV cache, launches q/k/v and gate/up as one grouped kernel each, and replays the whole decode step as a CUDA
+graph.  Everything that is not a BitLinear projection (norms, RoPE, attention, activation) uses stock torch
+operators: those are callers of the hot path, not part of it.
+
+Tensor parallel: heads and the MLP width are split over the ranks of a process group; q/k/v/gate/up are
+column-parallel, o/down row-parallel with one all-reduce each (the reference's plan).
+"""
+from __future__ import annotations
+
+import math
+from dataclasses import dataclass
+from typing import Optional
+
+import torch
+import torch.distributed as dist
+import torch.nn.functional as F
+
+from . import ops
+from . import tp as tpmod
+
+
+@dataclass
+class DecoderConfig:
+    layers: int
+    hidden: int
+    n_q: int
+    n_kv: int
+    head_dim: int
+    intermediate: int
+    vocab: int
+    rope_theta: float = 1e5
+    act: str = "silu"  # "silu" (SwiGLU) or "relu2" (the reference's SmolLM2 preset)
+    eps: float = 1e-5
+
+
+SMOLLM2_135M = DecoderConfig(layers=30, hidden=576, n_q=9, n_kv=3, head_dim=64, intermediate=1536, vocab=49152, rope_theta=1e5)
+LLAMA3_8B = DecoderConfig(layers=32, hidden=4096, n_q=32, n_kv=8, head_dim=128, intermediate=14336, vocab=128256, rope_theta=5e5)
+
+
+def _rms_norm(x: torch.Tensor, w: torch.Tensor, eps: float) -> torch.Tensor:
+    v = x.float()
+    return (v * torch.rsqrt(v.pow(2).mean(-1, keepdim=True) + eps)).to(x.dtype) * w
+
+
+def _rope(x: torch.Tensor, cos: torch.Tensor, sin: torch.Tensor) -> torch.Tensor:
+    """x [B, H, T, D]; cos/sin [T, D/2] (or broadcastable)."""
+    x1, x2 = x[..., : x.shape[-1] // 2], x[..., x.shape[-1] // 2 :]
+    return torch.cat([x1 * cos - x2 * sin, x2 * cos + x1 * sin], dim=-1).to(x.dtype)
+
+
+class TernaryDecoder:
+    """Random-initialised ternary decoder (weights N(0, 0.02), ternarized on the GPU)."""
+
+    def __init__(self, cfg: DecoderConfig, batch: int, max_ctx: int, device, group=None, seed: int = 0,
+                 dtype: torch.dtype = torch.bfloat16):
+        self.cfg, self.B, self.T, self.dev, self.dtype, self.group = cfg, batch, max_ctx, device, dtype, group
+        self.tp = dist.get_world_size(group) if (group is not None or dist.is_initialized()) else 1
+        self.rank = dist.get_rank(group) if (group is not None or dist.is_initialized()) else 0
+        if cfg.n_kv % self.tp or cfg.n_q % self.tp:
+            raise ValueError("heads must divide over the tensor-parallel ranks")
+        self.nq, self.nkv = cfg.n_q // self.tp, cfg.n_kv // self.tp
+        self.i_lo, self.i_hi = tpmod.shard_bounds(cfg.intermediate, self.tp, 64)[self.rank]
+        d, h = cfg.head_dim, cfg.hidden
+        gen = torch.Generator(device=device).manual_seed(seed)  # same seed on every rank: same full matrices
+
+        def ternary(n, k):
+            w = torch.randn(n, k, generator=gen, device=device, dtype=torch.float32) * 0.02
+            c, s = ops.pack_ternary(w)
+            return c, s
+
+        self.layers = []
+        for _ in range(cfg.layers):
+            L = {}
+            cq, sq = ternary(cfg.n_q * d, h)
+            ck, sk = ternary(cfg.n_kv * d, h)
+            cv, sv = ternary(cfg.n_kv * d, h)
+            co, so = ternary(h, cfg.n_q * d)
+            cg, sg = ternary(cfg.intermediate, h)
+            cu, su = ternary(cfg.intermediate, h)
+            cd, sd = ternary(h, cfg.intermediate)
+            r = self.rank
+            L["q"] = (tpmod.shard_codes_rows(cq, r * self.nq * d, (r + 1) * self.nq * d), sq)
+            L["k"] = (tpmod.shard_codes_rows(ck, r * self.nkv * d, (r + 1) * self.nkv * d), sk)
+            L["v"] = (tpmod.shard_codes_rows(cv, r * self.nkv * d, (r + 1) * self.nkv * d), sv)
+            L["o"] = (tpmod.shard_codes_k(co, r * self.nq * d, (r + 1) * self.nq * d), so)
+            L["gate"] = (tpmod.shard_codes_rows(cg, self.i_lo, self.i_hi), sg)
+            L["up"] = (tpmod.shard_codes_rows(cu, self.i_lo, self.i_hi), su)
+            L["down"] = (tpmod.shard_codes_k(cd, self.i_lo, self.i_hi), sd)
+            L["n1"] = torch.ones(h, dtype=dtype, device=device)
+            L["n2"] = torch.ones(h, dtype=dtype, device=device)
+            L["kc"] = torch.zeros(batch, self.nkv, max_ctx, d, dtype=dtype, device=device)
+            L["vc"] = torch.zeros(batch, self.nkv, max_ctx, d, dtype=dtype, device=device)
+            self.layers.append(L)
+        self.embed = (torch.randn(cfg.vocab, h, generator=gen, device=device, dtype=torch.float32) * 0.02).to(dtype)
+        self.lm_head = (torch.randn(cfg.vocab, h, generator=gen, device=device, dtype=torch.float32) * 0.02).to(dtype)
+        self.norm_f = torch.ones(h, dtype=dtype, device=device)
+        inv = 1.0 / (cfg.rope_theta ** (torch.arange(0, d, 2, device=device, dtype=torch.float32) / d))
+        ang = torch.arange(max_ctx, device=device, dtype=torch.float32)[:, None] * inv[None, :]
+        self.cos, self.sin = ang.cos(), ang.sin()
+        # static decode-step buffers (graph inputs / outputs)
+        self.tok = torch.zeros(batch, dtype=torch.long, device=device)
+        self.pos = torch.zeros((), dtype=torch.long, device=device)
+        self._step_bufs()
+        self.graph: Optional[torch.cuda.CUDAGraph] = None
+        self.next_tok = torch.zeros(batch, dtype=torch.long, device=device)
+
+    # ------------------------------------------------------------------ decode step buffers and groups
+    def _step_bufs(self):
+        cfg, B, d, dev, dt = self.cfg, self.B, self.cfg.head_dim, self.dev, self.dtype
+        for L in self.layers:
+            L["xn"] = torch.empty(B, cfg.hidden, dtype=dt, device=dev)
+            L["qkv"] = [torch.empty(B, self.nq * d, dtype=dt, device=dev), torch.empty(B, self.nkv * d, dtype=dt, device=dev),
+                        torch.empty(B, self.nkv * d, dtype=dt, device=dev)]
+            L["g_qkv"] = ops.DecodeGroup([dict(x=L["xn"], codes=L[n][0], w_scale=L[n][1], out=o)
+                                          for n, o in zip(("q", "k", "v"), L["qkv"])])
+            L["hn"] = torch.empty(B, cfg.hidden, dtype=dt, device=dev)
+            L["gu"] = [torch.empty(B, self.i_hi - self.i_lo, dtype=dt, device=dev) for _ in range(2)]
+            L["g_gu"] = ops.DecodeGroup([dict(x=L["hn"], codes=L[n][0], w_scale=L[n][1], out=o)
+                                         for n, o in zip(("gate", "up"), L["gu"])])
+
+    def _act(self, g, u):
+        return (F.silu(g) if self.cfg.act == "silu" else F.relu(g).pow(2)) * u
+
+    def _allreduce(self, y):
+        if self.tp > 1:
+            dist.all_reduce(y, group=self.group)
+        return y
+
+    def _decode_step(self):
+        """One token per sequence: reads self.tok / self.pos, writes self.next_tok; advances self.pos."""
+        cfg, B, d = self.cfg, self.B, self.cfg.head_dim
+        x = self.embed[self.tok]  # [B, hidden]
+        slot = self.pos % self.T
+        cos, sin = self.cos[slot], self.sin[slot]
+        valid = (torch.arange(self.T, device=self.dev) <= self.pos).view(1, 1, 1, self.T) if self.masked else None
+        for L in self.layers:
+            L["xn"].copy_(_rms_norm(x, L["n1"], cfg.eps))
+            q, k, v = L["g_qkv"].run()
+            q = _rope(q.view(B, self.nq, 1, d), cos, sin)
+            k = _rope(k.view(B, self.nkv, 1, d), cos, sin)
+            L["kc"].index_copy_(2, slot.view(1), k)
+            L["vc"].index_copy_(2, slot.view(1), v.view(B, self.nkv, 1, d))
+            a = F.scaled_dot_product_attention(q, L["kc"], L["vc"], attn_mask=valid, enable_gqa=True)
+            o = self._allreduce(ops.bitlinear(a.reshape(B, self.nq * d), L["o"][0], L["o"][1], path="decode"))
+            x = x + o
+            L["hn"].copy_(_rms_norm(x, L["n2"], cfg.eps))
+            g, u = L["g_gu"].run()
+            dn = self._allreduce(ops.bitlinear(self._act(g, u), L["down"][0], L["down"][1], path="decode"))
+            x = x + dn
+        logits = _rms_norm(x, self.norm_f, cfg.eps) @ self.lm_head.t()
+        self.logits = logits
+        self.next_tok.copy_(logits.argmax(-1))
+        self.pos.add_(1)
+
+    # ------------------------------------------------------------------ public
+    def prefill(self, ids: torch.Tensor):
+        """ids [B, S]: fills the KV cache for positions 0..S-1, leaves self.tok = greedy next token, pos = S."""
+        cfg, B, d = self.cfg, self.B, self.cfg.head_dim
+        S = ids.shape[1]
+        x = self.embed[ids]  # [B, S, hidden]
+        cos, sin = self.cos[:S], self.sin[:S]
+        for L in self.layers:
+            xn = _rms_norm(x, L["n1"], cfg.eps).reshape(B * S, cfg.hidden)
+            q = ops.bitlinear(xn, *L["q"]).view(B, S, self.nq, d).transpose(1, 2)
+            k = ops.bitlinear(xn, *L["k"]).view(B, S, self.nkv, d).transpose(1, 2)
+            v = ops.bitlinear(xn, *L["v"]).view(B, S, self.nkv, d).transpose(1, 2)
+            q, k = _rope(q, cos, sin), _rope(k, cos, sin)
+            L["kc"][:, :, :S] = k
+            L["vc"][:, :, :S] = v
+            a = F.scaled_dot_product_attention(q, k, v, is_causal=True, enable_gqa=True)
+            o = self._allreduce(ops.bitlinear(a.transpose(1, 2).reshape(B * S, self.nq * d), *L["o"]))
+            x = x + o.view(B, S, cfg.hidden)
+            hn = _rms_norm(x, L["n2"], cfg.eps).reshape(B * S, cfg.hidden)
+            g, u = ops.bitlinear(hn, *L["gate"]), ops.bitlinear(hn, *L["up"])
+            dn = self._allreduce(ops.bitlinear(self._act(g, u), *L["down"]))
+            x = x + dn.view(B, S, cfg.hidden)
+        logits = _rms_norm(x[:, -1], self.norm_f, cfg.eps) @ self.lm_head.t()
+        self.tok.copy_(logits.argmax(-1))
+        self.pos.fill_(S)
+        return logits
+
+    def capture(self, masked: bool = True):
+        """Warm up and capture the decode step as a CUDA graph."""
+        self.masked = masked
+        pos0, tok0 = self.pos.clone(), self.tok.clone()
+        s = torch.cuda.Stream()
+        s.wait_stream(torch.cuda.current_stream())
+        with torch.cuda.stream(s):
+            for _ in range(2):
+                self._decode_step()
+        torch.cuda.current_stream().wait_stream(s)
+        torch.cuda.synchronize()
+        self.graph = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(self.graph):
+            self._decode_step()
+        self.pos.copy_(pos0)
+        self.tok.copy_(tok0)
+
+    def decode(self, steps: int):
+        """Greedy decoding of `steps` tokens per sequence; returns [B, steps] token ids."""
+        out = []
+        for _ in range(steps):
+            self.graph.replay()
+            self.tok.copy_(self.next_tok)
+            out.append(self.next_tok.clone())
+        return torch.stack(out, 1)
+
+    def weight_bytes_per_step(self) -> int:
+        """Bytes this rank streams per decode step: packed projections + bf16 lm_head + the KV cache."""
+        cfg, d = self.cfg, self.cfg.head_dim
+        packed = sum(L[n][0].numel() for L in self.layers for n in ("q", "k", "v", "o", "gate", "up", "down"))
+        kv = 2 * len(self.layers) * self.B * self.nkv * self.T * d * 2
+        return packed + self.lm_head.numel() * 2 + kv
