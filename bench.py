@@ -474,6 +474,7 @@ def main():
                           "us_per_launch_single_chain": round(us_single, 3)})
     decoder = None
     if not args.no_decoder and not args.only_m and args.only_shape < 0:
+        graph = None
         for g in groups:  # free the sweep's buffers first
             g.clear()
         torch.cuda.empty_cache()
