@@ -135,16 +135,17 @@ class TernaryDecoder:
         """One token per sequence: reads self.tok / self.pos, writes self.next_tok; advances self.pos."""
         cfg, B, d = self.cfg, self.B, self.cfg.head_dim
         x = self.embed[self.tok]  # [B, hidden]
-        slot = self.pos % self.T
-        cos, sin = self.cos[slot], self.sin[slot]
+        slot = (self.pos % self.T).view(1)
+        # index_select keeps the position on the device (indexing with a 0-dim tensor would read it back to the host)
+        cos, sin = self.cos.index_select(0, slot), self.sin.index_select(0, slot)
         valid = (torch.arange(self.T, device=self.dev) <= self.pos).view(1, 1, 1, self.T) if self.masked else None
         for L in self.layers:
             L["xn"].copy_(_rms_norm(x, L["n1"], cfg.eps))
             q, k, v = L["g_qkv"].run()
             q = _rope(q.view(B, self.nq, 1, d), cos, sin)
             k = _rope(k.view(B, self.nkv, 1, d), cos, sin)
-            L["kc"].index_copy_(2, slot.view(1), k)
-            L["vc"].index_copy_(2, slot.view(1), v.view(B, self.nkv, 1, d))
+            L["kc"].index_copy_(2, slot, k)
+            L["vc"].index_copy_(2, slot, v.view(B, self.nkv, 1, d))
             a = F.scaled_dot_product_attention(q, L["kc"], L["vc"], attn_mask=valid, enable_gqa=True)
             o = self._allreduce(ops.bitlinear(a.reshape(B, self.nq * d), L["o"][0], L["o"][1], path="decode"))
             x = x + o
