@@ -168,7 +168,7 @@ def test_decode_against_golden(wf, name, dt):
 SHAPES = [  # (M, K, N)
     (1, 64, 16), (2, 128, 24), (3, 192, 40), (4, 576, 100), (5, 640, 16), (7, 1024, 33), (8, 2560, 64), (9, 512, 48),
     (16, 576, 1536), (17, 1088, 80), (33, 2560, 96), (64, 2560, 160), (64, 6912, 64), (70, 640, 32), (1, 6912, 2560),
-    (4, 2560, 6912), (1, 4096, 14336), (130, 256, 48),
+    (4, 2560, 6912), (1, 4096, 14336), (130, 256, 48), (32, 14336, 64), (9, 16384, 32),
 ]
 
 

@@ -336,8 +336,8 @@ __global__ void __launch_bounds__(DEC_THREADS, 1)
             consumer_sync();  // nobody still reads the multipliers / sums of the previous pass
             cur_p = pi;
             cur_chunk = chunk;
-            m0 = chunk * MT;
-            m_valid = min(MT, p.M - m0);
+            m0 = chunk * cfg.MTA;
+            m_valid = min(cfg.MTA, p.M - m0);
             quantize_tokens<XDT>(p, cfg.MTA, m0, m_valid, s_act, s_inv, s_rowsum, s_maxbits);
         }
         const int stage = n % cfg.stages;
@@ -505,7 +505,7 @@ __global__ void __launch_bounds__(STREAM_THREADS, 2)
         int pi, chunk, ritem;
         locate_item(probs, cfg.P, pre_it, pi, chunk, ritem);
         const wf_problem& p = probs[pi];
-        quantize_tokens<XDT, STREAM_THREADS>(p, cfg.MTA, chunk * MT, min(MT, p.M - chunk * MT), s_act + sgi * act_bytes, s_inv + sgi * MT,
+        quantize_tokens<XDT, STREAM_THREADS>(p, cfg.MTA, chunk * cfg.MTA, min(cfg.MTA, p.M - chunk * cfg.MTA), s_act + sgi * act_bytes, s_inv + sgi * MT,
                              s_rowsum + sgi * MT, s_maxbits + sgi * MT);
         pre_it = min(end, p._item_begin + (chunk + 1) * p._row_items);
     }
@@ -514,7 +514,7 @@ __global__ void __launch_bounds__(STREAM_THREADS, 2)
         locate_item(probs, cfg.P, it, pi, chunk, ritem);
         const wf_problem& p = probs[pi];
         const int seg_end = min(end, p._item_begin + (chunk + 1) * p._row_items);
-        const int m0 = chunk * MT, m_valid = min(MT, p.M - m0);
+        const int m0 = chunk * cfg.MTA, m_valid = min(cfg.MTA, p.M - m0);
         const int buf = seg % nbuf;
         if (seg >= nbuf) {
             consumer_sync<STREAM_THREADS>();  // every warp is done with the pass that used this buffer
@@ -702,10 +702,13 @@ static int plan_group(wf_problem* probs, int P, GroupPlan& g, bool write_fields)
     g.NT = NT;
     const int MT = NT * 8;
     g.MTA = Mmax < MT ? Mmax : MT;
+    // very large K: fewer tokens per pass, until the activations fit beside two 16-row stages
+    while (g.MTA > 1 && fixed_bytes(NT, 1) + static_cast<size_t>(g.KBmax) * g.MTA * TOK_STRIDE + 2u * 16 * pitch > SMEM_MAX)
+        g.MTA = (g.MTA + 1) / 2;
     const size_t act = (static_cast<size_t>(g.KBmax) * g.MTA * TOK_STRIDE + 127) / 128 * 128;
     // Enough 16-row items to give every consumer warp of every SM several of them: the warps work on their
     // own items.  Otherwise (a single small layer) the 16 warps of a CTA share each item and split K.
-    g.decoupled = count_items16(probs, P, MT) >= 32LL * sms && fixed_bytes(NT, 1) + act + 4u * 16 * pitch <= SMEM_STREAM_MAX;
+    g.decoupled = count_items16(probs, P, g.MTA) >= 32LL * sms && fixed_bytes(NT, 1) + act + 4u * 16 * pitch <= SMEM_STREAM_MAX;
     g.nbuf = (g.decoupled && fixed_bytes(NT, 1) + 2 * act + 6u * 16 * pitch <= SMEM_STREAM_MAX) ? 2 : 1;
     // item size: about 32 KB per stage, smaller while there are too few items to keep every SM busy
     int RI = g.decoupled ? 1 : 8;
@@ -713,7 +716,7 @@ static int plan_group(wf_problem* probs, int P, GroupPlan& g, bool write_fields)
     auto count_items = [&](int ri) {
         long long t = 0;
         for (int i = 0; i < P; ++i)
-            t += static_cast<long long>((probs[i].N + 16 * ri - 1) / (16 * ri)) * ((probs[i].M + MT - 1) / MT);
+            t += static_cast<long long>((probs[i].N + 16 * ri - 1) / (16 * ri)) * ((probs[i].M + g.MTA - 1) / g.MTA);
         return t;
     };
     while (RI > 1 && count_items(RI) < 4LL * sms) RI >>= 1;
@@ -745,7 +748,7 @@ static int plan_group(wf_problem* probs, int P, GroupPlan& g, bool write_fields)
         for (int i = 0; i < P; ++i) {
             probs[i]._item_begin = begin;
             probs[i]._row_items = (probs[i].N + 16 * RI - 1) / (16 * RI);
-            probs[i]._chunks = (probs[i].M + MT - 1) / MT;
+            probs[i]._chunks = (probs[i].M + g.MTA - 1) / g.MTA;
             begin += probs[i]._row_items * probs[i]._chunks;
             if (int rc = encode_maps(probs[i])) return rc;
         }
@@ -803,8 +806,7 @@ static int run_group(const char* who, const wf_problem* dev, wf_problem* host, i
         if (int rc = plan_group(host, P, g, false)) return rc;
         int begin = 0;
         for (int i = 0; i < P; ++i) {
-            const int MT = g.NT * 8;
-            const int ri = (host[i].N + 16 * g.RI - 1) / (16 * g.RI), ch = (host[i].M + MT - 1) / MT;
+            const int ri = (host[i].N + 16 * g.RI - 1) / (16 * g.RI), ch = (host[i].M + g.MTA - 1) / g.MTA;
             WF_REQUIRE(host[i]._item_begin == begin && host[i]._row_items == ri && host[i]._chunks == ch,
                        "%s: problem %d was not prepared by wf_bitlinear_decode_plan (or was changed afterwards)", who, i);
             begin += ri * ch;
