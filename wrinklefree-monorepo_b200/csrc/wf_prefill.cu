@@ -4,15 +4,15 @@
 //   acc[tok, n] = sum_k q[tok, k] * code[n, k]      (u8 codes = w + 1, s8 activations, s32 accumulate in TMEM)
 //   y[tok, n]   = (float(acc - rowsum[tok]) * inv_sx[tok]) * s_w + bias[n]
 //
-// One CTA computes a tile of 128 tokens x 256 weight rows.  Per 128-wide block of K:
-//   * warp 0 (one lane) issues two TMA loads: the int8 activation tile (128 tokens x 128 bytes,
-//     128-byte swizzle, the MMA's A operand) and the PACKED weight tile (256 rows x 32 bytes);
-//   * warps 2-5 expand the packed tile to int8 (one mask + shift per four weights) and store it
-//     K-major with the 128-byte swizzle pattern, as the MMA's B operand;
-//   * warp 1 (one lane) issues four tcgen05.mma.kind::i8 (M=128, N=256, K=32) into the TMEM accumulator
-//     and commits them to the barrier that frees the stage.
-// After the last block, warps 2-5 read the accumulator with tcgen05.ld (lane = token), apply the integer
-// correction and the fp32 rescale, and store y.  Every mbarrier wait is bounded.
+// Persistent CTAs (one per SM) walk over tiles of 128 tokens x 256 weight rows.  Per 128-wide block of K:
+//   * warp 0 (one lane) issues two TMA loads into a 4-deep ring: the int8 activation tile (128 tokens x
+//     128 bytes, 128-byte swizzle, the MMA's A operand) and the PACKED weight tile (256 rows x 32 bytes);
+//   * warps 2-5 expand the packed tile to int8 (one mask + shift per four weights) and store it K-major with
+//     the 128-byte swizzle pattern into a 3-deep ring, as the MMA's B operand;
+//   * warp 1 (one lane) issues four tcgen05.mma.kind::i8 (M=128, N=256, K=32) into one of two TMEM
+//     accumulators and commits them to the barriers that free the ring slots.
+// Warps 6-9 read a finished accumulator with tcgen05.ld (lane = token), apply the integer correction and the
+// fp32 rescale and store y while the next tile's MMAs fill the other accumulator.  Every mbarrier wait is bounded.
 #include <cuda.h>
 
 #include "wf_common.cuh"
@@ -30,15 +30,16 @@ int wf_check_linear_args(const char* who, const void* x, int x_dtype, int64_t ld
 namespace wf {
 
 constexpr int PF_BM = 128;      // tokens per tile (TMEM lanes)
-constexpr int PF_BN = 256;      // weight rows per tile (TMEM columns)
+constexpr int PF_BN = 256;      // weight rows per tile (TMEM columns of one accumulator)
 constexpr int PF_BK = 128;      // K per stage
-constexpr int PF_STAGES = 3;
-constexpr int PF_THREADS = 192; // warp 0 TMA, warp 1 MMA, warps 2-5 expand + epilogue
+constexpr int PF_TS = 4;        // stages of the TMA ring (activation tile + packed weight tile)
+constexpr int PF_BS = 3;        // stages of the expanded-weight ring
+constexpr int PF_THREADS = 320; // warp 0 TMA, warp 1 MMA, warps 2-5 expand, warps 6-9 epilogue
 constexpr int PF_A_BYTES = PF_BM * PF_BK;        // 16 KB
 constexpr int PF_P_BYTES = PF_BN * PF_BK / 4;    // 8 KB packed
 constexpr int PF_B_BYTES = PF_BN * PF_BK;        // 32 KB expanded
-constexpr int PF_STAGE_BYTES = PF_A_BYTES + PF_P_BYTES + PF_B_BYTES;
-constexpr size_t PF_SMEM = 1024 /*align slack*/ + PF_STAGES * PF_STAGE_BYTES + 256 /*barriers*/;
+constexpr int PF_T_BYTES = PF_A_BYTES + PF_P_BYTES;
+constexpr size_t PF_SMEM = 1024 /*align slack*/ + PF_TS * PF_T_BYTES + PF_BS * PF_B_BYTES + 256 /*barriers*/;
 
 struct PrefillParams {
     const float* x_scale;   // [M] per-token multipliers (nullable: 1)
@@ -52,6 +53,9 @@ struct PrefillParams {
     int64_t ldy;
     int32_t* acc_out;
     int M, N, K, layout;
+    int batch;            // independent problems stacked along rows: tokens [batch*M, K], weights [batch*N, K/4]
+    int w_scale_stride;   // floats between the weight scales of consecutive problems
+    int tiles_m, tiles_n; // per problem
 };
 
 __device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory"); }
@@ -123,35 +127,50 @@ __device__ __forceinline__ void expand_row(uint32_t packed_addr, uint32_t tile_a
     }
 }
 
+// Persistent kernel: CTA c computes tiles c, c + grid, ...  A tile = 128 tokens x 256 weight rows of one problem.
+// Rings and barriers (every wait bounded):
+//   TMA ring (PF_TS):  t_full[s]  <- TMA bytes;         t_empty[s] <- MMA commit (A read) + 4 expansion warps (packed read)
+//   B ring   (PF_BS):  b_full[s]  <- 4 expansion warps;  b_empty[s] <- MMA commit
+//   accumulators (2):  acc_full[a] <- MMA commit after the last K block; acc_empty[a] <- 4 epilogue warps
 __global__ void __launch_bounds__(PF_THREADS, 1)
     prefill_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_p, const PrefillParams p) {
     extern __shared__ uint8_t smem_raw[];
     // operand tiles need 1024-byte alignment for the 128-byte swizzle
     uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~static_cast<uintptr_t>(1023));
-    uint8_t* bars = smem + PF_STAGES * PF_STAGE_BYTES;
-    uint64_t* tma_full = reinterpret_cast<uint64_t*>(bars);           // [S] TMA bytes landed
-    uint64_t* b_full = tma_full + PF_STAGES;                          // [S] expansion written
-    uint64_t* mma_done = b_full + PF_STAGES;                          // [S] MMAs of the stage retired
-    uint64_t* acc_full = mma_done + PF_STAGES;                        // accumulator complete
-    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(acc_full + 1);
+    uint8_t* t_ring = smem;                              // [PF_TS][A 16 KB | packed 8 KB]
+    uint8_t* b_ring = smem + PF_TS * PF_T_BYTES;         // [PF_BS][32 KB]
+    uint64_t* t_full = reinterpret_cast<uint64_t*>(b_ring + PF_BS * PF_B_BYTES);
+    uint64_t* t_empty = t_full + PF_TS;
+    uint64_t* b_full = t_empty + PF_TS;
+    uint64_t* b_empty = b_full + PF_BS;
+    uint64_t* acc_full = b_empty + PF_BS;
+    uint64_t* acc_empty = acc_full + 2;
+    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(acc_empty + 2);
     volatile int* poisoned = reinterpret_cast<volatile int*>(tmem_slot + 1);
 
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
-    const int m0 = blockIdx.y * PF_BM, n0 = blockIdx.x * PF_BN;
     const int kblocks = (p.K + PF_BK - 1) / PF_BK;
+    const int tiles_per_problem = p.tiles_m * p.tiles_n;
+    const int total_tiles = tiles_per_problem * p.batch;
 
     if (tid == 0) {
-        for (int s = 0; s < PF_STAGES; ++s) {
-            mbar_init(&tma_full[s], 1);
-            mbar_init(&b_full[s], 4);  // one arrival per expansion warp
-            mbar_init(&mma_done[s], 1);
+        for (int s = 0; s < PF_TS; ++s) {
+            mbar_init(&t_full[s], 1);
+            mbar_init(&t_empty[s], 5);
         }
-        mbar_init(acc_full, 1);
+        for (int s = 0; s < PF_BS; ++s) {
+            mbar_init(&b_full[s], 4);
+            mbar_init(&b_empty[s], 1);
+        }
+        for (int a = 0; a < 2; ++a) {
+            mbar_init(&acc_full[a], 1);
+            mbar_init(&acc_empty[a], 4);
+        }
         *poisoned = 0;
         asm volatile("fence.mbarrier_init.release.cluster;\n" ::: "memory");
     }
-    if (warp == 1) {  // TMEM: 256 columns of 128 lanes hold the 128 x 256 int32 accumulator
-        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;\n" ::"r"(smem_u32(tmem_slot)), "r"(PF_BN));
+    if (warp == 1) {  // all 512 TMEM columns: two 128 x 256 int32 accumulators
+        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;\n" ::"r"(smem_u32(tmem_slot)), "r"(2 * PF_BN));
         asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;\n" ::);
     }
     tc_fence_before();
@@ -159,15 +178,26 @@ __global__ void __launch_bounds__(PF_THREADS, 1)
     tc_fence_after();
     const uint32_t tmem_base = *tmem_slot;
 
+    // tile -> (problem z, token block, row block); row blocks vary fastest so neighbouring CTAs share activations
+#define PF_TILE_COORDS(t)                                  \
+    const int z = (t) / tiles_per_problem;                 \
+    const int tm = ((t) % tiles_per_problem) / p.tiles_n;  \
+    const int tn = (t) % p.tiles_n;
+
     if (warp == 0) {
         if (lane == 0) {
-            for (int kb = 0; kb < kblocks; ++kb) {
-                const int s = kb % PF_STAGES;
-                if (kb >= PF_STAGES) mbar_wait(&mma_done[s], ((kb / PF_STAGES) - 1) & 1, poisoned);
-                uint8_t* st = smem + s * PF_STAGE_BYTES;
-                mbar_expect_tx(&tma_full[s], PF_A_BYTES + PF_P_BYTES);
-                tma_load_2d(st, &tmap_a, kb * PF_BK, m0, &tma_full[s]);
-                tma_load_2d(st + PF_A_BYTES, &tmap_p, kb * (PF_BK / 4), n0, &tma_full[s]);
+            int it = 0;
+            for (int t = blockIdx.x; t < total_tiles; t += gridDim.x) {
+                PF_TILE_COORDS(t)
+                const int row_a = z * p.M + tm * PF_BM, row_w = z * p.N + tn * PF_BN;
+                for (int kb = 0; kb < kblocks; ++kb, ++it) {
+                    const int s = it % PF_TS;
+                    if (it >= PF_TS) mbar_wait(&t_empty[s], ((it / PF_TS) - 1) & 1, poisoned);
+                    uint8_t* st = t_ring + s * PF_T_BYTES;
+                    mbar_expect_tx(&t_full[s], PF_T_BYTES);
+                    tma_load_2d(st, &tmap_a, kb * PF_BK, row_a, &t_full[s]);
+                    tma_load_2d(st + PF_A_BYTES, &tmap_p, kb * (PF_BK / 4), row_w, &t_full[s]);
+                }
             }
         }
     } else if (warp == 1) {
@@ -175,98 +205,126 @@ __global__ void __launch_bounds__(PF_THREADS, 1)
             // instruction descriptor: D = s32, A = signed 8-bit, B = unsigned 8-bit, both K-major, N = 256, M = 128
             const uint32_t idesc = (2u << 4) | (1u << 7) | (0u << 10) | (static_cast<uint32_t>(PF_BN >> 3) << 17) |
                                    (static_cast<uint32_t>(PF_BM >> 4) << 24);
-            for (int kb = 0; kb < kblocks; ++kb) {
-                const int s = kb % PF_STAGES;
-                const unsigned par = (kb / PF_STAGES) & 1;
-                mbar_wait(&tma_full[s], par, poisoned);
-                mbar_wait(&b_full[s], par, poisoned);
+            int it = 0, nt = 0;
+            for (int t = blockIdx.x; t < total_tiles; t += gridDim.x, ++nt) {
+                const int a = nt & 1;
+                if (nt >= 2) mbar_wait(&acc_empty[a], ((nt >> 1) - 1) & 1, poisoned);  // epilogue drained this accumulator
                 tc_fence_after();
-                const uint32_t a_addr = smem_u32(smem + s * PF_STAGE_BYTES);
-                const uint32_t b_addr = a_addr + PF_A_BYTES + PF_P_BYTES;
-                const uint64_t a_desc = smem_desc_sw128(a_addr), b_desc = smem_desc_sw128(b_addr);
+                const uint32_t d_tmem = tmem_base + a * PF_BN;
+                for (int kb = 0; kb < kblocks; ++kb, ++it) {
+                    const int ts = it % PF_TS, bs = it % PF_BS;
+                    mbar_wait(&t_full[ts], (it / PF_TS) & 1, poisoned);
+                    mbar_wait(&b_full[bs], (it / PF_BS) & 1, poisoned);
+                    tc_fence_after();
+                    const uint64_t a_desc = smem_desc_sw128(smem_u32(t_ring + ts * PF_T_BYTES));
+                    const uint64_t b_desc = smem_desc_sw128(smem_u32(b_ring + bs * PF_B_BYTES));
 #pragma unroll
-                for (int k = 0; k < PF_BK / 32; ++k)  // 32 bytes of K per MMA: advance the start address by 2 x 16 bytes
-                    mma_i8(tmem_base, a_desc + 2 * k, b_desc + 2 * k, idesc, (kb | k) ? 1u : 0u);
-                tc_commit(&mma_done[s]);
+                    for (int k = 0; k < PF_BK / 32; ++k)  // 32 bytes of K per MMA: advance the start address by 2 x 16 bytes
+                        mma_i8(d_tmem, a_desc + 2 * k, b_desc + 2 * k, idesc, (kb | k) ? 1u : 0u);
+                    tc_commit(&t_empty[ts]);
+                    tc_commit(&b_empty[bs]);
+                }
+                tc_commit(&acc_full[a]);
             }
-            tc_commit(acc_full);
         }
-    } else {
+    } else if (warp < 6) {
         // ---- expansion: 128 threads, two weight rows each per K block
         const int et = tid - 64;  // 0..127
-        for (int kb = 0; kb < kblocks; ++kb) {
-            const int s = kb % PF_STAGES;
-            mbar_wait(&tma_full[s], (kb / PF_STAGES) & 1, poisoned);
-            const uint32_t packed = smem_u32(smem + s * PF_STAGE_BYTES + PF_A_BYTES);
-            const uint32_t tile = packed + PF_P_BYTES;
-            expand_row(packed + et * 32, tile, et, p.layout);
-            expand_row(packed + (et + 128) * 32, tile, et + 128, p.layout);
-            asm volatile("fence.proxy.async.shared::cta;\n" ::: "memory");  // generic writes -> visible to the tensor core
-            __syncwarp();
-            if (lane == 0) mbar_arrive(&b_full[s]);
-        }
-        // ---- epilogue: this warp owns TMEM lanes 32 * (warp % 4) .. + 31, lane = token
-        mbar_wait(acc_full, 0, poisoned);
-        tc_fence_after();
-        const int lane_grp = (warp & 3) * 32;
-        const int tok = m0 + lane_grp + lane;
-        const bool tok_ok = tok < p.M;
-        const float s_w = p.w_scale ? __ldg(p.w_scale) : p.w_scale_host;
-        const float inv = tok_ok ? (p.x_scale ? __frcp_rn(p.x_scale[tok]) : 1.0f) : 0.f;
-        const int rs = tok_ok ? p.rowsum[tok] : 0;
-        const bool vec_ok = (p.ldy * (p.y_dtype == WF_F32 ? 4 : 2)) % 16 == 0 && reinterpret_cast<uintptr_t>(p.y) % 16 == 0;
-        for (int c0 = 0; c0 < PF_BN; c0 += 32) {
-            uint32_t v[32];
-            tmem_ld32(tmem_base + (static_cast<uint32_t>(lane_grp) << 16) + c0, v);
-            if (!tok_ok) continue;
-            const int nb = n0 + c0;
-            float o[32];
-#pragma unroll
-            for (int j = 0; j < 32; ++j) {
-                const int a = static_cast<int>(v[j]) - rs;
-                o[j] = rescale(a, inv, s_w);
-                if (p.bias && nb + j < p.N) o[j] = __fadd_rn(o[j], load1_rt(p.bias, p.bias_dtype, nb + j));
-                v[j] = static_cast<uint32_t>(a);
-            }
-            if (vec_ok && nb + 32 <= p.N) {
-                // 32 consecutive outputs of one token: 128-bit stores
-                if (p.y_dtype == WF_F32) {
-                    float4* dst = reinterpret_cast<float4*>(static_cast<float*>(p.y) + static_cast<int64_t>(tok) * p.ldy + nb);
-#pragma unroll
-                    for (int j = 0; j < 8; ++j) dst[j] = make_float4(o[4 * j], o[4 * j + 1], o[4 * j + 2], o[4 * j + 3]);
-                } else {
-                    uint32_t h[16];
-#pragma unroll
-                    for (int j = 0; j < 16; ++j) {
-                        if (p.y_dtype == WF_BF16) {
-                            __nv_bfloat162 t2 = __floats2bfloat162_rn(o[2 * j], o[2 * j + 1]);
-                            h[j] = *reinterpret_cast<uint32_t*>(&t2);
-                        } else {
-                            __half2 t2 = __floats2half2_rn(o[2 * j], o[2 * j + 1]);
-                            h[j] = *reinterpret_cast<uint32_t*>(&t2);
-                        }
-                    }
-                    uint4* dst = reinterpret_cast<uint4*>(static_cast<uint16_t*>(p.y) + static_cast<int64_t>(tok) * p.ldy + nb);
-#pragma unroll
-                    for (int j = 0; j < 4; ++j) dst[j] = make_uint4(h[4 * j], h[4 * j + 1], h[4 * j + 2], h[4 * j + 3]);
+        int it = 0;
+        for (int t = blockIdx.x; t < total_tiles; t += gridDim.x) {
+            for (int kb = 0; kb < kblocks; ++kb, ++it) {
+                const int ts = it % PF_TS, bs = it % PF_BS;
+                mbar_wait(&t_full[ts], (it / PF_TS) & 1, poisoned);
+                if (it >= PF_BS) mbar_wait(&b_empty[bs], ((it / PF_BS) - 1) & 1, poisoned);
+                const uint32_t packed = smem_u32(t_ring + ts * PF_T_BYTES + PF_A_BYTES);
+                const uint32_t tile = smem_u32(b_ring + bs * PF_B_BYTES);
+                expand_row(packed + et * 32, tile, et, p.layout);
+                expand_row(packed + (et + 128) * 32, tile, et + 128, p.layout);
+                asm volatile("fence.proxy.async.shared::cta;\n" ::: "memory");  // generic writes -> visible to the tensor core
+                __syncwarp();
+                if (lane == 0) {
+                    mbar_arrive(&b_full[bs]);
+                    mbar_arrive(&t_empty[ts]);  // the packed tile has been read
                 }
-            } else {
-#pragma unroll
-                for (int j = 0; j < 32; ++j)
-                    if (nb + j < p.N) store1_rt(p.y, p.y_dtype, static_cast<int64_t>(tok) * p.ldy + nb + j, o[j]);
             }
-            if (p.acc_out) {
+        }
+    } else {
+        // ---- epilogue: warp w owns TMEM lanes 32 * (w % 4) .. + 31, lane = token
+        const int lane_grp = (warp & 3) * 32;
+        int nt = 0;
+        for (int t = blockIdx.x; t < total_tiles; t += gridDim.x, ++nt) {
+            PF_TILE_COORDS(t)
+            const int a = nt & 1;
+            mbar_wait(&acc_full[a], (nt >> 1) & 1, poisoned);
+            tc_fence_after();
+            const int tok_in = tm * PF_BM + lane_grp + lane;  // token inside its problem
+            const bool tok_ok = tok_in < p.M;
+            const int64_t tok = static_cast<int64_t>(z) * p.M + tok_in;  // row of the stacked outputs
+            const float s_w = p.w_scale ? __ldg(p.w_scale + static_cast<int64_t>(z) * p.w_scale_stride) : p.w_scale_host;
+            const float inv = tok_ok ? (p.x_scale ? __frcp_rn(p.x_scale[tok]) : 1.0f) : 0.f;
+            const int rs = tok_ok ? p.rowsum[tok] : 0;
+            const bool vec_ok = (p.ldy * (p.y_dtype == WF_F32 ? 4 : 2)) % 16 == 0 && reinterpret_cast<uintptr_t>(p.y) % 16 == 0;
+            const int n0 = tn * PF_BN;
+            for (int c0 = 0; c0 < PF_BN; c0 += 32) {
+                uint32_t v[32];
+                tmem_ld32(tmem_base + (static_cast<uint32_t>(lane_grp) << 16) + a * PF_BN + c0, v);
+                if (c0 + 32 == PF_BN) {  // the accumulator is in registers: hand it back to the MMA warp
+                    tc_fence_before();
+                    __syncwarp();
+                    if (lane == 0) mbar_arrive(&acc_empty[a]);
+                }
+                if (!tok_ok) continue;
+                const int nb = n0 + c0;
+                if (nb >= p.N) continue;
+                float o[32];
 #pragma unroll
-                for (int j = 0; j < 32; ++j)
-                    if (nb + j < p.N) p.acc_out[static_cast<int64_t>(tok) * p.N + nb + j] = static_cast<int>(v[j]);
+                for (int j = 0; j < 32; ++j) {
+                    const int acc = static_cast<int>(v[j]) - rs;
+                    o[j] = rescale(acc, inv, s_w);
+                    if (p.bias && nb + j < p.N) o[j] = __fadd_rn(o[j], load1_rt(p.bias, p.bias_dtype, nb + j));
+                    v[j] = static_cast<uint32_t>(acc);
+                }
+                if (vec_ok && nb + 32 <= p.N) {
+                    // 32 consecutive outputs of one token: 128-bit stores
+                    if (p.y_dtype == WF_F32) {
+                        float4* dst = reinterpret_cast<float4*>(static_cast<float*>(p.y) + tok * p.ldy + nb);
+#pragma unroll
+                        for (int j = 0; j < 8; ++j) dst[j] = make_float4(o[4 * j], o[4 * j + 1], o[4 * j + 2], o[4 * j + 3]);
+                    } else {
+                        uint32_t h[16];
+#pragma unroll
+                        for (int j = 0; j < 16; ++j) {
+                            if (p.y_dtype == WF_BF16) {
+                                __nv_bfloat162 t2 = __floats2bfloat162_rn(o[2 * j], o[2 * j + 1]);
+                                h[j] = *reinterpret_cast<uint32_t*>(&t2);
+                            } else {
+                                __half2 t2 = __floats2half2_rn(o[2 * j], o[2 * j + 1]);
+                                h[j] = *reinterpret_cast<uint32_t*>(&t2);
+                            }
+                        }
+                        uint4* dst = reinterpret_cast<uint4*>(static_cast<uint16_t*>(p.y) + tok * p.ldy + nb);
+#pragma unroll
+                        for (int j = 0; j < 4; ++j) dst[j] = make_uint4(h[4 * j], h[4 * j + 1], h[4 * j + 2], h[4 * j + 3]);
+                    }
+                } else {
+#pragma unroll
+                    for (int j = 0; j < 32; ++j)
+                        if (nb + j < p.N) store1_rt(p.y, p.y_dtype, tok * p.ldy + nb + j, o[j]);
+                }
+                if (p.acc_out) {
+#pragma unroll
+                    for (int j = 0; j < 32; ++j)
+                        if (nb + j < p.N) p.acc_out[tok * p.N + nb + j] = static_cast<int>(v[j]);
+                }
             }
         }
     }
+#undef PF_TILE_COORDS
     tc_fence_before();
     __syncthreads();
     if (warp == 1) {
         tc_fence_after();
-        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;\n" ::"r"(tmem_base), "r"(PF_BN));
+        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;\n" ::"r"(tmem_base), "r"(2 * PF_BN));
     }
 }
 
@@ -388,12 +446,20 @@ extern "C" int wf_bitlinear_prefill(const void* x, int x_dtype, int64_t ldx, con
     pp.x_scale = qs; pp.rowsum = wsum; pp.w_scale = w_scale; pp.w_scale_host = w_scale_host; pp.bias = bias;
     pp.bias_dtype = bias_dtype; pp.y = y; pp.y_dtype = y_dtype; pp.ldy = ldy; pp.acc_out = acc_out;
     pp.M = static_cast<int>(M); pp.N = static_cast<int>(N); pp.K = static_cast<int>(K); pp.layout = layout;
+    pp.batch = 1; pp.w_scale_stride = 0;
+    pp.tiles_m = static_cast<int>((M + PF_BM - 1) / PF_BM);
+    pp.tiles_n = static_cast<int>((N + PF_BN - 1) / PF_BN);
     static thread_local bool configured = false;
+    static thread_local int sms = 148;
     if (!configured) {
         WF_CUDA(cudaFuncSetAttribute(prefill_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(PF_SMEM)));
+        int dev = 0;
+        WF_CUDA(cudaGetDevice(&dev));
+        WF_CUDA(cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev));
         configured = true;
     }
-    dim3 grid(static_cast<unsigned>((N + PF_BN - 1) / PF_BN), static_cast<unsigned>((M + PF_BM - 1) / PF_BM));
+    const long long tiles = static_cast<long long>(pp.tiles_m) * pp.tiles_n * pp.batch;
+    dim3 grid(static_cast<unsigned>(tiles < sms ? tiles : sms));
     prefill_kernel<<<grid, PF_THREADS, PF_SMEM, st>>>(tmap_a, tmap_p, pp);
     WF_CUDA(cudaGetLastError());
     return WF_OK;
