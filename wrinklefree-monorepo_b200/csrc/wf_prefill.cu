@@ -7,11 +7,11 @@
 // Persistent CTAs (one per SM) walk over tiles of 128 tokens x 256 weight rows.  Per 128-wide block of K:
 //   * warp 0 (one lane) issues two TMA loads into a 4-deep ring: the int8 activation tile (128 tokens x
 //     128 bytes, 128-byte swizzle, the MMA's A operand) and the PACKED weight tile (256 rows x 32 bytes);
-//   * warps 2-5 expand the packed tile to int8 (one mask + shift per four weights) and store it K-major with
+//   * warps 2-9 expand the packed tile to int8 (one mask + shift per four weights) and store it K-major with
 //     the 128-byte swizzle pattern into a 3-deep ring, as the MMA's B operand;
 //   * warp 1 (one lane) issues four tcgen05.mma.kind::i8 (M=128, N=256, K=32) into one of two TMEM
 //     accumulators and commits them to the barriers that free the ring slots.
-// Warps 6-9 read a finished accumulator with tcgen05.ld (lane = token), apply the integer correction and the
+// Warps 10-13 read a finished accumulator with tcgen05.ld (lane = token), apply the integer correction and the
 // fp32 rescale and store y while the next tile's MMAs fill the other accumulator.  Every mbarrier wait is bounded.
 #include <cuda.h>
 
@@ -34,7 +34,8 @@ constexpr int PF_BN = 256;      // weight rows per tile (TMEM columns of one acc
 constexpr int PF_BK = 128;      // K per stage
 constexpr int PF_TS = 4;        // stages of the TMA ring (activation tile + packed weight tile)
 constexpr int PF_BS = 3;        // stages of the expanded-weight ring
-constexpr int PF_THREADS = 320; // warp 0 TMA, warp 1 MMA, warps 2-5 expand, warps 6-9 epilogue
+constexpr int PF_EW = 8;         // expansion warps: 256 threads, one weight row each per K block
+constexpr int PF_THREADS = 64 + PF_EW * 32 + 128;  // warp 0 TMA, warp 1 MMA, warps 2-9 expand, warps 10-13 epilogue
 constexpr int PF_A_BYTES = PF_BM * PF_BK;        // 16 KB
 constexpr int PF_P_BYTES = PF_BN * PF_BK / 4;    // 8 KB packed
 constexpr int PF_B_BYTES = PF_BN * PF_BK;        // 32 KB expanded
@@ -129,8 +130,8 @@ __device__ __forceinline__ void expand_row(uint32_t packed_addr, uint32_t tile_a
 
 // Persistent kernel: CTA c computes tiles c, c + grid, ...  A tile = 128 tokens x 256 weight rows of one problem.
 // Rings and barriers (every wait bounded):
-//   TMA ring (PF_TS):  t_full[s]  <- TMA bytes;         t_empty[s] <- MMA commit (A read) + 4 expansion warps (packed read)
-//   B ring   (PF_BS):  b_full[s]  <- 4 expansion warps;  b_empty[s] <- MMA commit
+//   TMA ring (PF_TS):  t_full[s]  <- TMA bytes;         t_empty[s] <- MMA commit (A read) + the expansion warps (packed read)
+//   B ring   (PF_BS):  b_full[s]  <- the expansion warps;  b_empty[s] <- MMA commit
 //   accumulators (2):  acc_full[a] <- MMA commit after the last K block; acc_empty[a] <- 4 epilogue warps
 __global__ void __launch_bounds__(PF_THREADS, 1)
     prefill_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_p, const PrefillParams p) {
@@ -156,10 +157,10 @@ __global__ void __launch_bounds__(PF_THREADS, 1)
     if (tid == 0) {
         for (int s = 0; s < PF_TS; ++s) {
             mbar_init(&t_full[s], 1);
-            mbar_init(&t_empty[s], 5);
+            mbar_init(&t_empty[s], 1 + PF_EW);
         }
         for (int s = 0; s < PF_BS; ++s) {
-            mbar_init(&b_full[s], 4);
+            mbar_init(&b_full[s], PF_EW);
             mbar_init(&b_empty[s], 1);
         }
         for (int a = 0; a < 2; ++a) {
@@ -227,9 +228,9 @@ __global__ void __launch_bounds__(PF_THREADS, 1)
                 tc_commit(&acc_full[a]);
             }
         }
-    } else if (warp < 6) {
-        // ---- expansion: 128 threads, two weight rows each per K block
-        const int et = tid - 64;  // 0..127
+    } else if (warp < 2 + PF_EW) {
+        // ---- expansion: 256 threads, one weight row each per K block
+        const int et = tid - 64;  // 0..255
         int it = 0;
         for (int t = blockIdx.x; t < total_tiles; t += gridDim.x) {
             for (int kb = 0; kb < kblocks; ++kb, ++it) {
@@ -239,7 +240,6 @@ __global__ void __launch_bounds__(PF_THREADS, 1)
                 const uint32_t packed = smem_u32(t_ring + ts * PF_T_BYTES + PF_A_BYTES);
                 const uint32_t tile = smem_u32(b_ring + bs * PF_B_BYTES);
                 expand_row(packed + et * 32, tile, et, p.layout);
-                expand_row(packed + (et + 128) * 32, tile, et + 128, p.layout);
                 asm volatile("fence.proxy.async.shared::cta;\n" ::: "memory");  // generic writes -> visible to the tensor core
                 __syncwarp();
                 if (lane == 0) {
