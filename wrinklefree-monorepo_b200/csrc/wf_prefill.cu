@@ -5,13 +5,13 @@
 //   y[tok, n]   = (float(acc - rowsum[tok]) * inv_sx[tok]) * s_w + bias[n]
 //
 // Persistent CTAs (one per SM) walk over tiles of 128 tokens x 256 weight rows.  Per 128-wide block of K:
-//   * warp 0 (one lane) issues two TMA loads into a 4-deep ring: the int8 activation tile (128 tokens x
+//   * warps 0-1 (one lane each, alternating K blocks) issue two TMA loads into a 4-deep ring: the int8 activation tile (128 tokens x
 //     128 bytes, 128-byte swizzle, the MMA's A operand) and the PACKED weight tile (256 rows x 32 bytes);
-//   * warps 2-9 expand the packed tile to int8 (one mask + shift per four weights) and store it K-major with
+//   * warps 3-10 expand the packed tile to int8 (one mask + shift per four weights) and store it K-major with
 //     the 128-byte swizzle pattern into a 3-deep ring, as the MMA's B operand;
-//   * warp 1 (one lane) issues four tcgen05.mma.kind::i8 (M=128, N=256, K=32) into one of two TMEM
+//   * warp 2 (one lane) issues four tcgen05.mma.kind::i8 (M=128, N=256, K=32) into one of two TMEM
 //     accumulators and commits them to the barriers that free the ring slots.
-// Warps 10-13 read a finished accumulator with tcgen05.ld (lane = token), apply the integer correction and the
+// Warps 11-14 read a finished accumulator with tcgen05.ld (lane = token), apply the integer correction and the
 // fp32 rescale and store y while the next tile's MMAs fill the other accumulator.  Every mbarrier wait is bounded.
 #include <cuda.h>
 
@@ -35,7 +35,8 @@ constexpr int PF_BK = 128;      // K per stage
 constexpr int PF_TS = 4;        // stages of the TMA ring (activation tile + packed weight tile)
 constexpr int PF_BS = 3;        // stages of the expanded-weight ring
 constexpr int PF_EW = 8;         // expansion warps: 256 threads, one weight row each per K block
-constexpr int PF_THREADS = 64 + PF_EW * 32 + 128;  // warp 0 TMA, warp 1 MMA, warps 2-9 expand, warps 10-13 epilogue
+constexpr int PF_PW = 2;         // TMA producer warps (one lane each): K blocks are dealt round-robin
+constexpr int PF_THREADS = (PF_PW + 1 + PF_EW + 4) * 32;  // warps 0-1 TMA, warp 2 MMA, warps 3-10 expand, warps 11-14 epilogue
 constexpr int PF_A_BYTES = PF_BM * PF_BK;        // 16 KB
 constexpr int PF_P_BYTES = PF_BN * PF_BK / 4;    // 8 KB packed
 constexpr int PF_B_BYTES = PF_BN * PF_BK;        // 32 KB expanded
@@ -170,7 +171,7 @@ __global__ void __launch_bounds__(PF_THREADS, 1)
         *poisoned = 0;
         asm volatile("fence.mbarrier_init.release.cluster;\n" ::: "memory");
     }
-    if (warp == 1) {  // all 512 TMEM columns: two 128 x 256 int32 accumulators
+    if (warp == PF_PW) {  // all 512 TMEM columns: two 128 x 256 int32 accumulators
         asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;\n" ::"r"(smem_u32(tmem_slot)), "r"(2 * PF_BN));
         asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;\n" ::);
     }
@@ -185,13 +186,15 @@ __global__ void __launch_bounds__(PF_THREADS, 1)
     const int tm = ((t) % tiles_per_problem) / p.tiles_n;  \
     const int tn = (t) % p.tiles_n;
 
-    if (warp == 0) {
+    if (warp < PF_PW) {
+        // one thread cannot wait, arm and issue once per 512 tensor-core clocks: the producers alternate
         if (lane == 0) {
             int it = 0;
             for (int t = blockIdx.x; t < total_tiles; t += gridDim.x) {
                 PF_TILE_COORDS(t)
                 const int row_a = z * p.M + tm * PF_BM, row_w = z * p.N + tn * PF_BN;
                 for (int kb = 0; kb < kblocks; ++kb, ++it) {
+                    if (it % PF_PW != warp) continue;
                     const int s = it % PF_TS;
                     if (it >= PF_TS) mbar_wait(&t_empty[s], ((it / PF_TS) - 1) & 1, poisoned);
                     uint8_t* st = t_ring + s * PF_T_BYTES;
@@ -201,7 +204,7 @@ __global__ void __launch_bounds__(PF_THREADS, 1)
                 }
             }
         }
-    } else if (warp == 1) {
+    } else if (warp == PF_PW) {
         if (lane == 0) {
             // instruction descriptor: D = s32, A = signed 8-bit, B = unsigned 8-bit, both K-major, N = 256, M = 128
             const uint32_t idesc = (2u << 4) | (1u << 7) | (0u << 10) | (static_cast<uint32_t>(PF_BN >> 3) << 17) |
@@ -214,7 +217,7 @@ __global__ void __launch_bounds__(PF_THREADS, 1)
                 const uint32_t d_tmem = tmem_base + a * PF_BN;
                 for (int kb = 0; kb < kblocks; ++kb, ++it) {
                     const int ts = it % PF_TS, bs = it % PF_BS;
-                    mbar_wait(&t_full[ts], (it / PF_TS) & 1, poisoned);
+                    // b_full implies t_full: the expansion warps waited for the TMA bytes of this block before writing B
                     mbar_wait(&b_full[bs], (it / PF_BS) & 1, poisoned);
                     tc_fence_after();
                     const uint64_t a_desc = smem_desc_sw128(smem_u32(t_ring + ts * PF_T_BYTES));
@@ -228,9 +231,9 @@ __global__ void __launch_bounds__(PF_THREADS, 1)
                 tc_commit(&acc_full[a]);
             }
         }
-    } else if (warp < 2 + PF_EW) {
+    } else if (warp < PF_PW + 1 + PF_EW) {
         // ---- expansion: 256 threads, one weight row each per K block
-        const int et = tid - 64;  // 0..255
+        const int et = tid - (PF_PW + 1) * 32;  // 0..255
         int it = 0;
         for (int t = blockIdx.x; t < total_tiles; t += gridDim.x) {
             for (int kb = 0; kb < kblocks; ++kb, ++it) {
@@ -322,7 +325,7 @@ __global__ void __launch_bounds__(PF_THREADS, 1)
 #undef PF_TILE_COORDS
     tc_fence_before();
     __syncthreads();
-    if (warp == 1) {
+    if (warp == PF_PW) {
         tc_fence_after();
         asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;\n" ::"r"(tmem_base), "r"(2 * PF_BN));
     }
