@@ -106,25 +106,27 @@ __device__ __forceinline__ uint4 lds128p(uint32_t addr) {
     return v;
 }
 
-// Expands the 32 packed bytes of one weight row (128 weights) into 128 int8 bytes stored as row `r` of a
-// K-major tile with 128-byte swizzle (16-byte chunk c of the row lands at chunk c ^ (r & 7)).
-__device__ __forceinline__ void expand_row(uint32_t packed_addr, uint32_t tile_addr, int r, int layout) {
-    const uint4 p0 = lds128p(packed_addr), p1 = lds128p(packed_addr + 16);
-    const uint32_t w[8] = {p0.x, p0.y, p0.z, p0.w, p1.x, p1.y, p1.z, p1.w};
+// Expands one 16-byte half of a packed weight row (64 weights) into four 16-byte chunks of int8 stored in
+// row `r` of a K-major tile with 128-byte swizzle (chunk c of the row lands at chunk c ^ (r & 7)).
+// Consecutive lanes take consecutive 16-byte pieces of the packed tile, so the loads are conflict-free.
+__device__ __forceinline__ void expand_half(uint32_t packed_addr, uint32_t tile_addr, int r, int h, int layout) {
+    const uint4 pk = lds128p(packed_addr);
+    const uint32_t w[4] = {pk.x, pk.y, pk.z, pk.w};
     const uint32_t row = tile_addr + r * 128;
     const uint32_t m = 0x03030303u;
     const int x = r & 7;
     if (layout == WF_LAYOUT_WF16) {
-        // word c holds weights 16c..16c+15: bit pair j of byte b = weight 16c + 4j + b
+        // word i of this half holds weights 64h + 16i .. + 15: bit pair j of byte b = weight + 4j + b
 #pragma unroll
-        for (int c = 0; c < 8; ++c)
-            sts128(row + ((c ^ x) << 4), w[c] & m, (w[c] >> 2) & m, (w[c] >> 4) & m, (w[c] >> 6) & m);
+        for (int i = 0; i < 4; ++i)
+            sts128(row + (((4 * h + i) ^ x) << 4), w[i] & m, (w[i] >> 2) & m, (w[i] >> 4) & m, (w[i] >> 6) & m);
     } else {
-        // I2_S: byte j bits 7:6, 5:4, 3:2, 1:0 = weights j, j+32, j+64, j+96; chunk c covers weights 16c..16c+15
+        // I2_S: byte j of the row's 32 bytes holds weights j, j+32, j+64, j+96 at bits 7:6, 5:4, 3:2, 1:0;
+        // this half (bytes 16h .. 16h+15) therefore feeds chunks 2g + h, g = 0..3
 #pragma unroll
-        for (int c = 0; c < 8; ++c) {
-            const int sh = 6 - 2 * (c >> 1), wb = 4 * (c & 1);
-            sts128(row + ((c ^ x) << 4), (w[wb] >> sh) & m, (w[wb + 1] >> sh) & m, (w[wb + 2] >> sh) & m, (w[wb + 3] >> sh) & m);
+        for (int g = 0; g < 4; ++g) {
+            const int sh = 6 - 2 * g;
+            sts128(row + (((2 * g + h) ^ x) << 4), (w[0] >> sh) & m, (w[1] >> sh) & m, (w[2] >> sh) & m, (w[3] >> sh) & m);
         }
     }
 }
@@ -232,7 +234,7 @@ __global__ void __launch_bounds__(PF_THREADS, 1)
             }
         }
     } else if (warp < PF_PW + 1 + PF_EW) {
-        // ---- expansion: 256 threads, one weight row each per K block
+        // ---- expansion: 256 threads, two half rows (16 packed bytes) each per K block
         const int et = tid - (PF_PW + 1) * 32;  // 0..255
         int it = 0;
         for (int t = blockIdx.x; t < total_tiles; t += gridDim.x) {
@@ -242,7 +244,8 @@ __global__ void __launch_bounds__(PF_THREADS, 1)
                 if (it >= PF_BS) mbar_wait(&b_empty[bs], ((it / PF_BS) - 1) & 1, poisoned);
                 const uint32_t packed = smem_u32(t_ring + ts * PF_T_BYTES + PF_A_BYTES);
                 const uint32_t tile = smem_u32(b_ring + bs * PF_B_BYTES);
-                expand_row(packed + et * 32, tile, et, p.layout);
+                expand_half(packed + et * 16, tile, et >> 1, et & 1, p.layout);
+                expand_half(packed + (et + 256) * 16, tile, 128 + (et >> 1), et & 1, p.layout);
                 asm volatile("fence.proxy.async.shared::cta;\n" ::: "memory");  // generic writes -> visible to the tensor core
                 __syncwarp();
                 if (lane == 0) {
