@@ -34,6 +34,7 @@ SHAPES = [(2560, 2560), (6912, 2560), (2560, 6912)]  # (N, K)
 BATCHES = [1, 4, 16, 64]
 LAYERS = {(2560, 2560): 96, (6912, 2560): 40, (2560, 6912): 40}  # distinct weight matrices per shape
 METRIC = "ternary_decode_gemv_GBps"
+GEMM_MIN_M = 16  # token batches from here on run on the tensor-core contraction (one batched launch per layer stack)
 NCU_TRAFFIC_RATIO = 162.28 / 158.27  # dram bytes / algorithmic bytes, profiles/decode_stream_kernel_m1_2560x2560.md
 
 
@@ -108,14 +109,16 @@ def build_workload(wf, torch, device, rank: int, world: int, layers_scale: float
         row_parallel = world > 1 and k > n
         g = torch.Generator(device="cpu").manual_seed(1000 * si)
         gd = torch.Generator(device=device).manual_seed(1000 * si)
-        lay = []
         n_loc, k_lo, k_hi = n, 0, k
         if world > 1 and not row_parallel:
             r_lo, r_hi = tp.shard_bounds(n, world, 16)[rank]
             n_loc = r_hi - r_lo
         if row_parallel:
             k_lo, k_hi = tp.shard_bounds(k, world, 64)[rank]
-        for _ in range(nl):
+        # the layers of a stack live in one contiguous buffer so that the batched contraction can walk them
+        codes_stack = torch.empty(nl, n_loc, (k_hi - k_lo) // 4, dtype=torch.uint8, device=device)
+        scales_stack = torch.empty(nl, 2, dtype=torch.float32, device=device)
+        for li in range(nl):
             w = torch.randn(n, k, generator=gd, device=device, dtype=torch.float32) * 0.02
             codes, scale = wf.pack_ternary(w)  # one per-tensor scale for the whole matrix, then shard
             del w
@@ -123,26 +126,33 @@ def build_workload(wf, torch, device, rank: int, world: int, layers_scale: float
                 codes = tp.shard_codes_rows(codes, r_lo, r_hi)
             elif row_parallel:
                 codes = tp.shard_codes_k(codes, k_lo, k_hi)
-            lay.append((codes, scale))
+            codes_stack[li].copy_(codes)
+            scales_stack[li].copy_(scale)
+        lay = [(codes_stack[li], scales_stack[li]) for li in range(nl)]
         for m in BATCHES:
             x = torch.randn(nl, m, k, generator=g, dtype=torch.float32)
             x = gi.with_outliers(x, seed=1000 * si + m).to(torch.bfloat16)[..., k_lo:k_hi].contiguous()
             xd = x.to(device)
             y = torch.empty(nl, m, n_loc, dtype=torch.bfloat16, device=device)
-            grp = wf.DecodeGroup([dict(x=xd[li], codes=c, w_scale=s, out=y[li]) for li, (c, s) in enumerate(lay)])
-            groups.append(dict(n=n, k=k, m=m, layers=lay, x_host=x.pin_memory(), x=xd, y=y, group=grp, reduce=row_parallel))
+            batched = m >= GEMM_MIN_M
+            grp = None if batched else wf.DecodeGroup([dict(x=xd[li], codes=c, w_scale=s, out=y[li]) for li, (c, s) in enumerate(lay)])
+            groups.append(dict(n=n, k=k, m=m, layers=lay, x_host=x.pin_memory(), x=xd, y=y, group=grp, reduce=row_parallel,
+                               batched=batched, codes_stack=codes_stack, scales_stack=scales_stack))
     return groups
 
 
 def run_step(wf, groups, pdl: bool):
     """One pass over the sweep: every (shape, M) layer stack is one grouped launch."""
     for g in groups:
-        g["group"].run(pdl=pdl)
+        if g["batched"]:
+            wf.bitlinear_batched(g["x"], g["codes_stack"], g["scales_stack"], out=g["y"])
+        else:
+            g["group"].run(pdl=pdl)
         if g["reduce"]:  # row-parallel stack: sum the partial outputs of all ranks (the path's only exchange)
             import torch.distributed as dist
 
             dist.all_reduce(g["y"])
-    return len(groups)
+    return sum(2 if g["batched"] else 1 for g in groups)  # batched = quantization kernel + contraction
 
 
 def run_step_single(wf, groups, pdl: bool):
@@ -379,7 +389,7 @@ def main():
         pdl = False
         torch.cuda.synchronize()
         graph = capture(torch, lambda: run_step(wf, groups, pdl))
-    launches = len(groups)
+    launches = sum(2 if g["batched"] else 1 for g in groups)
     total_bytes = step_bytes(groups)
 
     def barrier():
@@ -435,9 +445,37 @@ def main():
     # the whole (unsharded) sweep's algorithmic bytes over the slowest rank's time
     full_bytes = sum(algorithmic_bytes(g["m"], g["n"], g["k"]) * len(g["layers"]) for g in groups)
     value = full_bytes / (ms * 1e-3) / 1e9
-    per_launch_bytes = total_bytes / launches / world  # what one rank's kernel moves
-    per_launch_us = ms * 1e3 / launches
-    achieved = per_launch_bytes / (per_launch_us * 1e-6) / 1e9
+    # roofline of the HBM-bound kernel of the path (the fused quantize + GEMV decode kernel): its launches of the step
+    # (the M < GEMM_MIN_M groups), timed on their own with CUDA events; the M >= GEMM_MIN_M groups run on the tensor-core
+    # contraction and are reported under "roofline_gemm"
+    dec_groups = [g for g in groups if not g["batched"]]
+    gemm_groups = [g for g in groups if g["batched"]]
+
+    def time_groups(gs):
+        if not gs:
+            return None
+        gr = capture(torch, lambda: run_step(wf, gs, pdl))
+        for _ in range(3):
+            gr.replay()
+        barrier()
+        a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        a.record()
+        for _ in range(args.steps):
+            gr.replay()
+        b.record()
+        barrier()
+        t = a.elapsed_time(b) / args.steps
+        if dist is not None:
+            tt = torch.tensor([t], device=device)
+            dist.all_reduce(tt, op=dist.ReduceOp.MAX)
+            t = tt.item()
+        return t
+
+    ms_dec, ms_gemm = time_groups(dec_groups), time_groups(gemm_groups)
+    dec_launches = max(1, len(dec_groups))
+    per_launch_bytes = step_bytes(dec_groups) / dec_launches / world if dec_groups else 0.0  # what one rank's kernel moves
+    per_launch_us = (ms_dec or 0.0) * 1e3 / dec_launches
+    achieved = per_launch_bytes / (per_launch_us * 1e-6) / 1e9 if dec_groups else 0.0
     # per (shape, M) breakdown, each group timed alone over its own layer stack (every rank takes part: the
     # row-parallel groups contain the all-reduce)
     breakdown = []
@@ -493,10 +531,20 @@ def main():
                          "frac": achieved / peaks["hbm_gbs"], "traffic": per_launch_bytes * NCU_TRAFFIC_RATIO,
                          "traffic_source": "ncu capture of the M=1 2560x2560 group (162.3 MB DRAM for 158.27 MB algorithmic), scaled",
                          "peak_kind": peak_kind + " copy bandwidth",
-                         "kernel": "decode_kernel", "bytes_per_launch": per_launch_bytes, "us_per_launch": per_launch_us},
+                         "kernel": "decode_stream_kernel", "launches": f"the {dec_launches} grouped launches with M < {GEMM_MIN_M}",
+                         "bytes_per_launch": per_launch_bytes, "us_per_launch": per_launch_us},
             "e2e": {"value": full_bytes / (ms_e2e * 1e-3) / 1e9, "unit": "GB/s", "h2d_bytes_per_step": h2d,
                     "d2h_bytes_per_step": d2h, "ms_per_step": ms_e2e},
             "gpu_launches": launches * args.steps, "clocks": clocks, "breakdown": breakdown}
+    if gemm_groups and ms_gemm:
+        ops_step = sum(2.0 * g["m"] * g["n"] * g["k"] * len(g["layers"]) for g in gemm_groups)
+        tops = ops_step / (ms_gemm * 1e-3) / 1e12
+        line["roofline_gemm"] = {"bound": "tensor", "kernel": "prefill_kernel (batched over each layer stack)",
+                                 "launches": f"the {len(gemm_groups)} stacks with M >= {GEMM_MIN_M}", "achieved": tops,
+                                 "unit": "TOPS", "peak": 2 * peaks["bf16_tflops"],
+                                 "peak_kind": "2 x measured bf16 burst (int8 dense proxy; nominal 4500)",
+                                 "frac": tops / (2 * peaks["bf16_tflops"]), "ms": ms_gemm,
+                                 "note": "useful ops 2*M*N*K; the 128-token MMA tile is partly padding at M = 16 and 64"}
     if decoder is not None:
         line["decode_tok_s"] = decoder
     if not args.only_m and args.only_shape < 0:

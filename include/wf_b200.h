@@ -199,6 +199,20 @@ int wf_bitlinear_prefill(const void* x, int x_dtype, int64_t ldx, const float* x
                          void* y, int y_dtype, int64_t ldy, int32_t* acc_out, int64_t M, int64_t N, int64_t K,
                          float eps, void* workspace, size_t workspace_bytes, unsigned flags, void* stream);
 
+/*
+ * `batch` independent layers of one shape in one launch of the tensor-core contraction (a stack of layers, the
+ * experts of a mixture, or the same projection of several model replicas).  Rows are stacked: x is
+ * [batch * M, K] (row stride ldx), codes [batch * N, K/4], y [batch * M, N] (row stride ldy); layer z multiplies
+ * tokens z*M .. z*M+M-1 with weight rows z*N .. z*N+N-1 and uses the scale w_scale[z * w_scale_stride].
+ * acc_out (nullable) is [batch * M, N].  workspace: wf_prefill_workspace_bytes(batch * M, K) bytes.
+ * Replaces the per-layer loop over bitnet_gemm_cpu
+ * (packages/inference/extern/sglang-bitnet/sgl-kernel/csrc/cpu/torch_extension_cpu.cpp:370-407).
+ */
+int wf_bitlinear_prefill_batched(const void* x, int x_dtype, int64_t ldx, const uint8_t* codes, int layout,
+                                 const float* w_scale, int64_t w_scale_stride, void* y, int y_dtype, int64_t ldy,
+                                 int32_t* acc_out, int64_t batch, int64_t M, int64_t N, int64_t K, float eps,
+                                 void* workspace, size_t workspace_bytes, void* stream);
+
 #ifdef __cplusplus
 }
 #endif

@@ -436,3 +436,20 @@ def test_grouped_throughput_mode_equals_single_calls(wf, oracle_c, m, dt):
         assert torch.equal(a1, a2)
         assert torch.equal(y1, y2)
     wf.device_status()
+
+
+def test_batched_prefill_equals_per_layer_calls(wf, oracle_c):
+    """Stacked layers in one tensor-core launch: every layer's accumulators equal the oracle's."""
+    rng = np.random.default_rng(91)
+    for (b, m, k, n) in ((3, 64, 512, 200), (5, 16, 576, 256), (2, 130, 256, 300)):
+        t = rng.integers(-1, 2, size=(b, n, k)).astype(np.int8)
+        x = torch.from_numpy(rng.standard_normal((b, m, k)).astype(np.float32)).bfloat16()
+        codes = torch.stack([wf.pack_codes(torch.from_numpy(t[i]).to(DEV)) for i in range(b)]).contiguous()
+        scales = torch.tensor([[0.01 * (i + 1), 0.0] for i in range(b)], device=DEV)
+        y, acc = wf.bitlinear_batched(x.to(DEV), codes, scales, out_dtype=torch.float32, want_acc=True)
+        for i in range(b):
+            q, s = oracle_c.act_quant(x[i].float().numpy(), 1)
+            acc_o = oracle_c.int_gemm(q, t[i])
+            assert np.array_equal(acc[i].cpu().numpy(), acc_o), (b, m, k, n, i)
+            assert np.array_equal(y[i].cpu().numpy(), oracle_c.rescale(acc_o, s, np.float32(0.01 * (i + 1))))
+    wf.device_status()

@@ -21,6 +21,7 @@ from .ops import (  # noqa: F401
     device_status,
     act_quant_i8,
     bitlinear,
+    bitlinear_batched,
     bitnet_gemm,
     bitnet_gemv,
     check_kernel_available,

@@ -63,6 +63,8 @@ _SIGNATURES = {
     "wf_prefill_workspace_bytes": (_sz, [_i64, _i64]),
     "wf_bitlinear_prefill": (_int, [_p, _int, _i64, _p, _p, _int, _p, _f32, _p, _int, _p, _int, _i64, _p, _i64, _i64, _i64,
                                     _f32, _p, _sz, _u32, _p]),
+    "wf_bitlinear_prefill_batched": (_int, [_p, _int, _i64, _p, _int, _p, _i64, _p, _int, _i64, _p, _i64, _i64, _i64, _i64, _f32,
+                                            _p, _sz, _p]),
 }
 
 _lib = None

@@ -392,14 +392,16 @@ extern "C" size_t wf_prefill_workspace_bytes(int64_t M, int64_t K) {
     return align_up(static_cast<size_t>(M) * K, 256) + 2 * align_up(static_cast<size_t>(M) * 4, 256);
 }
 
-extern "C" int wf_bitlinear_prefill(const void* x, int x_dtype, int64_t ldx, const float* x_scale, const uint8_t* codes,
-                                    int layout, const float* w_scale, float w_scale_host, const void* bias, int bias_dtype,
-                                    void* y, int y_dtype, int64_t ldy, int32_t* acc_out, int64_t M, int64_t N, int64_t K,
-                                    float eps, void* workspace, size_t workspace_bytes, unsigned flags, void* stream) {
-    (void)flags;
-    if (int rc = wf_check_linear_args("wf_bitlinear_prefill", x, x_dtype, ldx, x_scale, codes, layout, bias, bias_dtype, y,
-                                      y_dtype, ldy, M, N, K))
+// `batch` independent problems stacked along the rows: tokens [batch*M, K], weights [batch*N, K/4],
+// outputs [batch*M, N]; problem z uses the weight scale w_scale[z * w_scale_stride].
+static int prefill_impl(const char* who, const void* x, int x_dtype, int64_t ldx, const float* x_scale, const uint8_t* codes,
+                        int layout, const float* w_scale, int64_t w_scale_stride, float w_scale_host, const void* bias,
+                        int bias_dtype, void* y, int y_dtype, int64_t ldy, int32_t* acc_out, int64_t batch, int64_t M_one,
+                        int64_t N, int64_t K, float eps, void* workspace, size_t workspace_bytes, void* stream) {
+    const int64_t M = batch * M_one;  // rows of the stacked activations
+    if (int rc = wf_check_linear_args(who, x, x_dtype, ldx, x_scale, codes, layout, bias, bias_dtype, y, y_dtype, ldy, M, N, K))
         return rc;
+    WF_REQUIRE(batch >= 1 && batch * N < (1LL << 31), "%s: batch out of range", who);
     WF_REQUIRE(workspace && reinterpret_cast<uintptr_t>(workspace) % 256 == 0, "wf_bitlinear_prefill: workspace must be 256-byte aligned");
     if (workspace_bytes < wf_prefill_workspace_bytes(M, K))
         return fail(WF_E_SCRATCH, "wf_bitlinear_prefill: workspace of %zu bytes, need %zu", workspace_bytes,
@@ -440,7 +442,7 @@ extern "C" int wf_bitlinear_prefill(const void* x, int x_dtype, int64_t ldx, con
         if (r != CUDA_SUCCESS) return fail(WF_E_DEVICE, "cuTensorMapEncodeTiled (activations) failed with %d", (int)r);
     }
     {
-        const cuuint64_t dims[2] = {static_cast<cuuint64_t>(K / 4), static_cast<cuuint64_t>(N)};
+        const cuuint64_t dims[2] = {static_cast<cuuint64_t>(K / 4), static_cast<cuuint64_t>(batch * N)};
         const cuuint64_t strides[1] = {static_cast<cuuint64_t>(K / 4)};
         const cuuint32_t box[2] = {PF_BK / 4, PF_BN};
         CUresult r = enc(&tmap_p, CU_TENSOR_MAP_DATA_TYPE_UINT8, 2, const_cast<uint8_t*>(codes), dims, strides, box, ones,
@@ -451,9 +453,9 @@ extern "C" int wf_bitlinear_prefill(const void* x, int x_dtype, int64_t ldx, con
     PrefillParams pp;
     pp.x_scale = qs; pp.rowsum = wsum; pp.w_scale = w_scale; pp.w_scale_host = w_scale_host; pp.bias = bias;
     pp.bias_dtype = bias_dtype; pp.y = y; pp.y_dtype = y_dtype; pp.ldy = ldy; pp.acc_out = acc_out;
-    pp.M = static_cast<int>(M); pp.N = static_cast<int>(N); pp.K = static_cast<int>(K); pp.layout = layout;
-    pp.batch = 1; pp.w_scale_stride = 0;
-    pp.tiles_m = static_cast<int>((M + PF_BM - 1) / PF_BM);
+    pp.M = static_cast<int>(M_one); pp.N = static_cast<int>(N); pp.K = static_cast<int>(K); pp.layout = layout;
+    pp.batch = static_cast<int>(batch); pp.w_scale_stride = static_cast<int>(w_scale_stride);
+    pp.tiles_m = static_cast<int>((M_one + PF_BM - 1) / PF_BM);
     pp.tiles_n = static_cast<int>((N + PF_BN - 1) / PF_BN);
     static thread_local bool configured = false;
     static thread_local int sms = 148;
@@ -469,4 +471,23 @@ extern "C" int wf_bitlinear_prefill(const void* x, int x_dtype, int64_t ldx, con
     prefill_kernel<<<grid, PF_THREADS, PF_SMEM, st>>>(tmap_a, tmap_p, pp);
     WF_CUDA(cudaGetLastError());
     return WF_OK;
+}
+
+extern "C" int wf_bitlinear_prefill(const void* x, int x_dtype, int64_t ldx, const float* x_scale, const uint8_t* codes,
+                                    int layout, const float* w_scale, float w_scale_host, const void* bias, int bias_dtype,
+                                    void* y, int y_dtype, int64_t ldy, int32_t* acc_out, int64_t M, int64_t N, int64_t K,
+                                    float eps, void* workspace, size_t workspace_bytes, unsigned flags, void* stream) {
+    (void)flags;
+    return prefill_impl("wf_bitlinear_prefill", x, x_dtype, ldx, x_scale, codes, layout, w_scale, 0, w_scale_host, bias,
+                        bias_dtype, y, y_dtype, ldy, acc_out, 1, M, N, K, eps, workspace, workspace_bytes, stream);
+}
+
+extern "C" int wf_bitlinear_prefill_batched(const void* x, int x_dtype, int64_t ldx, const uint8_t* codes, int layout,
+                                            const float* w_scale, int64_t w_scale_stride, void* y, int y_dtype, int64_t ldy,
+                                            int32_t* acc_out, int64_t batch, int64_t M, int64_t N, int64_t K, float eps,
+                                            void* workspace, size_t workspace_bytes, void* stream) {
+    WF_REQUIRE(w_scale, "wf_bitlinear_prefill_batched: w_scale must point to the per-problem scales");
+    WF_REQUIRE(x_dtype != WF_I8, "wf_bitlinear_prefill_batched: takes floating-point activations");
+    return prefill_impl("wf_bitlinear_prefill_batched", x, x_dtype, ldx, nullptr, codes, layout, w_scale, w_scale_stride, 0.f,
+                        nullptr, 0, y, y_dtype, ldy, acc_out, batch, M, N, K, eps, workspace, workspace_bytes, stream);
 }

@@ -206,6 +206,35 @@ def bitlinear(x: torch.Tensor, codes: torch.Tensor, w_scale, bias: Optional[torc
     return (y, acc) if want_acc else y
 
 
+def bitlinear_batched(x: torch.Tensor, codes: torch.Tensor, w_scales: torch.Tensor, out: Optional[torch.Tensor] = None,
+                      out_dtype: Optional[torch.dtype] = None, layout: int = L.LAYOUT_WF16, eps: float = 1e-5,
+                      want_acc: bool = False):
+    """A stack of `B` independent BitLinear layers of one shape in one tensor-core launch.
+
+    x [B, M, K] (contiguous), codes uint8 [B, N, K/4] (contiguous), w_scales float32 [B] or [B, 2] (first column used).
+    Returns y [B, M, N] (and the int32 accumulators when want_acc).
+    """
+    _need_cuda(x, codes, w_scales)
+    b, m, k = x.shape
+    n = codes.shape[1]
+    if codes.shape != (b, n, k // 4) or not codes.is_contiguous() or not x.is_contiguous():
+        raise ValueError("bitlinear_batched needs contiguous x [B, M, K] and codes [B, N, K/4]")
+    if w_scales.dtype != torch.float32 or w_scales.shape[0] != b:
+        raise ValueError("w_scales must be float32 with one row per layer")
+    y = out if out is not None else torch.empty((b, m, n), dtype=out_dtype or x.dtype, device=x.device)
+    if not y.is_contiguous():
+        raise ValueError("out must be contiguous")
+    acc = torch.empty((b * m, n), dtype=torch.int32, device=x.device) if want_acc else None
+    lib = L.lib()
+    nbytes = lib.wf_prefill_workspace_bytes(b * m, k)
+    ws = _workspace(x.device, nbytes)
+    with torch.cuda.device(x.device):
+        L.check(lib.wf_bitlinear_prefill_batched(x.data_ptr(), _DT[x.dtype], k, codes.data_ptr(), layout, w_scales.data_ptr(),
+                                                 w_scales.stride(0), y.data_ptr(), _DT[y.dtype], n, _ptr(acc), b, m, n, k, eps,
+                                                 ws.data_ptr(), ws.numel(), _stream()), "wf_bitlinear_prefill_batched")
+    return (y, acc.view(b, m, n)) if want_acc else y
+
+
 class DecodeGroup:
     """Several independent BitLinear problems run as one persistent kernel (q/k/v, gate/up, or a
     stack of layers).  Build once, `run()` any number of times; the tensors given at construction
