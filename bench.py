@@ -472,6 +472,8 @@ def main():
         return t
 
     ms_dec, ms_gemm = time_groups(dec_groups), time_groups(gemm_groups)
+    gemm_ops = sum(2.0 * g["m"] * g["n"] * g["k"] * len(g["layers"]) for g in gemm_groups)
+    n_gemm_groups = len(gemm_groups)
     dec_launches = max(1, len(dec_groups))
     per_launch_bytes = step_bytes(dec_groups) / dec_launches / world if dec_groups else 0.0  # what one rank's kernel moves
     per_launch_us = (ms_dec or 0.0) * 1e3 / dec_launches
@@ -536,11 +538,10 @@ def main():
             "e2e": {"value": full_bytes / (ms_e2e * 1e-3) / 1e9, "unit": "GB/s", "h2d_bytes_per_step": h2d,
                     "d2h_bytes_per_step": d2h, "ms_per_step": ms_e2e},
             "gpu_launches": launches * args.steps, "clocks": clocks, "breakdown": breakdown}
-    if gemm_groups and ms_gemm:
-        ops_step = sum(2.0 * g["m"] * g["n"] * g["k"] * len(g["layers"]) for g in gemm_groups)
-        tops = ops_step / (ms_gemm * 1e-3) / 1e12
+    if n_gemm_groups and ms_gemm:
+        tops = gemm_ops / (ms_gemm * 1e-3) / 1e12
         line["roofline_gemm"] = {"bound": "tensor", "kernel": "prefill_kernel (batched over each layer stack)",
-                                 "launches": f"the {len(gemm_groups)} stacks with M >= {GEMM_MIN_M}", "achieved": tops,
+                                 "launches": f"the {n_gemm_groups} stacks with M >= {GEMM_MIN_M}", "achieved": tops,
                                  "unit": "TOPS", "peak": 2 * peaks["bf16_tflops"],
                                  "peak_kind": "2 x measured bf16 burst (int8 dense proxy; nominal 4500)",
                                  "frac": tops / (2 * peaks["bf16_tflops"]), "ms": ms_gemm,
