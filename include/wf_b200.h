@@ -157,7 +157,7 @@ int wf_bitlinear_decode(const void* x, int x_dtype, int64_t ldx, const float* x_
  *
  * Fields have the meaning of the wf_bitlinear_decode arguments of the same name.  All problems of a group
  * share x_dtype.  The fields starting with an underscore are filled by wf_bitlinear_decode_plan.
- * The struct is 384 bytes and both copies must start on a 64-byte boundary (it embeds TMA descriptors).
+ * The struct is 576 bytes and both copies must start on a 64-byte boundary (it embeds TMA descriptors).
  * Use: fill a host array, call wf_bitlinear_decode_plan on it, copy it unchanged to device memory
  * (it must stay there while the kernel runs; it may be reused for any number of launches), then call
  * wf_bitlinear_decode_grouped with both copies.
@@ -180,7 +180,9 @@ typedef struct WF_ALIGN64 wf_problem {
     int32_t x_dtype, y_dtype, bias_dtype, layout;
     float w_scale_host, eps;
     int32_t _item_begin, _row_items, _chunks, _kb_full, _tail_bytes; /* 128 bytes up to here */
-    uint64_t _tmap_main[16]; /* TMA descriptor: [K/512 blocks][N rows][128 bytes] view of codes */
+    int32_t _kb_seg, _ksegs, _pad[14]; /* K is streamed in _ksegs segments of _kb_seg 512-weight blocks */
+    uint64_t _tmap_main[16]; /* TMA descriptor: [K/512 blocks][N rows][128 bytes] view of codes, box of _kb_seg blocks */
+    uint64_t _tmap_last[16]; /* the same view with the (shorter) box of the last segment */
     uint64_t _tmap_tail[16]; /* TMA descriptor of the last, partial 128-byte column block (if any) */
 } wf_problem;
 

@@ -30,10 +30,11 @@ class Problem(C.Structure):
                 ("x_dtype", C.c_int32), ("y_dtype", C.c_int32), ("bias_dtype", C.c_int32), ("layout", C.c_int32),
                 ("w_scale_host", _f32), ("eps", _f32),
                 ("_item_begin", C.c_int32), ("_row_items", C.c_int32), ("_chunks", C.c_int32), ("_kb_full", C.c_int32),
-                ("_tail_bytes", C.c_int32), ("_tmap_main", C.c_uint64 * 16), ("_tmap_tail", C.c_uint64 * 16)]
+                ("_tail_bytes", C.c_int32), ("_kb_seg", C.c_int32), ("_ksegs", C.c_int32), ("_pad", C.c_int32 * 14),
+                ("_tmap_main", C.c_uint64 * 16), ("_tmap_last", C.c_uint64 * 16), ("_tmap_tail", C.c_uint64 * 16)]
 
 
-assert C.sizeof(Problem) == 384
+assert C.sizeof(Problem) == 576
 
 
 def aligned_problem_array(n: int):

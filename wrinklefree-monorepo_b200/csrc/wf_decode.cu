@@ -229,6 +229,32 @@ __device__ __forceinline__ void compute_unit(uint32_t w_r0, uint32_t w_r1, uint3
     }
 }
 
+
+// One K segment of one 16-row tile -> `dst` (consecutive 2 KB tiles, one per 512-weight block of the segment).
+// Returns the bytes that will arrive.  Segment s covers blocks [s * _kb_seg, min(KB, (s + 1) * _kb_seg)); full
+// blocks come through the 3-D view (box of _kb_seg blocks, or the shorter box of the last segment), the partial
+// last block of K through its own 2-D view.
+__device__ __forceinline__ unsigned segment_bytes(const wf_problem* p, int seg) {
+    const int KB = (p->K + 511) >> 9;
+    const int lo = seg * p->_kb_seg;
+    const int n = min(KB - lo, p->_kb_seg);
+    return static_cast<unsigned>(n) * TILE_BYTES;
+}
+__device__ __forceinline__ void issue_segment(const wf_problem* p, int row, int seg, uint8_t* dst, uint64_t* bar) {
+    const int KB = (p->K + 511) >> 9, kbf = p->_kb_full, lo = seg * p->_kb_seg;
+    const int n = min(KB - lo, p->_kb_seg);
+    if (kbf > 0) {
+        const int nfull = max(0, min(kbf - lo, p->_kb_seg));
+        if (nfull == p->_kb_seg)
+            tma_load_3d(dst, p->_tmap_main, 0, row, lo, bar);
+        else if (nfull > 0)
+            tma_load_3d(dst, p->_tmap_last, 0, row, lo, bar);
+        if (nfull < n) tma_load_2d(dst + nfull * TILE_BYTES, p->_tmap_tail, 0, row, bar);  // the partial block of K
+    } else {  // plain 2-D view: one request per 128-byte column block
+        for (int i = 0; i < n; ++i) tma_load_2d(dst + i * TILE_BYTES, p->_tmap_tail, (lo + i) * 128, row, bar);
+    }
+}
+
 // item index -> (problem, token pass, row item)
 __device__ __forceinline__ void locate_item(const wf_problem* __restrict__ probs, int P, int item, int& pi, int& chunk, int& ritem) {
     int lo = 0, hi = P - 1;
@@ -286,7 +312,7 @@ __global__ void __launch_bounds__(DEC_THREADS, 1)
         // Only one lane works: a whole 16-row tile over all of K is one TMA request (plus one for a K tail).
         if (lane == 0) {
             const wf_problem* p = &probs[pi];
-            int N = p->N, row_items = p->_row_items, chunks = p->_chunks, kbf = p->_kb_full, tail = p->_tail_bytes;
+            int N = p->N, row_items = p->_row_items, chunks = p->_chunks;
             int KB = (p->K + 511) >> 9;
             for (int it = beg, n = 0; it < end; ++it, ++n) {
                 const int stage = n % cfg.stages;
@@ -296,22 +322,16 @@ __global__ void __launch_bounds__(DEC_THREADS, 1)
                 tiles = tiles < cfg.RI ? tiles : cfg.RI;
                 mbar_expect_tx(&full[stage], static_cast<unsigned>(tiles * KB) * TILE_BYTES);
                 uint8_t* dst = s_stage + static_cast<size_t>(stage) * cfg.stage_bytes;
-                for (int rt = 0; rt < tiles; ++rt, dst += KB * TILE_BYTES) {
-                    if (kbf > 0) {
-                        tma_load_3d(dst, p->_tmap_main, 0, r0 + rt * 16, 0, &full[stage]);
-                        if (tail) tma_load_2d(dst + kbf * TILE_BYTES, p->_tmap_tail, 0, r0 + rt * 16, &full[stage]);
-                    } else {  // plain 2-D view: one request per 128-byte column block
-                        for (int kb = 0; kb < KB; ++kb)
-                            tma_load_2d(dst + kb * TILE_BYTES, p->_tmap_tail, kb * 128, r0 + rt * 16, &full[stage]);
-                    }
-                }
+                for (int rt = 0; rt < tiles; ++rt, dst += KB * TILE_BYTES)
+                    for (int seg = 0; seg < p->_ksegs; ++seg)
+                        issue_segment(p, r0 + rt * 16, seg, dst + seg * p->_kb_seg * TILE_BYTES, &full[stage]);
                 if (++ritem == row_items) {
                     ritem = 0;
                     if (++chunk == chunks) {
                         chunk = 0;
                         if (++pi < cfg.P) {
                             p = &probs[pi];
-                            N = p->N; row_items = p->_row_items; chunks = p->_chunks; kbf = p->_kb_full; tail = p->_tail_bytes;
+                            N = p->N; row_items = p->_row_items; chunks = p->_chunks;
                             KB = (p->K + 511) >> 9;
                         }
                     }
@@ -426,17 +446,6 @@ __device__ __forceinline__ void cursor_advance(ItemCursor& c, const wf_problem* 
     }
 }
 
-__device__ __forceinline__ void issue_item(const wf_problem* p, int ritem, uint8_t* dst, uint64_t* bar) {
-    const int KB = (p->K + 511) >> 9, kbf = p->_kb_full;
-    mbar_expect_tx(bar, static_cast<unsigned>(KB) * TILE_BYTES);
-    if (kbf > 0) {
-        tma_load_3d(dst, p->_tmap_main, 0, ritem * 16, 0, bar);
-        if (p->_tail_bytes) tma_load_2d(dst + kbf * TILE_BYTES, p->_tmap_tail, 0, ritem * 16, bar);
-    } else {
-        for (int kb = 0; kb < KB; ++kb) tma_load_2d(dst + kb * TILE_BYTES, p->_tmap_tail, kb * 128, ritem * 16, bar);
-    }
-}
-
 constexpr int STREAM_THREADS = 256;  // 8 warps; two such CTAs share an SM
 constexpr int SW = STREAM_THREADS / 32;
 
@@ -489,7 +498,10 @@ __global__ void __launch_bounds__(STREAM_THREADS, 2)
         locate_item(probs, cfg.P, nx_item, nx.pi, nx.chunk, nx.ritem);
         nx.row_items = probs[nx.pi]._row_items;
         nx.chunks = probs[nx.pi]._chunks;
-        if (lane == 0) issue_item(&probs[nx.pi], nx.ritem, my_stage, &full[warp]);
+        if (lane == 0) {
+            mbar_expect_tx(&full[warp], segment_bytes(&probs[nx.pi], 0));
+            issue_segment(&probs[nx.pi], nx.ritem * 16, 0, my_stage, &full[warp]);
+        }
     }
 
     // x may be produced by the previous kernel of the stream
@@ -524,7 +536,7 @@ __global__ void __launch_bounds__(STREAM_THREADS, 2)
         const uint32_t act0 = smem_u32(s_act + buf * act_bytes);
         const float* const inv_p = s_inv + buf * MT;
         const int* const rowsum_p = s_rowsum + buf * MT;
-        const int KB = (p.K + 511) >> 9;
+        const int KB = (p.K + 511) >> 9, kb_seg = p._kb_seg, ksegs = p._ksegs;
         const float s_w = p.w_scale ? __ldg(p.w_scale) : p.w_scale_host;
         void* const y = p.y;
         const void* const bias = p.bias;
@@ -534,8 +546,6 @@ __global__ void __launch_bounds__(STREAM_THREADS, 2)
         if (warp < S) {
             int j = it + ((warp - (it - beg)) % S + S) % S;  // first item of this warp in the pass
             for (; j < seg_end; j += S) {
-                mbar_wait(&full[warp], loads & 1, poisoned);
-                ++loads;
                 int acc[NT][FOURACC ? 4 : 1][4];
 #pragma unroll
                 for (int a = 0; a < NT; ++a)
@@ -543,22 +553,37 @@ __global__ void __launch_bounds__(STREAM_THREADS, 2)
                     for (int b = 0; b < (FOURACC ? 4 : 1); ++b)
 #pragma unroll
                         for (int c = 0; c < 4; ++c) acc[a][b][c] = 0;
+                const int my_row = (ritem + (j - it)) * 16;
+                // K arrives in segments through this warp's one stage; after each the warp requests what it needs next
+                for (int ks = 0; ks < ksegs; ++ks) {
+                    mbar_wait(&full[warp], loads & 1, poisoned);
+                    ++loads;
+                    const int kb0 = ks * kb_seg, kbn = min(KB - kb0, kb_seg);
 #pragma unroll 1
-                for (int kb = 0; kb < KB; ++kb)
-                    compute_unit<NT, FOURACC>(w_r0 + kb * TILE_BYTES, w_r0 + kb * TILE_BYTES + 1024,
-                                              act0 + kb * cfg.MTA * TOK_STRIDE, m_valid, g, t, acc);
-                // the stage has been read: request this warp's next item (it may belong to a later pass)
-                __syncwarp();
-                nx_item += S;
-                if (nx_item < end) {
-                    cursor_advance(nx, probs, cfg.P, S);
-                    if (lane == 0) {
-                        asm volatile("fence.proxy.async.shared::cta;\n" ::: "memory");
-                        issue_item(&probs[nx.pi], nx.ritem, my_stage, &full[warp]);
+                    for (int i = 0; i < kbn; ++i)
+                        compute_unit<NT, FOURACC>(w_r0 + i * TILE_BYTES, w_r0 + i * TILE_BYTES + 1024,
+                                                  act0 + (kb0 + i) * cfg.MTA * TOK_STRIDE, m_valid, g, t, acc);
+                    __syncwarp();  // the stage has been read
+                    if (ks + 1 < ksegs) {
+                        if (lane == 0) {
+                            asm volatile("fence.proxy.async.shared::cta;\n" ::: "memory");
+                            mbar_expect_tx(&full[warp], segment_bytes(&p, ks + 1));
+                            issue_segment(&p, my_row, ks + 1, my_stage, &full[warp]);
+                        }
+                    } else {
+                        nx_item += S;  // this warp's next item (it may belong to a later pass)
+                        if (nx_item < end) {
+                            cursor_advance(nx, probs, cfg.P, S);
+                            if (lane == 0) {
+                                asm volatile("fence.proxy.async.shared::cta;\n" ::: "memory");
+                                mbar_expect_tx(&full[warp], segment_bytes(&probs[nx.pi], 0));
+                                issue_segment(&probs[nx.pi], nx.ritem * 16, 0, my_stage, &full[warp]);
+                            }
+                        }
                     }
                 }
                 // epilogue straight from the accumulators: lane holds rows g, g+8 x tokens 2t, 2t+1 of every token tile
-                const int row_a = (ritem + (j - it)) * 16 + g, row_b = row_a + 8;
+                const int row_a = my_row + g, row_b = row_a + 8;
 #pragma unroll
                 for (int nt = 0; nt < NT; ++nt) {
 #pragma unroll
@@ -634,8 +659,18 @@ static EncodeTiledFn encode_fn() {
     return fn;
 }
 
+constexpr int KB_SEG_MAX = 7;  // 512-weight blocks per streamed K segment: 14 KB per 16-row tile
+
+static void k_segments(int K, int& kb_seg, int& ksegs) {
+    const int KB = (K + 511) / 512;
+    ksegs = (KB + KB_SEG_MAX - 1) / KB_SEG_MAX;
+    kb_seg = (KB + ksegs - 1) / ksegs;
+    ksegs = (KB + kb_seg - 1) / kb_seg;
+}
+
 // TMA descriptors of the packed weights of one problem.  Main: the full 128-byte column blocks as a 3-D tensor
-// [block][row][128 bytes], so that one box [all blocks][16 rows][128] lands in the stage as consecutive 2 KB tiles.
+// [block][row][128 bytes] with a box of [_kb_seg blocks][16 rows][128], so that one request lands a K segment of a
+// row tile in a stage as consecutive 2 KB tiles; Last: the same view with the shorter box of the last segment;
 // Tail: the last, partial column block as a 2-D tensor whose missing bytes are filled with zeros.  When the 3-D
 // view is refused, the plain 2-D view [row][K/4 bytes] is used with one request per column block.
 static int encode_maps(wf_problem& q) {
@@ -643,18 +678,28 @@ static int encode_maps(wf_problem& q) {
     if (!enc) return fail(WF_E_DEVICE, "cuTensorMapEncodeTiled is not available in this driver");
     const cuuint64_t rowbytes = static_cast<cuuint64_t>(q.K) / 4;
     const int kbf = static_cast<int>(rowbytes / 128), tail = static_cast<int>(rowbytes % 128);
+    int kb_seg, ksegs;
+    k_segments(q.K, kb_seg, ksegs);
+    q._kb_seg = kb_seg;
+    q._ksegs = ksegs;
     const cuuint32_t ones[3] = {1, 1, 1};
     void* base = const_cast<uint8_t*>(q.codes);
-    CUresult r = CUDA_SUCCESS;
-    if (kbf > 0) {
+    auto enc3 = [&](uint64_t* out, int box_blocks) {
         const cuuint64_t dims[3] = {128, static_cast<cuuint64_t>(q.N), static_cast<cuuint64_t>(kbf)};
         const cuuint64_t strides[2] = {rowbytes, 128};
-        const cuuint32_t box[3] = {128, 16, static_cast<cuuint32_t>(kbf)};
-        r = enc(reinterpret_cast<CUtensorMap*>(q._tmap_main), CU_TENSOR_MAP_DATA_TYPE_UINT8, 3, base, dims, strides, box, ones,
-                CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_NONE, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
-                CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+        const cuuint32_t box[3] = {128, 16, static_cast<cuuint32_t>(box_blocks)};
+        return enc(reinterpret_cast<CUtensorMap*>(out), CU_TENSOR_MAP_DATA_TYPE_UINT8, 3, base, dims, strides, box, ones,
+                   CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_NONE, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                   CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    };
+    CUresult r = CUDA_SUCCESS;
+    if (kbf > 0) {
+        // a segment holds either _kb_seg full blocks (main box) or, the last one, fewer (its own box)
+        if (kbf >= kb_seg) r = enc3(q._tmap_main, kb_seg);
+        const int last_full = kbf - (ksegs - 1) * kb_seg;  // full blocks of the last segment (may be <= 0)
+        if (r == CUDA_SUCCESS && last_full > 0 && last_full != kb_seg) r = enc3(q._tmap_last, last_full);
     }
-    if (kbf > 0 && kbf <= 256 && r == CUDA_SUCCESS) {
+    if (kbf > 0 && r == CUDA_SUCCESS) {
         q._kb_full = kbf;
         q._tail_bytes = tail;
         if (tail) {
@@ -708,8 +753,16 @@ static int plan_group(wf_problem* probs, int P, GroupPlan& g, bool write_fields)
     const size_t act = (static_cast<size_t>(g.KBmax) * g.MTA * TOK_STRIDE + 127) / 128 * 128;
     // Enough 16-row items to give every consumer warp of every SM several of them: the warps work on their
     // own items.  Otherwise (a single small layer) the 16 warps of a CTA share each item and split K.
-    g.decoupled = count_items16(probs, P, g.MTA) >= 32LL * sms && fixed_bytes(NT, 1) + act + 4u * 16 * pitch <= SMEM_STREAM_MAX;
-    g.nbuf = (g.decoupled && fixed_bytes(NT, 1) + 2 * act + 6u * 16 * pitch <= SMEM_STREAM_MAX) ? 2 : 1;
+    // streaming form: a stage holds one K segment of a 16-row tile
+    int seg_max = 1;
+    for (int i = 0; i < P; ++i) {
+        int kb_seg, ksegs;
+        k_segments(probs[i].K, kb_seg, ksegs);
+        seg_max = kb_seg > seg_max ? kb_seg : seg_max;
+    }
+    const size_t seg_stage = static_cast<size_t>(seg_max) * TILE_BYTES;
+    g.decoupled = count_items16(probs, P, g.MTA) >= 32LL * sms && fixed_bytes(NT, 1) + act + 4u * seg_stage <= SMEM_STREAM_MAX;
+    g.nbuf = (g.decoupled && fixed_bytes(NT, 1) + 2 * act + 6u * seg_stage <= SMEM_STREAM_MAX) ? 2 : 1;
     // item size: about 32 KB per stage, smaller while there are too few items to keep every SM busy
     int RI = g.decoupled ? 1 : 8;
     while (RI > 1 && 16 * RI * pitch > 32 * 1024) RI >>= 1;
@@ -722,7 +775,7 @@ static int plan_group(wf_problem* probs, int P, GroupPlan& g, bool write_fields)
     while (RI > 1 && count_items(RI) < 4LL * sms) RI >>= 1;
     while (RI > 1 && fixed_bytes(NT, RI) + act + 2u * 16 * RI * pitch > SMEM_MAX) RI >>= 1;
     g.RI = RI;
-    g.stage_bytes = 16 * RI * pitch;
+    g.stage_bytes = g.decoupled ? static_cast<int>(seg_stage) : 16 * RI * pitch;
     g.act_off = static_cast<int>(fixed_bytes(NT, RI));
     g.stage_off = g.act_off + static_cast<int>(g.nbuf * act);
     if (static_cast<size_t>(g.stage_off) + 2u * g.stage_bytes > SMEM_MAX)
@@ -807,7 +860,10 @@ static int run_group(const char* who, const wf_problem* dev, wf_problem* host, i
         int begin = 0;
         for (int i = 0; i < P; ++i) {
             const int ri = (host[i].N + 16 * g.RI - 1) / (16 * g.RI), ch = (host[i].M + g.MTA - 1) / g.MTA;
-            WF_REQUIRE(host[i]._item_begin == begin && host[i]._row_items == ri && host[i]._chunks == ch,
+            int kb_seg, ksegs;
+            k_segments(host[i].K, kb_seg, ksegs);
+            WF_REQUIRE(host[i]._item_begin == begin && host[i]._row_items == ri && host[i]._chunks == ch &&
+                           host[i]._kb_seg == kb_seg && host[i]._ksegs == ksegs,
                        "%s: problem %d was not prepared by wf_bitlinear_decode_plan (or was changed afterwards)", who, i);
             begin += ri * ch;
         }
