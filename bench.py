@@ -316,6 +316,11 @@ def decoder_section(wf, torch, device, world, full: bool):
 
 
 # ------------------------------------------------------------------ main
+def note(rank, msg):
+    """Progress marker on stderr (one line per phase and rank)."""
+    print(f"[bench r{rank} {time.strftime('%H:%M:%S')}] {msg}", file=sys.stderr, flush=True)
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -378,7 +383,9 @@ def main():
         BATCHES[:] = [args.only_m]
     if args.only_shape >= 0:
         SHAPES[:] = [SHAPES[args.only_shape]]
+    note(rank, "building workload")
     groups = build_workload(wf, torch, device, rank, world, args.layers_scale)
+    note(rank, "capturing step graph")
     pdl = not args.no_pdl
     try:
         graph = capture(torch, lambda: run_step(wf, groups, pdl))
@@ -397,6 +404,7 @@ def main():
             dist.barrier()
         torch.cuda.synchronize()
 
+    note(rank, "device-resident timing")
     # ---- device-resident timing
     for _ in range(warmup):
         graph.replay()
@@ -414,6 +422,7 @@ def main():
     ms = ev0.elapsed_time(ev1) / args.steps
     clocks = sampler.finish() if rank == 0 else None
 
+    note(rank, "end-to-end timing")
     # ---- end to end: pinned host activations in, outputs back to pinned host memory, every step
     h2d = sum(g["x_host"].numel() * 2 for g in groups)
     d2h = sum(g["y"].numel() * 2 for g in groups)
@@ -471,7 +480,9 @@ def main():
             t = tt.item()
         return t
 
+    note(rank, "timing kernel families")
     ms_dec, ms_gemm = time_groups(dec_groups), time_groups(gemm_groups)
+    note(rank, "breakdown")
     gemm_ops = sum(2.0 * g["m"] * g["n"] * g["k"] * len(g["layers"]) for g in gemm_groups)
     n_gemm_groups = len(gemm_groups)
     dec_launches = max(1, len(dec_groups))
@@ -518,10 +529,12 @@ def main():
         for g in groups:  # free the sweep's buffers first
             g.clear()
         torch.cuda.empty_cache()
+        note(rank, "decoder section")
         try:
             decoder = decoder_section(wf, torch, device, world, args.decoder_full)
         except Exception as e:  # the main line must survive a failure of this secondary section
             decoder = [{"error": repr(e)[:300]}]
+    note(rank, "done with collective phases")
     if rank != 0:
         if dist is not None:
             dist.destroy_process_group()
