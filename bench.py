@@ -536,8 +536,10 @@ def main():
             decoder = [{"error": repr(e)[:300]}]
     note(rank, "done with collective phases")
     if rank != 0:
-        if dist is not None:
-            dist.destroy_process_group()
+        # stay in step with rank 0 (it still runs single-GPU sections): tear the group down together
+        dist.barrier()
+        note(rank, "final barrier passed")
+        dist.destroy_process_group()
         return
     line = {"metric": METRIC, "value": value, "unit": "GB/s", "n_gpus": world, "steps": args.steps, "warmup": warmup,
             "ms_per_step": ms, "higher_is_better": True, "scaling": "strong", "vs_baseline": None, "dtype": "u8xs8->s32",
@@ -562,12 +564,16 @@ def main():
     if decoder is not None:
         line["decode_tok_s"] = decoder
     if not args.only_m and args.only_shape < 0:
+        note(rank, "prefill GEMM section")
         line["prefill_gemm"] = prefill_section(wf, torch, device, peaks)
+        note(rank, "prefill GEMM section done")
     if not args.no_cpu_baseline and world == 1:
         cb, _, _, _ = cpu_reference_run(3, 1)
         line["cpu_baseline"] = cb
-    print(json.dumps(line))
+    print(json.dumps(line), flush=True)
     if dist is not None:
+        dist.barrier()
+        note(rank, "final barrier passed")
         dist.destroy_process_group()
 
 
