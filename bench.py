@@ -316,6 +316,18 @@ def decoder_section(wf, torch, device, world, full: bool):
 
 
 # ------------------------------------------------------------------ main
+def finish(dist, torch, rank):
+    """Multi-rank exit.  The CUDA graphs of this run captured NCCL kernels, and tearing a communicator down while
+    such graphs exist blocks; every rank has nothing left to do after the final barrier, so the processes leave
+    without the teardown (exit status 0)."""
+    dist.barrier()
+    torch.cuda.synchronize()
+    note(rank, "final barrier passed")
+    sys.stdout.flush()
+    sys.stderr.flush()
+    os._exit(0)
+
+
 def note(rank, msg):
     """Progress marker on stderr (one line per phase and rank)."""
     print(f"[bench r{rank} {time.strftime('%H:%M:%S')}] {msg}", file=sys.stderr, flush=True)
@@ -537,9 +549,7 @@ def main():
     note(rank, "done with collective phases")
     if rank != 0:
         # stay in step with rank 0 (it still runs single-GPU sections): tear the group down together
-        dist.barrier()
-        note(rank, "final barrier passed")
-        dist.destroy_process_group()
+        finish(dist, torch, rank)
         return
     line = {"metric": METRIC, "value": value, "unit": "GB/s", "n_gpus": world, "steps": args.steps, "warmup": warmup,
             "ms_per_step": ms, "higher_is_better": True, "scaling": "strong", "vs_baseline": None, "dtype": "u8xs8->s32",
@@ -572,9 +582,7 @@ def main():
         line["cpu_baseline"] = cb
     print(json.dumps(line), flush=True)
     if dist is not None:
-        dist.barrier()
-        note(rank, "final barrier passed")
-        dist.destroy_process_group()
+        finish(dist, torch, rank)
 
 
 if __name__ == "__main__":
