@@ -383,7 +383,17 @@ def main():
 
         import datetime
 
-        dist.init_process_group("nccl", device_id=device, timeout=datetime.timedelta(seconds=90))
+        # NCCL announces its version on stdout when the communicator comes up; stdout carries the one JSON line only
+        saved = os.dup(1)
+        os.dup2(2, 1)
+        try:
+            dist.init_process_group("nccl", device_id=device, timeout=datetime.timedelta(seconds=90))
+            dist.barrier()
+            torch.cuda.synchronize()
+        finally:
+            sys.stdout.flush()
+            os.dup2(saved, 1)
+            os.close(saved)
 
     if args.prefill_only:
         peaks, _ = measured_peaks()
