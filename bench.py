@@ -430,11 +430,11 @@ def main():
     # ---- device-resident timing
     for _ in range(warmup):
         graph.replay()
-    barrier()
     sampler = ClockSampler(local_rank)
     if rank == 0:
         sampler.start()
         time.sleep(0.3)
+    barrier()  # after the sampler is up: no rank may enter the timed region ahead of the others
     ev0, ev1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     ev0.record()
     for _ in range(args.steps):
