@@ -215,6 +215,21 @@ int wf_bitlinear_prefill_batched(const void* x, int x_dtype, int64_t ldx, const 
                                  int32_t* acc_out, int64_t batch, int64_t M, int64_t N, int64_t K, float eps,
                                  void* workspace, size_t workspace_bytes, void* stream);
 
+/*
+ * Fused elementwise kernels around the projections of a decoder layer (bf16 tensors, contiguous rows).
+ * They replace operator chains of the callers of BitLinear in the reference model
+ * (packages/training/src/wrinklefree/models/subln.py / transformer.py:80-117 for residual + RMSNorm,
+ *  attention.py:14-64 for RoPE, ffn.py:51-87 for the gate activation) in the decode step.
+ * wf_add_rmsnorm_bf16: h[M,K] += delta (nullable), y = h * rsqrt(mean(h^2) + eps) * weight[K].
+ * wf_rope_kv_bf16:     rotates q [B, nq*D] in place and k [B, nkv*D] at position slot = *pos % T (device scalar),
+ *                      writes the rotated k and v into the caches [B, nkv, T, D]; cos/sin are fp32 [T, D/2].
+ * wf_act_mul_bf16:     out = act(gate) * up over n elements; mode 0 = SiLU, 1 = ReLU^2.
+ */
+int wf_add_rmsnorm_bf16(void* h, const void* delta, const void* weight, void* y, int64_t M, int64_t K, float eps, void* stream);
+int wf_rope_kv_bf16(void* q, const void* k, const void* v, const float* cos, const float* sin, const int64_t* pos, void* kcache,
+                    void* vcache, int64_t B, int nq, int nkv, int D, int T, void* stream);
+int wf_act_mul_bf16(const void* gate, const void* up, void* out, int64_t n, int mode, void* stream);
+
 #ifdef __cplusplus
 }
 #endif

@@ -122,6 +122,11 @@ class TernaryDecoder:
             L["gu"] = [torch.empty(B, self.i_hi - self.i_lo, dtype=dt, device=dev) for _ in range(2)]
             L["g_gu"] = ops.DecodeGroup([dict(x=L["hn"], codes=L[n][0], w_scale=L[n][1], out=o)
                                          for n, o in zip(("gate", "up"), L["gu"])])
+            L["act"] = torch.empty(B, self.i_hi - self.i_lo, dtype=dt, device=dev)
+            L["ob"] = torch.empty(B, cfg.hidden, dtype=dt, device=dev)
+            L["db"] = torch.empty(B, cfg.hidden, dtype=dt, device=dev)
+        self.h = torch.empty(B, cfg.hidden, dtype=dt, device=dev)
+        self.xf = torch.empty(B, cfg.hidden, dtype=dt, device=dev)
 
     def _act(self, g, u):
         return (F.silu(g) if self.cfg.act == "silu" else F.relu(g).pow(2)) * u
@@ -132,28 +137,25 @@ class TernaryDecoder:
         return y
 
     def _decode_step(self):
-        """One token per sequence: reads self.tok / self.pos, writes self.next_tok; advances self.pos."""
+        """One token per sequence: reads self.tok / self.pos, writes self.next_tok; advances self.pos.
+        Per layer: add+RMSNorm, q/k/v group, RoPE+cache write, attention, o, add+RMSNorm, gate/up group,
+        activation*up, down -- ten launches."""
         cfg, B, d = self.cfg, self.B, self.cfg.head_dim
-        x = self.embed[self.tok]  # [B, hidden]
-        slot = (self.pos % self.T).view(1)
-        # index_select keeps the position on the device (indexing with a 0-dim tensor would read it back to the host)
-        cos, sin = self.cos.index_select(0, slot), self.sin.index_select(0, slot)
+        self.h.copy_(self.embed[self.tok])  # residual stream [B, hidden]
         valid = (torch.arange(self.T, device=self.dev) <= self.pos).view(1, 1, 1, self.T) if self.masked else None
+        delta = None
         for L in self.layers:
-            L["xn"].copy_(_rms_norm(x, L["n1"], cfg.eps))
+            ops.add_rmsnorm_(self.h, delta, L["n1"], L["xn"], cfg.eps)
             q, k, v = L["g_qkv"].run()
-            q = _rope(q.view(B, self.nq, 1, d), cos, sin)
-            k = _rope(k.view(B, self.nkv, 1, d), cos, sin)
-            L["kc"].index_copy_(2, slot, k)
-            L["vc"].index_copy_(2, slot, v.view(B, self.nkv, 1, d))
-            a = F.scaled_dot_product_attention(q, L["kc"], L["vc"], attn_mask=valid, enable_gqa=True)
-            o = self._allreduce(ops.bitlinear(a.reshape(B, self.nq * d), L["o"][0], L["o"][1], path="decode"))
-            x = x + o
-            L["hn"].copy_(_rms_norm(x, L["n2"], cfg.eps))
+            ops.rope_kv_(q, k, v, self.cos, self.sin, self.pos, L["kc"], L["vc"])
+            a = F.scaled_dot_product_attention(q.view(B, self.nq, 1, d), L["kc"], L["vc"], attn_mask=valid, enable_gqa=True)
+            o = self._allreduce(ops.bitlinear(a.reshape(B, self.nq * d), L["o"][0], L["o"][1], out=L["ob"], path="decode"))
+            ops.add_rmsnorm_(self.h, o, L["n2"], L["hn"], cfg.eps)
             g, u = L["g_gu"].run()
-            dn = self._allreduce(ops.bitlinear(self._act(g, u), L["down"][0], L["down"][1], path="decode"))
-            x = x + dn
-        logits = _rms_norm(x, self.norm_f, cfg.eps) @ self.lm_head.t()
+            ops.act_mul(g, u, L["act"], self.cfg.act)
+            delta = self._allreduce(ops.bitlinear(L["act"], L["down"][0], L["down"][1], out=L["db"], path="decode"))
+        ops.add_rmsnorm_(self.h, delta, self.norm_f, self.xf, cfg.eps)
+        logits = self.xf @ self.lm_head.t()
         self.logits = logits
         self.next_tok.copy_(logits.argmax(-1))
         self.pos.add_(1)
