@@ -343,6 +343,7 @@ def main():
     ap.add_argument("--no-pdl", action="store_true")
     ap.add_argument("--prefill-only", action="store_true", help="run only the prefill GEMM section (profiling)")
     ap.add_argument("--no-decoder", action="store_true", help="skip the decoder tokens/s section")
+    ap.add_argument("--decoder-only", action="store_true", help="run only the decoder tokens/s section (profiling)")
     ap.add_argument("--decoder-full", action="store_true", help="also batch 256 of the 8B shape")
     ap.add_argument("--only-m", type=int, default=0, help="restrict the sweep to one token batch (profiling)")
     ap.add_argument("--only-shape", type=int, default=-1, help="restrict the sweep to one shape index (profiling)")
@@ -395,6 +396,9 @@ def main():
             os.dup2(saved, 1)
             os.close(saved)
 
+    if args.decoder_only:
+        print(json.dumps({"decode_tok_s": decoder_section(wf, torch, device, world, args.decoder_full)}))
+        return
     if args.prefill_only:
         peaks, _ = measured_peaks()
         res = prefill_section(wf, torch, device, peaks, [SHAPES[args.only_shape]] if args.only_shape >= 0 else None,
