@@ -7,7 +7,7 @@ Workload ("decode_gemv_sweep"): the decode GEMV sweep at BitNet-2B-like shapes â
 N(0, 0.02) absmean-ternarized and packed 2 bits per weight, activations bf16 N(0,1) with
 0.1 % outliers at +-20.  One step is one pass of the fused quantize-and-contract kernel over
 a stack of independent layers of every (shape, M) pair (one grouped, persistent launch per
-pair); the stacks hold more distinct packed weights (~0.5 GB) than the L2 cache, so every
+pair); the stacks hold more distinct packed weights (~0.6 GB) than the L2 cache, so every
 launch streams its weights from HBM.  The per-pair breakdown also times the same stack as one
 launch per layer, chained with programmatic dependent launch (the latency-bound form).
 `value` is algorithmic GB/s (packed codes + scale + bf16 x + bf16 y per launch) over the whole

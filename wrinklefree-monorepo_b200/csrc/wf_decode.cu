@@ -141,6 +141,8 @@ __device__ __forceinline__ void quantize_tokens(const wf_problem& p, int MTA, in
             int tok = tb + sub;
             float mx = 0.f;
             if (tok < m_valid) {
+                // several loads in flight per thread: these are dependent L2 round trips otherwise
+#pragma unroll 4
                 for (int k = lane_in * 8; k < p.K; k += tpt * 8) {
                     float f[8];
                     load8<XDT>(p.x, static_cast<int64_t>(m0 + tok) * p.ldx + k, f);
@@ -160,6 +162,7 @@ __device__ __forceinline__ void quantize_tokens(const wf_problem& p, int MTA, in
             if (tok < m_valid) {
                 const float s = act_scale_from_absmax<XDT>(__uint_as_float(s_maxbits[tok]), p.eps);
                 if (lane_in == 0) s_inv[tok] = __fdiv_rn(1.0f, s);
+#pragma unroll 4
                 for (int k = lane_in * 8; k < Kp; k += tpt * 8) {
                     uint32_t w0 = 0, w1 = 0;
                     if (k < p.K) {
@@ -467,7 +470,7 @@ __global__ void __launch_bounds__(STREAM_THREADS, 2)
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31, g = lane >> 2, t = lane & 3;
     const int S = cfg.stages;
     if (tid == 0) {
-        for (int s = 0; s < 2 * S; ++s) mbar_init(&full[s], 1);
+        for (int s = 0; s < S; ++s) mbar_init(&full[s], 1);
         *poisoned = 0;
         asm volatile("fence.mbarrier_init.release.cluster;\n" ::: "memory");
     }
@@ -487,42 +490,21 @@ __global__ void __launch_bounds__(STREAM_THREADS, 2)
         beg = static_cast<int>(static_cast<int64_t>(blockIdx.x) * cfg.total_items / gridDim.x);
         end = static_cast<int>(static_cast<int64_t>(blockIdx.x + 1) * cfg.total_items / gridDim.x);
     }
-    // Each warp owns two stages and keeps two requests in flight: while it consumes one K segment the next one
-    // (of the same row tile, or the first of its next row tile) is already on its way.
-    uint8_t* const my_stage0 = s_stage + static_cast<size_t>(2 * warp) * cfg.stage_bytes;
-    uint64_t* const my_full0 = &full[2 * warp];
-    const uint32_t w_base0 = smem_u32(my_stage0) + g * 128;
+    uint8_t* my_stage = s_stage + static_cast<size_t>(warp) * cfg.stage_bytes;
+    const uint32_t w_r0 = smem_u32(my_stage) + g * 128;
 
-    // cursor of the next (item, segment) this warp will request; the first two requests go out before anything else
-    ItemCursor nx = {};
-    int nx_item = beg + warp, nx_seg = 0, nx_ksegs = 1;
-    unsigned issued = 0, waited = 0;  // requests issued / consumed by this warp (stage = count & 1, parity = (count >> 1) & 1)
-    auto issue_next = [&]() {
-        if (nx_item >= end) return;
-        const wf_problem* q = &probs[nx.pi];
-        if (lane == 0) {
-            asm volatile("fence.proxy.async.shared::cta;\n" ::: "memory");
-            const unsigned b = issued & 1;
-            mbar_expect_tx(my_full0 + b, segment_bytes(q, nx_seg));
-            issue_segment(q, nx.ritem * 16, nx_seg, my_stage0 + b * cfg.stage_bytes, my_full0 + b);
-        }
-        ++issued;
-        if (++nx_seg == nx_ksegs) {
-            nx_seg = 0;
-            nx_item += S;
-            if (nx_item < end) {
-                cursor_advance(nx, probs, cfg.P, S);
-                nx_ksegs = probs[nx.pi]._ksegs;
-            }
-        }
-    };
+    // cursor of the next item this warp will request; the first request goes out before anything else
+    ItemCursor nx;
+    int nx_item = beg + warp;
+    unsigned loads = 0;  // completed + pending requests of this warp (parity of the wait)
     if (warp < S && nx_item < end) {
         locate_item(probs, cfg.P, nx_item, nx.pi, nx.chunk, nx.ritem);
         nx.row_items = probs[nx.pi]._row_items;
         nx.chunks = probs[nx.pi]._chunks;
-        nx_ksegs = probs[nx.pi]._ksegs;
-        issue_next();
-        issue_next();
+        if (lane == 0) {
+            mbar_expect_tx(&full[warp], segment_bytes(&probs[nx.pi], 0));
+            issue_segment(&probs[nx.pi], nx.ritem * 16, 0, my_stage, &full[warp]);
+        }
     }
 
     // x may be produced by the previous kernel of the stream
@@ -577,17 +559,31 @@ __global__ void __launch_bounds__(STREAM_THREADS, 2)
                 const int my_row = (ritem + (j - it)) * 16;
                 // K arrives in segments through this warp's one stage; after each the warp requests what it needs next
                 for (int ks = 0; ks < ksegs; ++ks) {
-                    const unsigned st = waited & 1;
-                    mbar_wait(my_full0 + st, (waited >> 1) & 1, poisoned);
-                    ++waited;
-                    const uint32_t wb = w_base0 + st * cfg.stage_bytes;
+                    mbar_wait(&full[warp], loads & 1, poisoned);
+                    ++loads;
                     const int kb0 = ks * kb_seg, kbn = min(KB - kb0, kb_seg);
 #pragma unroll 1
                     for (int i = 0; i < kbn; ++i)
-                        compute_unit<NT, FOURACC>(wb + i * TILE_BYTES, wb + i * TILE_BYTES + 1024,
+                        compute_unit<NT, FOURACC>(w_r0 + i * TILE_BYTES, w_r0 + i * TILE_BYTES + 1024,
                                                   act0 + (kb0 + i) * cfg.MTA * TOK_STRIDE, m_valid, g, t, acc);
-                    __syncwarp();  // the stage has been read: request the segment after the one already in flight
-                    issue_next();
+                    __syncwarp();  // the stage has been read
+                    if (ks + 1 < ksegs) {
+                        if (lane == 0) {
+                            asm volatile("fence.proxy.async.shared::cta;\n" ::: "memory");
+                            mbar_expect_tx(&full[warp], segment_bytes(&p, ks + 1));
+                            issue_segment(&p, my_row, ks + 1, my_stage, &full[warp]);
+                        }
+                    } else {
+                        nx_item += S;  // this warp's next item (it may belong to a later pass)
+                        if (nx_item < end) {
+                            cursor_advance(nx, probs, cfg.P, S);
+                            if (lane == 0) {
+                                asm volatile("fence.proxy.async.shared::cta;\n" ::: "memory");
+                                mbar_expect_tx(&full[warp], segment_bytes(&probs[nx.pi], 0));
+                                issue_segment(&probs[nx.pi], nx.ritem * 16, 0, my_stage, &full[warp]);
+                            }
+                        }
+                    }
                 }
                 // epilogue straight from the accumulators: lane holds rows g, g+8 x tokens 2t, 2t+1 of every token tile
                 const int row_a = my_row + g, row_b = row_a + 8;
@@ -666,7 +662,7 @@ static EncodeTiledFn encode_fn() {
     return fn;
 }
 
-constexpr int KB_SEG_MAX = 4;  // 512-weight blocks per streamed K segment: at most 8 KB per 16-row tile and stage
+constexpr int KB_SEG_MAX = 7;  // 512-weight blocks per streamed K segment: 14 KB per 16-row tile
 
 static void k_segments(int K, int& kb_seg, int& ksegs) {
     const int KB = (K + 511) / 512;
@@ -800,9 +796,9 @@ static int plan_group(wf_problem* probs, int P, GroupPlan& g, bool write_fields)
     int stages = static_cast<int>(((g.decoupled ? SMEM_STREAM_MAX : SMEM_MAX) - g.stage_off) / g.stage_bytes);
     if (stages > MAX_STAGES) stages = MAX_STAGES;
     if (!g.decoupled && stages > per_cta + 1) stages = per_cta + 1 > 2 ? per_cta + 1 : 2;
-    if (g.decoupled) stages = stages / 2 > SW ? SW : stages / 2;  // warps that stream: two stages each
+    if (g.decoupled && stages > SW) stages = SW;  // one owning warp per stage
     g.stages = stages;
-    g.smem = static_cast<size_t>(g.stage_off) + static_cast<size_t>(g.decoupled ? 2 * stages : stages) * g.stage_bytes;
+    g.smem = static_cast<size_t>(g.stage_off) + static_cast<size_t>(stages) * g.stage_bytes;
     if (write_fields) {
         int begin = 0;
         for (int i = 0; i < P; ++i) {
