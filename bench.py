@@ -32,7 +32,9 @@ sys.path.insert(0, os.path.join(ROOT, "tests", "golden"))
 
 SHAPES = [(2560, 2560), (6912, 2560), (2560, 6912)]  # (N, K)
 BATCHES = [1, 4, 16, 64]
-LAYERS = {(2560, 2560): 96, (6912, 2560): 40, (2560, 6912): 40}  # distinct weight matrices per shape
+# distinct weight matrices per shape: the count of each projection shape in one BitNet-2B-like model of 30 layers
+# (4 attention-sized, 2 gate/up, 1 down per layer): 594 MB of packed weights
+LAYERS = {(2560, 2560): 120, (6912, 2560): 60, (2560, 6912): 30}
 METRIC = "ternary_decode_gemv_GBps"
 GEMM_MIN_M = 16  # token batches from here on run on the tensor-core contraction (one batched launch per layer stack)
 NCU_TRAFFIC_RATIO = 162.28 / 158.27  # dram bytes / algorithmic bytes, profiles/decode_stream_kernel_m1_2560x2560.md
