@@ -60,6 +60,7 @@ struct DecodeCfg {
     int act_off, stage_off;  // byte offsets inside dynamic shared memory
     int nbuf;         // streaming form: activation buffers (2 when they are small, else 1)
     int cpp;          // streaming form: CTAs per problem when ranges are aligned to problems (0: contiguous split)
+    int ib_off, ib_cap;  // shared-memory copy of the problems' first item indices (searched instead of global memory)
     int decoupled;    // 1: every consumer warp owns whole 16-row items (RI == 1); 0: the 16 warps share each item
 };
 
@@ -259,11 +260,15 @@ __device__ __forceinline__ void issue_segment(const wf_problem* p, int row, int 
 }
 
 // item index -> (problem, token pass, row item)
-__device__ __forceinline__ void locate_item(const wf_problem* __restrict__ probs, int P, int item, int& pi, int& chunk, int& ritem) {
+// `ib` is the shared-memory table of _item_begin (valid for the first ib_cap problems): a search through global memory
+// is a chain of dependent cache misses, several microseconds per call.
+__device__ __forceinline__ void locate_item(const wf_problem* __restrict__ probs, int P, int item, int& pi, int& chunk, int& ritem,
+                                            const int* ib, int ib_cap) {
     int lo = 0, hi = P - 1;
     while (lo < hi) {  // last problem whose _item_begin <= item
         int mid = (lo + hi + 1) >> 1;
-        if (probs[mid]._item_begin <= item) lo = mid; else hi = mid - 1;
+        const int first = mid < ib_cap ? ib[mid] : probs[mid]._item_begin;
+        if (first <= item) lo = mid; else hi = mid - 1;
     }
     pi = lo;
     int local = item - probs[lo]._item_begin;
@@ -301,6 +306,8 @@ __global__ void __launch_bounds__(DEC_THREADS, 1)
         asm volatile("fence.mbarrier_init.release.cluster;\n" ::: "memory");
     }
     for (int i = tid; i < 2 * red_size; i += DEC_THREADS) s_red[i] = 0;
+    int* s_ib = reinterpret_cast<int*>(smem + cfg.ib_off);
+    for (int i = tid; i < cfg.ib_cap; i += DEC_THREADS) s_ib[i] = probs[i]._item_begin;
     __syncthreads();
 
     const int beg = static_cast<int>(static_cast<int64_t>(blockIdx.x) * cfg.total_items / gridDim.x);
@@ -311,7 +318,7 @@ __global__ void __launch_bounds__(DEC_THREADS, 1)
         // ---------------- producer: weights do not depend on the previous kernel, stream them right away
         // The item list is walked incrementally: one search at the start, then only counters.
         int pi, chunk, ritem;
-        locate_item(probs, cfg.P, beg, pi, chunk, ritem);
+        locate_item(probs, cfg.P, beg, pi, chunk, ritem, s_ib, cfg.ib_cap);
         // Only one lane works: a whole 16-row tile over all of K is one TMA request (plus one for a K tail).
         if (lane == 0) {
             const wf_problem* p = &probs[pi];
@@ -353,7 +360,7 @@ __global__ void __launch_bounds__(DEC_THREADS, 1)
 
     for (int it = beg, n = 0; it < end; ++it, ++n) {
         int pi, chunk, ritem;
-        locate_item(probs, cfg.P, it, pi, chunk, ritem);
+        locate_item(probs, cfg.P, it, pi, chunk, ritem, s_ib, cfg.ib_cap);
         const wf_problem& p = probs[pi];
         if (pi != cur_p || chunk != cur_chunk) {
             consumer_sync();  // nobody still reads the multipliers / sums of the previous pass
@@ -469,11 +476,14 @@ __global__ void __launch_bounds__(STREAM_THREADS, 2)
     asm volatile("griddepcontrol.launch_dependents;\n" ::: "memory");
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31, g = lane >> 2, t = lane & 3;
     const int S = cfg.stages;
+
     if (tid == 0) {
         for (int s = 0; s < S; ++s) mbar_init(&full[s], 1);
         *poisoned = 0;
         asm volatile("fence.mbarrier_init.release.cluster;\n" ::: "memory");
     }
+    int* s_ib = reinterpret_cast<int*>(smem + cfg.ib_off);
+    for (int i = tid; i < cfg.ib_cap; i += STREAM_THREADS) s_ib[i] = probs[i]._item_begin;
     __syncthreads();
 
     // The CTA's range of items: an even share of one problem when the grid divides well over the problems
@@ -498,7 +508,7 @@ __global__ void __launch_bounds__(STREAM_THREADS, 2)
     int nx_item = beg + warp;
     unsigned loads = 0;  // completed + pending requests of this warp (parity of the wait)
     if (warp < S && nx_item < end) {
-        locate_item(probs, cfg.P, nx_item, nx.pi, nx.chunk, nx.ritem);
+        locate_item(probs, cfg.P, nx_item, nx.pi, nx.chunk, nx.ritem, s_ib, cfg.ib_cap);
         nx.row_items = probs[nx.pi]._row_items;
         nx.chunks = probs[nx.pi]._chunks;
         if (lane == 0) {
@@ -518,7 +528,7 @@ __global__ void __launch_bounds__(STREAM_THREADS, 2)
     const int nbuf = cfg.nbuf;
     for (int sgi = 0; sgi < nbuf && pre_it < end; ++sgi) {
         int pi, chunk, ritem;
-        locate_item(probs, cfg.P, pre_it, pi, chunk, ritem);
+        locate_item(probs, cfg.P, pre_it, pi, chunk, ritem, s_ib, cfg.ib_cap);
         const wf_problem& p = probs[pi];
         quantize_tokens<XDT, STREAM_THREADS>(p, cfg.MTA, chunk * cfg.MTA, min(cfg.MTA, p.M - chunk * cfg.MTA), s_act + sgi * act_bytes, s_inv + sgi * MT,
                              s_rowsum + sgi * MT, s_maxbits + sgi * MT);
@@ -526,7 +536,7 @@ __global__ void __launch_bounds__(STREAM_THREADS, 2)
     }
     for (; it < end; ++seg) {
         int pi, chunk, ritem;
-        locate_item(probs, cfg.P, it, pi, chunk, ritem);
+        locate_item(probs, cfg.P, it, pi, chunk, ritem, s_ib, cfg.ib_cap);
         const wf_problem& p = probs[pi];
         const int seg_end = min(end, p._item_begin + (chunk + 1) * p._row_items);
         const int m0 = chunk * cfg.MTA, m_valid = min(cfg.MTA, p.M - m0);
@@ -640,10 +650,12 @@ static long long count_items16(const wf_problem* probs, int P, int MT) {
     return t;
 }
 
+constexpr int IB_CAP = 1024;  // problems whose first item index is cached in shared memory
+
 static size_t fixed_bytes(int NT, int RI) {
     const int MT = NT * 8;
     size_t b = 384 + static_cast<size_t>(MT) * 12 + 2u * RI * 16 * MT * 4;
-    return (b + 127) / 128 * 128;
+    return (b + 127) / 128 * 128 + IB_CAP * 4;
 }
 
 typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*, const cuuint64_t*,
@@ -876,6 +888,7 @@ static int run_group(const char* who, const wf_problem* dev, wf_problem* host, i
     DecodeCfg cfg;
     cfg.P = P; cfg.total_items = g.total_items; cfg.RI = g.RI; cfg.KBmax = g.KBmax; cfg.MTA = g.MTA; cfg.stages = g.stages;
     cfg.stage_bytes = g.stage_bytes; cfg.act_off = g.act_off; cfg.stage_off = g.stage_off; cfg.decoupled = g.decoupled; cfg.cpp = g.cpp; cfg.nbuf = g.nbuf;
+    cfg.ib_cap = P < IB_CAP ? P : IB_CAP; cfg.ib_off = g.act_off - IB_CAP * 4;
     cudaStream_t st = static_cast<cudaStream_t>(stream);
     switch (host[0].x_dtype) {
         case WF_F32: return dispatch_nt<WF_F32>(dev, host[0], cfg, g, flags, st);
