@@ -149,7 +149,7 @@ def run_step(wf, groups, pdl: bool):
         if g["batched"]:
             wf.bitlinear_batched(g["x"], g["codes_stack"], g["scales_stack"], out=g["y"])
         else:
-            g["group"].run(pdl=pdl)
+            g["group"].run(pdl=pdl, x_ready=True)  # the stacks are independent: no launch writes the next one's x
         if g["reduce"]:  # row-parallel stack: sum the partial outputs of all ranks (the path's only exchange)
             import torch.distributed as dist
 

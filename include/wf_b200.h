@@ -54,6 +54,11 @@ extern "C" {
 /* ---- launch flags of the contraction entry points ---- */
 #define WF_FLAG_PDL 1u /* launch with programmatic stream serialization: the kernel streams its
                           first weights before it waits for the previous kernel of the stream */
+#define WF_FLAG_X_READY 2u /* with WF_FLAG_PDL, grouped streaming launches only: the caller states that x was NOT
+                              written by the previous kernel of the stream (independent layers, experts, replicas).
+                              The kernel then reads x without waiting and only its stores wait for that kernel.
+                              Ignored by the other forms.  No counterpart in the reference (its CPU operators are
+                              synchronous calls). */
 
 int wf_version(void);
 const char* wf_last_error(void);

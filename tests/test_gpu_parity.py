@@ -431,10 +431,15 @@ def test_grouped_throughput_mode_equals_single_calls(wf, oracle_c, m, dt):
             q, s = oracle_c.act_quant(x.float().cpu().numpy(), {"f32": 0, "bf16": 1}[dt])
             assert np.array_equal(singles[0][1].cpu().numpy(), oracle_c.int_gemm(q, t.cpu().numpy()))
     grp = wf.DecodeGroup(probs)
-    outs = grp.run()
-    for (y1, a1), y2, a2 in zip(singles, outs, grp.accs):
-        assert torch.equal(a1, a2)
-        assert torch.equal(y1, y2)
+    # plain launch; chained launches with a programmatic dependency; the same with inputs declared ready (the kernel
+    # then reads x before it waits for the previous launch, and only its stores wait)
+    for rep, (pdl, x_ready) in enumerate([(False, False), (True, False), (True, True), (True, True)]):
+        for a in grp.accs:
+            a.fill_(-7)
+        outs = grp.run(pdl=pdl, x_ready=x_ready)
+        for (y1, a1), y2, a2 in zip(singles, outs, grp.accs):
+            assert torch.equal(a1, a2), (rep, pdl, x_ready)
+            assert torch.equal(y1, y2), (rep, pdl, x_ready)
     wf.device_status()
 
 

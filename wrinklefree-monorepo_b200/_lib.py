@@ -17,6 +17,7 @@ LAYOUT_WF16, LAYOUT_I2S, LAYOUT_SEQ_LSB, LAYOUT_SEQ_MSB, LAYOUT_HF = 0, 1, 2, 3,
 PACK_FP32, PACK_CAST_BF16, PACK_CAST_F16 = 0, 1, 2
 ACT_PER_TOKEN, ACT_PER_TENSOR = 0, 1
 FLAG_PDL = 1
+FLAG_X_READY = 2
 
 _i64, _int, _f32, _p, _sz, _u32 = C.c_int64, C.c_int, C.c_float, C.c_void_p, C.c_size_t, C.c_uint
 

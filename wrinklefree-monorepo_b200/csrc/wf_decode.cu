@@ -31,6 +31,7 @@
 // Every wait on an mbarrier is bounded: when the bound is hit the CTA records
 // WF_E_LIMIT in a device status word, stops waiting anywhere and runs to its end.
 #include <cuda.h>
+#include <cstddef>
 
 #include "wf_common.cuh"
 
@@ -60,6 +61,9 @@ struct DecodeCfg {
     int act_off, stage_off;  // byte offsets inside dynamic shared memory
     int nbuf;         // streaming form: activation buffers (2 when they are small, else 1)
     int cpp;          // streaming form: CTAs per problem when ranges are aligned to problems (0: contiguous split)
+    int hdr_off;      // two cached descriptor heads
+    int items_q, items_r;  // total_items = grid * items_q + items_r
+    int x_ready;      // streaming form: x does not depend on the previous kernel; only the stores wait for it
     int ib_off, ib_cap;  // shared-memory copy of the problems' first item indices (searched instead of global memory)
     int decoupled;    // 1: every consumer warp owns whole 16-row items (RI == 1); 0: the 16 warps share each item
 };
@@ -97,16 +101,25 @@ __device__ __forceinline__ int act_slot_of_k(int layout, int kl) {
 
 // ---- the quantization stage: x -> int8 in fragment order, per-token multiplier and sum ----
 // Executed by the 256 consumer threads together whenever the CTA moves to another (problem, token pass).
-template <int XDT, int NTHREADS = DEC_CONSUMERS>
-__device__ __forceinline__ void quantize_tokens(const wf_problem& p, int MTA, int m0, int m_valid, uint8_t* s_act, float* s_inv,
-                                                int* s_rowsum, unsigned* s_maxbits) {
+// Two phases with a barrier at the start of the second: the first reads x from global memory (absolute maximum per
+// token; int8 input is complete after it), the second re-reads it (cache hits) and writes the int8 fragments.  A
+// caller may put other work between them, e.g. requests for weights, which would otherwise queue ahead of x.
+constexpr int XC = 2;  // chunks of x a thread keeps in registers between the phases
+struct XCache {
+    float f[XC][8];
+};
+template <int XDT, int NTHREADS, int PHASE>
+__device__ __forceinline__ void quantize_phase(const wf_problem& p, int MTA, int m0, int m_valid, uint8_t* s_act, float* s_inv,
+                                               int* s_rowsum, unsigned* s_maxbits, XCache& cache) {
     const int tid = threadIdx.x;
-    const int KB = (p.K + 511) >> 9, Kp = KB * 512;
-    for (int i = tid; i < m_valid; i += NTHREADS) {
-        s_rowsum[i] = 0;
-        s_maxbits[i] = 0;
+    if constexpr (PHASE == 0) {
+        for (int i = tid; i < m_valid; i += NTHREADS) {
+            s_rowsum[i] = 0;
+            s_maxbits[i] = 0;
+        }
     }
-    consumer_sync<NTHREADS>();
+    consumer_sync<NTHREADS>();  // also publishes a descriptor head that was just copied to shared memory
+    const int KB = (p.K + 511) >> 9, Kp = KB * 512;
     // threads per token: all 256 for one token down to one warp per token for 8 or more
     int tpt = NTHREADS;
     while (tpt > 32 && NTHREADS / tpt < m_valid) tpt >>= 1;
@@ -114,6 +127,7 @@ __device__ __forceinline__ void quantize_tokens(const wf_problem& p, int MTA, in
     const int sub = tid / tpt, lane_in = tid % tpt;
 
     if constexpr (XDT == WF_I8) {
+        if constexpr (PHASE == 0)
         for (int tb = 0; tb < m_valid; tb += par) {
             int tok = tb + sub;
             int sum = 0;
@@ -135,18 +149,37 @@ __device__ __forceinline__ void quantize_tokens(const wf_problem& p, int MTA, in
             for (int o = 16; o > 0; o >>= 1) sum += __shfl_xor_sync(0xffffffffu, sum, o);
             if (tok < m_valid && (tid & 31) == 0) atomicAdd(&s_rowsum[tok], sum);
         }
-        if (tid < m_valid) s_inv[tid] = p.x_scale ? __frcp_rn(p.x_scale[m0 + tid]) : 1.0f;
+        if (PHASE == 0 && tid < m_valid) s_inv[tid] = p.x_scale ? __frcp_rn(p.x_scale[m0 + tid]) : 1.0f;
     } else {
+        // The first XC chunks (8 elements each) of a thread's share of the first token group stay in registers
+        // between the phases; what lies beyond is read again (cache hits).
         // pass 1: absmax per token
+        if constexpr (PHASE == 0)
         for (int tb = 0; tb < m_valid; tb += par) {
             int tok = tb + sub;
             float mx = 0.f;
             if (tok < m_valid) {
+                const int64_t base = static_cast<int64_t>(m0 + tok) * p.ldx;
+                int k = lane_in * 8;
+                if (tb == 0) {
+#pragma unroll
+                    for (int c = 0; c < XC; ++c, k += tpt * 8) {
+                        if (k < p.K) load8<XDT>(p.x, base + k, cache.f[c]);
+                    }
+                    k = lane_in * 8;
+#pragma unroll
+                    for (int c = 0; c < XC; ++c, k += tpt * 8) {
+                        if (k < p.K) {
+#pragma unroll
+                            for (int i = 0; i < 8; ++i) mx = fmaxf(mx, fabsf(cache.f[c][i]));
+                        }
+                    }
+                }
                 // several loads in flight per thread: these are dependent L2 round trips otherwise
 #pragma unroll 4
-                for (int k = lane_in * 8; k < p.K; k += tpt * 8) {
+                for (; k < p.K; k += tpt * 8) {
                     float f[8];
-                    load8<XDT>(p.x, static_cast<int64_t>(m0 + tok) * p.ldx + k, f);
+                    load8<XDT>(p.x, base + k, f);
 #pragma unroll
                     for (int i = 0; i < 8; ++i) mx = fmaxf(mx, fabsf(f[i]));
                 }
@@ -155,20 +188,18 @@ __device__ __forceinline__ void quantize_tokens(const wf_problem& p, int MTA, in
             for (int o = 16; o > 0; o >>= 1) mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, o));
             if (tok < m_valid && (tid & 31) == 0) atomicMax(&s_maxbits[tok], __float_as_uint(mx));
         }
-        consumer_sync<NTHREADS>();
         // pass 2: quantize, scatter, sum
+        if constexpr (PHASE == 1)
         for (int tb = 0; tb < m_valid; tb += par) {
             int tok = tb + sub;
             int sum = 0;
             if (tok < m_valid) {
                 const float s = act_scale_from_absmax<XDT>(__uint_as_float(s_maxbits[tok]), p.eps);
                 if (lane_in == 0) s_inv[tok] = __fdiv_rn(1.0f, s);
-#pragma unroll 4
-                for (int k = lane_in * 8; k < Kp; k += tpt * 8) {
+                const int64_t base = static_cast<int64_t>(m0 + tok) * p.ldx;
+                auto emit = [&](int k, const float (&f)[8], bool live) {
                     uint32_t w0 = 0, w1 = 0;
-                    if (k < p.K) {
-                        float f[8];
-                        load8<XDT>(p.x, static_cast<int64_t>(m0 + tok) * p.ldx + k, f);
+                    if (live) {
 #pragma unroll
                         for (int i = 0; i < 4; ++i) {
                             int a = quantize_one<XDT>(f[i], s), b = quantize_one<XDT>(f[4 + i], s);
@@ -178,9 +209,22 @@ __device__ __forceinline__ void quantize_tokens(const wf_problem& p, int MTA, in
                         }
                     }
                     int kb = k >> 9, kl = k & 511;
-                    uint8_t* base = s_act + (kb * MTA + tok) * TOK_STRIDE;
-                    *reinterpret_cast<uint32_t*>(base + act_slot_of_k(p.layout, kl)) = w0;
-                    *reinterpret_cast<uint32_t*>(base + act_slot_of_k(p.layout, kl + 4)) = w1;
+                    uint8_t* dst = s_act + (kb * MTA + tok) * TOK_STRIDE;
+                    *reinterpret_cast<uint32_t*>(dst + act_slot_of_k(p.layout, kl)) = w0;
+                    *reinterpret_cast<uint32_t*>(dst + act_slot_of_k(p.layout, kl + 4)) = w1;
+                };
+                int k = lane_in * 8;
+                if (tb == 0) {
+#pragma unroll
+                    for (int c = 0; c < XC; ++c, k += tpt * 8) {
+                        if (k < Kp) emit(k, cache.f[c], k < p.K);
+                    }
+                }
+#pragma unroll 4
+                for (; k < Kp; k += tpt * 8) {
+                    float f[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
+                    if (k < p.K) load8<XDT>(p.x, base + k, f);
+                    emit(k, f, k < p.K);
                 }
             }
 #pragma unroll
@@ -188,7 +232,15 @@ __device__ __forceinline__ void quantize_tokens(const wf_problem& p, int MTA, in
             if (tok < m_valid && (tid & 31) == 0) atomicAdd(&s_rowsum[tok], sum);
         }
     }
-    consumer_sync<NTHREADS>();
+    if constexpr (PHASE == 1) consumer_sync<NTHREADS>();
+}
+
+template <int XDT, int NTHREADS = DEC_CONSUMERS>
+__device__ __forceinline__ void quantize_tokens(const wf_problem& p, int MTA, int m0, int m_valid, uint8_t* s_act, float* s_inv,
+                                                int* s_rowsum, unsigned* s_maxbits) {
+    XCache cache;
+    quantize_phase<XDT, NTHREADS, 0>(p, MTA, m0, m_valid, s_act, s_inv, s_rowsum, s_maxbits, cache);
+    quantize_phase<XDT, NTHREADS, 1>(p, MTA, m0, m_valid, s_act, s_inv, s_rowsum, s_maxbits, cache);
 }
 
 __device__ __forceinline__ uint4 lds128(uint32_t addr) {
@@ -244,36 +296,68 @@ __device__ __forceinline__ unsigned segment_bytes(const wf_problem* p, int seg) 
     const int n = min(KB - lo, p->_kb_seg);
     return static_cast<unsigned>(n) * TILE_BYTES;
 }
-__device__ __forceinline__ void issue_segment(const wf_problem* p, int row, int seg, uint8_t* dst, uint64_t* bar) {
-    const int KB = (p->K + 511) >> 9, kbf = p->_kb_full, lo = seg * p->_kb_seg;
-    const int n = min(KB - lo, p->_kb_seg);
+// `h` supplies the scalar fields (it may be a copy of the descriptor's head in shared memory), `gp` the tensor maps,
+// which the TMA unit reads from global memory.
+__device__ __forceinline__ void issue_segment(const wf_problem* h, const wf_problem* gp, int row, int seg, uint8_t* dst, uint64_t* bar) {
+    const int KB = (h->K + 511) >> 9, kbf = h->_kb_full, lo = seg * h->_kb_seg;
+    const int n = min(KB - lo, h->_kb_seg);
     if (kbf > 0) {
-        const int nfull = max(0, min(kbf - lo, p->_kb_seg));
-        if (nfull == p->_kb_seg)
-            tma_load_3d(dst, p->_tmap_main, 0, row, lo, bar);
+        const int nfull = max(0, min(kbf - lo, h->_kb_seg));
+        if (nfull == h->_kb_seg)
+            tma_load_3d(dst, gp->_tmap_main, 0, row, lo, bar);
         else if (nfull > 0)
-            tma_load_3d(dst, p->_tmap_last, 0, row, lo, bar);
-        if (nfull < n) tma_load_2d(dst + nfull * TILE_BYTES, p->_tmap_tail, 0, row, bar);  // the partial block of K
+            tma_load_3d(dst, gp->_tmap_last, 0, row, lo, bar);
+        if (nfull < n) tma_load_2d(dst + nfull * TILE_BYTES, gp->_tmap_tail, 0, row, bar);  // the partial block of K
     } else {  // plain 2-D view: one request per 128-byte column block
-        for (int i = 0; i < n; ++i) tma_load_2d(dst + i * TILE_BYTES, p->_tmap_tail, (lo + i) * 128, row, bar);
+        for (int i = 0; i < n; ++i) tma_load_2d(dst + i * TILE_BYTES, gp->_tmap_tail, (lo + i) * 128, row, bar);
     }
+}
+__device__ __forceinline__ void issue_segment(const wf_problem* p, int row, int seg, uint8_t* dst, uint64_t* bar) {
+    issue_segment(p, p, row, seg, dst, bar);
+}
+
+// ---- the head of a descriptor, cached in shared memory -------------------------------------------------
+// Every read of a descriptor field from global memory is a round trip of half a microsecond, and a barrier
+// makes the compiler repeat it.  The CTA therefore copies the head (all fields before the tensor maps) of the
+// problem it works on into shared memory once, together with the VALUE of the weight scale.
+constexpr int HDR_WORDS = 36;    // 144 bytes: up to and including _kb_seg, _ksegs
+constexpr int HDR_STRIDE = 160;  // bytes per cached head; word HDR_WORDS holds the weight scale
+static_assert(offsetof(wf_problem, _pad) <= HDR_WORDS * 4 && offsetof(wf_problem, _tmap_main) >= HDR_WORDS * 4, "head of wf_problem");
+
+__device__ __forceinline__ void fill_header(uint8_t* slot, const wf_problem* src, int t) {
+    uint32_t* dst = reinterpret_cast<uint32_t*>(slot);
+    if (static_cast<unsigned>(t) < static_cast<unsigned>(HDR_WORDS))
+        dst[t] = reinterpret_cast<const uint32_t*>(src)[t];
+    else if (t == HDR_WORDS)
+        dst[HDR_WORDS] = __float_as_uint(src->w_scale ? __ldg(src->w_scale) : src->w_scale_host);
+}
+__device__ __forceinline__ float header_w_scale(const uint8_t* slot) {
+    return __uint_as_float(reinterpret_cast<const uint32_t*>(slot)[HDR_WORDS]);
 }
 
 // item index -> (problem, token pass, row item)
 // `ib` is the shared-memory table of _item_begin (valid for the first ib_cap problems): a search through global memory
 // is a chain of dependent cache misses, several microseconds per call.
+__device__ __forceinline__ int first_item(const wf_problem* __restrict__ probs, int pi, const int* ib, int ib_cap) {
+    return pi < ib_cap ? ib[pi] : probs[pi]._item_begin;
+}
+// item index -> problem, and the item's index inside the problem
+__device__ __forceinline__ int locate_problem(const wf_problem* __restrict__ probs, int P, int item, const int* ib, int ib_cap, int& local) {
+    int lo = 0, hi = P - 1;
+    while (lo < hi) {  // last problem whose first item <= item
+        int mid = (lo + hi + 1) >> 1;
+        if (first_item(probs, mid, ib, ib_cap) <= item) lo = mid; else hi = mid - 1;
+    }
+    local = item - first_item(probs, lo, ib, ib_cap);
+    return lo;
+}
 __device__ __forceinline__ void locate_item(const wf_problem* __restrict__ probs, int P, int item, int& pi, int& chunk, int& ritem,
                                             const int* ib, int ib_cap) {
-    int lo = 0, hi = P - 1;
-    while (lo < hi) {  // last problem whose _item_begin <= item
-        int mid = (lo + hi + 1) >> 1;
-        const int first = mid < ib_cap ? ib[mid] : probs[mid]._item_begin;
-        if (first <= item) lo = mid; else hi = mid - 1;
-    }
-    pi = lo;
-    int local = item - probs[lo]._item_begin;
-    chunk = local / probs[lo]._row_items;
-    ritem = local % probs[lo]._row_items;
+    int local;
+    pi = locate_problem(probs, P, item, ib, ib_cap, local);
+    const int row_items = probs[pi]._row_items;
+    chunk = local / row_items;
+    ritem = local % row_items;
 }
 
 template <int XDT, int NT, bool FOURACC>
@@ -310,8 +394,10 @@ __global__ void __launch_bounds__(DEC_THREADS, 1)
     for (int i = tid; i < cfg.ib_cap; i += DEC_THREADS) s_ib[i] = probs[i]._item_begin;
     __syncthreads();
 
-    const int beg = static_cast<int>(static_cast<int64_t>(blockIdx.x) * cfg.total_items / gridDim.x);
-    const int end = static_cast<int>(static_cast<int64_t>(blockIdx.x + 1) * cfg.total_items / gridDim.x);
+    // an even split of the item list: the first items_r CTAs take one item more
+    const int bx = blockIdx.x;
+    const int beg = bx * cfg.items_q + min(bx, cfg.items_r);
+    const int end = beg + cfg.items_q + (bx < cfg.items_r ? 1 : 0);
     const int rows_item = cfg.RI * 16;
 
     if (warp == DEC_CONSUMERS / 32) {
@@ -354,14 +440,28 @@ __global__ void __launch_bounds__(DEC_THREADS, 1)
     // ---------------- consumers
     const int g = lane >> 2, t = lane & 3;
     const int rt_local = warp % cfg.RI, ks = warp / cfg.RI, KS = NW / cfg.RI;
-    int cur_p = -1, cur_chunk = -1, m0 = 0, m_valid = 0;
+    uint8_t* s_hdr = smem + cfg.hdr_off;
+    const wf_problem& p = *reinterpret_cast<const wf_problem*>(s_hdr);  // head of the current problem (no tensor maps)
+    int hdr_p = -1, cur_p = -1, cur_chunk = -1, m0 = 0, m_valid = 0;
+    if (beg < end) {  // the descriptor does not depend on the previous kernel: fetch its head before waiting
+        int local;
+        hdr_p = locate_problem(probs, cfg.P, beg, s_ib, cfg.ib_cap, local);
+        fill_header(s_hdr, &probs[hdr_p], tid);
+    }
     // x may be produced by the previous kernel of the stream
     asm volatile("griddepcontrol.wait;\n" ::: "memory");
+    consumer_sync();
 
     for (int it = beg, n = 0; it < end; ++it, ++n) {
-        int pi, chunk, ritem;
-        locate_item(probs, cfg.P, it, pi, chunk, ritem, s_ib, cfg.ib_cap);
-        const wf_problem& p = probs[pi];
+        int local;
+        const int pi = locate_problem(probs, cfg.P, it, s_ib, cfg.ib_cap, local);
+        if (pi != hdr_p) {
+            consumer_sync();  // nobody still reads the previous head
+            fill_header(s_hdr, &probs[pi], tid);
+            hdr_p = pi;
+            consumer_sync();
+        }
+        const int chunk = local / p._row_items, ritem = local % p._row_items;
         if (pi != cur_p || chunk != cur_chunk) {
             consumer_sync();  // nobody still reads the multipliers / sums of the previous pass
             cur_p = pi;
@@ -412,7 +512,7 @@ __global__ void __launch_bounds__(DEC_THREADS, 1)
         consumer_sync();
 
         // epilogue: integer correction, fp32 rescale in the stated order, bias, store; clears the tile
-        const float s_w = p.w_scale ? __ldg(p.w_scale) : p.w_scale_host;
+        const float s_w = header_w_scale(s_hdr);
         int* redb = s_red + (n & 1) * red_size;
         const int r0 = ritem * rows_item;
         for (int idx = tid; idx < rows_item * m_valid; idx += DEC_CONSUMERS) {
@@ -443,19 +543,6 @@ struct ItemCursor {  // walks the item list in strides
     int pi, chunk, ritem, row_items, chunks;
 };
 
-__device__ __forceinline__ void cursor_advance(ItemCursor& c, const wf_problem* __restrict__ probs, int P, int by) {
-    c.ritem += by;
-    while (c.ritem >= c.row_items) {
-        c.ritem -= c.row_items;
-        if (++c.chunk == c.chunks) {
-            c.chunk = 0;
-            if (++c.pi >= P) return;
-            c.row_items = probs[c.pi]._row_items;
-            c.chunks = probs[c.pi]._chunks;
-        }
-    }
-}
-
 constexpr int STREAM_THREADS = 256;  // 8 warps; two such CTAs share an SM
 constexpr int SW = STREAM_THREADS / 32;
 
@@ -471,6 +558,8 @@ __global__ void __launch_bounds__(STREAM_THREADS, 2)
     unsigned* s_maxbits = reinterpret_cast<unsigned*>(smem + 384 + MT * 16);  // [2][MT]
     uint8_t* s_act = smem + cfg.act_off;                                    // [2][KBmax * MTA * TOK_STRIDE]
     uint8_t* s_stage = smem + cfg.stage_off;
+    uint8_t* s_hdr = smem + cfg.hdr_off;                                    // [2][HDR_STRIDE], one per activation buffer
+    int* s_ib = reinterpret_cast<int*>(smem + cfg.ib_off);
     const wf_problem* probs = dev_problems ? dev_problems : &single;
 
     asm volatile("griddepcontrol.launch_dependents;\n" ::: "memory");
@@ -482,8 +571,17 @@ __global__ void __launch_bounds__(STREAM_THREADS, 2)
         *poisoned = 0;
         asm volatile("fence.mbarrier_init.release.cluster;\n" ::: "memory");
     }
-    int* s_ib = reinterpret_cast<int*>(smem + cfg.ib_off);
     for (int i = tid; i < cfg.ib_cap; i += STREAM_THREADS) s_ib[i] = probs[i]._item_begin;
+    // When the CTAs' ranges are aligned to the problems the first problem is known without the table: its head is
+    // fetched in the same round trip.
+    int hdr_pi0 = -1, hdr_pi1 = -1;  // the problems whose heads the two slots hold
+    if (cfg.cpp > 0 || cfg.P == 1) {
+        const int pi = cfg.cpp > 0 ? blockIdx.x / cfg.cpp : 0;
+        if (pi < cfg.P) {
+            fill_header(s_hdr, &probs[pi], tid);
+            hdr_pi0 = pi;
+        }
+    }
     __syncthreads();
 
     // The CTA's range of items: an even share of one problem when the grid divides well over the problems
@@ -492,73 +590,142 @@ __global__ void __launch_bounds__(STREAM_THREADS, 2)
     if (cfg.cpp > 0) {
         const int pi = blockIdx.x / cfg.cpp, sub = blockIdx.x % cfg.cpp;
         if (pi >= cfg.P) return;
-        const int ib = probs[pi]._item_begin, cnt = probs[pi]._row_items * probs[pi]._chunks;
-        beg = ib + static_cast<int>(static_cast<int64_t>(sub) * cnt / cfg.cpp);
-        end = ib + static_cast<int>(static_cast<int64_t>(sub + 1) * cnt / cfg.cpp);
-        if (beg >= end) return;
+        const int ib = first_item(probs, pi, s_ib, cfg.ib_cap);
+        const int cnt = (pi + 1 < cfg.P ? first_item(probs, pi + 1, s_ib, cfg.ib_cap) : cfg.total_items) - ib;
+        const int q = cnt / cfg.cpp, r = cnt - q * cfg.cpp;  // the first r CTAs of the problem take one item more
+        beg = ib + sub * q + min(sub, r);
+        end = beg + q + (sub < r ? 1 : 0);
     } else {
-        beg = static_cast<int>(static_cast<int64_t>(blockIdx.x) * cfg.total_items / gridDim.x);
-        end = static_cast<int>(static_cast<int64_t>(blockIdx.x + 1) * cfg.total_items / gridDim.x);
+        const int bx = blockIdx.x;
+        beg = bx * cfg.items_q + min(bx, cfg.items_r);
+        end = beg + cfg.items_q + (bx < cfg.items_r ? 1 : 0);
     }
+    if (beg >= end) return;
+    // Warp w starts with item beg + w; every further item is claimed from this counter when a warp has consumed its
+    // stage, so a warp that meets slower memory channels takes fewer items instead of holding the CTA back.
+    int* s_next = reinterpret_cast<int*>(smem + 260);
+    if (tid == 0) *s_next = beg + S;  // published by the barriers of the quantization below
     uint8_t* my_stage = s_stage + static_cast<size_t>(warp) * cfg.stage_bytes;
     const uint32_t w_r0 = smem_u32(my_stage) + g * 128;
-
-    // cursor of the next item this warp will request; the first request goes out before anything else
-    ItemCursor nx;
-    int nx_item = beg + warp;
-    unsigned loads = 0;  // completed + pending requests of this warp (parity of the wait)
-    if (warp < S && nx_item < end) {
-        locate_item(probs, cfg.P, nx_item, nx.pi, nx.chunk, nx.ritem, s_ib, cfg.ib_cap);
-        nx.row_items = probs[nx.pi]._row_items;
-        nx.chunks = probs[nx.pi]._chunks;
-        if (lane == 0) {
-            mbar_expect_tx(&full[warp], segment_bytes(&probs[nx.pi], 0));
-            issue_segment(&probs[nx.pi], nx.ritem * 16, 0, my_stage, &full[warp]);
-        }
-    }
-
-    // x may be produced by the previous kernel of the stream
-    asm volatile("griddepcontrol.wait;\n" ::: "memory");
+    const wf_problem* const h0 = reinterpret_cast<const wf_problem*>(s_hdr);
+    const wf_problem* const h1 = reinterpret_cast<const wf_problem*>(s_hdr + HDR_STRIDE);
 
     // Two activation buffers: the first two passes of the CTA's range are quantized up front, so that a CTA
     // whose range crosses from one problem into the next does not stop streaming there.  Later passes (rare:
     // problems much smaller than a CTA's share) reuse the buffers behind a CTA-wide barrier.
     const int act_bytes = cfg.KBmax * cfg.MTA * TOK_STRIDE;
-    int seg = 0, it = beg, pre_it = beg;
     const int nbuf = cfg.nbuf;
-    for (int sgi = 0; sgi < nbuf && pre_it < end; ++sgi) {
-        int pi, chunk, ritem;
-        locate_item(probs, cfg.P, pre_it, pi, chunk, ritem, s_ib, cfg.ib_cap);
-        const wf_problem& p = probs[pi];
-        quantize_tokens<XDT, STREAM_THREADS>(p, cfg.MTA, chunk * cfg.MTA, min(cfg.MTA, p.M - chunk * cfg.MTA), s_act + sgi * act_bytes, s_inv + sgi * MT,
-                             s_rowsum + sgi * MT, s_maxbits + sgi * MT);
-        pre_it = min(end, p._item_begin + (chunk + 1) * p._row_items);
-    }
-    for (; it < end; ++seg) {
-        int pi, chunk, ritem;
-        locate_item(probs, cfg.P, it, pi, chunk, ritem, s_ib, cfg.ib_cap);
-        const wf_problem& p = probs[pi];
-        const int seg_end = min(end, p._item_begin + (chunk + 1) * p._row_items);
-        const int m0 = chunk * cfg.MTA, m_valid = min(cfg.MTA, p.M - m0);
-        const int buf = seg % nbuf;
-        if (seg >= nbuf) {
-            consumer_sync<STREAM_THREADS>();  // every warp is done with the pass that used this buffer
-            quantize_tokens<XDT, STREAM_THREADS>(p, cfg.MTA, m0, m_valid, s_act + buf * act_bytes, s_inv + buf * MT, s_rowsum + buf * MT,
-                                 s_maxbits + buf * MT);
+    int pre_chunk0 = 0, pre_chunk1 = 0, pre_end0 = end, pre_end1 = end, npre = 1;
+    {
+        int local;
+        const int pi = locate_problem(probs, cfg.P, beg, s_ib, cfg.ib_cap, local);
+        if (pi != hdr_pi0) {  // uniform over the CTA
+            fill_header(s_hdr, &probs[pi], tid);
+            hdr_pi0 = pi;
+            __syncthreads();
         }
+        pre_chunk0 = local / h0->_row_items;
+        pre_end0 = min(end, beg - local + (pre_chunk0 + 1) * h0->_row_items);
+        if (nbuf > 1 && pre_end0 < end) {
+            int local1;
+            hdr_pi1 = locate_problem(probs, cfg.P, pre_end0, s_ib, cfg.ib_cap, local1);
+            fill_header(s_hdr + HDR_STRIDE, &probs[hdr_pi1], tid);
+            __syncthreads();
+            pre_chunk1 = local1 / h1->_row_items;
+            pre_end1 = min(end, pre_end0 - local1 + (pre_chunk1 + 1) * h1->_row_items);
+            npre = 2;
+        }
+    }
+    // head of problem pi: a cached copy if there is one, else the descriptor in global memory
+    auto head_of = [&](int pi) -> const wf_problem* { return pi == hdr_pi0 ? h0 : (pi == hdr_pi1 ? h1 : &probs[pi]); };
+
+    // cursor of the item whose first K segment is in flight in this warp's stage (>= end: none)
+    ItemCursor nx;
+    int nx_item = warp < S ? beg + warp : end;
+    unsigned loads = 0;  // completed + pending requests of this warp (parity of the wait)
+    auto issue_first = [&]() {
+        if (warp < S && nx_item < end) {
+            int local;
+            nx.pi = locate_problem(probs, cfg.P, nx_item, s_ib, cfg.ib_cap, local);
+            const wf_problem* h = head_of(nx.pi);
+            nx.row_items = h->_row_items;
+            nx.chunks = h->_chunks;
+            nx.chunk = local / nx.row_items;
+            nx.ritem = local % nx.row_items;
+            if (lane == 0) {
+                mbar_expect_tx(&full[warp], segment_bytes(h, 0));
+                issue_segment(h, &probs[nx.pi], nx.ritem * 16, 0, my_stage, &full[warp]);
+            }
+        }
+    };
+    // The weights never depend on the previous kernel, x normally does: request weights, wait, read x.  Where the
+    // caller states that x is ready, x is read first (behind some 100 KB of weight requests per CTA its reads
+    // would wait for microseconds) and only the stores wait for the previous kernel.
+    if (!cfg.x_ready) {
+        issue_first();
+        asm volatile("griddepcontrol.wait;\n" ::: "memory");
+    }
+    XCache xcache0, xcache1;
+    {
+        const int m0 = pre_chunk0 * cfg.MTA;
+        quantize_phase<XDT, STREAM_THREADS, 0>(*h0, cfg.MTA, m0, min(cfg.MTA, h0->M - m0), s_act, s_inv, s_rowsum, s_maxbits, xcache0);
+    }
+    if (npre > 1) {
+        const int m0 = pre_chunk1 * cfg.MTA;
+        quantize_phase<XDT, STREAM_THREADS, 0>(*h1, cfg.MTA, m0, min(cfg.MTA, h1->M - m0), s_act + act_bytes, s_inv + MT, s_rowsum + MT,
+                                               s_maxbits + MT, xcache1);
+    }
+    if (cfg.x_ready) issue_first();
+    {
+        const int m0 = pre_chunk0 * cfg.MTA;
+        quantize_phase<XDT, STREAM_THREADS, 1>(*h0, cfg.MTA, m0, min(cfg.MTA, h0->M - m0), s_act, s_inv, s_rowsum, s_maxbits, xcache0);
+    }
+    if (npre > 1) {
+        const int m0 = pre_chunk1 * cfg.MTA;
+        quantize_phase<XDT, STREAM_THREADS, 1>(*h1, cfg.MTA, m0, min(cfg.MTA, h1->M - m0), s_act + act_bytes, s_inv + MT, s_rowsum + MT,
+                                               s_maxbits + MT, xcache1);
+    }
+    bool may_store = !cfg.x_ready;  // the previous kernel has been waited for
+
+    int it = beg;
+    for (int seg = 0; it < end; ++seg) {
+        const int buf = seg % nbuf;
+        uint8_t* const slot = s_hdr + buf * HDR_STRIDE;
+        const wf_problem& p = *reinterpret_cast<const wf_problem*>(slot);
+        int pi, chunk, seg_end;
+        if (seg < npre) {
+            pi = seg == 0 ? hdr_pi0 : hdr_pi1;
+            chunk = seg == 0 ? pre_chunk0 : pre_chunk1;
+            seg_end = seg == 0 ? pre_end0 : pre_end1;
+        } else {
+            consumer_sync<STREAM_THREADS>();  // every warp is done with the pass that used this buffer and this head
+            int local;
+            pi = locate_problem(probs, cfg.P, it, s_ib, cfg.ib_cap, local);
+            fill_header(slot, &probs[pi], tid);
+            if (buf == 0) hdr_pi0 = pi; else hdr_pi1 = pi;
+            consumer_sync<STREAM_THREADS>();
+            chunk = local / p._row_items;
+            seg_end = min(end, it - local + (chunk + 1) * p._row_items);
+            const int m0q = chunk * cfg.MTA;
+            quantize_tokens<XDT, STREAM_THREADS>(p, cfg.MTA, m0q, min(cfg.MTA, p.M - m0q), s_act + buf * act_bytes, s_inv + buf * MT,
+                                                 s_rowsum + buf * MT, s_maxbits + buf * MT);
+        }
+        const int m0 = chunk * cfg.MTA, m_valid = min(cfg.MTA, p.M - m0);
+        const int ritem = it - first_item(probs, pi, s_ib, cfg.ib_cap) - chunk * p._row_items;
+        const wf_problem* const gp = &probs[pi];
         const uint32_t act0 = smem_u32(s_act + buf * act_bytes);
         const float* const inv_p = s_inv + buf * MT;
         const int* const rowsum_p = s_rowsum + buf * MT;
         const int KB = (p.K + 511) >> 9, kb_seg = p._kb_seg, ksegs = p._ksegs;
-        const float s_w = p.w_scale ? __ldg(p.w_scale) : p.w_scale_host;
+        const float s_w = header_w_scale(slot);
         void* const y = p.y;
         const void* const bias = p.bias;
         int32_t* const acc_out = p.acc_out;
         const int64_t ldy = p.ldy;
         const int N = p.N, y_dtype = p.y_dtype, bias_dtype = p.bias_dtype;
-        if (warp < S) {
-            int j = it + ((warp - (it - beg)) % S + S) % S;  // first item of this warp in the pass
-            for (; j < seg_end; j += S) {
+        {
+            while (nx_item < seg_end) {  // this warp's items of the pass
+                const int j = nx_item;
                 int acc[NT][FOURACC ? 4 : 1][4];
 #pragma unroll
                 for (int a = 0; a < NT; ++a)
@@ -581,19 +748,38 @@ __global__ void __launch_bounds__(STREAM_THREADS, 2)
                         if (lane == 0) {
                             asm volatile("fence.proxy.async.shared::cta;\n" ::: "memory");
                             mbar_expect_tx(&full[warp], segment_bytes(&p, ks + 1));
-                            issue_segment(&p, my_row, ks + 1, my_stage, &full[warp]);
+                            issue_segment(&p, gp, my_row, ks + 1, my_stage, &full[warp]);
                         }
                     } else {
-                        nx_item += S;  // this warp's next item (it may belong to a later pass)
+                        int claimed = 0;  // this warp's next item (it may belong to a later pass)
+                        if (lane == 0) claimed = atomicAdd(s_next, 1);
+                        claimed = __shfl_sync(0xffffffffu, claimed, 0);
+                        const int step = claimed - nx_item;
+                        nx_item = claimed < end ? claimed : end;
                         if (nx_item < end) {
-                            cursor_advance(nx, probs, cfg.P, S);
+                            nx.ritem += step;
+                            while (nx.ritem >= nx.row_items) {
+                                nx.ritem -= nx.row_items;
+                                if (++nx.chunk == nx.chunks) {
+                                    nx.chunk = 0;
+                                    ++nx.pi;  // nx_item < end: the problem exists
+                                    const wf_problem* h = head_of(nx.pi);
+                                    nx.row_items = h->_row_items;
+                                    nx.chunks = h->_chunks;
+                                }
+                            }
                             if (lane == 0) {
+                                const wf_problem* h = head_of(nx.pi);
                                 asm volatile("fence.proxy.async.shared::cta;\n" ::: "memory");
-                                mbar_expect_tx(&full[warp], segment_bytes(&probs[nx.pi], 0));
-                                issue_segment(&probs[nx.pi], nx.ritem * 16, 0, my_stage, &full[warp]);
+                                mbar_expect_tx(&full[warp], segment_bytes(h, 0));
+                                issue_segment(h, &probs[nx.pi], nx.ritem * 16, 0, my_stage, &full[warp]);
                             }
                         }
                     }
+                }
+                if (!may_store) {  // y may still be in use by the previous kernel
+                    asm volatile("griddepcontrol.wait;\n" ::: "memory");
+                    may_store = true;
                 }
                 // epilogue straight from the accumulators: lane holds rows g, g+8 x tokens 2t, 2t+1 of every token tile
                 const int row_a = my_row + g, row_b = row_a + 8;
@@ -622,6 +808,8 @@ __global__ void __launch_bounds__(STREAM_THREADS, 2)
         }
         it = seg_end;
     }
+    // a kernel that follows with a programmatic dependency relies on this grid having waited for its own predecessor
+    if (!may_store) asm volatile("griddepcontrol.wait;\n" ::: "memory");
 }
 
 // ------------------------------------------------------------------ host side
@@ -655,7 +843,7 @@ constexpr int IB_CAP = 1024;  // problems whose first item index is cached in sh
 static size_t fixed_bytes(int NT, int RI) {
     const int MT = NT * 8;
     size_t b = 384 + static_cast<size_t>(MT) * 12 + 2u * RI * 16 * MT * 4;
-    return (b + 127) / 128 * 128 + IB_CAP * 4;
+    return (b + 127) / 128 * 128 + IB_CAP * 4 + 384;  // + table of first items + two descriptor heads
 }
 
 typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*, const cuuint64_t*,
@@ -798,7 +986,7 @@ static int plan_group(wf_problem* probs, int P, GroupPlan& g, bool write_fields)
     const long long total = count_items(RI);
     if (total > 0x7fffffffLL) return fail(WF_E_LIMIT, "wf_bitlinear_decode: too many work items");
     g.total_items = static_cast<int>(total);
-    g.grid = g.decoupled ? 2 * sms : (g.total_items <= 2 * sms ? g.total_items : sms);
+    g.grid = g.decoupled ? 2 * sms : (g.total_items < sms ? g.total_items : sms);  // one CTA of the shared form per SM: no second wave
     g.cpp = 0;
     if (g.decoupled && P <= g.grid) {
         const int cpp = g.grid / P;
@@ -888,7 +1076,9 @@ static int run_group(const char* who, const wf_problem* dev, wf_problem* host, i
     DecodeCfg cfg;
     cfg.P = P; cfg.total_items = g.total_items; cfg.RI = g.RI; cfg.KBmax = g.KBmax; cfg.MTA = g.MTA; cfg.stages = g.stages;
     cfg.stage_bytes = g.stage_bytes; cfg.act_off = g.act_off; cfg.stage_off = g.stage_off; cfg.decoupled = g.decoupled; cfg.cpp = g.cpp; cfg.nbuf = g.nbuf;
-    cfg.ib_cap = P < IB_CAP ? P : IB_CAP; cfg.ib_off = g.act_off - IB_CAP * 4;
+    cfg.ib_cap = P < IB_CAP ? P : IB_CAP; cfg.ib_off = g.act_off - IB_CAP * 4 - 384; cfg.hdr_off = g.act_off - 384;
+    cfg.x_ready = (flags & WF_FLAG_X_READY) ? 1 : 0;
+    cfg.items_q = g.total_items / g.grid; cfg.items_r = g.total_items % g.grid;
     cudaStream_t st = static_cast<cudaStream_t>(stream);
     switch (host[0].x_dtype) {
         case WF_F32: return dispatch_nt<WF_F32>(dev, host[0], cfg, g, flags, st);

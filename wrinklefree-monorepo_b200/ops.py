@@ -290,12 +290,15 @@ class DecodeGroup:
         self._dev = torch.frombuffer(bytearray(raw), dtype=torch.uint8).to(dev)
         self.count = len(problems)
 
-    def run(self, pdl: bool = False):
+    def run(self, pdl: bool = False, x_ready: bool = False):
+        """Launches the group.  `x_ready` (with `pdl`): the inputs were not written by the previous kernel of the
+        stream, so the kernel reads them without waiting for it (independent layers, experts, replicas)."""
         import ctypes as C
 
+        flags = (L.FLAG_PDL if pdl else 0) | (L.FLAG_X_READY if (pdl and x_ready) else 0)
         with torch.cuda.device(self.device):
             L.check(L.lib().wf_bitlinear_decode_grouped(self._dev.data_ptr(), C.addressof(self._host), self.count,
-                                                        L.FLAG_PDL if pdl else 0, _stream()), "wf_bitlinear_decode_grouped")
+                                                        flags, _stream()), "wf_bitlinear_decode_grouped")
         return self.outputs
 
 
