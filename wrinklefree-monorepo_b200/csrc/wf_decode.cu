@@ -63,6 +63,7 @@ struct DecodeCfg {
     int cpp;          // streaming form: CTAs per problem when ranges are aligned to problems (0: contiguous split)
     int hdr_off;      // two cached descriptor heads
     int items_q, items_r;  // total_items = grid * items_q + items_r
+    int uniform_items;     // streaming form: > 0 when all problems have equal M, N, K and layout: items of each
     int x_ready;      // streaming form: x does not depend on the previous kernel; only the stores wait for it
     int ib_off, ib_cap;  // shared-memory copy of the problems' first item indices (searched instead of global memory)
     int decoupled;    // 1: every consumer warp owns whole 16-row items (RI == 1); 0: the 16 warps share each item
@@ -338,11 +339,19 @@ __device__ __forceinline__ float header_w_scale(const uint8_t* slot) {
 // item index -> (problem, token pass, row item)
 // `ib` is the shared-memory table of _item_begin (valid for the first ib_cap problems): a search through global memory
 // is a chain of dependent cache misses, several microseconds per call.
-__device__ __forceinline__ int first_item(const wf_problem* __restrict__ probs, int pi, const int* ib, int ib_cap) {
+// `uni` > 0: every problem of the group has that many items (a stack of equal layers), no table is needed.
+__device__ __forceinline__ int first_item(const wf_problem* __restrict__ probs, int pi, const int* ib, int ib_cap, int uni = 0) {
+    if (uni > 0) return pi * uni;
     return pi < ib_cap ? ib[pi] : probs[pi]._item_begin;
 }
 // item index -> problem, and the item's index inside the problem
-__device__ __forceinline__ int locate_problem(const wf_problem* __restrict__ probs, int P, int item, const int* ib, int ib_cap, int& local) {
+__device__ __forceinline__ int locate_problem(const wf_problem* __restrict__ probs, int P, int item, const int* ib, int ib_cap, int& local,
+                                              int uni = 0) {
+    if (uni > 0) {
+        const int pi = item / uni;
+        local = item - pi * uni;
+        return pi;
+    }
     int lo = 0, hi = P - 1;
     while (lo < hi) {  // last problem whose first item <= item
         int mid = (lo + hi + 1) >> 1;
@@ -571,17 +580,12 @@ __global__ void __launch_bounds__(STREAM_THREADS, 2)
         *poisoned = 0;
         asm volatile("fence.mbarrier_init.release.cluster;\n" ::: "memory");
     }
-    for (int i = tid; i < cfg.ib_cap; i += STREAM_THREADS) s_ib[i] = probs[i]._item_begin;
-    // When the CTAs' ranges are aligned to the problems the first problem is known without the table: its head is
-    // fetched in the same round trip.
-    int hdr_pi0 = -1, hdr_pi1 = -1;  // the problems whose heads the two slots hold
-    if (cfg.cpp > 0 || cfg.P == 1) {
-        const int pi = cfg.cpp > 0 ? blockIdx.x / cfg.cpp : 0;
-        if (pi < cfg.P) {
-            fill_header(s_hdr, &probs[pi], tid);
-            hdr_pi0 = pi;
-        }
-    }
+    // A stack of equal problems needs no table of first items, and the scalar fields of every descriptor equal those
+    // of the copy that travels as a kernel parameter: the first requests for weights go out without any read of
+    // global memory before them.
+    const int uni = cfg.uniform_items;
+    if (uni == 0)
+        for (int i = tid; i < cfg.ib_cap; i += STREAM_THREADS) s_ib[i] = probs[i]._item_begin;
     __syncthreads();
 
     // The CTA's range of items: an even share of one problem when the grid divides well over the problems
@@ -590,8 +594,8 @@ __global__ void __launch_bounds__(STREAM_THREADS, 2)
     if (cfg.cpp > 0) {
         const int pi = blockIdx.x / cfg.cpp, sub = blockIdx.x % cfg.cpp;
         if (pi >= cfg.P) return;
-        const int ib = first_item(probs, pi, s_ib, cfg.ib_cap);
-        const int cnt = (pi + 1 < cfg.P ? first_item(probs, pi + 1, s_ib, cfg.ib_cap) : cfg.total_items) - ib;
+        const int ib = first_item(probs, pi, s_ib, cfg.ib_cap, uni);
+        const int cnt = (pi + 1 < cfg.P ? first_item(probs, pi + 1, s_ib, cfg.ib_cap, uni) : cfg.total_items) - ib;
         const int q = cnt / cfg.cpp, r = cnt - q * cfg.cpp;  // the first r CTAs of the problem take one item more
         beg = ib + sub * q + min(sub, r);
         end = beg + q + (sub < r ? 1 : 0);
@@ -604,50 +608,24 @@ __global__ void __launch_bounds__(STREAM_THREADS, 2)
     // Warp w starts with item beg + w; every further item is claimed from this counter when a warp has consumed its
     // stage, so a warp that meets slower memory channels takes fewer items instead of holding the CTA back.
     int* s_next = reinterpret_cast<int*>(smem + 260);
-    if (tid == 0) *s_next = beg + S;  // published by the barriers of the quantization below
+    if (tid == 0) *s_next = beg + S;  // published by the barriers below
     uint8_t* my_stage = s_stage + static_cast<size_t>(warp) * cfg.stage_bytes;
     const uint32_t w_r0 = smem_u32(my_stage) + g * 128;
     const wf_problem* const h0 = reinterpret_cast<const wf_problem*>(s_hdr);
     const wf_problem* const h1 = reinterpret_cast<const wf_problem*>(s_hdr + HDR_STRIDE);
-
-    // Two activation buffers: the first two passes of the CTA's range are quantized up front, so that a CTA
-    // whose range crosses from one problem into the next does not stop streaming there.  Later passes (rare:
-    // problems much smaller than a CTA's share) reuse the buffers behind a CTA-wide barrier.
-    const int act_bytes = cfg.KBmax * cfg.MTA * TOK_STRIDE;
-    const int nbuf = cfg.nbuf;
-    int pre_chunk0 = 0, pre_chunk1 = 0, pre_end0 = end, pre_end1 = end, npre = 1;
-    {
-        int local;
-        const int pi = locate_problem(probs, cfg.P, beg, s_ib, cfg.ib_cap, local);
-        if (pi != hdr_pi0) {  // uniform over the CTA
-            fill_header(s_hdr, &probs[pi], tid);
-            hdr_pi0 = pi;
-            __syncthreads();
-        }
-        pre_chunk0 = local / h0->_row_items;
-        pre_end0 = min(end, beg - local + (pre_chunk0 + 1) * h0->_row_items);
-        if (nbuf > 1 && pre_end0 < end) {
-            int local1;
-            hdr_pi1 = locate_problem(probs, cfg.P, pre_end0, s_ib, cfg.ib_cap, local1);
-            fill_header(s_hdr + HDR_STRIDE, &probs[hdr_pi1], tid);
-            __syncthreads();
-            pre_chunk1 = local1 / h1->_row_items;
-            pre_end1 = min(end, pre_end0 - local1 + (pre_chunk1 + 1) * h1->_row_items);
-            npre = 2;
-        }
-    }
-    // head of problem pi: a cached copy if there is one, else the descriptor in global memory
-    auto head_of = [&](int pi) -> const wf_problem* { return pi == hdr_pi0 ? h0 : (pi == hdr_pi1 ? h1 : &probs[pi]); };
+    int hdr_pi0 = -1, hdr_pi1 = -1;  // the problems whose heads the two slots hold
 
     // cursor of the item whose first K segment is in flight in this warp's stage (>= end: none)
     ItemCursor nx;
     int nx_item = warp < S ? beg + warp : end;
     unsigned loads = 0;  // completed + pending requests of this warp (parity of the wait)
-    auto issue_first = [&]() {
-        if (warp < S && nx_item < end) {
+    // head of problem pi: a cached copy if there is one, else the descriptor in global memory
+    auto head_of = [&](int pi) -> const wf_problem* { return pi == hdr_pi0 ? h0 : (pi == hdr_pi1 ? h1 : &probs[pi]); };
+    auto issue_first = [&](bool from_param) {
+        if (nx_item < end) {
             int local;
-            nx.pi = locate_problem(probs, cfg.P, nx_item, s_ib, cfg.ib_cap, local);
-            const wf_problem* h = head_of(nx.pi);
+            nx.pi = locate_problem(probs, cfg.P, nx_item, s_ib, cfg.ib_cap, local, uni);
+            const wf_problem* h = from_param ? &single : head_of(nx.pi);
             nx.row_items = h->_row_items;
             nx.chunks = h->_chunks;
             nx.chunk = local / nx.row_items;
@@ -658,11 +636,41 @@ __global__ void __launch_bounds__(STREAM_THREADS, 2)
             }
         }
     };
+    if (uni > 0) issue_first(true);
+
+    // Two activation buffers: the first two passes of the CTA's range are quantized up front, so that a CTA
+    // whose range crosses from one problem into the next does not stop streaming there.  Later passes (rare:
+    // problems much smaller than a CTA's share) reuse the buffers behind a CTA-wide barrier.
+    const int act_bytes = cfg.KBmax * cfg.MTA * TOK_STRIDE;
+    const int nbuf = cfg.nbuf;
+    int pre_chunk0 = 0, pre_chunk1 = 0, pre_end0 = end, pre_end1 = end, npre = 1;
+    {
+        int local;
+        hdr_pi0 = locate_problem(probs, cfg.P, beg, s_ib, cfg.ib_cap, local, uni);
+        fill_header(s_hdr, &probs[hdr_pi0], tid);
+        // the geometry of the first pass: from the parameter copy where all problems are equal, so that the head
+        // of a possible second problem is fetched in the same round trip
+        if (uni == 0) __syncthreads();
+        const int row_items0 = uni > 0 ? single._row_items : h0->_row_items;
+        pre_chunk0 = local / row_items0;
+        pre_end0 = min(end, beg - local + (pre_chunk0 + 1) * row_items0);
+        int local1 = 0;
+        if (nbuf > 1 && pre_end0 < end) {
+            hdr_pi1 = locate_problem(probs, cfg.P, pre_end0, s_ib, cfg.ib_cap, local1, uni);
+            fill_header(s_hdr + HDR_STRIDE, &probs[hdr_pi1], tid - 64);
+            npre = 2;
+        }
+        __syncthreads();
+        if (npre > 1) {
+            pre_chunk1 = local1 / h1->_row_items;
+            pre_end1 = min(end, pre_end0 - local1 + (pre_chunk1 + 1) * h1->_row_items);
+        }
+    }
     // The weights never depend on the previous kernel, x normally does: request weights, wait, read x.  Where the
     // caller states that x is ready, x is read first (behind some 100 KB of weight requests per CTA its reads
     // would wait for microseconds) and only the stores wait for the previous kernel.
     if (!cfg.x_ready) {
-        issue_first();
+        if (uni == 0) issue_first(false);
         asm volatile("griddepcontrol.wait;\n" ::: "memory");
     }
     XCache xcache0, xcache1;
@@ -675,7 +683,7 @@ __global__ void __launch_bounds__(STREAM_THREADS, 2)
         quantize_phase<XDT, STREAM_THREADS, 0>(*h1, cfg.MTA, m0, min(cfg.MTA, h1->M - m0), s_act + act_bytes, s_inv + MT, s_rowsum + MT,
                                                s_maxbits + MT, xcache1);
     }
-    if (cfg.x_ready) issue_first();
+    if (cfg.x_ready && uni == 0) issue_first(false);
     {
         const int m0 = pre_chunk0 * cfg.MTA;
         quantize_phase<XDT, STREAM_THREADS, 1>(*h0, cfg.MTA, m0, min(cfg.MTA, h0->M - m0), s_act, s_inv, s_rowsum, s_maxbits, xcache0);
@@ -700,7 +708,7 @@ __global__ void __launch_bounds__(STREAM_THREADS, 2)
         } else {
             consumer_sync<STREAM_THREADS>();  // every warp is done with the pass that used this buffer and this head
             int local;
-            pi = locate_problem(probs, cfg.P, it, s_ib, cfg.ib_cap, local);
+            pi = locate_problem(probs, cfg.P, it, s_ib, cfg.ib_cap, local, uni);
             fill_header(slot, &probs[pi], tid);
             if (buf == 0) hdr_pi0 = pi; else hdr_pi1 = pi;
             consumer_sync<STREAM_THREADS>();
@@ -711,7 +719,7 @@ __global__ void __launch_bounds__(STREAM_THREADS, 2)
                                                  s_rowsum + buf * MT, s_maxbits + buf * MT);
         }
         const int m0 = chunk * cfg.MTA, m_valid = min(cfg.MTA, p.M - m0);
-        const int ritem = it - first_item(probs, pi, s_ib, cfg.ib_cap) - chunk * p._row_items;
+        const int ritem = it - first_item(probs, pi, s_ib, cfg.ib_cap, uni) - chunk * p._row_items;
         const wf_problem* const gp = &probs[pi];
         const uint32_t act0 = smem_u32(s_act + buf * act_bytes);
         const float* const inv_p = s_inv + buf * MT;
@@ -1079,6 +1087,13 @@ static int run_group(const char* who, const wf_problem* dev, wf_problem* host, i
     cfg.ib_cap = P < IB_CAP ? P : IB_CAP; cfg.ib_off = g.act_off - IB_CAP * 4 - 384; cfg.hdr_off = g.act_off - 384;
     cfg.x_ready = (flags & WF_FLAG_X_READY) ? 1 : 0;
     cfg.items_q = g.total_items / g.grid; cfg.items_r = g.total_items % g.grid;
+    cfg.uniform_items = 0;
+    if (g.decoupled) {
+        bool same = true;
+        for (int i = 1; i < P && same; ++i)
+            same = host[i].M == host[0].M && host[i].N == host[0].N && host[i].K == host[0].K && host[i].layout == host[0].layout;
+        if (same) cfg.uniform_items = host[0]._row_items * host[0]._chunks;
+    }
     cudaStream_t st = static_cast<cudaStream_t>(stream);
     switch (host[0].x_dtype) {
         case WF_F32: return dispatch_nt<WF_F32>(dev, host[0], cfg, g, flags, st);
