@@ -229,11 +229,14 @@ int wf_bitlinear_prefill_batched(const void* x, int x_dtype, int64_t ldx, const 
  * wf_rope_kv_bf16:     rotates q [B, nq*D] in place and k [B, nkv*D] at position slot = *pos % T (device scalar),
  *                      writes the rotated k and v into the caches [B, nkv, T, D]; cos/sin are fp32 [T, D/2].
  * wf_act_mul_bf16:     out = act(gate) * up over n elements; mode 0 = SiLU, 1 = ReLU^2.
+ * flags: WF_FLAG_PDL chains the kernel to its neighbours in the stream with a programmatic dependency (each of
+ * these kernels lets its successor start at once and waits for its predecessor before it touches a tensor).
  */
-int wf_add_rmsnorm_bf16(void* h, const void* delta, const void* weight, void* y, int64_t M, int64_t K, float eps, void* stream);
+int wf_add_rmsnorm_bf16(void* h, const void* delta, const void* weight, void* y, int64_t M, int64_t K, float eps, unsigned flags,
+                        void* stream);
 int wf_rope_kv_bf16(void* q, const void* k, const void* v, const float* cos, const float* sin, const int64_t* pos, void* kcache,
-                    void* vcache, int64_t B, int nq, int nkv, int D, int T, void* stream);
-int wf_act_mul_bf16(const void* gate, const void* up, void* out, int64_t n, int mode, void* stream);
+                    void* vcache, int64_t B, int nq, int nkv, int D, int T, unsigned flags, void* stream);
+int wf_act_mul_bf16(const void* gate, const void* up, void* out, int64_t n, int mode, unsigned flags, void* stream);
 
 #ifdef __cplusplus
 }

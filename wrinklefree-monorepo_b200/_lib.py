@@ -65,9 +65,9 @@ _SIGNATURES = {
     "wf_prefill_workspace_bytes": (_sz, [_i64, _i64]),
     "wf_bitlinear_prefill": (_int, [_p, _int, _i64, _p, _p, _int, _p, _f32, _p, _int, _p, _int, _i64, _p, _i64, _i64, _i64,
                                     _f32, _p, _sz, _u32, _p]),
-    "wf_add_rmsnorm_bf16": (_int, [_p, _p, _p, _p, _i64, _i64, _f32, _p]),
-    "wf_rope_kv_bf16": (_int, [_p, _p, _p, _p, _p, _p, _p, _p, _i64, _int, _int, _int, _int, _p]),
-    "wf_act_mul_bf16": (_int, [_p, _p, _p, _i64, _int, _p]),
+    "wf_add_rmsnorm_bf16": (_int, [_p, _p, _p, _p, _i64, _i64, _f32, _u32, _p]),
+    "wf_rope_kv_bf16": (_int, [_p, _p, _p, _p, _p, _p, _p, _p, _i64, _int, _int, _int, _int, _u32, _p]),
+    "wf_act_mul_bf16": (_int, [_p, _p, _p, _i64, _int, _u32, _p]),
     "wf_bitlinear_prefill_batched": (_int, [_p, _int, _i64, _p, _int, _p, _i64, _p, _int, _i64, _p, _i64, _i64, _i64, _i64, _f32,
                                             _p, _sz, _p]),
 }

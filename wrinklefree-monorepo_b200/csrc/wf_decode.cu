@@ -64,6 +64,9 @@ struct DecodeCfg {
     int hdr_off;      // two cached descriptor heads
     int items_q, items_r;  // total_items = grid * items_q + items_r
     int uniform_items;     // streaming form: > 0 when all problems have equal M, N, K and layout: items of each
+    int x_early;           // ... and problem i reads x at x_base + i * x_stride (bytes), without x_scale
+    const void* x_base;
+    long long x_stride;
     int x_ready;      // streaming form: x does not depend on the previous kernel; only the stores wait for it
     int ib_off, ib_cap;  // shared-memory copy of the problems' first item indices (searched instead of global memory)
     int decoupled;    // 1: every consumer warp owns whole 16-row items (RI == 1); 0: the 16 warps share each item
@@ -102,146 +105,202 @@ __device__ __forceinline__ int act_slot_of_k(int layout, int kl) {
 
 // ---- the quantization stage: x -> int8 in fragment order, per-token multiplier and sum ----
 // Executed by the 256 consumer threads together whenever the CTA moves to another (problem, token pass).
-// Two phases with a barrier at the start of the second: the first reads x from global memory (absolute maximum per
-// token; int8 input is complete after it), the second re-reads it (cache hits) and writes the int8 fragments.  A
-// caller may put other work between them, e.g. requests for weights, which would otherwise queue ahead of x.
-constexpr int XC = 2;  // chunks of x a thread keeps in registers between the phases
+// Three phases.  ISSUE starts the reads of x from global memory into registers and returns without using them, so a
+// caller can put its first requests for weights behind them (ahead of them, some 100 KB per CTA, the reads of x would
+// wait for microseconds).  ABSMAX opens with a barrier (which also publishes a descriptor head that was just copied to
+// shared memory) and reduces the absolute maximum per token; int8 input is complete after it.  EMIT opens with a
+// barrier, writes the int8 fragments and the sums, and closes with a barrier.
+// The first XCache::XC chunks (8 elements each) of a thread's share of the first token group stay in registers from
+// ISSUE to EMIT; what lies beyond is read in ABSMAX and again in EMIT.
+// `p` supplies the scalar fields (K, ldx, layout, eps); x and x_scale are passed separately.
+enum { Q_ISSUE = 0, Q_ABSMAX = 1, Q_EMIT = 2 };
+template <int XDT>
 struct XCache {
-    float f[XC][8];
+    static constexpr int V = (XDT == WF_F32) ? 2 : 1;   // 16-byte loads per chunk
+    static constexpr int XC = (XDT == WF_F32) ? 3 : 6;  // chunks kept
+    uint4 r[XC][V];
 };
+template <int XDT>
+__device__ __forceinline__ void load8_raw(const void* base, int64_t elem_off, uint4 (&r)[XCache<XDT>::V]) {
+    if constexpr (XDT == WF_F32) {
+        const uint4* q = reinterpret_cast<const uint4*>(static_cast<const float*>(base) + elem_off);
+        r[0] = __ldg(q);
+        r[1] = __ldg(q + 1);
+    } else {
+        r[0] = __ldg(reinterpret_cast<const uint4*>(static_cast<const uint16_t*>(base) + elem_off));
+    }
+}
+template <int XDT>
+__device__ __forceinline__ void decode8(const uint4 (&r)[XCache<XDT>::V], float (&f)[8]) {
+    if constexpr (XDT == WF_F32) {
+        f[0] = __uint_as_float(r[0].x); f[1] = __uint_as_float(r[0].y); f[2] = __uint_as_float(r[0].z); f[3] = __uint_as_float(r[0].w);
+        f[4] = __uint_as_float(r[1].x); f[5] = __uint_as_float(r[1].y); f[6] = __uint_as_float(r[1].z); f[7] = __uint_as_float(r[1].w);
+    } else {
+        const uint32_t w[4] = {r[0].x, r[0].y, r[0].z, r[0].w};
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+            if constexpr (XDT == WF_BF16) {
+                f[2 * i] = __uint_as_float(w[i] << 16);
+                f[2 * i + 1] = __uint_as_float(w[i] & 0xffff0000u);
+            } else {
+                const float2 v = __half22float2(*reinterpret_cast<const __half2*>(&w[i]));
+                f[2 * i] = v.x;
+                f[2 * i + 1] = v.y;
+            }
+        }
+    }
+}
+
 template <int XDT, int NTHREADS, int PHASE>
-__device__ __forceinline__ void quantize_phase(const wf_problem& p, int MTA, int m0, int m_valid, uint8_t* s_act, float* s_inv,
-                                               int* s_rowsum, unsigned* s_maxbits, XCache& cache) {
+__device__ __forceinline__ void quantize_phase(const wf_problem& p, const void* x, const float* x_scale, int MTA, int m0, int m_valid,
+                                               uint8_t* s_act, float* s_inv, int* s_rowsum, unsigned* s_maxbits, XCache<XDT>& cache) {
+    constexpr int XC = XCache<XDT>::XC;
     const int tid = threadIdx.x;
-    if constexpr (PHASE == 0) {
+    if constexpr (PHASE == Q_ISSUE) {
         for (int i = tid; i < m_valid; i += NTHREADS) {
             s_rowsum[i] = 0;
             s_maxbits[i] = 0;
         }
+    } else {
+        consumer_sync<NTHREADS>();
     }
-    consumer_sync<NTHREADS>();  // also publishes a descriptor head that was just copied to shared memory
-    const int KB = (p.K + 511) >> 9, Kp = KB * 512;
-    // threads per token: all 256 for one token down to one warp per token for 8 or more
+    const int K = p.K, Kp = ((K + 511) >> 9) * 512;
+    // threads per token: all of them for one token down to one warp per token for 8 or more
     int tpt = NTHREADS;
     while (tpt > 32 && NTHREADS / tpt < m_valid) tpt >>= 1;
     const int par = NTHREADS / tpt;  // tokens handled concurrently
-    const int sub = tid / tpt, lane_in = tid % tpt;
+    const int sub = tid / tpt, lane_in = tid & (tpt - 1);
 
     if constexpr (XDT == WF_I8) {
-        if constexpr (PHASE == 0)
-        for (int tb = 0; tb < m_valid; tb += par) {
-            int tok = tb + sub;
-            int sum = 0;
-            if (tok < m_valid) {
-                const int8_t* row = static_cast<const int8_t*>(p.x) + static_cast<int64_t>(m0 + tok) * p.ldx;
-                for (int k = lane_in * 16; k < Kp; k += tpt * 16) {
-                    uint4 v = make_uint4(0, 0, 0, 0);
-                    if (k < p.K) v = __ldg(reinterpret_cast<const uint4*>(row + k));
-                    const uint32_t w[4] = {v.x, v.y, v.z, v.w};
+        if constexpr (PHASE == Q_ABSMAX) {
+            for (int tb = 0; tb < m_valid; tb += par) {
+                int tok = tb + sub;
+                int sum = 0;
+                if (tok < m_valid) {
+                    const int8_t* row = static_cast<const int8_t*>(x) + static_cast<int64_t>(m0 + tok) * p.ldx;
+                    for (int k = lane_in * 16; k < Kp; k += tpt * 16) {
+                        uint4 v = make_uint4(0, 0, 0, 0);
+                        if (k < K) v = __ldg(reinterpret_cast<const uint4*>(row + k));
+                        const uint32_t w[4] = {v.x, v.y, v.z, v.w};
 #pragma unroll
-                    for (int j = 0; j < 4; ++j) {
-                        sum += __dp4a(static_cast<int>(w[j]), 0x01010101, 0);
-                        int kb = (k + 4 * j) >> 9, kl = (k + 4 * j) & 511;
-                        *reinterpret_cast<uint32_t*>(s_act + (kb * MTA + tok) * TOK_STRIDE + act_slot_of_k(p.layout, kl)) = w[j];
+                        for (int j = 0; j < 4; ++j) {
+                            sum += __dp4a(static_cast<int>(w[j]), 0x01010101, 0);
+                            int kb = (k + 4 * j) >> 9, kl = (k + 4 * j) & 511;
+                            *reinterpret_cast<uint32_t*>(s_act + (kb * MTA + tok) * TOK_STRIDE + act_slot_of_k(p.layout, kl)) = w[j];
+                        }
                     }
                 }
-            }
 #pragma unroll
-            for (int o = 16; o > 0; o >>= 1) sum += __shfl_xor_sync(0xffffffffu, sum, o);
-            if (tok < m_valid && (tid & 31) == 0) atomicAdd(&s_rowsum[tok], sum);
+                for (int o = 16; o > 0; o >>= 1) sum += __shfl_xor_sync(0xffffffffu, sum, o);
+                if (tok < m_valid && (tid & 31) == 0) atomicAdd(&s_rowsum[tok], sum);
+            }
+            if (tid < m_valid) s_inv[tid] = x_scale ? __frcp_rn(x_scale[m0 + tid]) : 1.0f;
         }
-        if (PHASE == 0 && tid < m_valid) s_inv[tid] = p.x_scale ? __frcp_rn(p.x_scale[m0 + tid]) : 1.0f;
     } else {
-        // The first XC chunks (8 elements each) of a thread's share of the first token group stay in registers
-        // between the phases; what lies beyond is read again (cache hits).
-        // pass 1: absmax per token
-        if constexpr (PHASE == 0)
-        for (int tb = 0; tb < m_valid; tb += par) {
-            int tok = tb + sub;
-            float mx = 0.f;
+        if constexpr (PHASE == Q_ISSUE) {
+            const int tok = sub;
             if (tok < m_valid) {
                 const int64_t base = static_cast<int64_t>(m0 + tok) * p.ldx;
                 int k = lane_in * 8;
-                if (tb == 0) {
 #pragma unroll
-                    for (int c = 0; c < XC; ++c, k += tpt * 8) {
-                        if (k < p.K) load8<XDT>(p.x, base + k, cache.f[c]);
-                    }
-                    k = lane_in * 8;
-#pragma unroll
-                    for (int c = 0; c < XC; ++c, k += tpt * 8) {
-                        if (k < p.K) {
-#pragma unroll
-                            for (int i = 0; i < 8; ++i) mx = fmaxf(mx, fabsf(cache.f[c][i]));
-                        }
-                    }
-                }
-                // several loads in flight per thread: these are dependent L2 round trips otherwise
-#pragma unroll 4
-                for (; k < p.K; k += tpt * 8) {
-                    float f[8];
-                    load8<XDT>(p.x, base + k, f);
-#pragma unroll
-                    for (int i = 0; i < 8; ++i) mx = fmaxf(mx, fabsf(f[i]));
-                }
+                for (int c = 0; c < XC; ++c, k += tpt * 8)
+                    if (k < K) load8_raw<XDT>(x, base + k, cache.r[c]);
             }
-#pragma unroll
-            for (int o = 16; o > 0; o >>= 1) mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, o));
-            if (tok < m_valid && (tid & 31) == 0) atomicMax(&s_maxbits[tok], __float_as_uint(mx));
         }
-        // pass 2: quantize, scatter, sum
-        if constexpr (PHASE == 1)
-        for (int tb = 0; tb < m_valid; tb += par) {
-            int tok = tb + sub;
-            int sum = 0;
-            if (tok < m_valid) {
-                const float s = act_scale_from_absmax<XDT>(__uint_as_float(s_maxbits[tok]), p.eps);
-                if (lane_in == 0) s_inv[tok] = __fdiv_rn(1.0f, s);
-                const int64_t base = static_cast<int64_t>(m0 + tok) * p.ldx;
-                auto emit = [&](int k, const float (&f)[8], bool live) {
-                    uint32_t w0 = 0, w1 = 0;
-                    if (live) {
+        if constexpr (PHASE == Q_ABSMAX) {
+            for (int tb = 0; tb < m_valid; tb += par) {
+                int tok = tb + sub;
+                float mx = 0.f;
+                if (tok < m_valid) {
+                    const int64_t base = static_cast<int64_t>(m0 + tok) * p.ldx;
+                    int k = lane_in * 8;
+                    if (tb == 0) {
 #pragma unroll
-                        for (int i = 0; i < 4; ++i) {
-                            int a = quantize_one<XDT>(f[i], s), b = quantize_one<XDT>(f[4 + i], s);
-                            sum += a + b;
-                            w0 |= static_cast<uint32_t>(a & 0xff) << (8 * i);
-                            w1 |= static_cast<uint32_t>(b & 0xff) << (8 * i);
+                        for (int c = 0; c < XC; ++c, k += tpt * 8) {
+                            if (k < K) {
+                                float f[8];
+                                decode8<XDT>(cache.r[c], f);
+#pragma unroll
+                                for (int i = 0; i < 8; ++i) mx = fmaxf(mx, fabsf(f[i]));
+                            }
                         }
                     }
-                    int kb = k >> 9, kl = k & 511;
-                    uint8_t* dst = s_act + (kb * MTA + tok) * TOK_STRIDE;
-                    *reinterpret_cast<uint32_t*>(dst + act_slot_of_k(p.layout, kl)) = w0;
-                    *reinterpret_cast<uint32_t*>(dst + act_slot_of_k(p.layout, kl + 4)) = w1;
-                };
-                int k = lane_in * 8;
-                if (tb == 0) {
+                    // several loads in flight per thread: these are dependent round trips otherwise
+#pragma unroll 4
+                    for (; k < K; k += tpt * 8) {
+                        float f[8];
+                        load8<XDT>(x, base + k, f);
 #pragma unroll
-                    for (int c = 0; c < XC; ++c, k += tpt * 8) {
-                        if (k < Kp) emit(k, cache.f[c], k < p.K);
+                        for (int i = 0; i < 8; ++i) mx = fmaxf(mx, fabsf(f[i]));
                     }
                 }
-#pragma unroll 4
-                for (; k < Kp; k += tpt * 8) {
-                    float f[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
-                    if (k < p.K) load8<XDT>(p.x, base + k, f);
-                    emit(k, f, k < p.K);
-                }
-            }
 #pragma unroll
-            for (int o = 16; o > 0; o >>= 1) sum += __shfl_xor_sync(0xffffffffu, sum, o);
-            if (tok < m_valid && (tid & 31) == 0) atomicAdd(&s_rowsum[tok], sum);
+                for (int o = 16; o > 0; o >>= 1) mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, o));
+                if (tok < m_valid && (tid & 31) == 0) atomicMax(&s_maxbits[tok], __float_as_uint(mx));
+            }
+        }
+        if constexpr (PHASE == Q_EMIT) {
+            for (int tb = 0; tb < m_valid; tb += par) {
+                int tok = tb + sub;
+                int sum = 0;
+                if (tok < m_valid) {
+                    const float s = act_scale_from_absmax<XDT>(__uint_as_float(s_maxbits[tok]), p.eps);
+                    if (lane_in == 0) s_inv[tok] = __fdiv_rn(1.0f, s);
+                    const int64_t base = static_cast<int64_t>(m0 + tok) * p.ldx;
+                    const int layout = p.layout;
+                    auto emit = [&](int k, const float (&f)[8], bool live) {
+                        uint32_t w0 = 0, w1 = 0;
+                        if (live) {
+#pragma unroll
+                            for (int i = 0; i < 4; ++i) {
+                                int a = quantize_one<XDT>(f[i], s), b = quantize_one<XDT>(f[4 + i], s);
+                                sum += a + b;
+                                w0 |= static_cast<uint32_t>(a & 0xff) << (8 * i);
+                                w1 |= static_cast<uint32_t>(b & 0xff) << (8 * i);
+                            }
+                        }
+                        int kb = k >> 9, kl = k & 511;
+                        uint8_t* dst = s_act + (kb * MTA + tok) * TOK_STRIDE;
+                        *reinterpret_cast<uint32_t*>(dst + act_slot_of_k(layout, kl)) = w0;
+                        *reinterpret_cast<uint32_t*>(dst + act_slot_of_k(layout, kl + 4)) = w1;
+                    };
+                    int k = lane_in * 8;
+                    if (tb == 0) {
+#pragma unroll
+                        for (int c = 0; c < XC; ++c, k += tpt * 8) {
+                            if (k < Kp) {
+                                float f[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
+                                if (k < K) decode8<XDT>(cache.r[c], f);
+                                emit(k, f, k < K);
+                            }
+                        }
+                    }
+#pragma unroll 4
+                    for (; k < Kp; k += tpt * 8) {
+                        float f[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
+                        if (k < K) load8<XDT>(x, base + k, f);
+                        emit(k, f, k < K);
+                    }
+                }
+#pragma unroll
+                for (int o = 16; o > 0; o >>= 1) sum += __shfl_xor_sync(0xffffffffu, sum, o);
+                if (tok < m_valid && (tid & 31) == 0) atomicAdd(&s_rowsum[tok], sum);
+            }
         }
     }
-    if constexpr (PHASE == 1) consumer_sync<NTHREADS>();
+    if constexpr (PHASE == Q_EMIT) consumer_sync<NTHREADS>();
 }
 
+// All three phases in a row.  The caller has made the fields of `p` visible (a barrier after copying a head).
 template <int XDT, int NTHREADS = DEC_CONSUMERS>
 __device__ __forceinline__ void quantize_tokens(const wf_problem& p, int MTA, int m0, int m_valid, uint8_t* s_act, float* s_inv,
                                                 int* s_rowsum, unsigned* s_maxbits) {
-    XCache cache;
-    quantize_phase<XDT, NTHREADS, 0>(p, MTA, m0, m_valid, s_act, s_inv, s_rowsum, s_maxbits, cache);
-    quantize_phase<XDT, NTHREADS, 1>(p, MTA, m0, m_valid, s_act, s_inv, s_rowsum, s_maxbits, cache);
+    XCache<XDT> cache;
+    const void* x = p.x;
+    const float* xs = p.x_scale;
+    quantize_phase<XDT, NTHREADS, Q_ISSUE>(p, x, xs, MTA, m0, m_valid, s_act, s_inv, s_rowsum, s_maxbits, cache);
+    quantize_phase<XDT, NTHREADS, Q_ABSMAX>(p, x, xs, MTA, m0, m_valid, s_act, s_inv, s_rowsum, s_maxbits, cache);
+    quantize_phase<XDT, NTHREADS, Q_EMIT>(p, x, xs, MTA, m0, m_valid, s_act, s_inv, s_rowsum, s_maxbits, cache);
 }
 
 __device__ __forceinline__ uint4 lds128(uint32_t addr) {
@@ -636,63 +695,84 @@ __global__ void __launch_bounds__(STREAM_THREADS, 2)
             }
         }
     };
-    if (uni > 0) issue_first(true);
-
     // Two activation buffers: the first two passes of the CTA's range are quantized up front, so that a CTA
     // whose range crosses from one problem into the next does not stop streaming there.  Later passes (rare:
     // problems much smaller than a CTA's share) reuse the buffers behind a CTA-wide barrier.
     const int act_bytes = cfg.KBmax * cfg.MTA * TOK_STRIDE;
     const int nbuf = cfg.nbuf;
+    const bool early = cfg.x_early != 0;  // equal problems whose x lie at a constant stride: x is found without a head
     int pre_chunk0 = 0, pre_chunk1 = 0, pre_end0 = end, pre_end1 = end, npre = 1;
-    {
-        int local;
-        hdr_pi0 = locate_problem(probs, cfg.P, beg, s_ib, cfg.ib_cap, local, uni);
+    int local0, local1 = 0;
+    hdr_pi0 = locate_problem(probs, cfg.P, beg, s_ib, cfg.ib_cap, local0, uni);
+    uint32_t hw0 = 0, hw1 = 0;  // head words on their way from global memory (equal problems)
+    if (uni > 0) {
+        const int ri = single._row_items;  // the geometry of the passes follows from the parameter copy
+        pre_chunk0 = local0 / ri;
+        pre_end0 = min(end, beg - local0 + (pre_chunk0 + 1) * ri);
+        if (nbuf > 1 && pre_end0 < end) {
+            hdr_pi1 = locate_problem(probs, cfg.P, pre_end0, s_ib, cfg.ib_cap, local1, uni);
+            pre_chunk1 = local1 / ri;
+            pre_end1 = min(end, pre_end0 - local1 + (pre_chunk1 + 1) * ri);
+            npre = 2;
+        }
+        if (!(cfg.x_ready && early)) issue_first(true);
+        if (tid < HDR_WORDS) hw0 = reinterpret_cast<const uint32_t*>(&probs[hdr_pi0])[tid];
+        if (npre > 1 && tid >= 64 && tid < 64 + HDR_WORDS) hw1 = reinterpret_cast<const uint32_t*>(&probs[hdr_pi1])[tid - 64];
+    } else {
         fill_header(s_hdr, &probs[hdr_pi0], tid);
-        // the geometry of the first pass: from the parameter copy where all problems are equal, so that the head
-        // of a possible second problem is fetched in the same round trip
-        if (uni == 0) __syncthreads();
-        const int row_items0 = uni > 0 ? single._row_items : h0->_row_items;
-        pre_chunk0 = local / row_items0;
-        pre_end0 = min(end, beg - local + (pre_chunk0 + 1) * row_items0);
-        int local1 = 0;
+        __syncthreads();
+        pre_chunk0 = local0 / h0->_row_items;
+        pre_end0 = min(end, beg - local0 + (pre_chunk0 + 1) * h0->_row_items);
         if (nbuf > 1 && pre_end0 < end) {
             hdr_pi1 = locate_problem(probs, cfg.P, pre_end0, s_ib, cfg.ib_cap, local1, uni);
             fill_header(s_hdr + HDR_STRIDE, &probs[hdr_pi1], tid - 64);
-            npre = 2;
-        }
-        __syncthreads();
-        if (npre > 1) {
+            __syncthreads();
             pre_chunk1 = local1 / h1->_row_items;
             pre_end1 = min(end, pre_end0 - local1 + (pre_chunk1 + 1) * h1->_row_items);
+            npre = 2;
         }
+        if (!cfg.x_ready) issue_first(false);
     }
+    auto store_heads = [&]() {
+        if (tid < HDR_WORDS) reinterpret_cast<uint32_t*>(s_hdr)[tid] = hw0;
+        if (npre > 1 && tid >= 64 && tid < 64 + HDR_WORDS) reinterpret_cast<uint32_t*>(s_hdr + HDR_STRIDE)[tid - 64] = hw1;
+    };
     // The weights never depend on the previous kernel, x normally does: request weights, wait, read x.  Where the
-    // caller states that x is ready, x is read first (behind some 100 KB of weight requests per CTA its reads
-    // would wait for microseconds) and only the stores wait for the previous kernel.
-    if (!cfg.x_ready) {
-        if (uni == 0) issue_first(false);
-        asm volatile("griddepcontrol.wait;\n" ::: "memory");
+    // caller states that x is ready, the reads of x are started first and only the stores wait for the previous kernel.
+    if (!cfg.x_ready) asm volatile("griddepcontrol.wait;\n" ::: "memory");
+    if (uni > 0 && !early) {  // x is found through the heads
+        store_heads();
+        __syncthreads();
     }
-    XCache xcache0, xcache1;
-    {
-        const int m0 = pre_chunk0 * cfg.MTA;
-        quantize_phase<XDT, STREAM_THREADS, 0>(*h0, cfg.MTA, m0, min(cfg.MTA, h0->M - m0), s_act, s_inv, s_rowsum, s_maxbits, xcache0);
-    }
+    const wf_problem& q0 = early ? single : *h0;  // scalar fields for the first two phases
+    const wf_problem& q1 = early ? single : *h1;
+    const void* x0 = early ? static_cast<const void*>(static_cast<const char*>(cfg.x_base) + hdr_pi0 * cfg.x_stride) : h0->x;
+    const float* xs0 = early ? nullptr : h0->x_scale;
+    const void* x1 = nullptr;
+    const float* xs1 = nullptr;
     if (npre > 1) {
-        const int m0 = pre_chunk1 * cfg.MTA;
-        quantize_phase<XDT, STREAM_THREADS, 0>(*h1, cfg.MTA, m0, min(cfg.MTA, h1->M - m0), s_act + act_bytes, s_inv + MT, s_rowsum + MT,
-                                               s_maxbits + MT, xcache1);
+        x1 = early ? static_cast<const void*>(static_cast<const char*>(cfg.x_base) + hdr_pi1 * cfg.x_stride) : h1->x;
+        xs1 = early ? nullptr : h1->x_scale;
     }
-    if (cfg.x_ready && uni == 0) issue_first(false);
-    {
-        const int m0 = pre_chunk0 * cfg.MTA;
-        quantize_phase<XDT, STREAM_THREADS, 1>(*h0, cfg.MTA, m0, min(cfg.MTA, h0->M - m0), s_act, s_inv, s_rowsum, s_maxbits, xcache0);
-    }
-    if (npre > 1) {
-        const int m0 = pre_chunk1 * cfg.MTA;
-        quantize_phase<XDT, STREAM_THREADS, 1>(*h1, cfg.MTA, m0, min(cfg.MTA, h1->M - m0), s_act + act_bytes, s_inv + MT, s_rowsum + MT,
-                                               s_maxbits + MT, xcache1);
-    }
+    const int m00 = pre_chunk0 * cfg.MTA, mv0 = min(cfg.MTA, single.M - m00);  // M of the first problem: see below
+    const int m01 = pre_chunk1 * cfg.MTA;
+    XCache<XDT> xcache0, xcache1;
+    const int mvalid0 = uni > 0 ? mv0 : min(cfg.MTA, h0->M - m00);
+    const int mvalid1 = npre > 1 ? min(cfg.MTA, (uni > 0 ? single.M : h1->M) - m01) : 0;
+    quantize_phase<XDT, STREAM_THREADS, Q_ISSUE>(q0, x0, xs0, cfg.MTA, m00, mvalid0, s_act, s_inv, s_rowsum, s_maxbits, xcache0);
+    if (npre > 1)
+        quantize_phase<XDT, STREAM_THREADS, Q_ISSUE>(q1, x1, xs1, cfg.MTA, m01, mvalid1, s_act + act_bytes, s_inv + MT, s_rowsum + MT,
+                                                     s_maxbits + MT, xcache1);
+    if (cfg.x_ready && (early || uni == 0)) issue_first(early);  // behind the reads of x
+    if (early) store_heads();  // published by the barrier that opens the next phase
+    quantize_phase<XDT, STREAM_THREADS, Q_ABSMAX>(q0, x0, xs0, cfg.MTA, m00, mvalid0, s_act, s_inv, s_rowsum, s_maxbits, xcache0);
+    if (npre > 1)
+        quantize_phase<XDT, STREAM_THREADS, Q_ABSMAX>(q1, x1, xs1, cfg.MTA, m01, mvalid1, s_act + act_bytes, s_inv + MT, s_rowsum + MT,
+                                                      s_maxbits + MT, xcache1);
+    quantize_phase<XDT, STREAM_THREADS, Q_EMIT>(q0, x0, xs0, cfg.MTA, m00, mvalid0, s_act, s_inv, s_rowsum, s_maxbits, xcache0);
+    if (npre > 1)
+        quantize_phase<XDT, STREAM_THREADS, Q_EMIT>(q1, x1, xs1, cfg.MTA, m01, mvalid1, s_act + act_bytes, s_inv + MT, s_rowsum + MT,
+                                                    s_maxbits + MT, xcache1);
     bool may_store = !cfg.x_ready;  // the previous kernel has been waited for
 
     int it = beg;
@@ -725,7 +805,7 @@ __global__ void __launch_bounds__(STREAM_THREADS, 2)
         const float* const inv_p = s_inv + buf * MT;
         const int* const rowsum_p = s_rowsum + buf * MT;
         const int KB = (p.K + 511) >> 9, kb_seg = p._kb_seg, ksegs = p._ksegs;
-        const float s_w = header_w_scale(slot);
+        const float s_w = p.w_scale ? __ldg(p.w_scale) : p.w_scale_host;
         void* const y = p.y;
         const void* const bias = p.bias;
         int32_t* const acc_out = p.acc_out;
@@ -973,7 +1053,13 @@ static int plan_group(wf_problem* probs, int P, GroupPlan& g, bool write_fields)
     }
     const size_t seg_stage = static_cast<size_t>(seg_max) * TILE_BYTES;
     g.decoupled = count_items16(probs, P, g.MTA) >= 32LL * sms && fixed_bytes(NT, 1) + act + 4u * seg_stage <= SMEM_STREAM_MAX;
-    g.nbuf = (g.decoupled && fixed_bytes(NT, 1) + 2 * act + 6u * seg_stage <= SMEM_STREAM_MAX) ? 2 : 1;
+    // CTA ranges aligned to the problems (see g.cpp below) with all tokens in one pass: a CTA never meets a second pass
+    bool one_pass = false;
+    if (g.decoupled && P <= 2 * sms && Mmax <= g.MTA) {
+        const int c = 2 * sms / P;
+        one_pass = c * P * 10 >= 2 * sms * 9;
+    }
+    g.nbuf = (g.decoupled && !one_pass && fixed_bytes(NT, 1) + 2 * act + 6u * seg_stage <= SMEM_STREAM_MAX) ? 2 : 1;
     // item size: about 32 KB per stage, smaller while there are too few items to keep every SM busy
     int RI = g.decoupled ? 1 : 8;
     while (RI > 1 && 16 * RI * pitch > 32 * 1024) RI >>= 1;
@@ -1093,6 +1179,16 @@ static int run_group(const char* who, const wf_problem* dev, wf_problem* host, i
         for (int i = 1; i < P && same; ++i)
             same = host[i].M == host[0].M && host[i].N == host[0].N && host[i].K == host[0].K && host[i].layout == host[0].layout;
         if (same) cfg.uniform_items = host[0]._row_items * host[0]._chunks;
+    }
+    cfg.x_early = 0; cfg.x_base = host[0].x; cfg.x_stride = 0;
+    if (cfg.uniform_items > 0) {
+        const char* b0 = static_cast<const char*>(host[0].x);
+        const long long dx = P > 1 ? static_cast<const char*>(host[1].x) - b0 : 0;
+        bool ok = host[0].x_scale == nullptr && host[0].ldx == host[P > 1 ? 1 : 0].ldx;
+        for (int i = 1; i < P && ok; ++i)
+            ok = host[i].x_scale == nullptr && host[i].ldx == host[0].ldx && host[i].eps == host[0].eps &&
+                 static_cast<const char*>(host[i].x) - b0 == dx * i;
+        if (ok) { cfg.x_early = 1; cfg.x_stride = dx; }
     }
     cudaStream_t st = static_cast<cudaStream_t>(stream);
     switch (host[0].x_dtype) {

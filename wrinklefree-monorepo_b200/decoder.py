@@ -139,22 +139,24 @@ class TernaryDecoder:
     def _decode_step(self):
         """One token per sequence: reads self.tok / self.pos, writes self.next_tok; advances self.pos.
         Per layer: add+RMSNorm, q/k/v group, RoPE+cache write, attention, o, add+RMSNorm, gate/up group,
-        activation*up, down -- ten launches."""
+        activation*up, down -- ten launches, chained with programmatic dependencies: every kernel of this library
+        starts while its predecessor drains (the projections stream their first weights meanwhile) and waits for it
+        before it reads an activation."""
         cfg, B, d = self.cfg, self.B, self.cfg.head_dim
         self.h.copy_(self.embed[self.tok])  # residual stream [B, hidden]
         valid = (torch.arange(self.T, device=self.dev) <= self.pos).view(1, 1, 1, self.T) if self.masked else None
         delta = None
         for L in self.layers:
-            ops.add_rmsnorm_(self.h, delta, L["n1"], L["xn"], cfg.eps)
-            q, k, v = L["g_qkv"].run()
-            ops.rope_kv_(q, k, v, self.cos, self.sin, self.pos, L["kc"], L["vc"])
+            ops.add_rmsnorm_(self.h, delta, L["n1"], L["xn"], cfg.eps, pdl=True)
+            q, k, v = L["g_qkv"].run(pdl=True)
+            ops.rope_kv_(q, k, v, self.cos, self.sin, self.pos, L["kc"], L["vc"], pdl=True)
             a = F.scaled_dot_product_attention(q.view(B, self.nq, 1, d), L["kc"], L["vc"], attn_mask=valid, enable_gqa=True)
-            o = self._allreduce(ops.bitlinear(a.reshape(B, self.nq * d), L["o"][0], L["o"][1], out=L["ob"], path="decode"))
-            ops.add_rmsnorm_(self.h, o, L["n2"], L["hn"], cfg.eps)
-            g, u = L["g_gu"].run()
-            ops.act_mul(g, u, L["act"], self.cfg.act)
-            delta = self._allreduce(ops.bitlinear(L["act"], L["down"][0], L["down"][1], out=L["db"], path="decode"))
-        ops.add_rmsnorm_(self.h, delta, self.norm_f, self.xf, cfg.eps)
+            o = self._allreduce(ops.bitlinear(a.reshape(B, self.nq * d), L["o"][0], L["o"][1], out=L["ob"], path="decode", pdl=True))
+            ops.add_rmsnorm_(self.h, o, L["n2"], L["hn"], cfg.eps, pdl=True)
+            g, u = L["g_gu"].run(pdl=True)
+            ops.act_mul(g, u, L["act"], self.cfg.act, pdl=True)
+            delta = self._allreduce(ops.bitlinear(L["act"], L["down"][0], L["down"][1], out=L["db"], path="decode", pdl=True))
+        ops.add_rmsnorm_(self.h, delta, self.norm_f, self.xf, cfg.eps, pdl=True)
         logits = self.xf @ self.lm_head.t()
         self.logits = logits
         self.next_tok.copy_(logits.argmax(-1))

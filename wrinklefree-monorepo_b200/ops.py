@@ -302,33 +302,36 @@ class DecodeGroup:
         return self.outputs
 
 
-def add_rmsnorm_(h: torch.Tensor, delta: Optional[torch.Tensor], weight: torch.Tensor, out: torch.Tensor, eps: float):
-    """h += delta (if given), out = rmsnorm(h) * weight; bf16, contiguous [M, K]."""
+def add_rmsnorm_(h: torch.Tensor, delta: Optional[torch.Tensor], weight: torch.Tensor, out: torch.Tensor, eps: float,
+                 pdl: bool = False):
+    """h += delta (if given), out = rmsnorm(h) * weight; bf16, contiguous [M, K].  `pdl`: chain the launch to its
+    neighbours in the stream with a programmatic dependency (same meaning for the other kernels of this group)."""
     _need_cuda(h, delta, weight, out)
     m, k = h.shape
     with torch.cuda.device(h.device):
-        L.check(L.lib().wf_add_rmsnorm_bf16(h.data_ptr(), _ptr(delta), weight.data_ptr(), out.data_ptr(), m, k, eps, _stream()),
-                "wf_add_rmsnorm_bf16")
+        L.check(L.lib().wf_add_rmsnorm_bf16(h.data_ptr(), _ptr(delta), weight.data_ptr(), out.data_ptr(), m, k, eps,
+                                            L.FLAG_PDL if pdl else 0, _stream()), "wf_add_rmsnorm_bf16")
     return out
 
 
 def rope_kv_(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, cos: torch.Tensor, sin: torch.Tensor, pos: torch.Tensor,
-             kcache: torch.Tensor, vcache: torch.Tensor):
+             kcache: torch.Tensor, vcache: torch.Tensor, pdl: bool = False):
     """Decode-step RoPE of q (in place) and k, and the write of k, v into caches [B, nkv, T, D] at *pos % T."""
     _need_cuda(q, k, v, cos, sin, pos, kcache, vcache)
     b, nkv, t, d = kcache.shape
     nq = q.numel() // (b * d)
     with torch.cuda.device(q.device):
         L.check(L.lib().wf_rope_kv_bf16(q.data_ptr(), k.data_ptr(), v.data_ptr(), cos.data_ptr(), sin.data_ptr(), pos.data_ptr(),
-                                        kcache.data_ptr(), vcache.data_ptr(), b, nq, nkv, d, t, _stream()), "wf_rope_kv_bf16")
+                                        kcache.data_ptr(), vcache.data_ptr(), b, nq, nkv, d, t, L.FLAG_PDL if pdl else 0, _stream()),
+                "wf_rope_kv_bf16")
 
 
-def act_mul(gate: torch.Tensor, up: torch.Tensor, out: torch.Tensor, mode: str = "silu"):
+def act_mul(gate: torch.Tensor, up: torch.Tensor, out: torch.Tensor, mode: str = "silu", pdl: bool = False):
     """out = act(gate) * up (bf16); mode "silu" or "relu2"."""
     _need_cuda(gate, up, out)
     with torch.cuda.device(gate.device):
         L.check(L.lib().wf_act_mul_bf16(gate.data_ptr(), up.data_ptr(), out.data_ptr(), gate.numel(), 0 if mode == "silu" else 1,
-                                        _stream()), "wf_act_mul_bf16")
+                                        L.FLAG_PDL if pdl else 0, _stream()), "wf_act_mul_bf16")
     return out
 
 
