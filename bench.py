@@ -12,7 +12,8 @@ launch streams its weights from HBM.  The per-pair breakdown also times the same
 launch per layer, chained with programmatic dependent launch (the latency-bound form).
 `value` is algorithmic GB/s (packed codes + scale + bf16 x + bf16 y per launch) over the whole
 step with inputs resident in HBM; `e2e` is the same with the step's activations copied in from
-pinned host memory and its outputs copied back inside the timed region.
+pinned host memory and its outputs copied back inside the timed region (per stack, on three streams: copy-in,
+launches and copy-out of consecutive stacks overlap).
 """
 from __future__ import annotations
 
@@ -143,17 +144,22 @@ def build_workload(wf, torch, device, rank: int, world: int, layers_scale: float
     return groups
 
 
+def run_group(wf, g, pdl: bool):
+    """One (shape, M) layer stack: one grouped launch (or the quantization + contraction pair for M >= GEMM_MIN_M)."""
+    if g["batched"]:
+        wf.bitlinear_batched(g["x"], g["codes_stack"], g["scales_stack"], out=g["y"])
+    else:
+        g["group"].run(pdl=pdl, x_ready=True)  # the stacks are independent: no launch writes the next one's x
+    if g["reduce"]:  # row-parallel stack: sum the partial outputs of all ranks (the path's only exchange)
+        import torch.distributed as dist
+
+        dist.all_reduce(g["y"])
+
+
 def run_step(wf, groups, pdl: bool):
     """One pass over the sweep: every (shape, M) layer stack is one grouped launch."""
     for g in groups:
-        if g["batched"]:
-            wf.bitlinear_batched(g["x"], g["codes_stack"], g["scales_stack"], out=g["y"])
-        else:
-            g["group"].run(pdl=pdl, x_ready=True)  # the stacks are independent: no launch writes the next one's x
-        if g["reduce"]:  # row-parallel stack: sum the partial outputs of all ranks (the path's only exchange)
-            import torch.distributed as dist
-
-            dist.all_reduce(g["y"])
+        run_group(wf, g, pdl)
     return sum(2 if g["batched"] else 1 for g in groups)  # batched = quantization kernel + contraction
 
 
@@ -456,20 +462,53 @@ def main():
     d2h = sum(g["y"].numel() * 2 for g in groups)
     y_host = [torch.empty(g["y"].shape, dtype=torch.bfloat16).pin_memory() for g in groups]
 
-    def e2e_step():
-        for g in groups:
-            g["x"].copy_(g["x_host"], non_blocking=True)
-        graph.replay()
-        for g, yh in zip(groups, y_host):
-            yh.copy_(g["y"], non_blocking=True)
+    # Three streams: the copy-in of stack g, the launches of stack g - 1 and the copy-out of stack g - 2 overlap
+    # (the two copy directions run at the same time on the link); events order them per stack, also from one
+    # step to the next (x is not overwritten before the launch that read it has finished, y not before it is out).
+    s_in, s_run, s_out = torch.cuda.Stream(), torch.cuda.Stream(), torch.cuda.Stream()
+    ev_in = [torch.cuda.Event() for _ in groups]
+    ev_run = [torch.cuda.Event() for _ in groups]
+    ev_out = [torch.cuda.Event() for _ in groups]
+    state = {"first": True}
 
+    def e2e_fork():
+        for s_ in (s_in, s_run, s_out):
+            s_.wait_stream(torch.cuda.current_stream())
+
+    def e2e_join():
+        for s_ in (s_in, s_run, s_out):
+            torch.cuda.current_stream().wait_stream(s_)
+
+    def e2e_step():
+        for i, (g, yh) in enumerate(zip(groups, y_host)):
+            with torch.cuda.stream(s_in):
+                if not state["first"]:
+                    s_in.wait_event(ev_run[i])  # last step's launch has read x
+                g["x"].copy_(g["x_host"], non_blocking=True)
+                ev_in[i].record(s_in)
+            with torch.cuda.stream(s_run):
+                s_run.wait_event(ev_in[i])
+                if not state["first"]:
+                    s_run.wait_event(ev_out[i])  # last step's y has been copied out
+                run_group(wf, g, False)
+                ev_run[i].record(s_run)
+            with torch.cuda.stream(s_out):
+                s_out.wait_event(ev_run[i])
+                yh.copy_(g["y"], non_blocking=True)
+                ev_out[i].record(s_out)
+        state["first"] = False
+
+    e2e_fork()
     for _ in range(3):
         e2e_step()
+    e2e_join()
     barrier()
     e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     e0.record()
+    e2e_fork()
     for _ in range(args.steps):
         e2e_step()
+    e2e_join()
     e1.record()
     barrier()
     ms_e2e = e0.elapsed_time(e1) / args.steps
