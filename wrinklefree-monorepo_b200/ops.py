@@ -139,6 +139,7 @@ def act_quant_i8(x: torch.Tensor, per_tensor: bool = False, eps: float = 1e-5, w
 # --------------------------------------------------------------------------
 
 _workspaces = {}
+PREQUANT_MIN_TOKENS = 16  # decode path: tokens from which x is quantized once by a kernel of its own
 
 
 def _workspace(device, nbytes: int) -> torch.Tensor:
@@ -198,6 +199,10 @@ def bitlinear(x: torch.Tensor, codes: torch.Tensor, w_scale, bias: Optional[torc
                                              _ptr(ws), ws.numel() if ws is not None else 0, flags, _stream()),
                     "wf_bitlinear_prefill")
         else:
+            if x2.dtype != torch.int8 and m >= PREQUANT_MIN_TOKENS:
+                # every CTA of the decode kernel quantizes the tokens of its problem: from this many tokens on one
+                # quantization kernel in front of it is cheaper (same arithmetic, same bits)
+                x2, x_scale = act_quant_i8(x2, eps=eps)
             L.check(lib.wf_bitlinear_decode(x2.data_ptr(), _DT[x2.dtype], x2.stride(0), _ptr(x_scale), codes.data_ptr(),
                                             layout, ws_ptr, ws_host, _ptr(bias), _DT[bias.dtype] if bias is not None else 0,
                                             y.data_ptr(), _DT[y.dtype], y.stride(0), _ptr(acc), m, n, k, eps, flags,
@@ -254,6 +259,11 @@ class DecodeGroup:
         self.outputs, self.accs = [], []
         arr, self._raw = L.aligned_problem_array(len(problems))
         dev = problems[0]["x"].device
+        # With many tokens per problem x is quantized once per distinct input by a kernel of its own in run(), and
+        # the problems read the int8 copy (otherwise every CTA quantizes the tokens of its problem again).
+        prequant = all(pr["x"].dtype != torch.int8 and pr["x"].reshape(-1, pr["x"].shape[-1]).shape[0] >= PREQUANT_MIN_TOKENS
+                       for pr in problems)
+        self._quant = {}  # data_ptr of x -> (x2, q, scale, eps)
         for i, pr in enumerate(problems):
             x, codes, w_scale = pr["x"], pr["codes"], pr["w_scale"]
             bias, x_scale = pr.get("bias"), pr.get("x_scale")
@@ -264,6 +274,12 @@ class DecodeGroup:
                 raise ValueError("DecodeGroup needs x with unit inner stride and contiguous codes")
             m, n = x2.shape[0], codes.shape[0]
             out_dtype = pr.get("out_dtype") or (torch.float32 if x.dtype == torch.int8 else x.dtype)
+            if prequant:
+                key = (x2.data_ptr(), x2.stride(0), m, k, pr.get("eps", 1e-5))
+                if key not in self._quant:
+                    self._quant[key] = (x2, torch.empty((m, k), dtype=torch.int8, device=dev),
+                                        torch.empty(m, dtype=torch.float32, device=dev), pr.get("eps", 1e-5))
+                _, x2, x_scale, _ = self._quant[key]
             y = pr.get("out")
             if y is None:
                 y = torch.empty((m, n), dtype=out_dtype, device=dev)
@@ -295,8 +311,12 @@ class DecodeGroup:
         stream, so the kernel reads them without waiting for it (independent layers, experts, replicas)."""
         import ctypes as C
 
-        flags = (L.FLAG_PDL if pdl else 0) | (L.FLAG_X_READY if (pdl and x_ready) else 0)
+        flags = (L.FLAG_PDL if pdl else 0) | (L.FLAG_X_READY if (pdl and x_ready and not self._quant) else 0)
         with torch.cuda.device(self.device):
+            for (xs, q, scale, eps) in self._quant.values():
+                L.check(L.lib().wf_act_quant_i8(xs.data_ptr(), _DT[xs.dtype], xs.shape[0], xs.shape[1], xs.stride(0),
+                                                L.ACT_PER_TOKEN, eps, q.data_ptr(), scale.data_ptr(), None, _stream()),
+                        "wf_act_quant_i8")
             L.check(L.lib().wf_bitlinear_decode_grouped(self._dev.data_ptr(), C.addressof(self._host), self.count,
                                                         flags, _stream()), "wf_bitlinear_decode_grouped")
         return self.outputs
