@@ -38,7 +38,7 @@ BATCHES = [1, 4, 16, 64]
 LAYERS = {(2560, 2560): 120, (6912, 2560): 60, (2560, 6912): 30}
 METRIC = "ternary_decode_gemv_GBps"
 GEMM_MIN_M = 16  # token batches from here on run on the tensor-core contraction (one batched launch per layer stack)
-NCU_TRAFFIC_RATIO = 162.28 / 158.27  # dram bytes / algorithmic bytes, profiles/decode_stream_kernel_m1_2560x2560.md
+NCU_TRAFFIC_RATIO = 203.52 / 197.84  # dram bytes / algorithmic bytes, profiles/decode_stream_kernel_m1_2560x2560.md
 
 
 def algorithmic_bytes(m: int, n: int, k: int) -> int:
@@ -611,7 +611,7 @@ def main():
             "data": "synthetic", "config": dict(config, pdl=pdl, graph=True, parallelism=f"tp{world}" if world > 1 else "single"),
             "roofline": {"bound": "hbm", "achieved": achieved, "peak": peaks["hbm_gbs"], "unit": "GB/s",
                          "frac": achieved / peaks["hbm_gbs"], "traffic": per_launch_bytes * NCU_TRAFFIC_RATIO,
-                         "traffic_source": "ncu capture of the M=1 2560x2560 group (162.3 MB DRAM for 158.27 MB algorithmic), scaled",
+                         "traffic_source": "ncu capture of the M=1 2560x2560 group (203.5 MB DRAM for 197.8 MB algorithmic), scaled",
                          "peak_kind": peak_kind + " copy bandwidth",
                          "kernel": "decode_stream_kernel", "launches": f"the {dec_launches} grouped launches with M < {GEMM_MIN_M}",
                          "bytes_per_launch": per_launch_bytes, "us_per_launch": per_launch_us},
