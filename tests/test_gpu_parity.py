@@ -248,6 +248,33 @@ def test_prefill_entry_point_bit_exact(wf, oracle_c):
     wf.device_status()
 
 
+def test_small_m_contraction_bit_exact(wf, oracle_c):
+    """Up to 64 tokens the contraction swaps the operand roles (128 weight rows x 16/32/64 tokens, expanded weights in
+    tensor memory): partial row blocks, K tails (also a packed stage of a single K block), both layouts, bias, int8 input."""
+    L = wf._lib
+    rng = np.random.default_rng(23)
+    for (m, k, n) in ((1, 256, 64), (16, 576, 144), (17, 1024, 700), (33, 2560, 256), (64, 128, 257), (40, 6912, 300),
+                      (5, 640, 130), (64, 1664, 128)):
+        t = rng.integers(-1, 2, size=(n, k)).astype(np.int8)
+        x = torch.from_numpy(rng.standard_normal((m, k)).astype(np.float32)).bfloat16()
+        bias = torch.from_numpy(rng.standard_normal(n).astype(np.float32))
+        q, s = oracle_c.act_quant(x.float().numpy(), 1)
+        acc_o = oracle_c.int_gemm(q, t)
+        for lay in ((L.LAYOUT_WF16, L.LAYOUT_I2S) if k % 128 == 0 else (L.LAYOUT_WF16,)):
+            codes = wf.pack_codes(torch.from_numpy(t).to(DEV), lay)
+            y, acc = wf.bitlinear(x.to(DEV), codes, 0.02, layout=lay, out_dtype=torch.float32, want_acc=True, path="prefill")
+            assert np.array_equal(acc.cpu().numpy(), acc_o), (m, k, n, lay)
+            assert np.array_equal(y.cpu().numpy(), oracle_c.rescale(acc_o, s, 0.02)), (m, k, n, lay)
+        yb = wf.bitlinear(x.to(DEV), codes, 0.02, bias=bias.to(DEV), layout=lay, path="prefill")
+        assert yb.dtype == torch.bfloat16
+        want = torch.from_numpy(oracle_c.rescale(acc_o, s, 0.02, bias.numpy())).bfloat16()
+        assert torch.equal(yb.cpu(), want), (m, k, n)
+        yq, accq = wf.bitlinear(torch.from_numpy(q).to(DEV), codes, 0.02, layout=lay, x_scale=torch.from_numpy(s).to(DEV),
+                                want_acc=True, path="prefill")
+        assert np.array_equal(accq.cpu().numpy(), acc_o) and np.array_equal(yq.cpu().numpy(), oracle_c.rescale(acc_o, s, 0.02))
+    wf.device_status()
+
+
 @pytest.mark.parametrize("n,k", [(2560, 2560), (6912, 2560), (2560, 6912)])
 def test_prefill_full_size_against_decode_path(wf, n, k):
     """BASELINE prefill shapes at M = 512: the tensor-core path and the decode path agree bit for bit."""

@@ -334,6 +334,281 @@ __global__ void __launch_bounds__(PF_THREADS, 1)
     }
 }
 
+// ---------------------------------------------------------------------------------------------------------
+// Few tokens per problem (M <= 64): the roles of the operands are swapped.  The tile is 128 WEIGHT rows (the MMA's
+// M side) x NTOK tokens (the N side, 16/32/64), and the expanded weights never touch shared memory: four warps
+// expand the packed rows of a K block in registers (thread = weight row) and store them with tcgen05.st into a
+// ring of tensor-memory stages, from which the MMA takes its A operand; only the packed bytes (TMA, 128-byte rows
+// spanning four K blocks) and the small int8 token tile (TMA, the B operand) pass through shared memory.  With the
+// 128-token tile above, the shared-memory port (32 KB of expanded weights written and read again per K block, plus a
+// 16 KB token tile that is mostly padding) is the bound for small M.
+//   warp 0: TMA producer of the packed weights (ring of SM_PS stages: they come from HBM, the ring runs far ahead)
+//   warp 14: TMA producer of the token tiles (ring of SM_XS stages, in step with the tensor-memory stages)
+//   warp 1: MMA issuer: D[128 rows x NTOK] += A(tmem stage) x B(token tile), four K = 32 steps per K block
+//   warps 2-5 / 6-9: two expansion groups, alternate K blocks (a warp reaches the TMEM lanes 32 * (warp % 4) ..)
+//   warps 10-13: epilogue (thread = weight row; per token: correction, rescale, bias, store; the per-token constants
+//                of a problem are fetched into shared memory once, not once per tile)
+constexpr int SM_BM = 128;   // weight rows per tile
+constexpr int SM_BK = 128;   // K per MMA stage
+constexpr int SM_PK = 4;     // K blocks per packed-weight stage (rows of 128 bytes)
+constexpr int SM_PS = 8;     // packed-weight stages
+constexpr int SM_XS = 8;     // token-tile stages = tensor-memory stages of expanded weights
+constexpr int SM_P_BYTES = SM_BM * SM_PK * SM_BK / 4;  // 16 KB
+constexpr int SM_THREADS = 15 * 32;
+constexpr int SM_ACC_COLS = 128;  // two accumulators of up to 64 columns
+constexpr int SM_A_COLS = SM_BK / 4;  // 32 columns of 4 int8 per K block
+template <int NTOK>
+constexpr size_t sm_smem() {  // more than half of an SM's shared memory: two of these CTAs never share an SM
+    return 1024 + SM_PS * SM_P_BYTES + SM_XS * NTOK * SM_BK + 1024;
+}
+static_assert(sm_smem<16>() > 114 * 1024 && sm_smem<64>() <= 227 * 1024, "shared memory of the small-M contraction");
+
+__device__ __forceinline__ void mma_i8_ts(uint32_t d_tmem, uint32_t a_tmem, uint64_t b_desc, uint32_t idesc, uint32_t accumulate) {
+    asm volatile(
+        "{\n .reg .pred p;\n setp.ne.b32 p, %4, 0;\n"
+        " tcgen05.mma.cta_group::1.kind::i8 [%0], [%1], %2, %3, {%5, %5, %5, %5}, p;\n}\n" ::"r"(d_tmem),
+        "r"(a_tmem), "l"(b_desc), "r"(idesc), "r"(accumulate), "r"(0u)
+        : "memory");
+}
+__device__ __forceinline__ void tmem_st32(uint32_t addr, const uint32_t (&v)[32]) {
+    asm volatile(
+        "tcgen05.st.sync.aligned.32x32b.x32.b32 [%0], {%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,%16,%17,%18,%19,%20,%21,%22,"
+        "%23,%24,%25,%26,%27,%28,%29,%30,%31,%32};\n" ::"r"(addr),
+        "r"(v[0]), "r"(v[1]), "r"(v[2]), "r"(v[3]), "r"(v[4]), "r"(v[5]), "r"(v[6]), "r"(v[7]), "r"(v[8]), "r"(v[9]), "r"(v[10]),
+        "r"(v[11]), "r"(v[12]), "r"(v[13]), "r"(v[14]), "r"(v[15]), "r"(v[16]), "r"(v[17]), "r"(v[18]), "r"(v[19]), "r"(v[20]),
+        "r"(v[21]), "r"(v[22]), "r"(v[23]), "r"(v[24]), "r"(v[25]), "r"(v[26]), "r"(v[27]), "r"(v[28]), "r"(v[29]), "r"(v[30]),
+        "r"(v[31])
+        : "memory");
+    asm volatile("tcgen05.wait::st.sync.aligned;\n" ::: "memory");
+}
+template <int NREG>
+__device__ __forceinline__ void tmem_ldn(uint32_t addr, uint32_t (&v)[NREG]);
+template <>
+__device__ __forceinline__ void tmem_ldn<16>(uint32_t addr, uint32_t (&v)[16]) {
+    asm volatile(
+        "tcgen05.ld.sync.aligned.32x32b.x16.b32 {%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15}, [%16];\n"
+        : "=r"(v[0]), "=r"(v[1]), "=r"(v[2]), "=r"(v[3]), "=r"(v[4]), "=r"(v[5]), "=r"(v[6]), "=r"(v[7]), "=r"(v[8]), "=r"(v[9]),
+          "=r"(v[10]), "=r"(v[11]), "=r"(v[12]), "=r"(v[13]), "=r"(v[14]), "=r"(v[15])
+        : "r"(addr));
+    asm volatile("tcgen05.wait::ld.sync.aligned;\n" ::: "memory");
+}
+
+template <int NTOK>
+__global__ void __launch_bounds__(SM_THREADS, 1)
+    smallm_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_constant__ CUtensorMap tmap_p, const PrefillParams p) {
+    constexpr int X_BYTES = NTOK * SM_BK;
+    extern __shared__ uint8_t smem_raw[];
+    uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~static_cast<uintptr_t>(1023));
+    uint8_t* p_ring = smem;                           // [SM_PS][128 rows x 128 B], 128-byte swizzle
+    uint8_t* x_ring = p_ring + SM_PS * SM_P_BYTES;    // [SM_XS][NTOK rows x 128 B], 128-byte swizzle
+    uint64_t* p_full = reinterpret_cast<uint64_t*>(x_ring + SM_XS * X_BYTES);
+    uint64_t* p_empty = p_full + SM_PS;
+    uint64_t* x_full = p_empty + SM_PS;
+    uint64_t* a_full = x_full + SM_XS;        // expanded weights of the stage are in tensor memory
+    uint64_t* st_free = a_full + SM_XS;       // MMA commit: token tile and tensor-memory stage may be overwritten
+    uint64_t* acc_full = st_free + SM_XS;
+    uint64_t* acc_empty = acc_full + 2;
+    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(acc_empty + 2);
+    volatile int* poisoned = reinterpret_cast<volatile int*>(tmem_slot + 1);
+    int* s_rowsum = reinterpret_cast<int*>(tmem_slot + 2);   // [64] per-token constants of the epilogue's current problem
+    float* s_inv = reinterpret_cast<float*>(s_rowsum + 64);  // [64]
+
+    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    const int kblocks = (p.K + SM_BK - 1) / SM_BK;
+    const int total_tiles = p.tiles_n * p.batch;  // tiles_n = row blocks of 128 per problem
+
+    if (tid == 0) {
+        for (int s = 0; s < SM_PS; ++s) {
+            mbar_init(&p_full[s], 1);
+            mbar_init(&p_empty[s], 8);
+        }
+        for (int s = 0; s < SM_XS; ++s) {
+            mbar_init(&x_full[s], 1);
+            mbar_init(&a_full[s], 4);
+            mbar_init(&st_free[s], 1);
+        }
+        for (int a = 0; a < 2; ++a) {
+            mbar_init(&acc_full[a], 1);
+            mbar_init(&acc_empty[a], 4);
+        }
+        *poisoned = 0;
+        asm volatile("fence.mbarrier_init.release.cluster;\n" ::: "memory");
+    }
+    if (warp == 1) {
+        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;\n" ::"r"(smem_u32(tmem_slot)), "r"(512));
+        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;\n" ::);
+    }
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    const uint32_t tmem_base = *tmem_slot;
+    const uint32_t tmem_a = tmem_base + SM_ACC_COLS;  // SM_XS stages of SM_A_COLS columns
+
+    if (warp == 0) {
+        if (lane == 0) {
+            int pit = 0;
+            for (int t = blockIdx.x; t < total_tiles; t += gridDim.x) {
+                const int z = t / p.tiles_n, rb = t % p.tiles_n;
+                const int row_w = z * p.N + rb * SM_BM;
+                for (int kb = 0; kb < kblocks; kb += SM_PK, ++pit) {
+                    const int s = pit % SM_PS;
+                    if (pit >= SM_PS) mbar_wait(&p_empty[s], ((pit / SM_PS) - 1) & 1, poisoned);
+                    mbar_expect_tx(&p_full[s], SM_P_BYTES);  // a box that reaches past K is filled up with zeros
+                    tma_load_2d(p_ring + s * SM_P_BYTES, &tmap_p, (kb / SM_PK) * (SM_PK * SM_BK / 4), row_w, &p_full[s]);
+                }
+            }
+        }
+    } else if (warp == 14) {
+        if (lane == 0) {
+            int it = 0;
+            for (int t = blockIdx.x; t < total_tiles; t += gridDim.x) {
+                const int row_x = (t / p.tiles_n) * p.M;
+                for (int kb = 0; kb < kblocks; ++kb, ++it) {
+                    const int s = it % SM_XS;
+                    if (it >= SM_XS) mbar_wait(&st_free[s], ((it / SM_XS) - 1) & 1, poisoned);
+                    mbar_expect_tx(&x_full[s], X_BYTES);
+                    tma_load_2d(x_ring + s * X_BYTES, &tmap_x, kb * SM_BK, row_x, &x_full[s]);
+                }
+            }
+        }
+    } else if (warp == 1) {
+        if (lane == 0) {
+            // D = s32, A = unsigned 8-bit (codes, from tensor memory), B = signed 8-bit (tokens, K-major), N = NTOK, M = 128
+            const uint32_t idesc = (2u << 4) | (0u << 7) | (1u << 10) | (static_cast<uint32_t>(NTOK >> 3) << 17) |
+                                   (static_cast<uint32_t>(SM_BM >> 4) << 24);
+            int it = 0, nt = 0;
+            for (int t = blockIdx.x; t < total_tiles; t += gridDim.x, ++nt) {
+                const int a = nt & 1;
+                if (nt >= 2) mbar_wait(&acc_empty[a], ((nt >> 1) - 1) & 1, poisoned);
+                tc_fence_after();
+                const uint32_t d_tmem = tmem_base + a * NTOK;
+                for (int kb = 0; kb < kblocks; ++kb, ++it) {
+                    const int s = it % SM_XS;
+                    mbar_wait(&x_full[s], (it / SM_XS) & 1, poisoned);
+                    mbar_wait(&a_full[s], (it / SM_XS) & 1, poisoned);
+                    tc_fence_after();
+                    const uint64_t b_desc = smem_desc_sw128(smem_u32(x_ring + s * X_BYTES));
+#pragma unroll
+                    for (int k = 0; k < SM_BK / 32; ++k)
+                        mma_i8_ts(d_tmem, tmem_a + s * SM_A_COLS + k * 8, b_desc + 2 * k, idesc, (kb | k) ? 1u : 0u);
+                    tc_commit(&st_free[s]);
+                }
+                tc_commit(&acc_full[a]);
+            }
+        }
+    } else if (warp < 10) {
+        // ---- expansion: group g = (warp - 2) / 4 takes the K blocks with it % 2 == g; thread = weight row of the tile
+        const int grp = (warp - 2) >> 2;
+        const int quarter = warp & 3;           // the TMEM lanes this warp may access
+        const int r = quarter * 32 + lane;      // weight row inside the tile
+        const uint32_t m = 0x03030303u;
+        int it = 0, pit = 0;
+        for (int t = blockIdx.x; t < total_tiles; t += gridDim.x) {
+            for (int kb = 0; kb < kblocks; ++kb, ++it) {
+                const int j = kb % SM_PK;
+                const bool last_of_stage = j == SM_PK - 1 || kb == kblocks - 1;
+                const int ps = pit % SM_PS;
+                const bool mine = (it & 1) == grp;
+                if (mine) {
+                    const int s = it % SM_XS;
+                    mbar_wait(&p_full[ps], (pit / SM_PS) & 1, poisoned);
+                    if (it >= SM_XS) mbar_wait(&st_free[s], ((it / SM_XS) - 1) & 1, poisoned);
+                    tc_fence_after();
+                    // the row's 32 packed bytes of this K block: 16-byte chunks 2j, 2j + 1 (chunk c lies at c ^ (r & 7))
+                    const uint32_t row = smem_u32(p_ring + ps * SM_P_BYTES) + r * 128;
+                    const uint4 lo = lds128p(row + (((2 * j) ^ (r & 7)) << 4));
+                    const uint4 hi = lds128p(row + (((2 * j + 1) ^ (r & 7)) << 4));
+                    const uint32_t w[8] = {lo.x, lo.y, lo.z, lo.w, hi.x, hi.y, hi.z, hi.w};
+                    uint32_t v[32];  // column c = weights 4c .. 4c + 3 of the K block
+                    if (p.layout == WF_LAYOUT_WF16) {
+#pragma unroll
+                        for (int i = 0; i < 8; ++i) {
+                            v[4 * i] = w[i] & m;
+                            v[4 * i + 1] = (w[i] >> 2) & m;
+                            v[4 * i + 2] = (w[i] >> 4) & m;
+                            v[4 * i + 3] = (w[i] >> 6) & m;
+                        }
+                    } else {  // I2_S: byte b of the 32 holds weights b, b + 32, b + 64, b + 96 at bits 7:6, 5:4, 3:2, 1:0
+#pragma unroll
+                        for (int g = 0; g < 4; ++g)
+#pragma unroll
+                            for (int i = 0; i < 8; ++i) v[8 * g + i] = (w[i] >> (6 - 2 * g)) & m;
+                    }
+                    tmem_st32(tmem_a + s * SM_A_COLS + (static_cast<uint32_t>(quarter * 32) << 16), v);
+                    tc_fence_before();
+                    __syncwarp();
+                    if (lane == 0) mbar_arrive(&a_full[s]);
+                }
+                if (last_of_stage) {
+                    // every expansion warp walks the K blocks in order, so here all its reads of this packed stage are
+                    // done (they ended in registers before its tcgen05.st), whichever K blocks of the stage were its own
+                    // (a warp without a K block of its own in this stage still waits for the stage, so that it cannot
+                    // arrive twice within one phase of p_empty)
+                    if (!mine) mbar_wait(&p_full[ps], (pit / SM_PS) & 1, poisoned);
+                    __syncwarp();
+                    if (lane == 0) mbar_arrive(&p_empty[ps]);
+                    ++pit;
+                }
+            }
+        }
+    } else if (warp < 14) {
+        // ---- epilogue: thread = weight row (TMEM lane), registers = tokens
+        const int quarter = warp & 3;
+        const int r = quarter * 32 + lane;
+        const int et = tid - 10 * 32;  // 0..127
+        int nt = 0, cur_z = -1;
+        for (int t = blockIdx.x; t < total_tiles; t += gridDim.x, ++nt) {
+            const int z = t / p.tiles_n, rb = t % p.tiles_n;
+            const int a = nt & 1;
+            const int nrow = rb * SM_BM + r;
+            const bool row_ok = nrow < p.N;
+            if (z != cur_z) {  // uniform over the four warps: the constants of this problem's tokens
+                asm volatile("bar.sync 2, 128;\n" ::: "memory");  // nobody still reads the previous problem's
+                if (et < NTOK && et < p.M) {
+                    const int64_t tok = static_cast<int64_t>(z) * p.M + et;
+                    s_rowsum[et] = p.rowsum[tok];
+                    s_inv[et] = p.x_scale ? __frcp_rn(p.x_scale[tok]) : 1.0f;
+                }
+                asm volatile("bar.sync 2, 128;\n" ::: "memory");
+                cur_z = z;
+            }
+            const float s_w = p.w_scale ? __ldg(p.w_scale + static_cast<int64_t>(z) * p.w_scale_stride) : p.w_scale_host;
+            const float bias = (p.bias && row_ok) ? load1_rt(p.bias, p.bias_dtype, nrow) : 0.f;
+            mbar_wait(&acc_full[a], (nt >> 1) & 1, poisoned);
+            tc_fence_after();
+#pragma unroll
+            for (int c0 = 0; c0 < NTOK; c0 += 16) {
+                uint32_t v[16];
+                tmem_ldn<16>(tmem_base + (static_cast<uint32_t>(quarter * 32) << 16) + a * NTOK + c0, v);
+                if (c0 + 16 == NTOK) {  // the accumulator is in registers: hand it back to the MMA warp
+                    tc_fence_before();
+                    __syncwarp();
+                    if (lane == 0) mbar_arrive(&acc_empty[a]);
+                }
+                if (!row_ok) continue;
+#pragma unroll
+                for (int jt = 0; jt < 16; ++jt) {
+                    const int tok_in = c0 + jt;
+                    if (tok_in < p.M) {
+                        const int64_t tok = static_cast<int64_t>(z) * p.M + tok_in;
+                        const int acc = static_cast<int>(v[jt]) - s_rowsum[tok_in];
+                        float o = rescale(acc, s_inv[tok_in], s_w);
+                        if (p.bias) o = __fadd_rn(o, bias);
+                        store1_rt(p.y, p.y_dtype, tok * p.ldy + nrow, o);
+                        if (p.acc_out) p.acc_out[tok * p.N + nrow] = acc;
+                    }
+                }
+            }
+        }
+    }
+    tc_fence_before();
+    __syncthreads();
+    if (warp == 1) {
+        tc_fence_after();
+        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;\n" ::"r"(tmem_base), "r"(512));
+    }
+}
+
 // row sums of an int8 matrix (for activations that arrive already quantized)
 __global__ void rowsum_i8_kernel(const int8_t* __restrict__ q, int64_t ldq, int K, int32_t* __restrict__ rowsum) {
     const int64_t m = blockIdx.x;
@@ -430,12 +705,14 @@ static int prefill_impl(const char* who, const void* x, int x_dtype, int64_t ldx
 
     EncodeTiledFn enc = pf_encode_fn();
     if (!enc) return fail(WF_E_DEVICE, "cuTensorMapEncodeTiled is not available in this driver");
+    const bool small_m = M_one <= 64;  // few tokens per problem: weights on the MMA's M side, expanded into tensor memory
+    const int ntok = M_one <= 16 ? 16 : (M_one <= 32 ? 32 : 64);
     alignas(64) CUtensorMap tmap_a, tmap_p;
     const cuuint32_t ones[2] = {1, 1};
     {
         const cuuint64_t dims[2] = {static_cast<cuuint64_t>(K), static_cast<cuuint64_t>(M)};
         const cuuint64_t strides[1] = {static_cast<cuuint64_t>(ldq)};
-        const cuuint32_t box[2] = {PF_BK, PF_BM};
+        const cuuint32_t box[2] = {PF_BK, static_cast<cuuint32_t>(small_m ? ntok : PF_BM)};
         CUresult r = enc(&tmap_a, CU_TENSOR_MAP_DATA_TYPE_UINT8, 2, const_cast<int8_t*>(q), dims, strides, box, ones,
                          CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
                          CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
@@ -444,9 +721,11 @@ static int prefill_impl(const char* who, const void* x, int x_dtype, int64_t ldx
     {
         const cuuint64_t dims[2] = {static_cast<cuuint64_t>(K / 4), static_cast<cuuint64_t>(batch * N)};
         const cuuint64_t strides[1] = {static_cast<cuuint64_t>(K / 4)};
-        const cuuint32_t box[2] = {PF_BK / 4, PF_BN};
-        CUresult r = enc(&tmap_p, CU_TENSOR_MAP_DATA_TYPE_UINT8, 2, const_cast<uint8_t*>(codes), dims, strides, box, ones,
-                         CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_NONE, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+        const cuuint32_t box_big[2] = {PF_BK / 4, PF_BN};
+        const cuuint32_t box_small[2] = {SM_PK * SM_BK / 4, SM_BM};
+        CUresult r = enc(&tmap_p, CU_TENSOR_MAP_DATA_TYPE_UINT8, 2, const_cast<uint8_t*>(codes), dims, strides,
+                         small_m ? box_small : box_big, ones, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                         small_m ? CU_TENSOR_MAP_SWIZZLE_128B : CU_TENSOR_MAP_SWIZZLE_NONE, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
                          CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
         if (r != CUDA_SUCCESS) return fail(WF_E_DEVICE, "cuTensorMapEncodeTiled (packed weights) failed with %d", (int)r);
     }
@@ -461,10 +740,27 @@ static int prefill_impl(const char* who, const void* x, int x_dtype, int64_t ldx
     static thread_local int sms = 148;
     if (!configured) {
         WF_CUDA(cudaFuncSetAttribute(prefill_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(PF_SMEM)));
+        WF_CUDA(cudaFuncSetAttribute(smallm_kernel<16>, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(sm_smem<16>())));
+        WF_CUDA(cudaFuncSetAttribute(smallm_kernel<32>, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(sm_smem<32>())));
+        WF_CUDA(cudaFuncSetAttribute(smallm_kernel<64>, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(sm_smem<64>())));
         int dev = 0;
         WF_CUDA(cudaGetDevice(&dev));
         WF_CUDA(cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev));
         configured = true;
+    }
+    if (small_m) {
+        pp.tiles_m = 1;
+        pp.tiles_n = static_cast<int>((N + SM_BM - 1) / SM_BM);
+        const long long tiles = static_cast<long long>(pp.tiles_n) * pp.batch;
+        const unsigned grid = static_cast<unsigned>(tiles < sms ? tiles : sms);
+        if (ntok == 16)
+            smallm_kernel<16><<<grid, SM_THREADS, sm_smem<16>(), st>>>(tmap_a, tmap_p, pp);
+        else if (ntok == 32)
+            smallm_kernel<32><<<grid, SM_THREADS, sm_smem<32>(), st>>>(tmap_a, tmap_p, pp);
+        else
+            smallm_kernel<64><<<grid, SM_THREADS, sm_smem<64>(), st>>>(tmap_a, tmap_p, pp);
+        WF_CUDA(cudaGetLastError());
+        return WF_OK;
     }
     const long long tiles = static_cast<long long>(pp.tiles_m) * pp.tiles_n * pp.batch;
     dim3 grid(static_cast<unsigned>(tiles < sms ? tiles : sms));
