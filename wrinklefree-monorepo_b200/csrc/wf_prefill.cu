@@ -349,19 +349,20 @@ __global__ void __launch_bounds__(PF_THREADS, 1)
 //   warps 10-13: epilogue (thread = weight row; per token: correction, rescale, bias, store; the per-token constants
 //                of a problem are fetched into shared memory once, not once per tile)
 constexpr int SM_BM = 128;   // weight rows per tile
-constexpr int SM_BK = 128;   // K per MMA stage
-constexpr int SM_PK = 4;     // K blocks per packed-weight stage (rows of 128 bytes)
-constexpr int SM_PS = 8;     // packed-weight stages
-constexpr int SM_XS = 8;     // token-tile stages = tensor-memory stages of expanded weights
+constexpr int SM_BK = 128;   // K per swizzle atom (128 bytes of int8)
+constexpr int SM_PK = 4;     // atoms per stage: a stage is 512 weights of every row = one 128-byte packed row segment
+constexpr int SM_PS = 6;     // packed-weight stages
+constexpr int SM_XS = 3;     // token-tile stages = tensor-memory stages of expanded weights
 constexpr int SM_P_BYTES = SM_BM * SM_PK * SM_BK / 4;  // 16 KB
 constexpr int SM_THREADS = 15 * 32;
 constexpr int SM_ACC_COLS = 128;  // two accumulators of up to 64 columns
-constexpr int SM_A_COLS = SM_BK / 4;  // 32 columns of 4 int8 per K block
+constexpr int SM_A_COLS = SM_PK * SM_BK / 4;  // 128 columns of 4 int8 per stage
 template <int NTOK>
 constexpr size_t sm_smem() {  // more than half of an SM's shared memory: two of these CTAs never share an SM
-    return 1024 + SM_PS * SM_P_BYTES + SM_XS * NTOK * SM_BK + 1024;
+    return 1024 + SM_PS * SM_P_BYTES + SM_XS * NTOK * SM_PK * SM_BK + 1024;
 }
 static_assert(sm_smem<16>() > 114 * 1024 && sm_smem<64>() <= 227 * 1024, "shared memory of the small-M contraction");
+static_assert(SM_ACC_COLS + SM_XS * SM_A_COLS <= 512, "tensor memory of the small-M contraction");
 
 __device__ __forceinline__ void mma_i8_ts(uint32_t d_tmem, uint32_t a_tmem, uint64_t b_desc, uint32_t idesc, uint32_t accumulate) {
     asm volatile(
@@ -396,11 +397,12 @@ __device__ __forceinline__ void tmem_ldn<16>(uint32_t addr, uint32_t (&v)[16]) {
 template <int NTOK>
 __global__ void __launch_bounds__(SM_THREADS, 1)
     smallm_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_constant__ CUtensorMap tmap_p, const PrefillParams p) {
-    constexpr int X_BYTES = NTOK * SM_BK;
+    constexpr int X_ATOM = NTOK * SM_BK;        // one 128-byte swizzle atom of the token tile
+    constexpr int X_BYTES = SM_PK * X_ATOM;     // a stage: 512 values of K for every token
     extern __shared__ uint8_t smem_raw[];
     uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~static_cast<uintptr_t>(1023));
     uint8_t* p_ring = smem;                           // [SM_PS][128 rows x 128 B], 128-byte swizzle
-    uint8_t* x_ring = p_ring + SM_PS * SM_P_BYTES;    // [SM_XS][NTOK rows x 128 B], 128-byte swizzle
+    uint8_t* x_ring = p_ring + SM_PS * SM_P_BYTES;    // [SM_XS][SM_PK atoms][NTOK rows x 128 B], 128-byte swizzle
     uint64_t* p_full = reinterpret_cast<uint64_t*>(x_ring + SM_XS * X_BYTES);
     uint64_t* p_empty = p_full + SM_PS;
     uint64_t* x_full = p_empty + SM_PS;
@@ -414,13 +416,15 @@ __global__ void __launch_bounds__(SM_THREADS, 1)
     float* s_inv = reinterpret_cast<float*>(s_rowsum + 64);  // [64]
 
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
-    const int kblocks = (p.K + SM_BK - 1) / SM_BK;
+    // K is walked in stages of 512: one barrier round trip, one commit and sixteen MMAs per stage.  A last stage
+    // that reaches past K is zero-filled by the TMA unit on both operands (code 0 times activation 0).
+    const int stages = (p.K + SM_PK * SM_BK - 1) / (SM_PK * SM_BK);
     const int total_tiles = p.tiles_n * p.batch;  // tiles_n = row blocks of 128 per problem
 
     if (tid == 0) {
         for (int s = 0; s < SM_PS; ++s) {
             mbar_init(&p_full[s], 1);
-            mbar_init(&p_empty[s], 8);
+            mbar_init(&p_empty[s], 4);
         }
         for (int s = 0; s < SM_XS; ++s) {
             mbar_init(&x_full[s], 1);
@@ -446,28 +450,30 @@ __global__ void __launch_bounds__(SM_THREADS, 1)
 
     if (warp == 0) {
         if (lane == 0) {
-            int pit = 0;
+            int sit = 0;
             for (int t = blockIdx.x; t < total_tiles; t += gridDim.x) {
                 const int z = t / p.tiles_n, rb = t % p.tiles_n;
                 const int row_w = z * p.N + rb * SM_BM;
-                for (int kb = 0; kb < kblocks; kb += SM_PK, ++pit) {
-                    const int s = pit % SM_PS;
-                    if (pit >= SM_PS) mbar_wait(&p_empty[s], ((pit / SM_PS) - 1) & 1, poisoned);
-                    mbar_expect_tx(&p_full[s], SM_P_BYTES);  // a box that reaches past K is filled up with zeros
-                    tma_load_2d(p_ring + s * SM_P_BYTES, &tmap_p, (kb / SM_PK) * (SM_PK * SM_BK / 4), row_w, &p_full[s]);
+                for (int g = 0; g < stages; ++g, ++sit) {
+                    const int s = sit % SM_PS;
+                    if (sit >= SM_PS) mbar_wait(&p_empty[s], ((sit / SM_PS) - 1) & 1, poisoned);
+                    mbar_expect_tx(&p_full[s], SM_P_BYTES);
+                    tma_load_2d(p_ring + s * SM_P_BYTES, &tmap_p, g * (SM_PK * SM_BK / 4), row_w, &p_full[s]);
                 }
             }
         }
     } else if (warp == 14) {
         if (lane == 0) {
-            int it = 0;
+            int sit = 0;
             for (int t = blockIdx.x; t < total_tiles; t += gridDim.x) {
                 const int row_x = (t / p.tiles_n) * p.M;
-                for (int kb = 0; kb < kblocks; ++kb, ++it) {
-                    const int s = it % SM_XS;
-                    if (it >= SM_XS) mbar_wait(&st_free[s], ((it / SM_XS) - 1) & 1, poisoned);
+                for (int g = 0; g < stages; ++g, ++sit) {
+                    const int s = sit % SM_XS;
+                    if (sit >= SM_XS) mbar_wait(&st_free[s], ((sit / SM_XS) - 1) & 1, poisoned);
                     mbar_expect_tx(&x_full[s], X_BYTES);
-                    tma_load_2d(x_ring + s * X_BYTES, &tmap_x, kb * SM_BK, row_x, &x_full[s]);
+#pragma unroll
+                    for (int j = 0; j < SM_PK; ++j)  // an atom that lies past K arrives as zeros
+                        tma_load_2d(x_ring + s * X_BYTES + j * X_ATOM, &tmap_x, (g * SM_PK + j) * SM_BK, row_x, &x_full[s]);
                 }
             }
         }
@@ -476,50 +482,51 @@ __global__ void __launch_bounds__(SM_THREADS, 1)
             // D = s32, A = unsigned 8-bit (codes, from tensor memory), B = signed 8-bit (tokens, K-major), N = NTOK, M = 128
             const uint32_t idesc = (2u << 4) | (0u << 7) | (1u << 10) | (static_cast<uint32_t>(NTOK >> 3) << 17) |
                                    (static_cast<uint32_t>(SM_BM >> 4) << 24);
-            int it = 0, nt = 0;
+            int sit = 0, nt = 0;
             for (int t = blockIdx.x; t < total_tiles; t += gridDim.x, ++nt) {
                 const int a = nt & 1;
                 if (nt >= 2) mbar_wait(&acc_empty[a], ((nt >> 1) - 1) & 1, poisoned);
                 tc_fence_after();
                 const uint32_t d_tmem = tmem_base + a * NTOK;
-                for (int kb = 0; kb < kblocks; ++kb, ++it) {
-                    const int s = it % SM_XS;
-                    mbar_wait(&x_full[s], (it / SM_XS) & 1, poisoned);
-                    mbar_wait(&a_full[s], (it / SM_XS) & 1, poisoned);
+                for (int g = 0; g < stages; ++g, ++sit) {
+                    const int s = sit % SM_XS;
+                    mbar_wait(&x_full[s], (sit / SM_XS) & 1, poisoned);
+                    mbar_wait(&a_full[s], (sit / SM_XS) & 1, poisoned);
                     tc_fence_after();
-                    const uint64_t b_desc = smem_desc_sw128(smem_u32(x_ring + s * X_BYTES));
+                    const uint32_t xs = smem_u32(x_ring + s * X_BYTES);
 #pragma unroll
-                    for (int k = 0; k < SM_BK / 32; ++k)
-                        mma_i8_ts(d_tmem, tmem_a + s * SM_A_COLS + k * 8, b_desc + 2 * k, idesc, (kb | k) ? 1u : 0u);
+                    for (int kk = 0; kk < SM_PK * SM_BK / 32; ++kk) {  // 32 values of K per MMA
+                        const uint64_t b_desc = smem_desc_sw128(xs + (kk >> 2) * X_ATOM) + 2 * (kk & 3);
+                        mma_i8_ts(d_tmem, tmem_a + s * SM_A_COLS + kk * 8, b_desc, idesc, (g | kk) ? 1u : 0u);
+                    }
                     tc_commit(&st_free[s]);
                 }
                 tc_commit(&acc_full[a]);
             }
         }
     } else if (warp < 10) {
-        // ---- expansion: group g = (warp - 2) / 4 takes the K blocks with it % 2 == g; thread = weight row of the tile
+        // ---- expansion: group (warp - 2) / 4 takes every other stage; thread = weight row of the tile
         const int grp = (warp - 2) >> 2;
         const int quarter = warp & 3;           // the TMEM lanes this warp may access
         const int r = quarter * 32 + lane;      // weight row inside the tile
         const uint32_t m = 0x03030303u;
-        int it = 0, pit = 0;
+        int sit = 0;
         for (int t = blockIdx.x; t < total_tiles; t += gridDim.x) {
-            for (int kb = 0; kb < kblocks; ++kb, ++it) {
-                const int j = kb % SM_PK;
-                const bool last_of_stage = j == SM_PK - 1 || kb == kblocks - 1;
-                const int ps = pit % SM_PS;
-                const bool mine = (it & 1) == grp;
-                if (mine) {
-                    const int s = it % SM_XS;
-                    mbar_wait(&p_full[ps], (pit / SM_PS) & 1, poisoned);
-                    if (it >= SM_XS) mbar_wait(&st_free[s], ((it / SM_XS) - 1) & 1, poisoned);
-                    tc_fence_after();
-                    // the row's 32 packed bytes of this K block: 16-byte chunks 2j, 2j + 1 (chunk c lies at c ^ (r & 7))
-                    const uint32_t row = smem_u32(p_ring + ps * SM_P_BYTES) + r * 128;
+            for (int g = 0; g < stages; ++g, ++sit) {
+                if ((sit & 1) != grp) continue;
+                const int ps = sit % SM_PS, s = sit % SM_XS;
+                mbar_wait(&p_full[ps], (sit / SM_PS) & 1, poisoned);
+                if (sit >= SM_XS) mbar_wait(&st_free[s], ((sit / SM_XS) - 1) & 1, poisoned);
+                tc_fence_after();
+                const uint32_t row = smem_u32(p_ring + ps * SM_P_BYTES) + r * 128;
+                const uint32_t dst = tmem_a + s * SM_A_COLS + (static_cast<uint32_t>(quarter * 32) << 16);
+#pragma unroll
+                for (int j = 0; j < SM_PK; ++j) {
+                    // the row's 32 packed bytes of atom j: 16-byte chunks 2j, 2j + 1 (chunk c lies at c ^ (r & 7))
                     const uint4 lo = lds128p(row + (((2 * j) ^ (r & 7)) << 4));
                     const uint4 hi = lds128p(row + (((2 * j + 1) ^ (r & 7)) << 4));
                     const uint32_t w[8] = {lo.x, lo.y, lo.z, lo.w, hi.x, hi.y, hi.z, hi.w};
-                    uint32_t v[32];  // column c = weights 4c .. 4c + 3 of the K block
+                    uint32_t v[32];  // column c = weights 4c .. 4c + 3 of the atom
                     if (p.layout == WF_LAYOUT_WF16) {
 #pragma unroll
                         for (int i = 0; i < 8; ++i) {
@@ -530,24 +537,17 @@ __global__ void __launch_bounds__(SM_THREADS, 1)
                         }
                     } else {  // I2_S: byte b of the 32 holds weights b, b + 32, b + 64, b + 96 at bits 7:6, 5:4, 3:2, 1:0
 #pragma unroll
-                        for (int g = 0; g < 4; ++g)
+                        for (int q = 0; q < 4; ++q)
 #pragma unroll
-                            for (int i = 0; i < 8; ++i) v[8 * g + i] = (w[i] >> (6 - 2 * g)) & m;
+                            for (int i = 0; i < 8; ++i) v[8 * q + i] = (w[i] >> (6 - 2 * q)) & m;
                     }
-                    tmem_st32(tmem_a + s * SM_A_COLS + (static_cast<uint32_t>(quarter * 32) << 16), v);
-                    tc_fence_before();
-                    __syncwarp();
-                    if (lane == 0) mbar_arrive(&a_full[s]);
+                    tmem_st32(dst + j * 32, v);
                 }
-                if (last_of_stage) {
-                    // every expansion warp walks the K blocks in order, so here all its reads of this packed stage are
-                    // done (they ended in registers before its tcgen05.st), whichever K blocks of the stage were its own
-                    // (a warp without a K block of its own in this stage still waits for the stage, so that it cannot
-                    // arrive twice within one phase of p_empty)
-                    if (!mine) mbar_wait(&p_full[ps], (pit / SM_PS) & 1, poisoned);
-                    __syncwarp();
-                    if (lane == 0) mbar_arrive(&p_empty[ps]);
-                    ++pit;
+                tc_fence_before();
+                __syncwarp();
+                if (lane == 0) {
+                    mbar_arrive(&a_full[s]);
+                    mbar_arrive(&p_empty[ps]);  // the packed rows are in registers / tensor memory
                 }
             }
         }
