@@ -573,7 +573,15 @@ __global__ void __launch_bounds__(SM_THREADS, 1)
                 cur_z = z;
             }
             const float s_w = p.w_scale ? __ldg(p.w_scale + static_cast<int64_t>(z) * p.w_scale_stride) : p.w_scale_host;
-            const float bias = (p.bias && row_ok) ? load1_rt(p.bias, p.bias_dtype, nrow) : 0.f;
+            const bool has_bias = p.bias != nullptr;
+            const float bias = (has_bias && row_ok) ? load1_rt(p.bias, p.bias_dtype, nrow) : 0.f;
+            // These warps share their schedulers with the expansion warps: the per-token work is kept to a handful of
+            // instructions (pointer increments, the output type decided outside the loop).
+            const int64_t tok0 = static_cast<int64_t>(z) * p.M;
+            const bool fast16 = (p.y_dtype == WF_BF16 || p.y_dtype == WF_F16) && p.acc_out == nullptr;
+            uint16_t* y16 = static_cast<uint16_t*>(p.y) + tok0 * p.ldy + nrow;
+            const bool is_bf16 = p.y_dtype == WF_BF16;
+            const int mtok = p.M;
             mbar_wait(&acc_full[a], (nt >> 1) & 1, poisoned);
             tc_fence_after();
 #pragma unroll
@@ -586,16 +594,29 @@ __global__ void __launch_bounds__(SM_THREADS, 1)
                     if (lane == 0) mbar_arrive(&acc_empty[a]);
                 }
                 if (!row_ok) continue;
+                if (fast16) {
 #pragma unroll
-                for (int jt = 0; jt < 16; ++jt) {
-                    const int tok_in = c0 + jt;
-                    if (tok_in < p.M) {
-                        const int64_t tok = static_cast<int64_t>(z) * p.M + tok_in;
-                        const int acc = static_cast<int>(v[jt]) - s_rowsum[tok_in];
-                        float o = rescale(acc, s_inv[tok_in], s_w);
-                        if (p.bias) o = __fadd_rn(o, bias);
-                        store1_rt(p.y, p.y_dtype, tok * p.ldy + nrow, o);
-                        if (p.acc_out) p.acc_out[tok * p.N + nrow] = acc;
+                    for (int jt = 0; jt < 16; ++jt) {
+                        const int tok_in = c0 + jt;
+                        if (tok_in < mtok) {
+                            float o = rescale(static_cast<int>(v[jt]) - s_rowsum[tok_in], s_inv[tok_in], s_w);
+                            if (has_bias) o = __fadd_rn(o, bias);
+                            const uint16_t bits = is_bf16 ? __bfloat16_as_ushort(__float2bfloat16_rn(o)) : __half_as_ushort(__float2half_rn(o));
+                            y16[tok_in * p.ldy] = bits;
+                        }
+                    }
+                } else {
+#pragma unroll
+                    for (int jt = 0; jt < 16; ++jt) {
+                        const int tok_in = c0 + jt;
+                        if (tok_in < mtok) {
+                            const int64_t tok = tok0 + tok_in;
+                            const int acc = static_cast<int>(v[jt]) - s_rowsum[tok_in];
+                            float o = rescale(acc, s_inv[tok_in], s_w);
+                            if (has_bias) o = __fadd_rn(o, bias);
+                            store1_rt(p.y, p.y_dtype, tok * p.ldy + nrow, o);
+                            if (p.acc_out) p.acc_out[tok * p.N + nrow] = acc;
+                        }
                     }
                 }
             }
