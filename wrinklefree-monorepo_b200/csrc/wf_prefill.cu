@@ -346,23 +346,26 @@ __global__ void __launch_bounds__(PF_THREADS, 1)
 //   warp 14: TMA producer of the token tiles (ring of SM_XS stages, in step with the tensor-memory stages)
 //   warp 1: MMA issuer: D[128 rows x NTOK] += A(tmem stage) x B(token tile), four K = 32 steps per K block
 //   warps 2-5 / 6-9: two expansion groups, alternate K blocks (a warp reaches the TMEM lanes 32 * (warp % 4) ..)
-//   warps 10-13: epilogue (thread = weight row; per token: correction, rescale, bias, store; the per-token constants
-//                of a problem are fetched into shared memory once, not once per tile)
+//   warps 10-13 (and 15-18 from 32 tokens on: each group takes half of the token columns): epilogue (thread = weight
+//                row; per token: correction, rescale, bias, store; the per-token constants of a token block are
+//                fetched into shared memory once, not once per tile)
 constexpr int SM_BM = 128;   // weight rows per tile
 constexpr int SM_BK = 128;   // K per swizzle atom (128 bytes of int8)
 constexpr int SM_PK = 4;     // atoms per stage: a stage is 512 weights of every row = one 128-byte packed row segment
 constexpr int SM_PS = 6;     // packed-weight stages
-constexpr int SM_XS = 3;     // token-tile stages = tensor-memory stages of expanded weights
+template <int NTOK>
+constexpr int sm_xs() { return NTOK > 64 ? 2 : 3; }  // token-tile stages = tensor-memory stages of expanded weights
 constexpr int SM_P_BYTES = SM_BM * SM_PK * SM_BK / 4;  // 16 KB
-constexpr int SM_THREADS = 15 * 32;
-constexpr int SM_ACC_COLS = 128;  // two accumulators of up to 64 columns
+constexpr int SM_THREADS = 19 * 32;
+template <int NTOK>
+constexpr int sm_acc_cols() { return NTOK > 64 ? 256 : 128; }  // two accumulators of NTOK columns
 constexpr int SM_A_COLS = SM_PK * SM_BK / 4;  // 128 columns of 4 int8 per stage
 template <int NTOK>
 constexpr size_t sm_smem() {  // more than half of an SM's shared memory: two of these CTAs never share an SM
-    return 1024 + SM_PS * SM_P_BYTES + SM_XS * NTOK * SM_PK * SM_BK + 1024;
+    return 1024 + SM_PS * SM_P_BYTES + sm_xs<NTOK>() * NTOK * SM_PK * SM_BK + 2048;
 }
-static_assert(sm_smem<16>() > 114 * 1024 && sm_smem<64>() <= 227 * 1024, "shared memory of the small-M contraction");
-static_assert(SM_ACC_COLS + SM_XS * SM_A_COLS <= 512, "tensor memory of the small-M contraction");
+static_assert(sm_smem<16>() > 114 * 1024 && sm_smem<64>() <= 227 * 1024 && sm_smem<128>() <= 227 * 1024, "shared memory");
+static_assert(sm_acc_cols<64>() + sm_xs<64>() * SM_A_COLS <= 512 && sm_acc_cols<128>() + sm_xs<128>() * SM_A_COLS <= 512, "tensor memory");
 
 __device__ __forceinline__ void mma_i8_ts(uint32_t d_tmem, uint32_t a_tmem, uint64_t b_desc, uint32_t idesc, uint32_t accumulate) {
     asm volatile(
@@ -397,6 +400,10 @@ __device__ __forceinline__ void tmem_ldn<16>(uint32_t addr, uint32_t (&v)[16]) {
 template <int NTOK>
 __global__ void __launch_bounds__(SM_THREADS, 1)
     smallm_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_constant__ CUtensorMap tmap_p, const PrefillParams p) {
+    constexpr int EPI_GROUPS = NTOK >= 32 ? 2 : 1;  // epilogue warp groups; each takes NTOK / EPI_GROUPS token columns
+    constexpr int EPI_COLS = NTOK / EPI_GROUPS;
+    constexpr int SM_XS = NTOK > 64 ? 2 : 3;
+    constexpr int SM_ACC_COLS = NTOK > 64 ? 256 : 128;
     constexpr int X_ATOM = NTOK * SM_BK;        // one 128-byte swizzle atom of the token tile
     constexpr int X_BYTES = SM_PK * X_ATOM;     // a stage: 512 values of K for every token
     extern __shared__ uint8_t smem_raw[];
@@ -412,14 +419,17 @@ __global__ void __launch_bounds__(SM_THREADS, 1)
     uint64_t* acc_empty = acc_full + 2;
     uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(acc_empty + 2);
     volatile int* poisoned = reinterpret_cast<volatile int*>(tmem_slot + 1);
-    int* s_rowsum = reinterpret_cast<int*>(tmem_slot + 2);   // [64] per-token constants of the epilogue's current problem
-    float* s_inv = reinterpret_cast<float*>(s_rowsum + 64);  // [64]
+    int* s_rowsum = reinterpret_cast<int*>(tmem_slot + 2);   // [NTOK] per-token constants of the epilogue's current token block
+    float* s_inv = reinterpret_cast<float*>(s_rowsum + 128);  // [NTOK]
 
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     // K is walked in stages of 512: one barrier round trip, one commit and sixteen MMAs per stage.  A last stage
     // that reaches past K is zero-filled by the TMA unit on both operands (code 0 times activation 0).
     const int stages = (p.K + SM_PK * SM_BK - 1) / (SM_PK * SM_BK);
-    const int total_tiles = p.tiles_n * p.batch;  // tiles_n = row blocks of 128 per problem
+    // tile -> (problem z, token block tb of NTOK tokens, row block rb of 128 weight rows); row blocks vary fastest, so the
+    // CTAs that run side by side read the same token block
+    const int tiles_per_problem = p.tiles_m * p.tiles_n;
+    const int total_tiles = tiles_per_problem * p.batch;
 
     if (tid == 0) {
         for (int s = 0; s < SM_PS; ++s) {
@@ -433,7 +443,7 @@ __global__ void __launch_bounds__(SM_THREADS, 1)
         }
         for (int a = 0; a < 2; ++a) {
             mbar_init(&acc_full[a], 1);
-            mbar_init(&acc_empty[a], 4);
+            mbar_init(&acc_empty[a], 4 * EPI_GROUPS);
         }
         *poisoned = 0;
         asm volatile("fence.mbarrier_init.release.cluster;\n" ::: "memory");
@@ -452,7 +462,7 @@ __global__ void __launch_bounds__(SM_THREADS, 1)
         if (lane == 0) {
             int sit = 0;
             for (int t = blockIdx.x; t < total_tiles; t += gridDim.x) {
-                const int z = t / p.tiles_n, rb = t % p.tiles_n;
+                const int z = t / tiles_per_problem, rb = t % p.tiles_n;
                 const int row_w = z * p.N + rb * SM_BM;
                 for (int g = 0; g < stages; ++g, ++sit) {
                     const int s = sit % SM_PS;
@@ -466,7 +476,7 @@ __global__ void __launch_bounds__(SM_THREADS, 1)
         if (lane == 0) {
             int sit = 0;
             for (int t = blockIdx.x; t < total_tiles; t += gridDim.x) {
-                const int row_x = (t / p.tiles_n) * p.M;
+                const int row_x = (t / tiles_per_problem) * p.M + ((t % tiles_per_problem) / p.tiles_n) * NTOK;
                 for (int g = 0; g < stages; ++g, ++sit) {
                     const int s = sit % SM_XS;
                     if (sit >= SM_XS) mbar_wait(&st_free[s], ((sit / SM_XS) - 1) & 1, poisoned);
@@ -551,44 +561,47 @@ __global__ void __launch_bounds__(SM_THREADS, 1)
                 }
             }
         }
-    } else if (warp < 14) {
+    } else if (warp < 14 || (warp >= 15 && EPI_GROUPS == 2)) {
         // ---- epilogue: thread = weight row (TMEM lane), registers = tokens
         const int quarter = warp & 3;
         const int r = quarter * 32 + lane;
-        const int et = tid - 10 * 32;  // 0..127
-        int nt = 0, cur_z = -1;
+        const int egrp = warp >= 15 ? 1 : 0;
+        const int et = egrp * 128 + (warp - (egrp ? 15 : 10)) * 32 + lane;  // 0 .. 128 * EPI_GROUPS - 1
+        const int col0 = egrp * EPI_COLS;  // this group's first token column
+        int nt = 0, cur_zb = -1;
         for (int t = blockIdx.x; t < total_tiles; t += gridDim.x, ++nt) {
-            const int z = t / p.tiles_n, rb = t % p.tiles_n;
+            const int z = t / tiles_per_problem, zb = t / p.tiles_n, tb = (t % tiles_per_problem) / p.tiles_n, rb = t % p.tiles_n;
             const int a = nt & 1;
             const int nrow = rb * SM_BM + r;
             const bool row_ok = nrow < p.N;
-            if (z != cur_z) {  // uniform over the four warps: the constants of this problem's tokens
-                asm volatile("bar.sync 2, 128;\n" ::: "memory");  // nobody still reads the previous problem's
-                if (et < NTOK && et < p.M) {
-                    const int64_t tok = static_cast<int64_t>(z) * p.M + et;
+            const int tok_base = tb * NTOK;                 // first token of the block inside its problem
+            const int mtok = min(NTOK, p.M - tok_base);     // valid tokens of the block
+            if (zb != cur_zb) {  // uniform over the four warps: the constants of this token block
+                asm volatile("bar.sync 2, %0;\n" ::"n"(128 * EPI_GROUPS) : "memory");  // nobody still reads the previous block's
+                if (et < mtok) {
+                    const int64_t tok = static_cast<int64_t>(z) * p.M + tok_base + et;
                     s_rowsum[et] = p.rowsum[tok];
                     s_inv[et] = p.x_scale ? __frcp_rn(p.x_scale[tok]) : 1.0f;
                 }
-                asm volatile("bar.sync 2, 128;\n" ::: "memory");
-                cur_z = z;
+                asm volatile("bar.sync 2, %0;\n" ::"n"(128 * EPI_GROUPS) : "memory");
+                cur_zb = zb;
             }
             const float s_w = p.w_scale ? __ldg(p.w_scale + static_cast<int64_t>(z) * p.w_scale_stride) : p.w_scale_host;
             const bool has_bias = p.bias != nullptr;
             const float bias = (has_bias && row_ok) ? load1_rt(p.bias, p.bias_dtype, nrow) : 0.f;
             // These warps share their schedulers with the expansion warps: the per-token work is kept to a handful of
             // instructions (pointer increments, the output type decided outside the loop).
-            const int64_t tok0 = static_cast<int64_t>(z) * p.M;
+            const int64_t tok0 = static_cast<int64_t>(z) * p.M + tok_base;
             const bool fast16 = (p.y_dtype == WF_BF16 || p.y_dtype == WF_F16) && p.acc_out == nullptr;
             uint16_t* y16 = static_cast<uint16_t*>(p.y) + tok0 * p.ldy + nrow;
             const bool is_bf16 = p.y_dtype == WF_BF16;
-            const int mtok = p.M;
             mbar_wait(&acc_full[a], (nt >> 1) & 1, poisoned);
             tc_fence_after();
 #pragma unroll
-            for (int c0 = 0; c0 < NTOK; c0 += 16) {
+            for (int c0 = col0; c0 < col0 + EPI_COLS; c0 += 16) {
                 uint32_t v[16];
                 tmem_ldn<16>(tmem_base + (static_cast<uint32_t>(quarter * 32) << 16) + a * NTOK + c0, v);
-                if (c0 + 16 == NTOK) {  // the accumulator is in registers: hand it back to the MMA warp
+                if (c0 + 16 == col0 + EPI_COLS) {  // this group's columns are in registers: hand them back to the MMA warp
                     tc_fence_before();
                     __syncwarp();
                     if (lane == 0) mbar_arrive(&acc_empty[a]);
@@ -726,8 +739,8 @@ static int prefill_impl(const char* who, const void* x, int x_dtype, int64_t ldx
 
     EncodeTiledFn enc = pf_encode_fn();
     if (!enc) return fail(WF_E_DEVICE, "cuTensorMapEncodeTiled is not available in this driver");
-    const bool small_m = M_one <= 64;  // few tokens per problem: weights on the MMA's M side, expanded into tensor memory
-    const int ntok = M_one <= 16 ? 16 : (M_one <= 32 ? 32 : 64);
+    const bool small_m = true;  // weights on the MMA's M side, expanded into tensor memory; tokens in blocks of ntok
+    const int ntok = M_one <= 16 ? 16 : (M_one <= 32 ? 32 : (M_one <= 64 ? 64 : 128));
     alignas(64) CUtensorMap tmap_a, tmap_p;
     const cuuint32_t ones[2] = {1, 1};
     {
@@ -764,22 +777,25 @@ static int prefill_impl(const char* who, const void* x, int x_dtype, int64_t ldx
         WF_CUDA(cudaFuncSetAttribute(smallm_kernel<16>, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(sm_smem<16>())));
         WF_CUDA(cudaFuncSetAttribute(smallm_kernel<32>, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(sm_smem<32>())));
         WF_CUDA(cudaFuncSetAttribute(smallm_kernel<64>, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(sm_smem<64>())));
+        WF_CUDA(cudaFuncSetAttribute(smallm_kernel<128>, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(sm_smem<128>())));
         int dev = 0;
         WF_CUDA(cudaGetDevice(&dev));
         WF_CUDA(cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev));
         configured = true;
     }
     if (small_m) {
-        pp.tiles_m = 1;
+        pp.tiles_m = static_cast<int>((M_one + ntok - 1) / ntok);
         pp.tiles_n = static_cast<int>((N + SM_BM - 1) / SM_BM);
-        const long long tiles = static_cast<long long>(pp.tiles_n) * pp.batch;
+        const long long tiles = static_cast<long long>(pp.tiles_m) * pp.tiles_n * pp.batch;
         const unsigned grid = static_cast<unsigned>(tiles < sms ? tiles : sms);
         if (ntok == 16)
             smallm_kernel<16><<<grid, SM_THREADS, sm_smem<16>(), st>>>(tmap_a, tmap_p, pp);
         else if (ntok == 32)
             smallm_kernel<32><<<grid, SM_THREADS, sm_smem<32>(), st>>>(tmap_a, tmap_p, pp);
-        else
+        else if (ntok == 64)
             smallm_kernel<64><<<grid, SM_THREADS, sm_smem<64>(), st>>>(tmap_a, tmap_p, pp);
+        else
+            smallm_kernel<128><<<grid, SM_THREADS, sm_smem<128>(), st>>>(tmap_a, tmap_p, pp);
         WF_CUDA(cudaGetLastError());
         return WF_OK;
     }
