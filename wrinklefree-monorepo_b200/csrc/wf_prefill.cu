@@ -1,18 +1,20 @@
-// Contraction for large token counts (prefill): a dense int8 GEMM on the
-// 5th-generation tensor cores.
+// The tensor-core contraction (prefill, and every launch with 16 or more tokens per problem): a dense int8 GEMM on
+// the 5th-generation tensor cores.
 //
 //   acc[tok, n] = sum_k q[tok, k] * code[n, k]      (u8 codes = w + 1, s8 activations, s32 accumulate in TMEM)
 //   y[tok, n]   = (float(acc - rowsum[tok]) * inv_sx[tok]) * s_w + bias[n]
 //
-// Persistent CTAs (one per SM) walk over tiles of 128 tokens x 256 weight rows.  Per 128-wide block of K:
-//   * warps 0-1 (one lane each, alternating K blocks) issue two TMA loads into a 4-deep ring: the int8 activation tile (128 tokens x
-//     128 bytes, 128-byte swizzle, the MMA's A operand) and the PACKED weight tile (256 rows x 32 bytes);
-//   * warps 3-10 expand the packed tile to int8 (one mask + shift per four weights) and store it K-major with
-//     the 128-byte swizzle pattern into a 3-deep ring, as the MMA's B operand;
-//   * warp 2 (one lane) issues four tcgen05.mma.kind::i8 (M=128, N=256, K=32) into one of two TMEM
-//     accumulators and commits them to the barriers that free the ring slots.
-// Warps 11-14 read a finished accumulator with tcgen05.ld (lane = token), apply the integer correction and the
-// fp32 rescale and store y while the next tile's MMAs fill the other accumulator.  Every mbarrier wait is bounded.
+// The weights sit on the MMA's M side: a tile is 128 weight rows x NTOK tokens (NTOK = 16 / 32 / 64 for that many
+// tokens per problem, blocks of 128 beyond), and the expanded weights never touch shared memory.  Persistent CTAs (one
+// per SM) walk the tiles; K advances in stages of 512:
+//   * warp 0 (one lane): TMA of the PACKED weight rows (128 rows x 128 bytes, 128-byte swizzle), ring of 6 stages;
+//   * warp 14 (one lane): TMA of the int8 token tile (4 swizzle atoms of NTOK x 128 bytes, the MMA's B operand);
+//   * warps 2-5 / 6-9: two expansion groups that alternate stages; thread = weight row: 8 x ld.shared.v4, mask + shift
+//     to one int8 per byte, 4 x tcgen05.st of 32 columns into a ring of tensor-memory stages;
+//   * warp 1 (one lane): 16 x tcgen05.mma.kind::i8 (M = 128, N = NTOK, K = 32) with the A operand FROM TENSOR MEMORY,
+//     one commit per stage; two accumulators, so the epilogue of a tile runs under the next tile's MMAs;
+//   * warps 10-13 (and 15-18): epilogue, thread = weight row: tcgen05.ld, integer correction, fp32 rescale, store.
+// Every mbarrier wait is bounded.
 #include <cuda.h>
 
 #include "wf_common.cuh"
@@ -29,20 +31,6 @@ int wf_check_linear_args(const char* who, const void* x, int x_dtype, int64_t ld
 
 namespace wf {
 
-constexpr int PF_BM = 128;      // tokens per tile (TMEM lanes)
-constexpr int PF_BN = 256;      // weight rows per tile (TMEM columns of one accumulator)
-constexpr int PF_BK = 128;      // K per stage
-constexpr int PF_TS = 4;        // stages of the TMA ring (activation tile + packed weight tile)
-constexpr int PF_BS = 3;        // stages of the expanded-weight ring
-constexpr int PF_EW = 8;         // expansion warps: 256 threads, one weight row each per K block
-constexpr int PF_PW = 2;         // TMA producer warps (one lane each): K blocks are dealt round-robin
-constexpr int PF_THREADS = (PF_PW + 1 + PF_EW + 4) * 32;  // warps 0-1 TMA, warp 2 MMA, warps 3-10 expand, warps 11-14 epilogue
-constexpr int PF_A_BYTES = PF_BM * PF_BK;        // 16 KB
-constexpr int PF_P_BYTES = PF_BN * PF_BK / 4;    // 8 KB packed
-constexpr int PF_B_BYTES = PF_BN * PF_BK;        // 32 KB expanded
-constexpr int PF_T_BYTES = PF_A_BYTES + PF_P_BYTES;
-constexpr size_t PF_SMEM = 1024 /*align slack*/ + PF_TS * PF_T_BYTES + PF_BS * PF_B_BYTES + 256 /*barriers*/;
-
 struct PrefillParams {
     const float* x_scale;   // [M] per-token multipliers (nullable: 1)
     const int32_t* rowsum;  // [M]
@@ -57,7 +45,7 @@ struct PrefillParams {
     int M, N, K, layout;
     int batch;            // independent problems stacked along rows: tokens [batch*M, K], weights [batch*N, K/4]
     int w_scale_stride;   // floats between the weight scales of consecutive problems
-    int tiles_m, tiles_n; // per problem
+    int tiles_m, tiles_n; // per problem: token blocks of NTOK, row blocks of 128
 };
 
 __device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory"); }
@@ -77,278 +65,18 @@ __device__ __forceinline__ uint64_t smem_desc_sw128(uint32_t addr) {
     return d;
 }
 
-__device__ __forceinline__ void mma_i8(uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc, uint32_t idesc, uint32_t accumulate) {
-    asm volatile(
-        "{\n .reg .pred p;\n setp.ne.b32 p, %4, 0;\n"
-        " tcgen05.mma.cta_group::1.kind::i8 [%0], %1, %2, %3, {%5, %5, %5, %5}, p;\n}\n" ::"r"(d_tmem),
-        "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate), "r"(0u)
-        : "memory");
-}
-
-__device__ __forceinline__ void tmem_ld32(uint32_t addr, uint32_t (&v)[32]) {
-    asm volatile(
-        "tcgen05.ld.sync.aligned.32x32b.x32.b32 {%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,%16,%17,%18,%19,%20,%21,%22,"
-        "%23,%24,%25,%26,%27,%28,%29,%30,%31}, [%32];\n"
-        : "=r"(v[0]), "=r"(v[1]), "=r"(v[2]), "=r"(v[3]), "=r"(v[4]), "=r"(v[5]), "=r"(v[6]), "=r"(v[7]), "=r"(v[8]), "=r"(v[9]),
-          "=r"(v[10]), "=r"(v[11]), "=r"(v[12]), "=r"(v[13]), "=r"(v[14]), "=r"(v[15]), "=r"(v[16]), "=r"(v[17]), "=r"(v[18]),
-          "=r"(v[19]), "=r"(v[20]), "=r"(v[21]), "=r"(v[22]), "=r"(v[23]), "=r"(v[24]), "=r"(v[25]), "=r"(v[26]), "=r"(v[27]),
-          "=r"(v[28]), "=r"(v[29]), "=r"(v[30]), "=r"(v[31])
-        : "r"(addr));
-    asm volatile("tcgen05.wait::ld.sync.aligned;\n" ::: "memory");
-}
-
-__device__ __forceinline__ void sts128(uint32_t addr, uint32_t a, uint32_t b, uint32_t c, uint32_t d) {
-    asm volatile("st.shared.v4.u32 [%0], {%1,%2,%3,%4};\n" ::"r"(addr), "r"(a), "r"(b), "r"(c), "r"(d) : "memory");
-}
 __device__ __forceinline__ uint4 lds128p(uint32_t addr) {
     uint4 v;
     asm volatile("ld.shared.v4.u32 {%0,%1,%2,%3}, [%4];\n" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "r"(addr));
     return v;
 }
 
-// Expands one 16-byte half of a packed weight row (64 weights) into four 16-byte chunks of int8 stored in
-// row `r` of a K-major tile with 128-byte swizzle (chunk c of the row lands at chunk c ^ (r & 7)).
-// Consecutive lanes take consecutive 16-byte pieces of the packed tile, so the loads are conflict-free.
-__device__ __forceinline__ void expand_half(uint32_t packed_addr, uint32_t tile_addr, int r, int h, int layout) {
-    const uint4 pk = lds128p(packed_addr);
-    const uint32_t w[4] = {pk.x, pk.y, pk.z, pk.w};
-    const uint32_t row = tile_addr + r * 128;
-    const uint32_t m = 0x03030303u;
-    const int x = r & 7;
-    if (layout == WF_LAYOUT_WF16) {
-        // word i of this half holds weights 64h + 16i .. + 15: bit pair j of byte b = weight + 4j + b
-#pragma unroll
-        for (int i = 0; i < 4; ++i)
-            sts128(row + (((4 * h + i) ^ x) << 4), w[i] & m, (w[i] >> 2) & m, (w[i] >> 4) & m, (w[i] >> 6) & m);
-    } else {
-        // I2_S: byte j of the row's 32 bytes holds weights j, j+32, j+64, j+96 at bits 7:6, 5:4, 3:2, 1:0;
-        // this half (bytes 16h .. 16h+15) therefore feeds chunks 2g + h, g = 0..3
-#pragma unroll
-        for (int g = 0; g < 4; ++g) {
-            const int sh = 6 - 2 * g;
-            sts128(row + (((2 * g + h) ^ x) << 4), (w[0] >> sh) & m, (w[1] >> sh) & m, (w[2] >> sh) & m, (w[3] >> sh) & m);
-        }
-    }
-}
-
-// Persistent kernel: CTA c computes tiles c, c + grid, ...  A tile = 128 tokens x 256 weight rows of one problem.
-// Rings and barriers (every wait bounded):
-//   TMA ring (PF_TS):  t_full[s]  <- TMA bytes;         t_empty[s] <- MMA commit (A read) + the expansion warps (packed read)
-//   B ring   (PF_BS):  b_full[s]  <- the expansion warps;  b_empty[s] <- MMA commit
-//   accumulators (2):  acc_full[a] <- MMA commit after the last K block; acc_empty[a] <- 4 epilogue warps
-__global__ void __launch_bounds__(PF_THREADS, 1)
-    prefill_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_p, const PrefillParams p) {
-    extern __shared__ uint8_t smem_raw[];
-    // operand tiles need 1024-byte alignment for the 128-byte swizzle
-    uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~static_cast<uintptr_t>(1023));
-    uint8_t* t_ring = smem;                              // [PF_TS][A 16 KB | packed 8 KB]
-    uint8_t* b_ring = smem + PF_TS * PF_T_BYTES;         // [PF_BS][32 KB]
-    uint64_t* t_full = reinterpret_cast<uint64_t*>(b_ring + PF_BS * PF_B_BYTES);
-    uint64_t* t_empty = t_full + PF_TS;
-    uint64_t* b_full = t_empty + PF_TS;
-    uint64_t* b_empty = b_full + PF_BS;
-    uint64_t* acc_full = b_empty + PF_BS;
-    uint64_t* acc_empty = acc_full + 2;
-    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(acc_empty + 2);
-    volatile int* poisoned = reinterpret_cast<volatile int*>(tmem_slot + 1);
-
-    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
-    const int kblocks = (p.K + PF_BK - 1) / PF_BK;
-    const int tiles_per_problem = p.tiles_m * p.tiles_n;
-    const int total_tiles = tiles_per_problem * p.batch;
-
-    if (tid == 0) {
-        for (int s = 0; s < PF_TS; ++s) {
-            mbar_init(&t_full[s], 1);
-            mbar_init(&t_empty[s], 1 + PF_EW);
-        }
-        for (int s = 0; s < PF_BS; ++s) {
-            mbar_init(&b_full[s], PF_EW);
-            mbar_init(&b_empty[s], 1);
-        }
-        for (int a = 0; a < 2; ++a) {
-            mbar_init(&acc_full[a], 1);
-            mbar_init(&acc_empty[a], 4);
-        }
-        *poisoned = 0;
-        asm volatile("fence.mbarrier_init.release.cluster;\n" ::: "memory");
-    }
-    if (warp == PF_PW) {  // all 512 TMEM columns: two 128 x 256 int32 accumulators
-        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;\n" ::"r"(smem_u32(tmem_slot)), "r"(2 * PF_BN));
-        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;\n" ::);
-    }
-    tc_fence_before();
-    __syncthreads();
-    tc_fence_after();
-    const uint32_t tmem_base = *tmem_slot;
-
-    // tile -> (problem z, token block, row block); row blocks vary fastest so neighbouring CTAs share activations
-#define PF_TILE_COORDS(t)                                  \
-    const int z = (t) / tiles_per_problem;                 \
-    const int tm = ((t) % tiles_per_problem) / p.tiles_n;  \
-    const int tn = (t) % p.tiles_n;
-
-    if (warp < PF_PW) {
-        // one thread cannot wait, arm and issue once per 512 tensor-core clocks: the producers alternate
-        if (lane == 0) {
-            int it = 0;
-            for (int t = blockIdx.x; t < total_tiles; t += gridDim.x) {
-                PF_TILE_COORDS(t)
-                const int row_a = z * p.M + tm * PF_BM, row_w = z * p.N + tn * PF_BN;
-                for (int kb = 0; kb < kblocks; ++kb, ++it) {
-                    if (it % PF_PW != warp) continue;
-                    const int s = it % PF_TS;
-                    if (it >= PF_TS) mbar_wait(&t_empty[s], ((it / PF_TS) - 1) & 1, poisoned);
-                    uint8_t* st = t_ring + s * PF_T_BYTES;
-                    mbar_expect_tx(&t_full[s], PF_T_BYTES);
-                    tma_load_2d(st, &tmap_a, kb * PF_BK, row_a, &t_full[s]);
-                    tma_load_2d(st + PF_A_BYTES, &tmap_p, kb * (PF_BK / 4), row_w, &t_full[s]);
-                }
-            }
-        }
-    } else if (warp == PF_PW) {
-        if (lane == 0) {
-            // instruction descriptor: D = s32, A = signed 8-bit, B = unsigned 8-bit, both K-major, N = 256, M = 128
-            const uint32_t idesc = (2u << 4) | (1u << 7) | (0u << 10) | (static_cast<uint32_t>(PF_BN >> 3) << 17) |
-                                   (static_cast<uint32_t>(PF_BM >> 4) << 24);
-            int it = 0, nt = 0;
-            for (int t = blockIdx.x; t < total_tiles; t += gridDim.x, ++nt) {
-                const int a = nt & 1;
-                if (nt >= 2) mbar_wait(&acc_empty[a], ((nt >> 1) - 1) & 1, poisoned);  // epilogue drained this accumulator
-                tc_fence_after();
-                const uint32_t d_tmem = tmem_base + a * PF_BN;
-                for (int kb = 0; kb < kblocks; ++kb, ++it) {
-                    const int ts = it % PF_TS, bs = it % PF_BS;
-                    // b_full implies t_full: the expansion warps waited for the TMA bytes of this block before writing B
-                    mbar_wait(&b_full[bs], (it / PF_BS) & 1, poisoned);
-                    tc_fence_after();
-                    const uint64_t a_desc = smem_desc_sw128(smem_u32(t_ring + ts * PF_T_BYTES));
-                    const uint64_t b_desc = smem_desc_sw128(smem_u32(b_ring + bs * PF_B_BYTES));
-#pragma unroll
-                    for (int k = 0; k < PF_BK / 32; ++k)  // 32 bytes of K per MMA: advance the start address by 2 x 16 bytes
-                        mma_i8(d_tmem, a_desc + 2 * k, b_desc + 2 * k, idesc, (kb | k) ? 1u : 0u);
-                    tc_commit(&t_empty[ts]);
-                    tc_commit(&b_empty[bs]);
-                }
-                tc_commit(&acc_full[a]);
-            }
-        }
-    } else if (warp < PF_PW + 1 + PF_EW) {
-        // ---- expansion: 256 threads, two half rows (16 packed bytes) each per K block
-        const int et = tid - (PF_PW + 1) * 32;  // 0..255
-        int it = 0;
-        for (int t = blockIdx.x; t < total_tiles; t += gridDim.x) {
-            for (int kb = 0; kb < kblocks; ++kb, ++it) {
-                const int ts = it % PF_TS, bs = it % PF_BS;
-                mbar_wait(&t_full[ts], (it / PF_TS) & 1, poisoned);
-                if (it >= PF_BS) mbar_wait(&b_empty[bs], ((it / PF_BS) - 1) & 1, poisoned);
-                const uint32_t packed = smem_u32(t_ring + ts * PF_T_BYTES + PF_A_BYTES);
-                const uint32_t tile = smem_u32(b_ring + bs * PF_B_BYTES);
-                expand_half(packed + et * 16, tile, et >> 1, et & 1, p.layout);
-                expand_half(packed + (et + 256) * 16, tile, 128 + (et >> 1), et & 1, p.layout);
-                asm volatile("fence.proxy.async.shared::cta;\n" ::: "memory");  // generic writes -> visible to the tensor core
-                __syncwarp();
-                if (lane == 0) {
-                    mbar_arrive(&b_full[bs]);
-                    mbar_arrive(&t_empty[ts]);  // the packed tile has been read
-                }
-            }
-        }
-    } else {
-        // ---- epilogue: warp w owns TMEM lanes 32 * (w % 4) .. + 31, lane = token
-        const int lane_grp = (warp & 3) * 32;
-        int nt = 0;
-        for (int t = blockIdx.x; t < total_tiles; t += gridDim.x, ++nt) {
-            PF_TILE_COORDS(t)
-            const int a = nt & 1;
-            mbar_wait(&acc_full[a], (nt >> 1) & 1, poisoned);
-            tc_fence_after();
-            const int tok_in = tm * PF_BM + lane_grp + lane;  // token inside its problem
-            const bool tok_ok = tok_in < p.M;
-            const int64_t tok = static_cast<int64_t>(z) * p.M + tok_in;  // row of the stacked outputs
-            const float s_w = p.w_scale ? __ldg(p.w_scale + static_cast<int64_t>(z) * p.w_scale_stride) : p.w_scale_host;
-            const float inv = tok_ok ? (p.x_scale ? __frcp_rn(p.x_scale[tok]) : 1.0f) : 0.f;
-            const int rs = tok_ok ? p.rowsum[tok] : 0;
-            const bool vec_ok = (p.ldy * (p.y_dtype == WF_F32 ? 4 : 2)) % 16 == 0 && reinterpret_cast<uintptr_t>(p.y) % 16 == 0;
-            const int n0 = tn * PF_BN;
-            for (int c0 = 0; c0 < PF_BN; c0 += 32) {
-                uint32_t v[32];
-                tmem_ld32(tmem_base + (static_cast<uint32_t>(lane_grp) << 16) + a * PF_BN + c0, v);
-                if (c0 + 32 == PF_BN) {  // the accumulator is in registers: hand it back to the MMA warp
-                    tc_fence_before();
-                    __syncwarp();
-                    if (lane == 0) mbar_arrive(&acc_empty[a]);
-                }
-                if (!tok_ok) continue;
-                const int nb = n0 + c0;
-                if (nb >= p.N) continue;
-                float o[32];
-#pragma unroll
-                for (int j = 0; j < 32; ++j) {
-                    const int acc = static_cast<int>(v[j]) - rs;
-                    o[j] = rescale(acc, inv, s_w);
-                    if (p.bias && nb + j < p.N) o[j] = __fadd_rn(o[j], load1_rt(p.bias, p.bias_dtype, nb + j));
-                    v[j] = static_cast<uint32_t>(acc);
-                }
-                if (vec_ok && nb + 32 <= p.N) {
-                    // 32 consecutive outputs of one token: 128-bit stores
-                    if (p.y_dtype == WF_F32) {
-                        float4* dst = reinterpret_cast<float4*>(static_cast<float*>(p.y) + tok * p.ldy + nb);
-#pragma unroll
-                        for (int j = 0; j < 8; ++j) dst[j] = make_float4(o[4 * j], o[4 * j + 1], o[4 * j + 2], o[4 * j + 3]);
-                    } else {
-                        uint32_t h[16];
-#pragma unroll
-                        for (int j = 0; j < 16; ++j) {
-                            if (p.y_dtype == WF_BF16) {
-                                __nv_bfloat162 t2 = __floats2bfloat162_rn(o[2 * j], o[2 * j + 1]);
-                                h[j] = *reinterpret_cast<uint32_t*>(&t2);
-                            } else {
-                                __half2 t2 = __floats2half2_rn(o[2 * j], o[2 * j + 1]);
-                                h[j] = *reinterpret_cast<uint32_t*>(&t2);
-                            }
-                        }
-                        uint4* dst = reinterpret_cast<uint4*>(static_cast<uint16_t*>(p.y) + tok * p.ldy + nb);
-#pragma unroll
-                        for (int j = 0; j < 4; ++j) dst[j] = make_uint4(h[4 * j], h[4 * j + 1], h[4 * j + 2], h[4 * j + 3]);
-                    }
-                } else {
-#pragma unroll
-                    for (int j = 0; j < 32; ++j)
-                        if (nb + j < p.N) store1_rt(p.y, p.y_dtype, tok * p.ldy + nb + j, o[j]);
-                }
-                if (p.acc_out) {
-#pragma unroll
-                    for (int j = 0; j < 32; ++j)
-                        if (nb + j < p.N) p.acc_out[tok * p.N + nb + j] = static_cast<int>(v[j]);
-                }
-            }
-        }
-    }
-#undef PF_TILE_COORDS
-    tc_fence_before();
-    __syncthreads();
-    if (warp == PF_PW) {
-        tc_fence_after();
-        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;\n" ::"r"(tmem_base), "r"(2 * PF_BN));
-    }
-}
-
-// ---------------------------------------------------------------------------------------------------------
-// Few tokens per problem (M <= 64): the roles of the operands are swapped.  The tile is 128 WEIGHT rows (the MMA's
-// M side) x NTOK tokens (the N side, 16/32/64), and the expanded weights never touch shared memory: four warps
-// expand the packed rows of a K block in registers (thread = weight row) and store them with tcgen05.st into a
-// ring of tensor-memory stages, from which the MMA takes its A operand; only the packed bytes (TMA, 128-byte rows
-// spanning four K blocks) and the small int8 token tile (TMA, the B operand) pass through shared memory.  With the
-// 128-token tile above, the shared-memory port (32 KB of expanded weights written and read again per K block, plus a
-// 16 KB token tile that is mostly padding) is the bound for small M.
-//   warp 0: TMA producer of the packed weights (ring of SM_PS stages: they come from HBM, the ring runs far ahead)
-//   warp 14: TMA producer of the token tiles (ring of SM_XS stages, in step with the tensor-memory stages)
-//   warp 1: MMA issuer: D[128 rows x NTOK] += A(tmem stage) x B(token tile), four K = 32 steps per K block
-//   warps 2-5 / 6-9: two expansion groups, alternate K blocks (a warp reaches the TMEM lanes 32 * (warp % 4) ..)
-//   warps 10-13 (and 15-18 from 32 tokens on: each group takes half of the token columns): epilogue (thread = weight
-//                row; per token: correction, rescale, bias, store; the per-token constants of a token block are
-//                fetched into shared memory once, not once per tile)
+// What shaped this kernel (all measured on B200): with the expanded weights staged in shared memory (32 KB written
+// and read again per 128-wide K block, beside the token tile) the shared-memory port and the barrier round trips
+// bounded the pipeline at about a third of the tensor rate whatever the ring depths; a blocking mbarrier wait costs
+// ~260 cycles even when it succeeds at once (hence the non-blocking first test in mbar_wait); and for few tokens the
+// MMA issue rate (~29 ns per instruction of K = 32 whatever N <= 64) is the floor, so a barrier round trip per
+// 128-wide K block doubled the time: stages of 512 amortise it over sixteen MMAs.
 constexpr int SM_BM = 128;   // weight rows per tile
 constexpr int SM_BK = 128;   // K per swizzle atom (128 bytes of int8)
 constexpr int SM_PK = 4;     // atoms per stage: a stage is 512 weights of every row = one 128-byte packed row segment
@@ -399,7 +127,7 @@ __device__ __forceinline__ void tmem_ldn<16>(uint32_t addr, uint32_t (&v)[16]) {
 
 template <int NTOK>
 __global__ void __launch_bounds__(SM_THREADS, 1)
-    smallm_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_constant__ CUtensorMap tmap_p, const PrefillParams p) {
+    prefill_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_constant__ CUtensorMap tmap_p, const PrefillParams p) {
     constexpr int EPI_GROUPS = NTOK >= 32 ? 2 : 1;  // epilogue warp groups; each takes NTOK / EPI_GROUPS token columns
     constexpr int EPI_COLS = NTOK / EPI_GROUPS;
     constexpr int SM_XS = NTOK > 64 ? 2 : 3;
@@ -739,14 +467,13 @@ static int prefill_impl(const char* who, const void* x, int x_dtype, int64_t ldx
 
     EncodeTiledFn enc = pf_encode_fn();
     if (!enc) return fail(WF_E_DEVICE, "cuTensorMapEncodeTiled is not available in this driver");
-    const bool small_m = true;  // weights on the MMA's M side, expanded into tensor memory; tokens in blocks of ntok
     const int ntok = M_one <= 16 ? 16 : (M_one <= 32 ? 32 : (M_one <= 64 ? 64 : 128));
     alignas(64) CUtensorMap tmap_a, tmap_p;
     const cuuint32_t ones[2] = {1, 1};
     {
         const cuuint64_t dims[2] = {static_cast<cuuint64_t>(K), static_cast<cuuint64_t>(M)};
         const cuuint64_t strides[1] = {static_cast<cuuint64_t>(ldq)};
-        const cuuint32_t box[2] = {PF_BK, static_cast<cuuint32_t>(small_m ? ntok : PF_BM)};
+        const cuuint32_t box[2] = {SM_BK, static_cast<cuuint32_t>(ntok)};
         CUresult r = enc(&tmap_a, CU_TENSOR_MAP_DATA_TYPE_UINT8, 2, const_cast<int8_t*>(q), dims, strides, box, ones,
                          CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
                          CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
@@ -755,11 +482,9 @@ static int prefill_impl(const char* who, const void* x, int x_dtype, int64_t ldx
     {
         const cuuint64_t dims[2] = {static_cast<cuuint64_t>(K / 4), static_cast<cuuint64_t>(batch * N)};
         const cuuint64_t strides[1] = {static_cast<cuuint64_t>(K / 4)};
-        const cuuint32_t box_big[2] = {PF_BK / 4, PF_BN};
-        const cuuint32_t box_small[2] = {SM_PK * SM_BK / 4, SM_BM};
-        CUresult r = enc(&tmap_p, CU_TENSOR_MAP_DATA_TYPE_UINT8, 2, const_cast<uint8_t*>(codes), dims, strides,
-                         small_m ? box_small : box_big, ones, CU_TENSOR_MAP_INTERLEAVE_NONE,
-                         small_m ? CU_TENSOR_MAP_SWIZZLE_128B : CU_TENSOR_MAP_SWIZZLE_NONE, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+        const cuuint32_t box[2] = {SM_PK * SM_BK / 4, SM_BM};
+        CUresult r = enc(&tmap_p, CU_TENSOR_MAP_DATA_TYPE_UINT8, 2, const_cast<uint8_t*>(codes), dims, strides, box, ones,
+                         CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
                          CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
         if (r != CUDA_SUCCESS) return fail(WF_E_DEVICE, "cuTensorMapEncodeTiled (packed weights) failed with %d", (int)r);
     }
@@ -768,40 +493,30 @@ static int prefill_impl(const char* who, const void* x, int x_dtype, int64_t ldx
     pp.bias_dtype = bias_dtype; pp.y = y; pp.y_dtype = y_dtype; pp.ldy = ldy; pp.acc_out = acc_out;
     pp.M = static_cast<int>(M_one); pp.N = static_cast<int>(N); pp.K = static_cast<int>(K); pp.layout = layout;
     pp.batch = static_cast<int>(batch); pp.w_scale_stride = static_cast<int>(w_scale_stride);
-    pp.tiles_m = static_cast<int>((M_one + PF_BM - 1) / PF_BM);
-    pp.tiles_n = static_cast<int>((N + PF_BN - 1) / PF_BN);
+    pp.tiles_m = static_cast<int>((M_one + ntok - 1) / ntok);
+    pp.tiles_n = static_cast<int>((N + SM_BM - 1) / SM_BM);
     static thread_local bool configured = false;
     static thread_local int sms = 148;
     if (!configured) {
-        WF_CUDA(cudaFuncSetAttribute(prefill_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(PF_SMEM)));
-        WF_CUDA(cudaFuncSetAttribute(smallm_kernel<16>, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(sm_smem<16>())));
-        WF_CUDA(cudaFuncSetAttribute(smallm_kernel<32>, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(sm_smem<32>())));
-        WF_CUDA(cudaFuncSetAttribute(smallm_kernel<64>, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(sm_smem<64>())));
-        WF_CUDA(cudaFuncSetAttribute(smallm_kernel<128>, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(sm_smem<128>())));
+        WF_CUDA(cudaFuncSetAttribute(prefill_kernel<16>, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(sm_smem<16>())));
+        WF_CUDA(cudaFuncSetAttribute(prefill_kernel<32>, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(sm_smem<32>())));
+        WF_CUDA(cudaFuncSetAttribute(prefill_kernel<64>, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(sm_smem<64>())));
+        WF_CUDA(cudaFuncSetAttribute(prefill_kernel<128>, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(sm_smem<128>())));
         int dev = 0;
         WF_CUDA(cudaGetDevice(&dev));
         WF_CUDA(cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev));
         configured = true;
     }
-    if (small_m) {
-        pp.tiles_m = static_cast<int>((M_one + ntok - 1) / ntok);
-        pp.tiles_n = static_cast<int>((N + SM_BM - 1) / SM_BM);
-        const long long tiles = static_cast<long long>(pp.tiles_m) * pp.tiles_n * pp.batch;
-        const unsigned grid = static_cast<unsigned>(tiles < sms ? tiles : sms);
-        if (ntok == 16)
-            smallm_kernel<16><<<grid, SM_THREADS, sm_smem<16>(), st>>>(tmap_a, tmap_p, pp);
-        else if (ntok == 32)
-            smallm_kernel<32><<<grid, SM_THREADS, sm_smem<32>(), st>>>(tmap_a, tmap_p, pp);
-        else if (ntok == 64)
-            smallm_kernel<64><<<grid, SM_THREADS, sm_smem<64>(), st>>>(tmap_a, tmap_p, pp);
-        else
-            smallm_kernel<128><<<grid, SM_THREADS, sm_smem<128>(), st>>>(tmap_a, tmap_p, pp);
-        WF_CUDA(cudaGetLastError());
-        return WF_OK;
-    }
     const long long tiles = static_cast<long long>(pp.tiles_m) * pp.tiles_n * pp.batch;
-    dim3 grid(static_cast<unsigned>(tiles < sms ? tiles : sms));
-    prefill_kernel<<<grid, PF_THREADS, PF_SMEM, st>>>(tmap_a, tmap_p, pp);
+    const unsigned grid = static_cast<unsigned>(tiles < sms ? tiles : sms);
+    if (ntok == 16)
+        prefill_kernel<16><<<grid, SM_THREADS, sm_smem<16>(), st>>>(tmap_a, tmap_p, pp);
+    else if (ntok == 32)
+        prefill_kernel<32><<<grid, SM_THREADS, sm_smem<32>(), st>>>(tmap_a, tmap_p, pp);
+    else if (ntok == 64)
+        prefill_kernel<64><<<grid, SM_THREADS, sm_smem<64>(), st>>>(tmap_a, tmap_p, pp);
+    else
+        prefill_kernel<128><<<grid, SM_THREADS, sm_smem<128>(), st>>>(tmap_a, tmap_p, pp);
     WF_CUDA(cudaGetLastError());
     return WF_OK;
 }
