@@ -238,6 +238,24 @@ int wf_rope_kv_bf16(void* q, const void* k, const void* v, const float* cos, con
                     void* vcache, int64_t B, int nq, int nkv, int D, int T, unsigned flags, void* stream);
 int wf_act_mul_bf16(const void* gate, const void* up, void* out, int64_t n, int mode, unsigned flags, void* stream);
 
+/*
+ * One-shot all-reduce (sum) over peer memory for the small tensors that follow a row-parallel projection in the
+ * decode step; one process per GPU on one node.  It stands where the reference's tensor-parallel layers call the
+ * library all-reduce after o_proj / down_proj (sglang/srt/layers/linear.py:1419-1420); larger tensors stay on NCCL.
+ * Set-up, once per process group: every rank calls wf_ar_init (allocates its exchange buffer of 4 KiB + 2 * max_bytes
+ * and returns a CUDA IPC handle of wf_ar_handle_bytes() bytes), the ranks exchange the handles by any means, and every
+ * rank calls wf_ar_connect with all of them in rank order.  wf_ar_allreduce(in, out, n elements, dtype) may run in
+ * place, must be called by every rank with the same n and dtype in the same order, sums in rank order in fp32 (all
+ * ranks obtain identical bits) and takes WF_FLAG_PDL.  Its waits for the peers are bounded (about 0.1 s); a wait that
+ * ran out is reported by wf_ar_status (WF_E_LIMIT) and leaves `out` undefined.
+ */
+int wf_ar_handle_bytes(void);
+int wf_ar_init(int world, int rank, size_t max_bytes, void** ctx_out, unsigned char* handle_out);
+int wf_ar_connect(void* ctx, const unsigned char* handles);
+int wf_ar_allreduce(void* ctx, const void* in, void* out, int64_t n, int dtype, unsigned flags, void* stream);
+int wf_ar_status(void* ctx, int* out);
+int wf_ar_destroy(void* ctx);
+
 #ifdef __cplusplus
 }
 #endif

@@ -49,6 +49,38 @@ def _worker(rank, world, port, results):
         y = row(x.to(dev), out_dtype=torch.float32)
         err = float((y - full).abs().max() / full.abs().max())
         assert err < 2e-2, err
+        # the peer-memory all-reduce: equal to the fp32 sum in rank order on every rank, in place, repeatedly (the two
+        # exchange slots alternate), also inside a CUDA graph; a row-parallel layer built on it
+        ar = tp.OneShotAllReduce(max_bytes=1 << 20)
+        for rep, (numel, dt) in enumerate([(4096, torch.bfloat16), (8, torch.bfloat16), (262144, torch.bfloat16), (4096, torch.float32),
+                                           (520, torch.float16), (4096, torch.bfloat16)]):
+            parts = [(torch.randn(numel, generator=torch.Generator().manual_seed(100 * rep + r)) * 3).to(dt) for r in range(world)]
+            want = sum(p_.float() for p_ in parts).to(dt)
+            y = parts[rank].to(dev)
+            ar(y)
+            assert torch.equal(y.cpu(), want), (rep, numel, dt)
+        y = torch.ones(4096, dtype=torch.bfloat16, device=dev)
+        graph = torch.cuda.CUDAGraph()
+        side = torch.cuda.Stream()
+        side.wait_stream(torch.cuda.current_stream())
+        with torch.cuda.stream(side):
+            ar(y)
+        torch.cuda.current_stream().wait_stream(side)
+        torch.cuda.synchronize()
+        with torch.cuda.graph(graph):
+            ar(y, pdl=True)
+        for _ in range(3):
+            graph.replay()
+        torch.cuda.synchronize()
+        assert torch.equal(y.cpu(), torch.full((4096,), float(world ** 4), dtype=torch.bfloat16))
+        ar.status()
+        row2 = tp.RowParallelBitLinear(codes, scale, k, n, input_is_parallel=False, reduce_dtype=torch.float32, all_reduce=ar)
+        y2 = row2(x.to(dev), out_dtype=torch.float32)
+        assert float((y2 - full).abs().max() / full.abs().max()) < 2e-2
+        gathered = [torch.empty_like(y2) for _ in range(world)]
+        dist.all_gather(gathered, y2)
+        assert all(torch.equal(gathered[0], t_) for t_ in gathered)  # identical bits on every rank
+        ar.status()
         wf.device_status()
         results[rank] = "ok"
     finally:

@@ -68,6 +68,12 @@ _SIGNATURES = {
     "wf_add_rmsnorm_bf16": (_int, [_p, _p, _p, _p, _i64, _i64, _f32, _u32, _p]),
     "wf_rope_kv_bf16": (_int, [_p, _p, _p, _p, _p, _p, _p, _p, _i64, _int, _int, _int, _int, _u32, _p]),
     "wf_act_mul_bf16": (_int, [_p, _p, _p, _i64, _int, _u32, _p]),
+    "wf_ar_handle_bytes": (_int, []),
+    "wf_ar_init": (_int, [_int, _int, _sz, C.POINTER(C.c_void_p), _p]),
+    "wf_ar_connect": (_int, [_p, _p]),
+    "wf_ar_allreduce": (_int, [_p, _p, _p, _i64, _int, _u32, _p]),
+    "wf_ar_status": (_int, [_p, C.POINTER(C.c_int)]),
+    "wf_ar_destroy": (_int, [_p]),
     "wf_bitlinear_prefill_batched": (_int, [_p, _int, _i64, _p, _int, _p, _i64, _p, _int, _i64, _p, _i64, _i64, _i64, _i64, _f32,
                                             _p, _sz, _p]),
 }

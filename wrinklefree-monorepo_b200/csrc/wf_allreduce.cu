@@ -1,0 +1,254 @@
+// One-shot all-reduce over peer memory for the small tensors that follow a row-parallel projection in the decode
+// step (hidden x tokens: 8 KB for one token of the 8B shape).  At that size a library all-reduce is latency: several
+// launches and protocol round trips.  Here every rank
+//   1. copies its partial tensor into its own exported buffer (two slots, alternating by step),
+//   2. stores the step number into a flag word of its own INSIDE EVERY PEER'S buffer (after a system-scope fence),
+//   3. polls the flag words in its OWN buffer until every peer has published the step (bounded; local memory, so the
+//      polling crosses no link),
+//   4. reads all partial tensors through peer pointers (plain loads over NVLink, no multicast) and sums them in rank
+//      order in fp32, so every rank obtains bit-identical results.
+// Two slots are enough: a rank overwrites slot s & 1 at step s + 2 only after it has seen every peer's flag of step
+// s + 1, which a peer stores only after it has finished reading step s.
+// The buffers are plain cudaMalloc allocations exported with CUDA IPC handles (one process per GPU).
+#include <cuda_runtime.h>
+
+#include <cstdint>
+#include <cstring>
+#include <new>
+
+#include "wf_common.cuh"
+
+namespace wf {
+
+constexpr int AR_MAX_RANKS = 8;
+constexpr int AR_MAX_CTAS = 32;
+constexpr int AR_THREADS = 512;
+constexpr size_t AR_FLAG_BYTES = AR_MAX_CTAS * AR_MAX_RANKS * sizeof(unsigned);  // flags[cta][rank]
+constexpr size_t AR_HEADER = 4096;  // flags, step counter, ticket, status
+constexpr unsigned AR_SPIN_LIMIT = 1u << 22;
+
+struct ArPeers {
+    uint8_t* base[AR_MAX_RANKS];
+};
+
+struct ArCtx {
+    int world, rank, device;
+    size_t max_bytes;
+    uint8_t* local;
+    ArPeers peers;
+    bool connected;
+};
+
+__device__ __forceinline__ unsigned ld_acquire_sys(const unsigned* p) {
+    unsigned v;
+    asm volatile("ld.acquire.sys.global.u32 %0, [%1];\n" : "=r"(v) : "l"(p) : "memory");
+    return v;
+}
+__device__ __forceinline__ void st_release_sys(unsigned* p, unsigned v) {
+    asm volatile("st.release.sys.global.u32 [%0], %1;\n" ::"l"(p), "r"(v) : "memory");
+}
+__device__ __forceinline__ uint4 ld_peer16(const void* p) {  // another GPU's memory: never served from this SM's L1
+    uint4 v;
+    asm volatile("ld.relaxed.sys.global.v4.u32 {%0,%1,%2,%3}, [%4];\n" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "l"(p) : "memory");
+    return v;
+}
+
+template <int DT>
+__device__ __forceinline__ void accumulate8(const uint4& u, float (&acc)[8]) {
+    const uint32_t w[4] = {u.x, u.y, u.z, u.w};
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+        if constexpr (DT == WF_BF16) {
+            acc[2 * i] += __uint_as_float(w[i] << 16);
+            acc[2 * i + 1] += __uint_as_float(w[i] & 0xffff0000u);
+        } else {
+            const float2 v = __half22float2(*reinterpret_cast<const __half2*>(&w[i]));
+            acc[2 * i] += v.x;
+            acc[2 * i + 1] += v.y;
+        }
+    }
+}
+
+// header of a rank's buffer: flags[cta][rank] | step (at 2048) | ticket (2052) | status (2056)
+// n16: 16-byte chunks of the tensor; CTA c handles the chunks c, c + grid, ...
+template <int DT>
+__global__ void __launch_bounds__(AR_THREADS) allreduce_kernel(ArPeers peers, int world, int rank, size_t slot_bytes,
+                                                               const uint4* __restrict__ in, uint4* __restrict__ out, int64_t n16) {
+    asm volatile("griddepcontrol.launch_dependents;\n" ::: "memory");
+    uint8_t* mine = peers.base[rank];
+    unsigned* step_word = reinterpret_cast<unsigned*>(mine + 2048);
+    unsigned* ticket = reinterpret_cast<unsigned*>(mine + 2052);
+    unsigned* status = reinterpret_cast<unsigned*>(mine + 2056);
+    const int tid = threadIdx.x, cta = blockIdx.x;
+    asm volatile("griddepcontrol.wait;\n" ::: "memory");  // the partial tensor comes from the previous kernel
+    const unsigned step = *reinterpret_cast<volatile unsigned*>(step_word) + 1;
+    const size_t slot = AR_HEADER + (step & 1) * slot_bytes;
+
+    // 1. publish the partial tensor
+    uint4* my_slot = reinterpret_cast<uint4*>(mine + slot);
+    for (int64_t i = cta * static_cast<int64_t>(AR_THREADS) + tid; i < n16; i += static_cast<int64_t>(gridDim.x) * AR_THREADS)
+        my_slot[i] = in[i];
+    __threadfence_system();
+    __syncthreads();
+    // 2. tell every peer (and this rank itself)
+    if (tid < world) st_release_sys(reinterpret_cast<unsigned*>(peers.base[tid]) + cta * AR_MAX_RANKS + rank, step);
+    // 3. wait for every peer's flag of this step, in this rank's own memory
+    if (tid < world) {
+        const unsigned* f = reinterpret_cast<const unsigned*>(mine) + cta * AR_MAX_RANKS + tid;
+        unsigned it = 0;
+        // flags only grow; a difference below 2^31 means "not yet there"
+        while (static_cast<int>(ld_acquire_sys(f) - step) < 0) {
+            if (++it > AR_SPIN_LIMIT) {
+                atomicExch(status, static_cast<unsigned>(WF_E_LIMIT));
+                break;
+            }
+            __nanosleep(20);
+        }
+    }
+    __syncthreads();
+    // 4. sum in rank order
+    for (int64_t i = cta * static_cast<int64_t>(AR_THREADS) + tid; i < n16; i += static_cast<int64_t>(gridDim.x) * AR_THREADS) {
+        if constexpr (DT == WF_F32) {
+            float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
+            for (int r = 0; r < world; ++r) {
+                const uint4 u = ld_peer16(peers.base[r] + slot + i * 16);
+                acc.x += __uint_as_float(u.x); acc.y += __uint_as_float(u.y); acc.z += __uint_as_float(u.z); acc.w += __uint_as_float(u.w);
+            }
+            out[i] = make_uint4(__float_as_uint(acc.x), __float_as_uint(acc.y), __float_as_uint(acc.z), __float_as_uint(acc.w));
+        } else {
+            float acc[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
+            for (int r = 0; r < world; ++r) accumulate8<DT>(ld_peer16(peers.base[r] + slot + i * 16), acc);
+            uint32_t o[4];
+#pragma unroll
+            for (int j = 0; j < 4; ++j) {
+                if constexpr (DT == WF_BF16) {
+                    const __nv_bfloat162 t2 = __floats2bfloat162_rn(acc[2 * j], acc[2 * j + 1]);
+                    o[j] = *reinterpret_cast<const uint32_t*>(&t2);
+                } else {
+                    const __half2 t2 = __floats2half2_rn(acc[2 * j], acc[2 * j + 1]);
+                    o[j] = *reinterpret_cast<const uint32_t*>(&t2);
+                }
+            }
+            out[i] = make_uint4(o[0], o[1], o[2], o[3]);
+        }
+    }
+    // 5. the last CTA to finish advances the step
+    __syncthreads();
+    if (tid == 0) {
+        __threadfence();
+        if (atomicAdd(ticket, 1u) == gridDim.x - 1) {
+            *ticket = 0;
+            *reinterpret_cast<volatile unsigned*>(step_word) = step;
+        }
+    }
+}
+
+}  // namespace wf
+
+using namespace wf;
+
+extern "C" int wf_ar_handle_bytes(void) { return static_cast<int>(sizeof(cudaIpcMemHandle_t)); }
+
+extern "C" int wf_ar_init(int world, int rank, size_t max_bytes, void** ctx_out, unsigned char* handle_out) {
+    WF_REQUIRE(ctx_out && handle_out, "wf_ar_init: null pointer");
+    WF_REQUIRE(world >= 2 && world <= AR_MAX_RANKS && rank >= 0 && rank < world, "wf_ar_init: 2..%d ranks", AR_MAX_RANKS);
+    WF_REQUIRE(max_bytes >= 16 && max_bytes % 16 == 0 && max_bytes <= (64u << 20), "wf_ar_init: max_bytes must be a multiple of 16, at most 64 MiB");
+    if (int rc = require_device()) return rc;
+    ArCtx* c = new (std::nothrow) ArCtx();
+    WF_REQUIRE(c, "wf_ar_init: out of host memory");
+    c->world = world; c->rank = rank; c->max_bytes = max_bytes; c->connected = false;
+    WF_CUDA(cudaGetDevice(&c->device));
+    const size_t total = AR_HEADER + 2 * max_bytes;
+    void* p = nullptr;
+    cudaError_t e = cudaMalloc(&p, total);
+    if (e != cudaSuccess) {
+        delete c;
+        return cuda_fail(e, "cudaMalloc of the exchange buffer");
+    }
+    c->local = static_cast<uint8_t*>(p);
+    e = cudaMemset(p, 0, AR_HEADER);
+    cudaIpcMemHandle_t h;
+    if (e == cudaSuccess) e = cudaIpcGetMemHandle(&h, p);
+    if (e != cudaSuccess) {
+        cudaFree(p);
+        delete c;
+        return cuda_fail(e, "cudaIpcGetMemHandle");
+    }
+    std::memcpy(handle_out, &h, sizeof(h));
+    for (int r = 0; r < AR_MAX_RANKS; ++r) c->peers.base[r] = nullptr;
+    c->peers.base[rank] = c->local;
+    *ctx_out = c;
+    return WF_OK;
+}
+
+// handles: world x wf_ar_handle_bytes() bytes, entry r = the handle that rank r obtained from wf_ar_init
+extern "C" int wf_ar_connect(void* ctx, const unsigned char* handles) {
+    ArCtx* c = static_cast<ArCtx*>(ctx);
+    WF_REQUIRE(c && handles, "wf_ar_connect: null pointer");
+    WF_REQUIRE(!c->connected, "wf_ar_connect: already connected");
+    for (int r = 0; r < c->world; ++r) {
+        if (r == c->rank) continue;
+        cudaIpcMemHandle_t h;
+        std::memcpy(&h, handles + static_cast<size_t>(r) * sizeof(h), sizeof(h));
+        void* p = nullptr;
+        WF_CUDA(cudaIpcOpenMemHandle(&p, h, cudaIpcMemLazyEnablePeerAccess));
+        c->peers.base[r] = static_cast<uint8_t*>(p);
+    }
+    c->connected = true;
+    return WF_OK;
+}
+
+extern "C" int wf_ar_allreduce(void* ctx, const void* in, void* out, int64_t n, int dtype, unsigned flags, void* stream) {
+    ArCtx* c = static_cast<ArCtx*>(ctx);
+    WF_REQUIRE(c && in && out, "wf_ar_allreduce: null pointer");
+    WF_REQUIRE(c->connected, "wf_ar_allreduce: wf_ar_connect has not run");
+    WF_REQUIRE(dtype == WF_BF16 || dtype == WF_F16 || dtype == WF_F32, "wf_ar_allreduce: bf16, f16 or f32");
+    const int64_t bytes = n * (dtype == WF_F32 ? 4 : 2);
+    WF_REQUIRE(n > 0 && bytes % 16 == 0 && static_cast<size_t>(bytes) <= c->max_bytes,
+               "wf_ar_allreduce: %lld bytes; need a multiple of 16, at most %zu", static_cast<long long>(bytes), c->max_bytes);
+    WF_REQUIRE((reinterpret_cast<uintptr_t>(in) | reinterpret_cast<uintptr_t>(out)) % 16 == 0, "wf_ar_allreduce: tensors must be 16-byte aligned");
+    const int64_t n16 = bytes / 16;
+    int64_t grid = (n16 + AR_THREADS - 1) / AR_THREADS;
+    if (grid > AR_MAX_CTAS) grid = AR_MAX_CTAS;
+    cudaLaunchConfig_t lc = {};
+    lc.gridDim = dim3(static_cast<unsigned>(grid));
+    lc.blockDim = dim3(AR_THREADS);
+    lc.stream = static_cast<cudaStream_t>(stream);
+    cudaLaunchAttribute attr[1];
+    if (flags & WF_FLAG_PDL) {
+        attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+        attr[0].val.programmaticStreamSerializationAllowed = 1;
+        lc.attrs = attr;
+        lc.numAttrs = 1;
+    }
+    const uint4* in4 = static_cast<const uint4*>(in);
+    uint4* out4 = static_cast<uint4*>(out);
+    if (dtype == WF_BF16)
+        WF_CUDA(cudaLaunchKernelEx(&lc, allreduce_kernel<WF_BF16>, c->peers, c->world, c->rank, c->max_bytes, in4, out4, n16));
+    else if (dtype == WF_F16)
+        WF_CUDA(cudaLaunchKernelEx(&lc, allreduce_kernel<WF_F16>, c->peers, c->world, c->rank, c->max_bytes, in4, out4, n16));
+    else
+        WF_CUDA(cudaLaunchKernelEx(&lc, allreduce_kernel<WF_F32>, c->peers, c->world, c->rank, c->max_bytes, in4, out4, n16));
+    return WF_OK;
+}
+
+// 0 = no wait ran out; WF_E_LIMIT otherwise (the word is cleared)
+extern "C" int wf_ar_status(void* ctx, int* out) {
+    ArCtx* c = static_cast<ArCtx*>(ctx);
+    WF_REQUIRE(c && out, "wf_ar_status: null pointer");
+    unsigned v = 0;
+    WF_CUDA(cudaMemcpy(&v, c->local + 2056, sizeof(v), cudaMemcpyDeviceToHost));
+    if (v) WF_CUDA(cudaMemset(c->local + 2056, 0, sizeof(v)));
+    *out = static_cast<int>(v);
+    return WF_OK;
+}
+
+extern "C" int wf_ar_destroy(void* ctx) {
+    ArCtx* c = static_cast<ArCtx*>(ctx);
+    if (!c) return WF_OK;
+    for (int r = 0; r < c->world; ++r)
+        if (r != c->rank && c->peers.base[r]) cudaIpcCloseMemHandle(c->peers.base[r]);
+    cudaFree(c->local);
+    delete c;
+    return WF_OK;
+}

@@ -59,6 +59,7 @@ class TernaryDecoder:
     def __init__(self, cfg: DecoderConfig, batch: int, max_ctx: int, device, group=None, seed: int = 0,
                  dtype: torch.dtype = torch.bfloat16):
         self.cfg, self.B, self.T, self.dev, self.dtype, self.group = cfg, batch, max_ctx, device, dtype, group
+        self._oneshot = None  # peer-memory all-reduce for the row-parallel projections (set up at the first step)
         self.tp = dist.get_world_size(group) if (group is not None or dist.is_initialized()) else 1
         self.rank = dist.get_rank(group) if (group is not None or dist.is_initialized()) else 0
         if cfg.n_kv % self.tp or cfg.n_q % self.tp:
@@ -133,7 +134,9 @@ class TernaryDecoder:
 
     def _allreduce(self, y):
         if self.tp > 1:
-            dist.all_reduce(y, group=self.group)
+            if self._oneshot is None:
+                self._oneshot = tpmod.OneShotAllReduce(self.group, max_bytes=1 << 20)
+            self._oneshot(y, pdl=True)
         return y
 
     def _decode_step(self):

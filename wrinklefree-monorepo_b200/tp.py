@@ -25,6 +25,62 @@ from . import _lib as L
 from . import ops
 
 
+class OneShotAllReduce:
+    """Sum over the ranks of a process group for small CUDA tensors, by a kernel of this library that reads the
+    partial tensors through peer memory (one process per GPU on one node).  It stands where the reference's
+    row-parallel layers call the library all-reduce (linear.py:1419-1420); the sum runs in rank order in fp32, so
+    all ranks obtain identical bits.  Tensors above `max_bytes`, of other dtypes or not 16-byte sized fall back to
+    `dist.all_reduce`.  Set up collectively: every rank of `group` constructs it at the same point."""
+
+    _DT = {torch.bfloat16: L.WF_BF16, torch.float16: L.WF_F16, torch.float32: L.WF_F32}
+
+    def __init__(self, group=None, max_bytes: int = 1 << 20):
+        import ctypes as C
+
+        self.group = group
+        self.world, self.rank = dist.get_world_size(group), dist.get_rank(group)
+        self.max_bytes = max_bytes
+        self._ctx = None
+        if self.world < 2 or self.world > 8 or not torch.cuda.is_available():
+            return
+        lib = L.lib()
+        hb = lib.wf_ar_handle_bytes()
+        handle = (C.c_ubyte * hb)()
+        ctx = C.c_void_p()
+        L.check(lib.wf_ar_init(self.world, self.rank, max_bytes, C.byref(ctx), handle), "wf_ar_init")
+        gathered = [None] * self.world
+        dist.all_gather_object(gathered, bytes(handle), group=group)
+        blob = b"".join(gathered)
+        buf = (C.c_ubyte * len(blob)).from_buffer_copy(blob)
+        L.check(lib.wf_ar_connect(ctx, buf), "wf_ar_connect")
+        dist.barrier(group=group)  # every rank has mapped every buffer before the first use
+        self._ctx = ctx
+
+    def __call__(self, y: torch.Tensor, pdl: bool = False) -> torch.Tensor:
+        """In-place sum of y over the ranks."""
+        nbytes = y.numel() * y.element_size()
+        if (self._ctx is None or y.dtype not in self._DT or not y.is_contiguous() or nbytes > self.max_bytes or nbytes % 16
+                or y.data_ptr() % 16):
+            if self.world > 1:
+                dist.all_reduce(y, op=dist.ReduceOp.SUM, group=self.group)
+            return y
+        with torch.cuda.device(y.device):
+            L.check(L.lib().wf_ar_allreduce(self._ctx, y.data_ptr(), y.data_ptr(), y.numel(), self._DT[y.dtype],
+                                            L.FLAG_PDL if pdl else 0, torch.cuda.current_stream().cuda_stream), "wf_ar_allreduce")
+        return y
+
+    def status(self) -> None:
+        """Raises if a bounded wait for a peer ran out since the last call."""
+        import ctypes as C
+
+        if self._ctx is None:
+            return
+        v = C.c_int(0)
+        L.check(L.lib().wf_ar_status(self._ctx, C.byref(v)), "wf_ar_status")
+        if v.value:
+            raise RuntimeError("one-shot all-reduce: a wait for a peer ran out (a rank did not take part)")
+
+
 def shard_bounds(total: int, parts: int, align: int) -> List[Tuple[int, int]]:
     """Splits [0, total) into `parts` contiguous ranges whose sizes are multiples of `align`
     and differ by at most one unit (the first ranges take the larger share)."""
@@ -96,8 +152,10 @@ class RowParallelBitLinear(_ParallelBase):
 
     def __init__(self, codes_full: torch.Tensor, w_scale, in_features: int, out_features: int, group=None,
                  bias: Optional[torch.Tensor] = None, input_is_parallel: bool = True, layout: int = L.LAYOUT_WF16,
-                 reduce_dtype: Optional[torch.dtype] = None, linear_fn: Optional[Callable] = None):
+                 reduce_dtype: Optional[torch.dtype] = None, linear_fn: Optional[Callable] = None,
+                 all_reduce: Optional[Callable] = None):
         super().__init__(group, linear_fn)
+        self.all_reduce = all_reduce  # e.g. a OneShotAllReduce of the same group; default: dist.all_reduce
         self.in_features, self.out_features, self.layout = in_features, out_features, layout
         self.input_is_parallel, self.reduce_dtype = input_is_parallel, reduce_dtype
         self.bounds = shard_bounds(in_features, self.tp_size, 128 if layout == L.LAYOUT_I2S else 64)
@@ -114,7 +172,10 @@ class RowParallelBitLinear(_ParallelBase):
         red = self.reduce_dtype or out_dtype
         y = self._linear(x, self.codes, self.w_scale, bias=self.bias, layout=self.layout, out_dtype=red, **kw)
         if self.tp_size > 1:
-            dist.all_reduce(y, op=dist.ReduceOp.SUM, group=self.group)
+            if self.all_reduce is not None:
+                self.all_reduce(y)
+            else:
+                dist.all_reduce(y, op=dist.ReduceOp.SUM, group=self.group)
         return y if red == out_dtype else y.to(out_dtype)
 
 
