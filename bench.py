@@ -405,7 +405,9 @@ def main():
             os.close(saved)
 
     if args.decoder_only:
-        print(json.dumps({"decode_tok_s": decoder_section(wf, torch, device, world, args.decoder_full)}))
+        res = decoder_section(wf, torch, device, world, args.decoder_full)
+        if rank == 0:
+            print(json.dumps({"decode_tok_s": res}))
         return
     if args.prefill_only:
         peaks, _ = measured_peaks()

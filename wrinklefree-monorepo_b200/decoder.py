@@ -135,7 +135,7 @@ class TernaryDecoder:
     def _allreduce(self, y):
         if self.tp > 1:
             if self._oneshot is None:
-                self._oneshot = tpmod.OneShotAllReduce(self.group, max_bytes=1 << 20)
+                self._oneshot = tpmod.OneShotAllReduce(self.group, max_bytes=64 << 10)  # measured: NCCL is faster from 256 KB on
             self._oneshot(y, pdl=True)
         return y
 
