@@ -67,6 +67,15 @@ def _worker(rank, world, port, results):
         ys = [torch.empty_like(y) for _ in range(world)]
         dist.all_gather(ys, y)
         assert torch.equal(ys[0], ys[1])
+        # the peer-memory all-reduce needs GPUs: without them its wrapper falls back to the group's all_reduce, also
+        # as the `all_reduce` hook of a row-parallel layer
+        ar = tp.OneShotAllReduce()
+        v = torch.full((8,), float(rank + 1))
+        assert torch.equal(ar(v), torch.full((8,), 3.0))
+        ar.status()
+        row2 = tp.RowParallelBitLinear(codes, float(s_w), k, n, bias=bias, input_is_parallel=False, linear_fn=oracle_linear,
+                                       all_reduce=ar)
+        assert torch.equal(row2(x), y)
         results[rank] = "ok"
     finally:
         dist.destroy_process_group()
