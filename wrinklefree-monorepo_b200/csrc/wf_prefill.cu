@@ -11,7 +11,7 @@
 //   * warp 14 (one lane): TMA of the int8 token tile (4 swizzle atoms of NTOK x 128 bytes, the MMA's B operand);
 //   * warps 2-5 / 6-9: two expansion groups that alternate stages; thread = weight row: 8 x ld.shared.v4, mask + shift
 //     to one int8 per byte, 4 x tcgen05.st of 32 columns into a ring of tensor-memory stages;
-//   * warp 1 (one lane): 16 x tcgen05.mma.kind::i8 (M = 128, N = NTOK, K = 32) with the A operand FROM TENSOR MEMORY,
+//   * warp 1 (one lane): 16 x tcgen05.mma.cta_group::1.kind::i8 (M = 128, N = NTOK, K = 32), A operand FROM TENSOR MEMORY,
 //     one commit per stage; two accumulators, so the epilogue of a tile runs under the next tile's MMAs;
 //   * warps 10-13 (and 15-18): epilogue, thread = weight row: tcgen05.ld, integer correction, fp32 rescale, store.
 // Every mbarrier wait is bounded.
@@ -95,11 +95,20 @@ constexpr size_t sm_smem() {  // more than half of an SM's shared memory: two of
 static_assert(sm_smem<16>() > 114 * 1024 && sm_smem<64>() <= 227 * 1024 && sm_smem<128>() <= 227 * 1024, "shared memory");
 static_assert(sm_acc_cols<64>() + sm_xs<64>() * SM_A_COLS <= 512 && sm_acc_cols<128>() + sm_xs<128>() * SM_A_COLS <= 512, "tensor memory");
 
-__device__ __forceinline__ void mma_i8_ts(uint32_t d_tmem, uint32_t a_tmem, uint64_t b_desc, uint32_t idesc, uint32_t accumulate) {
+// The four MMAs of one 128-byte swizzle atom of K in one block of PTX: A advances by 8 tensor-memory columns, B by 32
+// bytes (2 in descriptor units) per step.  The issuing thread is the pipeline's critical path for few tokens, so the
+// address arithmetic is kept out of the compiler's hands and the predicate is set once.
+__device__ __forceinline__ void mma_i8_ts_x4(uint32_t d_tmem, uint32_t a_tmem, uint64_t b_desc, uint32_t idesc, uint32_t accumulate_first) {
     asm volatile(
-        "{\n .reg .pred p;\n setp.ne.b32 p, %4, 0;\n"
-        " tcgen05.mma.cta_group::1.kind::i8 [%0], [%1], %2, %3, {%5, %5, %5, %5}, p;\n}\n" ::"r"(d_tmem),
-        "r"(a_tmem), "l"(b_desc), "r"(idesc), "r"(accumulate), "r"(0u)
+        "{\n .reg .pred p, q;\n .reg .b32 a1, a2, a3;\n .reg .b64 b1, b2, b3;\n"
+        " setp.ne.b32 p, %4, 0;\n setp.eq.b32 q, %5, %5;\n"
+        " add.u32 a1, %1, 8;\n add.u32 a2, %1, 16;\n add.u32 a3, %1, 24;\n"
+        " add.u64 b1, %2, 2;\n add.u64 b2, %2, 4;\n add.u64 b3, %2, 6;\n"
+        " tcgen05.mma.cta_group::1.kind::i8 [%0], [%1], %2, %3, {%5, %5, %5, %5}, p;\n"
+        " tcgen05.mma.cta_group::1.kind::i8 [%0], [a1], b1, %3, {%5, %5, %5, %5}, q;\n"
+        " tcgen05.mma.cta_group::1.kind::i8 [%0], [a2], b2, %3, {%5, %5, %5, %5}, q;\n"
+        " tcgen05.mma.cta_group::1.kind::i8 [%0], [a3], b3, %3, {%5, %5, %5, %5}, q;\n}\n" ::"r"(d_tmem),
+        "r"(a_tmem), "l"(b_desc), "r"(idesc), "r"(accumulate_first), "r"(0u)
         : "memory");
 }
 __device__ __forceinline__ void tmem_st32(uint32_t addr, const uint32_t (&v)[32]) {
@@ -220,6 +229,12 @@ __global__ void __launch_bounds__(SM_THREADS, 1)
             // D = s32, A = unsigned 8-bit (codes, from tensor memory), B = signed 8-bit (tokens, K-major), N = NTOK, M = 128
             const uint32_t idesc = (2u << 4) | (0u << 7) | (1u << 10) | (static_cast<uint32_t>(NTOK >> 3) << 17) |
                                    (static_cast<uint32_t>(SM_BM >> 4) << 24);
+            // operand descriptors of every (stage, atom), fixed for the whole kernel
+            uint64_t bdesc[SM_XS][SM_PK];
+#pragma unroll
+            for (int s = 0; s < SM_XS; ++s)
+#pragma unroll
+                for (int j = 0; j < SM_PK; ++j) bdesc[s][j] = smem_desc_sw128(smem_u32(x_ring + s * X_BYTES + j * X_ATOM));
             int sit = 0, nt = 0;
             for (int t = blockIdx.x; t < total_tiles; t += gridDim.x, ++nt) {
                 const int a = nt & 1;
@@ -231,11 +246,16 @@ __global__ void __launch_bounds__(SM_THREADS, 1)
                     mbar_wait(&x_full[s], (sit / SM_XS) & 1, poisoned);
                     mbar_wait(&a_full[s], (sit / SM_XS) & 1, poisoned);
                     tc_fence_after();
-                    const uint32_t xs = smem_u32(x_ring + s * X_BYTES);
+                    const uint32_t a_stage = tmem_a + s * SM_A_COLS;
+                    // sixteen MMAs of 32 values of K: four per swizzle atom (the ring index is resolved by a switch so
+                    // that the descriptors stay in registers)
 #pragma unroll
-                    for (int kk = 0; kk < SM_PK * SM_BK / 32; ++kk) {  // 32 values of K per MMA
-                        const uint64_t b_desc = smem_desc_sw128(xs + (kk >> 2) * X_ATOM) + 2 * (kk & 3);
-                        mma_i8_ts(d_tmem, tmem_a + s * SM_A_COLS + kk * 8, b_desc, idesc, (g | kk) ? 1u : 0u);
+                    for (int ss = 0; ss < SM_XS; ++ss) {
+                        if (ss == s) {
+#pragma unroll
+                            for (int j = 0; j < SM_PK; ++j)
+                                mma_i8_ts_x4(d_tmem, a_stage + j * 32, bdesc[ss][j], idesc, (g | j) ? 1u : 0u);
+                        }
                     }
                     tc_commit(&st_free[s]);
                 }
