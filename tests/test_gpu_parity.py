@@ -395,6 +395,27 @@ def test_full_size_sweep_properties(wf, oracle_c, n, k, m):
     assert torch.equal(y, y2)
 
 
+@pytest.mark.parametrize("m", [1, 8, 20])
+def test_decode_many_items_per_cta_equals_contraction(wf, m):
+    """A single tall matrix (more 16-row items per CTA than ring stages) and a gate/up-like pair on shared tokens: the
+    decode kernel lets every warp take whole items there; results must equal the tensor-core path bit for bit."""
+    g = torch.Generator().manual_seed(900 + m)
+    n, k = 65536, 512  # 4096 items: about 28 per CTA, more than the ring has stages
+    w = torch.randn(n, k, generator=g) * 0.02
+    x = gi.with_outliers(torch.randn(m, k, generator=g), seed=4).bfloat16().to(DEV)
+    codes, scale = wf.pack_ternary(w.to(DEV))
+    y1, a1 = wf.bitlinear(x, codes, scale, want_acc=True, path="decode")
+    y2, a2 = wf.bitlinear(x, codes, scale, want_acc=True, path="prefill")
+    assert torch.equal(a1, a2) and torch.equal(y1, y2)
+    half = n // 2
+    grp = wf.DecodeGroup([dict(x=x, codes=codes[:half].contiguous(), w_scale=scale, want_acc=True),
+                          dict(x=x, codes=codes[half:].contiguous(), w_scale=scale, want_acc=True)])
+    for rep in range(2):
+        outs = grp.run(pdl=bool(rep))
+        assert torch.equal(torch.cat(grp.accs, 1), a2) and torch.equal(torch.cat(outs, 1), y2)
+    wf.device_status()
+
+
 # ---------------------------------------------------------------- grouped launches
 def test_grouped_decode_matches_single_calls(wf, oracle_c):
     """q/k/v-like and mixed-shape groups: one persistent launch, results identical to the oracle."""

@@ -62,6 +62,7 @@ struct DecodeCfg {
     int nbuf;         // streaming form: activation buffers (2 when they are small, else 1)
     int cpp;          // streaming form: CTAs per problem when ranges are aligned to problems (0: contiguous split)
     int hdr_off;      // two cached descriptor heads
+    int wide;         // shared form: every consumer warp takes whole items (all problems read the same x, several items per CTA)
     int items_q, items_r;  // total_items = grid * items_q + items_r
     int uniform_items;     // streaming form: > 0 when all problems have equal M, N, K and layout: items of each
     int x_early;           // ... and problem i reads x at x_base + i * x_stride (bytes), without x_scale
@@ -452,7 +453,7 @@ __global__ void __launch_bounds__(DEC_THREADS, 1)
     if (tid == 0) {
         for (int s = 0; s < cfg.stages; ++s) {
             mbar_init(&full[s], 1);
-            mbar_init(&empty[s], NW);
+            mbar_init(&empty[s], cfg.wide ? 1 : NW);
         }
         *poisoned = 0;
         asm volatile("fence.mbarrier_init.release.cluster;\n" ::: "memory");
@@ -519,6 +520,72 @@ __global__ void __launch_bounds__(DEC_THREADS, 1)
     // x may be produced by the previous kernel of the stream
     asm volatile("griddepcontrol.wait;\n" ::: "memory");
     consumer_sync();
+
+    if (cfg.wide) {
+        // Every problem of the group reads the same tokens and a CTA has several items: x is quantized once, then
+        // each warp takes whole items (all of K, epilogue from its own accumulators) and nothing synchronises the CTA
+        // any more.  With all 16 warps on one item at a time, the two barriers and the shared-memory reduction per
+        // item (about 0.7 us) made a 29 MB gate/up launch compute-latency-bound.
+        if (beg >= end) return;
+        const int m_all = min(cfg.MTA, p.M);
+        quantize_tokens<XDT>(p, cfg.MTA, 0, m_all, s_act, s_inv, s_rowsum, s_maxbits);
+        const uint32_t act0 = smem_u32(s_act);
+        const int KB = (p.K + 511) >> 9;
+        // Warp w owns stage w and takes the items w, w + W, ... (W = stages <= 16 warps): a barrier is then always waited
+        // on by the same warp, phase after phase.  (A warp that waits for a later phase of a barrier whose current phase
+        // has not completed would pass at once: the parity of the wait only tells two consecutive phases apart.)
+        const int W = cfg.stages;
+        for (int n = warp; warp < W && n < end - beg; n += W) {
+            int local;
+            const int pi = locate_problem(probs, cfg.P, beg + n, s_ib, cfg.ib_cap, local);
+            const wf_problem* hp = pi == hdr_p ? &p : &probs[pi];
+            const int my_row = local * 16;  // one pass of tokens: the item index is the row item
+            const int N = hp->N, y_dtype = hp->y_dtype, bias_dtype = hp->bias_dtype;
+            const float s_w = hp->w_scale ? __ldg(hp->w_scale) : hp->w_scale_host;
+            void* const y = hp->y;
+            const void* const bias = hp->bias;
+            int32_t* const acc_out = hp->acc_out;
+            const int64_t ldy = hp->ldy;
+            const int stage = warp;
+            mbar_wait(&full[stage], (n / W) & 1, poisoned);
+            int acc[NT][FOURACC ? 4 : 1][4];
+#pragma unroll
+            for (int a = 0; a < NT; ++a)
+#pragma unroll
+                for (int b = 0; b < (FOURACC ? 4 : 1); ++b)
+#pragma unroll
+                    for (int c = 0; c < 4; ++c) acc[a][b][c] = 0;
+            const uint32_t w_r0 = smem_u32(s_stage) + stage * cfg.stage_bytes + g * 128;
+#pragma unroll 1
+            for (int kb = 0; kb < KB; ++kb)
+                compute_unit<NT, FOURACC>(w_r0 + kb * TILE_BYTES, w_r0 + kb * TILE_BYTES + 1024, act0 + kb * cfg.MTA * TOK_STRIDE, m_all, g, t,
+                                          acc);
+            __syncwarp();
+            if (lane == 0) mbar_arrive(&empty[stage]);  // the stage has been read
+            const int row_a = my_row + g, row_b = row_a + 8;
+#pragma unroll
+            for (int nt = 0; nt < NT; ++nt) {
+#pragma unroll
+                for (int c = 0; c < 4; ++c) {
+                    int v;
+                    if constexpr (FOURACC)
+                        v = acc[nt][0][c] + (acc[nt][1][c] >> 2) + (acc[nt][2][c] >> 4) + (acc[nt][3][c] >> 6);
+                    else
+                        v = acc[nt][0][c];
+                    const int tok = nt * 8 + 2 * t + (c & 1);
+                    const int nrow = (c & 2) ? row_b : row_a;
+                    if (tok < m_all && nrow < N) {
+                        const int a = v - s_rowsum[tok];
+                        float out = rescale(a, s_inv[tok], s_w);
+                        if (bias) out = __fadd_rn(out, load1_rt(bias, bias_dtype, nrow));
+                        store1_rt(y, y_dtype, static_cast<int64_t>(tok) * ldy + nrow, out);
+                        if (acc_out) acc_out[static_cast<int64_t>(tok) * N + nrow] = a;
+                    }
+                }
+            }
+        }
+        return;
+    }
 
     for (int it = beg, n = 0; it < end; ++it, ++n) {
         int local;
@@ -1018,6 +1085,16 @@ static int encode_maps(wf_problem& q) {
     return WF_OK;
 }
 
+// All problems read the same tokens in one pass (q/k/v, gate/up, or a single problem): one quantization serves them all.
+static bool shares_x(const wf_problem* probs, int P, int MTA) {
+    if (probs[0].M > MTA || probs[0].M > 8) return false;  // measured with up to 8 tokens (one token tile)
+    for (int i = 1; i < P; ++i)
+        if (probs[i].x != probs[0].x || probs[i].x_scale != probs[0].x_scale || probs[i].ldx != probs[0].ldx || probs[i].M != probs[0].M ||
+            probs[i].K != probs[0].K || probs[i].layout != probs[0].layout || probs[i].eps != probs[0].eps)
+            return false;
+    return true;
+}
+
 // Chooses the token tile, the item size and the ring depth for a group, and fills the item fields.
 static int plan_group(wf_problem* probs, int P, GroupPlan& g, bool write_fields) {
     int Kmax = 0, Mmax = 0;
@@ -1071,6 +1148,8 @@ static int plan_group(wf_problem* probs, int P, GroupPlan& g, bool write_fields)
     };
     while (RI > 1 && count_items(RI) < 4LL * sms) RI >>= 1;
     while (RI > 1 && fixed_bytes(NT, RI) + act + 2u * 16 * RI * pitch > SMEM_MAX) RI >>= 1;
+    // several 16-row items per CTA on shared tokens: every warp takes whole items (see the kernel), items of 16 rows
+    if (!g.decoupled && shares_x(probs, P, g.MTA) && count_items(1) >= 3LL * sms) RI = 1;
     g.RI = RI;
     g.stage_bytes = g.decoupled ? static_cast<int>(seg_stage) : 16 * RI * pitch;
     g.act_off = static_cast<int>(fixed_bytes(NT, RI));
@@ -1172,6 +1251,7 @@ static int run_group(const char* who, const wf_problem* dev, wf_problem* host, i
     cfg.stage_bytes = g.stage_bytes; cfg.act_off = g.act_off; cfg.stage_off = g.stage_off; cfg.decoupled = g.decoupled; cfg.cpp = g.cpp; cfg.nbuf = g.nbuf;
     cfg.ib_cap = P < IB_CAP ? P : IB_CAP; cfg.ib_off = g.act_off - IB_CAP * 4 - 384; cfg.hdr_off = g.act_off - 384;
     cfg.x_ready = (flags & WF_FLAG_X_READY) ? 1 : 0;
+    cfg.wide = (!g.decoupled && g.RI == 1 && g.total_items >= 3LL * g.grid && shares_x(host, P, g.MTA)) ? 1 : 0;
     cfg.items_q = g.total_items / g.grid; cfg.items_r = g.total_items % g.grid;
     cfg.uniform_items = 0;
     if (g.decoupled) {
