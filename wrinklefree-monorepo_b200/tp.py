@@ -47,14 +47,22 @@ class OneShotAllReduce:
         hb = lib.wf_ar_handle_bytes()
         handle = (C.c_ubyte * hb)()
         ctx = C.c_void_p()
-        L.check(lib.wf_ar_init(self.world, self.rank, max_bytes, C.byref(ctx), handle), "wf_ar_init")
+        # Every step is collective: a rank whose set-up fails (no peer access, IPC not permitted) makes ALL ranks fall
+        # back to the group's all_reduce, so the ranks never disagree about the path.
+        ok = lib.wf_ar_init(self.world, self.rank, max_bytes, C.byref(ctx), handle) == 0
         gathered = [None] * self.world
-        dist.all_gather_object(gathered, bytes(handle), group=group)
-        blob = b"".join(gathered)
-        buf = (C.c_ubyte * len(blob)).from_buffer_copy(blob)
-        L.check(lib.wf_ar_connect(ctx, buf), "wf_ar_connect")
-        dist.barrier(group=group)  # every rank has mapped every buffer before the first use
-        self._ctx = ctx
+        dist.all_gather_object(gathered, bytes(handle) if ok else None, group=group)
+        ok = ok and all(h is not None for h in gathered)
+        if ok:
+            blob = b"".join(gathered)
+            buf = (C.c_ubyte * len(blob)).from_buffer_copy(blob)
+            ok = lib.wf_ar_connect(ctx, buf) == 0
+        flag = torch.tensor([1 if ok else 0], device="cuda")
+        dist.all_reduce(flag, op=dist.ReduceOp.MIN, group=group)  # also: every rank has mapped every buffer
+        if int(flag.item()) == 1:
+            self._ctx = ctx
+        elif ctx.value:
+            lib.wf_ar_destroy(ctx)
 
     def __call__(self, y: torch.Tensor, pdl: bool = False) -> torch.Tensor:
         """In-place sum of y over the ranks."""
