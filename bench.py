@@ -141,6 +141,9 @@ def build_workload(wf, torch, device, rank: int, world: int, layers_scale: float
             grp = None if batched else wf.DecodeGroup([dict(x=xd[li], codes=c, w_scale=s, out=y[li]) for li, (c, s) in enumerate(lay)])
             groups.append(dict(n=n, k=k, m=m, layers=lay, x_host=x.pin_memory(), x=xd, y=y, group=grp, reduce=row_parallel,
                                batched=batched, codes_stack=codes_stack, scales_stack=scales_stack))
+    # the stacks are independent: those on the streaming kernel go first, so that their launches chain (each starts
+    # while its predecessor drains), then those on the tensor-core contraction
+    groups.sort(key=lambda g_: g_["batched"])
     return groups
 
 
@@ -481,8 +484,15 @@ def main():
         for s_ in (s_in, s_run, s_out):
             torch.cuda.current_stream().wait_stream(s_)
 
+    # order of the stacks in the pipeline: the first copy-in and the last copy-out overlap with nothing, so the two
+    # smallest stacks go to the ends and the large ones to the middle
+    # (sizes of the unsharded stacks: every rank must walk the stacks in the same order, some carry an all-reduce)
+    by_size = sorted(range(len(groups)), key=lambda i_: (groups[i_]["m"] * (groups[i_]["n"] + groups[i_]["k"]) * len(groups[i_]["layers"]), i_))
+    e2e_order = by_size[:1] + by_size[2:][::-1] + by_size[1:2] if len(by_size) > 2 else by_size
+
     def e2e_step():
-        for i, (g, yh) in enumerate(zip(groups, y_host)):
+        for i in e2e_order:
+            g, yh = groups[i], y_host[i]
             with torch.cuda.stream(s_in):
                 if not state["first"]:
                     s_in.wait_event(ev_run[i])  # last step's launch has read x
