@@ -39,6 +39,10 @@ __global__ void __launch_bounds__(AQ_THREADS)
                            float* __restrict__ scale, int32_t* __restrict__ rowsum) {
     __shared__ float shf[AQ_THREADS / 32];
     __shared__ int shi[AQ_THREADS / 32];
+    // chained with a programmatic dependency: the next kernel may start (the contraction fetches its first weights
+    // meanwhile); x may come from the previous kernel and q may still be read by it, so everything else waits for it
+    asm volatile("griddepcontrol.launch_dependents;\n" ::: "memory");
+    asm volatile("griddepcontrol.wait;\n" ::: "memory");
     const int64_t m = blockIdx.x;
     float mx = 0.f;
     for (int64_t k = threadIdx.x * 8; k < K; k += AQ_THREADS * 8) {
@@ -131,10 +135,19 @@ extern "C" int wf_act_quant_i8(const void* x, int x_dtype, int64_t M, int64_t K,
     if (int rc = require_device()) return rc;
     cudaStream_t st = static_cast<cudaStream_t>(stream);
     if (mode == WF_ACT_PER_TOKEN) {
+        cudaLaunchConfig_t lc = {};
+        lc.gridDim = dim3(static_cast<unsigned>(M));
+        lc.blockDim = dim3(AQ_THREADS);
+        lc.stream = st;
+        cudaLaunchAttribute attr[1];
+        attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+        attr[0].val.programmaticStreamSerializationAllowed = 1;
+        lc.attrs = attr;
+        lc.numAttrs = 1;
         switch (x_dtype) {
-            case WF_F32: act_quant_token_kernel<WF_F32><<<(unsigned)M, AQ_THREADS, 0, st>>>(x, K, ldx, eps, q, scale, rowsum); break;
-            case WF_BF16: act_quant_token_kernel<WF_BF16><<<(unsigned)M, AQ_THREADS, 0, st>>>(x, K, ldx, eps, q, scale, rowsum); break;
-            default: act_quant_token_kernel<WF_F16><<<(unsigned)M, AQ_THREADS, 0, st>>>(x, K, ldx, eps, q, scale, rowsum); break;
+            case WF_F32: WF_CUDA(cudaLaunchKernelEx(&lc, act_quant_token_kernel<WF_F32>, x, K, ldx, eps, q, scale, rowsum)); break;
+            case WF_BF16: WF_CUDA(cudaLaunchKernelEx(&lc, act_quant_token_kernel<WF_BF16>, x, K, ldx, eps, q, scale, rowsum)); break;
+            default: WF_CUDA(cudaLaunchKernelEx(&lc, act_quant_token_kernel<WF_F16>, x, K, ldx, eps, q, scale, rowsum)); break;
         }
     } else if (mode == WF_ACT_PER_TENSOR) {
         WF_REQUIRE(x_dtype == WF_F32, "wf_act_quant_i8: per-tensor mode takes fp32 input (as the operator it replaces)");

@@ -159,6 +159,9 @@ __global__ void __launch_bounds__(SM_THREADS, 1)
     int* s_rowsum = reinterpret_cast<int*>(tmem_slot + 2);   // [NTOK] per-token constants of the epilogue's current token block
     float* s_inv = reinterpret_cast<float*>(s_rowsum + 128);  // [NTOK]
 
+    // chained with a programmatic dependency: the packed weights never depend on the previous kernel (normally the
+    // quantization of the tokens) and are requested at once; the token tiles and the per-token constants wait for it
+    asm volatile("griddepcontrol.launch_dependents;\n" ::: "memory");
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     // K is walked in stages of 512: one barrier round trip, one commit and sixteen MMAs per stage.  A last stage
     // that reaches past K is zero-filled by the TMA unit on both operands (code 0 times activation 0).
@@ -211,6 +214,7 @@ __global__ void __launch_bounds__(SM_THREADS, 1)
         }
     } else if (warp == 14) {
         if (lane == 0) {
+            asm volatile("griddepcontrol.wait;\n" ::: "memory");
             int sit = 0;
             for (int t = blockIdx.x; t < total_tiles; t += gridDim.x) {
                 const int row_x = (t / tiles_per_problem) * p.M + ((t % tiles_per_problem) / p.tiles_n) * NTOK;
@@ -316,6 +320,7 @@ __global__ void __launch_bounds__(SM_THREADS, 1)
         const int egrp = warp >= 15 ? 1 : 0;
         const int et = egrp * 128 + (warp - (egrp ? 15 : 10)) * 32 + lane;  // 0 .. 128 * EPI_GROUPS - 1
         const int col0 = egrp * EPI_COLS;  // this group's first token column
+        asm volatile("griddepcontrol.wait;\n" ::: "memory");
         int nt = 0, cur_zb = -1;
         for (int t = blockIdx.x; t < total_tiles; t += gridDim.x, ++nt) {
             const int z = t / tiles_per_problem, zb = t / p.tiles_n, tb = (t % tiles_per_problem) / p.tiles_n, rb = t % p.tiles_n;
@@ -528,16 +533,28 @@ static int prefill_impl(const char* who, const void* x, int x_dtype, int64_t ldx
         configured = true;
     }
     const long long tiles = static_cast<long long>(pp.tiles_m) * pp.tiles_n * pp.batch;
-    const unsigned grid = static_cast<unsigned>(tiles < sms ? tiles : sms);
-    if (ntok == 16)
-        prefill_kernel<16><<<grid, SM_THREADS, sm_smem<16>(), st>>>(tmap_a, tmap_p, pp);
-    else if (ntok == 32)
-        prefill_kernel<32><<<grid, SM_THREADS, sm_smem<32>(), st>>>(tmap_a, tmap_p, pp);
-    else if (ntok == 64)
-        prefill_kernel<64><<<grid, SM_THREADS, sm_smem<64>(), st>>>(tmap_a, tmap_p, pp);
-    else
-        prefill_kernel<128><<<grid, SM_THREADS, sm_smem<128>(), st>>>(tmap_a, tmap_p, pp);
-    WF_CUDA(cudaGetLastError());
+    cudaLaunchConfig_t lc = {};
+    lc.gridDim = dim3(static_cast<unsigned>(tiles < sms ? tiles : sms));
+    lc.blockDim = dim3(SM_THREADS);
+    lc.stream = st;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    lc.attrs = attr;
+    lc.numAttrs = 1;
+    if (ntok == 16) {
+        lc.dynamicSmemBytes = sm_smem<16>();
+        WF_CUDA(cudaLaunchKernelEx(&lc, prefill_kernel<16>, tmap_a, tmap_p, pp));
+    } else if (ntok == 32) {
+        lc.dynamicSmemBytes = sm_smem<32>();
+        WF_CUDA(cudaLaunchKernelEx(&lc, prefill_kernel<32>, tmap_a, tmap_p, pp));
+    } else if (ntok == 64) {
+        lc.dynamicSmemBytes = sm_smem<64>();
+        WF_CUDA(cudaLaunchKernelEx(&lc, prefill_kernel<64>, tmap_a, tmap_p, pp));
+    } else {
+        lc.dynamicSmemBytes = sm_smem<128>();
+        WF_CUDA(cudaLaunchKernelEx(&lc, prefill_kernel<128>, tmap_a, tmap_p, pp));
+    }
     return WF_OK;
 }
 
