@@ -38,8 +38,8 @@ extern "C" {
 /* ---- layouts of packed 2-bit weights (code = w + 1, 4 per byte, row-major [N, K/4]) ---- */
 #define WF_LAYOUT_WF16 0    /* this library's layout: per 32-bit word, byte b bit-pair j = weight 16*word + 4*j + b; K % 64 == 0 */
 #define WF_LAYOUT_I2S 1     /* 128-weight blocks of 32 bytes: byte j bits 7:6,5:4,3:2,1:0 = weights j, j+32, j+64, j+96; K % 128 == 0 */
-#define WF_LAYOUT_SEQ_LSB 2 /* byte j = weights 4j..4j+3 at shifts 0,2,4,6 (conversion source only) */
-#define WF_LAYOUT_SEQ_MSB 3 /* byte j = weights 4j..4j+3 at shifts 6,4,2,0 (conversion source only) */
+#define WF_LAYOUT_SEQ_LSB 2 /* byte j = weights 4j..4j+3 at shifts 0,2,4,6 (conversion only: the kernels do not consume it) */
+#define WF_LAYOUT_SEQ_MSB 3 /* byte j = weights 4j..4j+3 at shifts 6,4,2,0 (conversion only) */
 #define WF_LAYOUT_HF 4      /* [N/4, K] bytes: byte (r,c) = rows r, r+N/4, r+2N/4, r+3N/4 at shifts 0,2,4,6 (conversion source only) */
 
 /* ---- ternarization modes of wf_pack_ternary ---- */
@@ -100,7 +100,7 @@ int wf_pack_ternary_noalloc(const void* w, int w_dtype, int64_t N, int64_t K, in
                             uint8_t* codes_out, float* scale_out, void* stream);
 
 /*
- * Layout conversion of already-ternary packed weights into dst_layout (WF16 or I2S).
+ * Layout conversion of already-ternary packed weights into dst_layout (any row-major layout: WF16, I2S, SEQ_LSB, SEQ_MSB).
  * Replaces the Python packing loops: _pack_ternary_weights (packages/inference/src/wrinklefree_inference/cache/bitnet_converter.py:26-77),
  * repack_hf_weights / pack_weights (packages/inference/src/wrinklefree_inference/kernels/native.py:181-241),
  * pack_ternary_weights (packages/inference/src/wrinklefree_inference/kernels/bitnet_patch.py:81-112).
@@ -108,7 +108,22 @@ int wf_pack_ternary_noalloc(const void* w, int w_dtype, int64_t N, int64_t K, in
  */
 int wf_repack(const uint8_t* src, int src_layout, uint8_t* dst, int dst_layout, int64_t N, int64_t K, void* stream);
 
-/* Packs int8 ternary values {-1,0,1} [N,K] into `layout` (WF16 or I2S); unpacks the other way. */
+/*
+ * The max-abs quantizers of the inference side, on the GPU: scale_out[0] = max|w| and 2-bit codes written
+ * straight into dst_layout (any row-major layout).  scale_out must hold 2 floats (the second is scratch).
+ * WF_MAXABS_HALF replaces quantize_to_bitnet
+ *   (packages/inference/src/wrinklefree_inference/sglang_backend/bitnet_quantization.py:69-109): a maximum below
+ *   1e-6 counts as 1, codes +1 / -1 where w / max is above 0.5 / below -0.5, else 0; its bytes are WF_LAYOUT_SEQ_MSB.
+ * WF_MAXABS_SIGN replaces quantize_i2_s (packages/inference/extern/BitNet/src/ggml-bitnet-mad.cpp:46-92): codes by
+ *   the sign of w, 0 where |w| < 1e-6; its bytes are WF_LAYOUT_I2S (the scale that file appends after the data is
+ *   returned in scale_out instead).
+ */
+#define WF_MAXABS_HALF 0
+#define WF_MAXABS_SIGN 1
+int wf_quantize_maxabs(const void* w, int w_dtype, int64_t N, int64_t K, int64_t ldw, int rule, int dst_layout,
+                       uint8_t* codes_out, float* scale_out, void* stream);
+
+/* Packs int8 ternary values {-1,0,1} [N,K] into `layout` (any row-major layout); unpacks the other way (any layout). */
 int wf_pack_codes(const int8_t* ternary, uint8_t* dst, int layout, int64_t N, int64_t K, void* stream);
 int wf_unpack_codes(const uint8_t* src, int layout, int8_t* ternary, int64_t N, int64_t K, void* stream);
 
@@ -226,7 +241,8 @@ int wf_bitlinear_prefill_batched(const void* x, int x_dtype, int64_t ldx, const 
  * (packages/training/src/wrinklefree/models/subln.py / transformer.py:80-117 for residual + RMSNorm,
  *  attention.py:14-64 for RoPE, ffn.py:51-87 for the gate activation) in the decode step.
  * wf_add_rmsnorm_bf16: h[M,K] += delta (nullable), y = h * rsqrt(mean(h^2) + eps) * weight[K].
- * wf_rope_kv_bf16:     rotates q [B, nq*D] in place and k [B, nkv*D] at position slot = *pos % T (device scalar),
+ * wf_rope_kv_bf16:     rotates q [B, nq*D] in place and k [B, nkv*D] at position *pos (device scalar; the caller keeps it below T, the
+ *                      kernel only reduces it modulo T so that a stray value cannot leave the tables),
  *                      writes the rotated k and v into the caches [B, nkv, T, D]; cos/sin are fp32 [T, D/2].
  * wf_act_mul_bf16:     out = act(gate) * up over n elements; mode 0 = SiLU, 1 = ReLU^2.
  * flags: WF_FLAG_PDL chains the kernel to its neighbours in the stream with a programmatic dependency (each of

@@ -18,10 +18,30 @@ _i64, _i32, _f32 = C.c_int64, C.c_int, C.c_float
 _p = C.c_void_p
 
 
+def reference_root():
+    """A checkout of the reference project: $WF_REFERENCE_ROOT, else a directory named `reference` beside the
+    repository; None when neither holds the kernel sources."""
+    probe = os.path.join("packages", "inference", "extern", "sglang-bitnet", "sgl-kernel", "csrc", "bitnet", "bitnet_gemv.cpp")
+    for cand in (os.environ.get("WF_REFERENCE_ROOT"), os.path.join(os.path.dirname(os.path.dirname(HERE)), "reference")):
+        if cand and os.path.exists(os.path.join(cand, probe)):
+            return cand
+    return None
+
+
+def _system_compiler(name: str) -> str:
+    """The distribution's compiler when present (it carries OpenMP), else whatever PATH offers."""
+    sys_path = os.path.join(os.sep, "usr", "bin", name)
+    return sys_path if os.path.exists(sys_path) else name
+
+
 def build(quiet: bool = True) -> None:
-    """Compile the C oracle and, when the reference tree is present, oracle/_ref."""
-    env = dict(os.environ, CC="/usr/bin/gcc", CXX="/usr/bin/g++")
-    r = subprocess.run(["make", "-C", HERE], env=env, capture_output=True, text=True)
+    """Compile the C oracle and, when a reference checkout is found, oracle/_ref."""
+    env = dict(os.environ, CC=_system_compiler("gcc"), CXX=_system_compiler("g++"))
+    cmd = ["make", "-C", HERE]
+    ref = reference_root()
+    if ref:
+        cmd.append(f"REF={ref}")
+    r = subprocess.run(cmd, env=env, capture_output=True, text=True)
     if r.returncode != 0:
         raise RuntimeError("oracle build failed:\n" + r.stdout + r.stderr)
     if not quiet:
@@ -114,6 +134,9 @@ class Reference:
     def num_threads(self) -> int:
         return int(self.lib.ref_num_threads())
 
+    def set_num_threads(self, n: int) -> None:
+        self.lib.ref_set_num_threads(_i32(n))
+
     def vec_dot(self, packed_row, act):
         packed_row = np.ascontiguousarray(packed_row, dtype=np.uint8)
         act = np.ascontiguousarray(act, dtype=np.int8)
@@ -183,4 +206,57 @@ def load_reference():
         path = os.path.join(HERE, "_ref", f"libref_bitnet_{fl}.so")
         if os.path.exists(path):
             return Reference(C.CDLL(path), fl)
+    return None
+
+
+class GgmlReference:
+    """BitNet.cpp's I2_S routines (ggml-bitnet-mad.cpp compiled behind ggml_shim.cpp)."""
+
+    def __init__(self, lib):
+        self.lib = lib
+        lib.ggml_ref_num_threads.restype = _i32
+        lib.ggml_ref_quantize_i2_s.restype = C.c_size_t
+        lib.ggml_ref_quantize_i2_s.argtypes = [_p, _p, _i64, _i64]
+        lib.ggml_ref_vec_dot.restype = _f32
+        lib.ggml_ref_vec_dot.argtypes = [_i32, _p, _p]
+        lib.ggml_ref_mul_mat.argtypes = [_i32, _i32, _i32, _p, _p, _p, _p, _p, _f32]
+
+    def num_threads(self) -> int:
+        return int(self.lib.ggml_ref_num_threads())
+
+    def set_num_threads(self, n: int) -> None:
+        self.lib.ggml_ref_set_num_threads(_i32(n))
+
+    def quantize_i2_s(self, w):
+        """Returns (packed uint8 [N, K/4] in the I2_S block order, scale)."""
+        w = np.ascontiguousarray(w, dtype=np.float32)
+        n, k = w.shape
+        buf = np.zeros(n * k // 4 + 64, dtype=np.uint8)
+        self.lib.ggml_ref_quantize_i2_s(_ptr(w), _ptr(buf), _i64(n), _i64(k))
+        scale = buf[n * k // 4:n * k // 4 + 4].view(np.float32)[0]
+        return buf[:n * k // 4].reshape(n, k // 4).copy(), np.float32(scale)
+
+    def vec_dot(self, packed_row, act):
+        packed_row = np.ascontiguousarray(packed_row, dtype=np.uint8)
+        act = np.ascontiguousarray(act, dtype=np.int8)
+        return np.float32(self.lib.ggml_ref_vec_dot(_i32(act.size), _ptr(packed_row), _ptr(act)))
+
+    def mul_mat(self, packed, act, act_sums, act_scales, w_scale):
+        """[batch, rows] fp32 = (dot - act_sum) / act_scale * w_scale, rows in an OpenMP loop."""
+        packed = np.ascontiguousarray(packed, dtype=np.uint8)
+        act = np.ascontiguousarray(act, dtype=np.int8)
+        act_sums = np.ascontiguousarray(act_sums, dtype=np.float32)
+        act_scales = np.ascontiguousarray(act_scales, dtype=np.float32)
+        rows, kb = packed.shape
+        b = act.shape[0]
+        out = np.empty((b, rows), dtype=np.float32)
+        self.lib.ggml_ref_mul_mat(_i32(rows), _i32(kb * 4), _i32(b), _ptr(out), _ptr(packed), _ptr(act), _ptr(act_sums),
+                                  _ptr(act_scales), _f32(w_scale))
+        return out
+
+
+def load_ggml_reference():
+    path = os.path.join(HERE, "_ref", "libref_ggml_mad_avx2.so")
+    if "avx2" in _cpu_flags() and os.path.exists(path):
+        return GgmlReference(C.CDLL(path))
     return None

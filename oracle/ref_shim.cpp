@@ -25,6 +25,15 @@ int ref_num_threads() {
 #endif
 }
 
+// the OpenMP team size of the kernels below (a launcher may have exported OMP_NUM_THREADS=1)
+void ref_set_num_threads(int n) {
+#ifdef _OPENMP
+    if (n > 0) omp_set_num_threads(n);
+#else
+    (void)n;
+#endif
+}
+
 // bitnet_gemv.h:45-50
 int ref_vec_dot_i2_i8(int n, float* result, const uint8_t* packed, const int8_t* act) {
     try {

@@ -49,3 +49,47 @@ def sha(*arrays) -> str:
     for a in arrays:
         h.update(np.ascontiguousarray(a).tobytes())
     return h.hexdigest()
+
+
+# ---------------------------------------------------------------------------------------------
+# A two-layer decoder at SmolLM2-135M widths (hidden 576, 9 query / 3 KV heads of 64, SwiGLU-shaped MLP of 1536)
+# with a small vocabulary, for the whole-model parity fixtures.
+MODEL_CFG = dict(layers=2, hidden=576, n_q=9, n_kv=3, head_dim=64, intermediate=1536, vocab=1024, rope_theta=1e5,
+                 norm_eps=1e-6, max_pos=64)
+MODEL_BATCH, MODEL_PROMPT, MODEL_STEPS = 2, 24, 3  # ids [B, PROMPT + STEPS]; the last STEPS tokens are teacher-forced decode steps
+MODEL_KEEP_FROM = 16                               # logits are stored for positions KEEP_FROM .. PROMPT + STEPS - 1
+
+
+def model_weights(seed: int = 31):
+    """Seeded fp32 weights of the fixture decoder: dict name -> tensor, names after the reference's modules.
+    Projections ~ N(0, 0.02); norm weights ~ 1 + 0.1 N(0, 1) so that every norm matters to the result."""
+    c = MODEL_CFG
+    g = torch.Generator().manual_seed(seed)
+
+    def lin(n, k):
+        return torch.randn(n, k, generator=g, dtype=torch.float32) * 0.02
+
+    def norm(n):
+        return 1.0 + 0.1 * torch.randn(n, generator=g, dtype=torch.float32)
+
+    d, h, it = c["head_dim"], c["hidden"], c["intermediate"]
+    w = {"embed_tokens.weight": lin(c["vocab"], h), "lm_head.weight": lin(c["vocab"], h), "transformer.norm.weight": norm(h)}
+    for i in range(c["layers"]):
+        p = f"transformer.layers.{i}."
+        w[p + "input_layernorm.weight"] = norm(h)
+        w[p + "self_attn.q_proj.weight"] = lin(c["n_q"] * d, h)
+        w[p + "self_attn.k_proj.weight"] = lin(c["n_kv"] * d, h)
+        w[p + "self_attn.v_proj.weight"] = lin(c["n_kv"] * d, h)
+        w[p + "self_attn.subln.weight"] = norm(c["n_q"] * d)
+        w[p + "self_attn.o_proj.weight"] = lin(h, c["n_q"] * d)
+        w[p + "post_attention_layernorm.weight"] = norm(h)
+        w[p + "mlp.gate_proj.weight"] = lin(it, h)
+        w[p + "mlp.up_proj.weight"] = lin(it, h)
+        w[p + "mlp.subln.weight"] = norm(it)
+        w[p + "mlp.down_proj.weight"] = lin(h, it)
+    return w
+
+
+def model_ids(seed: int = 32) -> torch.Tensor:
+    g = torch.Generator().manual_seed(seed)
+    return torch.randint(0, MODEL_CFG["vocab"], (MODEL_BATCH, MODEL_PROMPT + MODEL_STEPS), generator=g)

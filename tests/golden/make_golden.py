@@ -1,13 +1,14 @@
 """Generate the golden vectors under tests/golden/ from the reference itself.
 
-Run where the reference checkout is mounted (default /root/reference):
+Run where a checkout of the reference project is available:
 
-    python tests/golden/make_golden.py [--ref /root/reference]
+    python tests/golden/make_golden.py --ref <checkout> [--only cases,packers,ggml,model]
 
-It imports the reference's PyTorch BitLinear and quantization helpers, its
-inference-side packers, and calls its compiled CPU kernel (oracle/_ref, built by
-`make -C oracle`), all on the seeded inputs of tests/golden/inputs.py, and
-writes one compressed .npz per case plus packers.npz and kat.npz.  The tests
+(`--ref` defaults to $WF_REFERENCE_ROOT, else a directory `reference` beside the repository.)
+It imports the reference's PyTorch BitLinear, quantization helpers and BitNetLlama model, its
+inference-side packers, and calls its compiled CPU kernels (oracle/_ref, built by
+`make -C oracle REF=<checkout>`), all on the seeded inputs of tests/golden/inputs.py, and
+writes one compressed .npz per case plus packers.npz, ggml.npz and model_<act>.npz.  The tests
 never need the reference: they read these files.
 """
 from __future__ import annotations
@@ -36,12 +37,31 @@ def _load_file(path, name):
 
 
 def main():
+    from oracle.clib import reference_root
+
     ap = argparse.ArgumentParser()
-    ap.add_argument("--ref", default="/root/reference")
+    ap.add_argument("--ref", default=reference_root())
+    ap.add_argument("--only", default="cases,packers,ggml,model")
     args = ap.parse_args()
     ref = args.ref
+    if not ref:
+        raise SystemExit("no reference checkout: pass --ref or set WF_REFERENCE_ROOT")
+    os.environ["WF_REFERENCE_ROOT"] = ref
+    only = set(args.only.split(","))
     sys.path.insert(0, os.path.join(ref, "packages/training/src"))
     sys.path.insert(0, os.path.join(ref, "packages/inference/src"))
+    torch.set_num_threads(1)  # fixed reduction order for the stored reference outputs
+    if "cases" in only:
+        cases()
+    if "packers" in only:
+        packers(ref)
+    if "ggml" in only:
+        ggml()
+    if "model" in only:
+        model()
+
+
+def cases():
 
     from wrinklefree.models.bitlinear import BitLinear
     from wrinklefree.quantization.activation_quant import activation_quantization_per_token
@@ -118,7 +138,9 @@ def main():
         np.savez_compressed(os.path.join(HERE, f"{name}.npz"), **out)
         print(name, {kk: getattr(v, "shape", v) for kk, v in out.items() if kk != "input_sha"})
 
-    # ---------------- packers of the inference package ----------------
+
+def packers(ref):
+    """Packers of the inference package."""
     pk = {}
     g = torch.Generator().manual_seed(21)
     w = torch.randn(16, 256, generator=g) * 0.02
@@ -163,10 +185,71 @@ def main():
         pk["quantize_to_bitnet_msb"] = p5.numpy()
         pk["quantize_to_bitnet_scale"] = np.float32(s5)
         pk["dequantize_bitnet"] = dequantize_bitnet(p5, s5, 16, 256).float().numpy()
+        # the same quantizer on raw (Gaussian) weights: max-abs scale, +-0.5 thresholds, and the apply() of its class
+        from wrinklefree_inference.sglang_backend.bitnet_quantization import BitNetLinearMethod
+
+        p6, s6 = quantize_to_bitnet(w)
+        pk["qtb_w_msb"] = p6.numpy()
+        pk["qtb_w_scale"] = np.float32(s6)
+        xq = torch.randn(5, 256, generator=g)
+        pk["qtb_x"] = xq.numpy()
+        pk["qtb_apply_bf16"] = BitNetLinearMethod().apply(p6, s6, xq, 16, 256).float().numpy()
     except Exception as e:  # pragma: no cover
         print("bitnet_quantization unavailable:", e)
     np.savez_compressed(os.path.join(HERE, "packers.npz"), **pk)
     print("packers", sorted(pk))
+
+
+def ggml():
+    """BitNet.cpp's I2_S routines (ggml-bitnet-mad.cpp) on ternary weights times a scale."""
+    from oracle.clib import load_ggml_reference
+
+    gg = load_ggml_reference()
+    assert gg is not None, "oracle/_ref/libref_ggml_mad_avx2.so missing"
+    rng = np.random.default_rng(41)
+    out = {}
+    for tag, (n, k, b) in {"a": (24, 256, 3), "b": (16, 4096 + 128, 2)}.items():  # b: more than 32 blocks per row
+        t = rng.integers(-1, 2, size=(n, k)).astype(np.int8)
+        w = t.astype(np.float32) * np.float32(0.0371)
+        w[0, :4] = [5e-7, -5e-7, 0.0371, -0.0371]  # below the 1e-6 dead zone -> code 0
+        packed, scale = gg.quantize_i2_s(w)
+        q = rng.integers(-127, 128, size=(b, k)).astype(np.int8)
+        sums = q.astype(np.int64).sum(1).astype(np.float32)
+        scales = (rng.random(b).astype(np.float32) + 0.5) * 30
+        out[f"{tag}_w"], out[f"{tag}_packed"], out[f"{tag}_scale"], out[f"{tag}_q"] = w, packed, scale, q
+        out[f"{tag}_act_scales"] = scales
+        out[f"{tag}_vec_dot"] = np.array([[gg.vec_dot(packed[r], q[i]) for r in range(n)] for i in range(b)], np.float32)
+        out[f"{tag}_mul_mat"] = gg.mul_mat(packed, q, sums, scales, float(scale))
+    np.savez_compressed(os.path.join(HERE, "ggml.npz"), **out)
+    print("ggml", {kk: getattr(v, "shape", v) for kk, v in out.items()})
+
+
+def model():
+    """The reference's BitNetLlama (llama.py:13-159) at the fixture decoder's size, fp32 and bf16, both activations."""
+    from wrinklefree.models.config import BitNetConfig
+    from wrinklefree.models.llama import BitNetLlama
+
+    c = gi.MODEL_CFG
+    ids = gi.model_ids()
+    weights = gi.model_weights()
+    for act in ("relu2", "silu"):
+        cfg = BitNetConfig(vocab_size=c["vocab"], hidden_size=c["hidden"], intermediate_size=c["intermediate"],
+                           num_hidden_layers=c["layers"], num_attention_heads=c["n_q"], num_kv_heads=c["n_kv"],
+                           head_dim=c["head_dim"], max_position_embeddings=c["max_pos"], rope_theta=c["rope_theta"],
+                           hidden_act=act, rms_norm_eps=c["norm_eps"], tie_word_embeddings=False, use_flash_attention=False)
+        out = {"input_sha": gi.sha(ids.numpy(), *[weights[k].numpy() for k in sorted(weights)])}
+        for tag, dt in (("f32", torch.float32), ("bf16", torch.bfloat16)):
+            m = BitNetLlama(cfg)
+            missing, unexpected = m.load_state_dict(weights, strict=False)
+            assert not unexpected and all("freqs_cis" in k for k in missing), (missing, unexpected)
+            for prm in m.parameters():  # parameters only: Module.to() would also cast the complex RoPE table to real
+                prm.data = prm.data.to(dt)
+            m.eval()
+            with torch.no_grad():
+                logits = m(ids)["logits"]
+            out[f"logits_{tag}"] = logits[:, gi.MODEL_KEEP_FROM:].float().numpy()
+        np.savez_compressed(os.path.join(HERE, f"model_{act}.npz"), **out)
+        print("model", act, {kk: getattr(v, "shape", v) for kk, v in out.items() if kk != "input_sha"})
 
 
 if __name__ == "__main__":

@@ -120,3 +120,149 @@ def test_linear_method_shapes_on_cpu(wf):
         if torch.cuda.is_available():
             raise RuntimeError("skip")
         m.apply(layer, torch.zeros(1, 256))
+
+
+def test_torch_operators_are_registered_with_fake_shapes(wf):
+    """torch.ops.wf_b200.* exist with the reference's operator argument lists, and their shape-only
+    implementations answer without a GPU (cpu_graph_runner.py:340-354 registers the same for the CPU operators)."""
+    from torch._subclasses.fake_tensor import FakeTensorMode
+
+    for name in wf.torch_ops.OPERATORS:
+        assert hasattr(torch.ops.wf_b200, name)
+    with FakeTensorMode():
+        pw = torch.empty(64, 32, dtype=torch.uint8, device="cuda")
+        a = torch.empty(5, 128, dtype=torch.int8, device="cuda")
+        out = torch.ops.wf_b200.bitnet_gemm(pw, a, 0.5)
+        assert out.shape == (5, 64) and out.dtype == torch.float32
+        assert torch.ops.wf_b200.bitnet_gemv(pw, a[0], 0.5).shape == (64,)
+        q, s = torch.ops.wf_b200.bitnet_quantize_activations(torch.empty(5, 128, device="cuda"))
+        assert q.dtype == torch.int8 and q.shape == (5, 128) and s.shape == (1,)
+        x = torch.empty(2, 3, 128, dtype=torch.bfloat16, device="cuda")
+        y = torch.ops.wf_b200.bitlinear(x, pw, torch.empty(2, device="cuda"), None, 0, 1e-5)
+        assert y.shape == (2, 3, 64) and y.dtype == torch.bfloat16
+        c, sc = torch.ops.wf_b200.pack_ternary(torch.empty(16, 256, device="cuda"), 0, 1e-5)
+        assert c.shape == (16, 64) and c.dtype == torch.uint8 and sc.shape == (2,)
+
+
+def test_model_conversion_inserts_subln(wf):
+    """convert_model_to_bitnet (stage1.py:169-214): q/k/v/gate/up become BitLinear with the same parameters,
+    o_proj / down_proj become Sequential(SubLN, BitLinear); excluded names are left alone."""
+    nn = torch.nn
+
+    class Attn(nn.Module):
+        def __init__(self):
+            super().__init__()
+            self.q_proj, self.k_proj, self.v_proj = nn.Linear(64, 64, bias=False), nn.Linear(64, 32), nn.Linear(64, 32)
+            self.o_proj = nn.Linear(64, 64, bias=False)
+
+    class Mlp(nn.Module):
+        def __init__(self):
+            super().__init__()
+            self.gate_proj, self.up_proj, self.down_proj = nn.Linear(64, 128), nn.Linear(64, 128), nn.Linear(128, 64)
+
+    class Layer(nn.Module):
+        def __init__(self):
+            super().__init__()
+            self.self_attn, self.mlp = Attn(), Mlp()
+
+    class Model(nn.Module):
+        def __init__(self):
+            super().__init__()
+            self.embed_tokens = nn.Embedding(10, 64)
+            self.layers = nn.ModuleList([Layer(), Layer()])
+            self.lm_head = nn.Linear(64, 10, bias=False)
+
+    m = Model()
+    before = {k: v.clone() for k, v in m.state_dict().items()}
+    wf.convert_model_to_bitnet(m, hidden_size=64, intermediate_size=128)
+    for layer in m.layers:
+        for name in ("q_proj", "k_proj", "v_proj"):
+            assert isinstance(getattr(layer.self_attn, name), wf.BitLinear)
+        assert isinstance(layer.self_attn.o_proj, nn.Sequential) and isinstance(layer.self_attn.o_proj[0], wf.SubLN)
+        assert isinstance(layer.self_attn.o_proj[1], wf.BitLinear) and layer.self_attn.o_proj[0].hidden_size == 64
+        assert isinstance(layer.mlp.down_proj[0], wf.SubLN) and layer.mlp.down_proj[0].hidden_size == 128
+        assert isinstance(layer.mlp.gate_proj, wf.BitLinear) and isinstance(layer.mlp.down_proj[1], wf.BitLinear)
+    assert type(m.lm_head) is nn.Linear
+    assert torch.equal(m.layers[1].mlp.down_proj[1].weight, before["layers.1.mlp.down_proj.weight"])
+    assert torch.equal(m.layers[0].self_attn.k_proj.bias, before["layers.0.self_attn.k_proj.bias"])
+    x = torch.randn(3, 128)
+    sub = m.layers[0].mlp.down_proj[0]
+    assert torch.allclose(sub(x), x * torch.rsqrt(x.pow(2).mean(-1, keepdim=True) + 1e-6), atol=1e-6)
+    assert wf.create_bitnet_config(block_size=128).block_size == 128
+
+
+def _reference_checkout():
+    from oracle.clib import reference_root
+
+    return reference_root()
+
+
+@pytest.mark.skipif(_reference_checkout() is None, reason="needs a checkout of the reference project")
+def test_drop_in_inside_the_reference_tree(wf, monkeypatch):
+    """The swap a maintainer makes: the reference's own callers (BitNetFFN, BitNetAttention, the stage-1 converter)
+    import `wrinklefree.models.bitlinear`; with that module's classes replaced by the drop-in they build drop-in
+    layers, `isinstance` checks hold, and the lambda schedule the reference's trainer installs in ITS module is the
+    one the drop-in reads."""
+    import importlib
+    import sys
+
+    ref = _reference_checkout()
+    monkeypatch.syspath_prepend(os.path.join(ref, "packages", "training", "src"))
+    for name in [n for n in sys.modules if n == "wrinklefree" or n.startswith("wrinklefree.")]:
+        monkeypatch.delitem(sys.modules, name)
+    ref_bl = importlib.import_module("wrinklefree.models.bitlinear")
+    ref_forward_cls = ref_bl.BitLinear
+    for name in ("BitLinear", "BitLinearNoActivationQuant", "convert_linear_to_bitlinear"):
+        monkeypatch.setattr(ref_bl, name, getattr(wf, name))
+    for name in ("wrinklefree.models.ffn", "wrinklefree.models.attention", "wrinklefree.models"):
+        sys.modules.pop(name, None)
+    ffn_mod = importlib.import_module("wrinklefree.models.ffn")
+    att_mod = importlib.import_module("wrinklefree.models.attention")
+    ref_lw = importlib.import_module("wrinklefree.quantization.lambda_warmup")
+
+    torch.manual_seed(1)
+    ffn = ffn_mod.BitNetFFN(64, 128, hidden_act="relu2")
+    att = att_mod.BitNetAttention(64, 4, 2, 16, max_position_embeddings=16)
+    assert isinstance(ffn.gate_proj, wf.BitLinear) and isinstance(att.o_proj, wf.BitLinear)
+    # same numbers as the reference's own class on the training formula (gradient enabled -> torch formula on CPU)
+    x = torch.randn(2, 5, 64, requires_grad=True)
+    twin = ref_forward_cls(64, 128)
+    twin.weight.data.copy_(ffn.gate_proj.weight.data)
+    assert torch.allclose(ffn.gate_proj(x), twin(x), atol=1e-6)
+    y = ffn(x)
+    y.sum().backward()
+    assert y.shape == (2, 5, 64) and ffn.down_proj.weight.grad is not None
+    # the trainer's call (training/stage2.py): the schedule goes into the reference module's global
+    warm = ref_lw.LambdaWarmup(warmup_steps=4)
+    ref_lw.set_global_lambda_warmup(warm)
+    try:
+        assert wf.get_current_lambda() == 0.0  # the drop-in sees it
+        plain = torch.nn.functional.linear(x, ffn.gate_proj.weight)
+        assert torch.allclose(ffn.gate_proj(x), plain, atol=1e-6)  # lambda = 0: no quantization
+        warm.step()
+        warm.step()
+        assert wf.get_current_lambda() == pytest.approx(0.5)
+        lam_half = ffn.gate_proj(x)
+        assert torch.allclose(lam_half, twin(x), atol=1e-6)  # the reference class mixes with the same lambda
+        with torch.no_grad():  # lambda < 1 keeps the drop-in off the packed path even without gradients
+            assert torch.allclose(ffn.gate_proj(x.detach()), lam_half.detach(), atol=1e-6)
+    finally:
+        ref_lw.set_global_lambda_warmup(None)
+    assert wf.get_current_lambda() == 1.0
+    # and the other direction: a schedule installed through the drop-in's module reaches the reference's global
+    wf.set_global_lambda_warmup(wf.LambdaWarmup(warmup_steps=2))
+    try:
+        assert ref_lw.get_current_lambda() == 0.0
+    finally:
+        wf.set_global_lambda_warmup(None)
+    assert ref_lw.get_global_lambda_warmup() is None
+
+
+def test_packed_weight_cache_invalidation(wf):
+    layer = wf.BitLinear(64, 8)
+    layer._packed[torch.float32] = ("stale",)
+    layer.load_state_dict({"weight": torch.zeros(8, 64)})
+    assert not layer._packed  # loaders write through .data: load_state_dict drops the packed copies
+    layer._packed[torch.float32] = ("stale",)
+    layer.invalidate_packed()
+    assert not layer._packed

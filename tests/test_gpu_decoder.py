@@ -92,3 +92,84 @@ def test_fused_elementwise_kernels(wf):
     assert torch.equal(q, want_q)
     assert torch.equal(kc[:, :, 5], want_k) and torch.equal(vc[:, :, 5], vv.view(B, nkv, D))
     assert not kc[:, :, 4].any() and not kc[:, :, 6].any()
+
+
+# ---------------------------------------------------------------- against the reference's own model
+import os  # noqa: E402
+
+import numpy as np  # noqa: E402
+
+import inputs as gi  # noqa: E402
+
+GOLD = os.path.join(os.path.dirname(__file__), "golden")
+
+
+def _fixture_decoder(act, dtype, pack_mode):
+    from wrinklefree_monorepo_b200.decoder import DecoderConfig, TernaryDecoder
+
+    c = gi.MODEL_CFG
+    z = np.load(os.path.join(GOLD, f"model_{act}.npz"))
+    weights, ids = gi.model_weights(), gi.model_ids()
+    assert gi.sha(ids.numpy(), *[weights[k].numpy() for k in sorted(weights)]) == str(z["input_sha"])
+    cfg = DecoderConfig(layers=c["layers"], hidden=c["hidden"], n_q=c["n_q"], n_kv=c["n_kv"], head_dim=c["head_dim"],
+                        intermediate=c["intermediate"], vocab=c["vocab"], rope_theta=c["rope_theta"], act=act,
+                        eps=c["norm_eps"], subln=True)
+    dev = torch.device("cuda", 0)
+    model = TernaryDecoder(cfg, gi.MODEL_BATCH, c["max_pos"], dev, dtype=dtype, weights=weights, pack_mode=pack_mode)
+    return model, ids.to(dev), z
+
+
+def _nerr(got, ref):
+    return float(np.abs(got - ref).max() / np.abs(ref).max())
+
+
+@pytest.mark.parametrize("act", ["relu2", "silu"])
+def test_prefill_equals_reference_model_fp32(wf, act):
+    """TernaryDecoder.prefill on the weights of the reference's BitNetLlama (2 layers at SmolLM2-135M widths, SubLN,
+    GQA, interleaved RoPE) against the reference's own fp32 forward, per position, err = max|a-b| / max|b|.
+
+    Rounding to int8 is discontinuous: an input that lands within a few 1e-7 of a rounding boundary is rounded the
+    other way when the fp32 summation order of a norm differs, that one code moves the token's hidden state by
+    ~1e-3, and the next quantizations amplify it to ~1e-2 at the logits.  The reference does this to itself: adding
+    3e-7 relative noise to its embeddings left 44 of 54 positions within 5e-7 and moved the other 10 by 0.5-1.7 %.
+    So: most positions must agree to 1e-5 (the computation is the same one), and no position may be off by more
+    than 3e-2 (a rounding cascade, not a different model)."""
+    model, ids, z = _fixture_decoder(act, torch.float32, torch.float32)
+    logits = model.prefill(ids, all_logits=True)
+    got = logits[:, gi.MODEL_KEEP_FROM:].float().cpu().numpy()
+    ref = z["logits_f32"]
+    err = np.abs(got - ref).max(-1).reshape(-1) / np.abs(ref).max()
+    print(f"fp32 {act}: per-position error sorted: {np.sort(err)}")
+    assert np.median(err) <= 1e-5 and (err <= 1e-5).mean() >= 0.5, np.sort(err)
+    assert err.max() <= 3e-2, err.max()
+    assert (got.argmax(-1) == ref.argmax(-1)).mean() >= 0.9
+    wf.device_status()
+
+
+@pytest.mark.parametrize("act", ["relu2", "silu"])
+def test_bf16_prefill_and_decode_steps_follow_reference_model(wf, act):
+    """bf16 end to end, weights ternarized by the cast-first rule of BitLinear.forward.  Held to the reference's bf16
+    forward within max|a-b| / max|b| <= 6e-2 (measured 0.037-0.041): the reference evaluates its norms, residuals and
+    attention in bf16 arithmetic, this decoder in fp32 with one rounding, so int8 codes near a rounding boundary differ
+    and the random two-layer network amplifies that.  For scale: the reference's own bf16 and fp32 forwards differ by
+    0.16 on this fixture, and this decoder must sit as close to the bf16 reference as that (checked as well).  The
+    CUDA-graphed decode step (fused norm, RoPE + cache write, grouped projections) is then teacher-forced over the next
+    positions and held to the same logits."""
+    model, ids, z = _fixture_decoder(act, torch.bfloat16, torch.bfloat16)
+    S, K0 = gi.MODEL_PROMPT, gi.MODEL_KEEP_FROM
+    logits = model.prefill(ids[:, :S], all_logits=True)
+    got = logits[:, K0:].float().cpu().numpy()
+    e_bf16, e_f32 = _nerr(got, z["logits_bf16"][:, :S - K0]), _nerr(got, z["logits_f32"][:, :S - K0])
+    print(f"prefill {act}: vs bf16 reference {e_bf16:.4f}, vs fp32 reference {e_f32:.4f}")
+    ref_gap = _nerr(z["logits_bf16"], z["logits_f32"])  # what bf16 arithmetic alone costs the reference
+    assert e_bf16 <= 6e-2 and e_bf16 < ref_gap / 2 and e_f32 <= 1.5 * ref_gap, (e_bf16, e_f32, ref_gap)
+    model.capture(masked=True)
+    for i in range(gi.MODEL_STEPS):
+        model.tok.copy_(ids[:, S + i])
+        model.graph.replay()
+        torch.cuda.synchronize()
+        step = model.logits.float().cpu().numpy()
+        e1, e2 = _nerr(step, z["logits_bf16"][:, S - K0 + i]), _nerr(step, z["logits_f32"][:, S - K0 + i])
+        print(f"step {i} {act}: vs bf16 reference {e1:.4f}, vs fp32 reference {e2:.4f}")
+        assert e1 <= 6e-2 and e2 <= 1.5 * ref_gap, (i, e1, e2)
+    wf.device_status()

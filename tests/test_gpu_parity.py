@@ -360,9 +360,9 @@ def test_linear_methods(wf):
     assert norm_err(pt.cpu().numpy(), z["i2s_gemm"] * z["i2s_act_scale"]) < 1e-6
     with pytest.raises(ValueError):
         method.create_weights(torch.nn.Module(), 576, [64], 576, 64, torch.bfloat16)  # K % 128 != 0
-    fp = wf.PackedBitNetLinearMethod().apply(packed, scale, x.to(DEV).bfloat16(), n, k)
+    fp = wf.PackedBitNetLinearMethod(layout=wf._lib.LAYOUT_I2S).apply(packed, scale, x.to(DEV).bfloat16(), n, k)
     assert fp.dtype == torch.bfloat16 and norm_err(fp.float().cpu().numpy(), z["y_f32"]) < 2e-2
-    nat = wf.BitNetLinearNative(k, n, packed, scale)(x.to(DEV))
+    nat = wf.BitNetLinearNative(k, n, packed, scale, layout=wf._lib.LAYOUT_I2S)(x.to(DEV))
     assert norm_err(nat.cpu().numpy(), z["y_f32"]) < 1e-5
 
 

@@ -9,11 +9,23 @@ from .lambda_warmup import (  # noqa: F401
     get_global_lambda_warmup,
     set_global_lambda_warmup,
 )
+from .convert import (  # noqa: F401
+    RMSNorm,
+    SubLN,
+    convert_attention_layer,
+    convert_mlp_layer,
+    convert_model_to_bitnet,
+)
 from .linear_method import (  # noqa: F401
     BitNetConfig,
     BitNetLinearMethod,
     BitNetLinearNative,
     PackedBitNetLinearMethod,
+    create_bitnet_config,
+    dequantize_bitnet,
+    pack_ternary_weights,
+    patch_model_with_native_kernels,
+    quantize_to_bitnet,
 )
 from .ops import (  # noqa: F401
     QK_I2_S,
@@ -28,6 +40,8 @@ from .ops import (  # noqa: F401
     pack_codes,
     pack_ternary,
     quantize_activations_i8,
+    quantize_maxabs,
     repack,
     unpack_codes,
 )
+from . import torch_ops  # noqa: F401,E402  (registers torch.ops.wf_b200.*)

@@ -16,6 +16,7 @@ WF_F32, WF_F16, WF_BF16, WF_I8 = 0, 1, 2, 3
 LAYOUT_WF16, LAYOUT_I2S, LAYOUT_SEQ_LSB, LAYOUT_SEQ_MSB, LAYOUT_HF = 0, 1, 2, 3, 4
 PACK_FP32, PACK_CAST_BF16, PACK_CAST_F16 = 0, 1, 2
 ACT_PER_TOKEN, ACT_PER_TENSOR = 0, 1
+MAXABS_HALF, MAXABS_SIGN = 0, 1
 FLAG_PDL = 1
 FLAG_X_READY = 2
 
@@ -54,6 +55,7 @@ _SIGNATURES = {
     "wf_pack_noalloc_scratch_bytes": (_sz, []),
     "wf_pack_ternary_noalloc": (_int, [_p, _int, _i64, _i64, _i64, _int, _f32, _p, _p, _p]),
     "wf_repack": (_int, [_p, _int, _p, _int, _i64, _i64, _p]),
+    "wf_quantize_maxabs": (_int, [_p, _int, _i64, _i64, _i64, _int, _int, _p, _p, _p]),
     "wf_pack_codes": (_int, [_p, _p, _int, _i64, _i64, _p]),
     "wf_unpack_codes": (_int, [_p, _int, _p, _i64, _i64, _p]),
     "wf_act_quant_i8": (_int, [_p, _int, _i64, _i64, _i64, _int, _f32, _p, _p, _p, _p]),

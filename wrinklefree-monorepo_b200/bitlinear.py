@@ -52,6 +52,16 @@ class BitLinear(nn.Linear):
             self._packed[dtype] = hit
         return hit[1], hit[2]
 
+    def invalidate_packed(self) -> None:
+        """Drops the packed copies.  In-place updates through autograd-visible operators are noticed by themselves
+        (the weight's version counter is part of the cache key); writes through `.data` (weight loaders) are not:
+        call this after them.  `load_state_dict` calls it."""
+        self._packed.clear()
+
+    def _load_from_state_dict(self, *args, **kwargs):
+        super()._load_from_state_dict(*args, **kwargs)
+        self.invalidate_packed()
+
     def _fast_path(self, x: torch.Tensor, lam: float) -> bool:
         if lam != 1.0:
             return False
@@ -110,6 +120,7 @@ def convert_linear_to_bitlinear(module: nn.Module, exclude_names: Optional[list]
             new.weight.data.copy_(child.weight.data)
             if child.bias is not None:
                 new.bias.data.copy_(child.bias.data)
+            new.invalidate_packed()
             setattr(module, name, new)
         else:
             convert_linear_to_bitlinear(child, exclude_names)

@@ -1,4 +1,5 @@
 // Error reporting, version and device check of the wf_b200 C ABI.
+#include <atomic>
 #include <cstring>
 
 #include "wf_common.cuh"
@@ -22,20 +23,38 @@ int cuda_fail(cudaError_t e, const char* what) {
     return WF_E_DEVICE;
 }
 
+static std::atomic<int> g_major[WF_MAX_DEVICES];  // compute capability major per device (0 = not queried yet)
+static std::atomic<int> g_sms[WF_MAX_DEVICES];    // multiprocessor count per device (0 = not queried yet)
+
+int current_device() {
+    int dev = -1;
+    return cudaGetDevice(&dev) == cudaSuccess ? dev : -1;
+}
+
 int require_device() {
     int dev = -1;
     cudaError_t e = cudaGetDevice(&dev);
     if (e != cudaSuccess) return cuda_fail(e, "cudaGetDevice");
-    static thread_local int checked_dev = -1;
-    if (checked_dev == dev) return WF_OK;
-    int major = 0;
-    e = cudaDeviceGetAttribute(&major, cudaDevAttrComputeCapabilityMajor, dev);
-    if (e != cudaSuccess) return cuda_fail(e, "cudaDeviceGetAttribute");
+    int major = (dev >= 0 && dev < WF_MAX_DEVICES) ? g_major[dev].load(std::memory_order_relaxed) : 0;
+    if (major == 0) {
+        e = cudaDeviceGetAttribute(&major, cudaDevAttrComputeCapabilityMajor, dev);
+        if (e != cudaSuccess) return cuda_fail(e, "cudaDeviceGetAttribute");
+        if (dev >= 0 && dev < WF_MAX_DEVICES) g_major[dev].store(major, std::memory_order_relaxed);
+    }
     if (major != 10)
         return fail(WF_E_DEVICE, "device %d has compute capability %d.x; this library is built for sm_100a only", dev,
                     major);
-    checked_dev = dev;
     return WF_OK;
+}
+
+int num_sms() {
+    const int dev = current_device();
+    int n = (dev >= 0 && dev < WF_MAX_DEVICES) ? g_sms[dev].load(std::memory_order_relaxed) : 0;
+    if (n <= 0) {
+        if (dev < 0 || cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || n <= 0) n = 148;
+        if (dev >= 0 && dev < WF_MAX_DEVICES) g_sms[dev].store(n, std::memory_order_relaxed);
+    }
+    return n;
 }
 
 }  // namespace wf

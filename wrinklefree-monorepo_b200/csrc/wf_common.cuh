@@ -32,6 +32,19 @@ int cuda_fail(cudaError_t e, const char* what);
 
 int require_device();  // WF_OK when the current device is compute capability 10.x
 
+// Per-device facts, keyed by device index (a process, and a single host thread, may drive several GPUs).
+constexpr int WF_MAX_DEVICES = 64;
+int current_device();   // index of the current device, or -1
+int num_sms();          // multiprocessors of the current device (148 when the query fails)
+
+// One-time per-device set-up of a kernel (cudaFuncSetAttribute is a per-device setting): `done` is a table with
+// one flag per device index; returns true when the caller still has to configure the current device.
+struct PerDeviceOnce {
+    unsigned char done[WF_MAX_DEVICES] = {};
+    bool needs(int dev) const { return dev < 0 || dev >= WF_MAX_DEVICES || !done[dev]; }
+    void mark(int dev) { if (dev >= 0 && dev < WF_MAX_DEVICES) done[dev] = 1; }
+};
+
 inline size_t dtype_size(int dt) { return dt == WF_F32 ? 4 : (dt == WF_I8 ? 1 : 2); }
 inline bool is_float_dtype(int dt) { return dt == WF_F32 || dt == WF_F16 || dt == WF_BF16; }
 

@@ -976,17 +976,6 @@ struct GroupPlan {
 constexpr size_t SMEM_MAX = 227 * 1024;
 constexpr size_t SMEM_STREAM_MAX = 113 * 1024;  // two streaming CTAs per SM
 
-static int num_sms() {
-    static thread_local int cached = 0;
-    if (!cached) {
-        int dev = 0, n = 0;
-        if (cudaGetDevice(&dev) != cudaSuccess || cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || n <= 0)
-            n = 148;
-        cached = n;
-    }
-    return cached;
-}
-
 static long long count_items16(const wf_problem* probs, int P, int MT) {
     long long t = 0;
     for (int i = 0; i < P; ++i) t += static_cast<long long>((probs[i].N + 15) / 16) * ((probs[i].M + MT - 1) / MT);
@@ -1189,10 +1178,11 @@ template <int XDT, int NT, bool FOURACC>
 static int launch_decode(const wf_problem* dev, const wf_problem& single, const DecodeCfg& cfg, const GroupPlan& g, unsigned flags,
                          cudaStream_t st) {
     auto kern = g.decoupled ? decode_stream_kernel<XDT, NT, FOURACC> : decode_kernel<XDT, NT, FOURACC>;
-    static thread_local bool configured[2] = {false, false};  // per instantiation
-    if (!configured[g.decoupled]) {
+    static PerDeviceOnce configured[2];  // per instantiation and kernel form; the attribute is a per-device setting
+    const int dev_now = current_device();
+    if (configured[g.decoupled].needs(dev_now)) {
         WF_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(SMEM_MAX)));
-        configured[g.decoupled] = true;
+        configured[g.decoupled].mark(dev_now);
     }
     cudaLaunchConfig_t lc = {};
     lc.gridDim = dim3(g.grid);

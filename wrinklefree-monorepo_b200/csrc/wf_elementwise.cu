@@ -119,7 +119,8 @@ __global__ void __launch_bounds__(NORM_THREADS) add_rmsnorm_kernel(__nv_bfloat16
 
 // Decode-step RoPE + cache write for one new token per sequence.  One block per (sequence, head): query heads are
 // rotated in place; key heads are rotated and written to kcache[b, head, slot, :], and the same block copies the
-// value head to vcache[b, head, slot, :].  cos/sin [T, D/2] fp32; slot = *pos % T is read on the device.
+// value head to vcache[b, head, slot, :].  cos/sin [T, D/2] fp32; the position *pos is read on the device
+// (the caller keeps it below T; it is reduced modulo T only so that a stray value stays inside the tables).
 __global__ void rope_kv_kernel(__nv_bfloat16* __restrict__ q, const __nv_bfloat16* __restrict__ k, const __nv_bfloat16* __restrict__ v,
                                const float* __restrict__ cosv, const float* __restrict__ sinv, const int64_t* __restrict__ pos,
                                __nv_bfloat16* __restrict__ kcache, __nv_bfloat16* __restrict__ vcache, int nq, int nkv, int D, int T) {

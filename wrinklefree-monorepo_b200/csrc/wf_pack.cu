@@ -6,6 +6,8 @@
 // (word >> 2j) & 0x03030303 is four consecutive weights as four bytes, the
 // operand shape of an int8 dot product.  I2S is the 128-weight block layout of
 // the reference's CPU kernels.
+#include <atomic>
+
 #include "wf_common.cuh"
 
 namespace wf {
@@ -137,16 +139,13 @@ __device__ __forceinline__ uint32_t fetch_code(const uint8_t* __restrict__ src, 
     }
 }
 
-// position of logical weight k inside its row for the two kernel layouts: byte index and shift
-__device__ __forceinline__ void code_slot(int layout, int64_t k, int64_t& byte, int& shift) {
-    if (layout == WF_LAYOUT_WF16) {
-        int r = static_cast<int>(k & 15);
-        byte = (k >> 4) * 4 + (r & 3);
-        shift = 2 * (r >> 2);
-    } else {
-        int r = static_cast<int>(k & 127);
-        byte = (k >> 7) * 32 + (r & 31);
-        shift = 6 - 2 * (r >> 5);
+// logical weight (inside its row) stored at (byte, bit pair s) of a row-major destination layout
+__device__ __forceinline__ int64_t dst_weight(int layout, int64_t byte, int s) {
+    switch (layout) {
+        case WF_LAYOUT_WF16: return (byte >> 2) * 16 + 4 * s + (byte & 3);
+        case WF_LAYOUT_I2S: return (byte >> 5) * 128 + 32 * (3 - s) + (byte & 31);
+        case WF_LAYOUT_SEQ_LSB: return 4 * byte + s;
+        default: return 4 * byte + (3 - s);  // WF_LAYOUT_SEQ_MSB
     }
 }
 
@@ -160,13 +159,51 @@ __global__ void repack_kernel(const uint8_t* __restrict__ src, int src_layout, u
         uint32_t out = 0;
 #pragma unroll
         for (int s = 0; s < 4; ++s) {
-            int64_t k;  // logical weight stored at (byte, bit pair s) of the destination layout
-            if (dst_layout == WF_LAYOUT_WF16)
-                k = (byte >> 2) * 16 + 4 * s + (byte & 3);
-            else
-                k = (byte >> 5) * 128 + 32 * (3 - s) + (byte & 31);
+            const int64_t k = dst_weight(dst_layout, byte, s);
             uint32_t code = ternary ? static_cast<uint32_t>(ternary[n * K + k] + 1) : fetch_code(src, src_layout, N, K, n, k);
             out |= (code & 3u) << (2 * s);
+        }
+        dst[o] = static_cast<uint8_t>(out);
+    }
+}
+
+// ---- the max-abs quantizers of the inference side ----
+// absmax over the whole matrix: non-negative floats order like their bit patterns, one atomicMax per block
+template <int WDT>
+__global__ void abs_max_kernel(const void* __restrict__ w, int64_t N, int64_t K, int64_t ldw, unsigned* __restrict__ maxbits) {
+    float mx = 0.f;
+    const int64_t total = N * K;
+    for (int64_t o = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x; o < total;
+         o += static_cast<int64_t>(gridDim.x) * blockDim.x)
+        mx = fmaxf(mx, fabsf(load1<WDT>(w, (o / K) * ldw + o % K)));
+#pragma unroll
+    for (int s = 16; s > 0; s >>= 1) mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, s));
+    if ((threadIdx.x & 31) == 0) atomicMax(maxbits, __float_as_uint(mx));
+}
+
+// one thread per output byte; rule 0: codes by thresholds at +-0.5 of w / max, rule 1: by sign with a 1e-6 dead zone
+template <int WDT>
+__global__ void maxabs_pack_kernel(const void* __restrict__ w, int64_t N, int64_t K, int64_t ldw, int rule, int dst_layout,
+                                   const unsigned* __restrict__ maxbits, uint8_t* __restrict__ dst, float* __restrict__ scale_out) {
+    float mx = __uint_as_float(*maxbits);
+    if (rule == WF_MAXABS_HALF && mx < 1e-6f) mx = 1.0f;
+    if (blockIdx.x == 0 && threadIdx.x == 0) *scale_out = mx;
+    const int64_t total = N * (K / 4);
+    for (int64_t o = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x; o < total;
+         o += static_cast<int64_t>(gridDim.x) * blockDim.x) {
+        const int64_t n = o / (K / 4), byte = o % (K / 4);
+        uint32_t out = 0;
+#pragma unroll
+        for (int s = 0; s < 4; ++s) {
+            const float v = load1<WDT>(w, n * ldw + dst_weight(dst_layout, byte, s));
+            uint32_t code = 1;
+            if (rule == WF_MAXABS_HALF) {
+                const float t = __fdiv_rn(v, mx);
+                code = t > 0.5f ? 2u : (t < -0.5f ? 0u : 1u);
+            } else if (fabs(static_cast<double>(v)) >= 1e-6) {
+                code = static_cast<double>(v) * static_cast<double>(mx) > 0.0 ? 2u : 0u;
+            }
+            out |= code << (2 * s);
         }
         dst[o] = static_cast<uint8_t>(out);
     }
@@ -180,10 +217,12 @@ __global__ void unpack_kernel(const uint8_t* __restrict__ src, int layout, int8_
         ternary[o] = static_cast<int8_t>(static_cast<int>(fetch_code(src, layout, N, K, o / K, o % K)) - 1);
 }
 
+constexpr int PACK_MAX_GRID = 148 * 8;  // blocks of the two packing kernels = partial sums in the scratch
+
 static int pack_grid(int64_t N, int64_t K) {
     int64_t blocks = (N * K + PACK_WEIGHTS_PER_BLOCK - 1) / PACK_WEIGHTS_PER_BLOCK;
     if (blocks < 1) blocks = 1;
-    if (blocks > 148 * 8) blocks = 148 * 8;
+    if (blocks > PACK_MAX_GRID) blocks = PACK_MAX_GRID;
     return static_cast<int>(blocks);
 }
 
@@ -264,7 +303,7 @@ static int grid_for(int64_t total) {
 
 int wf_repack(const uint8_t* src, int src_layout, uint8_t* dst, int dst_layout, int64_t N, int64_t K, void* stream) {
     WF_REQUIRE(src && dst, "wf_repack: null pointer");
-    WF_REQUIRE(dst_layout == WF_LAYOUT_WF16 || dst_layout == WF_LAYOUT_I2S, "wf_repack: destination must be WF16 or I2S");
+    WF_REQUIRE(dst_layout >= WF_LAYOUT_WF16 && dst_layout <= WF_LAYOUT_SEQ_MSB, "wf_repack: destination must be a row-major layout (not HF)");
     if (int rc = check_layout_dims("wf_repack(src)", src_layout, N, K)) return rc;
     if (int rc = check_layout_dims("wf_repack(dst)", dst_layout, N, K)) return rc;
     if (int rc = require_device()) return rc;
@@ -276,7 +315,7 @@ int wf_repack(const uint8_t* src, int src_layout, uint8_t* dst, int dst_layout, 
 
 int wf_pack_codes(const int8_t* ternary, uint8_t* dst, int layout, int64_t N, int64_t K, void* stream) {
     WF_REQUIRE(ternary && dst, "wf_pack_codes: null pointer");
-    WF_REQUIRE(layout == WF_LAYOUT_WF16 || layout == WF_LAYOUT_I2S, "wf_pack_codes: layout must be WF16 or I2S");
+    WF_REQUIRE(layout >= WF_LAYOUT_WF16 && layout <= WF_LAYOUT_SEQ_MSB, "wf_pack_codes: layout must be row-major (not HF)");
     if (int rc = check_layout_dims("wf_pack_codes", layout, N, K)) return rc;
     if (int rc = require_device()) return rc;
     repack_kernel<<<grid_for(N * (K / 4)), 256, 0, static_cast<cudaStream_t>(stream)>>>(nullptr, 0, dst, layout, N, K, ternary);
@@ -289,6 +328,38 @@ int wf_unpack_codes(const uint8_t* src, int layout, int8_t* ternary, int64_t N, 
     if (int rc = check_layout_dims("wf_unpack_codes", layout, N, K)) return rc;
     if (int rc = require_device()) return rc;
     unpack_kernel<<<grid_for(N * K), 256, 0, static_cast<cudaStream_t>(stream)>>>(src, layout, ternary, N, K);
+    WF_CUDA(cudaGetLastError());
+    return WF_OK;
+}
+
+int wf_quantize_maxabs(const void* w, int w_dtype, int64_t N, int64_t K, int64_t ldw, int rule, int dst_layout,
+                       uint8_t* codes_out, float* scale_out, void* stream) {
+    WF_REQUIRE(w && codes_out && scale_out, "wf_quantize_maxabs: null pointer");
+    WF_REQUIRE(is_float_dtype(w_dtype), "wf_quantize_maxabs: unsupported weight dtype %d", w_dtype);
+    WF_REQUIRE(rule == WF_MAXABS_HALF || rule == WF_MAXABS_SIGN, "wf_quantize_maxabs: unknown rule %d", rule);
+    WF_REQUIRE(dst_layout >= WF_LAYOUT_WF16 && dst_layout <= WF_LAYOUT_SEQ_MSB, "wf_quantize_maxabs: destination must be a row-major layout");
+    WF_REQUIRE(ldw >= K, "wf_quantize_maxabs: row stride must cover K");
+    if (int rc = check_layout_dims("wf_quantize_maxabs", dst_layout, N, K)) return rc;
+    if (int rc = require_device()) return rc;
+    cudaStream_t st = static_cast<cudaStream_t>(stream);
+    // the running maximum lives in the second float of scale_out until the packing kernel has read it
+    unsigned* maxbits = reinterpret_cast<unsigned*>(scale_out) + 1;
+    WF_CUDA(cudaMemsetAsync(maxbits, 0, sizeof(unsigned), st));
+    const int g1 = grid_for(N * K), g2 = grid_for(N * (K / 4));
+    switch (w_dtype) {
+        case WF_F32:
+            abs_max_kernel<WF_F32><<<g1, 256, 0, st>>>(w, N, K, ldw, maxbits);
+            maxabs_pack_kernel<WF_F32><<<g2, 256, 0, st>>>(w, N, K, ldw, rule, dst_layout, maxbits, codes_out, scale_out);
+            break;
+        case WF_BF16:
+            abs_max_kernel<WF_BF16><<<g1, 256, 0, st>>>(w, N, K, ldw, maxbits);
+            maxabs_pack_kernel<WF_BF16><<<g2, 256, 0, st>>>(w, N, K, ldw, rule, dst_layout, maxbits, codes_out, scale_out);
+            break;
+        default:
+            abs_max_kernel<WF_F16><<<g1, 256, 0, st>>>(w, N, K, ldw, maxbits);
+            maxabs_pack_kernel<WF_F16><<<g2, 256, 0, st>>>(w, N, K, ldw, rule, dst_layout, maxbits, codes_out, scale_out);
+            break;
+    }
     WF_CUDA(cudaGetLastError());
     return WF_OK;
 }
@@ -313,25 +384,25 @@ int wf_unpack_codes(const uint8_t* src, int layout, int8_t* ternary, int64_t N, 
 // ---------------------------------------------------------------------------------------------
 namespace wf {
 
-constexpr int NOALLOC_MAX_PARTIALS = 148 * 8;  // the largest grid launch_pack ever uses
+constexpr int NOALLOC_MAX_PARTIALS = PACK_MAX_GRID;  // the largest grid launch_pack ever uses
 static __device__ __align__(256) double g_pack_noalloc_scratch[NOALLOC_MAX_PARTIALS];
 
 constexpr int NOALLOC_MAX_DEVICES = 64;
-static double* g_noalloc_ptr[NOALLOC_MAX_DEVICES] = {};  // device address of the array, per device
+static std::atomic<double*> g_noalloc_ptr[NOALLOC_MAX_DEVICES];  // device address of the array, per device (zero-initialised)
 
 // Set-up, once per device, with that device current.
 static int noalloc_scratch(double** out) {
     int dev = -1;
     WF_CUDA(cudaGetDevice(&dev));
     if (dev < 0 || dev >= NOALLOC_MAX_DEVICES) return fail(WF_E_LIMIT, "wf_pack_ternary_noalloc: device index %d not supported", dev);
-    if (!g_noalloc_ptr[dev]) {
+    if (!g_noalloc_ptr[dev].load(std::memory_order_acquire)) {
         double* ptr = nullptr;
         cudaError_t e = cudaGetSymbolAddress(reinterpret_cast<void**>(&ptr), g_pack_noalloc_scratch);
         if (e != cudaSuccess) return cuda_fail(e, "cudaGetSymbolAddress(g_pack_noalloc_scratch)");
         if (!ptr) return fail(WF_E_DEVICE, "wf_pack_ternary_noalloc: no device address for the scratch array");
-        g_noalloc_ptr[dev] = ptr;
+        g_noalloc_ptr[dev].store(ptr, std::memory_order_release);
     }
-    *out = g_noalloc_ptr[dev];
+    *out = g_noalloc_ptr[dev].load(std::memory_order_acquire);
     return WF_OK;
 }
 
@@ -353,9 +424,6 @@ extern "C" int wf_pack_ternary_noalloc(const void* w, int w_dtype, int64_t N, in
     WF_REQUIRE(ldw >= K && (ldw * dtype_size(w_dtype)) % 16 == 0, "wf_pack_ternary_noalloc: row stride must cover K and keep rows 16-byte aligned");
     WF_REQUIRE(reinterpret_cast<uintptr_t>(w) % 16 == 0 && reinterpret_cast<uintptr_t>(codes_out) % 16 == 0,
                "wf_pack_ternary_noalloc: w and codes_out must be 16-byte aligned");
-    if (wf_pack_scratch_bytes(N, K) > wf_pack_noalloc_scratch_bytes())
-        return fail(WF_E_LIMIT, "wf_pack_ternary_noalloc: this matrix needs %zu bytes of scratch, the fixed array holds %zu",
-                    wf_pack_scratch_bytes(N, K), wf_pack_noalloc_scratch_bytes());
     if (int rc = require_device()) return rc;
     double* partial = nullptr;
     if (int rc = noalloc_scratch(&partial)) return rc;

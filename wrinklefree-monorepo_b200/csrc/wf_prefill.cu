@@ -520,17 +520,15 @@ static int prefill_impl(const char* who, const void* x, int x_dtype, int64_t ldx
     pp.batch = static_cast<int>(batch); pp.w_scale_stride = static_cast<int>(w_scale_stride);
     pp.tiles_m = static_cast<int>((M_one + ntok - 1) / ntok);
     pp.tiles_n = static_cast<int>((N + SM_BM - 1) / SM_BM);
-    static thread_local bool configured = false;
-    static thread_local int sms = 148;
-    if (!configured) {
+    static PerDeviceOnce configured;  // the attribute is a per-device setting
+    const int dev_now = current_device();
+    const int sms = num_sms();
+    if (configured.needs(dev_now)) {
         WF_CUDA(cudaFuncSetAttribute(prefill_kernel<16>, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(sm_smem<16>())));
         WF_CUDA(cudaFuncSetAttribute(prefill_kernel<32>, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(sm_smem<32>())));
         WF_CUDA(cudaFuncSetAttribute(prefill_kernel<64>, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(sm_smem<64>())));
         WF_CUDA(cudaFuncSetAttribute(prefill_kernel<128>, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(sm_smem<128>())));
-        int dev = 0;
-        WF_CUDA(cudaGetDevice(&dev));
-        WF_CUDA(cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev));
-        configured = true;
+        configured.mark(dev_now);
     }
     const long long tiles = static_cast<long long>(pp.tiles_m) * pp.tiles_n * pp.batch;
     cudaLaunchConfig_t lc = {};

@@ -4,7 +4,8 @@ Skeleton after the reference's model (wrinklefree/models/attention.py:126-218, f
 RMSNorm -> q/k/v BitLinear -> RoPE -> GQA attention -> o BitLinear -> residual -> RMSNorm -> gate/up BitLinear ->
 act(gate) * up -> down BitLinear -> residual; bf16 embedding and lm_head.  Unlike the reference it keeps a bf16
 KV cache, launches q/k/v and gate/up as one grouped kernel each, and replays the whole decode step as a CUDA
-graph.  Everything that is not a BitLinear projection (norms, RoPE, attention, activation) uses stock torch
+graph.  With `subln=True` and weights loaded under the reference's parameter names it computes the reference
+model (BitNetLlama) itself.  Everything that is not a BitLinear projection (norms, RoPE, attention, activation) uses stock torch
 operators: those are callers of the hot path, not part of it.
 
 Tensor parallel: heads and the MLP width are split over the ranks of a process group; q/k/v/gate/up are
@@ -35,7 +36,9 @@ class DecoderConfig:
     vocab: int
     rope_theta: float = 1e5
     act: str = "silu"  # "silu" (SwiGLU) or "relu2" (the reference's SmolLM2 preset)
-    eps: float = 1e-5
+    eps: float = 1e-5  # RMSNorm epsilon (the reference's rms_norm_eps defaults to 1e-6)
+    subln: bool = False  # sub-layer norms in front of o_proj and down_proj (wrinklefree/models/attention.py:213, ffn.py:84)
+    subln_eps: float = 1e-6
 
 
 SMOLLM2_135M = DecoderConfig(layers=30, hidden=576, n_q=9, n_kv=3, head_dim=64, intermediate=1536, vocab=49152, rope_theta=1e5)
@@ -53,37 +56,78 @@ def _rope(x: torch.Tensor, cos: torch.Tensor, sin: torch.Tensor) -> torch.Tensor
     return torch.cat([x1 * cos - x2 * sin, x2 * cos + x1 * sin], dim=-1).to(x.dtype)
 
 
+def _causal_attention(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor) -> torch.Tensor:
+    """Prompt attention, q [B, Hq, S, D], k/v [B, Hkv, S, D].  Low-precision inputs use the fused library kernel; fp32
+    inputs are evaluated with plain fp32 matrix products and an fp32 softmax, as the reference's attention does
+    (attention.py:189-208) - the fused kernels round fp32 operands to TF32."""
+    if q.dtype != torch.float32:
+        return F.scaled_dot_product_attention(q, k, v, is_causal=True, enable_gqa=True)
+    rep = q.shape[1] // k.shape[1]
+    k, v = k.repeat_interleave(rep, dim=1), v.repeat_interleave(rep, dim=1)
+    S = q.shape[2]
+    scores = torch.matmul(q, k.transpose(-2, -1)) * (1.0 / math.sqrt(q.shape[-1]))
+    scores = scores + torch.full((S, S), float("-inf"), device=q.device).triu(1)
+    return torch.matmul(torch.softmax(scores, dim=-1), v)
+
+
 class TernaryDecoder:
     """Random-initialised ternary decoder (weights N(0, 0.02), ternarized on the GPU)."""
 
     def __init__(self, cfg: DecoderConfig, batch: int, max_ctx: int, device, group=None, seed: int = 0,
-                 dtype: torch.dtype = torch.bfloat16):
+                 dtype: torch.dtype = torch.bfloat16, weights: Optional[dict] = None, pack_mode: torch.dtype = torch.float32):
+        """`weights`: optional fp32 state dict under the reference model's parameter names (BitNetLlama,
+        wrinklefree/models/llama.py:13-59); without it the weights are drawn from N(0, 0.02) with `seed`.
+        `pack_mode`: arithmetic of the ternarization (torch.float32, or the input dtype for the cast-first rule of
+        BitLinear.forward)."""
         self.cfg, self.B, self.T, self.dev, self.dtype, self.group = cfg, batch, max_ctx, device, dtype, group
         self._oneshot = None  # peer-memory all-reduce for the row-parallel projections (set up at the first step)
         self.tp = dist.get_world_size(group) if (group is not None or dist.is_initialized()) else 1
         self.rank = dist.get_rank(group) if (group is not None or dist.is_initialized()) else 0
         if cfg.n_kv % self.tp or cfg.n_q % self.tp:
             raise ValueError("heads must divide over the tensor-parallel ranks")
+        if cfg.subln and self.tp > 1:
+            raise NotImplementedError("sub-layer norms over a sharded width need one more exchange; not built for tp > 1")
         self.nq, self.nkv = cfg.n_q // self.tp, cfg.n_kv // self.tp
         self.i_lo, self.i_hi = tpmod.shard_bounds(cfg.intermediate, self.tp, 64)[self.rank]
         d, h = cfg.head_dim, cfg.hidden
         gen = torch.Generator(device=device).manual_seed(seed)  # same seed on every rank: same full matrices
+        # The reference rotates interleaved pairs (2i, 2i+1) of a head (attention.py:41-64); the kernels here rotate
+        # the pairs (i, i + d/2).  Scores are invariant under one permutation of q and k inside every head, so loaded
+        # q/k weights are permuted once: new row i = old row 2i, new row i + d/2 = old row 2i + 1.
+        perm = torch.cat([torch.arange(0, d, 2), torch.arange(1, d, 2)])
 
-        def ternary(n, k):
-            w = torch.randn(n, k, generator=gen, device=device, dtype=torch.float32) * 0.02
-            c, s = ops.pack_ternary(w)
+        def given(name, n, k, heads=0):
+            w = weights[name].to(device=device, dtype=torch.float32)
+            if tuple(w.shape) != (n, k):
+                raise ValueError(f"{name}: expected {(n, k)}, got {tuple(w.shape)}")
+            if heads:
+                w = w.view(heads, d, k)[:, perm.to(device)].reshape(n, k)
+            return w
+
+        def ternary(n, k, name=None, heads=0):
+            if weights is not None:
+                w = given(name, n, k, heads)
+            else:
+                w = torch.randn(n, k, generator=gen, device=device, dtype=torch.float32) * 0.02
+            c, s = ops.pack_ternary(w, mode=pack_mode, eps=1e-5)
             return c, s
 
+        def vec(name, n):
+            if weights is not None and name in weights:
+                return weights[name].to(device=device, dtype=dtype).contiguous()
+            return torch.ones(n, dtype=dtype, device=device)
+
         self.layers = []
-        for _ in range(cfg.layers):
+        for li in range(cfg.layers):
             L = {}
-            cq, sq = ternary(cfg.n_q * d, h)
-            ck, sk = ternary(cfg.n_kv * d, h)
-            cv, sv = ternary(cfg.n_kv * d, h)
-            co, so = ternary(h, cfg.n_q * d)
-            cg, sg = ternary(cfg.intermediate, h)
-            cu, su = ternary(cfg.intermediate, h)
-            cd, sd = ternary(h, cfg.intermediate)
+            pre = f"transformer.layers.{li}."
+            cq, sq = ternary(cfg.n_q * d, h, pre + "self_attn.q_proj.weight", cfg.n_q)
+            ck, sk = ternary(cfg.n_kv * d, h, pre + "self_attn.k_proj.weight", cfg.n_kv)
+            cv, sv = ternary(cfg.n_kv * d, h, pre + "self_attn.v_proj.weight")
+            co, so = ternary(h, cfg.n_q * d, pre + "self_attn.o_proj.weight")
+            cg, sg = ternary(cfg.intermediate, h, pre + "mlp.gate_proj.weight")
+            cu, su = ternary(cfg.intermediate, h, pre + "mlp.up_proj.weight")
+            cd, sd = ternary(h, cfg.intermediate, pre + "mlp.down_proj.weight")
             r = self.rank
             L["q"] = (tpmod.shard_codes_rows(cq, r * self.nq * d, (r + 1) * self.nq * d), sq)
             L["k"] = (tpmod.shard_codes_rows(ck, r * self.nkv * d, (r + 1) * self.nkv * d), sk)
@@ -92,20 +136,28 @@ class TernaryDecoder:
             L["gate"] = (tpmod.shard_codes_rows(cg, self.i_lo, self.i_hi), sg)
             L["up"] = (tpmod.shard_codes_rows(cu, self.i_lo, self.i_hi), su)
             L["down"] = (tpmod.shard_codes_k(cd, self.i_lo, self.i_hi), sd)
-            L["n1"] = torch.ones(h, dtype=dtype, device=device)
-            L["n2"] = torch.ones(h, dtype=dtype, device=device)
+            L["n1"] = vec(pre + "input_layernorm.weight", h)
+            L["n2"] = vec(pre + "post_attention_layernorm.weight", h)
+            if cfg.subln:
+                L["sa"] = vec(pre + "self_attn.subln.weight", cfg.n_q * d)
+                L["sf"] = vec(pre + "mlp.subln.weight", cfg.intermediate)
             L["kc"] = torch.zeros(batch, self.nkv, max_ctx, d, dtype=dtype, device=device)
             L["vc"] = torch.zeros(batch, self.nkv, max_ctx, d, dtype=dtype, device=device)
             self.layers.append(L)
-        self.embed = (torch.randn(cfg.vocab, h, generator=gen, device=device, dtype=torch.float32) * 0.02).to(dtype)
-        self.lm_head = (torch.randn(cfg.vocab, h, generator=gen, device=device, dtype=torch.float32) * 0.02).to(dtype)
-        self.norm_f = torch.ones(h, dtype=dtype, device=device)
+        if weights is not None:
+            self.embed = weights["embed_tokens.weight"].to(device=device, dtype=dtype)
+            self.lm_head = weights["lm_head.weight"].to(device=device, dtype=dtype) if "lm_head.weight" in weights else self.embed
+        else:
+            self.embed = (torch.randn(cfg.vocab, h, generator=gen, device=device, dtype=torch.float32) * 0.02).to(dtype)
+            self.lm_head = (torch.randn(cfg.vocab, h, generator=gen, device=device, dtype=torch.float32) * 0.02).to(dtype)
+        self.norm_f = vec("transformer.norm.weight", h)
         inv = 1.0 / (cfg.rope_theta ** (torch.arange(0, d, 2, device=device, dtype=torch.float32) / d))
         ang = torch.arange(max_ctx, device=device, dtype=torch.float32)[:, None] * inv[None, :]
         self.cos, self.sin = ang.cos(), ang.sin()
         # static decode-step buffers (graph inputs / outputs)
         self.tok = torch.zeros(batch, dtype=torch.long, device=device)
         self.pos = torch.zeros((), dtype=torch.long, device=device)
+        self._pos_host = 0  # host mirror of pos for the bound check of decode()
         self._step_bufs()
         self.graph: Optional[torch.cuda.CUDAGraph] = None
         self.next_tok = torch.zeros(batch, dtype=torch.long, device=device)
@@ -124,6 +176,9 @@ class TernaryDecoder:
             L["g_gu"] = ops.DecodeGroup([dict(x=L["hn"], codes=L[n][0], w_scale=L[n][1], out=o)
                                          for n, o in zip(("gate", "up"), L["gu"])])
             L["act"] = torch.empty(B, self.i_hi - self.i_lo, dtype=dt, device=dev)
+            if cfg.subln:
+                L["an"] = torch.empty(B, self.nq * d, dtype=dt, device=dev)
+                L["actn"] = torch.empty(B, self.i_hi - self.i_lo, dtype=dt, device=dev)
             L["ob"] = torch.empty(B, cfg.hidden, dtype=dt, device=dev)
             L["db"] = torch.empty(B, cfg.hidden, dtype=dt, device=dev)
         self.h = torch.empty(B, cfg.hidden, dtype=dt, device=dev)
@@ -158,7 +213,10 @@ class TernaryDecoder:
             # tokens (measured: 14 vs 20 us for 4096 x 4096 at 32 tokens; narrow layers stay faster on the decode kernel)
             big = B >= 16 and cfg.hidden >= 2048
             path = "prefill" if big else "decode"
-            o = self._allreduce(ops.bitlinear(a.reshape(B, self.nq * d), L["o"][0], L["o"][1], out=L["ob"], path=path, pdl=True))
+            a = a.reshape(B, self.nq * d)
+            if cfg.subln:
+                a = ops.add_rmsnorm_(a, None, L["sa"], L["an"], cfg.subln_eps, pdl=True)
+            o = self._allreduce(ops.bitlinear(a, L["o"][0], L["o"][1], out=L["ob"], path=path, pdl=True))
             ops.add_rmsnorm_(self.h, o, L["n2"], L["hn"], cfg.eps, pdl=True)
             if big:
                 hq, hs = ops.act_quant_i8(L["hn"], eps=1e-5)  # one quantization for gate and up
@@ -166,8 +224,10 @@ class TernaryDecoder:
                         for n, o_ in zip(("gate", "up"), L["gu"]))
             else:
                 g, u = L["g_gu"].run(pdl=True)
-            ops.act_mul(g, u, L["act"], self.cfg.act, pdl=True)
-            delta = self._allreduce(ops.bitlinear(L["act"], L["down"][0], L["down"][1], out=L["db"], path=path, pdl=True))
+            act = ops.act_mul(g, u, L["act"], self.cfg.act, pdl=True)
+            if cfg.subln:
+                act = ops.add_rmsnorm_(act, None, L["sf"], L["actn"], cfg.subln_eps, pdl=True)
+            delta = self._allreduce(ops.bitlinear(act, L["down"][0], L["down"][1], out=L["db"], path=path, pdl=True))
         ops.add_rmsnorm_(self.h, delta, self.norm_f, self.xf, cfg.eps, pdl=True)
         logits = self.xf @ self.lm_head.t()
         self.logits = logits
@@ -175,10 +235,13 @@ class TernaryDecoder:
         self.pos.add_(1)
 
     # ------------------------------------------------------------------ public
-    def prefill(self, ids: torch.Tensor):
-        """ids [B, S]: fills the KV cache for positions 0..S-1, leaves self.tok = greedy next token, pos = S."""
+    def prefill(self, ids: torch.Tensor, all_logits: bool = False):
+        """ids [B, S]: fills the KV cache for positions 0..S-1, leaves self.tok = greedy next token, pos = S.
+        Returns the logits of the last position [B, vocab], or of every position [B, S, vocab] with `all_logits`."""
         cfg, B, d = self.cfg, self.B, self.cfg.head_dim
         S = ids.shape[1]
+        if S > self.T:
+            raise ValueError(f"prompt of {S} tokens exceeds the cache of {self.T}")
         x = self.embed[ids]  # [B, S, hidden]
         cos, sin = self.cos[:S], self.sin[:S]
         for L in self.layers:
@@ -189,16 +252,23 @@ class TernaryDecoder:
             q, k = _rope(q, cos, sin), _rope(k, cos, sin)
             L["kc"][:, :, :S] = k
             L["vc"][:, :, :S] = v
-            a = F.scaled_dot_product_attention(q, k, v, is_causal=True, enable_gqa=True)
-            o = self._allreduce(ops.bitlinear(a.transpose(1, 2).reshape(B * S, self.nq * d), *L["o"]))
+            a = _causal_attention(q, k, v)
+            a = a.transpose(1, 2).reshape(B * S, self.nq * d)
+            if cfg.subln:
+                a = _rms_norm(a, L["sa"], cfg.subln_eps)
+            o = self._allreduce(ops.bitlinear(a, *L["o"]))
             x = x + o.view(B, S, cfg.hidden)
             hn = _rms_norm(x, L["n2"], cfg.eps).reshape(B * S, cfg.hidden)
             g, u = ops.bitlinear(hn, *L["gate"]), ops.bitlinear(hn, *L["up"])
-            dn = self._allreduce(ops.bitlinear(self._act(g, u), *L["down"]))
+            act = self._act(g, u)
+            if cfg.subln:
+                act = _rms_norm(act, L["sf"], cfg.subln_eps)
+            dn = self._allreduce(ops.bitlinear(act, *L["down"]))
             x = x + dn.view(B, S, cfg.hidden)
-        logits = _rms_norm(x[:, -1], self.norm_f, cfg.eps) @ self.lm_head.t()
-        self.tok.copy_(logits.argmax(-1))
+        logits = _rms_norm(x if all_logits else x[:, -1], self.norm_f, cfg.eps) @ self.lm_head.t()
+        self.tok.copy_(logits[:, -1].argmax(-1) if all_logits else logits.argmax(-1))
         self.pos.fill_(S)
+        self._pos_host = S
         return logits
 
     def capture(self, masked: bool = True):
@@ -220,6 +290,9 @@ class TernaryDecoder:
 
     def decode(self, steps: int):
         """Greedy decoding of `steps` tokens per sequence; returns [B, steps] token ids."""
+        if self._pos_host + steps > self.T:  # the cache and the rotary table hold T positions
+            raise ValueError(f"decoding {steps} tokens from position {self._pos_host} exceeds the context of {self.T}")
+        self._pos_host += steps
         out = []
         for _ in range(steps):
             self.graph.replay()

@@ -9,6 +9,7 @@ packed-weight CUDA path.
 from __future__ import annotations
 
 import math
+import sys
 from typing import Optional
 
 
@@ -54,16 +55,33 @@ class LambdaWarmup:
 
 
 _global: Optional[LambdaWarmup] = None
+_REFERENCE_MODULE = "wrinklefree.quantization.lambda_warmup"
+
+
+def _reference_module():
+    """The reference's own lambda_warmup module when the host process has imported it.  Its trainer installs the
+    schedule there (training/stage2.py sets that module's global), so a drop-in layer must read the same global or
+    it would run fully quantized while the trainer believes lambda < 1."""
+    mod = sys.modules.get(_REFERENCE_MODULE)
+    return mod if (mod is not None and mod is not sys.modules.get(__name__)) else None
 
 
 def get_global_lambda_warmup() -> Optional[LambdaWarmup]:
+    ref = _reference_module()
+    if ref is not None and ref.get_global_lambda_warmup() is not None:
+        return ref.get_global_lambda_warmup()
     return _global
 
 
 def set_global_lambda_warmup(warmup: Optional[LambdaWarmup]) -> None:
+    """Installs the schedule here and, when the reference's module is loaded, there too: one shared state."""
     global _global
     _global = warmup
+    ref = _reference_module()
+    if ref is not None:
+        ref.set_global_lambda_warmup(warmup)
 
 
 def get_current_lambda() -> float:
-    return 1.0 if _global is None else _global.lambda_val
+    w = get_global_lambda_warmup()
+    return 1.0 if w is None else w.lambda_val

@@ -9,9 +9,11 @@
   packed weight explicitly (wrinklefree_inference/sglang_backend/bitnet_quantization.py:366-409).
 * ``BitNetLinearNative``: the patched module (wrinklefree_inference/kernels/bitnet_patch.py:28-78).
 
-Weights arrive in the I2_S block layout, as checkpoints of the reference store
-them; the kernels consume that layout directly.  No host synchronisation
-happens in ``apply`` (the reference calls ``scale.item()`` per call).
+The SGLang plug-in's weights arrive in the I2_S block layout, as checkpoints of
+the reference store them; the kernels consume that layout directly.  The two
+first-party classes take the byte orders of their own packers (sequential,
+MSB-first and LSB-first) and convert once.  No host synchronisation happens in
+``apply`` (the reference calls ``scale.item()`` per call).
 """
 from __future__ import annotations
 
@@ -115,12 +117,36 @@ class BitNetLinearMethod:
         return ops.bitlinear(x, layer.qweight, layer.scale, bias=bias, layout=L.LAYOUT_I2S, out_dtype=torch.float32)
 
 
-class PackedBitNetLinearMethod:
-    """First-party signature: apply(packed_weight, scale, x, out_features, in_features, bias)."""
+def _kernel_copy(packed: torch.Tensor, layout: int, n: int, k: int) -> torch.Tensor:
+    """Packed weights in a layout the kernels consume: WF16 / I2S as they are, the sequential and HF
+    layouts converted once on the GPU."""
+    if layout in (L.LAYOUT_WF16, L.LAYOUT_I2S):
+        return packed if packed.is_contiguous() else packed.contiguous()
+    return ops.repack(packed, layout, n, k, L.LAYOUT_WF16)
 
-    def __init__(self, compute_dtype: torch.dtype = torch.bfloat16, layout: int = L.LAYOUT_I2S):
+
+class PackedBitNetLinearMethod:
+    """First-party signature: apply(packed_weight, scale, x, out_features, in_features, bias)
+    (wrinklefree_inference/sglang_backend/bitnet_quantization.py:366-409).
+
+    `packed_weight` holds the bytes that interface's own packer emits: `quantize_to_bitnet` writes four consecutive
+    weights per byte, first weight in the top bit pair (L.LAYOUT_SEQ_MSB), which is the default here.  The bytes are
+    converted to the kernels' layout once per tensor and the copy is cached (keyed like the reference's cache of
+    dequantized weights, by tensor identity; `clear_cache` drops it).  Activations are quantized to int8 per token
+    (W2A8), where the reference multiplies dequantized weights in bf16."""
+
+    def __init__(self, compute_dtype: torch.dtype = torch.bfloat16, layout: int = L.LAYOUT_SEQ_MSB):
         self.compute_dtype = compute_dtype
         self.layout = layout
+        self._cache: Dict[tuple, torch.Tensor] = {}
+
+    def _kernel_weight(self, packed: torch.Tensor, n: int, k: int) -> torch.Tensor:
+        key = (packed.data_ptr(), packed._version, n, k, packed.device)
+        hit = self._cache.get(key)
+        if hit is None:
+            hit = _kernel_copy(packed, self.layout, n, k)
+            self._cache[key] = hit
+        return hit
 
     def apply(self, packed_weight: torch.Tensor, scale, x: torch.Tensor, out_features: int, in_features: int,
               bias: Optional[torch.Tensor] = None, sparsity_config=None) -> torch.Tensor:
@@ -128,27 +154,112 @@ class PackedBitNetLinearMethod:
             raise NotImplementedError("activation sparsity is not part of the CUDA path")
         if packed_weight.shape != (out_features, in_features // 4):
             raise ValueError(f"packed_weight shape {tuple(packed_weight.shape)} != ({out_features}, {in_features // 4})")
-        return ops.bitlinear(x.to(self.compute_dtype), packed_weight, scale, bias=bias, layout=self.layout,
-                             out_dtype=self.compute_dtype)
+        codes = self._kernel_weight(packed_weight, out_features, in_features)
+        lay = self.layout if self.layout in (L.LAYOUT_WF16, L.LAYOUT_I2S) else L.LAYOUT_WF16
+        return ops.bitlinear(x.to(self.compute_dtype), codes, scale, bias=bias, layout=lay, out_dtype=self.compute_dtype)
 
-    def clear_cache(self):  # the reference caches dequantized weights; nothing is cached here
-        pass
+    def clear_cache(self):
+        self._cache.clear()
+
+
+def quantize_to_bitnet(weights: torch.Tensor, block_size: int = BITNET_BLOCK_SIZE):
+    """GPU twin of quantize_to_bitnet (sglang_backend/bitnet_quantization.py:69-109): (packed uint8 [N, K/4] in the
+    SEQ_MSB byte order, scale = max|w| as a float32 tensor [1] on the device - no host synchronisation)."""
+    if weights.shape[1] % block_size != 0:
+        raise ValueError(f"in_features must be divisible by {block_size}")
+    return ops.quantize_maxabs(weights, "half", L.LAYOUT_SEQ_MSB)
+
+
+def dequantize_bitnet(packed: torch.Tensor, scale, out_features: int, in_features: int,
+                      layout: int = L.LAYOUT_SEQ_MSB) -> torch.Tensor:
+    """float32 [N, K] = ternary * scale (sglang_backend/bitnet_quantization.py:211-252), unpacked on the GPU."""
+    t = ops.unpack_codes(packed, out_features, in_features, layout).to(torch.float32)
+    return t * (scale if isinstance(scale, torch.Tensor) else float(scale))
+
+
+def pack_ternary_weights(weight: torch.Tensor):
+    """GPU twin of pack_ternary_weights (wrinklefree_inference/kernels/bitnet_patch.py:81-112): rounds to
+    {-1, 0, 1}, packs four consecutive weights per byte, first weight in the low bit pair (L.LAYOUT_SEQ_LSB);
+    scale = max|w| (below 1e-6: 1) as a float32 device tensor."""
+    if weight.shape[1] % 4 != 0:
+        raise ValueError(f"in_features ({weight.shape[1]}) must be divisible by 4")
+    t = torch.round(weight.float()).clamp_(-1, 1).to(torch.int8)
+    mx = weight.abs().max().float()
+    return ops.pack_codes(t, L.LAYOUT_SEQ_LSB), torch.where(mx < 1e-6, torch.ones_like(mx), mx)
 
 
 class BitNetLinearNative(nn.Module):
-    """Linear layer on packed 2-bit weights (I2_S layout by default)."""
+    """Linear layer on packed 2-bit weights (wrinklefree_inference/kernels/bitnet_patch.py:28-78).  `packed_weight`
+    arrives in the byte order of the packer that sits next to that class, `pack_ternary_weights` (L.LAYOUT_SEQ_LSB);
+    pass layout=L.LAYOUT_I2S for checkpoints in the block layout.  A kernel-layout copy is made once at construction;
+    the original bytes stay in the `packed_weight` buffer (state_dict compatible)."""
 
     def __init__(self, in_features: int, out_features: int, packed_weight: torch.Tensor, weight_scale: torch.Tensor,
-                 bias: Optional[torch.Tensor] = None, layout: int = L.LAYOUT_I2S):
+                 bias: Optional[torch.Tensor] = None, layout: int = L.LAYOUT_SEQ_LSB, act_quant: str = "per_token"):
         super().__init__()
-        self.in_features, self.out_features, self.layout = in_features, out_features, layout
+        self.in_features, self.out_features, self.layout, self.act_quant = in_features, out_features, layout, act_quant
         self.register_buffer("packed_weight", packed_weight)
         self.register_buffer("weight_scale", weight_scale.reshape(-1).to(torch.float32))
         if bias is not None:
             self.register_buffer("bias", bias)
         else:
             self.bias = None
+        self._kernel = None  # (key, codes in a kernel layout)
+
+    def _codes(self) -> torch.Tensor:
+        pw = self.packed_weight
+        key = (pw.data_ptr(), pw._version, pw.device)
+        if self._kernel is None or self._kernel[0] != key:
+            self._kernel = (key, _kernel_copy(pw, self.layout, self.out_features, self.in_features))
+        return self._kernel[1]
 
     def forward(self, x: torch.Tensor) -> torch.Tensor:
-        return ops.bitlinear(x, self.packed_weight, self.weight_scale, bias=self.bias, layout=self.layout,
-                             out_dtype=torch.float32 if x.dtype == torch.float32 else x.dtype)
+        lay = self.layout if self.layout in (L.LAYOUT_WF16, L.LAYOUT_I2S) else L.LAYOUT_WF16
+        out_dtype = torch.float32 if x.dtype == torch.float32 else x.dtype
+        if self.act_quant == "per_tensor":  # the arithmetic of the class this mirrors: one scale for the whole batch
+            q, s = ops.quantize_activations_i8(x.reshape(-1, self.in_features))
+            out = ops.bitlinear(q, self._codes(), self.weight_scale, layout=lay, out_dtype=torch.float32) * s
+            out = out + self.bias if self.bias is not None else out
+            return out.to(out_dtype).reshape(*x.shape[:-1], self.out_features)
+        return ops.bitlinear(x, self._codes(), self.weight_scale, bias=self.bias, layout=lay, out_dtype=out_dtype)
+
+
+def patch_model_with_native_kernels(model: nn.Module) -> int:
+    """Replaces every linear-like module that carries packed uint8 weights (attribute `weight` of dtype uint8 with a
+    `weight_scale` or `scale`) or float weights that are already ternary by a BitNetLinearNative
+    (wrinklefree_inference/kernels/bitnet_patch.py:165-210).  Returns the number of modules replaced."""
+    if not ops.check_kernel_available():
+        return 0
+    patched = 0
+    for name, module in list(model.named_modules()):
+        if not (isinstance(module, nn.Linear) or "Linear" in type(module).__name__) or isinstance(module, BitNetLinearNative):
+            continue
+        w = getattr(module, "weight", None)
+        if w is None or w.numel() == 0:
+            continue
+        w = w.data
+        if w.dtype == torch.uint8:
+            packed = w
+            sc = getattr(module, "weight_scale", None)
+            sc = sc if sc is not None else getattr(module, "scale", None)
+            scale = sc.data if sc is not None else torch.ones(1, device=w.device)
+        else:
+            r = torch.round(w.float())
+            if not bool(((r.abs() <= 1) & ((w.float() - r).abs() < 1e-6)).all()):
+                continue  # not ternary: left alone, as the reference does
+            packed, scale = pack_ternary_weights(w)  # max|w| of ternary values is 1 (all-zero: 1 as well)
+            scale = scale.reshape(1)
+        n, k = packed.shape[0], packed.shape[1] * 4
+        if k % BITNET_BLOCK_SIZE != 0:
+            continue
+        bias = module.bias.data if getattr(module, "bias", None) is not None else None
+        native = BitNetLinearNative(k, n, packed, scale.to(w.device), bias)
+        parent = model.get_submodule(".".join(name.split(".")[:-1])) if "." in name else model
+        setattr(parent, name.split(".")[-1], native)
+        patched += 1
+    return patched
+
+
+def create_bitnet_config(**kwargs) -> BitNetConfig:
+    """Factory kept from sglang/srt/layers/quantization/bitnet.py:259-261."""
+    return BitNetConfig(**kwargs)

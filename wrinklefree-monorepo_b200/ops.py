@@ -88,6 +88,26 @@ def repack(src: torch.Tensor, src_layout: int, n: int, k: int, dst_layout: int =
     return dst
 
 
+def quantize_maxabs(weight: torch.Tensor, rule: str = "half", layout: int = L.LAYOUT_SEQ_MSB) -> Tuple[torch.Tensor, torch.Tensor]:
+    """The max-abs quantizers of the inference side on the GPU: returns (packed uint8 [N, K/4] in `layout`,
+    scale float32 [1] = max|w|).  rule "half": codes by thresholds at +-0.5 of w / max (quantize_to_bitnet,
+    sglang_backend/bitnet_quantization.py:69-109, whose bytes are SEQ_MSB); rule "sign": codes by sign with a
+    1e-6 dead zone (quantize_i2_s, BitNet/src/ggml-bitnet-mad.cpp:46-92, whose bytes are I2S)."""
+    _need_cuda(weight)
+    if weight.dim() != 2:
+        raise ValueError("quantize_maxabs expects a 2-D weight")
+    if weight.stride(1) != 1:
+        weight = weight.contiguous()
+    n, k = weight.shape
+    codes = torch.empty((n, k // 4), dtype=torch.uint8, device=weight.device)
+    scale = torch.empty(2, dtype=torch.float32, device=weight.device)
+    with torch.cuda.device(weight.device):
+        L.check(L.lib().wf_quantize_maxabs(weight.data_ptr(), _DT[weight.dtype], n, k, weight.stride(0),
+                                           L.MAXABS_HALF if rule == "half" else L.MAXABS_SIGN, layout, codes.data_ptr(),
+                                           scale.data_ptr(), _stream()), "wf_quantize_maxabs")
+    return codes, scale[:1]
+
+
 def pack_codes(ternary: torch.Tensor, layout: int = L.LAYOUT_WF16) -> torch.Tensor:
     """Pack int8 values in {-1, 0, 1} [N, K] into a kernel layout."""
     _need_cuda(ternary)
@@ -338,7 +358,8 @@ def add_rmsnorm_(h: torch.Tensor, delta: Optional[torch.Tensor], weight: torch.T
 
 def rope_kv_(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, cos: torch.Tensor, sin: torch.Tensor, pos: torch.Tensor,
              kcache: torch.Tensor, vcache: torch.Tensor, pdl: bool = False):
-    """Decode-step RoPE of q (in place) and k, and the write of k, v into caches [B, nkv, T, D] at *pos % T."""
+    """Decode-step RoPE of q (in place) and k, and the write of k, v into caches [B, nkv, T, D] at position *pos, which the
+    caller keeps below T (cache slot and rotary angle both come from it)."""
     _need_cuda(q, k, v, cos, sin, pos, kcache, vcache)
     b, nkv, t, d = kcache.shape
     nq = q.numel() // (b * d)
