@@ -38,7 +38,11 @@ BATCHES = [1, 4, 16, 64]
 LAYERS = {(2560, 2560): 120, (6912, 2560): 60, (2560, 6912): 30}
 METRIC = "ternary_decode_gemv_GBps"
 GEMM_MIN_M = 16  # token batches from here on run on the tensor-core contraction (one batched launch per layer stack)
-NCU_TRAFFIC_RATIO = 203.52 / 197.84  # dram bytes / algorithmic bytes, profiles/decode_stream_kernel_m1_2560x2560.md
+REPEATS = 5      # the --steps region is timed this many times; the median is reported, with min and max
+# DRAM bytes (ncu dram__bytes_read.sum + dram__bytes_write.sum, one capture per stack, one launch) over the algorithmic
+# bytes of the same launch, for the streaming kernel's stacks: (shape index, M) -> ratio.  Stacks without a capture of
+# their own use the mean of the measured ones.
+NCU_TRAFFIC_RATIO = {(0, 1): 203.52 / 197.84}
 
 
 def algorithmic_bytes(m: int, n: int, k: int) -> int:
@@ -196,9 +200,20 @@ def capture(torch, fn):
 
 
 # ------------------------------------------------------------------ CPU reference arm
-def cpu_reference_run(steps: int, warmup: int, nl: int = 2):
-    """Times the reference's own CPU kernel (bitnet_gemm_i2_i8 compiled from its sources, behind
-    oracle/_ref) on a bounded sample of the sweep; falls back to the C port of the oracle."""
+def host_threads() -> int:
+    """Cores this process may use (a launcher may have exported OMP_NUM_THREADS=1: the thread count is set explicitly)."""
+    try:
+        return len(os.sched_getaffinity(0))
+    except AttributeError:
+        return os.cpu_count() or 1
+
+
+def cpu_reference_run(steps: int, warmup: int, layers_scale: float = 1.0):
+    """Times the reference's own CPU path on the sweep: per layer and token batch `quantize_activations_i8` of the fp32
+    activations, then `bitnet_gemm_i2_i8` on I2_S weights (its bitnet_gemv.cpp compiled from its sources behind
+    oracle/_ref, all host threads); falls back to the C port of the oracle when no compiled reference is present.
+    The stacks have the benchmark's full layer counts; their weights are two random matrices per shape repeated through
+    one contiguous buffer (distinct addresses, so the host caches see the same footprint as distinct layers)."""
     import numpy as np
 
     from oracle import bitlinear_oracle as O
@@ -207,48 +222,130 @@ def cpu_reference_run(steps: int, warmup: int, nl: int = 2):
     ref = load_reference()
     kind = "reference" if ref is not None else "port"
     port = load_oracle()
-    cores = ref.num_threads() if ref is not None else port.num_threads()
+    cores = host_threads()
+    if ref is not None:
+        ref.set_num_threads(cores)
+        cores = ref.num_threads()
+    else:
+        cores = port.num_threads()
     rng = np.random.default_rng(0)
-    # nl layers per shape in the sample, rotated so the weights do not stay in the cores' L1/L2
     work = []
     for (n, k) in SHAPES:
-        mats = []
-        for _ in range(nl):
-            t = rng.integers(-1, 2, size=(n, k)).astype(np.int8)
-            mats.append(O.pack_i2s(t) if ref is not None else port.pack_wf16(t))
+        nl = max(2, int(LAYERS[(n, k)] * layers_scale))
+        base = []
+        for _ in range(2):  # N(0, 0.02) weights, absmean-ternarized
+            w = (rng.standard_normal((n, k)) * 0.02).astype(np.float32)
+            t = port.ternarize(w, port.absmean(w))
+            base.append(O.pack_i2s(t) if ref is not None else port.pack_wf16(t))
+        stack = np.empty((nl,) + base[0].shape, dtype=np.uint8)
+        for li in range(nl):
+            stack[li] = base[li % 2]
         for m in BATCHES:
-            q = rng.integers(-127, 128, size=(m, k)).astype(np.int8)
-            work.append((n, k, m, mats, q))
+            x = rng.standard_normal((m, k)).astype(np.float32)  # N(0, 1) with 0.1 % outliers at +-20, bf16 values
+            out_mask = rng.random((m, k)) < 1e-3
+            x = np.where(out_mask, np.where(rng.random((m, k)) < 0.5, -20.0, 20.0), x).astype(np.float32)
+            work.append((n, k, m, stack, O.bf16_round(x)))
 
     def one_step():
-        for (n, k, m, mats, q) in work:
-            for p in mats:
+        for (n, k, m, stack, x) in work:
+            for li in range(stack.shape[0]):
                 if ref is not None:
-                    ref.gemm(p, q, 0.02)
+                    q, s = ref.quantize_activations(x)
+                    ref.gemm(stack[li], q, 0.02 * float(s))
                 else:
-                    port.gemm_wf16(q, p)
+                    q, s = port.act_quant(x, 0)
+                    port.gemm_wf16(q, stack[li])
 
-    bytes_step = sum(algorithmic_bytes(m, n, k) * nl for (n, k, m, _, _) in work)
+    bytes_step = sum(algorithmic_bytes(m, n, k) * stack.shape[0] for (n, k, m, stack, _) in work)
     for _ in range(warmup):
         one_step()
     t0 = time.perf_counter()
     for _ in range(steps):
         one_step()
     dt = (time.perf_counter() - t0) / steps
-    sample = (f"{nl} layers per shape x 3 shapes x M in {BATCHES}, int8 activations already quantized, "
-              f"{steps} steps of {dt * 1e3:.1f} ms; kernel: " +
-              ("bitnet_gemm_i2_i8 (AVX-%s build of the reference's bitnet_gemv.cpp, OpenMP)" % ref.flavour.replace("avx", "")
+    sample = (f"the full sweep ({[w[3].shape[0] for w in work[::len(BATCHES)]]} layers per shape x M in {BATCHES}), fp32 activations "
+              f"quantized inside the timed loop, {steps} steps of {dt * 1e3:.1f} ms after {warmup} warm-up; kernel: " +
+              ("quantize_activations_i8 + bitnet_gemm_i2_i8 (AVX-%s build of the reference's bitnet_gemv.cpp, OpenMP)" % ref.flavour.replace("avx", "")
                if ref is not None else "scalar C port of the oracle (OpenMP)"))
     return dict(value=bytes_step / dt / 1e9, unit="GB/s", cores=cores, kind=kind, sample=sample), steps, warmup, dt
+
+
+def cpu_other_baselines():
+    """The two other CPU paths the reference has for this operator, on a bounded sample (one layer per shape and token
+    batch), same byte accounting: the PyTorch BitLinear forward (restated in oracle/torch_bitlinear.py: it re-ternarizes
+    the fp32 weight on every call) and BitNet.cpp's ggml_vec_dot_i2_i8_s in an OpenMP row loop (oracle/_ref)."""
+    import numpy as np
+    import torch
+
+    from oracle import bitlinear_oracle as O
+    from oracle import torch_bitlinear as TB
+    from oracle.clib import load_ggml_reference
+
+    out = []
+    cores = host_threads()
+    torch.set_num_threads(cores)
+    rng = np.random.default_rng(1)
+    g = torch.Generator().manual_seed(1)
+    for dt_name, dt in (("bf16", torch.bfloat16), ("f32", torch.float32)):
+        tot_b, tot_t = 0, 0.0
+        for (n, k) in [(1536, 576)] + SHAPES:
+            w = torch.randn(n, k, generator=g) * 0.02
+            for m in ([16] if (n, k) == (1536, 576) else BATCHES):
+                x = torch.randn(m, k, generator=g).to(dt)
+                with torch.no_grad():
+                    TB.bitlinear_forward(x, w)
+                    t0 = time.perf_counter()
+                    TB.bitlinear_forward(x, w)
+                    tot_t += time.perf_counter() - t0
+                tot_b += algorithmic_bytes(m, n, k)
+        out.append(dict(kind="port", path=f"PyTorch BitLinear.forward ({dt_name} input, weight re-ternarized per call)", cores=cores,
+                        value=tot_b / tot_t / 1e9, unit="GB/s", sample="one layer per shape (config-1 shape and the three sweep shapes) and token batch"))
+    gg = load_ggml_reference()
+    if gg is not None:
+        gg.set_num_threads(cores)
+        tot_b, tot_t = 0, 0.0
+        for (n, k) in SHAPES:
+            if k % 128:
+                continue
+            packed = O.pack_i2s(rng.integers(-1, 2, size=(n, k)).astype(np.int8))
+            for m in BATCHES:
+                q = rng.integers(-127, 128, size=(m, k)).astype(np.int8)
+                sums, scales = q.astype(np.int64).sum(1).astype(np.float32), np.full(m, 30.0, np.float32)
+                gg.mul_mat(packed, q, sums, scales, 0.02)
+                t0 = time.perf_counter()
+                gg.mul_mat(packed, q, sums, scales, 0.02)
+                tot_t += time.perf_counter() - t0
+                tot_b += algorithmic_bytes(m, n, k)
+        out.append(dict(kind="reference", path="BitNet.cpp ggml_vec_dot_i2_i8_s in an OpenMP row loop (AVX2 build of ggml-bitnet-mad.cpp)",
+                        cores=gg.num_threads(), value=tot_b / tot_t / 1e9, unit="GB/s", sample="one layer per sweep shape and token batch, int8 activations given"))
+    else:
+        out.append(dict(kind="reference", path="BitNet.cpp ggml_vec_dot_i2_i8_s", unavailable="oracle/_ref holds no build of it on this host"))
+    return out
 
 
 # ------------------------------------------------------------------ prefill GEMM (secondary figures of the same line)
 PREFILL_M = [512, 2048, 8192]
 
 
-def prefill_section(wf, torch, device, peaks, shapes=None, ms=None):
+def int8_peak(wf):
+    """Measured int8 tensor-core rate of this GPU (TOPS): every SM issues tcgen05.mma.kind::i8 M128 N256 K32 on operands
+    resident in shared memory (the library's wf_probe_i8_mma); also the time per instruction at N = 16 and 64."""
+    import ctypes as C
+
+    lib = wf._lib.lib()
+    res = {}
+    for n in (256, 128, 64, 16):
+        tops, ns = C.c_double(0), C.c_double(0)
+        wf._lib.check(lib.wf_probe_i8_mma(n, 20000, C.byref(tops), C.byref(ns)), "wf_probe_i8_mma")
+        res[n] = (tops.value, ns.value)
+    return {"tops_n256": round(res[256][0], 1), "tops_n128": round(res[128][0], 1),
+            "ns_per_mma": {str(n): round(res[n][1], 2) for n in res}}
+
+
+def prefill_section(wf, torch, device, peak_tops, shapes=None, ms=None):
     """int8 x ternary GEMM on tcgen05 at the sweep's shapes: TOPS = 2*M*N*K / time, for the whole operator
-    (activation quantization + contraction) with bf16 activations resident in HBM."""
+    (activation quantization + contraction) with bf16 activations resident in HBM.  Fractions: of the measured
+    int8 rate (`peak_tops`, see int8_peak) and of the nominal 4500 TOPS."""
     out = []
     gd = torch.Generator(device=device).manual_seed(4242)
     for (n, k) in (shapes or [(2560, 2560), (6912, 2560), (2560, 6912)]):
@@ -261,24 +358,152 @@ def prefill_section(wf, torch, device, peaks, shapes=None, ms=None):
                 graph.replay()
             torch.cuda.synchronize()
             a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-            reps = 10
-            a.record()
-            for _ in range(reps):
-                graph.replay()
-            b.record()
-            torch.cuda.synchronize()
-            us = a.elapsed_time(b) * 1e3 / reps
+            reps, samples = 10, []
+            for _ in range(3):
+                a.record()
+                for _ in range(reps):
+                    graph.replay()
+                b.record()
+                torch.cuda.synchronize()
+                samples.append(a.elapsed_time(b) * 1e3 / reps)
+            us = statistics.median(samples)
             tops = 2.0 * m * n * k / us / 1e6
             out.append({"N": n, "K": k, "M": m, "us": round(us, 2), "TOPS": round(tops, 1),
-                        "frac_of_2x_measured_bf16": round(tops / (2 * peaks["bf16_tflops"]), 4),
+                        "frac_of_measured_int8": round(tops / peak_tops, 4),
                         "frac_of_nominal_int8_4500": round(tops / 4500.0, 4)})
     return out
+
+
+# ------------------------------------------------------------------ the plug-in call, end to end
+def plugin_e2e(wf, torch, device, steps: int, n: int = 2560, k: int = 2560, m: int = 16, nl: int = 120):
+    """One stack of the sweep driven the way a serving framework drives the layer: per layer
+    `BitNetLinearMethod.apply(layer, x)` on I2_S weights registered by `create_weights`, with that layer's activations
+    copied from pinned host memory before the call and its fp32 output copied back after it, every step."""
+    import inputs as gi
+
+    method = wf.BitNetLinearMethod(wf.BitNetConfig())
+    gd = torch.Generator(device=device).manual_seed(77)
+    layers = []
+    for _ in range(nl):
+        codes, scale = wf.pack_ternary(torch.randn(n, k, generator=gd, device=device) * 0.02)
+        layer = torch.nn.Module()
+        method.create_weights(layer, k, [n], k, n, torch.bfloat16)
+        layer = layer.to(device)
+        layer.qweight.data.copy_(wf.repack(codes, wf._lib.LAYOUT_WF16, n, k, wf._lib.LAYOUT_I2S))
+        layer.scale.data.copy_(scale[:1])
+        method.process_weights_after_loading(layer)
+        layers.append(layer)
+    g = torch.Generator().manual_seed(78)
+    x_host = gi.with_outliers(torch.randn(nl, m, k, generator=g), seed=78).to(torch.bfloat16).pin_memory()
+    y_host = torch.empty(nl, m, n, dtype=torch.float32).pin_memory()
+    x_dev = torch.empty(nl, m, k, dtype=torch.bfloat16, device=device)
+
+    def step():
+        for li, layer in enumerate(layers):
+            x_dev[li].copy_(x_host[li], non_blocking=True)
+            y_host[li].copy_(method.apply(layer, x_dev[li]), non_blocking=True)
+
+    for _ in range(2):
+        step()
+    torch.cuda.synchronize()
+    samples = []
+    for _ in range(3):
+        a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        a.record()
+        for _ in range(steps):
+            step()
+        b.record()
+        torch.cuda.synchronize()
+        samples.append(a.elapsed_time(b) / steps)
+    ms = statistics.median(samples)
+    return {"call": "BitNetLinearMethod.apply(layer, x) per layer, I2_S weights", "stack": f"{nl} layers of {n}x{k}, M = {m}",
+            "ms_per_step": round(ms, 4), "us_per_layer": round(ms * 1e3 / nl, 3),
+            "value": algorithmic_bytes(m, n, k) * nl / (ms * 1e-3) / 1e9, "unit": "GB/s",
+            "h2d_bytes_per_step": x_host.numel() * 2, "d2h_bytes_per_step": y_host.numel() * 4}
+
+
+# ------------------------------------------------------------------ tensor-parallel parity (multi-rank runs)
+def tp_parity_check(wf, torch, dist, device, rank: int, world: int) -> str:
+    """One small fixed case per rank, checked against the CPU oracle before anything is timed: the accumulators of
+    this rank's column shard and of its row (K) shard bit for bit, the gathered column-parallel output and the reduced
+    row-parallel output identical on all ranks, the reduced output within 1e-2 (max|a-b| / max|b|) of the unsharded
+    result, and one round of the peer-memory all-reduce against the library all-reduce.  Returns "ok" or the first
+    failure; the oracle is the checker here, nothing of it is timed."""
+    import numpy as np
+
+    from oracle.clib import load_oracle
+    from wrinklefree_monorepo_b200 import tp
+
+    try:
+        oc = load_oracle()
+        n, k, m = 128 * world, 512 * world, 5
+        g = torch.Generator().manual_seed(4321)
+        w = torch.randn(n, k, generator=g) * 0.02
+        x = torch.randn(m, k, generator=g).bfloat16()
+        codes, scale = wf.pack_ternary(w.to(device))
+        t = wf.unpack_codes(codes, n, k).cpu().numpy()
+        s_w = float(scale[0])
+        q_full, s_full = oc.act_quant(x.float().numpy(), 1)
+        y_full = oc.rescale(oc.int_gemm(q_full, t), s_full, s_w)
+        fails = []
+        # column-parallel: rows of this rank
+        col = tp.ColumnParallelBitLinear(codes, scale, k, n, gather_output=True)
+        lo, hi = col.bounds[rank]
+        _, acc = wf.bitlinear(x.to(device), col.codes, scale, want_acc=True, out_dtype=torch.float32)
+        if not np.array_equal(acc.cpu().numpy(), oc.int_gemm(q_full, t[lo:hi])):
+            fails.append("column shard accumulators differ from the oracle")
+        yc = col(x.to(device), out_dtype=torch.float32)
+        if not np.array_equal(yc.cpu().numpy(), y_full):
+            fails.append("gathered column-parallel output differs from the oracle")
+        # row-parallel: K slice of this rank, local activation scales
+        row = tp.RowParallelBitLinear(codes, scale, k, n, reduce_dtype=torch.float32)
+        k0, k1 = row.bounds[rank]
+        x_loc = x[:, k0:k1].contiguous()
+        q_loc, s_loc = oc.act_quant(x_loc.float().numpy(), 1)
+        y_part, acc = wf.bitlinear(x_loc.to(device), row.codes, scale, want_acc=True, out_dtype=torch.float32)
+        if not np.array_equal(acc.cpu().numpy(), oc.int_gemm(q_loc, t[:, k0:k1])):
+            fails.append("row shard accumulators differ from the oracle")
+        if not np.array_equal(y_part.cpu().numpy(), oc.rescale(oc.int_gemm(q_loc, t[:, k0:k1]), s_loc, s_w)):
+            fails.append("row shard partial output differs from the oracle")
+        parts = [torch.empty_like(y_part) for _ in range(world)]
+        dist.all_gather(parts, y_part)
+        want = parts[0].clone()
+        for p_ in parts[1:]:
+            want += p_  # fixed rank order, fp32
+        yr = row(x_loc.to(device), out_dtype=torch.float32)  # library all-reduce
+        err = float((yr.cpu() - torch.from_numpy(y_full)).abs().max() / np.abs(y_full).max())
+        if err > 1e-2:
+            fails.append(f"reduced row-parallel output off the unsharded result by {err:.3e}")
+        one = tp.OneShotAllReduce()
+        row2 = tp.RowParallelBitLinear(codes, scale, k, n, reduce_dtype=torch.float32, all_reduce=one)
+        yo = row2(x_loc.to(device), out_dtype=torch.float32)
+        if one._ctx is not None and not torch.equal(yo, want):
+            fails.append("peer-memory all-reduce differs from the rank-ordered fp32 sum")
+        for name, y_ in (("library", yr), ("peer-memory", yo)):
+            allr = [torch.empty_like(y_) for _ in range(world)]
+            dist.all_gather(allr, y_)
+            if any(not torch.equal(allr[0], a_) for a_ in allr[1:]):
+                fails.append(f"{name} all-reduce: ranks hold different bits")
+        b = torch.randn(64, 4096, generator=torch.Generator().manual_seed(rank)).bfloat16().to(device)
+        b1, b2 = b.clone(), b.clone()
+        one(b1)
+        dist.all_reduce(b2)
+        if float((b1.float() - b2.float()).abs().max()) > 2e-2 * float(b2.float().abs().max()):
+            fails.append("peer-memory all-reduce (bf16) off the library all-reduce")
+        one.status()
+        ok = torch.tensor([0 if fails else 1], device=device)
+        dist.all_reduce(ok, op=dist.ReduceOp.MIN)
+        if fails:
+            return f"rank {rank}: " + "; ".join(fails)
+        return "ok" if int(ok.item()) == 1 else "a rank other than 0 failed (see its stderr)"
+    except Exception as e:  # the benchmark line must still be printed
+        return "error: " + repr(e)[:300]
 
 
 # ------------------------------------------------------------------ decoder tokens/s (secondary figures)
 def decoder_section(wf, torch, device, world, full: bool):
     """Greedy decode tokens/s of random-init ternary decoders on the BitLinear kernels (CUDA-graphed step):
-    Llama-3-8B shape at a 2048-token context for batch 1 and 32 (256 with --decoder-full), tensor-parallel over
+    Llama-3-8B shape at a 2048-token context for batch 1, 32 and 256 (--decoder-quick drops 256), tensor-parallel over
     the ranks; on one GPU also the SmolLM2-135M shape (batch 32, 512-token prompt, 128 steps)."""
     from wrinklefree_monorepo_b200.decoder import LLAMA3_8B, SMOLLM2_135M, TernaryDecoder
 
@@ -297,7 +522,7 @@ def decoder_section(wf, torch, device, world, full: bool):
         return a.elapsed_time(b) / steps
 
     for batch in ([1, 32, 256] if full else [1, 32]):
-        model = TernaryDecoder(LLAMA3_8B, batch, 2048, device, seed=7)
+        model = TernaryDecoder(LLAMA3_8B, batch, 2048 + 32, device, seed=7)  # room for the timed steps behind the context
         for L in model.layers:  # a context of 2048 random tokens' keys and values
             L["kc"].normal_()
             L["vc"].normal_()
@@ -311,7 +536,7 @@ def decoder_section(wf, torch, device, world, full: bool):
         del model
         torch.cuda.empty_cache()
     if world == 1:
-        model = TernaryDecoder(SMOLLM2_135M, 32, 640, device, seed=8)
+        model = TernaryDecoder(SMOLLM2_135M, 32, 512 + 160, device, seed=8)
         g = torch.Generator().manual_seed(9)
         ids = torch.randint(0, SMOLLM2_135M.vocab, (32, 512), generator=g).to(device)
         torch.cuda.synchronize()
@@ -355,7 +580,7 @@ def main():
     ap.add_argument("--prefill-only", action="store_true", help="run only the prefill GEMM section (profiling)")
     ap.add_argument("--no-decoder", action="store_true", help="skip the decoder tokens/s section")
     ap.add_argument("--decoder-only", action="store_true", help="run only the decoder tokens/s section (profiling)")
-    ap.add_argument("--decoder-full", action="store_true", help="also batch 256 of the 8B shape")
+    ap.add_argument("--decoder-quick", action="store_true", help="skip batch 256 of the 8B shape")
     ap.add_argument("--only-m", type=int, default=0, help="restrict the sweep to one token batch (profiling)")
     ap.add_argument("--only-shape", type=int, default=-1, help="restrict the sweep to one shape index (profiling)")
     ap.add_argument("--no-cpu-baseline", action="store_true")
@@ -365,13 +590,13 @@ def main():
     local_rank = int(os.environ.get("LOCAL_RANK", "0"))
     warmup = max(args.warmup, 3)
     config = {"workload": "decode_gemv_sweep", "shapes_NxK": ["%dx%d" % s for s in SHAPES], "batches_M": BATCHES,
-              "layers_per_shape": [LAYERS[s] for s in SHAPES], "activations": "bf16 N(0,1) + 0.1% outliers at +-20",
+              "layers_per_shape": [max(2, int(LAYERS[s] * args.layers_scale)) for s in SHAPES], "activations": "bf16 N(0,1) + 0.1% outliers at +-20",
               "weights": "N(0,0.02) absmean-ternarized, 2 bits/weight", "l2": "inputs larger than L2 (distinct weights per launch)"}
 
     if args.impl == "reference":
         if rank != 0:
             return
-        cb, steps, wu, dt = cpu_reference_run(args.steps, warmup)
+        cb, steps, wu, dt = cpu_reference_run(args.steps, warmup, args.layers_scale)
         line = {"impl": "reference", "metric": METRIC, "value": cb["value"], "unit": "GB/s", "n_gpus": args.gpus,
                 "steps": steps, "warmup": wu, "ms_per_step": dt * 1e3, "higher_is_better": True, "scaling": "strong",
                 "vs_baseline": None, "dtype": "u8xs8->s32", "data": "synthetic", "config": config, "cpu_baseline": cb,
@@ -408,13 +633,13 @@ def main():
             os.close(saved)
 
     if args.decoder_only:
-        res = decoder_section(wf, torch, device, world, args.decoder_full)
+        res = decoder_section(wf, torch, device, world, not args.decoder_quick)
         if rank == 0:
             print(json.dumps({"decode_tok_s": res}))
         return
     if args.prefill_only:
         peaks, _ = measured_peaks()
-        res = prefill_section(wf, torch, device, peaks, [SHAPES[args.only_shape]] if args.only_shape >= 0 else None,
+        res = prefill_section(wf, torch, device, int8_peak(wf)["tops_n256"], [SHAPES[args.only_shape]] if args.only_shape >= 0 else None,
                               [args.only_m] if args.only_m else None)
         print(json.dumps({"prefill_gemm": res}))
         return
@@ -443,23 +668,39 @@ def main():
             dist.barrier()
         torch.cuda.synchronize()
 
+    # ---- tensor-parallel parity evidence (every rank, before anything is timed)
+    tp_parity = None
+    if dist is not None:
+        note(rank, "tensor-parallel parity check")
+        tp_parity = tp_parity_check(wf, torch, dist, device, rank, world)
+
+    def timed_replays(gr, steps):
+        """REPEATS timings of `steps` replays each, on the device, max over ranks per repeat -> list of ms per step."""
+        out = []
+        for _ in range(REPEATS):
+            barrier()
+            a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            a.record()
+            for _ in range(steps):
+                gr.replay()
+            b.record()
+            barrier()
+            out.append(a.elapsed_time(b) / steps)
+        if dist is not None:
+            t = torch.tensor(out, device=device)
+            dist.all_reduce(t, op=dist.ReduceOp.MAX)
+            out = t.tolist()
+        return out
+
     note(rank, "device-resident timing")
-    # ---- device-resident timing
     for _ in range(warmup):
         graph.replay()
     sampler = ClockSampler(local_rank)
     if rank == 0:
         sampler.start()
         time.sleep(0.3)
-    barrier()  # after the sampler is up: no rank may enter the timed region ahead of the others
-    ev0, ev1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-    ev0.record()
-    for _ in range(args.steps):
-        graph.replay()
-    ev1.record()
-    barrier()
-    ms = ev0.elapsed_time(ev1) / args.steps
-    clocks = sampler.finish() if rank == 0 else None
+    ms_all = timed_replays(graph, args.steps)
+    ms = statistics.median(ms_all)
 
     note(rank, "end-to-end timing")
     # ---- end to end: pinned host activations in, outputs back to pinned host memory, every step
@@ -514,21 +755,29 @@ def main():
     for _ in range(3):
         e2e_step()
     e2e_join()
-    barrier()
-    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-    e0.record()
-    e2e_fork()
-    for _ in range(args.steps):
-        e2e_step()
-    e2e_join()
-    e1.record()
-    barrier()
-    ms_e2e = e0.elapsed_time(e1) / args.steps
-
+    e2e_all = []
+    for _ in range(REPEATS):
+        barrier()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        e2e_fork()
+        for _ in range(args.steps):
+            e2e_step()
+        e2e_join()
+        e1.record()
+        barrier()
+        e2e_all.append(e0.elapsed_time(e1) / args.steps)
     if dist is not None:
-        t = torch.tensor([ms, ms_e2e], device=device)
+        t = torch.tensor(e2e_all, device=device)
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
-        ms, ms_e2e = t.tolist()
+        e2e_all = t.tolist()
+    ms_e2e = statistics.median(e2e_all)
+    clocks = sampler.finish() if rank == 0 else None
+
+    # ---- the same through the plug-in call a serving framework makes (one stack, one GPU): per layer
+    # BitNetLinearMethod.apply(layer, x) on I2_S weights, host activations in, fp32 outputs back, every step
+    plugin = plugin_e2e(wf, torch, device, args.steps) if (world == 1 and not args.only_m and args.only_shape < 0) else None
+
     peaks, peak_kind = measured_peaks()
     # the whole (unsharded) sweep's algorithmic bytes over the slowest rank's time
     full_bytes = sum(algorithmic_bytes(g["m"], g["n"], g["k"]) * len(g["layers"]) for g in groups)
@@ -545,19 +794,7 @@ def main():
         gr = capture(torch, lambda: run_step(wf, gs, pdl))
         for _ in range(3):
             gr.replay()
-        barrier()
-        a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-        a.record()
-        for _ in range(args.steps):
-            gr.replay()
-        b.record()
-        barrier()
-        t = a.elapsed_time(b) / args.steps
-        if dist is not None:
-            tt = torch.tensor([t], device=device)
-            dist.all_reduce(tt, op=dist.ReduceOp.MAX)
-            t = tt.item()
-        return t
+        return statistics.median(timed_replays(gr, args.steps))
 
     note(rank, "timing kernel families")
     ms_dec, ms_gemm = time_groups(dec_groups), time_groups(gemm_groups)
@@ -568,6 +805,11 @@ def main():
     per_launch_bytes = step_bytes(dec_groups) / dec_launches / world if dec_groups else 0.0  # what one rank's kernel moves
     per_launch_us = (ms_dec or 0.0) * 1e3 / dec_launches
     achieved = per_launch_bytes / (per_launch_us * 1e-6) / 1e9 if dec_groups else 0.0
+    # DRAM traffic per launch from the ncu captures of these stacks (ratio to the algorithmic bytes, per stack)
+    mean_ratio = sum(NCU_TRAFFIC_RATIO.values()) / len(NCU_TRAFFIC_RATIO)
+    shape_idx = {s_: i_ for i_, s_ in enumerate([(2560, 2560), (6912, 2560), (2560, 6912)])}
+    traffic = sum(algorithmic_bytes(g["m"], g["n"], g["k"]) * len(g["layers"]) / world *
+                  NCU_TRAFFIC_RATIO.get((shape_idx.get((g["n"], g["k"]), -1), g["m"]), mean_ratio) for g in dec_groups) / dec_launches
     # per (shape, M) breakdown, each group timed alone over its own layer stack (every rank takes part: the
     # row-parallel groups contain the all-reduce)
     breakdown = []
@@ -578,13 +820,15 @@ def main():
             gr.replay()
         torch.cuda.synchronize()
         a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-        a.record()
-        reps = 10
-        for _ in range(reps):
-            gr.replay()
-        b.record()
-        torch.cuda.synchronize()
-        us = a.elapsed_time(b) * 1e3 / reps / len(g["layers"])
+        reps, samples = 10, []
+        for _ in range(3):
+            a.record()
+            for _ in range(reps):
+                gr.replay()
+            b.record()
+            torch.cuda.synchronize()
+            samples.append(a.elapsed_time(b) * 1e3 / reps / len(g["layers"]))
+        us = statistics.median(samples)
         # the same stack as one launch per layer, chained with programmatic dependent launch
         gs = capture(torch, lambda: run_step_single(wf, gg, pdl))
         for _ in range(3):
@@ -598,6 +842,7 @@ def main():
         us_single = a.elapsed_time(b) * 1e3 / reps / len(g["layers"])
         by = algorithmic_bytes(g["m"], g["n"], g["k"])
         breakdown.append({"N": g["n"], "K": g["k"], "M": g["m"], "layers": len(g["layers"]),
+                          "kernel": "prefill_kernel" if g["batched"] else "decode_stream_kernel",
                           "us_per_layer_grouped": round(us, 3), "GBps": round(by / us / 1e3, 1),
                           "frac_hbm": round(by / us / 1e3 / peaks["hbm_gbs"], 4),
                           "GBps_reference_accounting": round(reference_bytes(g["m"], g["n"], g["k"]) / us / 1e3, 1),
@@ -610,7 +855,7 @@ def main():
         torch.cuda.empty_cache()
         note(rank, "decoder section")
         try:
-            decoder = decoder_section(wf, torch, device, world, args.decoder_full)
+            decoder = decoder_section(wf, torch, device, world, not args.decoder_quick)
         except Exception as e:  # the main line must survive a failure of this secondary section
             decoder = [{"error": repr(e)[:300]}]
     note(rank, "done with collective phases")
@@ -618,34 +863,56 @@ def main():
         # stay in step with rank 0 (it still runs single-GPU sections): tear the group down together
         finish(dist, torch, rank)
         return
+    med = lambda v: {"median": round(statistics.median(v), 5), "min": round(min(v), 5), "max": round(max(v), 5), "repeats": len(v)}
     line = {"metric": METRIC, "value": value, "unit": "GB/s", "n_gpus": world, "steps": args.steps, "warmup": warmup,
-            "ms_per_step": ms, "higher_is_better": True, "scaling": "strong", "vs_baseline": None, "dtype": "u8xs8->s32",
-            "data": "synthetic", "config": dict(config, pdl=pdl, graph=True, parallelism=f"tp{world}" if world > 1 else "single"),
+            "ms_per_step": ms, "ms_per_step_repeats": med(ms_all), "higher_is_better": True, "scaling": "strong", "vs_baseline": None,
+            "dtype": "u8xs8->s32", "data": "synthetic", "config": config,
+            "launch": {"pdl": pdl, "graph": True, "parallelism": f"tp{world}" if world > 1 else "single"},
             "roofline": {"bound": "hbm", "achieved": achieved, "peak": peaks["hbm_gbs"], "unit": "GB/s",
-                         "frac": achieved / peaks["hbm_gbs"], "traffic": per_launch_bytes * NCU_TRAFFIC_RATIO,
-                         "traffic_source": "ncu capture of the M=1 2560x2560 group (203.5 MB DRAM for 197.8 MB algorithmic), scaled",
+                         "frac": achieved / peaks["hbm_gbs"], "frac_of_nominal_8000": achieved / 8000.0, "traffic": traffic,
+                         "traffic_source": "ncu dram__bytes_read.sum + dram__bytes_write.sum of one launch per stack, as a ratio to the "
+                                           "algorithmic bytes: " + ", ".join(f"shape {k_[0]} M={k_[1]}: {v_:.3f}" for k_, v_ in sorted(NCU_TRAFFIC_RATIO.items())) +
+                                           "; other stacks: their mean",
                          "peak_kind": peak_kind + " copy bandwidth",
                          "kernel": "decode_stream_kernel", "launches": f"the {dec_launches} grouped launches with M < {GEMM_MIN_M}",
                          "bytes_per_launch": per_launch_bytes, "us_per_launch": per_launch_us},
             "e2e": {"value": full_bytes / (ms_e2e * 1e-3) / 1e9, "unit": "GB/s", "h2d_bytes_per_step": h2d,
-                    "d2h_bytes_per_step": d2h, "ms_per_step": ms_e2e},
+                    "d2h_bytes_per_step": d2h, "ms_per_step": ms_e2e, "ms_per_step_repeats": med(e2e_all),
+                    "call": "ops.DecodeGroup.run / ops.bitlinear_batched per stack (ctypes -> C ABI), pinned host buffers, three streams"},
             "gpu_launches": launches * args.steps, "clocks": clocks, "breakdown": breakdown}
+    if plugin is not None:
+        line["e2e"]["plugin"] = plugin
+    if tp_parity is not None:
+        line["tp_parity"] = tp_parity
+    i8 = None
+    if world == 1 or rank == 0:
+        try:
+            i8 = int8_peak(wf)
+            line["int8_peak_measured"] = i8
+        except Exception as e:
+            line["int8_peak_measured"] = {"error": repr(e)[:200]}
+    peak_tops = i8["tops_n256"] if i8 else 4500.0
     if n_gemm_groups and ms_gemm:
         tops = gemm_ops / (ms_gemm * 1e-3) / 1e12
         line["roofline_gemm"] = {"bound": "tensor", "kernel": "prefill_kernel (batched over each layer stack)",
                                  "launches": f"the {n_gemm_groups} stacks with M >= {GEMM_MIN_M}", "achieved": tops,
-                                 "unit": "TOPS", "peak": 2 * peaks["bf16_tflops"],
-                                 "peak_kind": "2 x measured bf16 burst (int8 dense proxy; nominal 4500)",
-                                 "frac": tops / (2 * peaks["bf16_tflops"]), "ms": ms_gemm,
-                                 "note": "useful ops 2*M*N*K; the 128-token MMA tile is partly padding at M = 16 and 64"}
+                                 "unit": "TOPS", "peak": peak_tops,
+                                 "peak_kind": "measured tcgen05.mma.kind::i8 rate (M128 N256 K32, operands resident)" if i8 else "nominal",
+                                 "frac": tops / peak_tops, "frac_of_nominal_4500": tops / 4500.0, "ms": ms_gemm,
+                                 "note": "useful ops 2*M*N*K; at M = 16 / 64 these stacks are bound by weight streaming and the "
+                                         "instruction issue rate, not by the tensor rate"}
     if decoder is not None:
         line["decode_tok_s"] = decoder
     if not args.only_m and args.only_shape < 0:
         note(rank, "prefill GEMM section")
-        line["prefill_gemm"] = prefill_section(wf, torch, device, peaks)
+        line["prefill_gemm"] = prefill_section(wf, torch, device, peak_tops)
         note(rank, "prefill GEMM section done")
     if not args.no_cpu_baseline and world == 1:
-        cb, _, _, _ = cpu_reference_run(3, 1)
+        cb, _, _, _ = cpu_reference_run(3, 1, args.layers_scale)
+        try:
+            cb["others"] = cpu_other_baselines()
+        except Exception as e:
+            cb["others"] = [{"error": repr(e)[:200]}]
         line["cpu_baseline"] = cb
     print(json.dumps(line), flush=True)
     if dist is not None:

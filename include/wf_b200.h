@@ -67,6 +67,15 @@ const char* wf_last_error(void);
 int wf_device_check(void);
 
 /*
+ * Measurement aid, no counterpart in the reference: the rate of the int8 tensor-core instruction on the current
+ * device.  Every SM issues 4 * iters tcgen05.mma.kind::i8 (M = 128, N = n, K = 32) on operands resident in shared
+ * memory; *tops_out receives 2 * 128 * n * 32 operations per instruction over the measured time, summed over the
+ * SMs (the measured denominator of the contraction's roofline), *ns_per_mma_out (nullable) the time per instruction
+ * of one SM.  Synchronizes the device; runs on the default stream.
+ */
+int wf_probe_i8_mma(int n, int iters, double* tops_out, double* ns_per_mma_out);
+
+/*
  * Absmean ternarization + 2-bit packing of a weight matrix into WF_LAYOUT_WF16.
  * Replaces: ternary_weight_quantization_no_scale (packages/training/src/wrinklefree/quantization/weight_quant.py:35-56),
  *           BitLinear.weight_quant for the cast-first modes (packages/training/src/wrinklefree/models/bitlinear.py:46-64,103),

@@ -57,7 +57,7 @@ def sha(*arrays) -> str:
 MODEL_CFG = dict(layers=2, hidden=576, n_q=9, n_kv=3, head_dim=64, intermediate=1536, vocab=1024, rope_theta=1e5,
                  norm_eps=1e-6, max_pos=64)
 MODEL_BATCH, MODEL_PROMPT, MODEL_STEPS = 2, 24, 3  # ids [B, PROMPT + STEPS]; the last STEPS tokens are teacher-forced decode steps
-MODEL_KEEP_FROM = 16                               # logits are stored for positions KEEP_FROM .. PROMPT + STEPS - 1
+MODEL_KEEP_FROM = 0                                # logits are stored for positions KEEP_FROM .. PROMPT + STEPS - 1
 
 
 def model_weights(seed: int = 31):

@@ -199,3 +199,38 @@ def test_kat_balanced_blocks_times_ones():
     t[:, 128:256] = -1
     acc = O.int_gemm(np.ones((1, 384), np.int8), t)
     assert not acc.any()
+
+
+@pytest.mark.parametrize("name", list(gi.CASES))
+def test_torch_restatement_of_the_reference_forward(name):
+    """oracle/torch_bitlinear.py (the timed "PyTorch BitLinear" CPU baseline) against outputs of the reference's own
+    class: same operators in the same order, so fp32 agrees to summation order and bf16 / f16 to one rounding."""
+    import torch
+
+    from oracle import torch_bitlinear as TB
+
+    z = np.load(os.path.join(GOLD, f"{name}.npz"))
+    x, w = gi.make_inputs(name)
+    torch.set_num_threads(1)
+    for tag, dt, tol in (("f32", torch.float32, 1e-6), ("bf16", torch.bfloat16, 1e-2), ("f16", torch.float16, 2e-3)):
+        y = TB.bitlinear_forward(x.to(dt), w).float().numpy()
+        assert np.abs(y - z[f"y_{tag}"]).max() <= tol * np.abs(z[f"y_{tag}"]).max(), tag
+    yb = TB.bitlinear_forward(x, w, torch.from_numpy(z["bias"])).numpy()
+    assert np.abs(yb - z["y_bias_f32"]).max() <= 1e-6 * np.abs(z["y_bias_f32"]).max()
+
+
+@pytest.mark.parametrize("tag", ["a", "b"])
+def test_oracle_against_bitnet_cpp_goldens(tag):
+    """BitNet.cpp's quantize_i2_s / ggml_vec_dot_i2_i8_s outputs (made by its compiled source) against the oracle:
+    the I2_S block packing of the sign codes, the uncorrected dot product sum (code * a), and the glue arithmetic
+    (dot - sum a) / s_x * s_w (ggml.c:12491-12493)."""
+    z = np.load(os.path.join(GOLD, "ggml.npz"))
+    w, q = z[f"{tag}_w"], z[f"{tag}_q"]
+    t = np.where(np.abs(w.astype(np.float64)) < 1e-6, 0, np.sign(w)).astype(np.int8)
+    assert np.array_equal(O.pack_i2s(t), z[f"{tag}_packed"])
+    assert np.float32(np.abs(w).max()) == z[f"{tag}_scale"]
+    acc = O.int_gemm(q, t)
+    sums = q.astype(np.int64).sum(1, keepdims=True)
+    assert np.array_equal((acc + sums).astype(np.float32), z[f"{tag}_vec_dot"])
+    want = (acc.astype(np.float32) / z[f"{tag}_act_scales"][:, None]) * z[f"{tag}_scale"]
+    assert np.allclose(want, z[f"{tag}_mul_mat"], rtol=2e-7, atol=0)

@@ -50,6 +50,7 @@ _SIGNATURES = {
     "wf_version": (_int, []),
     "wf_last_error": (C.c_char_p, []),
     "wf_device_check": (_int, []),
+    "wf_probe_i8_mma": (_int, [_int, _int, C.POINTER(C.c_double), C.POINTER(C.c_double)]),
     "wf_pack_scratch_bytes": (_sz, [_i64, _i64]),
     "wf_pack_ternary": (_int, [_p, _int, _i64, _i64, _i64, _int, _f32, _p, _p, _p, _sz, _p]),
     "wf_pack_noalloc_scratch_bytes": (_sz, []),
