@@ -132,8 +132,8 @@ def test_prefill_equals_reference_model_fp32(wf, act):
     other way when the fp32 summation order of a norm differs, that one code moves the token's hidden state by
     ~1e-3, and the next quantizations amplify it to ~1e-2 at the logits.  The reference does this to itself: adding
     3e-7 relative noise to its embeddings left 44 of 54 positions within 5e-7 and moved the other 10 by 0.5-1.7 %.
-    So: most positions must agree to 1e-5 (the computation is the same one), and no position may be off by more
-    than 3e-2 (a rounding cascade, not a different model)."""
+    So: at least 60 % of the positions must agree to 1e-5 (the computation is the same one), and no position may be
+    off by more than 3e-2 (a rounding cascade, not a different model)."""
     model, ids, z = _fixture_decoder(act, torch.float32, torch.float32)
     logits = model.prefill(ids, all_logits=True)
     got = logits[:, gi.MODEL_KEEP_FROM:].float().cpu().numpy()
@@ -142,9 +142,9 @@ def test_prefill_equals_reference_model_fp32(wf, act):
     np.set_printoptions(precision=1, linewidth=250)
     print(f"fp32 {act}: per-position error\n{err}")
     # A position's result depends on every earlier position of its sequence through attention, so a cascade, once
-    # started, reaches all later positions; the first positions have nothing upstream and must agree tightly.
-    assert (err[:, :4] <= 1e-5).all(), err[:, :4]
-    assert (err <= 1e-5).mean() >= 0.25, (err <= 1e-5).mean()
+    # started, reaches the later positions of that sequence.  Measured: 45 / 36 of the 54 positions (relu2 / silu)
+    # agree to 1e-6, the others sit at 5e-4 .. 1.7e-2.
+    assert (err <= 1e-5).mean() >= 0.6, (err <= 1e-5).mean()
     assert err.max() <= 3e-2, err.max()
     assert (got.argmax(-1) == ref.argmax(-1)).mean() >= 0.9
     wf.device_status()
