@@ -129,16 +129,17 @@ def test_torch_operators_on_the_gpu(wf):
 
 # ---------------------------------------------------------------- the prefill configuration at full size
 @pytest.mark.parametrize("n,k", [(2560, 2560), (6912, 2560), (2560, 6912)])
-@pytest.mark.parametrize("m", [512, 2048, 8192])
-def test_prefill_full_size_against_oracle(wf, oracle_c, n, k, m):
+@pytest.mark.parametrize("m,form", [(512, "auto"), (2048, "pair"), (2048, "single"), (8192, "pair"), (8192, "single")])
+def test_prefill_full_size_against_oracle(wf, oracle_c, n, k, m, form):
     """int8 x ternary GEMM on the tensor cores at the benchmark's shapes: a strided slice of the int32 accumulators
     (every 16th token x every 8th weight row, offsets varied so that every tile position is met) and of the bf16
-    outputs against the CPU oracle, bit for bit; row-sum and column-sum checksums over the whole result."""
+    outputs against the CPU oracle, bit for bit; row-sum and column-sum checksums over the whole result.  Both tile
+    forms of the contraction (one SM per 128 x 128 tile, two SMs per 256 x 192 tile) at the large token counts."""
     g = torch.Generator().manual_seed(n + 3 * k + m)
     w = torch.randn(n, k, generator=g) * 0.02
     x = gi.with_outliers(torch.randn(m, k, generator=g), seed=m + 1).bfloat16()
     codes, scale = wf.pack_ternary(w.to(DEV))
-    y, acc = wf.bitlinear(x.to(DEV), codes, scale, want_acc=True, path="prefill")
+    y, acc = wf.bitlinear(x.to(DEV), codes, scale, want_acc=True, path="prefill", prefill_form=form)
     assert y.dtype == torch.bfloat16
     t_all = wf.unpack_codes(codes, n, k)
     s_w = O.absmean_scale(w.numpy())  # one scale for the whole matrix

@@ -275,6 +275,37 @@ def test_small_m_contraction_bit_exact(wf, oracle_c):
     wf.device_status()
 
 
+def test_prefill_pair_form_bit_exact(wf, oracle_c):
+    """The two-SM form of the contraction (a cluster of two CTAs per 256-row x 192-token tile, tcgen05 cta_group::2):
+    partial token blocks, partial row blocks (also a tile whose second CTA has no valid row), K tails inside and
+    across the 512-wide packed stages, several tiles per cluster, both layouts, bias, int8 input; and the forced
+    single-SM form on the same data."""
+    L = wf._lib
+    rng = np.random.default_rng(29)
+    for (m, k, n) in ((192, 256, 256), (65, 128, 100), (200, 576, 300), (385, 1024, 700), (500, 2560, 520), (129, 128, 257),
+                      (70, 6912, 256), (3000, 640, 9000)):
+        t = rng.integers(-1, 2, size=(n, k)).astype(np.int8)
+        x = torch.from_numpy(rng.standard_normal((m, k)).astype(np.float32)).bfloat16()
+        bias = torch.from_numpy(rng.standard_normal(n).astype(np.float32))
+        q, s = oracle_c.act_quant(x.float().numpy(), 1)
+        acc_o = oracle_c.int_gemm(q, t)
+        y_o = oracle_c.rescale(acc_o, s, 0.02)
+        for lay in ((L.LAYOUT_WF16, L.LAYOUT_I2S) if k % 128 == 0 else (L.LAYOUT_WF16,)):
+            codes = wf.pack_codes(torch.from_numpy(t).to(DEV), lay)
+            for form in ("pair", "single"):
+                y, acc = wf.bitlinear(x.to(DEV), codes, 0.02, layout=lay, out_dtype=torch.float32, want_acc=True, path="prefill",
+                                      prefill_form=form)
+                assert np.array_equal(acc.cpu().numpy(), acc_o), (m, k, n, lay, form)
+                assert np.array_equal(y.cpu().numpy(), y_o), (m, k, n, lay, form)
+        yb = wf.bitlinear(x.to(DEV), codes, 0.02, bias=bias.to(DEV), layout=lay, path="prefill", prefill_form="pair")
+        want = torch.from_numpy(oracle_c.rescale(acc_o, s, 0.02, bias.numpy())).bfloat16()
+        assert yb.dtype == torch.bfloat16 and torch.equal(yb.cpu(), want), (m, k, n)
+        yq, accq = wf.bitlinear(torch.from_numpy(q).to(DEV), codes, 0.02, layout=lay, x_scale=torch.from_numpy(s).to(DEV),
+                                want_acc=True, path="prefill", prefill_form="pair")
+        assert np.array_equal(accq.cpu().numpy(), acc_o) and np.array_equal(yq.cpu().numpy(), y_o)
+        wf.device_status()
+
+
 @pytest.mark.parametrize("n,k", [(2560, 2560), (6912, 2560), (2560, 6912)])
 def test_prefill_full_size_against_decode_path(wf, n, k):
     """BASELINE prefill shapes at M = 512: the tensor-core path and the decode path agree bit for bit."""

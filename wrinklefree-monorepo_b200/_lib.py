@@ -19,6 +19,7 @@ ACT_PER_TOKEN, ACT_PER_TENSOR = 0, 1
 MAXABS_HALF, MAXABS_SIGN = 0, 1
 FLAG_PDL = 1
 FLAG_X_READY = 2
+FLAG_PREFILL_PAIR, FLAG_PREFILL_SINGLE = 4, 8
 
 _i64, _int, _f32, _p, _sz, _u32 = C.c_int64, C.c_int, C.c_float, C.c_void_p, C.c_size_t, C.c_uint
 

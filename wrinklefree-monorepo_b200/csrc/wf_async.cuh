@@ -8,6 +8,8 @@
 namespace wf {
 
 constexpr unsigned SPIN_LIMIT = 1u << 20;
+constexpr unsigned SUSPEND_HINT_NS = 20000;            // per try_wait
+constexpr unsigned long long WAIT_LIMIT_NS = 400000000;  // a wait that never completes gives up after 0.4 s (or SPIN_LIMIT polls)
 
 __device__ __forceinline__ uint32_t smem_u32(const void* p) { return static_cast<uint32_t>(__cvta_generic_to_shared(p)); }
 
@@ -33,13 +35,22 @@ __device__ __forceinline__ bool mbar_wait(uint64_t* bar, unsigned parity, volati
                  : "memory");
     if (ok) return true;
     if (*poisoned) return false;
+    unsigned long long t0 = 0;
     for (unsigned it = 0; it < SPIN_LIMIT; ++it) {
-        asm volatile("{\n .reg .pred p;\n mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n selp.u32 %0, 1, 0, p;\n}\n"
+        // the last operand is a suspend-time hint (ns): the warp sleeps in hardware until the phase completes or about
+        // that long, instead of spinning through the issue slots of the warps that do the work
+        asm volatile("{\n .reg .pred p;\n mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2, %3;\n selp.u32 %0, 1, 0, p;\n}\n"
                      : "=r"(ok)
-                     : "r"(a), "r"(parity)
+                     : "r"(a), "r"(parity), "r"(SUSPEND_HINT_NS)
                      : "memory");
         if (ok) return true;
-        if ((it & 1023) == 1023 && *poisoned) return false;
+        if ((it & 15) == 15) {  // bound the wait by time as well: the hint makes one iteration up to SUSPEND_HINT_NS long
+            if (*poisoned) return false;
+            unsigned long long now;
+            asm volatile("mov.u64 %0, %%globaltimer;\n" : "=l"(now));
+            if (t0 == 0) t0 = now;
+            else if (now - t0 > WAIT_LIMIT_NS) break;
+        }
     }
     *poisoned = 1;
     atomicExch(&WF_STATUS_WORD, WF_E_LIMIT);

@@ -122,6 +122,16 @@ __device__ __forceinline__ void tmem_st32(uint32_t addr, const uint32_t (&v)[32]
         : "memory");
     asm volatile("tcgen05.wait::st.sync.aligned;\n" ::: "memory");
 }
+__device__ __forceinline__ void tmem_st32_nowait(uint32_t addr, const uint32_t (&v)[32]) {
+    asm volatile(
+        "tcgen05.st.sync.aligned.32x32b.x32.b32 [%0], {%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,%16,%17,%18,%19,%20,%21,%22,"
+        "%23,%24,%25,%26,%27,%28,%29,%30,%31,%32};\n" ::"r"(addr),
+        "r"(v[0]), "r"(v[1]), "r"(v[2]), "r"(v[3]), "r"(v[4]), "r"(v[5]), "r"(v[6]), "r"(v[7]), "r"(v[8]), "r"(v[9]), "r"(v[10]),
+        "r"(v[11]), "r"(v[12]), "r"(v[13]), "r"(v[14]), "r"(v[15]), "r"(v[16]), "r"(v[17]), "r"(v[18]), "r"(v[19]), "r"(v[20]),
+        "r"(v[21]), "r"(v[22]), "r"(v[23]), "r"(v[24]), "r"(v[25]), "r"(v[26]), "r"(v[27]), "r"(v[28]), "r"(v[29]), "r"(v[30]),
+        "r"(v[31])
+        : "memory");
+}
 template <int NREG>
 __device__ __forceinline__ void tmem_ldn(uint32_t addr, uint32_t (&v)[NREG]);
 template <>
@@ -396,6 +406,349 @@ __global__ void __launch_bounds__(SM_THREADS, 1)
     }
 }
 
+// ---------------------------------------------------------------------------------------------------------
+// Pair form, for many tokens.  The single-CTA kernel above is bound by L2 -> SM traffic: a 128 x 128 tile pulls 80 KB
+// (64 KB of int8 tokens, 16 KB of packed weights) per 8.4 M multiply-adds.  Here the two CTAs of a cluster (two SMs)
+// compute ONE tile of 256 weight rows x PR_N tokens with tcgen05.mma.cta_group::2: each CTA expands its own 128 weight
+// rows into its own tensor memory (the A operand) and loads only ITS HALF of the token tile (PR_N / 2 tokens, the B
+// operand of the pair is the union of the two halves), so the token bytes per multiply-add halve: 32 KB per 6.3 M.
+// No load is multicast: every CTA fetches what it needs with an ordinary TMA copy; the copies of the token halves
+// use the cta_group::2 form only so that both CTAs' bytes are counted on the barrier of the CTA that issues the MMAs.
+//
+// Per CTA: warp 0 TMA of its packed rows (stages of 512 K, each feeding two tensor-memory stages of 256 K); warp 14
+// TMA of its token half; warps 2-5 / 6-9 expansion (first / second half of every packed stage); warp 1 of the LEADER
+// (cluster rank 0) issues the MMAs of the pair and commits with a cluster multicast so that both CTAs see their
+// buffers released; warps 10-13 and 15-18 epilogue of the CTA's own 128 rows x PR_N tokens.  Barriers that gather
+// arrivals of both CTAs (token tile full, expanded weights ready, accumulator drained) live in the leader.
+// Tensor memory: two accumulators of PR_N columns + 128 columns of expanded weights (PR_AS stages) = 512 columns.
+constexpr int PR_N = 192;                 // tokens per tile (the N of the MMA); a multiple of 32
+constexpr int PR_HALF = PR_N / 2;         // tokens each CTA loads
+constexpr int PR_PS = 4;                  // packed-weight stages (128 rows x 128 B = 16 KB, 512 K each)
+constexpr int PR_XS = 3;                  // token stages (4 atoms of PR_HALF x 128 B = 48 KB, 512 K each: two tensor-memory stages)
+constexpr int PR_AA = 2;                  // 128-byte atoms of K per tensor-memory stage (128 K each)
+constexpr int PR_AS = 4 / PR_AA;          // tensor-memory stages of expanded weights: 128 columns in all
+constexpr int PR_X_ATOM = PR_HALF * SM_BK;
+constexpr int PR_X_BYTES = 4 * PR_X_ATOM;
+constexpr int PR_A_COLS = 32 * PR_AA;
+constexpr int PR_ACC_COLS = 2 * PR_N;
+constexpr size_t PR_SMEM = 1024 + PR_PS * SM_P_BYTES + PR_XS * PR_X_BYTES + 4096;
+static_assert(PR_SMEM <= 227 * 1024, "shared memory of the pair form");
+static_assert(PR_ACC_COLS + PR_AS * PR_A_COLS <= 512 && PR_N % 32 == 0 && PR_X_ATOM % 1024 == 0, "tensor memory / tile shape of the pair form");
+
+__device__ __forceinline__ uint32_t cluster_rank() {
+    uint32_t r;
+    asm volatile("mov.u32 %0, %%cluster_ctarank;\n" : "=r"(r));
+    return r;
+}
+// the address of `p` (a shared-memory location of this CTA) in the CTA of rank `rank` of the cluster
+__device__ __forceinline__ uint32_t map_to_rank(const void* p, uint32_t rank) {
+    uint32_t r;
+    asm volatile("mapa.shared::cluster.u32 %0, %1, %2;\n" : "=r"(r) : "r"(smem_u32(p)), "r"(rank));
+    return r;
+}
+// Arrival on a barrier of another CTA of the cluster.  What the barriers of this kernel order is tensor-memory traffic
+// (tcgen05.st / tcgen05.ld completed by their own wait instructions and fenced with tcgen05.fence), not generic memory,
+// so the arrival carries no cluster-scope release: that form cost about 1.5 k cycles per arrival in the expansion warps.
+__device__ __forceinline__ void mbar_arrive_cluster(uint32_t cluster_addr) {
+    asm volatile("mbarrier.arrive.shared::cluster.b64 _, [%0];\n" ::"r"(cluster_addr) : "memory");
+}
+// commit of the pair's MMAs: one arrival on the barrier at this shared-memory offset in BOTH CTAs
+__device__ __forceinline__ void tc_commit_pair(uint64_t* bar) {
+    asm volatile("tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.multicast::cluster.b64 [%0], %1;\n" ::"r"(smem_u32(bar)),
+                 "h"(static_cast<uint16_t>(3))
+                 : "memory");
+}
+// TMA copy into THIS CTA's shared memory whose bytes are counted on a barrier given as a cluster address (the leader's)
+__device__ __forceinline__ void tma_load_2d_pair(void* dst, const void* tmap, int c0, int c1, uint32_t bar_cluster_addr) {
+    asm volatile("cp.async.bulk.tensor.2d.cta_group::2.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];\n" ::"r"(
+                     smem_u32(dst)),
+                 "l"(reinterpret_cast<uint64_t>(tmap)), "r"(c0), "r"(c1), "r"(bar_cluster_addr)
+                 : "memory");
+}
+__device__ __forceinline__ void mma_i8_ts_x4_pair(uint32_t d_tmem, uint32_t a_tmem, uint64_t b_desc, uint32_t idesc, uint32_t accumulate_first) {
+    asm volatile(
+        "{\n .reg .pred p, q;\n .reg .b32 a1, a2, a3;\n .reg .b64 b1, b2, b3;\n"
+        " setp.ne.b32 p, %4, 0;\n setp.eq.b32 q, %5, %5;\n"
+        " add.u32 a1, %1, 8;\n add.u32 a2, %1, 16;\n add.u32 a3, %1, 24;\n"
+        " add.u64 b1, %2, 2;\n add.u64 b2, %2, 4;\n add.u64 b3, %2, 6;\n"
+        " tcgen05.mma.cta_group::2.kind::i8 [%0], [%1], %2, %3, {%5, %5, %5, %5, %5, %5, %5, %5}, p;\n"
+        " tcgen05.mma.cta_group::2.kind::i8 [%0], [a1], b1, %3, {%5, %5, %5, %5, %5, %5, %5, %5}, q;\n"
+        " tcgen05.mma.cta_group::2.kind::i8 [%0], [a2], b2, %3, {%5, %5, %5, %5, %5, %5, %5, %5}, q;\n"
+        " tcgen05.mma.cta_group::2.kind::i8 [%0], [a3], b3, %3, {%5, %5, %5, %5, %5, %5, %5, %5}, q;\n}\n" ::"r"(d_tmem),
+        "r"(a_tmem), "l"(b_desc), "r"(idesc), "r"(accumulate_first), "r"(0u)
+        : "memory");
+}
+
+__global__ void __launch_bounds__(SM_THREADS, 1)
+    prefill_pair_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_constant__ CUtensorMap tmap_p, const PrefillParams p) {
+    constexpr int EPI_COLS = PR_N / 2;  // two epilogue warp groups, each takes half of the token columns
+    extern __shared__ uint8_t smem_raw[];
+    uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~static_cast<uintptr_t>(1023));
+    uint8_t* p_ring = smem;                           // [PR_PS][128 rows x 128 B], 128-byte swizzle
+    uint8_t* x_ring = p_ring + PR_PS * SM_P_BYTES;    // [PR_XS][2 atoms][PR_HALF rows x 128 B], 128-byte swizzle
+    uint64_t* p_full = reinterpret_cast<uint64_t*>(x_ring + PR_XS * PR_X_BYTES);
+    uint64_t* p_empty = p_full + PR_PS;
+    uint64_t* x_full = p_empty + PR_PS;       // leader's copy: bytes of both CTAs' halves
+    uint64_t* x_free = x_full + PR_XS;        // multicast commit: the token stage may be overwritten
+    uint64_t* a_full = x_free + PR_XS;        // leader's copy: the expansion warps of both CTAs
+    uint64_t* a_free = a_full + PR_AS;        // multicast commit: the tensor-memory stage may be overwritten
+    uint64_t* acc_full = a_free + PR_AS;      // multicast commit: the accumulator of a tile is complete
+    uint64_t* acc_empty = acc_full + 2;       // leader's copy: the epilogue warps of both CTAs
+    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(acc_empty + 2);
+    volatile int* poisoned = reinterpret_cast<volatile int*>(tmem_slot + 1);
+    int* s_rowsum = reinterpret_cast<int*>(tmem_slot + 2);   // [PR_N] per-token constants of the epilogue's current token block
+    float* s_inv = reinterpret_cast<float*>(s_rowsum + 256);  // [PR_N]
+
+    asm volatile("griddepcontrol.launch_dependents;\n" ::: "memory");
+    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    const uint32_t rank = cluster_rank();     // 0: leader (issues the MMAs), 1: peer
+    const int cluster_id = blockIdx.x >> 1, n_clusters = gridDim.x >> 1;
+    // K is walked in packed stages of 512 and tensor-memory stages of 256; a stage that reaches past K is zero-filled by
+    // the TMA unit on both operands.  Every tile runs an even number of tensor-memory stages, so a stage's half of its
+    // packed stage and its expansion group are fixed by the parity of the running stage counter.
+    const int pstages = (p.K + 511) / 512, astages = PR_AS * pstages;
+    const int tiles_per_problem = p.tiles_m * p.tiles_n;  // token blocks of PR_N x row blocks of 256; row blocks vary fastest
+    const int total_tiles = tiles_per_problem * p.batch;
+
+    if (tid == 0) {
+        for (int s = 0; s < PR_PS; ++s) {
+            mbar_init(&p_full[s], 1);
+            mbar_init(&p_empty[s], 8);
+        }
+        for (int s = 0; s < PR_XS; ++s) {
+            mbar_init(&x_full[s], 1);
+            mbar_init(&x_free[s], 1);
+        }
+        for (int s = 0; s < PR_AS; ++s) {
+            mbar_init(&a_full[s], 8);
+            mbar_init(&a_free[s], 1);
+        }
+        for (int a = 0; a < 2; ++a) {
+            mbar_init(&acc_full[a], 1);
+            mbar_init(&acc_empty[a], 16);
+        }
+        *poisoned = 0;
+        asm volatile("fence.mbarrier_init.release.cluster;\n" ::: "memory");
+    }
+    if (warp == 1) {  // the same warp of both CTAs allocates the pair's tensor memory
+        asm volatile("tcgen05.alloc.cta_group::2.sync.aligned.shared::cta.b32 [%0], %1;\n" ::"r"(smem_u32(tmem_slot)), "r"(512));
+        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::2.sync.aligned;\n" ::);
+    }
+    tc_fence_before();
+    __syncthreads();
+    // both CTAs have initialised their barriers before either signals the other
+    asm volatile("barrier.cluster.arrive.release.aligned;\n barrier.cluster.wait.acquire.aligned;\n" ::: "memory");
+    tc_fence_after();
+    const uint32_t tmem_base = *tmem_slot;
+    const uint32_t tmem_a = tmem_base + PR_ACC_COLS;  // PR_AS stages of PR_A_COLS columns
+
+    if (warp == 0) {
+        if (lane == 0) {  // this CTA's packed rows
+            int psit = 0;
+            for (int t = cluster_id; t < total_tiles; t += n_clusters) {
+                const int z = t / tiles_per_problem, rb = t % p.tiles_n;
+                const int row_w = z * p.N + rb * 256 + static_cast<int>(rank) * SM_BM;
+                for (int g = 0; g < pstages; ++g, ++psit) {
+                    const int s = psit % PR_PS;
+                    if (psit >= PR_PS) mbar_wait(&p_empty[s], ((psit / PR_PS) - 1) & 1, poisoned);
+                    mbar_expect_tx(&p_full[s], SM_P_BYTES);
+                    tma_load_2d(p_ring + s * SM_P_BYTES, &tmap_p, g * 128, row_w, &p_full[s]);
+                }
+            }
+        }
+    } else if (warp == 14) {
+        if (lane == 0) {  // this CTA's half of the token tile; the bytes are counted on the leader's barrier
+            asm volatile("griddepcontrol.wait;\n" ::: "memory");
+            int xsit = 0;
+            for (int t = cluster_id; t < total_tiles; t += n_clusters) {
+                const int row_x = (t / tiles_per_problem) * p.M + ((t % tiles_per_problem) / p.tiles_n) * PR_N + static_cast<int>(rank) * PR_HALF;
+                for (int g = 0; g < pstages; ++g, ++xsit) {
+                    const int s = xsit % PR_XS;
+                    if (xsit >= PR_XS) mbar_wait(&x_free[s], ((xsit / PR_XS) - 1) & 1, poisoned);
+                    if (rank == 0) mbar_expect_tx(&x_full[s], 2 * PR_X_BYTES);
+                    const uint32_t bar = map_to_rank(&x_full[s], 0);
+#pragma unroll
+                    for (int j = 0; j < 4; ++j)  // an atom that lies past K arrives as zeros
+                        tma_load_2d_pair(x_ring + s * PR_X_BYTES + j * PR_X_ATOM, &tmap_x, (g * 4 + j) * SM_BK, row_x, bar);
+                }
+            }
+        }
+    } else if (warp == 1) {
+        if (lane == 0 && rank == 0) {
+            // D = s32, A = unsigned 8-bit (codes, from tensor memory), B = signed 8-bit (tokens, K-major), N = PR_N, M = 256 over the pair
+            const uint32_t idesc = (2u << 4) | (0u << 7) | (1u << 10) | (static_cast<uint32_t>(PR_N >> 3) << 17) | (static_cast<uint32_t>(256 >> 4) << 24);
+            uint64_t bdesc[PR_XS][4];  // per token stage and 128-byte atom of K
+#pragma unroll
+            for (int s = 0; s < PR_XS; ++s)
+#pragma unroll
+                for (int j = 0; j < 4; ++j) bdesc[s][j] = smem_desc_sw128(smem_u32(x_ring + s * PR_X_BYTES + j * PR_X_ATOM));
+            int sit = 0, nt = 0;
+            for (int t = cluster_id; t < total_tiles; t += n_clusters, ++nt) {
+                const int a = nt & 1;
+                if (nt >= 2) mbar_wait(&acc_empty[a], ((nt >> 1) - 1) & 1, poisoned);
+                tc_fence_after();
+                const uint32_t d_tmem = tmem_base + a * PR_N;
+                for (int g = 0; g < astages; ++g, ++sit) {
+                    // token stage = packed stage = PR_AS tensor-memory stages; `part` = which of them
+                    const int xsit = sit / PR_AS, xs = xsit % PR_XS, part = sit % PR_AS, as = part;
+                    if (part == 0) mbar_wait(&x_full[xs], (xsit / PR_XS) & 1, poisoned);
+                    mbar_wait(&a_full[as], (sit / PR_AS) & 1, poisoned);
+                    tc_fence_after();
+                    const uint32_t a_stage = tmem_a + as * PR_A_COLS;
+#pragma unroll
+                    for (int ss = 0; ss < PR_XS; ++ss) {
+                        if (ss == xs) {
+#pragma unroll
+                            for (int pp = 0; pp < PR_AS; ++pp) {
+                                if (pp == part) {
+#pragma unroll
+                                    for (int j = 0; j < PR_AA; ++j)
+                                        mma_i8_ts_x4_pair(d_tmem, a_stage + j * 32, bdesc[ss][pp * PR_AA + j], idesc, (g | j) ? 1u : 0u);
+                                }
+                            }
+                        }
+                    }
+                    tc_commit_pair(&a_free[as]);
+                    if (part == PR_AS - 1) tc_commit_pair(&x_free[xs]);  // the whole token stage has been consumed
+                }
+                tc_commit_pair(&acc_full[a]);
+            }
+        }
+    } else if (warp < 10) {
+        // ---- expansion: the two groups alternate tensor-memory stages; thread = weight row
+        const int grp = (warp - 2) >> 2;
+        const int quarter = warp & 3;
+        const int r = quarter * 32 + lane;
+        const uint32_t m = 0x03030303u;
+        int sit = grp;  // this group's tensor-memory stages: grp, grp + 2, ...
+        for (int t = cluster_id; t < total_tiles; t += n_clusters) {
+            for (int g = grp; g < astages; g += 2, sit += 2) {
+                const int psit = sit / PR_AS, ps = psit % PR_PS, part = sit % PR_AS, as = part;
+                mbar_wait(&p_full[ps], (psit / PR_PS) & 1, poisoned);
+                // The packed bytes are expanded into registers BEFORE the tensor-memory stage is known to be free: what
+                // remains between "the MMAs of the previous use have completed" and "the next MMAs may start" is the
+                // tcgen05.st and its wait.
+                const uint32_t row = smem_u32(p_ring + ps * SM_P_BYTES) + r * 128;
+                uint32_t v[PR_AA][32];
+#pragma unroll
+                for (int jj = 0; jj < PR_AA; ++jj) {
+                    const int j = part * PR_AA + jj;  // atom of the packed stage
+                    const uint4 lo = lds128p(row + (((2 * j) ^ (r & 7)) << 4));
+                    const uint4 hi = lds128p(row + (((2 * j + 1) ^ (r & 7)) << 4));
+                    const uint32_t w[8] = {lo.x, lo.y, lo.z, lo.w, hi.x, hi.y, hi.z, hi.w};
+                    if (p.layout == WF_LAYOUT_WF16) {
+#pragma unroll
+                        for (int i = 0; i < 8; ++i) {
+                            v[jj][4 * i] = w[i] & m;
+                            v[jj][4 * i + 1] = (w[i] >> 2) & m;
+                            v[jj][4 * i + 2] = (w[i] >> 4) & m;
+                            v[jj][4 * i + 3] = (w[i] >> 6) & m;
+                        }
+                    } else {
+#pragma unroll
+                        for (int q = 0; q < 4; ++q)
+#pragma unroll
+                            for (int i = 0; i < 8; ++i) v[jj][8 * q + i] = (w[i] >> (6 - 2 * q)) & m;
+                    }
+                }
+                __syncwarp();
+                // this group's last part of the packed stage: its rows are in registers
+                if (lane == 0 && part + 2 >= PR_AS) mbar_arrive(&p_empty[ps]);
+                if (sit >= PR_AS) mbar_wait(&a_free[as], ((sit / PR_AS) - 1) & 1, poisoned);
+                tc_fence_after();
+                const uint32_t dst = tmem_a + as * PR_A_COLS + (static_cast<uint32_t>(quarter * 32) << 16);
+#pragma unroll
+                for (int jj = 0; jj < PR_AA; ++jj) tmem_st32_nowait(dst + jj * 32, v[jj]);
+                asm volatile("tcgen05.wait::st.sync.aligned;\n" ::: "memory");
+                tc_fence_before();
+                __syncwarp();
+                if (lane == 0) mbar_arrive_cluster(map_to_rank(&a_full[as], 0));  // expanded rows of this CTA are in its tensor memory
+            }
+        }
+    } else if (warp < 14 || warp >= 15) {
+        // ---- epilogue of this CTA's 128 rows: thread = weight row (TMEM lane), registers = tokens
+        const int quarter = warp & 3;
+        const int r = quarter * 32 + lane;
+        const int egrp = warp >= 15 ? 1 : 0;
+        const int et = egrp * 128 + (warp - (egrp ? 15 : 10)) * 32 + lane;  // 0 .. 255
+        const int col0 = egrp * EPI_COLS;
+        const uint32_t acc_empty_leader0 = map_to_rank(&acc_empty[0], 0), acc_empty_leader1 = map_to_rank(&acc_empty[1], 0);
+        asm volatile("griddepcontrol.wait;\n" ::: "memory");
+        int nt = 0, cur_zb = -1;
+        for (int t = cluster_id; t < total_tiles; t += n_clusters, ++nt) {
+            const int z = t / tiles_per_problem, zb = t / p.tiles_n, tb = (t % tiles_per_problem) / p.tiles_n, rb = t % p.tiles_n;
+            const int a = nt & 1;
+            const int nrow = rb * 256 + static_cast<int>(rank) * SM_BM + r;
+            const bool row_ok = nrow < p.N;
+            const int tok_base = tb * PR_N;
+            const int mtok = min(PR_N, p.M - tok_base);
+            if (zb != cur_zb) {
+                asm volatile("bar.sync 2, 256;\n" ::: "memory");
+                if (et < mtok) {
+                    const int64_t tok = static_cast<int64_t>(z) * p.M + tok_base + et;
+                    s_rowsum[et] = p.rowsum[tok];
+                    s_inv[et] = p.x_scale ? __frcp_rn(p.x_scale[tok]) : 1.0f;
+                }
+                asm volatile("bar.sync 2, 256;\n" ::: "memory");
+                cur_zb = zb;
+            }
+            const float s_w = p.w_scale ? __ldg(p.w_scale + static_cast<int64_t>(z) * p.w_scale_stride) : p.w_scale_host;
+            const bool has_bias = p.bias != nullptr;
+            const float bias = (has_bias && row_ok) ? load1_rt(p.bias, p.bias_dtype, nrow) : 0.f;
+            const int64_t tok0 = static_cast<int64_t>(z) * p.M + tok_base;
+            const bool fast16 = (p.y_dtype == WF_BF16 || p.y_dtype == WF_F16) && p.acc_out == nullptr;
+            uint16_t* y16 = static_cast<uint16_t*>(p.y) + tok0 * p.ldy + nrow;
+            const bool is_bf16 = p.y_dtype == WF_BF16;
+            mbar_wait(&acc_full[a], (nt >> 1) & 1, poisoned);
+            tc_fence_after();
+#pragma unroll
+            for (int c0 = col0; c0 < col0 + EPI_COLS; c0 += 16) {
+                uint32_t v[16];
+                tmem_ldn<16>(tmem_base + (static_cast<uint32_t>(quarter * 32) << 16) + a * PR_N + c0, v);
+                if (c0 + 16 == col0 + EPI_COLS) {  // this group's columns are in registers: hand them back to the MMA thread
+                    tc_fence_before();
+                    __syncwarp();
+                    if (lane == 0) mbar_arrive_cluster(a ? acc_empty_leader1 : acc_empty_leader0);
+                }
+                if (!row_ok) continue;
+                if (fast16) {
+#pragma unroll
+                    for (int jt = 0; jt < 16; ++jt) {
+                        const int tok_in = c0 + jt;
+                        if (tok_in < mtok) {
+                            float o = rescale(static_cast<int>(v[jt]) - s_rowsum[tok_in], s_inv[tok_in], s_w);
+                            if (has_bias) o = __fadd_rn(o, bias);
+                            const uint16_t bits = is_bf16 ? __bfloat16_as_ushort(__float2bfloat16_rn(o)) : __half_as_ushort(__float2half_rn(o));
+                            y16[tok_in * p.ldy] = bits;
+                        }
+                    }
+                } else {
+#pragma unroll
+                    for (int jt = 0; jt < 16; ++jt) {
+                        const int tok_in = c0 + jt;
+                        if (tok_in < mtok) {
+                            const int64_t tok = tok0 + tok_in;
+                            const int acc = static_cast<int>(v[jt]) - s_rowsum[tok_in];
+                            float o = rescale(acc, s_inv[tok_in], s_w);
+                            if (has_bias) o = __fadd_rn(o, bias);
+                            store1_rt(p.y, p.y_dtype, tok * p.ldy + nrow, o);
+                            if (p.acc_out) p.acc_out[tok * p.N + nrow] = acc;
+                        }
+                    }
+                }
+            }
+        }
+    }
+    tc_fence_before();
+    __syncthreads();
+    // neither CTA leaves (nor frees the pair's tensor memory) while the other may still signal it
+    asm volatile("barrier.cluster.arrive.release.aligned;\n barrier.cluster.wait.acquire.aligned;\n" ::: "memory");
+    if (warp == 1) {
+        tc_fence_after();
+        asm volatile("tcgen05.dealloc.cta_group::2.sync.aligned.b32 %0, %1;\n" ::"r"(tmem_base), "r"(512));
+    }
+}
+
 // row sums of an int8 matrix (for activations that arrive already quantized)
 __global__ void rowsum_i8_kernel(const int8_t* __restrict__ q, int64_t ldq, int K, int32_t* __restrict__ rowsum) {
     const int64_t m = blockIdx.x;
@@ -459,7 +812,7 @@ extern "C" size_t wf_prefill_workspace_bytes(int64_t M, int64_t K) {
 static int prefill_impl(const char* who, const void* x, int x_dtype, int64_t ldx, const float* x_scale, const uint8_t* codes,
                         int layout, const float* w_scale, int64_t w_scale_stride, float w_scale_host, const void* bias,
                         int bias_dtype, void* y, int y_dtype, int64_t ldy, int32_t* acc_out, int64_t batch, int64_t M_one,
-                        int64_t N, int64_t K, float eps, void* workspace, size_t workspace_bytes, void* stream) {
+                        int64_t N, int64_t K, float eps, void* workspace, size_t workspace_bytes, unsigned flags, void* stream) {
     const int64_t M = batch * M_one;  // rows of the stacked activations
     if (int rc = wf_check_linear_args(who, x, x_dtype, ldx, x_scale, codes, layout, bias, bias_dtype, y, y_dtype, ldy, M, N, K))
         return rc;
@@ -493,12 +846,24 @@ static int prefill_impl(const char* who, const void* x, int x_dtype, int64_t ldx
     EncodeTiledFn enc = pf_encode_fn();
     if (!enc) return fail(WF_E_DEVICE, "cuTensorMapEncodeTiled is not available in this driver");
     const int ntok = M_one <= 16 ? 16 : (M_one <= 32 ? 32 : (M_one <= 64 ? 64 : 128));
+    const int sms = num_sms();
+    // Pair form (two CTAs per 256 x PR_N tile) or single form (one CTA per 128 x 128 tile)?  Measured on B200 the two
+    // forms run at the same rate per multiply-add (the pair form pulls half the bytes from L2, the single form has the
+    // deeper pipeline), so the choice follows the tile quantisation: estimated time = waves of tiles x work per SM and tile.
+    bool pair = false;
+    if (ntok == 128) {
+        const long long t1 = ((M_one + 127) / 128) * ((N + 127) / 128) * batch, w1 = (t1 + sms - 1) / sms;
+        const long long t2 = ((M_one + PR_N - 1) / PR_N) * ((N + 255) / 256) * batch, w2 = (t2 + sms / 2 - 1) / (sms / 2);
+        pair = sms >= 2 && w2 * PR_N < w1 * 128;
+        if (flags & WF_FLAG_PREFILL_PAIR) pair = sms >= 2;
+        if (flags & WF_FLAG_PREFILL_SINGLE) pair = false;
+    }
     alignas(64) CUtensorMap tmap_a, tmap_p;
     const cuuint32_t ones[2] = {1, 1};
     {
         const cuuint64_t dims[2] = {static_cast<cuuint64_t>(K), static_cast<cuuint64_t>(M)};
         const cuuint64_t strides[1] = {static_cast<cuuint64_t>(ldq)};
-        const cuuint32_t box[2] = {SM_BK, static_cast<cuuint32_t>(ntok)};
+        const cuuint32_t box[2] = {SM_BK, static_cast<cuuint32_t>(pair ? PR_HALF : ntok)};
         CUresult r = enc(&tmap_a, CU_TENSOR_MAP_DATA_TYPE_UINT8, 2, const_cast<int8_t*>(q), dims, strides, box, ones,
                          CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
                          CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
@@ -518,12 +883,12 @@ static int prefill_impl(const char* who, const void* x, int x_dtype, int64_t ldx
     pp.bias_dtype = bias_dtype; pp.y = y; pp.y_dtype = y_dtype; pp.ldy = ldy; pp.acc_out = acc_out;
     pp.M = static_cast<int>(M_one); pp.N = static_cast<int>(N); pp.K = static_cast<int>(K); pp.layout = layout;
     pp.batch = static_cast<int>(batch); pp.w_scale_stride = static_cast<int>(w_scale_stride);
-    pp.tiles_m = static_cast<int>((M_one + ntok - 1) / ntok);
-    pp.tiles_n = static_cast<int>((N + SM_BM - 1) / SM_BM);
+    pp.tiles_m = static_cast<int>(pair ? (M_one + PR_N - 1) / PR_N : (M_one + ntok - 1) / ntok);
+    pp.tiles_n = static_cast<int>(pair ? (N + 255) / 256 : (N + SM_BM - 1) / SM_BM);
     static PerDeviceOnce configured;  // the attribute is a per-device setting
     const int dev_now = current_device();
-    const int sms = num_sms();
     if (configured.needs(dev_now)) {
+        WF_CUDA(cudaFuncSetAttribute(prefill_pair_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(PR_SMEM)));
         WF_CUDA(cudaFuncSetAttribute(prefill_kernel<16>, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(sm_smem<16>())));
         WF_CUDA(cudaFuncSetAttribute(prefill_kernel<32>, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(sm_smem<32>())));
         WF_CUDA(cudaFuncSetAttribute(prefill_kernel<64>, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(sm_smem<64>())));
@@ -535,12 +900,22 @@ static int prefill_impl(const char* who, const void* x, int x_dtype, int64_t ldx
     lc.gridDim = dim3(static_cast<unsigned>(tiles < sms ? tiles : sms));
     lc.blockDim = dim3(SM_THREADS);
     lc.stream = st;
-    cudaLaunchAttribute attr[1];
+    cudaLaunchAttribute attr[2];
     attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
     attr[0].val.programmaticStreamSerializationAllowed = 1;
     lc.attrs = attr;
     lc.numAttrs = 1;
-    if (ntok == 16) {
+    if (pair) {
+        const long long clusters = tiles < sms / 2 ? tiles : sms / 2;
+        lc.gridDim = dim3(static_cast<unsigned>(2 * clusters));
+        attr[1].id = cudaLaunchAttributeClusterDimension;
+        attr[1].val.clusterDim.x = 2;
+        attr[1].val.clusterDim.y = 1;
+        attr[1].val.clusterDim.z = 1;
+        lc.numAttrs = 2;
+        lc.dynamicSmemBytes = PR_SMEM;
+        WF_CUDA(cudaLaunchKernelEx(&lc, prefill_pair_kernel, tmap_a, tmap_p, pp));
+    } else if (ntok == 16) {
         lc.dynamicSmemBytes = sm_smem<16>();
         WF_CUDA(cudaLaunchKernelEx(&lc, prefill_kernel<16>, tmap_a, tmap_p, pp));
     } else if (ntok == 32) {
@@ -560,9 +935,8 @@ extern "C" int wf_bitlinear_prefill(const void* x, int x_dtype, int64_t ldx, con
                                     int layout, const float* w_scale, float w_scale_host, const void* bias, int bias_dtype,
                                     void* y, int y_dtype, int64_t ldy, int32_t* acc_out, int64_t M, int64_t N, int64_t K,
                                     float eps, void* workspace, size_t workspace_bytes, unsigned flags, void* stream) {
-    (void)flags;
     return prefill_impl("wf_bitlinear_prefill", x, x_dtype, ldx, x_scale, codes, layout, w_scale, 0, w_scale_host, bias,
-                        bias_dtype, y, y_dtype, ldy, acc_out, 1, M, N, K, eps, workspace, workspace_bytes, stream);
+                        bias_dtype, y, y_dtype, ldy, acc_out, 1, M, N, K, eps, workspace, workspace_bytes, flags, stream);
 }
 
 extern "C" int wf_bitlinear_prefill_batched(const void* x, int x_dtype, int64_t ldx, const uint8_t* codes, int layout,
@@ -572,5 +946,5 @@ extern "C" int wf_bitlinear_prefill_batched(const void* x, int x_dtype, int64_t 
     WF_REQUIRE(w_scale, "wf_bitlinear_prefill_batched: w_scale must point to the per-problem scales");
     WF_REQUIRE(x_dtype != WF_I8, "wf_bitlinear_prefill_batched: takes floating-point activations");
     return prefill_impl("wf_bitlinear_prefill_batched", x, x_dtype, ldx, nullptr, codes, layout, w_scale, w_scale_stride, 0.f,
-                        nullptr, 0, y, y_dtype, ldy, acc_out, batch, M, N, K, eps, workspace, workspace_bytes, stream);
+                        nullptr, 0, y, y_dtype, ldy, acc_out, batch, M, N, K, eps, workspace, workspace_bytes, 0u, stream);
 }

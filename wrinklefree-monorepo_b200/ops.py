@@ -173,7 +173,7 @@ def _workspace(device, nbytes: int) -> torch.Tensor:
 def bitlinear(x: torch.Tensor, codes: torch.Tensor, w_scale, bias: Optional[torch.Tensor] = None,
               out_dtype: Optional[torch.dtype] = None, layout: int = L.LAYOUT_WF16, x_scale: Optional[torch.Tensor] = None,
               eps: float = 1e-5, want_acc: bool = False, pdl: bool = False, path: str = "auto",
-              out: Optional[torch.Tensor] = None):
+              out: Optional[torch.Tensor] = None, prefill_form: str = "auto"):
     """y = BitLinear(x) on packed weights: per-token int8 quantization of x (fused for small
     token counts), exact int32 contraction with the ternary codes, fp32 rescale
     ``(float(acc) * (1/s_x[m])) * s_w`` and optional bias.
@@ -181,6 +181,7 @@ def bitlinear(x: torch.Tensor, codes: torch.Tensor, w_scale, bias: Optional[torc
     x: [..., K] float32/float16/bfloat16, or int8 (already quantized; x_scale [M] optional).
     codes: uint8 [N, K/4] in `layout`.  w_scale: device tensor (first element used) or float.
     path: "auto" (decode kernel for few tokens, the tensor-core contraction otherwise), "decode" or "prefill".
+    prefill_form: "auto", or "pair" / "single" to force the two-SM or the one-SM tile form of the contraction.
     Returns y [..., N] (and the int32 accumulators [M, N] when want_acc).
     """
     _need_cuda(x, codes, bias, x_scale)
@@ -206,6 +207,7 @@ def bitlinear(x: torch.Tensor, codes: torch.Tensor, w_scale, bias: Optional[torc
         codes = codes.contiguous()
     lib = L.lib()
     flags = L.FLAG_PDL if pdl else 0
+    flags |= {"auto": 0, "pair": L.FLAG_PREFILL_PAIR, "single": L.FLAG_PREFILL_SINGLE}[prefill_form]
     # auto: the tensor-core contraction above DECODE_MAX_TOKENS tokens, and from 16 tokens on for matrices of at least
     # 4 Mi weights (measured: 4096 x 4096 at 32 tokens 14 us against 20 us on the decode kernel; small layers the reverse)
     use_prefill = path == "prefill" or (path == "auto" and (m > DECODE_MAX_TOKENS or (m >= 16 and n * k >= (1 << 22))))
