@@ -530,9 +530,14 @@ def decoder_section(wf, torch, device, world, full: bool):
         model.capture(masked=False)
         ms = timed(model, 16)
         by = model.weight_bytes_per_step()
-        out.append({"model": "llama3-8b-shape", "tp": world, "batch": batch, "context": 2048, "ms_per_step": round(ms, 3),
-                    "tok_s": round(batch / ms * 1e3, 1), "GB_per_step_per_rank": round(by / 1e9, 3),
-                    "GBps_per_rank": round(by / ms / 1e6, 1)})
+        row = {"model": "llama3-8b-shape", "tp": world, "batch": batch, "context": 2048, "ms_per_step": round(ms, 3),
+               "tok_s": round(batch / ms * 1e3, 1), "GB_per_step_per_rank": round(by / 1e9, 3),
+               "GBps_per_rank": round(by / ms / 1e6, 1), "attention": "wf_attn_decode_bf16"}
+        if world == 1:  # the same step with the framework's fused attention in place of this library's kernel
+            model.pos.fill_(2047)
+            model.capture(masked=False, attention="library")
+            row["ms_per_step_library_attention"] = round(timed(model, 16), 3)
+        out.append(row)
         del model
         torch.cuda.empty_cache()
     if world == 1:

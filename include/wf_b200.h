@@ -51,6 +51,12 @@ extern "C" {
 #define WF_ACT_PER_TOKEN 0  /* per row absmax, arithmetic in the element type of x */
 #define WF_ACT_PER_TENSOR 1 /* one absmax for the whole tensor, fp32, scale = max/127 returned */
 
+/* ---- fused input modes of a grouped decode problem (wf_problem.x_mode) ---- */
+#define WF_X_PLAIN 0
+#define WF_X_SILU 1
+#define WF_X_RELU2 2
+#define WF_X_NORM 3
+
 /* ---- launch flags of the contraction entry points ---- */
 #define WF_FLAG_PDL 1u /* launch with programmatic stream serialization: the kernel streams its
                           first weights before it waits for the previous kernel of the stream */
@@ -213,7 +219,29 @@ typedef struct WF_ALIGN64 wf_problem {
     int32_t x_dtype, y_dtype, bias_dtype, layout;
     float w_scale_host, eps;
     int32_t _item_begin, _row_items, _chunks, _kb_full, _tail_bytes; /* 128 bytes up to here */
-    int32_t _kb_seg, _ksegs, _pad[14]; /* K is streamed in _ksegs segments of _kb_seg 512-weight blocks */
+    int32_t _kb_seg, _ksegs; /* K is streamed in _ksegs segments of _kb_seg 512-weight blocks */
+    /* Fused input (bf16 x only; zero-initialise for a plain projection).  The activations the projection quantizes are
+     * computed on the fly, with the arithmetic of the unfused kernels of this library:
+     *   WF_X_SILU / WF_X_RELU2: act(x) * x2, x = gate and x2 = up of an MLP (wf_act_mul_bf16) - replaces the activation
+     *     in front of down_proj (packages/training/src/wrinklefree/models/ffn.py:74-87; bitnet_mlp_forward_cpu fuses it the
+     *     same way, packages/inference/extern/sglang-bitnet/sgl-kernel/csrc/cpu/bitnet_fused_layer.cpp:150-375);
+     *   WF_X_NORM: h = x (+ x2), then h * rsqrt(mean(h^2) + norm_eps) * norm_w (wf_add_rmsnorm_bf16) - the residual add and
+     *     RMSNorm in front of q/k/v or gate/up (the A100 stack fuses the quantization into its norm,
+     *     packages/inference/extern/BitNet/gpu/model.py:54-76); h_out (nullable) receives h, written once per launch.
+     * x2 and h_out have the row stride of x. */
+    const void* x2;
+    const void* norm_w;
+    void* h_out;
+    int32_t x_mode;
+    float norm_eps;
+    /* Optional: a range of global memory (typically the packed weights of the NEXT launch of the stream) that this
+     * launch asks the L2 cache to fetch while it runs (non-multicast cp.async.bulk.prefetch.L2, issued at kernel entry,
+     * spread over the CTAs).  A decode step at small batch is a chain of short, latency-bound launches: with the next
+     * weights on their way to L2 meanwhile, the HBM transfer overlaps the chain instead of adding to it.
+     * prefetch_bytes must be a multiple of 16, prefetch 16-byte aligned; 0 / NULL: none. */
+    const void* prefetch;
+    int64_t prefetch_bytes;
+    int32_t _pad[2];
     uint64_t _tmap_main[16]; /* TMA descriptor: [K/512 blocks][N rows][128 bytes] view of codes, box of _kb_seg blocks */
     uint64_t _tmap_last[16]; /* the same view with the (shorter) box of the last segment */
     uint64_t _tmap_tail[16]; /* TMA descriptor of the last, partial 128-byte column block (if any) */
@@ -266,6 +294,24 @@ int wf_add_rmsnorm_bf16(void* h, const void* delta, const void* weight, void* y,
 int wf_rope_kv_bf16(void* q, const void* k, const void* v, const float* cos, const float* sin, const int64_t* pos, void* kcache,
                     void* vcache, int64_t B, int nq, int nkv, int D, int T, unsigned flags, void* stream);
 int wf_act_mul_bf16(const void* gate, const void* up, void* out, int64_t n, int mode, unsigned flags, void* stream);
+
+/*
+ * Decode-step attention over the bf16 KV cache (one new token per sequence, grouped-query heads): for every query head
+ * out[b, h, :] = softmax_t(scale * q[b, h, :] . K[b, kv(h), t, :]) V[b, kv(h), t, :] over the valid positions t.
+ * Replaces, for the decode step, the attention core of the reference model
+ * (packages/training/src/wrinklefree/models/attention.py:186-208: repeat_kv, QK^T, fp32 softmax, PV) on the layout of a
+ * KV cache (packages/inference/src/wrinklefree_inference/kv_cache/kv_cache.py:96-370 keeps one; the reference model itself
+ * recomputes the prompt every step).
+ * q: [B, nq * D] bf16 (already rotated); kcache / vcache: [B, nkv, T, D] bf16; out: [B, nq * D] bf16.
+ * pos: device scalar, positions 0 .. *pos are valid (nullable: all T positions).  nq % nkv == 0, nq / nkv <= 8, D = 64 or 128.
+ * Keys and values are read once per step for the whole group of query heads; persistent CTAs share the tiles of all
+ * (sequence, KV head) pairs evenly and merge shared pairs in the same launch.  workspace: wf_attn_decode_workspace_bytes(...) bytes, 256-byte aligned
+ * (merge tickets and partial results), ZERO before its first use (every launch leaves its tickets zero again); it may
+ * be shared by the launches of one stream, also of different shapes.  flags: WF_FLAG_PDL.
+ */
+size_t wf_attn_decode_workspace_bytes(int64_t B, int nq, int nkv, int D, int T);
+int wf_attn_decode_bf16(const void* q, const void* kcache, const void* vcache, const int64_t* pos, void* out, int64_t B, int nq,
+                        int nkv, int D, int T, float scale, void* workspace, size_t workspace_bytes, unsigned flags, void* stream);
 
 /*
  * One-shot all-reduce (sum) over peer memory for the small tensors that follow a row-parallel projection in the

@@ -177,3 +177,115 @@ def test_bf16_prefill_and_decode_steps_follow_reference_model(wf, act):
         print(f"step {i} {act}: vs bf16 reference {e1:.4f}, vs fp32 reference {e2:.4f}")
         assert e1 <= 6e-2 and e2 <= 1.5 * ref_gap, (i, e1, e2)
     wf.device_status()
+
+
+@pytest.mark.parametrize("B,nq,nkv,D,T,pos", [(1, 32, 8, 128, 2080, 2047), (3, 9, 3, 64, 100, 37), (32, 32, 8, 128, 300, 299),
+                                              (2, 4, 4, 64, 64, 0), (5, 8, 1, 128, 1000, None), (7, 6, 2, 64, 130, 128), (300, 8, 4, 128, 70, 69)])
+def test_decode_attention_kernel(wf, B, nq, nkv, D, T, pos):
+    """The decode-step attention kernel (grouped-query heads, context split over CTAs and merged in the launch, bf16
+    cache) against fp32 softmax attention over the valid positions: max|a-b| / max|b| <= 1e-2 (the probabilities are
+    rounded to bf16 in front of the second product, the output is bf16).  Positions beyond the valid length hold
+    large garbage that must not leak in."""
+    from wrinklefree_monorepo_b200 import ops
+
+    dev = torch.device("cuda", 0)
+    g = torch.Generator().manual_seed(B * 1000 + T)
+    q = torch.randn(B, nq * D, generator=g).bfloat16().to(dev)
+    kc = torch.randn(B, nkv, T, D, generator=g).bfloat16().to(dev)
+    vc = torch.randn(B, nkv, T, D, generator=g).bfloat16().to(dev)
+    n_valid = T if pos is None else pos + 1
+    kc[:, :, n_valid:] = 1e4
+    vc[:, :, n_valid:] = -1e4
+    out = torch.empty(B, nq * D, dtype=torch.bfloat16, device=dev)
+    pos_t = None if pos is None else torch.tensor(pos, dtype=torch.long, device=dev)
+    for _ in range(2):  # the merge tickets must be reusable
+        out.fill_(7)
+        ops.attn_decode(q, kc, vc, pos_t, out)
+        qf = q.float().view(B, nkv, nq // nkv, D)
+        kf, vf = kc.float()[:, :, :n_valid], vc.float()[:, :, :n_valid]
+        s = torch.einsum("bhgd,bhtd->bhgt", qf, kf) * D ** -0.5
+        ref = torch.einsum("bhgt,bhtd->bhgd", torch.softmax(s, -1), vf).reshape(B, nq * D)
+        err = float((out.float() - ref).abs().max() / ref.abs().max())
+        assert err <= 1e-2, err
+
+
+def test_fused_inputs_of_grouped_projections(wf, oracle_c):
+    """The fused input modes of the grouped decode kernel against the unfused kernels of the library: rmsnorm(x + x2)
+    in front of a q/k/v-like group (all three forms of the kernel: shared tokens, a single matrix, a streaming
+    stack), and act(gate) * up in front of a down-like projection.  Activation modes: accumulators and outputs
+    identical to the unfused chain.  Norm mode: the residual output identical; the projection outputs within 1e-2
+    (the mean of squares is summed in another order, which may move single int8 codes)."""
+    from wrinklefree_monorepo_b200 import ops
+
+    dev = torch.device("cuda", 0)
+    g = torch.Generator().manual_seed(11)
+    for (m, k, ns) in ((1, 4096, (4096, 1024, 1024)), (5, 576, (576, 192, 192)), (3, 2560, (6912,)), (20, 640, (512, 512))):
+        h = torch.randn(m, k, generator=g).bfloat16().to(dev)
+        delta = torch.randn(m, k, generator=g).bfloat16().to(dev)
+        w = (1 + 0.1 * torch.randn(k, generator=g)).bfloat16().to(dev)
+        mats = [wf.pack_ternary((torch.randn(n, k, generator=g) * 0.02).to(dev)) for n in ns]
+        for with_delta in (True, False):
+            # unfused: norm kernel, then the group on its output
+            h_ref = h.clone()
+            xn = torch.empty_like(h)
+            ops.add_rmsnorm_(h_ref, delta if with_delta else None, w, xn, 1e-5)
+            ref = ops.DecodeGroup([dict(x=xn, codes=c, w_scale=s_, out_dtype=torch.float32) for c, s_ in mats]).run()
+            h_out = torch.zeros_like(h)
+            probs = [dict(x=h, x2=delta if with_delta else None, x_mode="norm", norm_w=w, norm_eps=1e-5, codes=c, w_scale=s_,
+                          out_dtype=torch.float32, h_out=h_out if i == 0 else None) for i, (c, s_) in enumerate(mats)]
+            grp = ops.DecodeGroup(probs)
+            for pdl in (False, True):
+                h_out.zero_()
+                got = grp.run(pdl=pdl)
+                assert torch.equal(h_out, h_ref), (m, k, with_delta)
+                for a, b in zip(got, ref):
+                    err = float((a - b).abs().max() / b.abs().max())
+                    assert err <= 1e-2, (m, k, with_delta, err)
+    # a streaming stack (thousands of row items) with the norm fused in
+    m, k = 2, 1024
+    h = torch.randn(m, k, generator=g).bfloat16().to(dev)
+    w = (1 + 0.1 * torch.randn(k, generator=g)).bfloat16().to(dev)
+    mats = [wf.pack_ternary((torch.randn(6000 + 16 * i, k, generator=g) * 0.02).to(dev)) for i in range(8)]
+    xn = torch.empty_like(h)
+    ops.add_rmsnorm_(h.clone(), None, w, xn, 1e-6)
+    ref = ops.DecodeGroup([dict(x=xn, codes=c, w_scale=s_, out_dtype=torch.float32) for c, s_ in mats]).run()
+    got = ops.DecodeGroup([dict(x=h, x_mode="norm", norm_w=w, norm_eps=1e-6, codes=c, w_scale=s_, out_dtype=torch.float32) for c, s_ in mats]).run(pdl=True)
+    for a, b in zip(got, ref):
+        assert float((a - b).abs().max() / b.abs().max()) <= 1e-2
+    # activation modes: bit-exact against act_mul + projection
+    for (m, k, n, mode) in ((1, 14336, 4096, "silu"), (4, 1536, 576, "relu2"), (9, 1024, 300, "silu"), (33, 640, 128, "relu2")):
+        gate = torch.randn(m, k, generator=g).bfloat16().to(dev)
+        up = torch.randn(m, k, generator=g).bfloat16().to(dev)
+        codes, sc = wf.pack_ternary((torch.randn(n, k, generator=g) * 0.02).to(dev))
+        act = torch.empty_like(gate)
+        ops.act_mul(gate, up, act, mode)
+        y_ref, acc_ref = wf.bitlinear(act, codes, sc, out_dtype=torch.float32, want_acc=True, path="decode")
+        grp = ops.DecodeGroup([dict(x=gate, x2=up, x_mode=mode, codes=codes, w_scale=sc, out_dtype=torch.float32, want_acc=True)])
+        y = grp.run()[0]
+        assert torch.equal(grp.accs[0], acc_ref) and torch.equal(y, y_ref), (m, k, n, mode)
+    wf.device_status()
+
+
+def test_fused_decode_step_equals_unfused(wf):
+    """The six-launch decode step (fused inputs) against the ten-launch step of the same model."""
+    from wrinklefree_monorepo_b200.decoder import DecoderConfig, TernaryDecoder
+
+    cfg = DecoderConfig(layers=3, hidden=256, n_q=4, n_kv=2, head_dim=64, intermediate=512, vocab=1000)
+    dev = torch.device("cuda", 0)
+    B, S, T = 3, 7, 16
+    ids = torch.randint(0, cfg.vocab, (B, S), generator=torch.Generator().manual_seed(6)).to(dev)
+    outs = []
+    for fuse in (True, False):
+        m = TernaryDecoder(cfg, B, T, dev, seed=2, fuse=fuse)
+        assert m.fused == fuse
+        m.capture(masked=True)
+        steps = []
+        for t in range(S):
+            m.tok.copy_(ids[:, t])
+            m.graph.replay()
+            steps.append(m.logits.float().clone())
+        outs.append(torch.stack(steps))
+    err = float((outs[0] - outs[1]).abs().max() / outs[1].abs().max())
+    assert err <= 2e-2, err
+    assert (outs[0].argmax(-1) == outs[1].argmax(-1)).float().mean() >= 0.9
+    wf.device_status()

@@ -537,3 +537,66 @@ def test_batched_prefill_equals_per_layer_calls(wf, oracle_c):
             assert np.array_equal(acc[i].cpu().numpy(), acc_o), (b, m, k, n, i)
             assert np.array_equal(y[i].cpu().numpy(), oracle_c.rescale(acc_o, s, np.float32(0.01 * (i + 1))))
     wf.device_status()
+
+
+# ---------------------------------------------------------------- training step on the packed weights
+@pytest.mark.parametrize("dt,tol", [("f32", 1e-5), ("bf16", 2e-2)])
+def test_training_step_on_packed_weights(wf, dt, tol):
+    """With gradients enabled at lambda = 1 the module runs the packed forward inside a straight-through autograd
+    function.  Its output and its gradients are held to the reference's own formula
+    (F.linear(x + (aq(x) - x).detach(), w + (wq(w) - w).detach(), b), bitlinear.py:99-113) evaluated by autograd on
+    the same tensors; an optimizer step must invalidate the cached codes (test_paper_verification.py:302-381 checks
+    the same properties of the reference: gradients reach x, weight and bias and are non-zero)."""
+    z, x, w = load("k512")
+    m, k, n, _ = gi.CASES["k512"]
+    tdt = TDT[dt]
+    g = torch.Generator().manual_seed(17)
+    bias0 = torch.randn(n, generator=g) * 0.1
+    dy = torch.randn(2, m // 2, n, generator=g).to(tdt).to(DEV)
+    layer = wf.BitLinear(k, n, bias=True).to(DEV)
+    with torch.no_grad():
+        layer.weight.copy_(w.to(DEV))
+        layer.bias.copy_(bias0.to(DEV))
+    xg = x.to(tdt).to(DEV).reshape(2, m // 2, k).requires_grad_(True)
+    y = layer(xg)
+    assert y.grad_fn is not None and "PackedSTE" in type(y.grad_fn).__name__ and y.dtype == tdt
+    y.backward(dy)
+    # the reference formula on the same tensors
+    xr = x.to(tdt).to(DEV).reshape(2, m // 2, k).requires_grad_(True)
+    wr = layer.weight.detach().clone().requires_grad_(True)
+    br = layer.bias.detach().clone().requires_grad_(True)
+    wl = wr.to(tdt)
+    w_quant = wl + (layer.weight_quant(wl) - wl).detach()
+    x_quant = xr + (layer.activation_quant(xr) - xr).detach()
+    y_ref = torch.nn.functional.linear(x_quant, w_quant, br.to(tdt))
+    y_ref.backward(dy)
+
+    def rel(a, b):
+        return float((a.float() - b.float()).abs().max() / b.float().abs().max())
+
+    assert rel(y, y_ref) <= (1e-5 if dt == "f32" else 1e-2)
+    assert rel(xg.grad, xr.grad) <= tol and rel(layer.weight.grad, wr.grad) <= tol and rel(layer.bias.grad, br.grad) <= tol
+    assert layer.weight.grad.dtype == layer.weight.dtype and float(xg.grad.abs().sum()) > 0
+    # an optimizer step changes the weight: the next forward must re-pack
+    codes_before = layer.packed_weight(tdt)[0].clone()
+    opt = torch.optim.SGD(layer.parameters(), lr=0.5)
+    opt.step()
+    y2 = layer(xg.detach())
+    codes_after = layer.packed_weight(tdt)[0]
+    assert not torch.equal(codes_before, codes_after)
+    with torch.no_grad():
+        want = torch.nn.functional.linear(layer.activation_quant(xg.detach()), layer.weight_quant(layer.weight.to(tdt)), layer.bias.to(tdt))
+    assert rel(y2, want) <= (1e-5 if dt == "f32" else 1e-2)
+    # during the lambda warm-up the module evaluates the reference's mixing formula
+    warm = wf.LambdaWarmup(warmup_steps=4)
+    wf.set_global_lambda_warmup(warm)
+    try:
+        warm.step()
+        warm.step()  # lambda = 0.5
+        y3 = layer(xg)
+        assert "PackedSTE" not in type(y3.grad_fn).__name__
+        wl2 = layer.weight.to(tdt)
+        want3 = torch.nn.functional.linear(xg + 0.5 * (layer.activation_quant(xg) - xg), wl2 + 0.5 * (layer.weight_quant(wl2) - wl2), layer.bias.to(tdt))
+        assert rel(y3, want3) <= 1e-6
+    finally:
+        wf.set_global_lambda_warmup(None)

@@ -81,6 +81,29 @@ def _worker(rank, world, port, results):
         dist.all_gather(gathered, y2)
         assert all(torch.equal(gathered[0], t_) for t_ in gathered)  # identical bits on every rank
         ar.status()
+        # ---- the decoder: heads, MLP width and the output head sharded over the ranks, against one rank on its own
+        from wrinklefree_monorepo_b200.decoder import DecoderConfig, TernaryDecoder
+
+        solo = [dist.new_group([r]) for r in range(world)][rank]  # collective: every rank creates every group
+        cfg = DecoderConfig(layers=2, hidden=256, n_q=4, n_kv=2, head_dim=64, intermediate=512, vocab=1000)
+        ids = torch.randint(0, cfg.vocab, (3, 9), generator=torch.Generator().manual_seed(5)).to(dev)
+        m_tp = TernaryDecoder(cfg, 3, 16, dev, seed=3)
+        m_1 = TernaryDecoder(cfg, 3, 16, dev, seed=3, group=solo)
+        assert m_tp.tp == world and m_1.tp == 1 and m_tp.lm_head.shape[0] == cfg.vocab // world
+        l_tp, l_1 = m_tp.prefill(ids).float(), m_1.prefill(ids).float()
+        assert l_tp.shape == l_1.shape
+        assert float((l_tp - l_1).abs().max() / l_1.abs().max()) < 3e-2  # row-parallel layers quantize their K slices locally
+        m_tp.capture(masked=True)
+        m_1.capture(masked=True)
+        toks_tp, toks_1 = m_tp.decode(4), m_1.decode(4)
+        both = [torch.empty_like(toks_tp) for _ in range(world)]
+        dist.all_gather(both, toks_tp)
+        assert all(torch.equal(both[0], t_) for t_ in both)  # every rank picked the same tokens
+        assert int(toks_tp.max()) < cfg.vocab and (toks_tp == toks_1).float().mean() >= 0.5
+        # the sharded head's greedy pick equals the arg-max of the gathered rows
+        full = [torch.empty_like(m_tp.logits) for _ in range(world)]
+        dist.all_gather(full, m_tp.logits.contiguous())
+        assert torch.equal(torch.cat(full, -1).float().argmax(-1), m_tp.next_tok)
         wf.device_status()
         results[rank] = "ok"
     finally:

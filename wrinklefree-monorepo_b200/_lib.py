@@ -17,6 +17,7 @@ LAYOUT_WF16, LAYOUT_I2S, LAYOUT_SEQ_LSB, LAYOUT_SEQ_MSB, LAYOUT_HF = 0, 1, 2, 3,
 PACK_FP32, PACK_CAST_BF16, PACK_CAST_F16 = 0, 1, 2
 ACT_PER_TOKEN, ACT_PER_TENSOR = 0, 1
 MAXABS_HALF, MAXABS_SIGN = 0, 1
+X_PLAIN, X_SILU, X_RELU2, X_NORM = 0, 1, 2, 3
 FLAG_PDL = 1
 FLAG_X_READY = 2
 FLAG_PREFILL_PAIR, FLAG_PREFILL_SINGLE = 4, 8
@@ -33,7 +34,8 @@ class Problem(C.Structure):
                 ("x_dtype", C.c_int32), ("y_dtype", C.c_int32), ("bias_dtype", C.c_int32), ("layout", C.c_int32),
                 ("w_scale_host", _f32), ("eps", _f32),
                 ("_item_begin", C.c_int32), ("_row_items", C.c_int32), ("_chunks", C.c_int32), ("_kb_full", C.c_int32),
-                ("_tail_bytes", C.c_int32), ("_kb_seg", C.c_int32), ("_ksegs", C.c_int32), ("_pad", C.c_int32 * 14),
+                ("_tail_bytes", C.c_int32), ("_kb_seg", C.c_int32), ("_ksegs", C.c_int32),
+                ("x2", _p), ("norm_w", _p), ("h_out", _p), ("x_mode", C.c_int32), ("norm_eps", _f32), ("prefetch", _p), ("prefetch_bytes", _i64), ("_pad", C.c_int32 * 2),
                 ("_tmap_main", C.c_uint64 * 16), ("_tmap_last", C.c_uint64 * 16), ("_tmap_tail", C.c_uint64 * 16)]
 
 
@@ -72,6 +74,8 @@ _SIGNATURES = {
     "wf_add_rmsnorm_bf16": (_int, [_p, _p, _p, _p, _i64, _i64, _f32, _u32, _p]),
     "wf_rope_kv_bf16": (_int, [_p, _p, _p, _p, _p, _p, _p, _p, _i64, _int, _int, _int, _int, _u32, _p]),
     "wf_act_mul_bf16": (_int, [_p, _p, _p, _i64, _int, _u32, _p]),
+    "wf_attn_decode_workspace_bytes": (_sz, [_i64, _int, _int, _int, _int]),
+    "wf_attn_decode_bf16": (_int, [_p, _p, _p, _p, _p, _i64, _int, _int, _int, _int, _f32, _p, _sz, _u32, _p]),
     "wf_ar_handle_bytes": (_int, []),
     "wf_ar_init": (_int, [_int, _int, _sz, C.POINTER(C.c_void_p), _p]),
     "wf_ar_connect": (_int, [_p, _p]),

@@ -2,14 +2,15 @@
 (wrinklefree/models/bitlinear.py:12-192): same class names, constructor,
 methods, parameters and state_dict.
 
-Inference (no gradient needed, lambda == 1, CUDA input) runs on the packed
-weights through the C ABI: the weight is absmean-ternarized and packed once per
-weight version and input dtype, and every forward is one fused
-quantize-and-contract kernel.  Whenever a gradient is required or the lambda
-warm-up is active, the module evaluates the straight-through-estimator formula
-of the reference with torch operators, because that formula *is* the training
-definition; it is not an accelerated path and the CUDA kernels never route
-through it.
+At lambda == 1 a CUDA input runs on the packed weights through the C ABI: the
+weight is absmean-ternarized and packed once per weight version and input dtype
+(an optimizer step changes the version, so the next forward re-packs), and
+every forward is a quantize-and-contract kernel.  With gradients enabled the
+same forward is wrapped in a straight-through autograd function whose backward
+uses the ternary codes and the saved int8 activations.  Only while the lambda
+warm-up is active (0 <= lambda < 1 mixes float and quantized operands) and for
+gradients on a machine without a GPU does the module evaluate the reference's
+formula with torch operators.
 """
 from __future__ import annotations
 
@@ -21,6 +22,45 @@ import torch.nn.functional as F
 
 from . import ops
 from .lambda_warmup import get_current_lambda
+
+
+class _PackedSTE(torch.autograd.Function):
+    """Training step of a BitLinear at lambda = 1 on the packed weights (straight-through estimator).
+
+    Forward: per-token int8 quantization + exact integer contraction with the cached ternary codes + fp32 rescale, i.e.
+    the value of ``F.linear(activation_quant(x), weight_quant(w), bias)`` without re-ternarizing the latent weight or
+    running a float GEMM over integer-valued operands (wrinklefree/models/bitlinear.py:99-113).
+    Backward: the gradients autograd derives from the reference's ``v + (quant(v) - v).detach()`` form:
+    dX = dY @ weight_quant(w)  (the ternary codes times their scale, unpacked on the GPU for this one product),
+    dW = dY^T @ activation_quant(x)  (rebuilt from the saved int8 codes and per-token scales, 1 byte per element saved
+    instead of the activation itself), dbias = sum(dY)."""
+
+    @staticmethod
+    def forward(ctx, x, weight, bias, layer):
+        codes, scale = layer.packed_weight(x.dtype)
+        k = x.shape[-1]
+        q, s = ops.act_quant_i8(x.reshape(-1, k), eps=layer.eps)
+        y = ops.bitlinear(q, codes, scale, bias=bias, x_scale=s, out_dtype=x.dtype)
+        ctx.save_for_backward(q, s, codes, scale)
+        ctx.in_shape, ctx.x_dtype, ctx.w_dtype = x.shape, x.dtype, weight.dtype
+        ctx.has_bias = bias is not None
+        return y.reshape(*x.shape[:-1], weight.shape[0])
+
+    @staticmethod
+    def backward(ctx, dy):
+        q, s, codes, scale = ctx.saved_tensors
+        n, k = codes.shape[0], codes.shape[1] * 4
+        dy2 = dy.reshape(-1, n)
+        dx = dw = db = None
+        if ctx.needs_input_grad[0]:
+            w_q = ops.unpack_codes(codes, n, k).to(dy2.dtype) * scale[0].to(dy2.dtype)
+            dx = (dy2 @ w_q).reshape(ctx.in_shape)
+        if ctx.needs_input_grad[1]:
+            x_q = q.to(ctx.x_dtype) / s.to(ctx.x_dtype).unsqueeze(1)  # the values activation_quant(x) holds
+            dw = (dy2.t() @ x_q.to(dy2.dtype)).to(ctx.w_dtype)
+        if ctx.has_bias and ctx.needs_input_grad[2]:
+            db = dy2.sum(0)
+        return dx, dw, db, None
 
 
 class BitLinear(nn.Linear):
@@ -62,25 +102,25 @@ class BitLinear(nn.Linear):
         super()._load_from_state_dict(*args, **kwargs)
         self.invalidate_packed()
 
-    def _fast_path(self, x: torch.Tensor, lam: float) -> bool:
-        if lam != 1.0:
-            return False
-        if torch.is_grad_enabled() and (x.requires_grad or self.weight.requires_grad
-                                        or (self.bias is not None and self.bias.requires_grad)):
-            return False
-        return True
+    def _needs_grad(self, x: torch.Tensor) -> bool:
+        return torch.is_grad_enabled() and (x.requires_grad or self.weight.requires_grad
+                                            or (self.bias is not None and self.bias.requires_grad))
 
     def forward(self, x: torch.Tensor) -> torch.Tensor:
         lam = get_current_lambda()
-        if self._fast_path(x, lam):
+        needs_grad = self._needs_grad(x)
+        if lam == 1.0 and (x.is_cuda or not needs_grad):
             if not x.is_cuda:
                 raise RuntimeError("BitLinear inference runs on the CUDA kernels only; got a CPU tensor "
                                    "(there is no CPU fallback)")
             if x.dtype not in (torch.float32, torch.bfloat16, torch.float16):
                 raise TypeError(f"BitLinear: unsupported input dtype {x.dtype}")
+            if needs_grad:  # training at full quantization: packed forward, straight-through backward
+                return _PackedSTE.apply(x, self.weight, self.bias, self)
             codes, scale = self.packed_weight(x.dtype)
             return ops.bitlinear(x, codes, scale, bias=self.bias, out_dtype=x.dtype, eps=self.eps)
-        # training definition (straight-through estimator with lambda mixing)
+        # the reference's formula with torch operators: lambda warm-up (0 < lambda < 1 mixes float and quantized
+        # operands, which is no single packed product), and gradients on a machine without a GPU
         w = self.weight.to(x.dtype)
         w_quant = w + lam * (self.weight_quant(w) - w).detach()
         x_quant = x + lam * (self.activation_quant(x) - x).detach()

@@ -71,6 +71,8 @@ struct DecodeCfg {
     int x_ready;      // streaming form: x does not depend on the previous kernel; only the stores wait for it
     int ib_off, ib_cap;  // shared-memory copy of the problems' first item indices (searched instead of global memory)
     int decoupled;    // 1: every consumer warp owns whole 16-row items (RI == 1); 0: the 16 warps share each item
+    int ss_off;       // per-warp partial sums of squares of the fused RMSNorm input mode: [2][MT][16] floats
+    int prefetch;     // some problem names a range to prefetch into L2
 };
 
 template <int NTHREADS = DEC_CONSUMERS>
@@ -152,11 +154,66 @@ __device__ __forceinline__ void decode8(const uint4 (&r)[XCache<XDT>::V], float 
     }
 }
 
+// ---- fused input modes (bf16 only): the activations a projection quantizes are computed on the fly from the
+// tensors its unfused predecessor kernel would have read, with that kernel's arithmetic (every intermediate rounded
+// to bf16 where the kernel rounds), so the int8 codes equal those of the unfused chain up to the summation order of
+// the norm's mean of squares.
+//   WF_X_SILU / WF_X_RELU2: x = act(x) * x2            (the gate activation in front of a down projection)
+//   WF_X_NORM:              h = x (+ x2);  x = h * rsqrt(mean(h^2) + norm_eps) * norm_w   (residual add + RMSNorm)
+__device__ __forceinline__ float rbf(float v) { return __bfloat162float(__float2bfloat16_rn(v)); }
+__device__ __forceinline__ float fused_act(float a, int mode) {
+    float t;
+    if (mode == WF_X_SILU) {
+        t = a / (1.0f + __expf(-a));
+    } else {
+        const float rl = rbf(fmaxf(a, 0.f));
+        t = rl * rl;
+    }
+    return rbf(t);
+}
+// the residual stream values h = bf16(x + x2) of 8 consecutive k
+template <int XDT>
+__device__ __forceinline__ void load8_resid(const wf_problem& p, const void* x, int64_t off, float (&f)[8]) {
+    load8<XDT>(x, off, f);
+    if (p.x2) {
+        float d[8];
+        load8<XDT>(p.x2, off, d);
+#pragma unroll
+        for (int i = 0; i < 8; ++i) f[i] = rbf(f[i] + d[i]);
+    }
+}
+// the effective activations of 8 consecutive k of the row that starts at element `base`
+template <int XDT>
+__device__ __forceinline__ void load8_eff(const wf_problem& p, const void* x, int64_t base, int k, float rnorm, float (&f)[8]) {
+    if constexpr (XDT != WF_BF16) {
+        load8<XDT>(x, base + k, f);
+    } else {
+        if (p.x_mode == WF_X_PLAIN) {
+            load8<XDT>(x, base + k, f);
+        } else if (p.x_mode == WF_X_NORM) {
+            load8_resid<XDT>(p, x, base + k, f);
+            float w[8];
+            load8<XDT>(p.norm_w, k, w);
+#pragma unroll
+            for (int i = 0; i < 8; ++i) f[i] = rbf(rbf(f[i] * rnorm) * w[i]);
+        } else {
+            float u[8];
+            load8<XDT>(x, base + k, f);
+            load8<XDT>(p.x2, base + k, u);
+#pragma unroll
+            for (int i = 0; i < 8; ++i) f[i] = rbf(fused_act(f[i], p.x_mode) * u[i]);
+        }
+    }
+}
+
 template <int XDT, int NTHREADS, int PHASE>
 __device__ __forceinline__ void quantize_phase(const wf_problem& p, const void* x, const float* x_scale, int MTA, int m0, int m_valid,
-                                               uint8_t* s_act, float* s_inv, int* s_rowsum, unsigned* s_maxbits, XCache<XDT>& cache) {
+                                               uint8_t* s_act, float* s_inv, int* s_rowsum, unsigned* s_maxbits, XCache<XDT>& cache,
+                                               float* s_ss = nullptr, bool write_h = false) {
     constexpr int XC = XCache<XDT>::XC;
     const int tid = threadIdx.x;
+    bool fused = false;  // a fused input mode: the register cache of raw x is not used
+    if constexpr (XDT == WF_BF16) fused = p.x_mode != WF_X_PLAIN;
     if constexpr (PHASE == Q_ISSUE) {
         for (int i = tid; i < m_valid; i += NTHREADS) {
             s_rowsum[i] = 0;
@@ -200,7 +257,7 @@ __device__ __forceinline__ void quantize_phase(const wf_problem& p, const void* 
     } else {
         if constexpr (PHASE == Q_ISSUE) {
             const int tok = sub;
-            if (tok < m_valid) {
+            if (tok < m_valid && !fused) {
                 const int64_t base = static_cast<int64_t>(m0 + tok) * p.ldx;
                 int k = lane_in * 8;
 #pragma unroll
@@ -209,13 +266,52 @@ __device__ __forceinline__ void quantize_phase(const wf_problem& p, const void* 
             }
         }
         if constexpr (PHASE == Q_ABSMAX) {
+            if constexpr (XDT == WF_BF16) {
+                if (p.x_mode == WF_X_NORM) {
+                    // mean of squares of the residual stream per token: thread partial over its k in ascending order,
+                    // shuffle tree, then the warps' partials are summed in warp order by whoever needs the result
+                    for (int tb = 0; tb < m_valid; tb += par) {
+                        const int tok = tb + sub;
+                        float ss = 0.f;
+                        if (tok < m_valid) {
+                            const int64_t base = static_cast<int64_t>(m0 + tok) * p.ldx;
+                            for (int k = lane_in * 8; k < K; k += tpt * 8) {
+                                float f[8];
+                                load8_resid<XDT>(p, x, base + k, f);
+#pragma unroll
+                                for (int i = 0; i < 8; ++i) ss += f[i] * f[i];
+                                if (write_h) {  // the updated residual stream, written by one CTA of the launch
+                                    uint4 o;
+                                    o.x = __bfloat16_as_ushort(__float2bfloat16_rn(f[0])) | (static_cast<uint32_t>(__bfloat16_as_ushort(__float2bfloat16_rn(f[1]))) << 16);
+                                    o.y = __bfloat16_as_ushort(__float2bfloat16_rn(f[2])) | (static_cast<uint32_t>(__bfloat16_as_ushort(__float2bfloat16_rn(f[3]))) << 16);
+                                    o.z = __bfloat16_as_ushort(__float2bfloat16_rn(f[4])) | (static_cast<uint32_t>(__bfloat16_as_ushort(__float2bfloat16_rn(f[5]))) << 16);
+                                    o.w = __bfloat16_as_ushort(__float2bfloat16_rn(f[6])) | (static_cast<uint32_t>(__bfloat16_as_ushort(__float2bfloat16_rn(f[7]))) << 16);
+                                    *reinterpret_cast<uint4*>(static_cast<__nv_bfloat16*>(p.h_out) + base + k) = o;
+                                }
+                            }
+                        }
+#pragma unroll
+                        for (int o = 16; o > 0; o >>= 1) ss += __shfl_xor_sync(0xffffffffu, ss, o);
+                        if (tok < m_valid && (tid & 31) == 0) s_ss[tok * 16 + (lane_in >> 5)] = ss;
+                    }
+                    consumer_sync<NTHREADS>();
+                }
+            }
             for (int tb = 0; tb < m_valid; tb += par) {
                 int tok = tb + sub;
                 float mx = 0.f;
                 if (tok < m_valid) {
                     const int64_t base = static_cast<int64_t>(m0 + tok) * p.ldx;
                     int k = lane_in * 8;
-                    if (tb == 0) {
+                    float rnorm = 1.f;
+                    if constexpr (XDT == WF_BF16) {
+                        if (p.x_mode == WF_X_NORM) {
+                            float tot = 0.f;
+                            for (int w = 0; w < tpt / 32; ++w) tot += s_ss[tok * 16 + w];
+                            rnorm = rsqrtf(tot / static_cast<float>(K) + p.norm_eps);
+                        }
+                    }
+                    if (tb == 0 && !fused) {
 #pragma unroll
                         for (int c = 0; c < XC; ++c, k += tpt * 8) {
                             if (k < K) {
@@ -230,7 +326,7 @@ __device__ __forceinline__ void quantize_phase(const wf_problem& p, const void* 
 #pragma unroll 4
                     for (; k < K; k += tpt * 8) {
                         float f[8];
-                        load8<XDT>(x, base + k, f);
+                        load8_eff<XDT>(p, x, base, k, rnorm, f);
 #pragma unroll
                         for (int i = 0; i < 8; ++i) mx = fmaxf(mx, fabsf(f[i]));
                     }
@@ -266,7 +362,15 @@ __device__ __forceinline__ void quantize_phase(const wf_problem& p, const void* 
                         *reinterpret_cast<uint32_t*>(dst + act_slot_of_k(layout, kl + 4)) = w1;
                     };
                     int k = lane_in * 8;
-                    if (tb == 0) {
+                    float rnorm = 1.f;
+                    if constexpr (XDT == WF_BF16) {
+                        if (p.x_mode == WF_X_NORM) {
+                            float tot = 0.f;
+                            for (int w = 0; w < tpt / 32; ++w) tot += s_ss[tok * 16 + w];
+                            rnorm = rsqrtf(tot / static_cast<float>(K) + p.norm_eps);
+                        }
+                    }
+                    if (tb == 0 && !fused) {
 #pragma unroll
                         for (int c = 0; c < XC; ++c, k += tpt * 8) {
                             if (k < Kp) {
@@ -279,7 +383,7 @@ __device__ __forceinline__ void quantize_phase(const wf_problem& p, const void* 
 #pragma unroll 4
                     for (; k < Kp; k += tpt * 8) {
                         float f[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
-                        if (k < K) load8<XDT>(x, base + k, f);
+                        if (k < K) load8_eff<XDT>(p, x, base, k, rnorm, f);
                         emit(k, f, k < K);
                     }
                 }
@@ -295,13 +399,13 @@ __device__ __forceinline__ void quantize_phase(const wf_problem& p, const void* 
 // All three phases in a row.  The caller has made the fields of `p` visible (a barrier after copying a head).
 template <int XDT, int NTHREADS = DEC_CONSUMERS>
 __device__ __forceinline__ void quantize_tokens(const wf_problem& p, int MTA, int m0, int m_valid, uint8_t* s_act, float* s_inv,
-                                                int* s_rowsum, unsigned* s_maxbits) {
+                                                int* s_rowsum, unsigned* s_maxbits, float* s_ss, bool write_h) {
     XCache<XDT> cache;
     const void* x = p.x;
     const float* xs = p.x_scale;
-    quantize_phase<XDT, NTHREADS, Q_ISSUE>(p, x, xs, MTA, m0, m_valid, s_act, s_inv, s_rowsum, s_maxbits, cache);
-    quantize_phase<XDT, NTHREADS, Q_ABSMAX>(p, x, xs, MTA, m0, m_valid, s_act, s_inv, s_rowsum, s_maxbits, cache);
-    quantize_phase<XDT, NTHREADS, Q_EMIT>(p, x, xs, MTA, m0, m_valid, s_act, s_inv, s_rowsum, s_maxbits, cache);
+    quantize_phase<XDT, NTHREADS, Q_ISSUE>(p, x, xs, MTA, m0, m_valid, s_act, s_inv, s_rowsum, s_maxbits, cache, s_ss, write_h);
+    quantize_phase<XDT, NTHREADS, Q_ABSMAX>(p, x, xs, MTA, m0, m_valid, s_act, s_inv, s_rowsum, s_maxbits, cache, s_ss, write_h);
+    quantize_phase<XDT, NTHREADS, Q_EMIT>(p, x, xs, MTA, m0, m_valid, s_act, s_inv, s_rowsum, s_maxbits, cache, s_ss, write_h);
 }
 
 __device__ __forceinline__ uint4 lds128(uint32_t addr) {
@@ -381,9 +485,9 @@ __device__ __forceinline__ void issue_segment(const wf_problem* p, int row, int 
 // Every read of a descriptor field from global memory is a round trip of half a microsecond, and a barrier
 // makes the compiler repeat it.  The CTA therefore copies the head (all fields before the tensor maps) of the
 // problem it works on into shared memory once, together with the VALUE of the weight scale.
-constexpr int HDR_WORDS = 36;    // 144 bytes: up to and including _kb_seg, _ksegs
-constexpr int HDR_STRIDE = 160;  // bytes per cached head; word HDR_WORDS holds the weight scale
-static_assert(offsetof(wf_problem, _pad) <= HDR_WORDS * 4 && offsetof(wf_problem, _tmap_main) >= HDR_WORDS * 4, "head of wf_problem");
+constexpr int HDR_WORDS = 42;    // 168 bytes: up to and including the fused-input fields
+constexpr int HDR_STRIDE = 192;  // bytes per cached head; word HDR_WORDS holds the weight scale
+static_assert(offsetof(wf_problem, prefetch) == HDR_WORDS * 4 && offsetof(wf_problem, _tmap_main) >= HDR_WORDS * 4, "head of wf_problem");
 
 __device__ __forceinline__ void fill_header(uint8_t* slot, const wf_problem* src, int t) {
     uint32_t* dst = reinterpret_cast<uint32_t*>(slot);
@@ -427,6 +531,22 @@ __device__ __forceinline__ void locate_item(const wf_problem* __restrict__ probs
     const int row_items = probs[pi]._row_items;
     chunk = local / row_items;
     ritem = local % row_items;
+}
+
+// Asks L2 for this CTA's share of every problem's prefetch range (see wf_problem.prefetch); thread `tid` of `nthreads`.
+__device__ __forceinline__ void issue_l2_prefetch(const wf_problem* __restrict__ probs, int P, int tid, int nthreads) {
+    constexpr long long PIECE = 16384;  // bytes per instruction
+    for (int i = 0; i < P; ++i) {
+        const char* base = static_cast<const char*>(probs[i].prefetch);
+        const long long bytes = probs[i].prefetch_bytes;
+        if (!base || bytes <= 0) continue;
+        const long long per = ((bytes + gridDim.x - 1) / gridDim.x + 15) / 16 * 16;
+        const long long lo = per * blockIdx.x, hi = lo + per < bytes ? lo + per : bytes;
+        for (long long o = lo + static_cast<long long>(tid) * PIECE; o < hi; o += static_cast<long long>(nthreads) * PIECE) {
+            const unsigned n = static_cast<unsigned>(hi - o < PIECE ? hi - o : PIECE);
+            asm volatile("cp.async.bulk.prefetch.L2.global [%0], %1;\n" ::"l"(base + o), "r"(n) : "memory");
+        }
+    }
 }
 
 template <int XDT, int NT, bool FOURACC>
@@ -474,7 +594,9 @@ __global__ void __launch_bounds__(DEC_THREADS, 1)
         // The item list is walked incrementally: one search at the start, then only counters.
         int pi, chunk, ritem;
         locate_item(probs, cfg.P, beg, pi, chunk, ritem, s_ib, cfg.ib_cap);
-        // Only one lane works: a whole 16-row tile over all of K is one TMA request (plus one for a K tail).
+        // Only one lane streams: a whole 16-row tile over all of K is one TMA request (plus one for a K tail).  The other
+        // lanes ask L2 for the ranges the problems name (the next launch's weights), beside the stream.
+        if (lane != 0 && cfg.prefetch) issue_l2_prefetch(probs, cfg.P, lane - 1, 31);
         if (lane == 0) {
             const wf_problem* p = &probs[pi];
             int N = p->N, row_items = p->_row_items, chunks = p->_chunks;
@@ -528,7 +650,12 @@ __global__ void __launch_bounds__(DEC_THREADS, 1)
         // item (about 0.7 us) made a 29 MB gate/up launch compute-latency-bound.
         if (beg >= end) return;
         const int m_all = min(cfg.MTA, p.M);
-        quantize_tokens<XDT>(p, cfg.MTA, 0, m_all, s_act, s_inv, s_rowsum, s_maxbits);
+        {
+            int local_first;
+            locate_problem(probs, cfg.P, beg, s_ib, cfg.ib_cap, local_first);
+            quantize_tokens<XDT>(p, cfg.MTA, 0, m_all, s_act, s_inv, s_rowsum, s_maxbits, reinterpret_cast<float*>(smem + cfg.ss_off),
+                                 p.h_out != nullptr && local_first == 0);
+        }
         const uint32_t act0 = smem_u32(s_act);
         const int KB = (p.K + 511) >> 9;
         // Warp w owns stage w and takes the items w, w + W, ... (W = stages <= 16 warps): a barrier is then always waited
@@ -603,7 +730,8 @@ __global__ void __launch_bounds__(DEC_THREADS, 1)
             cur_chunk = chunk;
             m0 = chunk * cfg.MTA;
             m_valid = min(cfg.MTA, p.M - m0);
-            quantize_tokens<XDT>(p, cfg.MTA, m0, m_valid, s_act, s_inv, s_rowsum, s_maxbits);
+            quantize_tokens<XDT>(p, cfg.MTA, m0, m_valid, s_act, s_inv, s_rowsum, s_maxbits, reinterpret_cast<float*>(smem + cfg.ss_off),
+                                 p.h_out != nullptr && ritem == 0);
         }
         const int stage = n % cfg.stages;
         mbar_wait(&full[stage], (n / cfg.stages) & 1, poisoned);
@@ -694,6 +822,7 @@ __global__ void __launch_bounds__(STREAM_THREADS, 2)
     uint8_t* s_act = smem + cfg.act_off;                                    // [2][KBmax * MTA * TOK_STRIDE]
     uint8_t* s_stage = smem + cfg.stage_off;
     uint8_t* s_hdr = smem + cfg.hdr_off;                                    // [2][HDR_STRIDE], one per activation buffer
+    float* const s_ss = reinterpret_cast<float*>(smem + cfg.ss_off);                        // [2][MT * 16]
     int* s_ib = reinterpret_cast<int*>(smem + cfg.ib_off);
     const wf_problem* probs = dev_problems ? dev_problems : &single;
 
@@ -804,6 +933,7 @@ __global__ void __launch_bounds__(STREAM_THREADS, 2)
         if (tid < HDR_WORDS) reinterpret_cast<uint32_t*>(s_hdr)[tid] = hw0;
         if (npre > 1 && tid >= 64 && tid < 64 + HDR_WORDS) reinterpret_cast<uint32_t*>(s_hdr + HDR_STRIDE)[tid - 64] = hw1;
     };
+    if (cfg.prefetch) issue_l2_prefetch(probs, cfg.P, tid, STREAM_THREADS);  // behind this CTA's own first requests
     // The weights never depend on the previous kernel, x normally does: request weights, wait, read x.  Where the
     // caller states that x is ready, the reads of x are started first and only the stores wait for the previous kernel.
     if (!cfg.x_ready) asm volatile("griddepcontrol.wait;\n" ::: "memory");
@@ -826,20 +956,23 @@ __global__ void __launch_bounds__(STREAM_THREADS, 2)
     XCache<XDT> xcache0, xcache1;
     const int mvalid0 = uni > 0 ? mv0 : min(cfg.MTA, h0->M - m00);
     const int mvalid1 = npre > 1 ? min(cfg.MTA, (uni > 0 ? single.M : h1->M) - m01) : 0;
-    quantize_phase<XDT, STREAM_THREADS, Q_ISSUE>(q0, x0, xs0, cfg.MTA, m00, mvalid0, s_act, s_inv, s_rowsum, s_maxbits, xcache0);
+    // fused input modes: the CTA that owns the first row item of a (problem, token pass) writes the residual stream
+    const bool wh0 = !early && uni == 0 && h0->h_out != nullptr && (local0 % h0->_row_items) == 0;
+    const bool wh1 = npre > 1 && !early && uni == 0 && h1->h_out != nullptr && (local1 % h1->_row_items) == 0;
+    quantize_phase<XDT, STREAM_THREADS, Q_ISSUE>(q0, x0, xs0, cfg.MTA, m00, mvalid0, s_act, s_inv, s_rowsum, s_maxbits, xcache0, s_ss, wh0);
     if (npre > 1)
         quantize_phase<XDT, STREAM_THREADS, Q_ISSUE>(q1, x1, xs1, cfg.MTA, m01, mvalid1, s_act + act_bytes, s_inv + MT, s_rowsum + MT,
-                                                     s_maxbits + MT, xcache1);
+                                                     s_maxbits + MT, xcache1, s_ss + MT * 16, wh1);
     if (cfg.x_ready && (early || uni == 0)) issue_first(early);  // behind the reads of x
     if (early) store_heads();  // published by the barrier that opens the next phase
-    quantize_phase<XDT, STREAM_THREADS, Q_ABSMAX>(q0, x0, xs0, cfg.MTA, m00, mvalid0, s_act, s_inv, s_rowsum, s_maxbits, xcache0);
+    quantize_phase<XDT, STREAM_THREADS, Q_ABSMAX>(q0, x0, xs0, cfg.MTA, m00, mvalid0, s_act, s_inv, s_rowsum, s_maxbits, xcache0, s_ss, wh0);
     if (npre > 1)
         quantize_phase<XDT, STREAM_THREADS, Q_ABSMAX>(q1, x1, xs1, cfg.MTA, m01, mvalid1, s_act + act_bytes, s_inv + MT, s_rowsum + MT,
-                                                      s_maxbits + MT, xcache1);
-    quantize_phase<XDT, STREAM_THREADS, Q_EMIT>(q0, x0, xs0, cfg.MTA, m00, mvalid0, s_act, s_inv, s_rowsum, s_maxbits, xcache0);
+                                                      s_maxbits + MT, xcache1, s_ss + MT * 16, wh1);
+    quantize_phase<XDT, STREAM_THREADS, Q_EMIT>(q0, x0, xs0, cfg.MTA, m00, mvalid0, s_act, s_inv, s_rowsum, s_maxbits, xcache0, s_ss, wh0);
     if (npre > 1)
         quantize_phase<XDT, STREAM_THREADS, Q_EMIT>(q1, x1, xs1, cfg.MTA, m01, mvalid1, s_act + act_bytes, s_inv + MT, s_rowsum + MT,
-                                                    s_maxbits + MT, xcache1);
+                                                    s_maxbits + MT, xcache1, s_ss + MT * 16, wh1);
     bool may_store = !cfg.x_ready;  // the previous kernel has been waited for
 
     int it = beg;
@@ -863,7 +996,8 @@ __global__ void __launch_bounds__(STREAM_THREADS, 2)
             seg_end = min(end, it - local + (chunk + 1) * p._row_items);
             const int m0q = chunk * cfg.MTA;
             quantize_tokens<XDT, STREAM_THREADS>(p, cfg.MTA, m0q, min(cfg.MTA, p.M - m0q), s_act + buf * act_bytes, s_inv + buf * MT,
-                                                 s_rowsum + buf * MT, s_maxbits + buf * MT);
+                                                 s_rowsum + buf * MT, s_maxbits + buf * MT, s_ss + buf * MT * 16,
+                                                 p.h_out != nullptr && (local % p._row_items) == 0);
         }
         const int m0 = chunk * cfg.MTA, m_valid = min(cfg.MTA, p.M - m0);
         const int ritem = it - first_item(probs, pi, s_ib, cfg.ib_cap, uni) - chunk * p._row_items;
@@ -984,9 +1118,13 @@ static long long count_items16(const wf_problem* probs, int P, int MT) {
 
 constexpr int IB_CAP = 1024;  // problems whose first item index is cached in shared memory
 
+static size_t ss_offset(int NT, int RI) {  // the norm's partial sums follow the per-token constants and the reduction tiles
+    const int MT = NT * 8;
+    return (384 + static_cast<size_t>(MT) * 24 + 2u * RI * 16 * MT * 4 + 15) / 16 * 16;
+}
 static size_t fixed_bytes(int NT, int RI) {
     const int MT = NT * 8;
-    size_t b = 384 + static_cast<size_t>(MT) * 12 + 2u * RI * 16 * MT * 4;
+    size_t b = ss_offset(NT, RI) + 2u * MT * 16 * 4;
     return (b + 127) / 128 * 128 + IB_CAP * 4 + 384;  // + table of first items + two descriptor heads
 }
 
@@ -1079,7 +1217,9 @@ static bool shares_x(const wf_problem* probs, int P, int MTA) {
     if (probs[0].M > MTA || probs[0].M > 8) return false;  // measured with up to 8 tokens (one token tile)
     for (int i = 1; i < P; ++i)
         if (probs[i].x != probs[0].x || probs[i].x_scale != probs[0].x_scale || probs[i].ldx != probs[0].ldx || probs[i].M != probs[0].M ||
-            probs[i].K != probs[0].K || probs[i].layout != probs[0].layout || probs[i].eps != probs[0].eps)
+            probs[i].K != probs[0].K || probs[i].layout != probs[0].layout || probs[i].eps != probs[0].eps ||
+            probs[i].x_mode != probs[0].x_mode || probs[i].x2 != probs[0].x2 || probs[i].norm_w != probs[0].norm_w ||
+            probs[i].norm_eps != probs[0].norm_eps)
             return false;
     return true;
 }
@@ -1240,6 +1380,10 @@ static int run_group(const char* who, const wf_problem* dev, wf_problem* host, i
     cfg.P = P; cfg.total_items = g.total_items; cfg.RI = g.RI; cfg.KBmax = g.KBmax; cfg.MTA = g.MTA; cfg.stages = g.stages;
     cfg.stage_bytes = g.stage_bytes; cfg.act_off = g.act_off; cfg.stage_off = g.stage_off; cfg.decoupled = g.decoupled; cfg.cpp = g.cpp; cfg.nbuf = g.nbuf;
     cfg.ib_cap = P < IB_CAP ? P : IB_CAP; cfg.ib_off = g.act_off - IB_CAP * 4 - 384; cfg.hdr_off = g.act_off - 384;
+    cfg.ss_off = static_cast<int>(ss_offset(g.NT, g.RI));
+    cfg.prefetch = 0;
+    if (P <= 8)
+        for (int i = 0; i < P; ++i) cfg.prefetch |= (host[i].prefetch != nullptr && host[i].prefetch_bytes > 0) ? 1 : 0;
     cfg.x_ready = (flags & WF_FLAG_X_READY) ? 1 : 0;
     cfg.wide = (!g.decoupled && g.RI == 1 && g.total_items >= 3LL * g.grid && shares_x(host, P, g.MTA)) ? 1 : 0;
     cfg.items_q = g.total_items / g.grid; cfg.items_r = g.total_items % g.grid;
@@ -1255,6 +1399,7 @@ static int run_group(const char* who, const wf_problem* dev, wf_problem* host, i
         const char* b0 = static_cast<const char*>(host[0].x);
         const long long dx = P > 1 ? static_cast<const char*>(host[1].x) - b0 : 0;
         bool ok = host[0].x_scale == nullptr && host[0].ldx == host[P > 1 ? 1 : 0].ldx;
+        for (int i = 0; i < P && ok; ++i) ok = host[i].x_mode == WF_X_PLAIN;  // fused inputs are found through the heads
         for (int i = 1; i < P && ok; ++i)
             ok = host[i].x_scale == nullptr && host[i].ldx == host[0].ldx && host[i].eps == host[0].eps &&
                  static_cast<const char*>(host[i].x) - b0 == dx * i;
@@ -1297,8 +1442,22 @@ int wf_check_linear_args(const char* who, const void* x, int x_dtype, int64_t ld
 }
 
 static int wf::check_problem(const char* who, const wf_problem& q) {
-    return wf_check_linear_args(who, q.x, q.x_dtype, q.ldx, q.x_scale, q.codes, q.layout, q.bias, q.bias_dtype, q.y, q.y_dtype,
-                                q.ldy, q.M, q.N, q.K);
+    if (int rc = wf_check_linear_args(who, q.x, q.x_dtype, q.ldx, q.x_scale, q.codes, q.layout, q.bias, q.bias_dtype, q.y, q.y_dtype,
+                                      q.ldy, q.M, q.N, q.K))
+        return rc;
+    WF_REQUIRE(q.x_mode >= WF_X_PLAIN && q.x_mode <= WF_X_NORM, "%s: unknown x_mode %d", who, q.x_mode);
+    WF_REQUIRE(q.prefetch_bytes >= 0 && q.prefetch_bytes % 16 == 0 && (reinterpret_cast<uintptr_t>(q.prefetch) & 15) == 0,
+               "%s: the prefetch range must be 16-byte aligned and a multiple of 16 bytes", who);
+    if (q.x_mode != WF_X_PLAIN) {
+        WF_REQUIRE(q.x_dtype == WF_BF16, "%s: fused input modes take bf16 tensors", who);
+        WF_REQUIRE(q.K % 8 == 0, "%s: fused input modes need K %% 8 == 0", who);
+        auto al16 = [](const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15) == 0; };
+        if (q.x_mode == WF_X_NORM)
+            WF_REQUIRE(q.norm_w && al16(q.norm_w) && al16(q.x2) && al16(q.h_out), "%s: the RMSNorm input mode needs a 16-byte aligned norm_w (x2, h_out optional, aligned)", who);
+        else
+            WF_REQUIRE(q.x2 && al16(q.x2), "%s: the activation input modes need x2 (the `up` tensor), 16-byte aligned", who);
+    }
+    return WF_OK;
 }
 
 extern "C" int wf_bitlinear_decode(const void* x, int x_dtype, int64_t ldx, const float* x_scale, const uint8_t* codes,

@@ -5,11 +5,12 @@ RMSNorm -> q/k/v BitLinear -> RoPE -> GQA attention -> o BitLinear -> residual -
 act(gate) * up -> down BitLinear -> residual; bf16 embedding and lm_head.  Unlike the reference it keeps a bf16
 KV cache, launches q/k/v and gate/up as one grouped kernel each, and replays the whole decode step as a CUDA
 graph.  With `subln=True` and weights loaded under the reference's parameter names it computes the reference
-model (BitNetLlama) itself.  Everything that is not a BitLinear projection (norms, RoPE, attention, activation) uses stock torch
-operators: those are callers of the hot path, not part of it.
+model (BitNetLlama) itself.  In the decode step the norms, RoPE + cache write, attention over the cache and the gate
+activation are kernels of this library as well; the prompt pass uses stock torch operators around the projections.
 
 Tensor parallel: heads and the MLP width are split over the ranks of a process group; q/k/v/gate/up are
-column-parallel, o/down row-parallel with one all-reduce each (the reference's plan).
+column-parallel, o/down row-parallel with one all-reduce each (the reference's plan); the output head is sharded by
+vocabulary rows and the greedy token comes from one all-gather of per-rank (maximum, index) pairs.
 """
 from __future__ import annotations
 
@@ -74,11 +75,20 @@ class TernaryDecoder:
     """Random-initialised ternary decoder (weights N(0, 0.02), ternarized on the GPU)."""
 
     def __init__(self, cfg: DecoderConfig, batch: int, max_ctx: int, device, group=None, seed: int = 0,
-                 dtype: torch.dtype = torch.bfloat16, weights: Optional[dict] = None, pack_mode: torch.dtype = torch.float32):
+                 dtype: torch.dtype = torch.bfloat16, weights: Optional[dict] = None, pack_mode: torch.dtype = torch.float32,
+                 fuse: Optional[bool] = None, prefetch: bool = False):
         """`weights`: optional fp32 state dict under the reference model's parameter names (BitNetLlama,
         wrinklefree/models/llama.py:13-59); without it the weights are drawn from N(0, 0.02) with `seed`.
         `pack_mode`: arithmetic of the ternarization (torch.float32, or the input dtype for the cast-first rule of
-        BitLinear.forward)."""
+        BitLinear.forward).  `fuse`: True runs the decode step of small batches with the fused input modes of the
+        grouped kernel (six launches per layer instead of ten); measured on B200 the separate norm / activation kernels,
+        which overlap the projections' weight streaming through programmatic launches, are faster, so it is off by
+        default."""
+        self._fuse_opt = fuse
+        # decode step: every projection group asks L2 for the following launches' weights.  Measured on B200 at batch 1
+        # (8B shape) this made the step slower (2.05 -> 2.25 ms: the prefetch competes with the running launch's own
+        # stream), so it is off by default.
+        self.prefetch = prefetch
         self.cfg, self.B, self.T, self.dev, self.dtype, self.group = cfg, batch, max_ctx, device, dtype, group
         self._oneshot = None  # peer-memory all-reduce for the row-parallel projections (set up at the first step)
         self.tp = dist.get_world_size(group) if (group is not None or dist.is_initialized()) else 1
@@ -151,6 +161,14 @@ class TernaryDecoder:
             self.embed = (torch.randn(cfg.vocab, h, generator=gen, device=device, dtype=torch.float32) * 0.02).to(dtype)
             self.lm_head = (torch.randn(cfg.vocab, h, generator=gen, device=device, dtype=torch.float32) * 0.02).to(dtype)
         self.norm_f = vec("transformer.norm.weight", h)
+        # tensor parallel: the output head is sharded by vocabulary rows; every rank scores its rows, and the greedy token
+        # is the best of the per-rank (maximum, index) pairs - one small all-gather per step instead of streaming the
+        # whole head on every rank
+        self.v_lo, self.v_hi = (0, cfg.vocab)
+        if self.tp > 1:
+            self.v_lo, self.v_hi = tpmod.shard_bounds(cfg.vocab, self.tp, 1)[self.rank]
+            self.lm_head = self.lm_head[self.v_lo:self.v_hi].contiguous()
+            self._cand = torch.empty(self.tp, 2, batch, dtype=torch.float32, device=device)
         inv = 1.0 / (cfg.rope_theta ** (torch.arange(0, d, 2, device=device, dtype=torch.float32) / d))
         ang = torch.arange(max_ctx, device=device, dtype=torch.float32)[:, None] * inv[None, :]
         self.cos, self.sin = ang.cos(), ang.sin()
@@ -158,31 +176,59 @@ class TernaryDecoder:
         self.tok = torch.zeros(batch, dtype=torch.long, device=device)
         self.pos = torch.zeros((), dtype=torch.long, device=device)
         self._pos_host = 0  # host mirror of pos for the bound check of decode()
+        self.masked, self.attention = True, "kernel"
         self._step_bufs()
         self.graph: Optional[torch.cuda.CUDAGraph] = None
         self.next_tok = torch.zeros(batch, dtype=torch.long, device=device)
 
     # ------------------------------------------------------------------ decode step buffers and groups
     def _step_bufs(self):
+        """Static buffers and launch groups of the decode step.  Small batches (the projections on the fused
+        quantize-and-contract kernel) use the fused input modes: the residual add + RMSNorm runs inside the q/k/v and
+        gate/up launches and the gate activation inside the down launch, six launches per layer.  The residual stream
+        alternates between two buffers (a fused launch reads one and writes the other)."""
         cfg, B, d, dev, dt = self.cfg, self.B, self.cfg.head_dim, self.dev, self.dtype
-        for L in self.layers:
+        self.big = B >= 16 and cfg.hidden >= 2048  # projections on the tensor-core contraction for few tokens
+        self.fused = dt == torch.bfloat16 and not self.big and not cfg.subln and cfg.hidden % 8 == 0 and self._fuse_opt is True
+        self.h = torch.empty(B, cfg.hidden, dtype=dt, device=dev)
+        self.h2 = torch.empty(B, cfg.hidden, dtype=dt, device=dev)
+        self.xf = torch.empty(B, cfg.hidden, dtype=dt, device=dev)
+        mode = "silu" if cfg.act == "silu" else "relu2"
+        prev_down = None
+        for li, L in enumerate(self.layers):
             L["xn"] = torch.empty(B, cfg.hidden, dtype=dt, device=dev)
             L["qkv"] = [torch.empty(B, self.nq * d, dtype=dt, device=dev), torch.empty(B, self.nkv * d, dtype=dt, device=dev),
                         torch.empty(B, self.nkv * d, dtype=dt, device=dev)]
-            L["g_qkv"] = ops.DecodeGroup([dict(x=L["xn"], codes=L[n][0], w_scale=L[n][1], out=o)
-                                          for n, o in zip(("q", "k", "v"), L["qkv"])])
             L["hn"] = torch.empty(B, cfg.hidden, dtype=dt, device=dev)
             L["gu"] = [torch.empty(B, self.i_hi - self.i_lo, dtype=dt, device=dev) for _ in range(2)]
-            L["g_gu"] = ops.DecodeGroup([dict(x=L["hn"], codes=L[n][0], w_scale=L[n][1], out=o)
-                                         for n, o in zip(("gate", "up"), L["gu"])])
             L["act"] = torch.empty(B, self.i_hi - self.i_lo, dtype=dt, device=dev)
+            L["attn"] = torch.empty(B, self.nq * d, dtype=dt, device=dev)
             if cfg.subln:
                 L["an"] = torch.empty(B, self.nq * d, dtype=dt, device=dev)
                 L["actn"] = torch.empty(B, self.i_hi - self.i_lo, dtype=dt, device=dev)
             L["ob"] = torch.empty(B, cfg.hidden, dtype=dt, device=dev)
             L["db"] = torch.empty(B, cfg.hidden, dtype=dt, device=dev)
-        self.h = torch.empty(B, cfg.hidden, dtype=dt, device=dev)
-        self.xf = torch.empty(B, cfg.hidden, dtype=dt, device=dev)
+            if self.fused:
+                # q/k/v: rmsnorm(h + previous down output) -> h2;  gate/up: rmsnorm(h2 + o output) -> h
+                first = dict(x_mode="norm", x2=prev_down, norm_w=L["n1"], norm_eps=cfg.eps)
+                L["g_qkv"] = ops.DecodeGroup([dict(x=self.h, codes=L[n][0], w_scale=L[n][1], out=o, h_out=self.h2 if n == "q" else None, **first)
+                                              for n, o in zip(("q", "k", "v"), L["qkv"])])
+                L["g_o"] = ops.DecodeGroup([dict(x=L["attn"], codes=L["o"][0], w_scale=L["o"][1], out=L["ob"])])
+                second = dict(x_mode="norm", x2=L["ob"], norm_w=L["n2"], norm_eps=cfg.eps)
+                L["g_gu"] = ops.DecodeGroup([dict(x=self.h2, codes=L[n][0], w_scale=L[n][1], out=o, h_out=self.h if n == "gate" else None, **second)
+                                             for n, o in zip(("gate", "up"), L["gu"])])
+                L["g_down"] = ops.DecodeGroup([dict(x=L["gu"][0], x2=L["gu"][1], x_mode=mode, codes=L["down"][0], w_scale=L["down"][1], out=L["db"])])
+                prev_down = L["db"]
+            else:
+                # every group asks L2 for the weights of the launches that follow it, so that their HBM transfer overlaps
+                # this chain of short launches: q/k/v -> o, gate, up;  gate/up -> down, the next layer's q
+                nxt = self.layers[li + 1] if li + 1 < len(self.layers) else None
+                pf1 = {"q": L["o"][0], "k": L["gate"][0], "v": L["up"][0]} if self.prefetch else {}
+                pf2 = {"gate": L["down"][0], "up": nxt["q"][0] if nxt else None} if self.prefetch else {}
+                L["g_qkv"] = ops.DecodeGroup([dict(x=L["xn"], codes=L[n][0], w_scale=L[n][1], out=o, prefetch=pf1.get(n))
+                                              for n, o in zip(("q", "k", "v"), L["qkv"])])
+                L["g_gu"] = ops.DecodeGroup([dict(x=L["hn"], codes=L[n][0], w_scale=L[n][1], out=o, prefetch=pf2.get(n))
+                                             for n, o in zip(("gate", "up"), L["gu"])])
 
     def _act(self, g, u):
         return (F.silu(g) if self.cfg.act == "silu" else F.relu(g).pow(2)) * u
@@ -202,16 +248,23 @@ class TernaryDecoder:
         before it reads an activation."""
         cfg, B, d = self.cfg, self.B, self.cfg.head_dim
         self.h.copy_(self.embed[self.tok])  # residual stream [B, hidden]
-        valid = (torch.arange(self.T, device=self.dev) <= self.pos).view(1, 1, 1, self.T) if self.masked else None
+        if self.fused:
+            return self._decode_step_fused()
+        valid = None
+        if self.masked and self.attention == "library":
+            valid = (torch.arange(self.T, device=self.dev) <= self.pos).view(1, 1, 1, self.T)
         delta = None
         for L in self.layers:
             ops.add_rmsnorm_(self.h, delta, L["n1"], L["xn"], cfg.eps, pdl=True)
             q, k, v = L["g_qkv"].run(pdl=True)
             ops.rope_kv_(q, k, v, self.cos, self.sin, self.pos, L["kc"], L["vc"], pdl=True)
-            a = F.scaled_dot_product_attention(q.view(B, self.nq, 1, d), L["kc"], L["vc"], attn_mask=valid, enable_gqa=True)
+            if self.attention == "library":  # the framework's fused kernel, kept as a comparison for the benchmark
+                a = F.scaled_dot_product_attention(q.view(B, self.nq, 1, d), L["kc"], L["vc"], attn_mask=valid, enable_gqa=True)
+            else:
+                a = ops.attn_decode(q, L["kc"], L["vc"], self.pos if self.masked else None, L["attn"], pdl=True)
             # from 16 sequences on the single projections of a wide model run on the tensor-core contraction for few
             # tokens (measured: 14 vs 20 us for 4096 x 4096 at 32 tokens; narrow layers stay faster on the decode kernel)
-            big = B >= 16 and cfg.hidden >= 2048
+            big = self.big
             path = "prefill" if big else "decode"
             a = a.reshape(B, self.nq * d)
             if cfg.subln:
@@ -229,9 +282,42 @@ class TernaryDecoder:
                 act = ops.add_rmsnorm_(act, None, L["sf"], L["actn"], cfg.subln_eps, pdl=True)
             delta = self._allreduce(ops.bitlinear(act, L["down"][0], L["down"][1], out=L["db"], path=path, pdl=True))
         ops.add_rmsnorm_(self.h, delta, self.norm_f, self.xf, cfg.eps, pdl=True)
-        logits = self.xf @ self.lm_head.t()
+        self._greedy(self.xf @ self.lm_head.t())
+        self.pos.add_(1)
+
+    def _greedy(self, logits):
+        """next_tok = argmax over the vocabulary; `logits` are this rank's rows of the head."""
         self.logits = logits
-        self.next_tok.copy_(logits.argmax(-1))
+        if self.tp == 1:
+            self.next_tok.copy_(logits.argmax(-1))
+            return
+        mx, idx = logits.float().max(-1)
+        mine = torch.stack([mx, (idx + self.v_lo).float()])  # vocabulary indices are exact in fp32 (< 2^24)
+        dist.all_gather_into_tensor(self._cand.view(-1), mine.view(-1), group=self.group)
+        best = self._cand[:, 0].argmax(0)  # [B]: the rank that holds the maximum (the lowest rank on ties)
+        self.next_tok.copy_(self._cand[:, 1].gather(0, best.unsqueeze(0)).squeeze(0).long())
+
+    def _decode_step_fused(self):
+        """Six launches per layer: q/k/v (residual add + RMSNorm + quantization fused in), RoPE + cache write, attention,
+        o, gate/up (residual add + RMSNorm fused in), down (gate activation fused in); with tensor parallelism the two
+        row-parallel outputs are summed over the ranks in between."""
+        cfg = self.cfg
+        for L in self.layers:
+            q, k, v = L["g_qkv"].run(pdl=True)
+            ops.rope_kv_(q, k, v, self.cos, self.sin, self.pos, L["kc"], L["vc"], pdl=True)
+            if self.attention == "library":  # the framework's fused kernel, kept as a comparison for the benchmark
+                valid = (torch.arange(self.T, device=self.dev) <= self.pos).view(1, 1, 1, self.T) if self.masked else None
+                L["attn"].copy_(F.scaled_dot_product_attention(q.view(self.B, self.nq, 1, cfg.head_dim), L["kc"], L["vc"], attn_mask=valid,
+                                                               enable_gqa=True).reshape(self.B, -1))
+            else:
+                ops.attn_decode(q, L["kc"], L["vc"], self.pos if self.masked else None, L["attn"], pdl=True)
+            L["g_o"].run(pdl=True)
+            self._allreduce(L["ob"])
+            L["g_gu"].run(pdl=True)
+            L["g_down"].run(pdl=True)
+            self._allreduce(L["db"])
+        ops.add_rmsnorm_(self.h, self.layers[-1]["db"], self.norm_f, self.xf, cfg.eps, pdl=True)
+        self._greedy(self.xf @ self.lm_head.t())
         self.pos.add_(1)
 
     # ------------------------------------------------------------------ public
@@ -266,14 +352,21 @@ class TernaryDecoder:
             dn = self._allreduce(ops.bitlinear(act, *L["down"]))
             x = x + dn.view(B, S, cfg.hidden)
         logits = _rms_norm(x if all_logits else x[:, -1], self.norm_f, cfg.eps) @ self.lm_head.t()
+        if self.tp > 1:  # the prompt pass returns the full rows
+            parts = [torch.empty(*logits.shape[:-1], hi - lo, dtype=logits.dtype, device=logits.device)
+                     for lo, hi in tpmod.shard_bounds(cfg.vocab, self.tp, 1)]
+            dist.all_gather(parts, logits.contiguous(), group=self.group)
+            logits = torch.cat(parts, -1)
         self.tok.copy_(logits[:, -1].argmax(-1) if all_logits else logits.argmax(-1))
         self.pos.fill_(S)
         self._pos_host = S
         return logits
 
-    def capture(self, masked: bool = True):
-        """Warm up and capture the decode step as a CUDA graph."""
+    def capture(self, masked: bool = True, attention: str = "kernel"):
+        """Warm up and capture the decode step as a CUDA graph.  `attention`: "kernel" (this library's decode
+        attention) or "library" (the framework's fused attention, for comparison)."""
         self.masked = masked
+        self.attention = attention
         pos0, tok0 = self.pos.clone(), self.tok.clone()
         s = torch.cuda.Stream()
         s.wait_stream(torch.cuda.current_stream())

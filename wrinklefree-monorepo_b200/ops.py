@@ -271,7 +271,17 @@ class DecodeGroup:
 
     problems: iterable of dicts with keys x, codes, w_scale and optionally bias, out, out_dtype,
     layout, x_scale, eps, want_acc.  All x must share a dtype.
+
+    `prefetch`: a tensor whose bytes the launch asks L2 to fetch while it runs (the next launch's packed weights).
+
+    Fused inputs (bf16): `x_mode` "silu" / "relu2" with `x2`: the projection quantizes act(x) * x2 (x = gate,
+    x2 = up: the activation in front of a down projection); `x_mode` "norm" with `norm_w`, optional `x2`, `h_out`,
+    `norm_eps`: it quantizes rmsnorm(x + x2) * norm_w and writes x + x2 to h_out (residual add + RMSNorm in front
+    of q/k/v or gate/up).  The arithmetic is that of `act_mul` / `add_rmsnorm_`, so a fused launch replaces the
+    separate kernel.
     """
+
+    _XMODE = {None: L.X_PLAIN, "plain": L.X_PLAIN, "silu": L.X_SILU, "relu2": L.X_RELU2, "norm": L.X_NORM}
 
     def __init__(self, problems):
         import ctypes as C
@@ -286,7 +296,7 @@ class DecodeGroup:
         # With many tokens per problem x is quantized once per distinct input by a kernel of its own in run(), and
         # the problems read the int8 copy (otherwise every CTA quantizes the tokens of its problem again).
         prequant = all(pr["x"].dtype != torch.int8 and pr["x"].reshape(-1, pr["x"].shape[-1]).shape[0] >= PREQUANT_MIN_TOKENS
-                       for pr in problems)
+                       and not pr.get("x_mode") for pr in problems)
         self._quant = {}  # data_ptr of x -> (x2, q, scale, eps)
         for i, pr in enumerate(problems):
             x, codes, w_scale = pr["x"], pr["codes"], pr["w_scale"]
@@ -319,6 +329,21 @@ class DecodeGroup:
             q.x_dtype, q.y_dtype = _DT[x2.dtype], _DT[y.dtype]
             q.bias_dtype = _DT[bias.dtype] if bias is not None else 0
             q.layout, q.eps = pr.get("layout", L.LAYOUT_WF16), pr.get("eps", 1e-5)
+            mode = self._XMODE[pr.get("x_mode")]
+            if mode != L.X_PLAIN:
+                second, norm_w, h_out = pr.get("x2"), pr.get("norm_w"), pr.get("h_out")
+                _need_cuda(second, norm_w, h_out)
+                for t_ in (second, h_out):
+                    if t_ is not None and (t_.dtype != x.dtype or t_.reshape(-1, k).stride(0) != x2.stride(0)):
+                        raise ValueError("x2 / h_out must have the dtype and row stride of x")
+                q.x_mode, q.norm_eps = mode, pr.get("norm_eps", 1e-6)
+                q.x2, q.norm_w, q.h_out = _ptr(second), _ptr(norm_w), _ptr(h_out)
+                self._keep += [second, norm_w, h_out]
+            pf = pr.get("prefetch")  # a tensor (typically the next launch's packed weights) to pull into L2 meanwhile
+            if pf is not None:
+                _need_cuda(pf)
+                q.prefetch, q.prefetch_bytes = pf.data_ptr(), pf.numel() * pf.element_size() // 16 * 16
+                self._keep.append(pf)
             self._keep += [x2, codes, w_scale, bias, x_scale, y, acc]
             self.outputs.append(y.reshape(*x.shape[:-1], n))
             self.accs.append(acc)
@@ -369,6 +394,32 @@ def rope_kv_(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, cos: torch.Tenso
         L.check(L.lib().wf_rope_kv_bf16(q.data_ptr(), k.data_ptr(), v.data_ptr(), cos.data_ptr(), sin.data_ptr(), pos.data_ptr(),
                                         kcache.data_ptr(), vcache.data_ptr(), b, nq, nkv, d, t, L.FLAG_PDL if pdl else 0, _stream()),
                 "wf_rope_kv_bf16")
+
+
+_attn_ws = {}
+
+
+def attn_decode(q: torch.Tensor, kcache: torch.Tensor, vcache: torch.Tensor, pos: Optional[torch.Tensor], out: torch.Tensor,
+                scale: Optional[float] = None, pdl: bool = False):
+    """Decode-step attention over the bf16 KV cache: q [B, nq*D] (rotated), caches [B, nkv, T, D], `pos` a device
+    scalar (positions 0..pos are attended to; None: all T), out [B, nq*D].  Grouped-query heads share one pass over
+    their keys and values."""
+    _need_cuda(q, kcache, vcache, pos, out)
+    b, nkv, t, d = kcache.shape
+    nq = q.numel() // (b * d)
+    if q.dtype != torch.bfloat16 or kcache.dtype != torch.bfloat16 or not (kcache.is_contiguous() and vcache.is_contiguous()):
+        raise ValueError("attn_decode needs contiguous bf16 tensors")
+    lib = L.lib()
+    nbytes = lib.wf_attn_decode_workspace_bytes(b, nq, nkv, d, t)
+    ws = _attn_ws.get(q.device)
+    if ws is None or ws.numel() < nbytes:
+        ws = torch.zeros(max(nbytes, 1 << 16), dtype=torch.uint8, device=q.device)
+        _attn_ws[q.device] = ws
+    with torch.cuda.device(q.device):
+        L.check(lib.wf_attn_decode_bf16(q.data_ptr(), kcache.data_ptr(), vcache.data_ptr(), _ptr(pos), out.data_ptr(), b, nq, nkv, d, t,
+                                        float(scale if scale is not None else d ** -0.5), ws.data_ptr(), ws.numel(),
+                                        L.FLAG_PDL if pdl else 0, _stream()), "wf_attn_decode_bf16")
+    return out
 
 
 def act_mul(gate: torch.Tensor, up: torch.Tensor, out: torch.Tensor, mode: str = "silu", pdl: bool = False):
