@@ -42,7 +42,7 @@ REPEATS = 5      # the --steps region is timed this many times; the median is re
 # DRAM bytes (ncu dram__bytes_read.sum + dram__bytes_write.sum, one capture per stack, one launch) over the algorithmic
 # bytes of the same launch, for the streaming kernel's stacks: (shape index, M) -> ratio.  Stacks without a capture of
 # their own use the mean of the measured ones.
-NCU_TRAFFIC_RATIO = {(0, 1): 203.52 / 197.84}
+NCU_TRAFFIC_RATIO = {(0, 1): 1.029, (0, 4): 1.014, (1, 1): 1.013, (1, 4): 1.010, (2, 1): 1.021, (2, 4): 1.018}
 
 
 def algorithmic_bytes(m: int, n: int, k: int) -> int:

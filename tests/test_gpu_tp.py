@@ -2,8 +2,11 @@
 process; the CUDA kernels run on its own GPU.  Column-parallel shards reproduce the single-GPU result exactly;
 row-parallel partial sums are checked per shard bit for bit against the oracle, the reduced output within the
 normalised tolerance."""
+import datetime
 import os
 import sys
+import time
+import traceback
 
 import numpy as np
 import pytest
@@ -20,13 +23,16 @@ def _worker(rank, world, port, results):
     os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port), NCCL_NVLS_ENABLE="0")
     torch.cuda.set_device(rank)
     dev = torch.device("cuda", rank)
-    dist.init_process_group("nccl", rank=rank, world_size=world, device_id=dev)
+    dist.init_process_group("nccl", rank=rank, world_size=world, device_id=dev, timeout=datetime.timedelta(seconds=120))
     try:
         from __graft_entry__ import load_package
         from oracle import bitlinear_oracle as O
 
         wf = load_package()
         from wrinklefree_monorepo_b200 import tp
+
+        def at(stage):  # where a rank that never finishes had got to
+            results[f"at{rank}"] = stage
 
         g = torch.Generator().manual_seed(0)
         n, k, m = 512, 1344, 6  # K = 21 units of 64: uneven split
@@ -35,6 +41,7 @@ def _worker(rank, world, port, results):
         codes, scale = wf.pack_ternary(w.to(dev))
         full = wf.bitlinear(x.to(dev), codes, scale, out_dtype=torch.float32)
 
+        at("column/row parallel")
         col = tp.ColumnParallelBitLinear(codes, scale, k, n, gather_output=True)
         y = col(x.to(dev), out_dtype=torch.float32)
         assert torch.equal(y, full)
@@ -51,6 +58,7 @@ def _worker(rank, world, port, results):
         assert err < 2e-2, err
         # the peer-memory all-reduce: equal to the fp32 sum in rank order on every rank, in place, repeatedly (the two
         # exchange slots alternate), also inside a CUDA graph; a row-parallel layer built on it
+        at("one-shot all-reduce")
         ar = tp.OneShotAllReduce(max_bytes=1 << 20)
         for rep, (numel, dt) in enumerate([(4096, torch.bfloat16), (8, torch.bfloat16), (262144, torch.bfloat16), (4096, torch.float32),
                                            (520, torch.float16), (4096, torch.bfloat16)]):
@@ -84,18 +92,23 @@ def _worker(rank, world, port, results):
         # ---- the decoder: heads, MLP width and the output head sharded over the ranks, against one rank on its own
         from wrinklefree_monorepo_b200.decoder import DecoderConfig, TernaryDecoder
 
+        at("decoder build")
         solo = [dist.new_group([r]) for r in range(world)][rank]  # collective: every rank creates every group
         cfg = DecoderConfig(layers=2, hidden=256, n_q=4, n_kv=2, head_dim=64, intermediate=512, vocab=1000)
         ids = torch.randint(0, cfg.vocab, (3, 9), generator=torch.Generator().manual_seed(5)).to(dev)
         m_tp = TernaryDecoder(cfg, 3, 16, dev, seed=3)
         m_1 = TernaryDecoder(cfg, 3, 16, dev, seed=3, group=solo)
         assert m_tp.tp == world and m_1.tp == 1 and m_tp.lm_head.shape[0] == cfg.vocab // world
+        at("decoder prefill")
         l_tp, l_1 = m_tp.prefill(ids).float(), m_1.prefill(ids).float()
         assert l_tp.shape == l_1.shape
         assert float((l_tp - l_1).abs().max() / l_1.abs().max()) < 3e-2  # row-parallel layers quantize their K slices locally
+        at("decoder capture")
         m_tp.capture(masked=True)
         m_1.capture(masked=True)
+        at("decoder decode")
         toks_tp, toks_1 = m_tp.decode(4), m_1.decode(4)
+        at("decoder checks")
         both = [torch.empty_like(toks_tp) for _ in range(world)]
         dist.all_gather(both, toks_tp)
         assert all(torch.equal(both[0], t_) for t_ in both)  # every rank picked the same tokens
@@ -106,8 +119,16 @@ def _worker(rank, world, port, results):
         assert torch.equal(torch.cat(full, -1).float().argmax(-1), m_tp.next_tok)
         wf.device_status()
         results[rank] = "ok"
-    finally:
-        dist.destroy_process_group()
+    except BaseException:
+        # the peer may be inside a collective: report and leave without the orderly teardown; the parent ends the other rank
+        results[rank] = traceback.format_exc()
+        os._exit(1)
+    # captured steps hold the communicator of their collectives: release them before the group goes away
+    at("teardown")
+    m_tp.release()
+    m_1.release()
+    dist.destroy_process_group()
+    at("done")
 
 
 def test_tp2_nccl():
@@ -115,5 +136,15 @@ def test_tp2_nccl():
         pytest.skip("needs two GPUs")
     mgr = mp.Manager()
     results = mgr.dict()
-    mp.spawn(_worker, args=(2, 29650 + os.getpid() % 300, results), nprocs=2, join=True)
-    assert dict(results) == {0: "ok", 1: "ok"}
+    ctx = mp.spawn(_worker, args=(2, 29650 + os.getpid() % 300, results), nprocs=2, join=False)
+    deadline = time.time() + 300
+    try:
+        while not ctx.join(timeout=5):
+            if time.time() > deadline:
+                for p in ctx.processes:  # exactly the two children started above
+                    if p.is_alive():
+                        p.kill()
+                pytest.fail(f"ranks still running after 300 s; reported so far: {dict(results)}")
+    except Exception as e:  # a rank left with an error: show what it recorded
+        pytest.fail(f"{e}\n{dict(results)}")
+    assert {r: results.get(r) for r in (0, 1)} == {0: "ok", 1: "ok"}, dict(results)

@@ -9,8 +9,9 @@
 // per SM) walk the tiles; K advances in stages of 512:
 //   * warp 0 (one lane): TMA of the PACKED weight rows (128 rows x 128 bytes, 128-byte swizzle), ring of 6 stages;
 //   * warp 14 (one lane): TMA of the int8 token tile (4 swizzle atoms of NTOK x 128 bytes, the MMA's B operand);
-//   * warps 2-5 / 6-9: two expansion groups that alternate stages; thread = weight row: 8 x ld.shared.v4, mask + shift
-//     to one int8 per byte, 4 x tcgen05.st of 32 columns into a ring of tensor-memory stages;
+//   * warps 2-5 / 6-9: two expansion groups, each takes half of every stage; thread = weight row: 4 x ld.shared.v4, mask +
+//     shift to one int8 per byte (into registers, before the tensor-memory stage is free), 2 x tcgen05.st of 32 columns
+//     into a ring of tensor-memory stages;
 //   * warp 1 (one lane): 16 x tcgen05.mma.cta_group::1.kind::i8 (M = 128, N = NTOK, K = 32), A operand FROM TENSOR MEMORY,
 //     one commit per stage; two accumulators, so the epilogue of a tile runs under the next tile's MMAs;
 //   * warps 10-13 (and 15-18): epilogue, thread = weight row: tcgen05.ld, integer correction, fp32 rescale, store.
@@ -184,11 +185,11 @@ __global__ void __launch_bounds__(SM_THREADS, 1)
     if (tid == 0) {
         for (int s = 0; s < SM_PS; ++s) {
             mbar_init(&p_full[s], 1);
-            mbar_init(&p_empty[s], 4);
+            mbar_init(&p_empty[s], 8);
         }
         for (int s = 0; s < SM_XS; ++s) {
             mbar_init(&x_full[s], 1);
-            mbar_init(&a_full[s], 4);
+            mbar_init(&a_full[s], 8);
             mbar_init(&st_free[s], 1);
         }
         for (int a = 0; a < 2; ++a) {
@@ -277,7 +278,10 @@ __global__ void __launch_bounds__(SM_THREADS, 1)
             }
         }
     } else if (warp < 10) {
-        // ---- expansion: group (warp - 2) / 4 takes every other stage; thread = weight row of the tile
+        // ---- expansion: both groups work on EVERY stage, group (warp - 2) / 4 on its half of the stage's four atoms;
+        // thread = weight row of the tile.  A group's two atoms are expanded into registers BEFORE the tensor-memory stage
+        // is known to be free, so that only two tcgen05.st and their wait lie between "the MMAs of the stage's previous
+        // use have completed" and "the next may start".
         const int grp = (warp - 2) >> 2;
         const int quarter = warp & 3;           // the TMEM lanes this warp may access
         const int r = quarter * 32 + lane;      // weight row inside the tile
@@ -285,42 +289,43 @@ __global__ void __launch_bounds__(SM_THREADS, 1)
         int sit = 0;
         for (int t = blockIdx.x; t < total_tiles; t += gridDim.x) {
             for (int g = 0; g < stages; ++g, ++sit) {
-                if ((sit & 1) != grp) continue;
                 const int ps = sit % SM_PS, s = sit % SM_XS;
                 mbar_wait(&p_full[ps], (sit / SM_PS) & 1, poisoned);
-                if (sit >= SM_XS) mbar_wait(&st_free[s], ((sit / SM_XS) - 1) & 1, poisoned);
-                tc_fence_after();
                 const uint32_t row = smem_u32(p_ring + ps * SM_P_BYTES) + r * 128;
-                const uint32_t dst = tmem_a + s * SM_A_COLS + (static_cast<uint32_t>(quarter * 32) << 16);
+                uint32_t v[2][32];  // column c of an atom = its weights 4c .. 4c + 3
 #pragma unroll
-                for (int j = 0; j < SM_PK; ++j) {
+                for (int jj = 0; jj < 2; ++jj) {
+                    const int j = 2 * grp + jj;
                     // the row's 32 packed bytes of atom j: 16-byte chunks 2j, 2j + 1 (chunk c lies at c ^ (r & 7))
                     const uint4 lo = lds128p(row + (((2 * j) ^ (r & 7)) << 4));
                     const uint4 hi = lds128p(row + (((2 * j + 1) ^ (r & 7)) << 4));
                     const uint32_t w[8] = {lo.x, lo.y, lo.z, lo.w, hi.x, hi.y, hi.z, hi.w};
-                    uint32_t v[32];  // column c = weights 4c .. 4c + 3 of the atom
                     if (p.layout == WF_LAYOUT_WF16) {
 #pragma unroll
                         for (int i = 0; i < 8; ++i) {
-                            v[4 * i] = w[i] & m;
-                            v[4 * i + 1] = (w[i] >> 2) & m;
-                            v[4 * i + 2] = (w[i] >> 4) & m;
-                            v[4 * i + 3] = (w[i] >> 6) & m;
+                            v[jj][4 * i] = w[i] & m;
+                            v[jj][4 * i + 1] = (w[i] >> 2) & m;
+                            v[jj][4 * i + 2] = (w[i] >> 4) & m;
+                            v[jj][4 * i + 3] = (w[i] >> 6) & m;
                         }
                     } else {  // I2_S: byte b of the 32 holds weights b, b + 32, b + 64, b + 96 at bits 7:6, 5:4, 3:2, 1:0
 #pragma unroll
                         for (int q = 0; q < 4; ++q)
 #pragma unroll
-                            for (int i = 0; i < 8; ++i) v[8 * q + i] = (w[i] >> (6 - 2 * q)) & m;
+                            for (int i = 0; i < 8; ++i) v[jj][8 * q + i] = (w[i] >> (6 - 2 * q)) & m;
                     }
-                    tmem_st32(dst + j * 32, v);
                 }
+                __syncwarp();
+                if (lane == 0) mbar_arrive(&p_empty[ps]);  // this warp's packed rows are in registers
+                if (sit >= SM_XS) mbar_wait(&st_free[s], ((sit / SM_XS) - 1) & 1, poisoned);
+                tc_fence_after();
+                const uint32_t dst = tmem_a + s * SM_A_COLS + grp * 64 + (static_cast<uint32_t>(quarter * 32) << 16);
+                tmem_st32_nowait(dst, v[0]);
+                tmem_st32_nowait(dst + 32, v[1]);
+                asm volatile("tcgen05.wait::st.sync.aligned;\n" ::: "memory");
                 tc_fence_before();
                 __syncwarp();
-                if (lane == 0) {
-                    mbar_arrive(&a_full[s]);
-                    mbar_arrive(&p_empty[ps]);  // the packed rows are in registers / tensor memory
-                }
+                if (lane == 0) mbar_arrive(&a_full[s]);
             }
         }
     } else if (warp < 14 || (warp >= 15 && EPI_GROUPS == 2)) {

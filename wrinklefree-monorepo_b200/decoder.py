@@ -381,6 +381,13 @@ class TernaryDecoder:
         self.pos.copy_(pos0)
         self.tok.copy_(tok0)
 
+    def release(self):
+        """Drop the captured step graph.  A graph of a tensor-parallel step holds the communicator of its collectives:
+        a process group is destroyed only after every such graph has been released."""
+        if self.graph is not None:
+            torch.cuda.synchronize()
+            self.graph = None
+
     def decode(self, steps: int):
         """Greedy decoding of `steps` tokens per sequence; returns [B, steps] token ids."""
         if self._pos_host + steps > self.T:  # the cache and the rotary table hold T positions
