@@ -151,6 +151,24 @@ def build_workload(wf, torch, device, rank: int, world: int, layers_scale: float
     return groups
 
 
+def merge_streaming(wf, groups):
+    """The streaming stacks (M < GEMM_MIN_M) of equal K become ONE grouped launch each: the problems of a grouped launch
+    need not be alike, and what a launch costs beside its bytes (entry to first data, the tail, the hand-over of the SMs
+    to the next launch) is then paid once per K instead of once per stack.  Equal K because the shared-memory plan of a
+    launch is made for its largest K: a 2560-wide stack inside a 6912-wide plan would keep half of its stages."""
+    by_k = {}
+    for g in groups:
+        if not g["batched"]:
+            by_k.setdefault(g["k"], []).append(g)
+    for members in by_k.values():
+        if len(members) < 2:
+            continue
+        probs = [dict(x=m["x"][li], codes=c, w_scale=s_, out=m["y"][li]) for m in members for li, (c, s_) in enumerate(m["layers"])]
+        merged = dict(members=members, group=wf.DecodeGroup(probs))
+        for m in members:
+            m["merged"] = merged
+
+
 def run_group(wf, g, pdl: bool):
     """One (shape, M) layer stack: one grouped launch (or the quantization + contraction pair for M >= GEMM_MIN_M)."""
     if g["batched"]:
@@ -164,10 +182,26 @@ def run_group(wf, g, pdl: bool):
 
 
 def run_step(wf, groups, pdl: bool):
-    """One pass over the sweep: every (shape, M) layer stack is one grouped launch."""
+    """One pass over the sweep (or over the given part of it): the streaming stacks whose merged launch is complete in
+    `groups` run as that one launch, every other (shape, M) layer stack as its own grouped launch."""
+    present = {id(g) for g in groups}
+    done, launches = set(), 0
     for g in groups:
+        mg = g.get("merged")
+        if mg is not None and all(id(m) in present for m in mg["members"]):
+            if id(mg) not in done:
+                done.add(id(mg))
+                mg["group"].run(pdl=pdl, x_ready=True)
+                launches += 1
+                for m in mg["members"]:
+                    if m["reduce"]:
+                        import torch.distributed as dist
+
+                        dist.all_reduce(m["y"])
+            continue
         run_group(wf, g, pdl)
-    return sum(2 if g["batched"] else 1 for g in groups)  # batched = quantization kernel + contraction
+        launches += 2 if g["batched"] else 1  # batched = quantization kernel + contraction
+    return launches
 
 
 def run_step_single(wf, groups, pdl: bool):
@@ -589,6 +623,7 @@ def main():
     ap.add_argument("--only-m", type=int, default=0, help="restrict the sweep to one token batch (profiling)")
     ap.add_argument("--only-shape", type=int, default=-1, help="restrict the sweep to one shape index (profiling)")
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--no-merge", action="store_true", help="one grouped launch per (shape, M) stack instead of one per K")
     args = ap.parse_args()
     rank = int(os.environ.get("RANK", "0"))
     world = int(os.environ.get("WORLD_SIZE", "1"))
@@ -654,18 +689,21 @@ def main():
         SHAPES[:] = [SHAPES[args.only_shape]]
     note(rank, "building workload")
     groups = build_workload(wf, torch, device, rank, world, args.layers_scale)
+    if not args.no_merge:
+        merge_streaming(wf, groups)
     note(rank, "capturing step graph")
     pdl = not args.no_pdl
+    counted = {}
     try:
-        graph = capture(torch, lambda: run_step(wf, groups, pdl))
+        graph = capture(torch, lambda: counted.__setitem__("n", run_step(wf, groups, pdl)))
     except RuntimeError as e:  # programmatic dependent launch not capturable here: plain edges
         if not pdl:
             raise
         print(f"[bench] capture with programmatic dependent launch failed ({e}); retrying without", file=sys.stderr)
         pdl = False
         torch.cuda.synchronize()
-        graph = capture(torch, lambda: run_step(wf, groups, pdl))
-    launches = sum(2 if g["batched"] else 1 for g in groups)
+        graph = capture(torch, lambda: counted.__setitem__("n", run_step(wf, groups, pdl)))
+    launches = counted["n"]  # kernels of this library per step
     total_bytes = step_bytes(groups)
 
     def barrier():
@@ -796,7 +834,7 @@ def main():
     def time_groups(gs):
         if not gs:
             return None
-        gr = capture(torch, lambda: run_step(wf, gs, pdl))
+        gr = capture(torch, lambda: counted.__setitem__(id(gs), run_step(wf, gs, pdl)))
         for _ in range(3):
             gr.replay()
         return statistics.median(timed_replays(gr, args.steps))
@@ -806,7 +844,7 @@ def main():
     note(rank, "breakdown")
     gemm_ops = sum(2.0 * g["m"] * g["n"] * g["k"] * len(g["layers"]) for g in gemm_groups)
     n_gemm_groups = len(gemm_groups)
-    dec_launches = max(1, len(dec_groups))
+    dec_launches = max(1, counted.get(id(dec_groups), len(dec_groups)))
     per_launch_bytes = step_bytes(dec_groups) / dec_launches / world if dec_groups else 0.0  # what one rank's kernel moves
     per_launch_us = (ms_dec or 0.0) * 1e3 / dec_launches
     achieved = per_launch_bytes / (per_launch_us * 1e-6) / 1e9 if dec_groups else 0.0
@@ -879,7 +917,8 @@ def main():
                                            "algorithmic bytes: " + ", ".join(f"shape {k_[0]} M={k_[1]}: {v_:.3f}" for k_, v_ in sorted(NCU_TRAFFIC_RATIO.items())) +
                                            "; other stacks: their mean",
                          "peak_kind": peak_kind + " copy bandwidth",
-                         "kernel": "decode_stream_kernel", "launches": f"the {dec_launches} grouped launches with M < {GEMM_MIN_M}",
+                         "kernel": "decode_stream_kernel", "launches": f"the {dec_launches} grouped launches of the step that hold its {len(dec_groups)} stacks with M < {GEMM_MIN_M}"
+                                     + (" (stacks of equal K share a launch)" if dec_launches < len(dec_groups) else ""),
                          "bytes_per_launch": per_launch_bytes, "us_per_launch": per_launch_us},
             "e2e": {"value": full_bytes / (ms_e2e * 1e-3) / 1e9, "unit": "GB/s", "h2d_bytes_per_step": h2d,
                     "d2h_bytes_per_step": d2h, "ms_per_step": ms_e2e, "ms_per_step_repeats": med(e2e_all),

@@ -416,35 +416,83 @@ __device__ __forceinline__ uint4 lds128(uint32_t addr) {
 
 // One unit: 16 rows x 512 weights from the stage (rows g and g+8 of the tile, 2 x 16 bytes each per lane)
 // against the activations of one k-block.
+// Order matters more than count here.  The MMAs of one accumulator are a dependent chain (about 35 cycles each), and
+// the shared-memory loads are volatile statements that the compiler keeps where they are written: a load directly in
+// front of the MMA that uses it, followed by a second MMA on the same accumulator, serialises a unit into sixteen
+// round trips (measured: 717 cycles per unit, 45 per MMA, the warp idle in between).  So every load of a unit is
+// issued before its first MMA, and consecutive MMAs go to different accumulators.
 template <int NT, bool FOURACC>
 __device__ __forceinline__ void compute_unit(uint32_t w_r0, uint32_t w_r1, uint32_t s_act_kb, int m_valid, int g, int t,
                                              int (&acc)[NT][FOURACC ? 4 : 1][4]) {
+    auto code = [](uint32_t w, int pp) -> uint32_t {
+        if constexpr (FOURACC)
+            return w & (0x03030303u << (2 * pp));
+        else
+            return (w >> (2 * pp)) & 0x03030303u;
+    };
+    if constexpr (NT == 1) {
+        uint4 ra[2], rb[2], bw[2][4];
 #pragma unroll
-    for (int h = 0; h < 2; ++h) {
-        const uint4 ra = lds128(w_r0 + h * 64 + t * 16);
-        const uint4 rb = lds128(w_r1 + h * 64 + t * 16);
-        const uint32_t wa[4] = {ra.x, ra.y, ra.z, ra.w};
-        const uint32_t wb[4] = {rb.x, rb.y, rb.z, rb.w};
+        for (int h = 0; h < 2; ++h) {
+            ra[h] = lds128(w_r0 + h * 64 + t * 16);
+            rb[h] = lds128(w_r1 + h * 64 + t * 16);
+        }
+        const bool tok_ok = g < m_valid;
 #pragma unroll
-        for (int pp = 0; pp < 4; ++pp) {
-            uint32_t a0[4], a1[4];
+        for (int h = 0; h < 2; ++h)
 #pragma unroll
-            for (int i = 0; i < 4; ++i) {
-                if constexpr (FOURACC) {
-                    a0[i] = wa[i] & (0x03030303u << (2 * pp));
-                    a1[i] = wb[i] & (0x03030303u << (2 * pp));
-                } else {
-                    a0[i] = (wa[i] >> (2 * pp)) & 0x03030303u;
-                    a1[i] = (wb[i] >> (2 * pp)) & 0x03030303u;
-                }
+            for (int pp = 0; pp < 4; ++pp) {
+                bw[h][pp] = make_uint4(0, 0, 0, 0);
+                if (tok_ok) bw[h][pp] = lds128(s_act_kb + g * TOK_STRIDE + ((h * 4 + pp) * 4 + t) * 16);
+            }
+        if constexpr (FOURACC) {
+#pragma unroll
+            for (int h = 0; h < 2; ++h) {
+#pragma unroll
+                for (int pp = 0; pp < 4; ++pp)
+                    mma_u8s8(acc[0][pp], code(ra[h].x, pp), code(rb[h].x, pp), code(ra[h].y, pp), code(rb[h].y, pp), bw[h][pp].x, bw[h][pp].y);
+#pragma unroll
+                for (int pp = 0; pp < 4; ++pp)
+                    mma_u8s8(acc[0][pp], code(ra[h].z, pp), code(rb[h].z, pp), code(ra[h].w, pp), code(rb[h].w, pp), bw[h][pp].z, bw[h][pp].w);
+            }
+        } else {  // one accumulator: four partial sums of the unit keep the chains apart
+            int part[4][4] = {};
+#pragma unroll
+            for (int h = 0; h < 2; ++h) {
+#pragma unroll
+                for (int pp = 0; pp < 4; ++pp)
+                    mma_u8s8(part[pp], code(ra[h].x, pp), code(rb[h].x, pp), code(ra[h].y, pp), code(rb[h].y, pp), bw[h][pp].x, bw[h][pp].y);
+#pragma unroll
+                for (int pp = 0; pp < 4; ++pp)
+                    mma_u8s8(part[pp], code(ra[h].z, pp), code(rb[h].z, pp), code(ra[h].w, pp), code(rb[h].w, pp), bw[h][pp].z, bw[h][pp].w);
             }
 #pragma unroll
-            for (int nt = 0; nt < NT; ++nt) {
-                const int tok = nt * 8 + g;
-                uint4 bw = make_uint4(0, 0, 0, 0);
-                if (tok < m_valid) bw = lds128(s_act_kb + tok * TOK_STRIDE + ((h * 4 + pp) * 4 + t) * 16);
-                mma_u8s8(acc[nt][FOURACC ? pp : 0], a0[0], a1[0], a0[1], a1[1], bw.x, bw.y);
-                mma_u8s8(acc[nt][FOURACC ? pp : 0], a0[2], a1[2], a0[3], a1[3], bw.z, bw.w);
+            for (int c = 0; c < 4; ++c) acc[0][0][c] += (part[0][c] + part[1][c]) + (part[2][c] + part[3][c]);
+        }
+    } else {
+#pragma unroll
+        for (int h = 0; h < 2; ++h) {
+            const uint4 ra = lds128(w_r0 + h * 64 + t * 16);
+            const uint4 rb = lds128(w_r1 + h * 64 + t * 16);
+#pragma unroll
+            for (int pp = 0; pp < 4; ++pp) {
+                const uint32_t a0 = code(ra.x, pp), a1 = code(rb.x, pp), a2 = code(ra.y, pp), a3 = code(rb.y, pp);
+                const uint32_t c0 = code(ra.z, pp), c1 = code(rb.z, pp), c2 = code(ra.w, pp), c3 = code(rb.w, pp);
+                constexpr int NG = NT < 4 ? NT : 4;  // token tiles whose activations are in registers at a time
+#pragma unroll
+                for (int n0 = 0; n0 < NT; n0 += NG) {
+                    uint4 bw[NG];
+#pragma unroll
+                    for (int nt = 0; nt < NG; ++nt) {
+                        const int tok = (n0 + nt) * 8 + g;
+                        bw[nt] = make_uint4(0, 0, 0, 0);
+                        if (tok < m_valid) bw[nt] = lds128(s_act_kb + tok * TOK_STRIDE + ((h * 4 + pp) * 4 + t) * 16);
+                    }
+#pragma unroll
+                    for (int nt = 0; nt < NG; ++nt) mma_u8s8(acc[n0 + nt][FOURACC ? pp : 0], a0, a1, a2, a3, bw[nt].x, bw[nt].y);
+#pragma unroll
+                    for (int nt = 0; nt < NG; ++nt) mma_u8s8(acc[n0 + nt][FOURACC ? pp : 0], c0, c1, c2, c3, bw[nt].z, bw[nt].w);
+                }
             }
         }
     }

@@ -82,19 +82,33 @@ constexpr int SM_BM = 128;   // weight rows per tile
 constexpr int SM_BK = 128;   // K per swizzle atom (128 bytes of int8)
 constexpr int SM_PK = 4;     // atoms per stage: a stage is 512 weights of every row = one 128-byte packed row segment
 constexpr int SM_PS = 6;     // packed-weight stages
+// Issuing threads.  One thread issues a tcgen05.mma of K = 32 every ~26 ns whatever the instruction's size; the tensor
+// pipe itself needs 17 ns for N = 64 and less than 7 ns for N = 16 (measured with the A operand in tensor memory: two
+// issuing threads on separate accumulators reach 13 ns per instruction, four 6.6 ns).  For few tokens per tile the
+// MMAs of a stage are therefore shared out among several threads (one per warp), atom by atom, each with an accumulator
+// of its own; the epilogue adds the partial accumulators.
 template <int NTOK>
-constexpr int sm_xs() { return NTOK > 64 ? 2 : 3; }  // token-tile stages = tensor-memory stages of expanded weights
+__host__ __device__ constexpr int sm_issuers() { return NTOK <= 16 ? 4 : (NTOK <= 64 ? 2 : 1); }
+template <int NTOK>
+__host__ __device__ constexpr int sm_acc_cols() { return 2 * sm_issuers<NTOK>() * NTOK <= 128 ? 128 : 256; }  // two buffers of one accumulator per issuer
+constexpr int SM_A_COLS = SM_PK * SM_BK / 4;  // 128 columns of 4 int8 per stage
+template <int NTOK>
+__host__ __device__ constexpr int sm_xs() { return (512 - sm_acc_cols<NTOK>()) / SM_A_COLS; }  // token-tile stages = tensor-memory stages of expanded weights
 constexpr int SM_P_BYTES = SM_BM * SM_PK * SM_BK / 4;  // 16 KB
 constexpr int SM_THREADS = 19 * 32;
+// the second issuer of the two-issuer forms is a warp of its own behind the others; the four-issuer form (16 tokens)
+// uses the warps that the wider forms give to their second epilogue group
 template <int NTOK>
-constexpr int sm_acc_cols() { return NTOK > 64 ? 256 : 128; }  // two accumulators of NTOK columns
-constexpr int SM_A_COLS = SM_PK * SM_BK / 4;  // 128 columns of 4 int8 per stage
+__host__ __device__ constexpr int sm_threads() { return SM_THREADS + (sm_issuers<NTOK>() == 2 ? 32 : 0); }
 template <int NTOK>
 constexpr size_t sm_smem() {  // more than half of an SM's shared memory: two of these CTAs never share an SM
     return 1024 + SM_PS * SM_P_BYTES + sm_xs<NTOK>() * NTOK * SM_PK * SM_BK + 2048;
 }
 static_assert(sm_smem<16>() > 114 * 1024 && sm_smem<64>() <= 227 * 1024 && sm_smem<128>() <= 227 * 1024, "shared memory");
-static_assert(sm_acc_cols<64>() + sm_xs<64>() * SM_A_COLS <= 512 && sm_acc_cols<128>() + sm_xs<128>() * SM_A_COLS <= 512, "tensor memory");
+static_assert(sm_acc_cols<16>() + sm_xs<16>() * SM_A_COLS <= 512 && sm_acc_cols<32>() + sm_xs<32>() * SM_A_COLS <= 512 &&
+                  sm_acc_cols<64>() + sm_xs<64>() * SM_A_COLS <= 512 && sm_acc_cols<128>() + sm_xs<128>() * SM_A_COLS <= 512 &&
+                  sm_xs<16>() == 3 && sm_xs<32>() == 3 && sm_xs<64>() == 2 && sm_xs<128>() == 2,
+              "tensor memory");
 
 // The four MMAs of one 128-byte swizzle atom of K in one block of PTX: A advances by 8 tensor-memory columns, B by 32
 // bytes (2 in descriptor units) per step.  The issuing thread is the pipeline's critical path for few tokens, so the
@@ -146,12 +160,14 @@ __device__ __forceinline__ void tmem_ldn<16>(uint32_t addr, uint32_t (&v)[16]) {
 }
 
 template <int NTOK>
-__global__ void __launch_bounds__(SM_THREADS, 1)
+__global__ void __launch_bounds__(sm_threads<NTOK>(), 1)
     prefill_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_constant__ CUtensorMap tmap_p, const PrefillParams p) {
     constexpr int EPI_GROUPS = NTOK >= 32 ? 2 : 1;  // epilogue warp groups; each takes NTOK / EPI_GROUPS token columns
     constexpr int EPI_COLS = NTOK / EPI_GROUPS;
-    constexpr int SM_XS = NTOK > 64 ? 2 : 3;
-    constexpr int SM_ACC_COLS = NTOK > 64 ? 256 : 128;
+    constexpr int SM_XS = sm_xs<NTOK>();
+    constexpr int SM_ACC_COLS = sm_acc_cols<NTOK>();
+    constexpr int NI = sm_issuers<NTOK>();   // issuing threads; issuer i takes the atoms i, i + NI, ... of every stage
+    constexpr int ACC_BUF = NI * NTOK;       // columns of one accumulator buffer: one partial accumulator per issuer
     constexpr int X_ATOM = NTOK * SM_BK;        // one 128-byte swizzle atom of the token tile
     constexpr int X_BYTES = SM_PK * X_ATOM;     // a stage: 512 values of K for every token
     extern __shared__ uint8_t smem_raw[];
@@ -190,10 +206,10 @@ __global__ void __launch_bounds__(SM_THREADS, 1)
         for (int s = 0; s < SM_XS; ++s) {
             mbar_init(&x_full[s], 1);
             mbar_init(&a_full[s], 8);
-            mbar_init(&st_free[s], 1);
+            mbar_init(&st_free[s], NI);
         }
         for (int a = 0; a < 2; ++a) {
-            mbar_init(&acc_full[a], 1);
+            mbar_init(&acc_full[a], NI);
             mbar_init(&acc_empty[a], 4 * EPI_GROUPS);
         }
         *poisoned = 0;
@@ -208,6 +224,8 @@ __global__ void __launch_bounds__(SM_THREADS, 1)
     tc_fence_after();
     const uint32_t tmem_base = *tmem_slot;
     const uint32_t tmem_a = tmem_base + SM_ACC_COLS;  // SM_XS stages of SM_A_COLS columns
+    // the issuing warps: warp 1, and warps 15-17 (four issuers) or warp 19 (two issuers)
+    const int issuer = warp == 1 ? 0 : ((NI == 4 && warp >= 15 && warp <= 17) ? warp - 14 : ((NI == 2 && warp == 19) ? 1 : -1));
 
     if (warp == 0) {
         if (lane == 0) {
@@ -239,40 +257,42 @@ __global__ void __launch_bounds__(SM_THREADS, 1)
                 }
             }
         }
-    } else if (warp == 1) {
+    } else if (issuer >= 0) {
         if (lane == 0) {
             // D = s32, A = unsigned 8-bit (codes, from tensor memory), B = signed 8-bit (tokens, K-major), N = NTOK, M = 128
             const uint32_t idesc = (2u << 4) | (0u << 7) | (1u << 10) | (static_cast<uint32_t>(NTOK >> 3) << 17) |
                                    (static_cast<uint32_t>(SM_BM >> 4) << 24);
-            // operand descriptors of every (stage, atom), fixed for the whole kernel
-            uint64_t bdesc[SM_XS][SM_PK];
+            constexpr int MY_ATOMS = SM_PK / NI;
+            // operand descriptors of this thread's atoms of every stage, fixed for the whole kernel
+            uint64_t bdesc[SM_XS][MY_ATOMS];
 #pragma unroll
             for (int s = 0; s < SM_XS; ++s)
 #pragma unroll
-                for (int j = 0; j < SM_PK; ++j) bdesc[s][j] = smem_desc_sw128(smem_u32(x_ring + s * X_BYTES + j * X_ATOM));
+                for (int jj = 0; jj < MY_ATOMS; ++jj)
+                    bdesc[s][jj] = smem_desc_sw128(smem_u32(x_ring + s * X_BYTES + (issuer + jj * NI) * X_ATOM));
             int sit = 0, nt = 0;
             for (int t = blockIdx.x; t < total_tiles; t += gridDim.x, ++nt) {
                 const int a = nt & 1;
                 if (nt >= 2) mbar_wait(&acc_empty[a], ((nt >> 1) - 1) & 1, poisoned);
                 tc_fence_after();
-                const uint32_t d_tmem = tmem_base + a * NTOK;
+                const uint32_t d_tmem = tmem_base + a * ACC_BUF + issuer * NTOK;
                 for (int g = 0; g < stages; ++g, ++sit) {
                     const int s = sit % SM_XS;
                     mbar_wait(&x_full[s], (sit / SM_XS) & 1, poisoned);
                     mbar_wait(&a_full[s], (sit / SM_XS) & 1, poisoned);
                     tc_fence_after();
                     const uint32_t a_stage = tmem_a + s * SM_A_COLS;
-                    // sixteen MMAs of 32 values of K: four per swizzle atom (the ring index is resolved by a switch so
-                    // that the descriptors stay in registers)
+                    // four MMAs of 32 values of K per swizzle atom (the ring index is resolved by a switch so that the
+                    // descriptors stay in registers)
 #pragma unroll
                     for (int ss = 0; ss < SM_XS; ++ss) {
                         if (ss == s) {
 #pragma unroll
-                            for (int j = 0; j < SM_PK; ++j)
-                                mma_i8_ts_x4(d_tmem, a_stage + j * 32, bdesc[ss][j], idesc, (g | j) ? 1u : 0u);
+                            for (int jj = 0; jj < MY_ATOMS; ++jj)
+                                mma_i8_ts_x4(d_tmem, a_stage + (issuer + jj * NI) * 32, bdesc[ss][jj], idesc, (g | jj) ? 1u : 0u);
                         }
                     }
-                    tc_commit(&st_free[s]);
+                    tc_commit(&st_free[s]);  // one arrival per issuer
                 }
                 tc_commit(&acc_full[a]);
             }
@@ -328,7 +348,7 @@ __global__ void __launch_bounds__(SM_THREADS, 1)
                 if (lane == 0) mbar_arrive(&a_full[s]);
             }
         }
-    } else if (warp < 14 || (warp >= 15 && EPI_GROUPS == 2)) {
+    } else if (warp < 14 || (warp >= 15 && warp <= 18 && EPI_GROUPS == 2)) {
         // ---- epilogue: thread = weight row (TMEM lane), registers = tokens
         const int quarter = warp & 3;
         const int r = quarter * 32 + lane;
@@ -368,7 +388,14 @@ __global__ void __launch_bounds__(SM_THREADS, 1)
 #pragma unroll
             for (int c0 = col0; c0 < col0 + EPI_COLS; c0 += 16) {
                 uint32_t v[16];
-                tmem_ldn<16>(tmem_base + (static_cast<uint32_t>(quarter * 32) << 16) + a * NTOK + c0, v);
+                tmem_ldn<16>(tmem_base + (static_cast<uint32_t>(quarter * 32) << 16) + a * ACC_BUF + c0, v);
+#pragma unroll
+                for (int i = 1; i < NI; ++i) {  // the other issuers' partial accumulators
+                    uint32_t u[16];
+                    tmem_ldn<16>(tmem_base + (static_cast<uint32_t>(quarter * 32) << 16) + a * ACC_BUF + i * NTOK + c0, u);
+#pragma unroll
+                    for (int jt = 0; jt < 16; ++jt) v[jt] += u[jt];
+                }
                 if (c0 + 16 == col0 + EPI_COLS) {  // this group's columns are in registers: hand them back to the MMA warp
                     tc_fence_before();
                     __syncwarp();
@@ -921,12 +948,15 @@ static int prefill_impl(const char* who, const void* x, int x_dtype, int64_t ldx
         lc.dynamicSmemBytes = PR_SMEM;
         WF_CUDA(cudaLaunchKernelEx(&lc, prefill_pair_kernel, tmap_a, tmap_p, pp));
     } else if (ntok == 16) {
+        lc.blockDim = dim3(sm_threads<16>());
         lc.dynamicSmemBytes = sm_smem<16>();
         WF_CUDA(cudaLaunchKernelEx(&lc, prefill_kernel<16>, tmap_a, tmap_p, pp));
     } else if (ntok == 32) {
+        lc.blockDim = dim3(sm_threads<32>());
         lc.dynamicSmemBytes = sm_smem<32>();
         WF_CUDA(cudaLaunchKernelEx(&lc, prefill_kernel<32>, tmap_a, tmap_p, pp));
     } else if (ntok == 64) {
+        lc.blockDim = dim3(sm_threads<64>());
         lc.dynamicSmemBytes = sm_smem<64>();
         WF_CUDA(cudaLaunchKernelEx(&lc, prefill_kernel<64>, tmap_a, tmap_p, pp));
     } else {
