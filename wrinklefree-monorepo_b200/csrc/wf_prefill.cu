@@ -9,12 +9,14 @@
 // per SM) walk the tiles; K advances in stages of 512:
 //   * warp 0 (one lane): TMA of the PACKED weight rows (128 rows x 128 bytes, 128-byte swizzle), ring of 6 stages;
 //   * warp 14 (one lane): TMA of the int8 token tile (4 swizzle atoms of NTOK x 128 bytes, the MMA's B operand);
-//   * warps 2-5 / 6-9: two expansion groups, each takes half of every stage; thread = weight row: 4 x ld.shared.v4, mask +
-//     shift to one int8 per byte (into registers, before the tensor-memory stage is free), 2 x tcgen05.st of 32 columns
-//     into a ring of tensor-memory stages;
-//   * warp 1 (one lane): 16 x tcgen05.mma.cta_group::1.kind::i8 (M = 128, N = NTOK, K = 32), A operand FROM TENSOR MEMORY,
-//     one commit per stage; two accumulators, so the epilogue of a tile runs under the next tile's MMAs;
-//   * warps 10-13 (and 15-18): epilogue, thread = weight row: tcgen05.ld, integer correction, fp32 rescale, store.
+//   * warps 2-5 / 6-9: expansion, each half takes two of a stage's four atoms; thread = weight row: 4 x ld.shared.v4, mask +
+//     shift to one int8 per byte, 2 x tcgen05.st of 32 columns into a ring of tensor-memory stages;
+//   * warp 1 (one lane): tcgen05.mma.cta_group::1.kind::i8 (M = 128, N = NTOK, K = 32), A operand FROM TENSOR MEMORY, sixteen
+//     per stage and one commit; two accumulator buffers, so the epilogue of a tile runs under the next tile's MMAs.  The
+//     forms for few tokens have two or three issuing threads (warps 1 and 19, or 1, 15 and 16), one per ring slot, each
+//     with a partial accumulator of its own;
+//   * warps 10-13 (and 15-18): epilogue, thread = weight row: tcgen05.ld (summing the partial accumulators), integer
+//     correction, fp32 rescale, store.
 // Every mbarrier wait is bounded.
 #include <cuda.h>
 
@@ -85,19 +87,22 @@ constexpr int SM_PS = 6;     // packed-weight stages
 // Issuing threads.  One thread issues a tcgen05.mma of K = 32 every ~26 ns whatever the instruction's size; the tensor
 // pipe itself needs 17 ns for N = 64 and less than 7 ns for N = 16 (measured with the A operand in tensor memory: two
 // issuing threads on separate accumulators reach 13 ns per instruction, four 6.6 ns).  For few tokens per tile the
-// MMAs of a stage are therefore shared out among several threads (one per warp), atom by atom, each with an accumulator
-// of its own; the epilogue adds the partial accumulators.
+// stages are therefore shared out among several issuing threads (one per warp): thread i takes the stages that land in
+// ring slot i, sixteen MMAs and one commit each, into an accumulator of its own; the epilogue adds the partial
+// accumulators.  (Sharing out the four atoms of every stage instead was slower: each issuing thread then runs the whole
+// per-stage bookkeeping, and a single thread's instruction stream is what limits it.)
 template <int NTOK>
-__host__ __device__ constexpr int sm_issuers() { return NTOK <= 16 ? 4 : (NTOK <= 64 ? 2 : 1); }
+__host__ __device__ constexpr int sm_issuers() { return NTOK <= 16 ? 3 : (NTOK <= 64 ? 2 : 1); }
 template <int NTOK>
 __host__ __device__ constexpr int sm_acc_cols() { return 2 * sm_issuers<NTOK>() * NTOK <= 128 ? 128 : 256; }  // two buffers of one accumulator per issuer
 constexpr int SM_A_COLS = SM_PK * SM_BK / 4;  // 128 columns of 4 int8 per stage
+// token-tile stages = tensor-memory stages of expanded weights; with several issuers one ring slot per issuer
 template <int NTOK>
-__host__ __device__ constexpr int sm_xs() { return (512 - sm_acc_cols<NTOK>()) / SM_A_COLS; }  // token-tile stages = tensor-memory stages of expanded weights
+__host__ __device__ constexpr int sm_xs() { return sm_issuers<NTOK>() > 1 ? sm_issuers<NTOK>() : (512 - sm_acc_cols<NTOK>()) / SM_A_COLS; }
 constexpr int SM_P_BYTES = SM_BM * SM_PK * SM_BK / 4;  // 16 KB
 constexpr int SM_THREADS = 19 * 32;
-// the second issuer of the two-issuer forms is a warp of its own behind the others; the four-issuer form (16 tokens)
-// uses the warps that the wider forms give to their second epilogue group
+// the second issuer of the two-issuer forms is a warp of its own behind the others; the three-issuer form (16 tokens)
+// uses warps that the wider forms give to their second epilogue group
 template <int NTOK>
 __host__ __device__ constexpr int sm_threads() { return SM_THREADS + (sm_issuers<NTOK>() == 2 ? 32 : 0); }
 template <int NTOK>
@@ -107,7 +112,7 @@ constexpr size_t sm_smem() {  // more than half of an SM's shared memory: two of
 static_assert(sm_smem<16>() > 114 * 1024 && sm_smem<64>() <= 227 * 1024 && sm_smem<128>() <= 227 * 1024, "shared memory");
 static_assert(sm_acc_cols<16>() + sm_xs<16>() * SM_A_COLS <= 512 && sm_acc_cols<32>() + sm_xs<32>() * SM_A_COLS <= 512 &&
                   sm_acc_cols<64>() + sm_xs<64>() * SM_A_COLS <= 512 && sm_acc_cols<128>() + sm_xs<128>() * SM_A_COLS <= 512 &&
-                  sm_xs<16>() == 3 && sm_xs<32>() == 3 && sm_xs<64>() == 2 && sm_xs<128>() == 2,
+                  sm_xs<16>() == 3 && sm_xs<32>() == 2 && sm_xs<64>() == 2 && sm_xs<128>() == 2,
               "tensor memory");
 
 // The four MMAs of one 128-byte swizzle atom of K in one block of PTX: A advances by 8 tensor-memory columns, B by 32
@@ -166,8 +171,9 @@ __global__ void __launch_bounds__(sm_threads<NTOK>(), 1)
     constexpr int EPI_COLS = NTOK / EPI_GROUPS;
     constexpr int SM_XS = sm_xs<NTOK>();
     constexpr int SM_ACC_COLS = sm_acc_cols<NTOK>();
-    constexpr int NI = sm_issuers<NTOK>();   // issuing threads; issuer i takes the atoms i, i + NI, ... of every stage
+    constexpr int NI = sm_issuers<NTOK>();   // issuing threads; with several, issuer i takes the stages of ring slot i
     constexpr int ACC_BUF = NI * NTOK;       // columns of one accumulator buffer: one partial accumulator per issuer
+    static_assert(NI == 1 || NI == SM_XS, "one ring slot per issuer");
     constexpr int X_ATOM = NTOK * SM_BK;        // one 128-byte swizzle atom of the token tile
     constexpr int X_BYTES = SM_PK * X_ATOM;     // a stage: 512 values of K for every token
     extern __shared__ uint8_t smem_raw[];
@@ -176,8 +182,7 @@ __global__ void __launch_bounds__(sm_threads<NTOK>(), 1)
     uint8_t* x_ring = p_ring + SM_PS * SM_P_BYTES;    // [SM_XS][SM_PK atoms][NTOK rows x 128 B], 128-byte swizzle
     uint64_t* p_full = reinterpret_cast<uint64_t*>(x_ring + SM_XS * X_BYTES);
     uint64_t* p_empty = p_full + SM_PS;
-    uint64_t* x_full = p_empty + SM_PS;
-    uint64_t* a_full = x_full + SM_XS;        // expanded weights of the stage are in tensor memory
+    uint64_t* a_full = p_empty + SM_PS;       // the stage's token tile has landed AND its expanded weights are in tensor memory
     uint64_t* st_free = a_full + SM_XS;       // MMA commit: token tile and tensor-memory stage may be overwritten
     uint64_t* acc_full = st_free + SM_XS;
     uint64_t* acc_empty = acc_full + 2;
@@ -204,9 +209,8 @@ __global__ void __launch_bounds__(sm_threads<NTOK>(), 1)
             mbar_init(&p_empty[s], 8);
         }
         for (int s = 0; s < SM_XS; ++s) {
-            mbar_init(&x_full[s], 1);
-            mbar_init(&a_full[s], 8);
-            mbar_init(&st_free[s], NI);
+            mbar_init(&a_full[s], 8 + 1);  // eight expansion warps + the token tile's bytes
+            mbar_init(&st_free[s], 1);
         }
         for (int a = 0; a < 2; ++a) {
             mbar_init(&acc_full[a], NI);
@@ -224,8 +228,8 @@ __global__ void __launch_bounds__(sm_threads<NTOK>(), 1)
     tc_fence_after();
     const uint32_t tmem_base = *tmem_slot;
     const uint32_t tmem_a = tmem_base + SM_ACC_COLS;  // SM_XS stages of SM_A_COLS columns
-    // the issuing warps: warp 1, and warps 15-17 (four issuers) or warp 19 (two issuers)
-    const int issuer = warp == 1 ? 0 : ((NI == 4 && warp >= 15 && warp <= 17) ? warp - 14 : ((NI == 2 && warp == 19) ? 1 : -1));
+    // the issuing warps: warp 1, and warps 15-16 (three issuers) or warp 19 (two issuers)
+    const int issuer = warp == 1 ? 0 : ((NI == 3 && warp >= 15 && warp <= 16) ? warp - 14 : ((NI == 2 && warp == 19) ? 1 : -1));
 
     if (warp == 0) {
         if (lane == 0) {
@@ -250,10 +254,10 @@ __global__ void __launch_bounds__(sm_threads<NTOK>(), 1)
                 for (int g = 0; g < stages; ++g, ++sit) {
                     const int s = sit % SM_XS;
                     if (sit >= SM_XS) mbar_wait(&st_free[s], ((sit / SM_XS) - 1) & 1, poisoned);
-                    mbar_expect_tx(&x_full[s], X_BYTES);
+                    mbar_expect_tx(&a_full[s], X_BYTES);
 #pragma unroll
                     for (int j = 0; j < SM_PK; ++j)  // an atom that lies past K arrives as zeros
-                        tma_load_2d(x_ring + s * X_BYTES + j * X_ATOM, &tmap_x, (g * SM_PK + j) * SM_BK, row_x, &x_full[s]);
+                        tma_load_2d(x_ring + s * X_BYTES + j * X_ATOM, &tmap_x, (g * SM_PK + j) * SM_BK, row_x, &a_full[s]);
                 }
             }
         }
@@ -262,46 +266,75 @@ __global__ void __launch_bounds__(sm_threads<NTOK>(), 1)
             // D = s32, A = unsigned 8-bit (codes, from tensor memory), B = signed 8-bit (tokens, K-major), N = NTOK, M = 128
             const uint32_t idesc = (2u << 4) | (0u << 7) | (1u << 10) | (static_cast<uint32_t>(NTOK >> 3) << 17) |
                                    (static_cast<uint32_t>(SM_BM >> 4) << 24);
-            constexpr int MY_ATOMS = SM_PK / NI;
-            // operand descriptors of this thread's atoms of every stage, fixed for the whole kernel
-            uint64_t bdesc[SM_XS][MY_ATOMS];
+            if constexpr (NI > 1) {
+                // This thread's stages are those of ring slot `issuer`: operands, barriers and the accumulator column are fixed.
+                uint64_t bdesc[SM_PK];
 #pragma unroll
-            for (int s = 0; s < SM_XS; ++s)
-#pragma unroll
-                for (int jj = 0; jj < MY_ATOMS; ++jj)
-                    bdesc[s][jj] = smem_desc_sw128(smem_u32(x_ring + s * X_BYTES + (issuer + jj * NI) * X_ATOM));
-            int sit = 0, nt = 0;
-            for (int t = blockIdx.x; t < total_tiles; t += gridDim.x, ++nt) {
-                const int a = nt & 1;
-                if (nt >= 2) mbar_wait(&acc_empty[a], ((nt >> 1) - 1) & 1, poisoned);
-                tc_fence_after();
-                const uint32_t d_tmem = tmem_base + a * ACC_BUF + issuer * NTOK;
-                for (int g = 0; g < stages; ++g, ++sit) {
-                    const int s = sit % SM_XS;
-                    mbar_wait(&x_full[s], (sit / SM_XS) & 1, poisoned);
-                    mbar_wait(&a_full[s], (sit / SM_XS) & 1, poisoned);
-                    tc_fence_after();
-                    const uint32_t a_stage = tmem_a + s * SM_A_COLS;
-                    // four MMAs of 32 values of K per swizzle atom (the ring index is resolved by a switch so that the
-                    // descriptors stay in registers)
-#pragma unroll
-                    for (int ss = 0; ss < SM_XS; ++ss) {
-                        if (ss == s) {
-#pragma unroll
-                            for (int jj = 0; jj < MY_ATOMS; ++jj)
-                                mma_i8_ts_x4(d_tmem, a_stage + (issuer + jj * NI) * 32, bdesc[ss][jj], idesc, (g | jj) ? 1u : 0u);
-                        }
+                for (int j = 0; j < SM_PK; ++j) bdesc[j] = smem_desc_sw128(smem_u32(x_ring + issuer * X_BYTES + j * X_ATOM));
+                const uint32_t a_stage = tmem_a + issuer * SM_A_COLS;
+                uint64_t* const my_full = &a_full[issuer];
+                uint64_t* const my_free = &st_free[issuer];
+                unsigned par = 0;  // parity of the next wait on my_full
+                int nt = 0, sit0 = 0;
+                for (int t = blockIdx.x; t < total_tiles; t += gridDim.x, ++nt, sit0 += stages) {
+                    const int a = nt & 1;
+                    const int r0 = sit0 % NI;
+                    const int g0 = issuer >= r0 ? issuer - r0 : issuer - r0 + NI;  // this thread's first stage of the tile
+                    if (nt >= 2) mbar_wait(&acc_empty[a], ((nt >> 1) - 1) & 1, poisoned);
+                    if (g0 >= stages) {  // a tile of fewer stages than issuers: nothing of it is this thread's
+                        mbar_arrive(&acc_full[a]);
+                        continue;
                     }
-                    tc_commit(&st_free[s]);  // one arrival per issuer
+                    tc_fence_after();
+                    const uint32_t d_tmem = tmem_base + a * ACC_BUF + issuer * NTOK;
+                    for (int g = g0; g < stages; g += NI) {
+                        mbar_wait(my_full, par, poisoned);
+                        par ^= 1;
+                        tc_fence_after();
+#pragma unroll
+                        for (int j = 0; j < SM_PK; ++j) mma_i8_ts_x4(d_tmem, a_stage + j * 32, bdesc[j], idesc, (g != g0 || j) ? 1u : 0u);
+                        tc_commit(my_free);
+                    }
+                    tc_commit(&acc_full[a]);
                 }
-                tc_commit(&acc_full[a]);
+            } else {
+                // operand descriptors of every (stage, atom), fixed for the whole kernel
+                uint64_t bdesc[SM_XS][SM_PK];
+#pragma unroll
+                for (int s = 0; s < SM_XS; ++s)
+#pragma unroll
+                    for (int j = 0; j < SM_PK; ++j) bdesc[s][j] = smem_desc_sw128(smem_u32(x_ring + s * X_BYTES + j * X_ATOM));
+                int sit = 0, nt = 0;
+                for (int t = blockIdx.x; t < total_tiles; t += gridDim.x, ++nt) {
+                    const int a = nt & 1;
+                    if (nt >= 2) mbar_wait(&acc_empty[a], ((nt >> 1) - 1) & 1, poisoned);
+                    tc_fence_after();
+                    const uint32_t d_tmem = tmem_base + a * ACC_BUF;
+                    for (int g = 0; g < stages; ++g, ++sit) {
+                        const int s = sit % SM_XS;
+                        mbar_wait(&a_full[s], (sit / SM_XS) & 1, poisoned);
+                        tc_fence_after();
+                        const uint32_t a_stage = tmem_a + s * SM_A_COLS;
+                        // sixteen MMAs of 32 values of K: four per swizzle atom (the ring index is resolved by a switch so
+                        // that the descriptors stay in registers)
+#pragma unroll
+                        for (int ss = 0; ss < SM_XS; ++ss) {
+                            if (ss == s) {
+#pragma unroll
+                                for (int j = 0; j < SM_PK; ++j)
+                                    mma_i8_ts_x4(d_tmem, a_stage + j * 32, bdesc[ss][j], idesc, (g | j) ? 1u : 0u);
+                            }
+                        }
+                        tc_commit(&st_free[s]);
+                    }
+                    tc_commit(&acc_full[a]);
+                }
             }
         }
     } else if (warp < 10) {
-        // ---- expansion: both groups work on EVERY stage, group (warp - 2) / 4 on its half of the stage's four atoms;
-        // thread = weight row of the tile.  A group's two atoms are expanded into registers BEFORE the tensor-memory stage
-        // is known to be free, so that only two tcgen05.st and their wait lie between "the MMAs of the stage's previous
-        // use have completed" and "the next may start".
+        // ---- expansion: warps 2-5 expand atoms 0 and 1 of every stage's four, warps 6-9 atoms 2 and 3; thread = weight
+        // row of the tile.  (A second set of eight warps on alternate stages gained nothing: the sets share the SM's
+        // integer pipes.)
         const int grp = (warp - 2) >> 2;
         const int quarter = warp & 3;           // the TMEM lanes this warp may access
         const int r = quarter * 32 + lane;      // weight row inside the tile
@@ -312,36 +345,39 @@ __global__ void __launch_bounds__(sm_threads<NTOK>(), 1)
                 const int ps = sit % SM_PS, s = sit % SM_XS;
                 mbar_wait(&p_full[ps], (sit / SM_PS) & 1, poisoned);
                 const uint32_t row = smem_u32(p_ring + ps * SM_P_BYTES) + r * 128;
-                uint32_t v[2][32];  // column c of an atom = its weights 4c .. 4c + 3
+                // the row's 32 packed bytes of atom j: 16-byte chunks 2j, 2j + 1 (chunk c lies at c ^ (r & 7))
+                uint4 pk[4];
+#pragma unroll
+                for (int c = 0; c < 4; ++c) pk[c] = lds128p(row + (((4 * grp + c) ^ (r & 7)) << 4));
+                // the loads have returned once their values are used; the slot is handed back after the first atom
+                if (sit >= SM_XS) mbar_wait(&st_free[s], ((sit / SM_XS) - 1) & 1, poisoned);
+                tc_fence_after();
+                const uint32_t dst = tmem_a + s * SM_A_COLS + grp * 64 + (static_cast<uint32_t>(quarter * 32) << 16);
 #pragma unroll
                 for (int jj = 0; jj < 2; ++jj) {
-                    const int j = 2 * grp + jj;
-                    // the row's 32 packed bytes of atom j: 16-byte chunks 2j, 2j + 1 (chunk c lies at c ^ (r & 7))
-                    const uint4 lo = lds128p(row + (((2 * j) ^ (r & 7)) << 4));
-                    const uint4 hi = lds128p(row + (((2 * j + 1) ^ (r & 7)) << 4));
-                    const uint32_t w[8] = {lo.x, lo.y, lo.z, lo.w, hi.x, hi.y, hi.z, hi.w};
+                    const uint32_t w[8] = {pk[2 * jj].x, pk[2 * jj].y, pk[2 * jj].z, pk[2 * jj].w,
+                                           pk[2 * jj + 1].x, pk[2 * jj + 1].y, pk[2 * jj + 1].z, pk[2 * jj + 1].w};
+                    uint32_t v[32];  // column c of the atom = its weights 4c .. 4c + 3
                     if (p.layout == WF_LAYOUT_WF16) {
 #pragma unroll
                         for (int i = 0; i < 8; ++i) {
-                            v[jj][4 * i] = w[i] & m;
-                            v[jj][4 * i + 1] = (w[i] >> 2) & m;
-                            v[jj][4 * i + 2] = (w[i] >> 4) & m;
-                            v[jj][4 * i + 3] = (w[i] >> 6) & m;
+                            v[4 * i] = w[i] & m;
+                            v[4 * i + 1] = (w[i] >> 2) & m;
+                            v[4 * i + 2] = (w[i] >> 4) & m;
+                            v[4 * i + 3] = (w[i] >> 6) & m;
                         }
                     } else {  // I2_S: byte b of the 32 holds weights b, b + 32, b + 64, b + 96 at bits 7:6, 5:4, 3:2, 1:0
 #pragma unroll
                         for (int q = 0; q < 4; ++q)
 #pragma unroll
-                            for (int i = 0; i < 8; ++i) v[jj][8 * q + i] = (w[i] >> (6 - 2 * q)) & m;
+                            for (int i = 0; i < 8; ++i) v[8 * q + i] = (w[i] >> (6 - 2 * q)) & m;
+                    }
+                    tmem_st32_nowait(dst + jj * 32, v);
+                    if (jj == 1) {  // every packed byte of this warp's share is in registers or on its way to tensor memory
+                        __syncwarp();
+                        if (lane == 0) mbar_arrive(&p_empty[ps]);
                     }
                 }
-                __syncwarp();
-                if (lane == 0) mbar_arrive(&p_empty[ps]);  // this warp's packed rows are in registers
-                if (sit >= SM_XS) mbar_wait(&st_free[s], ((sit / SM_XS) - 1) & 1, poisoned);
-                tc_fence_after();
-                const uint32_t dst = tmem_a + s * SM_A_COLS + grp * 64 + (static_cast<uint32_t>(quarter * 32) << 16);
-                tmem_st32_nowait(dst, v[0]);
-                tmem_st32_nowait(dst + 32, v[1]);
                 asm volatile("tcgen05.wait::st.sync.aligned;\n" ::: "memory");
                 tc_fence_before();
                 __syncwarp();
@@ -388,13 +424,22 @@ __global__ void __launch_bounds__(sm_threads<NTOK>(), 1)
 #pragma unroll
             for (int c0 = col0; c0 < col0 + EPI_COLS; c0 += 16) {
                 uint32_t v[16];
-                tmem_ldn<16>(tmem_base + (static_cast<uint32_t>(quarter * 32) << 16) + a * ACC_BUF + c0, v);
+                if constexpr (NI == 1) {
+                    tmem_ldn<16>(tmem_base + (static_cast<uint32_t>(quarter * 32) << 16) + a * ACC_BUF + c0, v);
+                } else {  // the sum of the issuers' partial accumulators (an issuer without a stage in this tile wrote none)
 #pragma unroll
-                for (int i = 1; i < NI; ++i) {  // the other issuers' partial accumulators
-                    uint32_t u[16];
-                    tmem_ldn<16>(tmem_base + (static_cast<uint32_t>(quarter * 32) << 16) + a * ACC_BUF + i * NTOK + c0, u);
+                    for (int jt = 0; jt < 16; ++jt) v[jt] = 0;
+                    const int r0 = static_cast<int>((static_cast<long long>(nt) * stages) % NI);
 #pragma unroll
-                    for (int jt = 0; jt < 16; ++jt) v[jt] += u[jt];
+                    for (int i = 0; i < NI; ++i) {
+                        const int g0 = i >= r0 ? i - r0 : i - r0 + NI;
+                        if (g0 < stages) {
+                            uint32_t u[16];
+                            tmem_ldn<16>(tmem_base + (static_cast<uint32_t>(quarter * 32) << 16) + a * ACC_BUF + i * NTOK + c0, u);
+#pragma unroll
+                            for (int jt = 0; jt < 16; ++jt) v[jt] += u[jt];
+                        }
+                    }
                 }
                 if (c0 + 16 == col0 + EPI_COLS) {  // this group's columns are in registers: hand them back to the MMA warp
                     tc_fence_before();
