@@ -323,12 +323,17 @@ int wf_attn_decode_bf16(const void* q, const void* kcache, const void* vcache, c
  * place, must be called by every rank with the same n and dtype in the same order, sums in rank order in fp32 (all
  * ranks obtain identical bits) and takes WF_FLAG_PDL.  Its waits for the peers are bounded (about 0.1 s); a wait that
  * ran out is reported by wf_ar_status (WF_E_LIMIT) and leaves `out` undefined.
+ * After such a report the ranks no longer agree on the step: wf_ar_step reads this rank's count of completed
+ * all-reduces, and wf_ar_set_step (on every rank, with one common value above every rank's count, e.g. their maximum
+ * + 2, between two host-side barriers and with no all-reduce in flight) puts the group back in step.
  */
 int wf_ar_handle_bytes(void);
 int wf_ar_init(int world, int rank, size_t max_bytes, void** ctx_out, unsigned char* handle_out);
 int wf_ar_connect(void* ctx, const unsigned char* handles);
 int wf_ar_allreduce(void* ctx, const void* in, void* out, int64_t n, int dtype, unsigned flags, void* stream);
 int wf_ar_status(void* ctx, int* out);
+int wf_ar_step(void* ctx, unsigned* out);
+int wf_ar_set_step(void* ctx, unsigned step);
 int wf_ar_destroy(void* ctx);
 
 #ifdef __cplusplus

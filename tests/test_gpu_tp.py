@@ -89,6 +89,28 @@ def _worker(rank, world, port, results):
         dist.all_gather(gathered, y2)
         assert all(torch.equal(gathered[0], t_) for t_ in gathered)  # identical bits on every rank
         ar.status()
+        # ---- a peer that does not take part: the wait runs out after a fraction of a second, the kernel returns, the host
+        # reads the status, the group re-synchronises and the next all-reduce is right again (no fault is provoked: the
+        # waiting kernel polls a flag that nobody sets and gives up)
+        at("bounded wait")
+        dist.barrier()
+        y = torch.ones(4096, dtype=torch.bfloat16, device=dev)
+        if rank == 0:
+            ar(y)  # rank 1 sits this one out
+        torch.cuda.synchronize()
+        timed_out = False
+        try:
+            ar.status()
+        except RuntimeError as e:
+            timed_out = "ran out" in str(e)
+        assert timed_out == (rank == 0), (rank, timed_out)
+        ar.resync()
+        for rep in range(3):
+            y = torch.full((4096,), float(rank + 1 + rep), dtype=torch.bfloat16, device=dev)
+            ar(y)
+            assert torch.equal(y.cpu(), torch.full((4096,), float(sum(r + 1 + rep for r in range(world))), dtype=torch.bfloat16)), rep
+        ar.status()
+        wf.device_status()
         # ---- the decoder: heads, MLP width and the output head sharded over the ranks, against one rank on its own
         from wrinklefree_monorepo_b200.decoder import DecoderConfig, TernaryDecoder
 

@@ -81,6 +81,8 @@ _SIGNATURES = {
     "wf_ar_connect": (_int, [_p, _p]),
     "wf_ar_allreduce": (_int, [_p, _p, _p, _i64, _int, _u32, _p]),
     "wf_ar_status": (_int, [_p, C.POINTER(C.c_int)]),
+    "wf_ar_step": (_int, [_p, C.POINTER(C.c_uint)]),
+    "wf_ar_set_step": (_int, [_p, _u32]),
     "wf_ar_destroy": (_int, [_p]),
     "wf_bitlinear_prefill_batched": (_int, [_p, _int, _i64, _p, _int, _p, _i64, _p, _int, _i64, _p, _i64, _i64, _i64, _i64, _f32,
                                             _p, _sz, _p]),

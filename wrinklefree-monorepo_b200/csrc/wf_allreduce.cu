@@ -243,6 +243,26 @@ extern "C" int wf_ar_status(void* ctx, int* out) {
     return WF_OK;
 }
 
+// this rank's count of completed all-reduces (waits for the device)
+extern "C" int wf_ar_step(void* ctx, unsigned* out) {
+    ArCtx* c = static_cast<ArCtx*>(ctx);
+    WF_REQUIRE(c && out, "wf_ar_step: null pointer");
+    WF_CUDA(cudaDeviceSynchronize());
+    WF_CUDA(cudaMemcpy(out, c->local + 2048, sizeof(unsigned), cudaMemcpyDeviceToHost));
+    return WF_OK;
+}
+
+// Re-synchronisation after a wait that ran out: every rank sets the same step, larger than any flag published so far
+// (flags only grow, so stale flags read as "not yet there"); the ticket and the status word are cleared.
+extern "C" int wf_ar_set_step(void* ctx, unsigned step) {
+    ArCtx* c = static_cast<ArCtx*>(ctx);
+    WF_REQUIRE(c, "wf_ar_set_step: null pointer");
+    WF_CUDA(cudaDeviceSynchronize());
+    const unsigned words[3] = {step, 0u, 0u};  // step | ticket | status
+    WF_CUDA(cudaMemcpy(c->local + 2048, words, sizeof(words), cudaMemcpyHostToDevice));
+    return WF_OK;
+}
+
 extern "C" int wf_ar_destroy(void* ctx) {
     ArCtx* c = static_cast<ArCtx*>(ctx);
     if (!c) return WF_OK;

@@ -89,6 +89,23 @@ class OneShotAllReduce:
             raise RuntimeError("one-shot all-reduce: a wait for a peer ran out (a rank did not take part)")
 
 
+    def resync(self) -> None:
+        """Collective, after `status()` raised on any rank: puts every rank on one common step and clears the status,
+        so that the next all-reduce runs normally.  (A rank that sat out a call is behind the others by one step; the
+        flags of the ranks that waited in vain are ahead of it.)"""
+        import ctypes as C
+
+        if self._ctx is None:
+            return
+        lib = L.lib()
+        v = C.c_uint(0)
+        L.check(lib.wf_ar_step(self._ctx, C.byref(v)), "wf_ar_step")
+        t = torch.tensor([v.value], dtype=torch.int64, device="cuda")
+        dist.all_reduce(t, op=dist.ReduceOp.MAX, group=self.group)  # also: nobody is inside an all-reduce any more
+        L.check(lib.wf_ar_set_step(self._ctx, int(t.item()) + 2), "wf_ar_set_step")
+        dist.barrier(group=self.group)  # nobody launches before every rank has set the step
+
+
 def shard_bounds(total: int, parts: int, align: int) -> List[Tuple[int, int]]:
     """Splits [0, total) into `parts` contiguous ranges whose sizes are multiples of `align`
     and differ by at most one unit (the first ranges take the larger share)."""
