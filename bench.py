@@ -39,10 +39,10 @@ LAYERS = {(2560, 2560): 120, (6912, 2560): 60, (2560, 6912): 30}
 METRIC = "ternary_decode_gemv_GBps"
 GEMM_MIN_M = 16  # token batches from here on run on the tensor-core contraction (one batched launch per layer stack)
 REPEATS = 5      # the --steps region is timed this many times; the median is reported, with min and max
-# DRAM bytes (ncu dram__bytes_read.sum + dram__bytes_write.sum, one capture per stack, one launch) over the algorithmic
-# bytes of the same launch, for the streaming kernel's stacks: (shape index, M) -> ratio.  Stacks without a capture of
-# their own use the mean of the measured ones.
-NCU_TRAFFIC_RATIO = {(0, 1): 1.029, (0, 4): 1.014, (1, 1): 1.013, (1, 4): 1.010, (2, 1): 1.021, (2, 4): 1.018}
+# DRAM bytes (ncu dram__bytes_read.sum + dram__bytes_write.sum of the streaming kernel's four launches of the step, one
+# capture of the bench command itself) over the algorithmic bytes of the same launch: (shape index, M) -> the ratio of
+# the launch that holds the stack.  Stacks without a capture of their own use the mean of the measured ones.
+NCU_TRAFFIC_RATIO = {(0, 1): 1.016, (1, 1): 1.016, (0, 4): 1.007, (1, 4): 1.007, (2, 1): 1.018, (2, 4): 1.018}
 
 
 def algorithmic_bytes(m: int, n: int, k: int) -> int:
@@ -152,15 +152,18 @@ def build_workload(wf, torch, device, rank: int, world: int, layers_scale: float
 
 
 def merge_streaming(wf, groups):
-    """The streaming stacks (M < GEMM_MIN_M) of equal K become ONE grouped launch each: the problems of a grouped launch
-    need not be alike, and what a launch costs beside its bytes (entry to first data, the tail, the hand-over of the SMs
-    to the next launch) is then paid once per K instead of once per stack.  Equal K because the shared-memory plan of a
-    launch is made for its largest K: a 2560-wide stack inside a 6912-wide plan would keep half of its stages."""
-    by_k = {}
+    """The streaming stacks (M < GEMM_MIN_M) of equal K and equal M become ONE grouped launch each: the problems of a
+    grouped launch need not be alike, and what a launch costs beside its bytes (entry to first data, the tail, the
+    hand-over of the SMs to the next launch) is then paid once per launch instead of once per stack.
+    Equal K because the shared-memory plan of a launch is made for its largest K (a 2560-wide stack inside a 6912-wide
+    plan would keep half of its stages); equal M so that no weight matrix occurs twice in a launch: the M = 1 and M = 4
+    stacks of a shape hold the same weights, and a launch over both found 39 % of its bytes in L2 (ncu: 569 MB of DRAM
+    reads for 936 MB of algorithmic bytes), which is not the streaming case this bench is about."""
+    by_key = {}
     for g in groups:
         if not g["batched"]:
-            by_k.setdefault(g["k"], []).append(g)
-    for members in by_k.values():
+            by_key.setdefault((g["k"], g["m"]), []).append(g)
+    for members in by_key.values():
         if len(members) < 2:
             continue
         probs = [dict(x=m["x"][li], codes=c, w_scale=s_, out=m["y"][li]) for m in members for li, (c, s_) in enumerate(m["layers"])]
@@ -623,7 +626,7 @@ def main():
     ap.add_argument("--only-m", type=int, default=0, help="restrict the sweep to one token batch (profiling)")
     ap.add_argument("--only-shape", type=int, default=-1, help="restrict the sweep to one shape index (profiling)")
     ap.add_argument("--no-cpu-baseline", action="store_true")
-    ap.add_argument("--no-merge", action="store_true", help="one grouped launch per (shape, M) stack instead of one per K")
+    ap.add_argument("--no-merge", action="store_true", help="one grouped launch per (shape, M) stack instead of one per (K, M)")
     args = ap.parse_args()
     rank = int(os.environ.get("RANK", "0"))
     world = int(os.environ.get("WORLD_SIZE", "1"))
@@ -913,12 +916,12 @@ def main():
             "launch": {"pdl": pdl, "graph": True, "parallelism": f"tp{world}" if world > 1 else "single"},
             "roofline": {"bound": "hbm", "achieved": achieved, "peak": peaks["hbm_gbs"], "unit": "GB/s",
                          "frac": achieved / peaks["hbm_gbs"], "frac_of_nominal_8000": achieved / 8000.0, "traffic": traffic,
-                         "traffic_source": "ncu dram__bytes_read.sum + dram__bytes_write.sum of one launch per stack, as a ratio to the "
+                         "traffic_source": "ncu dram__bytes_read.sum + dram__bytes_write.sum of the step's streaming launches, as a ratio to the "
                                            "algorithmic bytes: " + ", ".join(f"shape {k_[0]} M={k_[1]}: {v_:.3f}" for k_, v_ in sorted(NCU_TRAFFIC_RATIO.items())) +
                                            "; other stacks: their mean",
                          "peak_kind": peak_kind + " copy bandwidth",
                          "kernel": "decode_stream_kernel", "launches": f"the {dec_launches} grouped launches of the step that hold its {len(dec_groups)} stacks with M < {GEMM_MIN_M}"
-                                     + (" (stacks of equal K share a launch)" if dec_launches < len(dec_groups) else ""),
+                                     + (" (stacks of equal K and M share a launch)" if dec_launches < len(dec_groups) else ""),
                          "bytes_per_launch": per_launch_bytes, "us_per_launch": per_launch_us},
             "e2e": {"value": full_bytes / (ms_e2e * 1e-3) / 1e9, "unit": "GB/s", "h2d_bytes_per_step": h2d,
                     "d2h_bytes_per_step": d2h, "ms_per_step": ms_e2e, "ms_per_step_repeats": med(e2e_all),
