@@ -314,6 +314,16 @@ int wf_attn_decode_bf16(const void* q, const void* kcache, const void* vcache, c
                         int nkv, int D, int T, float scale, void* workspace, size_t workspace_bytes, unsigned flags, void* stream);
 
 /*
+ * Dense bf16 linear layer: y[M, N] = x[M, K] . w[N, K]^T, bf16 operands (row strides ldx, ldw in elements, multiples
+ * of 8; x and w 16-byte aligned; K a multiple of 8), fp32 accumulation on the tensor cores, y of y_dtype (WF_F32 /
+ * WF_BF16 / WF_F16, row stride ldy).  It is the output head of the ternary decoder, the one matrix the reference keeps
+ * in full precision (nn.Linear lm_head of BitNetLlama, packages/training/src/wrinklefree/models/llama.py:53,140; F.linear in
+ * the serving runtime): one pass over w serves up to 256 tokens.  Takes WF_FLAG_PDL.
+ */
+int wf_linear_bf16(const void* x, int64_t ldx, const void* w, int64_t ldw, void* y, int y_dtype, int64_t ldy, int64_t M,
+                   int64_t N, int64_t K, unsigned flags, void* stream);
+
+/*
  * One-shot all-reduce (sum) over peer memory for the small tensors that follow a row-parallel projection in the
  * decode step; one process per GPU on one node.  It stands where the reference's tensor-parallel layers call the
  * library all-reduce after o_proj / down_proj (sglang/srt/layers/linear.py:1419-1420); larger tensors stay on NCCL.

@@ -289,3 +289,41 @@ def test_fused_decode_step_equals_unfused(wf):
     assert err <= 2e-2, err
     assert (outs[0].argmax(-1) == outs[1].argmax(-1)).float().mean() >= 0.9
     wf.device_status()
+
+
+@pytest.mark.parametrize("m,n,k", [(1, 1000, 576), (3, 130, 72), (32, 5000, 4096), (256, 3000, 4096), (300, 1100, 1024), (17, 128, 8)])
+@pytest.mark.parametrize("out_dtype", [torch.bfloat16, torch.float32])
+def test_linear_bf16_output_head(wf, m, n, k, out_dtype):
+    """The bf16 linear kernel (the decoder's output head) against an fp32 matmul of the same bf16 operands: the products
+    are exact in fp32, only the order of the fp32 additions differs (tolerance 1e-3 of the largest output for f32, one
+    bf16 rounding step more for bf16 outputs); row tails, token tails, K tails, more than 256 tokens."""
+    dev = torch.device("cuda", 0)
+    g = torch.Generator(device=dev).manual_seed(m * 1000 + n + k)
+    x = torch.randn(m, k, generator=g, device=dev).bfloat16()
+    w = (torch.randn(n, k, generator=g, device=dev) * 0.05).bfloat16()
+    ref = x.float() @ w.float().t()
+    y = wf.linear_bf16(x, w, out_dtype=out_dtype)
+    assert y.shape == (m, n) and y.dtype == out_dtype
+    tol = 1e-3 if out_dtype == torch.float32 else 1e-2
+    err = float((y.float() - ref).abs().max() / ref.abs().max())
+    assert err < tol, err
+    # strided views: rows of a wider buffer on both sides, and into a wider output
+    if k >= 64:
+        xw = torch.zeros(m, k + 16, dtype=torch.bfloat16, device=dev)
+        xw[:, :k] = x
+        ww = torch.zeros(n, k + 8, dtype=torch.bfloat16, device=dev)
+        ww[:, :k] = w
+        out = torch.full((m, n + 5), 7.0, dtype=out_dtype, device=dev)
+        wf.linear_bf16(xw[:, :k], ww[:, :k], out=out[:, :n])
+        assert torch.equal(out[:, :n], y) and bool((out[:, n:] == 7.0).all())
+    wf.device_status()
+
+
+def test_linear_bf16_rejects_what_it_cannot_run(wf):
+    dev = torch.device("cuda", 0)
+    x = torch.zeros(2, 64, dtype=torch.bfloat16, device=dev)
+    w = torch.zeros(8, 64, dtype=torch.bfloat16, device=dev)
+    with pytest.raises(ValueError):
+        wf.linear_bf16(x.float(), w)
+    with pytest.raises(RuntimeError):
+        wf.linear_bf16(x[:, :60], w[:, :60])  # K not a multiple of 8

@@ -37,6 +37,7 @@ from .ops import (  # noqa: F401
     bitnet_gemm,
     bitnet_gemv,
     check_kernel_available,
+    linear_bf16,
     pack_codes,
     pack_ternary,
     quantize_activations_i8,

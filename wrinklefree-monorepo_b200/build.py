@@ -9,7 +9,7 @@ HERE = os.path.dirname(os.path.abspath(__file__))
 CSRC = os.path.join(HERE, "csrc")
 LIB = os.path.join(HERE, "libwf_b200.so")
 SOURCES = ["wf_capi.cu", "wf_pack.cu", "wf_actquant.cu", "wf_decode.cu", "wf_prefill.cu", "wf_elementwise.cu",
-           "wf_allreduce.cu", "wf_probe.cu", "wf_attention.cu"]
+           "wf_allreduce.cu", "wf_probe.cu", "wf_attention.cu", "wf_linear.cu"]
 NVCC_FLAGS = [
     "-O3", "-std=c++17", "-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo",
     "-Xcompiler", "-fPIC",

@@ -1539,6 +1539,7 @@ extern "C" int wf_bitlinear_decode_grouped(const wf_problem* dev_problems, const
 }
 
 extern "C" int wf_prefill_status_fetch(int* out);
+extern "C" int wf_linear_status_fetch(int* out);
 
 extern "C" int wf_device_status(void) {
     if (int rc = require_device()) return rc;
@@ -1546,6 +1547,8 @@ extern "C" int wf_device_status(void) {
     int v = 0, v2 = 0;
     if (int rc = wf_prefill_status_fetch(&v2)) return rc;
     if (v2) return fail(v2, "a bounded wait inside the prefill kernel ran out; the outputs of that launch are invalid");
+    if (int rc = wf_linear_status_fetch(&v2)) return rc;
+    if (v2) return fail(v2, "a bounded wait inside the bf16 linear kernel ran out; the outputs of that launch are invalid");
     WF_CUDA(cudaMemcpyFromSymbol(&v, g_decode_status, sizeof(int)));
     if (v) {
         int zero = 0;

@@ -193,6 +193,7 @@ class TernaryDecoder:
         self.h = torch.empty(B, cfg.hidden, dtype=dt, device=dev)
         self.h2 = torch.empty(B, cfg.hidden, dtype=dt, device=dev)
         self.xf = torch.empty(B, cfg.hidden, dtype=dt, device=dev)
+        self.head_out = torch.empty(B, self.lm_head.shape[0], dtype=dt, device=dev) if dt == torch.bfloat16 else None
         mode = "silu" if cfg.act == "silu" else "relu2"
         prev_down = None
         for li, L in enumerate(self.layers):
@@ -282,8 +283,15 @@ class TernaryDecoder:
                 act = ops.add_rmsnorm_(act, None, L["sf"], L["actn"], cfg.subln_eps, pdl=True)
             delta = self._allreduce(ops.bitlinear(act, L["down"][0], L["down"][1], out=L["db"], path=path, pdl=True))
         ops.add_rmsnorm_(self.h, delta, self.norm_f, self.xf, cfg.eps, pdl=True)
-        self._greedy(self.xf @ self.lm_head.t())
+        self._greedy(self._head(self.xf, self.head_out, pdl=True))
         self.pos.add_(1)
+
+    def _head(self, x, out=None, pdl=False):
+        """This rank's rows of the output head: a kernel of this library for bf16, the framework's matmul for the fp32
+        model that the parity tests hold against the reference."""
+        if x.dtype == torch.bfloat16 and self.lm_head.dtype == torch.bfloat16:
+            return ops.linear_bf16(x, self.lm_head, out=out, pdl=pdl)
+        return x @ self.lm_head.t()
 
     def _greedy(self, logits):
         """next_tok = argmax over the vocabulary; `logits` are this rank's rows of the head."""
@@ -317,7 +325,7 @@ class TernaryDecoder:
             L["g_down"].run(pdl=True)
             self._allreduce(L["db"])
         ops.add_rmsnorm_(self.h, self.layers[-1]["db"], self.norm_f, self.xf, cfg.eps, pdl=True)
-        self._greedy(self.xf @ self.lm_head.t())
+        self._greedy(self._head(self.xf, self.head_out, pdl=True))
         self.pos.add_(1)
 
     # ------------------------------------------------------------------ public
@@ -351,7 +359,7 @@ class TernaryDecoder:
                 act = _rms_norm(act, L["sf"], cfg.subln_eps)
             dn = self._allreduce(ops.bitlinear(act, *L["down"]))
             x = x + dn.view(B, S, cfg.hidden)
-        logits = _rms_norm(x if all_logits else x[:, -1], self.norm_f, cfg.eps) @ self.lm_head.t()
+        logits = self._head(_rms_norm(x if all_logits else x[:, -1], self.norm_f, cfg.eps))
         if self.tp > 1:  # the prompt pass returns the full rows
             parts = [torch.empty(*logits.shape[:-1], hi - lo, dtype=logits.dtype, device=logits.device)
                      for lo, hi in tpmod.shard_bounds(cfg.vocab, self.tp, 1)]

@@ -422,6 +422,31 @@ def attn_decode(q: torch.Tensor, kcache: torch.Tensor, vcache: torch.Tensor, pos
     return out
 
 
+def linear_bf16(x: torch.Tensor, weight: torch.Tensor, out: Optional[torch.Tensor] = None, out_dtype: Optional[torch.dtype] = None,
+                pdl: bool = False) -> torch.Tensor:
+    """y = x @ weight.T for bf16 x [..., K] and weight [N, K] (fp32 accumulation on the tensor cores): the output head of
+    the decoder, the one matrix the reference keeps in full precision.  `out` [..., N] of bf16 / f16 / f32 (default: bf16)."""
+    _need_cuda(x, weight, out)
+    k = x.shape[-1]
+    x2 = x.reshape(-1, k)
+    if x.dtype != torch.bfloat16 or weight.dtype != torch.bfloat16 or weight.dim() != 2 or weight.shape[1] != k:
+        raise ValueError("linear_bf16 needs bf16 x [..., K] and weight [N, K]")
+    if x2.stride(1) != 1:
+        x2 = x2.contiguous()
+    if weight.stride(1) != 1:
+        raise ValueError("linear_bf16 needs weight rows with unit stride")
+    m, n = x2.shape[0], weight.shape[0]
+    if out is None:
+        out = torch.empty(*x.shape[:-1], n, dtype=out_dtype or torch.bfloat16, device=x.device)
+    y2 = out.view(-1, n) if out.dim() != 2 else out
+    if y2.shape[0] != m or y2.stride(1) != 1 or out.dtype not in (torch.bfloat16, torch.float16, torch.float32):
+        raise ValueError("linear_bf16: `out` must be [..., N] of bf16, f16 or f32 with unit inner stride")
+    with torch.cuda.device(x.device):
+        L.check(L.lib().wf_linear_bf16(x2.data_ptr(), x2.stride(0), weight.data_ptr(), weight.stride(0), y2.data_ptr(), _DT[out.dtype],
+                                       y2.stride(0), m, n, k, L.FLAG_PDL if pdl else 0, _stream()), "wf_linear_bf16")
+    return out
+
+
 def act_mul(gate: torch.Tensor, up: torch.Tensor, out: torch.Tensor, mode: str = "silu", pdl: bool = False):
     """out = act(gate) * up (bf16); mode "silu" or "relu2"."""
     _need_cuda(gate, up, out)
