@@ -66,9 +66,10 @@ extern "C" {
                               Ignored by the other forms.  No counterpart in the reference (its CPU operators are
                               synchronous calls). */
 
-#define WF_FLAG_PREFILL_PAIR 4u   /* wf_bitlinear_prefill, more than 64 tokens: force the form in which two CTAs (a cluster of two
-                                     SMs, tcgen05 cta_group::2) share each 256-row x 192-token tile; default: chosen by tile count */
-#define WF_FLAG_PREFILL_SINGLE 8u /* ... force the form with one CTA per 128-row x 128-token tile */
+#define WF_FLAG_PREFILL_PAIR 4u   /* wf_bitlinear_prefill, more than 64 tokens: use the form in which two CTAs (a cluster of two
+                                     SMs, tcgen05 cta_group::2) share each 256-row x 192-token tile (half the token bytes from
+                                     L2 per multiply-add; measured slower than the default on B200) */
+#define WF_FLAG_PREFILL_SINGLE 8u /* ... the form with one CTA per 128-row x 128-token tile (the default) */
 
 int wf_version(void);
 const char* wf_last_error(void);

@@ -497,20 +497,22 @@ __global__ void __launch_bounds__(sm_threads<NTOK>(), 1)
 // (cluster rank 0) issues the MMAs of the pair and commits with a cluster multicast so that both CTAs see their
 // buffers released; warps 10-13 and 15-18 epilogue of the CTA's own 128 rows x PR_N tokens.  Barriers that gather
 // arrivals of both CTAs (token tile full, expanded weights ready, accumulator drained) live in the leader.
-// Tensor memory: two accumulators of PR_N columns + 128 columns of expanded weights (PR_AS stages) = 512 columns.
+// Tensor memory: two accumulators of PR_N columns + a ring of PR_AS stages of expanded weights (256 K each) = 512 columns.
 constexpr int PR_N = 192;                 // tokens per tile (the N of the MMA); a multiple of 32
 constexpr int PR_HALF = PR_N / 2;         // tokens each CTA loads
 constexpr int PR_PS = 4;                  // packed-weight stages (128 rows x 128 B = 16 KB, 512 K each)
 constexpr int PR_XS = 3;                  // token stages (4 atoms of PR_HALF x 128 B = 48 KB, 512 K each: two tensor-memory stages)
 constexpr int PR_AA = 2;                  // 128-byte atoms of K per tensor-memory stage (128 K each)
-constexpr int PR_AS = 4 / PR_AA;          // tensor-memory stages of expanded weights: 128 columns in all
-constexpr int PR_X_ATOM = PR_HALF * SM_BK;
-constexpr int PR_X_BYTES = 4 * PR_X_ATOM;
+constexpr int PR_PARTS = 4 / PR_AA;       // tensor-memory stages that one packed stage (512 K) feeds
 constexpr int PR_A_COLS = 32 * PR_AA;
 constexpr int PR_ACC_COLS = 2 * PR_N;
+constexpr int PR_AS = (512 - PR_ACC_COLS) / PR_A_COLS;  // ring of tensor-memory stages of expanded weights: what the accumulators leave
+constexpr int PR_X_ATOM = PR_HALF * SM_BK;
+constexpr int PR_X_BYTES = 4 * PR_X_ATOM;
 constexpr size_t PR_SMEM = 1024 + PR_PS * SM_P_BYTES + PR_XS * PR_X_BYTES + 4096;
 static_assert(PR_SMEM <= 227 * 1024, "shared memory of the pair form");
-static_assert(PR_ACC_COLS + PR_AS * PR_A_COLS <= 512 && PR_N % 32 == 0 && PR_X_ATOM % 1024 == 0, "tensor memory / tile shape of the pair form");
+static_assert(PR_ACC_COLS + PR_AS * PR_A_COLS <= 512 && PR_N % 32 == 0 && PR_X_ATOM % 1024 == 0 && PR_AS % PR_PARTS == 0 && PR_PARTS == 2,
+              "tensor memory / tile shape of the pair form");
 
 __device__ __forceinline__ uint32_t cluster_rank() {
     uint32_t r;
@@ -583,7 +585,7 @@ __global__ void __launch_bounds__(SM_THREADS, 1)
     // K is walked in packed stages of 512 and tensor-memory stages of 256; a stage that reaches past K is zero-filled by
     // the TMA unit on both operands.  Every tile runs an even number of tensor-memory stages, so a stage's half of its
     // packed stage and its expansion group are fixed by the parity of the running stage counter.
-    const int pstages = (p.K + 511) / 512, astages = PR_AS * pstages;
+    const int pstages = (p.K + 511) / 512, astages = PR_PARTS * pstages;
     const int tiles_per_problem = p.tiles_m * p.tiles_n;  // token blocks of PR_N x row blocks of 256; row blocks vary fastest
     const int total_tiles = tiles_per_problem * p.batch;
 
@@ -666,8 +668,8 @@ __global__ void __launch_bounds__(SM_THREADS, 1)
                 tc_fence_after();
                 const uint32_t d_tmem = tmem_base + a * PR_N;
                 for (int g = 0; g < astages; ++g, ++sit) {
-                    // token stage = packed stage = PR_AS tensor-memory stages; `part` = which of them
-                    const int xsit = sit / PR_AS, xs = xsit % PR_XS, part = sit % PR_AS, as = part;
+                    // token stage = packed stage = PR_PARTS tensor-memory stages; `part` = which of them
+                    const int xsit = sit / PR_PARTS, xs = xsit % PR_XS, part = sit % PR_PARTS, as = sit % PR_AS;
                     if (part == 0) mbar_wait(&x_full[xs], (xsit / PR_XS) & 1, poisoned);
                     mbar_wait(&a_full[as], (sit / PR_AS) & 1, poisoned);
                     tc_fence_after();
@@ -676,7 +678,7 @@ __global__ void __launch_bounds__(SM_THREADS, 1)
                     for (int ss = 0; ss < PR_XS; ++ss) {
                         if (ss == xs) {
 #pragma unroll
-                            for (int pp = 0; pp < PR_AS; ++pp) {
+                            for (int pp = 0; pp < PR_PARTS; ++pp) {
                                 if (pp == part) {
 #pragma unroll
                                     for (int j = 0; j < PR_AA; ++j)
@@ -686,7 +688,7 @@ __global__ void __launch_bounds__(SM_THREADS, 1)
                         }
                     }
                     tc_commit_pair(&a_free[as]);
-                    if (part == PR_AS - 1) tc_commit_pair(&x_free[xs]);  // the whole token stage has been consumed
+                    if (part == PR_PARTS - 1) tc_commit_pair(&x_free[xs]);  // the whole token stage has been consumed
                 }
                 tc_commit_pair(&acc_full[a]);
             }
@@ -700,7 +702,7 @@ __global__ void __launch_bounds__(SM_THREADS, 1)
         int sit = grp;  // this group's tensor-memory stages: grp, grp + 2, ...
         for (int t = cluster_id; t < total_tiles; t += n_clusters) {
             for (int g = grp; g < astages; g += 2, sit += 2) {
-                const int psit = sit / PR_AS, ps = psit % PR_PS, part = sit % PR_AS, as = part;
+                const int psit = sit / PR_PARTS, ps = psit % PR_PS, part = sit % PR_PARTS, as = sit % PR_AS;
                 mbar_wait(&p_full[ps], (psit / PR_PS) & 1, poisoned);
                 // The packed bytes are expanded into registers BEFORE the tensor-memory stage is known to be free: what
                 // remains between "the MMAs of the previous use have completed" and "the next MMAs may start" is the
@@ -730,7 +732,7 @@ __global__ void __launch_bounds__(SM_THREADS, 1)
                 }
                 __syncwarp();
                 // this group's last part of the packed stage: its rows are in registers
-                if (lane == 0 && part + 2 >= PR_AS) mbar_arrive(&p_empty[ps]);
+                if (lane == 0 && part + 2 >= PR_PARTS) mbar_arrive(&p_empty[ps]);
                 if (sit >= PR_AS) mbar_wait(&a_free[as], ((sit / PR_AS) - 1) & 1, poisoned);
                 tc_fence_after();
                 const uint32_t dst = tmem_a + as * PR_A_COLS + (static_cast<uint32_t>(quarter * 32) << 16);
@@ -924,17 +926,12 @@ static int prefill_impl(const char* who, const void* x, int x_dtype, int64_t ldx
     if (!enc) return fail(WF_E_DEVICE, "cuTensorMapEncodeTiled is not available in this driver");
     const int ntok = M_one <= 16 ? 16 : (M_one <= 32 ? 32 : (M_one <= 64 ? 64 : 128));
     const int sms = num_sms();
-    // Pair form (two CTAs per 256 x PR_N tile) or single form (one CTA per 128 x 128 tile)?  Measured on B200 the two
-    // forms run at the same rate per multiply-add (the pair form pulls half the bytes from L2, the single form has the
-    // deeper pipeline), so the choice follows the tile quantisation: estimated time = waves of tiles x work per SM and tile.
+    // Single form (one CTA per 128 x 128 tile) unless the caller asks for the pair form (two CTAs per 256 x PR_N tile):
+    // measured on B200 at M = 512 ... 8192 on the three sweep shapes the single form is the faster one everywhere
+    // (1.41 / 1.68 / 2.13 POPS against 1.22 / 1.58 / 1.79 at M = 8192; a pair tile of 128 tokens with a ring of four
+    // tensor-memory stages was slower still), although the pair form pulls half the token bytes from L2.
     bool pair = false;
-    if (ntok == 128) {
-        const long long t1 = ((M_one + 127) / 128) * ((N + 127) / 128) * batch, w1 = (t1 + sms - 1) / sms;
-        const long long t2 = ((M_one + PR_N - 1) / PR_N) * ((N + 255) / 256) * batch, w2 = (t2 + sms / 2 - 1) / (sms / 2);
-        pair = sms >= 2 && w2 * PR_N < w1 * 128;
-        if (flags & WF_FLAG_PREFILL_PAIR) pair = sms >= 2;
-        if (flags & WF_FLAG_PREFILL_SINGLE) pair = false;
-    }
+    if (ntok == 128 && (flags & WF_FLAG_PREFILL_PAIR) && !(flags & WF_FLAG_PREFILL_SINGLE)) pair = sms >= 2;
     alignas(64) CUtensorMap tmap_a, tmap_p;
     const cuuint32_t ones[2] = {1, 1};
     {
