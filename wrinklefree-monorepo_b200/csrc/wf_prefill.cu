@@ -164,6 +164,42 @@ __device__ __forceinline__ void tmem_ldn<16>(uint32_t addr, uint32_t (&v)[16]) {
     asm volatile("tcgen05.wait::ld.sync.aligned;\n" ::: "memory");
 }
 
+// Sixteen token columns of one weight row: integer correction, fp32 rescale, 16-bit store.  The per-token constants come
+// as vectors from shared memory, the output type is decided outside the loops and the pointer runs along the token axis:
+// the epilogue warps share their schedulers with the expansion warps, and at 2560-wide K a tile's epilogue (128 x 128
+// outputs) used to take longer than its MMAs.
+__device__ __forceinline__ void epilogue16(const uint32_t (&v)[16], const int* s_rowsum, const float* s_inv, float s_w, bool has_bias,
+                                           float bias, bool is_bf16, uint16_t* yp, int64_t ldy, int valid) {
+    int rs[16];
+    float iv[16];
+#pragma unroll
+    for (int q = 0; q < 4; ++q) {
+        const int4 a = *reinterpret_cast<const int4*>(s_rowsum + 4 * q);
+        const float4 b = *reinterpret_cast<const float4*>(s_inv + 4 * q);
+        rs[4 * q] = a.x; rs[4 * q + 1] = a.y; rs[4 * q + 2] = a.z; rs[4 * q + 3] = a.w;
+        iv[4 * q] = b.x; iv[4 * q + 1] = b.y; iv[4 * q + 2] = b.z; iv[4 * q + 3] = b.w;
+    }
+    float o[16];
+#pragma unroll
+    for (int jt = 0; jt < 16; ++jt) {
+        o[jt] = rescale(static_cast<int>(v[jt]) - rs[jt], iv[jt], s_w);
+        if (has_bias) o[jt] = __fadd_rn(o[jt], bias);
+    }
+    if (valid >= 16) {
+        if (is_bf16) {
+#pragma unroll
+            for (int jt = 0; jt < 16; ++jt, yp += ldy) *yp = __bfloat16_as_ushort(__float2bfloat16_rn(o[jt]));
+        } else {
+#pragma unroll
+            for (int jt = 0; jt < 16; ++jt, yp += ldy) *yp = __half_as_ushort(__float2half_rn(o[jt]));
+        }
+    } else {
+#pragma unroll
+        for (int jt = 0; jt < 16; ++jt, yp += ldy)
+            if (jt < valid) *yp = is_bf16 ? __bfloat16_as_ushort(__float2bfloat16_rn(o[jt])) : __half_as_ushort(__float2half_rn(o[jt]));
+    }
+}
+
 template <int NTOK>
 __global__ void __launch_bounds__(sm_threads<NTOK>(), 1)
     prefill_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_constant__ CUtensorMap tmap_p, const PrefillParams p) {
@@ -188,7 +224,8 @@ __global__ void __launch_bounds__(sm_threads<NTOK>(), 1)
     uint64_t* acc_empty = acc_full + 2;
     uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(acc_empty + 2);
     volatile int* poisoned = reinterpret_cast<volatile int*>(tmem_slot + 1);
-    int* s_rowsum = reinterpret_cast<int*>(tmem_slot + 2);   // [NTOK] per-token constants of the epilogue's current token block
+    // [NTOK] per-token constants of the epilogue's current token block, read as 16-byte vectors
+    int* s_rowsum = reinterpret_cast<int*>((reinterpret_cast<uintptr_t>(tmem_slot + 2) + 15) & ~static_cast<uintptr_t>(15));
     float* s_inv = reinterpret_cast<float*>(s_rowsum + 128);  // [NTOK]
 
     // chained with a programmatic dependency: the packed weights never depend on the previous kernel (normally the
@@ -448,16 +485,7 @@ __global__ void __launch_bounds__(sm_threads<NTOK>(), 1)
                 }
                 if (!row_ok) continue;
                 if (fast16) {
-#pragma unroll
-                    for (int jt = 0; jt < 16; ++jt) {
-                        const int tok_in = c0 + jt;
-                        if (tok_in < mtok) {
-                            float o = rescale(static_cast<int>(v[jt]) - s_rowsum[tok_in], s_inv[tok_in], s_w);
-                            if (has_bias) o = __fadd_rn(o, bias);
-                            const uint16_t bits = is_bf16 ? __bfloat16_as_ushort(__float2bfloat16_rn(o)) : __half_as_ushort(__float2half_rn(o));
-                            y16[tok_in * p.ldy] = bits;
-                        }
-                    }
+                    epilogue16(v, s_rowsum + c0, s_inv + c0, s_w, has_bias, bias, is_bf16, y16 + static_cast<int64_t>(c0) * p.ldy, p.ldy, mtok - c0);
                 } else {
 #pragma unroll
                     for (int jt = 0; jt < 16; ++jt) {
@@ -575,7 +603,8 @@ __global__ void __launch_bounds__(SM_THREADS, 1)
     uint64_t* acc_empty = acc_full + 2;       // leader's copy: the epilogue warps of both CTAs
     uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(acc_empty + 2);
     volatile int* poisoned = reinterpret_cast<volatile int*>(tmem_slot + 1);
-    int* s_rowsum = reinterpret_cast<int*>(tmem_slot + 2);   // [PR_N] per-token constants of the epilogue's current token block
+    // [PR_N] per-token constants of the epilogue's current token block, read as 16-byte vectors
+    int* s_rowsum = reinterpret_cast<int*>((reinterpret_cast<uintptr_t>(tmem_slot + 2) + 15) & ~static_cast<uintptr_t>(15));
     float* s_inv = reinterpret_cast<float*>(s_rowsum + 256);  // [PR_N]
 
     asm volatile("griddepcontrol.launch_dependents;\n" ::: "memory");
@@ -791,16 +820,7 @@ __global__ void __launch_bounds__(SM_THREADS, 1)
                 }
                 if (!row_ok) continue;
                 if (fast16) {
-#pragma unroll
-                    for (int jt = 0; jt < 16; ++jt) {
-                        const int tok_in = c0 + jt;
-                        if (tok_in < mtok) {
-                            float o = rescale(static_cast<int>(v[jt]) - s_rowsum[tok_in], s_inv[tok_in], s_w);
-                            if (has_bias) o = __fadd_rn(o, bias);
-                            const uint16_t bits = is_bf16 ? __bfloat16_as_ushort(__float2bfloat16_rn(o)) : __half_as_ushort(__float2half_rn(o));
-                            y16[tok_in * p.ldy] = bits;
-                        }
-                    }
+                    epilogue16(v, s_rowsum + c0, s_inv + c0, s_w, has_bias, bias, is_bf16, y16 + static_cast<int64_t>(c0) * p.ldy, p.ldy, mtok - c0);
                 } else {
 #pragma unroll
                     for (int jt = 0; jt < 16; ++jt) {
