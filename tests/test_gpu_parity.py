@@ -141,6 +141,28 @@ def test_act_quant_edge_cases(wf):
         assert np.array_equal(q.cpu().numpy(), qo) and np.array_equal(s.cpu().numpy(), so)
 
 
+@pytest.mark.parametrize("k", [72, 2560, 6912, 16384])
+@pytest.mark.parametrize("dt", ["f32", "bf16", "f16"])
+def test_act_quant_many_tokens(wf, k, dt):
+    """A few hundred tokens of the widths the sweep uses (and one beyond): codes, multipliers and row sums equal the
+    oracle's, outliers, an all-zero token and a strided view included."""
+    g = torch.Generator().manual_seed(k)
+    m = 203
+    x = gi.with_outliers(torch.randn(m, k, generator=g), seed=k)
+    x[5] = 0
+    x[6] *= 1e-6
+    xd = x.to(TDT[dt])
+    q, s, rs = wf.act_quant_i8(xd.to(DEV), want_rowsum=True)
+    qo, so = O.act_quant_per_token(xd.float().numpy(), dt)
+    assert np.array_equal(q.cpu().numpy(), qo) and np.array_equal(s.cpu().numpy(), so)
+    assert np.array_equal(rs.cpu().numpy(), qo.astype(np.int32).sum(1))
+    # a strided view: rows of a wider buffer
+    wide = torch.zeros(m, k + 24, dtype=TDT[dt])
+    wide[:, :k] = xd
+    q2, s2 = wf.act_quant_i8(wide.to(DEV)[:, :k])
+    assert torch.equal(q2, q) and torch.equal(s2, s)
+
+
 # ---------------------------------------------------------------- contraction
 @pytest.mark.parametrize("name", list(gi.CASES))
 @pytest.mark.parametrize("dt", ["f32", "bf16", "f16"])
