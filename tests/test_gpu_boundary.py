@@ -164,3 +164,26 @@ def test_prefill_full_size_against_oracle(wf, oracle_c, n, k, m, form):
     inv = (1.0 / torch.from_numpy(s).to(DEV)).unsqueeze(1)
     assert torch.equal(y, ((acc.float() * inv) * scale[0]).bfloat16())
     wf.device_status()
+
+
+def test_weight_only_variant_on_the_bf16_kernel(wf):
+    """BitLinearNoActivationQuant at inference: this library's bf16 kernel on the cached quantized weight against the
+    reference's formula evaluated by torch (same bf16 operands; the sums differ in order only), the cache follows the weight."""
+    torch.manual_seed(3)
+    layer = wf.BitLinearNoActivationQuant(576, 200, bias=True).to(DEV)
+    x = torch.randn(5, 7, 576, device=DEV).bfloat16()
+    with torch.no_grad():
+        y = layer(x)
+        w = layer.weight.to(torch.bfloat16)
+        ref = torch.nn.functional.linear(x.float(), layer.weight_quant(w).float(), layer.bias.float())
+    assert y.shape == (5, 7, 200) and y.dtype == torch.bfloat16
+    assert float((y.float() - ref).abs().max() / ref.abs().max()) < 1e-2
+    with torch.no_grad():
+        layer.weight.mul_(-1.0)  # an in-place update is seen through the version counter
+        y2 = layer(x)
+    ref2 = torch.nn.functional.linear(x.float(), layer.weight_quant(layer.weight.to(torch.bfloat16)).float(), layer.bias.float())
+    assert float((y2.float() - ref2).abs().max() / ref2.abs().max()) < 1e-2
+    # with a gradient needed the torch formula runs and gradients flow to the weight
+    xg = x.clone().requires_grad_(True)
+    layer(xg).float().sum().backward()
+    assert layer.weight.grad is not None and xg.grad is not None

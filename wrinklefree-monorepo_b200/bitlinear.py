@@ -129,18 +129,42 @@ class BitLinear(nn.Linear):
 
 
 class BitLinearNoActivationQuant(nn.Linear):
-    """Weight-only variant (wrinklefree/models/bitlinear.py:116-151); torch formula only."""
+    """Weight-only variant (wrinklefree/models/bitlinear.py:116-151): ternary weights, activations as they are.
+    Inference on bf16 CUDA tensors at lambda == 1 runs this library's bf16 tensor-core kernel on the quantized weight,
+    which is computed once by the reference's own formula (in bf16, like the reference's forward) and kept until the
+    weight changes; everything else evaluates the formula with torch operators."""
 
     def __init__(self, in_features: int, out_features: int, bias: bool = False, eps: float = 1e-5):
         super().__init__(in_features, out_features, bias=bias)
         self.eps = eps
+        self._wq = None  # (key, quantized weight in bf16)
 
     def weight_quant(self, w: torch.Tensor) -> torch.Tensor:
         scale = 1.0 / w.abs().mean().clamp(min=self.eps)
         return (w * scale).round().clamp(-1, 1) / scale
 
+    def invalidate_packed(self) -> None:
+        """Drops the cached quantized weight (after writes through `.data`; `load_state_dict` calls it)."""
+        self._wq = None
+
+    def _load_from_state_dict(self, *args, **kwargs):
+        super()._load_from_state_dict(*args, **kwargs)
+        self.invalidate_packed()
+
+    def quantized_weight(self) -> torch.Tensor:
+        key = (self.weight._version, self.weight.data_ptr(), self.weight.device)
+        if self._wq is None or self._wq[0] != key:
+            with torch.no_grad():
+                self._wq = (key, self.weight_quant(self.weight.detach().to(torch.bfloat16)).contiguous())
+        return self._wq[1]
+
     def forward(self, x: torch.Tensor) -> torch.Tensor:
         lam = get_current_lambda()
+        needs_grad = torch.is_grad_enabled() and (x.requires_grad or self.weight.requires_grad
+                                                  or (self.bias is not None and self.bias.requires_grad))
+        if (lam == 1.0 and not needs_grad and x.is_cuda and x.dtype == torch.bfloat16 and self.in_features % 8 == 0):
+            y = ops.linear_bf16(x, self.quantized_weight())
+            return y if self.bias is None else y + self.bias.to(x.dtype)
         w = self.weight.to(x.dtype)
         w_quant = w + lam * (self.weight_quant(w) - w).detach()
         bias = self.bias.to(x.dtype) if self.bias is not None else None
