@@ -172,23 +172,48 @@ def merge_streaming(wf, groups):
             m["merged"] = merged
 
 
-def run_group(wf, g, pdl: bool):
+def run_group(wf, g, pdl: bool, reduce: bool = True):
     """One (shape, M) layer stack: one grouped launch (or the quantization + contraction pair for M >= GEMM_MIN_M)."""
     if g["batched"]:
         wf.bitlinear_batched(g["x"], g["codes_stack"], g["scales_stack"], out=g["y"])
     else:
         g["group"].run(pdl=pdl, x_ready=True)  # the stacks are independent: no launch writes the next one's x
-    if g["reduce"]:  # row-parallel stack: sum the partial outputs of all ranks (the path's only exchange)
+    if reduce and g["reduce"]:  # row-parallel stack: sum the partial outputs of all ranks (the path's only exchange)
         import torch.distributed as dist
 
         dist.all_reduce(g["y"])
 
 
+_SIDE = {}
+
+
 def run_step(wf, groups, pdl: bool):
     """One pass over the sweep (or over the given part of it): the streaming stacks whose merged launch is complete in
-    `groups` run as that one launch, every other (shape, M) layer stack as its own grouped launch."""
+    `groups` run as that one launch, every other (shape, M) layer stack as its own grouped launch.  The exchange of a
+    row-parallel stack runs on a second stream behind its launch: the stacks are independent, so the next stack's
+    launches need not wait for it (the step ends when both streams have)."""
+    import torch
+
     present = {id(g) for g in groups}
     done, launches = set(), 0
+    main = torch.cuda.current_stream()
+    side = None
+
+    def exchange(members):
+        nonlocal side
+        members = [m for m in members if m["reduce"]]
+        if not members:
+            return
+        import torch.distributed as dist
+
+        if side is None:
+            dev = torch.cuda.current_device()
+            side = _SIDE.get(dev) or _SIDE.setdefault(dev, torch.cuda.Stream())
+        side.wait_stream(main)
+        with torch.cuda.stream(side):
+            for m in members:
+                dist.all_reduce(m["y"])
+
     for g in groups:
         mg = g.get("merged")
         if mg is not None and all(id(m) in present for m in mg["members"]):
@@ -196,14 +221,13 @@ def run_step(wf, groups, pdl: bool):
                 done.add(id(mg))
                 mg["group"].run(pdl=pdl, x_ready=True)
                 launches += 1
-                for m in mg["members"]:
-                    if m["reduce"]:
-                        import torch.distributed as dist
-
-                        dist.all_reduce(m["y"])
+                exchange(mg["members"])
             continue
-        run_group(wf, g, pdl)
+        run_group(wf, g, pdl, reduce=False)
         launches += 2 if g["batched"] else 1  # batched = quantization kernel + contraction
+        exchange([g])
+    if side is not None:
+        main.wait_stream(side)
     return launches
 
 
