@@ -495,9 +495,12 @@ def plugin_e2e(wf, torch, device, steps: int, n: int = 2560, k: int = 2560, m: i
 def tp_parity_check(wf, torch, dist, device, rank: int, world: int) -> str:
     """One small fixed case per rank, checked against the CPU oracle before anything is timed: the accumulators of
     this rank's column shard and of its row (K) shard bit for bit, the gathered column-parallel output and the reduced
-    row-parallel output identical on all ranks, the reduced output within 1e-2 (max|a-b| / max|b|) of the unsharded
-    result, and one round of the peer-memory all-reduce against the library all-reduce.  Returns "ok" or the first
-    failure; the oracle is the checker here, nothing of it is timed."""
+    row-parallel output identical on all ranks, the peer-memory sum equal to the rank-ordered fp32 sum of the (oracle-
+    checked) partial outputs, and one round of the peer-memory all-reduce against the library all-reduce.  The reduced
+    output is also held to the UNSHARDED result within 2e-2 (max|a-b| / max|b|): every rank quantizes its K slice with
+    its own per-token scale, as the reference's row-parallel layer does, so the two differ by the rounding noise of
+    `world` independent quantizations (1.1e-2 at eight ranks of 512 inputs each) — a sanity bound, not the parity
+    criterion.  Returns "ok" or the first failure; the oracle is the checker here, nothing of it is timed."""
     import numpy as np
 
     from oracle.clib import load_oracle
@@ -541,7 +544,7 @@ def tp_parity_check(wf, torch, dist, device, rank: int, world: int) -> str:
             want += p_  # fixed rank order, fp32
         yr = row(x_loc.to(device), out_dtype=torch.float32)  # library all-reduce
         err = float((yr.cpu() - torch.from_numpy(y_full)).abs().max() / np.abs(y_full).max())
-        if err > 1e-2:
+        if err > 2e-2:
             fails.append(f"reduced row-parallel output off the unsharded result by {err:.3e}")
         one = tp.OneShotAllReduce()
         row2 = tp.RowParallelBitLinear(codes, scale, k, n, reduce_dtype=torch.float32, all_reduce=one)
