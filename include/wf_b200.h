@@ -242,7 +242,12 @@ typedef struct WF_ALIGN64 wf_problem {
      * prefetch_bytes must be a multiple of 16, prefetch 16-byte aligned; 0 / NULL: none. */
     const void* prefetch;
     int64_t prefetch_bytes;
-    int32_t _pad[2];
+    /* Optional: the exchange of a row-parallel projection fused into this launch.  A device pointer obtained from
+     * wf_ar_xchg: besides writing y, the launch pushes its partial output into every rank's exchange buffer and
+     * publishes the step; wf_ar_reduce_add_rmsnorm on every rank then sums the partial outputs (see there).  y must be a
+     * contiguous 16-bit tensor (ldy == N, N even) of at most the exchange's max_bytes; at most one problem of a launch
+     * sets xchg.  NULL: none. */
+    const void* xchg;
     uint64_t _tmap_main[16]; /* TMA descriptor: [K/512 blocks][N rows][128 bytes] view of codes, box of _kb_seg blocks */
     uint64_t _tmap_last[16]; /* the same view with the (shorter) box of the last segment */
     uint64_t _tmap_tail[16]; /* TMA descriptor of the last, partial 128-byte column block (if any) */
@@ -338,6 +343,14 @@ int wf_linear_bf16(const void* x, int64_t ldx, const void* w, int64_t ldw, void*
  * all-reduces, and wf_ar_set_step (on every rank, with one common value above every rank's count, e.g. their maximum
  * + 2, between two host-side barriers and with no all-reduce in flight) puts the group back in step.
  */
+/* The device-side descriptor of an exchange (filled by wf_ar_connect inside the exchange buffer). */
+typedef struct wf_xchg {
+    int32_t world, rank;
+    uint64_t slot_bytes; /* capacity of one (slot, source) region = max_bytes of wf_ar_init */
+    uint64_t push_off;   /* offset of the push regions inside every rank's buffer */
+    void* peer[8];       /* every rank's buffer, as seen from this rank */
+} wf_xchg;
+
 int wf_ar_handle_bytes(void);
 int wf_ar_init(int world, int rank, size_t max_bytes, void** ctx_out, unsigned char* handle_out);
 int wf_ar_connect(void* ctx, const unsigned char* handles);
@@ -345,6 +358,19 @@ int wf_ar_allreduce(void* ctx, const void* in, void* out, int64_t n, int dtype, 
 int wf_ar_status(void* ctx, int* out);
 int wf_ar_step(void* ctx, unsigned* out);
 int wf_ar_set_step(void* ctx, unsigned step);
+/*
+ * The exchange fused into the row-parallel projection (the reference sums after o_proj / down_proj with a library
+ * all-reduce, sglang/srt/layers/linear.py:1419-1420; its custom all-reduce pushes and polls in the same way,
+ * sgl-kernel/csrc/allreduce/custom_all_reduce.cuh:203-260).  wf_ar_xchg returns the device pointer to put into
+ * wf_problem.xchg of the projection's grouped launch.  wf_ar_reduce_add_rmsnorm is the consumer, on every rank, after that
+ * launch in the same stream: it waits (bounded, about 0.2 s, then WF_E_LIMIT through wf_ar_status) until every rank
+ * has pushed this step, forms delta = the sum of the partial outputs in rank order in fp32, rounded to bf16 (the bits
+ * of wf_ar_allreduce on the same partial outputs), and continues as wf_add_rmsnorm_bf16(h, delta, weight, y): h += delta,
+ * y = rmsnorm(h) * weight.  M x K bf16, K a multiple of 8 and at most 16384, M * K * 2 <= max_bytes.  Takes WF_FLAG_PDL.
+ */
+int wf_ar_xchg(void* ctx, const void** dev_desc_out);
+int wf_ar_reduce_add_rmsnorm(void* ctx, void* h, const void* weight, void* y, int64_t M, int64_t K, float eps, unsigned flags,
+                             void* stream);
 int wf_ar_destroy(void* ctx);
 
 #ifdef __cplusplus

@@ -111,6 +111,42 @@ def _worker(rank, world, port, results):
             assert torch.equal(y.cpu(), torch.full((4096,), float(sum(r + 1 + rep for r in range(world))), dtype=torch.bfloat16)), rep
         ar.status()
         wf.device_status()
+        # ---- the exchange fused into the row-parallel projection: the launch pushes its partial output to every rank, the
+        # residual add + RMSNorm sums what was pushed.  Same bits as projection -> peer-memory all-reduce -> add + RMSNorm;
+        # both kernel forms (a single layer: 16 warps share an item; 152 problems in the launch: streaming),
+        # several rounds (the two slots alternate).
+        at("fused exchange")
+        xp = ar.xchg_ptr()
+        assert xp is not None
+        for (n2, k2, m2, extra) in [(512, 1344, 1, 0), (512, 1344, 5, 0), (512, 1344, 2, 151)]:
+            g2 = torch.Generator().manual_seed(n2 + m2)
+            w2 = torch.randn(n2, k2, generator=g2) * 0.02
+            c2, s2 = wf.pack_ternary(w2.to(dev))
+            lo2, hi2 = tp.shard_bounds(k2, world, 64)[rank]
+            shard = tp.shard_codes_k(c2, lo2, hi2)
+            wn = (torch.rand(n2, generator=g2) + 0.5).bfloat16().to(dev)
+            for rep in range(3):
+                xs = torch.randn(m2, k2, generator=g2).bfloat16()[:, lo2:hi2].contiguous().to(dev)
+                h0 = torch.randn(m2, n2, generator=g2).bfloat16().to(dev)
+                # unfused: projection, peer-memory all-reduce, residual add + RMSNorm
+                part = wf.bitlinear(xs, shard, s2, out_dtype=torch.bfloat16)
+                ar(part)
+                h_ref, y_ref = h0.clone(), torch.empty_like(h0)
+                wf.ops.add_rmsnorm_(h_ref, part, wn, y_ref, 1e-5)
+                # fused
+                out = torch.empty(m2, n2, dtype=torch.bfloat16, device=dev)
+                # `extra` more problems in the launch (plain ones: thousands of items put it on the streaming form)
+                scratch = [torch.empty(m2, n2, dtype=torch.bfloat16, device=dev) for _ in range(extra)]
+                grp = wf.DecodeGroup([dict(x=xs, codes=shard, w_scale=s2, out=out, xchg=xp)] +
+                                     [dict(x=xs, codes=shard, w_scale=s2, out=o_) for o_ in scratch])
+                grp.run(pdl=True)
+                h_f, y_f = h0.clone(), torch.empty_like(h0)
+                ar.reduce_add_rmsnorm_(h_f, wn, y_f, 1e-5, pdl=True)
+                torch.cuda.synchronize()
+                assert torch.equal(h_f, h_ref) and torch.equal(y_f, y_ref), (n2, m2, extra, rep)
+                assert all(torch.equal(o_, out) for o_ in scratch)
+        ar.status()
+        wf.device_status()
         # ---- the decoder: heads, MLP width and the output head sharded over the ranks, against one rank on its own
         from wrinklefree_monorepo_b200.decoder import DecoderConfig, TernaryDecoder
 
@@ -139,6 +175,14 @@ def _worker(rank, world, port, results):
         full = [torch.empty_like(m_tp.logits) for _ in range(world)]
         dist.all_gather(full, m_tp.logits.contiguous())
         assert torch.equal(torch.cat(full, -1).float().argmax(-1), m_tp.next_tok)
+        # the fused exchange (the default for few sequences) against the exchange as a kernel of its own: same bits
+        assert m_tp.fuse_exchange
+        m_sep = TernaryDecoder(cfg, 3, 16, dev, seed=3, fuse_exchange=False)
+        assert not m_sep.fuse_exchange
+        m_sep.prefill(ids)
+        m_sep.capture(masked=True)
+        toks_sep = m_sep.decode(4)
+        assert torch.equal(toks_sep, toks_tp) and torch.equal(m_sep.logits, m_tp.logits)
         wf.device_status()
         results[rank] = "ok"
     except BaseException:
@@ -149,6 +193,7 @@ def _worker(rank, world, port, results):
     at("teardown")
     m_tp.release()
     m_1.release()
+    m_sep.release()
     dist.destroy_process_group()
     at("done")
 

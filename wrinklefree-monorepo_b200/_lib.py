@@ -35,7 +35,7 @@ class Problem(C.Structure):
                 ("w_scale_host", _f32), ("eps", _f32),
                 ("_item_begin", C.c_int32), ("_row_items", C.c_int32), ("_chunks", C.c_int32), ("_kb_full", C.c_int32),
                 ("_tail_bytes", C.c_int32), ("_kb_seg", C.c_int32), ("_ksegs", C.c_int32),
-                ("x2", _p), ("norm_w", _p), ("h_out", _p), ("x_mode", C.c_int32), ("norm_eps", _f32), ("prefetch", _p), ("prefetch_bytes", _i64), ("_pad", C.c_int32 * 2),
+                ("x2", _p), ("norm_w", _p), ("h_out", _p), ("x_mode", C.c_int32), ("norm_eps", _f32), ("prefetch", _p), ("prefetch_bytes", _i64), ("xchg", _p),
                 ("_tmap_main", C.c_uint64 * 16), ("_tmap_last", C.c_uint64 * 16), ("_tmap_tail", C.c_uint64 * 16)]
 
 
@@ -82,6 +82,8 @@ _SIGNATURES = {
     "wf_ar_connect": (_int, [_p, _p]),
     "wf_ar_allreduce": (_int, [_p, _p, _p, _i64, _int, _u32, _p]),
     "wf_ar_status": (_int, [_p, C.POINTER(C.c_int)]),
+    "wf_ar_xchg": (_int, [_p, C.POINTER(C.c_void_p)]),
+    "wf_ar_reduce_add_rmsnorm": (_int, [_p, _p, _p, _p, _i64, _i64, _f32, _u32, _p]),
     "wf_ar_step": (_int, [_p, C.POINTER(C.c_uint)]),
     "wf_ar_set_step": (_int, [_p, _u32]),
     "wf_ar_destroy": (_int, [_p]),

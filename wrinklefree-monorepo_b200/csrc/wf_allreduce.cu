@@ -17,6 +17,7 @@
 #include <new>
 
 #include "wf_common.cuh"
+#include "wf_xchg.cuh"
 
 namespace wf {
 
@@ -143,6 +144,107 @@ __global__ void __launch_bounds__(AR_THREADS) allreduce_kernel(ArPeers peers, in
     }
 }
 
+// ---- consumer of a fused exchange: delta = sum of the pushed partial outputs, then h += delta, y = rmsnorm(h) * w ----
+// One block per token row; the row stays in registers.  The arithmetic after the sum is that of the residual add +
+// RMSNorm kernel of this library, the sum itself that of allreduce_kernel (fp32 in rank order, rounded to bf16).
+constexpr int XR_THREADS = 512;
+constexpr int XR_CHUNKS = 4;  // 8-element chunks per thread: rows up to 16384 elements
+
+__device__ __forceinline__ float xr_lo(uint32_t w) { return __uint_as_float(w << 16); }
+__device__ __forceinline__ float xr_hi(uint32_t w) { return __uint_as_float(w & 0xffff0000u); }
+__device__ __forceinline__ uint32_t xr_pack(float lo, float hi) {
+    const __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi);
+    return *reinterpret_cast<const uint32_t*>(&v);
+}
+__device__ __forceinline__ float xr_round(float v) { return __bfloat162float(__float2bfloat16_rn(v)); }
+
+__global__ void __launch_bounds__(XR_THREADS) reduce_add_rmsnorm_kernel(const wf_xchg* __restrict__ xd, __nv_bfloat16* __restrict__ h,
+                                                                        const __nv_bfloat16* __restrict__ w, __nv_bfloat16* __restrict__ y,
+                                                                        int K, float eps) {
+    __shared__ float sh[XR_THREADS / 32];
+    asm volatile("griddepcontrol.launch_dependents;\n" ::: "memory");
+    const int64_t m = blockIdx.x;
+    const int tid = threadIdx.x;
+    const int chunks = K >> 3;
+    uint4 hv[XR_CHUNKS], wv[XR_CHUNKS];
+#pragma unroll
+    for (int c = 0; c < XR_CHUNKS; ++c) {  // the norm weights do not depend on the previous kernel
+        const int i = tid + c * XR_THREADS;
+        if (i < chunks) wv[c] = __ldg(reinterpret_cast<const uint4*>(w) + i);
+    }
+    asm volatile("griddepcontrol.wait;\n" ::: "memory");
+    const wf_xchg x = *xd;
+    uint8_t* mine = static_cast<uint8_t*>(x.peer[x.rank]);
+    const unsigned step = *reinterpret_cast<volatile unsigned*>(mine + XCHG_PSTEP_OFF) + 1;
+    // every rank has pushed this step: poll this rank's own flag words (bounded)
+    if (tid < x.world) {
+        const unsigned* f = reinterpret_cast<const unsigned*>(mine + XCHG_PFLAG_OFF) + tid;
+        unsigned it = 0;
+        while (static_cast<int>(xchg_ld_acquire_sys(f) - step) < 0) {  // flags only grow
+            if (++it > AR_SPIN_LIMIT) {
+                atomicExch(reinterpret_cast<unsigned*>(mine + XCHG_STATUS_OFF), static_cast<unsigned>(WF_E_LIMIT));
+                break;
+            }
+            __nanosleep(20);
+        }
+    }
+    __syncthreads();
+    const uint8_t* slot = mine + x.push_off + static_cast<uint64_t>(step & 1) * x.world * x.slot_bytes;
+    uint4* hrow = reinterpret_cast<uint4*>(h + m * K);
+    float ss = 0.f;
+#pragma unroll
+    for (int c = 0; c < XR_CHUNKS; ++c) {
+        const int i = tid + c * XR_THREADS;
+        if (i < chunks) {
+            float acc[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
+            for (int r = 0; r < x.world; ++r)  // pushed by peers: read past this SM's L1
+                accumulate8<WF_BF16>(ld_peer16(slot + r * x.slot_bytes + (static_cast<uint64_t>(m) * K + 8 * static_cast<uint64_t>(i)) * 2), acc);
+            const uint4 hh = hrow[i];
+            uint32_t a[4] = {hh.x, hh.y, hh.z, hh.w};
+#pragma unroll
+            for (int e = 0; e < 4; ++e) {
+                const uint32_t d = xr_pack(acc[2 * e], acc[2 * e + 1]);  // delta, rounded to bf16 like the all-reduced tensor
+                a[e] = xr_pack(xr_lo(a[e]) + xr_lo(d), xr_hi(a[e]) + xr_hi(d));  // the residual stream stays bf16
+                ss += xr_lo(a[e]) * xr_lo(a[e]) + xr_hi(a[e]) * xr_hi(a[e]);
+            }
+            hv[c] = make_uint4(a[0], a[1], a[2], a[3]);
+            hrow[i] = hv[c];
+        }
+    }
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) ss += __shfl_xor_sync(0xffffffffu, ss, o);
+    if ((tid & 31) == 0) sh[tid >> 5] = ss;
+    __syncthreads();
+    float tot = 0.f;
+#pragma unroll
+    for (int i = 0; i < XR_THREADS / 32; ++i) tot += sh[i];
+    const float rn = rsqrtf(tot / static_cast<float>(K) + eps);
+    uint4* yrow = reinterpret_cast<uint4*>(y + m * K);
+#pragma unroll
+    for (int c = 0; c < XR_CHUNKS; ++c) {
+        const int i = tid + c * XR_THREADS;
+        if (i < chunks) {
+            const uint32_t a[4] = {hv[c].x, hv[c].y, hv[c].z, hv[c].w};
+            const uint32_t g[4] = {wv[c].x, wv[c].y, wv[c].z, wv[c].w};
+            uint32_t o[4];
+#pragma unroll
+            for (int e = 0; e < 4; ++e)
+                o[e] = xr_pack(xr_round(xr_lo(a[e]) * rn) * xr_lo(g[e]), xr_round(xr_hi(a[e]) * rn) * xr_hi(g[e]));
+            yrow[i] = make_uint4(o[0], o[1], o[2], o[3]);
+        }
+    }
+    // the last block to finish advances this rank's count of consumed exchanges
+    __syncthreads();
+    if (tid == 0) {
+        __threadfence();
+        unsigned* ticket = reinterpret_cast<unsigned*>(mine + XCHG_CTICKET_OFF);
+        if (atomicAdd(ticket, 1u) == gridDim.x - 1) {
+            *ticket = 0;
+            *reinterpret_cast<volatile unsigned*>(mine + XCHG_PSTEP_OFF) = step;
+        }
+    }
+}
+
 }  // namespace wf
 
 using namespace wf;
@@ -158,7 +260,8 @@ extern "C" int wf_ar_init(int world, int rank, size_t max_bytes, void** ctx_out,
     WF_REQUIRE(c, "wf_ar_init: out of host memory");
     c->world = world; c->rank = rank; c->max_bytes = max_bytes; c->connected = false;
     WF_CUDA(cudaGetDevice(&c->device));
-    const size_t total = AR_HEADER + 2 * max_bytes;
+    // header | two slots of the stand-alone all-reduce | two push slots of `world` source regions each
+    const size_t total = AR_HEADER + 2 * max_bytes + 2 * static_cast<size_t>(world) * max_bytes;
     void* p = nullptr;
     cudaError_t e = cudaMalloc(&p, total);
     if (e != cudaSuccess) {
@@ -194,7 +297,50 @@ extern "C" int wf_ar_connect(void* ctx, const unsigned char* handles) {
         WF_CUDA(cudaIpcOpenMemHandle(&p, h, cudaIpcMemLazyEnablePeerAccess));
         c->peers.base[r] = static_cast<uint8_t*>(p);
     }
+    wf_xchg d = {};
+    d.world = c->world;
+    d.rank = c->rank;
+    d.slot_bytes = c->max_bytes;
+    d.push_off = AR_HEADER + 2 * c->max_bytes;
+    for (int r = 0; r < c->world; ++r) d.peer[r] = c->peers.base[r];
+    WF_CUDA(cudaMemcpy(c->local + XCHG_DESC_OFF, &d, sizeof(d), cudaMemcpyHostToDevice));
     c->connected = true;
+    return WF_OK;
+}
+
+extern "C" int wf_ar_xchg(void* ctx, const void** dev_desc_out) {
+    ArCtx* c = static_cast<ArCtx*>(ctx);
+    WF_REQUIRE(c && dev_desc_out, "wf_ar_xchg: null pointer");
+    WF_REQUIRE(c->connected, "wf_ar_xchg: wf_ar_connect has not run");
+    *dev_desc_out = c->local + XCHG_DESC_OFF;
+    return WF_OK;
+}
+
+extern "C" int wf_ar_reduce_add_rmsnorm(void* ctx, void* h, const void* weight, void* y, int64_t M, int64_t K, float eps, unsigned flags,
+                                        void* stream) {
+    ArCtx* c = static_cast<ArCtx*>(ctx);
+    WF_REQUIRE(c && h && weight && y, "wf_ar_reduce_add_rmsnorm: null pointer");
+    WF_REQUIRE(c->connected, "wf_ar_reduce_add_rmsnorm: wf_ar_connect has not run");
+    WF_REQUIRE(M >= 1 && K >= 8 && K % 8 == 0 && K <= XR_THREADS * XR_CHUNKS * 8, "wf_ar_reduce_add_rmsnorm: K must be a multiple of 8, at most %d",
+               XR_THREADS * XR_CHUNKS * 8);
+    WF_REQUIRE(static_cast<size_t>(M) * K * 2 <= c->max_bytes, "wf_ar_reduce_add_rmsnorm: %lld x %lld exceeds the exchange's %zu bytes",
+               (long long)M, (long long)K, c->max_bytes);
+    WF_REQUIRE((reinterpret_cast<uintptr_t>(h) | reinterpret_cast<uintptr_t>(weight) | reinterpret_cast<uintptr_t>(y)) % 16 == 0,
+               "wf_ar_reduce_add_rmsnorm: tensors must be 16-byte aligned");
+    cudaLaunchConfig_t lc = {};
+    lc.gridDim = dim3(static_cast<unsigned>(M));
+    lc.blockDim = dim3(XR_THREADS);
+    lc.stream = static_cast<cudaStream_t>(stream);
+    cudaLaunchAttribute attr[1];
+    if (flags & WF_FLAG_PDL) {
+        attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+        attr[0].val.programmaticStreamSerializationAllowed = 1;
+        lc.attrs = attr;
+        lc.numAttrs = 1;
+    }
+    const wf_xchg* desc = reinterpret_cast<const wf_xchg*>(c->local + XCHG_DESC_OFF);
+    WF_CUDA(cudaLaunchKernelEx(&lc, reduce_add_rmsnorm_kernel, desc, static_cast<__nv_bfloat16*>(h), static_cast<const __nv_bfloat16*>(weight),
+                               static_cast<__nv_bfloat16*>(y), static_cast<int>(K), eps));
     return WF_OK;
 }
 
@@ -248,7 +394,10 @@ extern "C" int wf_ar_step(void* ctx, unsigned* out) {
     ArCtx* c = static_cast<ArCtx*>(ctx);
     WF_REQUIRE(c && out, "wf_ar_step: null pointer");
     WF_CUDA(cudaDeviceSynchronize());
-    WF_CUDA(cudaMemcpy(out, c->local + 2048, sizeof(unsigned), cudaMemcpyDeviceToHost));
+    unsigned pulled = 0, pushed = 0;
+    WF_CUDA(cudaMemcpy(&pulled, c->local + 2048, sizeof(unsigned), cudaMemcpyDeviceToHost));
+    WF_CUDA(cudaMemcpy(&pushed, c->local + XCHG_PSTEP_OFF, sizeof(unsigned), cudaMemcpyDeviceToHost));
+    *out = pulled > pushed ? pulled : pushed;  // the stand-alone all-reduce and the fused exchange count separately
     return WF_OK;
 }
 
@@ -260,6 +409,8 @@ extern "C" int wf_ar_set_step(void* ctx, unsigned step) {
     WF_CUDA(cudaDeviceSynchronize());
     const unsigned words[3] = {step, 0u, 0u};  // step | ticket | status
     WF_CUDA(cudaMemcpy(c->local + 2048, words, sizeof(words), cudaMemcpyHostToDevice));
+    const unsigned pwords[3] = {step, 0u, 0u};  // consumed exchanges | producer ticket | consumer ticket
+    WF_CUDA(cudaMemcpy(c->local + XCHG_PSTEP_OFF, pwords, sizeof(pwords), cudaMemcpyHostToDevice));
     return WF_OK;
 }
 

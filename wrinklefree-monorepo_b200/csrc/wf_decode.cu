@@ -34,6 +34,7 @@
 #include <cstddef>
 
 #include "wf_common.cuh"
+#include "wf_xchg.cuh"
 
 namespace wf {
 __device__ int g_decode_status = 0;
@@ -73,6 +74,7 @@ struct DecodeCfg {
     int decoupled;    // 1: every consumer warp owns whole 16-row items (RI == 1); 0: the 16 warps share each item
     int ss_off;       // per-warp partial sums of squares of the fused RMSNorm input mode: [2][MT][16] floats
     int prefetch;     // some problem names a range to prefetch into L2
+    const void* xchg; // the exchange that problems of this launch push their outputs to (wf_problem.xchg), or null
 };
 
 template <int NTHREADS = DEC_CONSUMERS>
@@ -597,6 +599,33 @@ __device__ __forceinline__ void issue_l2_prefetch(const wf_problem* __restrict__
     }
 }
 
+// The push side of a fused exchange: copies what this CTA has produced (the items [beg, end) of the work list; rows_item
+// rows each) from its local outputs into every rank's exchange buffer, then reports the CTA as finished.  Called by the
+// `nthreads` threads that made the stores, after all of them have passed a barrier; every CTA of the grid calls it, with
+// an empty range when it had no work.  Consecutive items of one (problem, token pass) go out as one block of rows.
+template <int NTHREADS>
+__device__ __forceinline__ void xchg_push_items(const DecodeCfg& cfg, const wf_problem* __restrict__ probs, int beg, int end, int rows_item,
+                                                const int* s_ib, int uni, int tid, unsigned grid) {
+    const wf_xchg* x = static_cast<const wf_xchg*>(cfg.xchg);
+    const unsigned step = xchg_step(x);
+    for (int it = beg; it < end;) {
+        int local;
+        const int pi = locate_problem(probs, cfg.P, it, s_ib, cfg.ib_cap, local, uni);
+        const wf_problem* q = &probs[pi];
+        const int row_items = q->_row_items, chunk = local / row_items, ritem = local % row_items;
+        const int run = min(end - it, row_items - ritem);
+        const int64_t bytes = static_cast<int64_t>(q->M) * q->N * 2;
+        if (q->xchg != nullptr && static_cast<uint64_t>(bytes) <= x->slot_bytes) {
+            const int m0 = chunk * cfg.MTA;
+            xchg_push_block(x, step, static_cast<const uint16_t*>(q->y), q->ldy, q->N, m0, min(q->M, m0 + cfg.MTA), ritem * rows_item,
+                            min(q->N, (ritem + run) * rows_item), tid, NTHREADS);
+        }
+        it += run;
+    }
+    asm volatile("bar.sync 3, %0;\n" ::"n"(NTHREADS) : "memory");  // every thread's peer stores are issued
+    if (tid == 0) xchg_cta_done(x, step, grid);
+}
+
 template <int XDT, int NT, bool FOURACC>
 __global__ void __launch_bounds__(DEC_THREADS, 1)
     decode_kernel(const wf_problem* __restrict__ dev_problems, const __grid_constant__ wf_problem single, const DecodeCfg cfg) {
@@ -696,7 +725,10 @@ __global__ void __launch_bounds__(DEC_THREADS, 1)
         // each warp takes whole items (all of K, epilogue from its own accumulators) and nothing synchronises the CTA
         // any more.  With all 16 warps on one item at a time, the two barriers and the shared-memory reduction per
         // item (about 0.7 us) made a 29 MB gate/up launch compute-latency-bound.
-        if (beg >= end) return;
+        if (beg >= end) {
+            if (cfg.xchg) xchg_push_items<DEC_CONSUMERS>(cfg, probs, beg, beg, rows_item, s_ib, 0, tid, gridDim.x);
+            return;
+        }
         const int m_all = min(cfg.MTA, p.M);
         {
             int local_first;
@@ -758,6 +790,10 @@ __global__ void __launch_bounds__(DEC_THREADS, 1)
                     }
                 }
             }
+        }
+        if (cfg.xchg) {
+            consumer_sync();  // every warp's outputs are written
+            xchg_push_items<DEC_CONSUMERS>(cfg, probs, beg, end, rows_item, s_ib, 0, tid, gridDim.x);
         }
         return;
     }
@@ -841,6 +877,10 @@ __global__ void __launch_bounds__(DEC_THREADS, 1)
             if (p.acc_out) p.acc_out[m * p.N + nrow] = a;
         }
     }
+    if (cfg.xchg) {
+        consumer_sync();  // every thread's outputs are written
+        xchg_push_items<DEC_CONSUMERS>(cfg, probs, beg, end, rows_item, s_ib, 0, tid, gridDim.x);
+    }
 }
 
 // ---- streaming form: every warp owns one stage and is its own producer ------------------------------
@@ -896,7 +936,13 @@ __global__ void __launch_bounds__(STREAM_THREADS, 2)
     int beg, end;
     if (cfg.cpp > 0) {
         const int pi = blockIdx.x / cfg.cpp, sub = blockIdx.x % cfg.cpp;
-        if (pi >= cfg.P) return;
+        if (pi >= cfg.P) {
+            if (cfg.xchg) {
+                asm volatile("griddepcontrol.wait;\n" ::: "memory");  // the step follows from the previous exchange's consumer
+                xchg_push_items<STREAM_THREADS>(cfg, probs, 0, 0, 16, s_ib, uni, tid, gridDim.x);
+            }
+            return;
+        }
         const int ib = first_item(probs, pi, s_ib, cfg.ib_cap, uni);
         const int cnt = (pi + 1 < cfg.P ? first_item(probs, pi + 1, s_ib, cfg.ib_cap, uni) : cfg.total_items) - ib;
         const int q = cnt / cfg.cpp, r = cnt - q * cfg.cpp;  // the first r CTAs of the problem take one item more
@@ -907,7 +953,13 @@ __global__ void __launch_bounds__(STREAM_THREADS, 2)
         beg = bx * cfg.items_q + min(bx, cfg.items_r);
         end = beg + cfg.items_q + (bx < cfg.items_r ? 1 : 0);
     }
-    if (beg >= end) return;
+    if (beg >= end) {
+        if (cfg.xchg) {
+            asm volatile("griddepcontrol.wait;\n" ::: "memory");
+            xchg_push_items<STREAM_THREADS>(cfg, probs, 0, 0, 16, s_ib, uni, tid, gridDim.x);
+        }
+        return;
+    }
     // Warp w starts with item beg + w; every further item is claimed from this counter when a warp has consumed its
     // stage, so a warp that meets slower memory channels takes fewer items instead of holding the CTA back.
     int* s_next = reinterpret_cast<int*>(smem + 260);
@@ -1147,6 +1199,10 @@ __global__ void __launch_bounds__(STREAM_THREADS, 2)
     }
     // a kernel that follows with a programmatic dependency relies on this grid having waited for its own predecessor
     if (!may_store) asm volatile("griddepcontrol.wait;\n" ::: "memory");
+    if (cfg.xchg) {
+        __syncthreads();  // every warp's outputs are written
+        xchg_push_items<STREAM_THREADS>(cfg, probs, beg, end, 16, s_ib, uni, tid, gridDim.x);
+    }
 }
 
 // ------------------------------------------------------------------ host side
@@ -1429,6 +1485,12 @@ static int run_group(const char* who, const wf_problem* dev, wf_problem* host, i
     cfg.stage_bytes = g.stage_bytes; cfg.act_off = g.act_off; cfg.stage_off = g.stage_off; cfg.decoupled = g.decoupled; cfg.cpp = g.cpp; cfg.nbuf = g.nbuf;
     cfg.ib_cap = P < IB_CAP ? P : IB_CAP; cfg.ib_off = g.act_off - IB_CAP * 4 - 384; cfg.hdr_off = g.act_off - 384;
     cfg.ss_off = static_cast<int>(ss_offset(g.NT, g.RI));
+    cfg.xchg = nullptr;
+    for (int i = 0; i < P; ++i) {
+        if (!host[i].xchg) continue;
+        if (cfg.xchg) return fail(WF_E_ARG, "%s: one problem of a launch may push to an exchange (its output fills the exchange's slot)", who);
+        cfg.xchg = host[i].xchg;
+    }
     cfg.prefetch = 0;
     if (P <= 8)
         for (int i = 0; i < P; ++i) cfg.prefetch |= (host[i].prefetch != nullptr && host[i].prefetch_bytes > 0) ? 1 : 0;
@@ -1496,6 +1558,9 @@ static int wf::check_problem(const char* who, const wf_problem& q) {
     WF_REQUIRE(q.x_mode >= WF_X_PLAIN && q.x_mode <= WF_X_NORM, "%s: unknown x_mode %d", who, q.x_mode);
     WF_REQUIRE(q.prefetch_bytes >= 0 && q.prefetch_bytes % 16 == 0 && (reinterpret_cast<uintptr_t>(q.prefetch) & 15) == 0,
                "%s: the prefetch range must be 16-byte aligned and a multiple of 16 bytes", who);
+    if (q.xchg)
+        WF_REQUIRE((q.y_dtype == WF_BF16 || q.y_dtype == WF_F16) && q.ldy == q.N && q.N % 2 == 0 && (reinterpret_cast<uintptr_t>(q.y) & 3) == 0,
+                   "%s: a fused exchange needs a contiguous 16-bit output with an even number of columns", who);
     if (q.x_mode != WF_X_PLAIN) {
         WF_REQUIRE(q.x_dtype == WF_BF16, "%s: fused input modes take bf16 tensors", who);
         WF_REQUIRE(q.K % 8 == 0, "%s: fused input modes need K %% 8 == 0", who);

@@ -76,15 +76,18 @@ class TernaryDecoder:
 
     def __init__(self, cfg: DecoderConfig, batch: int, max_ctx: int, device, group=None, seed: int = 0,
                  dtype: torch.dtype = torch.bfloat16, weights: Optional[dict] = None, pack_mode: torch.dtype = torch.float32,
-                 fuse: Optional[bool] = None, prefetch: bool = False):
+                 fuse: Optional[bool] = None, prefetch: bool = False, fuse_exchange: Optional[bool] = None):
         """`weights`: optional fp32 state dict under the reference model's parameter names (BitNetLlama,
         wrinklefree/models/llama.py:13-59); without it the weights are drawn from N(0, 0.02) with `seed`.
         `pack_mode`: arithmetic of the ternarization (torch.float32, or the input dtype for the cast-first rule of
         BitLinear.forward).  `fuse`: True runs the decode step of small batches with the fused input modes of the
         grouped kernel (six launches per layer instead of ten); measured on B200 the separate norm / activation kernels,
         which overlap the projections' weight streaming through programmatic launches, are faster, so it is off by
-        default."""
+        default.  `fuse_exchange` (tensor parallel, up to 8 sequences, bf16): the row-parallel projections push their partial
+        outputs to every rank inside their own launch and the residual add + RMSNorm that follows sums them (on unless False)."""
         self._fuse_opt = fuse
+        # tensor parallel, few tokens: False keeps the exchange after o_proj / down_proj a kernel of its own
+        self._xchg_opt = fuse_exchange
         # decode step: every projection group asks L2 for the following launches' weights.  Measured on B200 at batch 1
         # (8B shape) this made the step slower (2.05 -> 2.25 ms: the prefetch competes with the running launch's own
         # stream), so it is off by default.
@@ -194,6 +197,14 @@ class TernaryDecoder:
         self.h2 = torch.empty(B, cfg.hidden, dtype=dt, device=dev)
         self.xf = torch.empty(B, cfg.hidden, dtype=dt, device=dev)
         self.head_out = torch.empty(B, self.lm_head.shape[0], dtype=dt, device=dev) if dt == torch.bfloat16 else None
+        # Tensor parallel, few tokens: the exchange after o_proj / down_proj is fused into those launches (they push their
+        # partial outputs to every rank) and into the residual add + RMSNorm that follows (it sums what was pushed).
+        self.fuse_exchange = False
+        if self.tp > 1 and self._xchg_opt is not False:
+            if self._oneshot is None:
+                self._oneshot = tpmod.OneShotAllReduce(self.group, max_bytes=64 << 10)  # measured: NCCL is faster from 256 KB on
+            self.fuse_exchange = (dt == torch.bfloat16 and not self.big and not self.fused and cfg.hidden % 8 == 0 and cfg.hidden <= 16384
+                                  and B * cfg.hidden * 2 <= self._oneshot.max_bytes and self._oneshot.xchg_ptr() is not None)
         mode = "silu" if cfg.act == "silu" else "relu2"
         prev_down = None
         for li, L in enumerate(self.layers):
@@ -230,6 +241,11 @@ class TernaryDecoder:
                                               for n, o in zip(("q", "k", "v"), L["qkv"])])
                 L["g_gu"] = ops.DecodeGroup([dict(x=L["hn"], codes=L[n][0], w_scale=L[n][1], out=o, prefetch=pf2.get(n))
                                              for n, o in zip(("gate", "up"), L["gu"])])
+                if self.fuse_exchange:
+                    xp = self._oneshot.xchg_ptr()
+                    L["g_o"] = ops.DecodeGroup([dict(x=L["an"] if cfg.subln else L["attn"], codes=L["o"][0], w_scale=L["o"][1], out=L["ob"], xchg=xp)])
+                    L["g_down"] = ops.DecodeGroup([dict(x=L["actn"] if cfg.subln else L["act"], codes=L["down"][0], w_scale=L["down"][1],
+                                                        out=L["db"], xchg=xp)])
 
     def _act(self, g, u):
         return (F.silu(g) if self.cfg.act == "silu" else F.relu(g).pow(2)) * u
@@ -255,8 +271,12 @@ class TernaryDecoder:
         if self.masked and self.attention == "library":
             valid = (torch.arange(self.T, device=self.dev) <= self.pos).view(1, 1, 1, self.T)
         delta = None
+        fx = self.fuse_exchange
         for L in self.layers:
-            ops.add_rmsnorm_(self.h, delta, L["n1"], L["xn"], cfg.eps, pdl=True)
+            if fx and delta is not None:  # the previous layer's down projection has pushed its partial outputs
+                self._oneshot.reduce_add_rmsnorm_(self.h, L["n1"], L["xn"], cfg.eps, pdl=True)
+            else:
+                ops.add_rmsnorm_(self.h, delta, L["n1"], L["xn"], cfg.eps, pdl=True)
             q, k, v = L["g_qkv"].run(pdl=True)
             ops.rope_kv_(q, k, v, self.cos, self.sin, self.pos, L["kc"], L["vc"], pdl=True)
             if self.attention == "library":  # the framework's fused kernel, kept as a comparison for the benchmark
@@ -270,8 +290,14 @@ class TernaryDecoder:
             a = a.reshape(B, self.nq * d)
             if cfg.subln:
                 a = ops.add_rmsnorm_(a, None, L["sa"], L["an"], cfg.subln_eps, pdl=True)
-            o = self._allreduce(ops.bitlinear(a, L["o"][0], L["o"][1], out=L["ob"], path=path, pdl=True))
-            ops.add_rmsnorm_(self.h, o, L["n2"], L["hn"], cfg.eps, pdl=True)
+            if fx:
+                if a.data_ptr() != L["g_o"].x_ptr:
+                    L["attn"].copy_(a)  # the comparison attention writes its own tensor
+                L["g_o"].run(pdl=True)
+                self._oneshot.reduce_add_rmsnorm_(self.h, L["n2"], L["hn"], cfg.eps, pdl=True)
+            else:
+                o = self._allreduce(ops.bitlinear(a, L["o"][0], L["o"][1], out=L["ob"], path=path, pdl=True))
+                ops.add_rmsnorm_(self.h, o, L["n2"], L["hn"], cfg.eps, pdl=True)
             if big:
                 hq, hs = ops.act_quant_i8(L["hn"], eps=1e-5)  # one quantization for gate and up
                 g, u = (ops.bitlinear(hq, L[n][0], L[n][1], x_scale=hs, out=o_, path="prefill")
@@ -281,8 +307,14 @@ class TernaryDecoder:
             act = ops.act_mul(g, u, L["act"], self.cfg.act, pdl=True)
             if cfg.subln:
                 act = ops.add_rmsnorm_(act, None, L["sf"], L["actn"], cfg.subln_eps, pdl=True)
-            delta = self._allreduce(ops.bitlinear(act, L["down"][0], L["down"][1], out=L["db"], path=path, pdl=True))
-        ops.add_rmsnorm_(self.h, delta, self.norm_f, self.xf, cfg.eps, pdl=True)
+            if fx:
+                delta = L["g_down"].run(pdl=True)[0]
+            else:
+                delta = self._allreduce(ops.bitlinear(act, L["down"][0], L["down"][1], out=L["db"], path=path, pdl=True))
+        if fx:
+            self._oneshot.reduce_add_rmsnorm_(self.h, self.norm_f, self.xf, cfg.eps, pdl=True)
+        else:
+            ops.add_rmsnorm_(self.h, delta, self.norm_f, self.xf, cfg.eps, pdl=True)
         self._greedy(self._head(self.xf, self.head_out, pdl=True))
         self.pos.add_(1)
 

@@ -274,6 +274,9 @@ class DecodeGroup:
 
     `prefetch`: a tensor whose bytes the launch asks L2 to fetch while it runs (the next launch's packed weights).
 
+    `xchg`: the device pointer of an exchange (`tp.OneShotAllReduce.xchg_ptr()`): a row-parallel projection pushes its
+    partial output to every rank inside the launch; `OneShotAllReduce.reduce_add_rmsnorm_` consumes it.
+
     Fused inputs (bf16): `x_mode` "silu" / "relu2" with `x2`: the projection quantizes act(x) * x2 (x = gate,
     x2 = up: the activation in front of a down projection); `x_mode` "norm" with `norm_w`, optional `x2`, `h_out`,
     `norm_eps`: it quantizes rmsnorm(x + x2) * norm_w and writes x + x2 to h_out (residual add + RMSNorm in front
@@ -291,6 +294,7 @@ class DecodeGroup:
             raise ValueError("empty group")
         self._keep = []
         self.outputs, self.accs = [], []
+        self.x_ptr = None  # address of the first pushing problem's input (a caller may have to copy into it)
         arr, self._raw = L.aligned_problem_array(len(problems))
         dev = problems[0]["x"].device
         # With many tokens per problem x is quantized once per distinct input by a kernel of its own in run(), and
@@ -339,6 +343,10 @@ class DecodeGroup:
                 q.x_mode, q.norm_eps = mode, pr.get("norm_eps", 1e-6)
                 q.x2, q.norm_w, q.h_out = _ptr(second), _ptr(norm_w), _ptr(h_out)
                 self._keep += [second, norm_w, h_out]
+            if pr.get("xchg"):  # device pointer of an exchange (tp.OneShotAllReduce.xchg_ptr()): the launch pushes this output
+                q.xchg = int(pr["xchg"])
+                if self.x_ptr is None:
+                    self.x_ptr = x2.data_ptr()
             pf = pr.get("prefetch")  # a tensor (typically the next launch's packed weights) to pull into L2 meanwhile
             if pf is not None:
                 _need_cuda(pf)

@@ -77,6 +77,30 @@ class OneShotAllReduce:
                                             L.FLAG_PDL if pdl else 0, torch.cuda.current_stream().cuda_stream), "wf_ar_allreduce")
         return y
 
+    def xchg_ptr(self):
+        """Device pointer of this exchange's descriptor, for `DecodeGroup(..., xchg=ptr)`: the row-parallel projection
+        then pushes its partial output to every rank itself; `reduce_add_rmsnorm_` is the matching consumer.  None when
+        the peer-memory path is not available."""
+        import ctypes as C
+
+        if self._ctx is None:
+            return None
+        p = C.c_void_p()
+        L.check(L.lib().wf_ar_xchg(self._ctx, C.byref(p)), "wf_ar_xchg")
+        return p.value
+
+    def reduce_add_rmsnorm_(self, h: torch.Tensor, weight: torch.Tensor, y: torch.Tensor, eps: float, pdl: bool = False) -> torch.Tensor:
+        """Consumer of a fused exchange, on every rank after the pushing launch: h += sum over the ranks of the pushed
+        partial outputs (fp32 in rank order, rounded to bf16: the bits of the stand-alone all-reduce), y = rmsnorm(h) * weight."""
+        if self._ctx is None:
+            raise RuntimeError("the peer-memory exchange is not available on this group")
+        m, k = h.shape
+        with torch.cuda.device(h.device):
+            L.check(L.lib().wf_ar_reduce_add_rmsnorm(self._ctx, h.data_ptr(), weight.data_ptr(), y.data_ptr(), m, k, float(eps),
+                                                     L.FLAG_PDL if pdl else 0, torch.cuda.current_stream().cuda_stream),
+                    "wf_ar_reduce_add_rmsnorm")
+        return y
+
     def status(self) -> None:
         """Raises if a bounded wait for a peer ran out since the last call."""
         import ctypes as C
