@@ -244,7 +244,7 @@ typedef struct WF_ALIGN64 wf_problem {
     int64_t prefetch_bytes;
     /* Optional: the exchange of a row-parallel projection fused into this launch.  A device pointer obtained from
      * wf_ar_xchg: besides writing y, the launch pushes its partial output into every rank's exchange buffer and
-     * publishes the step; wf_ar_reduce_add_rmsnorm on every rank then sums the partial outputs (see there).  y must be a
+     * reports the delivered elements; wf_ar_reduce_add_rmsnorm on every rank then sums the partial outputs (see there).  y must be a
      * contiguous 16-bit tensor (ldy == N, N even) of at most the exchange's max_bytes; at most one problem of a launch
      * sets xchg.  NULL: none. */
     const void* xchg;

@@ -175,7 +175,7 @@ def _worker(rank, world, port, results):
         full = [torch.empty_like(m_tp.logits) for _ in range(world)]
         dist.all_gather(full, m_tp.logits.contiguous())
         assert torch.equal(torch.cat(full, -1).float().argmax(-1), m_tp.next_tok)
-        # the fused exchange (the default for few sequences) against the exchange as a kernel of its own: same bits
+        # the fused exchange (the default from two sequences on) against the exchange as a kernel of its own: same bits
         assert m_tp.fuse_exchange
         m_sep = TernaryDecoder(cfg, 3, 16, dev, seed=3, fuse_exchange=False)
         assert not m_sep.fuse_exchange

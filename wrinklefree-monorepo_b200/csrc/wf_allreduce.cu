@@ -158,7 +158,7 @@ __device__ __forceinline__ uint32_t xr_pack(float lo, float hi) {
 }
 __device__ __forceinline__ float xr_round(float v) { return __bfloat162float(__float2bfloat16_rn(v)); }
 
-__global__ void __launch_bounds__(XR_THREADS) reduce_add_rmsnorm_kernel(const wf_xchg* __restrict__ xd, __nv_bfloat16* __restrict__ h,
+__global__ void __launch_bounds__(XR_THREADS) reduce_add_rmsnorm_kernel(const wf_xchg x, __nv_bfloat16* __restrict__ h,
                                                                         const __nv_bfloat16* __restrict__ w, __nv_bfloat16* __restrict__ y,
                                                                         int K, float eps) {
     __shared__ float sh[XR_THREADS / 32];
@@ -173,14 +173,22 @@ __global__ void __launch_bounds__(XR_THREADS) reduce_add_rmsnorm_kernel(const wf
         if (i < chunks) wv[c] = __ldg(reinterpret_cast<const uint4*>(w) + i);
     }
     asm volatile("griddepcontrol.wait;\n" ::: "memory");
-    const wf_xchg x = *xd;
     uint8_t* mine = static_cast<uint8_t*>(x.peer[x.rank]);
-    const unsigned step = *reinterpret_cast<volatile unsigned*>(mine + XCHG_PSTEP_OFF) + 1;
-    // every rank has pushed this step: poll this rank's own flag words (bounded)
+    // the count of consumed exchanges and both slots' counters are requested together: one round trip, not two
+    const volatile unsigned* pstep_p = reinterpret_cast<volatile unsigned*>(mine + XCHG_PSTEP_OFF);
+    unsigned* const counts0 = reinterpret_cast<unsigned*>(mine + XCHG_PCOUNT_OFF);
+    unsigned first[2] = {0u, 0u};
     if (tid < x.world) {
-        const unsigned* f = reinterpret_cast<const unsigned*>(mine + XCHG_PFLAG_OFF) + tid;
+        first[0] = xchg_ld_acquire_sys(counts0 + tid);
+        first[1] = xchg_ld_acquire_sys(counts0 + 8 + tid);
+    }
+    const unsigned step = *pstep_p + 1;
+    unsigned* counts = counts0 + (step & 1) * 8;
+    // every rank has delivered all of its M x K elements of this step: poll this rank's own counters (bounded)
+    if (tid < x.world) {
+        const unsigned want = gridDim.x * static_cast<unsigned>(K);
         unsigned it = 0;
-        while (static_cast<int>(xchg_ld_acquire_sys(f) - step) < 0) {  // flags only grow
+        while ((it == 0 ? first[step & 1] : xchg_ld_acquire_sys(counts + tid)) < want) {
             if (++it > AR_SPIN_LIMIT) {
                 atomicExch(reinterpret_cast<unsigned*>(mine + XCHG_STATUS_OFF), static_cast<unsigned>(WF_E_LIMIT));
                 break;
@@ -240,6 +248,8 @@ __global__ void __launch_bounds__(XR_THREADS) reduce_add_rmsnorm_kernel(const wf
         unsigned* ticket = reinterpret_cast<unsigned*>(mine + XCHG_CTICKET_OFF);
         if (atomicAdd(ticket, 1u) == gridDim.x - 1) {
             *ticket = 0;
+            for (int r = 0; r < x.world; ++r) counts[r] = 0;  // the slot's next use is two exchanges away
+            __threadfence();
             *reinterpret_cast<volatile unsigned*>(mine + XCHG_PSTEP_OFF) = step;
         }
     }
@@ -338,7 +348,12 @@ extern "C" int wf_ar_reduce_add_rmsnorm(void* ctx, void* h, const void* weight, 
         lc.attrs = attr;
         lc.numAttrs = 1;
     }
-    const wf_xchg* desc = reinterpret_cast<const wf_xchg*>(c->local + XCHG_DESC_OFF);
+    wf_xchg desc = {};
+    desc.world = c->world;
+    desc.rank = c->rank;
+    desc.slot_bytes = c->max_bytes;
+    desc.push_off = AR_HEADER + 2 * c->max_bytes;
+    for (int r = 0; r < c->world; ++r) desc.peer[r] = c->peers.base[r];
     WF_CUDA(cudaLaunchKernelEx(&lc, reduce_add_rmsnorm_kernel, desc, static_cast<__nv_bfloat16*>(h), static_cast<const __nv_bfloat16*>(weight),
                                static_cast<__nv_bfloat16*>(y), static_cast<int>(K), eps));
     return WF_OK;
@@ -409,8 +424,8 @@ extern "C" int wf_ar_set_step(void* ctx, unsigned step) {
     WF_CUDA(cudaDeviceSynchronize());
     const unsigned words[3] = {step, 0u, 0u};  // step | ticket | status
     WF_CUDA(cudaMemcpy(c->local + 2048, words, sizeof(words), cudaMemcpyHostToDevice));
-    const unsigned pwords[3] = {step, 0u, 0u};  // consumed exchanges | producer ticket | consumer ticket
-    WF_CUDA(cudaMemcpy(c->local + XCHG_PSTEP_OFF, pwords, sizeof(pwords), cudaMemcpyHostToDevice));
+    const unsigned pwords[18] = {0u, 0u, 0u, 0u, 0u, 0u, 0u, 0u, 0u, 0u, 0u, 0u, 0u, 0u, 0u, 0u, step, 0u};  // delivered elements [2][8] | consumed exchanges | consumer ticket
+    WF_CUDA(cudaMemcpy(c->local + XCHG_PCOUNT_OFF, pwords, sizeof(pwords), cudaMemcpyHostToDevice));
     return WF_OK;
 }
 

@@ -48,6 +48,7 @@ constexpr int TILE_BYTES = 2048;  // one unit of packed weights in a stage: 16 r
 constexpr int DEC_CONSUMERS = 512;               // 16 consumer warps
 constexpr int NW = DEC_CONSUMERS / 32;
 constexpr int DEC_THREADS = DEC_CONSUMERS + 32;  // + 1 producer warp
+constexpr int XCHG_SMEM_OFF = 272;  // shared-memory bytes 272 .. 371: the exchange descriptor of a pushing launch (free in both kernels)
 constexpr int TOK_STRIDE = 576;  // bytes of shared memory per (k-block, token): 512 + 64 skew (conflict-free 128-bit reads)
 constexpr int MAX_STAGES = 16;
 
@@ -600,14 +601,15 @@ __device__ __forceinline__ void issue_l2_prefetch(const wf_problem* __restrict__
 }
 
 // The push side of a fused exchange: copies what this CTA has produced (the items [beg, end) of the work list; rows_item
-// rows each) from its local outputs into every rank's exchange buffer, then reports the CTA as finished.  Called by the
-// `nthreads` threads that made the stores, after all of them have passed a barrier; every CTA of the grid calls it, with
-// an empty range when it had no work.  Consecutive items of one (problem, token pass) go out as one block of rows.
+// rows each) from its local outputs into every rank's exchange buffer and reports the number of elements.  Called by the
+// `nthreads` threads that made the stores, after all of them have passed a barrier.  Consecutive items of one (problem,
+// token pass) go out as one block of rows.  A CTA without work has nothing to report.
 template <int NTHREADS>
 __device__ __forceinline__ void xchg_push_items(const DecodeCfg& cfg, const wf_problem* __restrict__ probs, int beg, int end, int rows_item,
-                                                const int* s_ib, int uni, int tid, unsigned grid) {
-    const wf_xchg* x = static_cast<const wf_xchg*>(cfg.xchg);
-    const unsigned step = xchg_step(x);
+                                                const int* s_ib, int uni, int tid, const uint8_t* s_xchg) {
+    const wf_xchg* x = reinterpret_cast<const wf_xchg*>(s_xchg);  // fetched into shared memory at the kernel's start
+    const unsigned step = *reinterpret_cast<const unsigned*>(s_xchg + 96) + 1;
+    unsigned elems = 0;
     for (int it = beg; it < end;) {
         int local;
         const int pi = locate_problem(probs, cfg.P, it, s_ib, cfg.ib_cap, local, uni);
@@ -616,14 +618,16 @@ __device__ __forceinline__ void xchg_push_items(const DecodeCfg& cfg, const wf_p
         const int run = min(end - it, row_items - ritem);
         const int64_t bytes = static_cast<int64_t>(q->M) * q->N * 2;
         if (q->xchg != nullptr && static_cast<uint64_t>(bytes) <= x->slot_bytes) {
-            const int m0 = chunk * cfg.MTA;
-            xchg_push_block(x, step, static_cast<const uint16_t*>(q->y), q->ldy, q->N, m0, min(q->M, m0 + cfg.MTA), ritem * rows_item,
-                            min(q->N, (ritem + run) * rows_item), tid, NTHREADS);
+            const int m0 = chunk * cfg.MTA, m1 = min(q->M, m0 + cfg.MTA);
+            const int r0 = ritem * rows_item, r1 = min(q->N, (ritem + run) * rows_item);
+            xchg_push_block(x, step, static_cast<const uint16_t*>(q->y), q->ldy, q->N, m0, m1, r0, r1, tid, NTHREADS);
+            elems += static_cast<unsigned>((m1 - m0) * (r1 - r0));
         }
         it += run;
     }
+    if (elems == 0) return;  // uniform over the CTA
     asm volatile("bar.sync 3, %0;\n" ::"n"(NTHREADS) : "memory");  // every thread's peer stores are issued
-    if (tid == 0) xchg_cta_done(x, step, grid);
+    if (tid == 0) xchg_report(x, step, elems);
 }
 
 template <int XDT, int NT, bool FOURACC>
@@ -718,6 +722,8 @@ __global__ void __launch_bounds__(DEC_THREADS, 1)
     }
     // x may be produced by the previous kernel of the stream
     asm volatile("griddepcontrol.wait;\n" ::: "memory");
+    uint8_t* const s_xchg = smem + XCHG_SMEM_OFF;
+    if (cfg.xchg) xchg_fetch_async(cfg.xchg, s_xchg, tid);  // used at the end
     consumer_sync();
 
     if (cfg.wide) {
@@ -726,7 +732,7 @@ __global__ void __launch_bounds__(DEC_THREADS, 1)
         // any more.  With all 16 warps on one item at a time, the two barriers and the shared-memory reduction per
         // item (about 0.7 us) made a 29 MB gate/up launch compute-latency-bound.
         if (beg >= end) {
-            if (cfg.xchg) xchg_push_items<DEC_CONSUMERS>(cfg, probs, beg, beg, rows_item, s_ib, 0, tid, gridDim.x);
+            if (cfg.xchg) xchg_fetch_wait(tid);  // no copy is left in flight
             return;
         }
         const int m_all = min(cfg.MTA, p.M);
@@ -792,8 +798,9 @@ __global__ void __launch_bounds__(DEC_THREADS, 1)
             }
         }
         if (cfg.xchg) {
+            xchg_fetch_wait(tid);
             consumer_sync();  // every warp's outputs are written
-            xchg_push_items<DEC_CONSUMERS>(cfg, probs, beg, end, rows_item, s_ib, 0, tid, gridDim.x);
+            xchg_push_items<DEC_CONSUMERS>(cfg, probs, beg, end, rows_item, s_ib, 0, tid, s_xchg);
         }
         return;
     }
@@ -878,8 +885,9 @@ __global__ void __launch_bounds__(DEC_THREADS, 1)
         }
     }
     if (cfg.xchg) {
+        xchg_fetch_wait(tid);
         consumer_sync();  // every thread's outputs are written
-        xchg_push_items<DEC_CONSUMERS>(cfg, probs, beg, end, rows_item, s_ib, 0, tid, gridDim.x);
+        xchg_push_items<DEC_CONSUMERS>(cfg, probs, beg, end, rows_item, s_ib, 0, tid, s_xchg);
     }
 }
 
@@ -936,13 +944,7 @@ __global__ void __launch_bounds__(STREAM_THREADS, 2)
     int beg, end;
     if (cfg.cpp > 0) {
         const int pi = blockIdx.x / cfg.cpp, sub = blockIdx.x % cfg.cpp;
-        if (pi >= cfg.P) {
-            if (cfg.xchg) {
-                asm volatile("griddepcontrol.wait;\n" ::: "memory");  // the step follows from the previous exchange's consumer
-                xchg_push_items<STREAM_THREADS>(cfg, probs, 0, 0, 16, s_ib, uni, tid, gridDim.x);
-            }
-            return;
-        }
+        if (pi >= cfg.P) return;
         const int ib = first_item(probs, pi, s_ib, cfg.ib_cap, uni);
         const int cnt = (pi + 1 < cfg.P ? first_item(probs, pi + 1, s_ib, cfg.ib_cap, uni) : cfg.total_items) - ib;
         const int q = cnt / cfg.cpp, r = cnt - q * cfg.cpp;  // the first r CTAs of the problem take one item more
@@ -953,13 +955,7 @@ __global__ void __launch_bounds__(STREAM_THREADS, 2)
         beg = bx * cfg.items_q + min(bx, cfg.items_r);
         end = beg + cfg.items_q + (bx < cfg.items_r ? 1 : 0);
     }
-    if (beg >= end) {
-        if (cfg.xchg) {
-            asm volatile("griddepcontrol.wait;\n" ::: "memory");
-            xchg_push_items<STREAM_THREADS>(cfg, probs, 0, 0, 16, s_ib, uni, tid, gridDim.x);
-        }
-        return;
-    }
+    if (beg >= end) return;
     // Warp w starts with item beg + w; every further item is claimed from this counter when a warp has consumed its
     // stage, so a warp that meets slower memory channels takes fewer items instead of holding the CTA back.
     int* s_next = reinterpret_cast<int*>(smem + 260);
@@ -1037,6 +1033,8 @@ __global__ void __launch_bounds__(STREAM_THREADS, 2)
     // The weights never depend on the previous kernel, x normally does: request weights, wait, read x.  Where the
     // caller states that x is ready, the reads of x are started first and only the stores wait for the previous kernel.
     if (!cfg.x_ready) asm volatile("griddepcontrol.wait;\n" ::: "memory");
+    uint8_t* const s_xchg = smem + XCHG_SMEM_OFF;
+    if (cfg.xchg) xchg_fetch_async(cfg.xchg, s_xchg, tid);  // used at the end (a pushing launch always waits here: see run_group)
     if (uni > 0 && !early) {  // x is found through the heads
         store_heads();
         __syncthreads();
@@ -1200,8 +1198,9 @@ __global__ void __launch_bounds__(STREAM_THREADS, 2)
     // a kernel that follows with a programmatic dependency relies on this grid having waited for its own predecessor
     if (!may_store) asm volatile("griddepcontrol.wait;\n" ::: "memory");
     if (cfg.xchg) {
+        xchg_fetch_wait(tid);
         __syncthreads();  // every warp's outputs are written
-        xchg_push_items<STREAM_THREADS>(cfg, probs, beg, end, 16, s_ib, uni, tid, gridDim.x);
+        xchg_push_items<STREAM_THREADS>(cfg, probs, beg, end, 16, s_ib, uni, tid, s_xchg);
     }
 }
 
@@ -1494,7 +1493,7 @@ static int run_group(const char* who, const wf_problem* dev, wf_problem* host, i
     cfg.prefetch = 0;
     if (P <= 8)
         for (int i = 0; i < P; ++i) cfg.prefetch |= (host[i].prefetch != nullptr && host[i].prefetch_bytes > 0) ? 1 : 0;
-    cfg.x_ready = (flags & WF_FLAG_X_READY) ? 1 : 0;
+    cfg.x_ready = ((flags & WF_FLAG_X_READY) && !cfg.xchg) ? 1 : 0;  // a pushing launch reads the exchange's step after its predecessors
     cfg.wide = (!g.decoupled && g.RI == 1 && g.total_items >= 3LL * g.grid && shares_x(host, P, g.MTA)) ? 1 : 0;
     cfg.items_q = g.total_items / g.grid; cfg.items_r = g.total_items % g.grid;
     cfg.uniform_items = 0;
@@ -1516,6 +1515,9 @@ static int run_group(const char* who, const wf_problem* dev, wf_problem* host, i
         if (ok) { cfg.x_early = 1; cfg.x_stride = dx; }
     }
     cudaStream_t st = static_cast<cudaStream_t>(stream);
+    // A group of one problem travels as a kernel parameter, like a single launch: its fields and tensor maps are then read
+    // without a round trip to global memory at the kernel's entry.
+    if (P == 1) dev = nullptr;
     switch (host[0].x_dtype) {
         case WF_F32: return dispatch_nt<WF_F32>(dev, host[0], cfg, g, flags, st);
         case WF_BF16: return dispatch_nt<WF_BF16>(dev, host[0], cfg, g, flags, st);

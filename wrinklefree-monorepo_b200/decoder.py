@@ -84,7 +84,8 @@ class TernaryDecoder:
         grouped kernel (six launches per layer instead of ten); measured on B200 the separate norm / activation kernels,
         which overlap the projections' weight streaming through programmatic launches, are faster, so it is off by
         default.  `fuse_exchange` (tensor parallel, up to 8 sequences, bf16): the row-parallel projections push their partial
-        outputs to every rank inside their own launch and the residual add + RMSNorm that follows sums them (on unless False)."""
+        outputs to every rank inside their own launch and the residual add + RMSNorm that follows sums them (default: from two
+        sequences on; True / False force it)."""
         self._fuse_opt = fuse
         # tensor parallel, few tokens: False keeps the exchange after o_proj / down_proj a kernel of its own
         self._xchg_opt = fuse_exchange
@@ -203,8 +204,12 @@ class TernaryDecoder:
         if self.tp > 1 and self._xchg_opt is not False:
             if self._oneshot is None:
                 self._oneshot = tpmod.OneShotAllReduce(self.group, max_bytes=64 << 10)  # measured: NCCL is faster from 256 KB on
-            self.fuse_exchange = (dt == torch.bfloat16 and not self.big and not self.fused and cfg.hidden % 8 == 0 and cfg.hidden <= 16384
-                                  and B * cfg.hidden * 2 <= self._oneshot.max_bytes and self._oneshot.xchg_ptr() is not None)
+            # measured on two B200s, 8B shape: 2 % faster than the exchange as a kernel of its own at 4 sequences, 2-5 %
+            # slower at 1 (every CTA of the projection ends with its push): on from two sequences unless asked for
+            wanted = self._xchg_opt is True or B >= 2
+            self.fuse_exchange = (wanted and dt == torch.bfloat16 and not self.big and not self.fused and cfg.hidden % 8 == 0
+                                  and cfg.hidden <= 16384 and B * cfg.hidden * 2 <= self._oneshot.max_bytes
+                                  and self._oneshot.xchg_ptr() is not None)
         mode = "silu" if cfg.act == "silu" else "relu2"
         prev_down = None
         for li, L in enumerate(self.layers):
