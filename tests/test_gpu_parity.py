@@ -622,3 +622,26 @@ def test_training_step_on_packed_weights(wf, dt, tol):
         assert rel(y3, want3) <= 1e-6
     finally:
         wf.set_global_lambda_warmup(None)
+
+
+@pytest.mark.parametrize("k", [64, 512, 1024, 1536, 2560])
+@pytest.mark.parametrize("m", [16, 33, 64])
+def test_few_token_contraction_stage_counts(wf, k, m):
+    """The few-token forms of the contraction share the K stages out among two or three issuing threads with partial
+    accumulators: every count of stages per tile (fewer than issuing threads, equal, more, not a multiple), one layer
+    and a stack, against the decode kernel's outputs bit for bit (both are held to the oracle elsewhere)."""
+    g = torch.Generator(device=DEV).manual_seed(k + m)
+    n = 384
+    for layers in (1, 5):
+        codes = torch.empty(layers, n, k // 4, dtype=torch.uint8, device=DEV)
+        scales = torch.empty(layers, 2, device=DEV)
+        for i in range(layers):
+            c, s = wf.pack_ternary(torch.randn(n, k, generator=g, device=DEV) * 0.02)
+            codes[i].copy_(c)
+            scales[i].copy_(s)
+        x = torch.randn(layers, m, k, generator=g, device=DEV).bfloat16()
+        y = torch.empty(layers, m, n, dtype=torch.float32, device=DEV)
+        wf.bitlinear_batched(x, codes, scales, out=y)
+        for i in range(layers):
+            assert torch.equal(wf.bitlinear(x[i], codes[i], scales[i], out_dtype=torch.float32, path="decode"), y[i]), (layers, i)
+    wf.device_status()
