@@ -300,6 +300,17 @@ int wf_add_rmsnorm_bf16(void* h, const void* delta, const void* weight, void* y,
 int wf_rope_kv_bf16(void* q, const void* k, const void* v, const float* cos, const float* sin, const int64_t* pos, void* kcache,
                     void* vcache, int64_t B, int nq, int nkv, int D, int T, unsigned flags, void* stream);
 int wf_act_mul_bf16(const void* gate, const void* up, void* out, int64_t n, int mode, unsigned flags, void* stream);
+/*
+ * The same two kernels with the per-token int8 quantization of the projection that follows fused in (the reference's
+ * fused CPU layer shares one activation quantization between gate and up and the A100 stack quantizes inside its norm:
+ * sgl-kernel/csrc/cpu/bitnet_fused_layer.cpp:150-375, BitNet/gpu/model.py:54-76): q [M, K] int8 and q_scale [M] receive
+ * what wf_act_quant_i8(WF_ACT_PER_TOKEN, quant_eps) would produce from the bf16 result, bit for bit; the bf16 result
+ * itself is written only when y / out is not NULL.  Rows of a multiple of 8 elements, at most 16384.
+ */
+int wf_add_rmsnorm_quant_bf16(void* h, const void* delta, const void* weight, void* y, int8_t* q, float* q_scale, int64_t M,
+                              int64_t K, float eps, float quant_eps, unsigned flags, void* stream);
+int wf_act_mul_quant_bf16(const void* gate, const void* up, void* out, int8_t* q, float* q_scale, int64_t M, int64_t I, int mode,
+                          float quant_eps, unsigned flags, void* stream);
 
 /*
  * Decode-step attention over the bf16 KV cache (one new token per sequence, grouped-query heads): for every query head

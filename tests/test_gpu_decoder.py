@@ -327,3 +327,37 @@ def test_linear_bf16_rejects_what_it_cannot_run(wf):
         wf.linear_bf16(x.float(), w)
     with pytest.raises(RuntimeError):
         wf.linear_bf16(x[:, :60], w[:, :60])  # K not a multiple of 8
+
+
+@pytest.mark.parametrize("m,k", [(1, 4096), (5, 576), (3, 14336), (2, 16384), (33, 2048)])
+def test_norm_and_activation_with_fused_quantization(wf, m, k):
+    """The residual add + RMSNorm and the gate activation that quantize their own result: int8 codes, per-token multipliers,
+    the updated residual stream and the optional bf16 copy equal the unfused chain (kernel, then act_quant_i8) bit for bit."""
+    from wrinklefree_monorepo_b200 import ops
+
+    dev = torch.device("cuda", 0)
+    g = torch.Generator(device=dev).manual_seed(m * 100 + k)
+    h0 = torch.randn(m, k, generator=g, device=dev).bfloat16()
+    delta = torch.randn(m, k, generator=g, device=dev).bfloat16()
+    w = (torch.rand(k, generator=g, device=dev) + 0.5).bfloat16()
+    for d in (delta, None):
+        h_ref, y_ref = h0.clone(), torch.empty_like(h0)
+        ops.add_rmsnorm_(h_ref, d, w, y_ref, 1e-5)
+        q_ref, s_ref = wf.act_quant_i8(y_ref, eps=1e-5)
+        h_f, y_f = h0.clone(), torch.empty_like(h0)
+        q = torch.empty(m, k, dtype=torch.int8, device=dev)
+        s = torch.empty(m, dtype=torch.float32, device=dev)
+        ops.add_rmsnorm_quant_(h_f, d, w, q, s, 1e-5, out=y_f)
+        assert torch.equal(h_f, h_ref) and torch.equal(y_f, y_ref) and torch.equal(q, q_ref) and torch.equal(s, s_ref)
+        q2, s2 = torch.empty_like(q), torch.empty_like(s)
+        ops.add_rmsnorm_quant_(h0.clone(), d, w, q2, s2, 1e-5)  # without the bf16 copy
+        assert torch.equal(q2, q_ref) and torch.equal(s2, s_ref)
+    up = torch.randn(m, k, generator=g, device=dev).bfloat16()
+    for mode in ("silu", "relu2"):
+        a_ref = ops.act_mul(h0, up, torch.empty_like(h0), mode)
+        q_ref, s_ref = wf.act_quant_i8(a_ref, eps=1e-5)
+        q = torch.empty(m, k, dtype=torch.int8, device=dev)
+        s = torch.empty(m, dtype=torch.float32, device=dev)
+        out = torch.empty_like(h0)
+        ops.act_mul_quant(h0, up, q, s, mode, out=out)
+        assert torch.equal(out, a_ref) and torch.equal(q, q_ref) and torch.equal(s, s_ref)

@@ -150,7 +150,7 @@ def test_act_quant_many_tokens(wf, k, dt):
     m = 203
     x = gi.with_outliers(torch.randn(m, k, generator=g), seed=k)
     x[5] = 0
-    x[6] *= 1e-6
+    x[6] *= 1e-3 if dt == "f16" else 1e-6  # small against eps, still a normal number in every type
     xd = x.to(TDT[dt])
     q, s, rs = wf.act_quant_i8(xd.to(DEV), want_rowsum=True)
     qo, so = O.act_quant_per_token(xd.float().numpy(), dt)

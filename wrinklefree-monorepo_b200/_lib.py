@@ -76,6 +76,8 @@ _SIGNATURES = {
     "wf_act_mul_bf16": (_int, [_p, _p, _p, _i64, _int, _u32, _p]),
     "wf_attn_decode_workspace_bytes": (_sz, [_i64, _int, _int, _int, _int]),
     "wf_attn_decode_bf16": (_int, [_p, _p, _p, _p, _p, _i64, _int, _int, _int, _int, _f32, _p, _sz, _u32, _p]),
+    "wf_add_rmsnorm_quant_bf16": (_int, [_p, _p, _p, _p, _p, _p, _i64, _i64, _f32, _f32, _u32, _p]),
+    "wf_act_mul_quant_bf16": (_int, [_p, _p, _p, _p, _p, _i64, _i64, _int, _f32, _u32, _p]),
     "wf_linear_bf16": (_int, [_p, _i64, _p, _i64, _p, _int, _i64, _i64, _i64, _i64, _u32, _p]),
     "wf_ar_handle_bytes": (_int, []),
     "wf_ar_init": (_int, [_int, _int, _sz, C.POINTER(C.c_void_p), _p]),

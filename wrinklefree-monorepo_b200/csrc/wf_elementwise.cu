@@ -19,15 +19,52 @@ __device__ __forceinline__ float round_bf(float v) { return bf(__float2bfloat16_
 __device__ __forceinline__ void pdl_trigger() { asm volatile("griddepcontrol.launch_dependents;\n" ::: "memory"); }
 __device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;\n" ::: "memory"); }
 
+// Per-token int8 quantization of a row that a block holds in registers as packed bf16 pairs (chunk c of thread t = elements
+// 8 * (t + c * THREADS) .. + 7): block-wide absmax, then the arithmetic of act_quant_token_kernel<bf16>.  `sh` is a
+// scratch of THREADS / 32 floats that the caller no longer reads.
+template <int THREADS, int CHUNKS>
+__device__ __forceinline__ void quantize_row_bf16(const uint32_t (&o)[CHUNKS][4], float mx, int chunks, int tid, float* sh, int8_t* qrow,
+                                                  float* scale_out, float q_eps) {
+#pragma unroll
+    for (int s = 16; s > 0; s >>= 1) mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, s));
+    __syncthreads();  // the scratch is free
+    if ((tid & 31) == 0) sh[tid >> 5] = mx;
+    __syncthreads();
+    float tot = sh[0];
+#pragma unroll
+    for (int i = 1; i < THREADS / 32; ++i) tot = fmaxf(tot, sh[i]);
+    const float sc = act_scale_from_absmax<WF_BF16>(tot, q_eps);
+#pragma unroll
+    for (int c = 0; c < CHUNKS; ++c) {
+        const int i = tid + c * THREADS;
+        if (i < chunks) {
+            uint32_t w0 = 0, w1 = 0;
+#pragma unroll
+            for (int e = 0; e < 2; ++e) {
+                const int a0 = quantize_one<WF_BF16>(bf_lo(o[c][e]), sc), a1 = quantize_one<WF_BF16>(bf_hi(o[c][e]), sc);
+                const int b0 = quantize_one<WF_BF16>(bf_lo(o[c][2 + e]), sc), b1 = quantize_one<WF_BF16>(bf_hi(o[c][2 + e]), sc);
+                w0 |= (static_cast<uint32_t>(a0 & 0xff) << (16 * e)) | (static_cast<uint32_t>(a1 & 0xff) << (16 * e + 8));
+                w1 |= (static_cast<uint32_t>(b0 & 0xff) << (16 * e)) | (static_cast<uint32_t>(b1 & 0xff) << (16 * e + 8));
+            }
+            *reinterpret_cast<uint2*>(qrow + 8 * static_cast<int64_t>(i)) = make_uint2(w0, w1);
+        }
+    }
+    if (tid == 0) *scale_out = sc;
+}
+
 constexpr int NORM_THREADS = 512;
 constexpr int NORM_CHUNKS = 4;  // 8-element chunks per thread held in registers: rows up to 16384 elements
 
 // h[m, :] += delta[m, :] (when delta != nullptr); y[m, :] = h * rsqrt(mean(h^2) + eps) * w.  One block per row.
 // VEC: K % 8 == 0 and K <= NORM_THREADS * NORM_CHUNKS * 8, the row stays in registers; else two passes over global memory.
+// With `q` (VEC only) the normalised row is also quantized to int8 per token, with the arithmetic of the stand-alone
+// quantization kernel on the bf16 values (absmax, multiplier 127 / max rounded like torch's, round half to even): the
+// projections that follow read q and q_scale and no kernel stands between the norm and them; y may then be null.
 template <bool VEC>
 __global__ void __launch_bounds__(NORM_THREADS) add_rmsnorm_kernel(__nv_bfloat16* __restrict__ h, const __nv_bfloat16* __restrict__ delta,
                                                                    const __nv_bfloat16* __restrict__ w, __nv_bfloat16* __restrict__ y,
-                                                                   int K, float eps) {
+                                                                   int K, float eps, int8_t* __restrict__ q, float* __restrict__ q_scale,
+                                                                   float q_eps) {
     __shared__ float sh[NORM_THREADS / 32];
     pdl_trigger();
     const int64_t m = blockIdx.x;
@@ -93,19 +130,25 @@ __global__ void __launch_bounds__(NORM_THREADS) add_rmsnorm_kernel(__nv_bfloat16
     // normalise in fp32, round to bf16, then scale by the bf16 weight (the order of the unfused operator chain)
     if constexpr (VEC) {
         const int chunks = K >> 3;
-        uint4* yrow = reinterpret_cast<uint4*>(y + m * K);
+        uint4* yrow = y ? reinterpret_cast<uint4*>(y + m * K) : nullptr;
+        uint32_t o[NORM_CHUNKS][4];
+        float mx = 0.f;
 #pragma unroll
         for (int c = 0; c < NORM_CHUNKS; ++c) {
             const int i = tid + c * NORM_THREADS;
             if (i < chunks) {
                 const uint32_t a[4] = {hv[c].x, hv[c].y, hv[c].z, hv[c].w};
                 const uint32_t g[4] = {wv[c].x, wv[c].y, wv[c].z, wv[c].w};
-                uint32_t o[4];
 #pragma unroll
-                for (int e = 0; e < 4; ++e)
-                    o[e] = pack_bf(round_bf(bf_lo(a[e]) * r) * bf_lo(g[e]), round_bf(bf_hi(a[e]) * r) * bf_hi(g[e]));
-                yrow[i] = make_uint4(o[0], o[1], o[2], o[3]);
+                for (int e = 0; e < 4; ++e) {
+                    o[c][e] = pack_bf(round_bf(bf_lo(a[e]) * r) * bf_lo(g[e]), round_bf(bf_hi(a[e]) * r) * bf_hi(g[e]));
+                    mx = fmaxf(mx, fmaxf(fabsf(bf_lo(o[c][e])), fabsf(bf_hi(o[c][e]))));
+                }
+                if (y) yrow[i] = make_uint4(o[c][0], o[c][1], o[c][2], o[c][3]);
             }
+        }
+        if (q) {
+            quantize_row_bf16<NORM_THREADS, NORM_CHUNKS>(o, mx, chunks, tid, sh, q + m * K, q_scale + m, q_eps);
         }
     } else {
         for (int k = tid * 2; k < K; k += NORM_THREADS * 2) {
@@ -185,6 +228,37 @@ __global__ void __launch_bounds__(256) act_mul_kernel(const __nv_bfloat16* __res
         out[i] = __float2bfloat16_rn(act_one(bf(g[i]), mode) * bf(u[i]));
 }
 
+// act(g) * u of one token row per block, quantized to int8 per token on the way (and written as bf16 when `out` is given):
+// the activation in front of down_proj together with the quantization that projection would otherwise run itself.
+constexpr int AMQ_THREADS = 512;
+constexpr int AMQ_CHUNKS = 4;  // rows up to 16384 elements
+__global__ void __launch_bounds__(AMQ_THREADS) act_mul_quant_kernel(const __nv_bfloat16* __restrict__ g, const __nv_bfloat16* __restrict__ u,
+                                                                    __nv_bfloat16* __restrict__ out, int8_t* __restrict__ q,
+                                                                    float* __restrict__ q_scale, int I, int mode, float q_eps) {
+    __shared__ float sh[AMQ_THREADS / 32];
+    pdl_trigger();
+    pdl_wait();
+    const int64_t m = blockIdx.x;
+    const int tid = threadIdx.x, chunks = I >> 3;
+    uint32_t o[AMQ_CHUNKS][4];
+    float mx = 0.f;
+#pragma unroll
+    for (int c = 0; c < AMQ_CHUNKS; ++c) {
+        const int i = tid + c * AMQ_THREADS;
+        if (i < chunks) {
+            const uint4 a = __ldg(reinterpret_cast<const uint4*>(g + m * I) + i), b = __ldg(reinterpret_cast<const uint4*>(u + m * I) + i);
+            const uint32_t av[4] = {a.x, a.y, a.z, a.w}, bv[4] = {b.x, b.y, b.z, b.w};
+#pragma unroll
+            for (int e = 0; e < 4; ++e) {
+                o[c][e] = pack_bf(act_one(bf_lo(av[e]), mode) * bf_lo(bv[e]), act_one(bf_hi(av[e]), mode) * bf_hi(bv[e]));
+                mx = fmaxf(mx, fmaxf(fabsf(bf_lo(o[c][e])), fabsf(bf_hi(o[c][e]))));
+            }
+            if (out) reinterpret_cast<uint4*>(out + m * I)[i] = make_uint4(o[c][0], o[c][1], o[c][2], o[c][3]);
+        }
+    }
+    quantize_row_bf16<AMQ_THREADS, AMQ_CHUNKS>(o, mx, chunks, tid, sh, q + m * I, q_scale + m, q_eps);
+}
+
 template <typename... KArgs, typename... Args>
 static cudaError_t launch(void (*kernel)(KArgs...), unsigned grid, unsigned block, unsigned flags, void* stream, Args... args) {
     cudaLaunchConfig_t lc = {};
@@ -215,7 +289,37 @@ extern "C" int wf_add_rmsnorm_bf16(void* h, const void* delta, const void* weigh
                      (!delta || al16(delta));
     WF_CUDA(launch(vec ? add_rmsnorm_kernel<true> : add_rmsnorm_kernel<false>, static_cast<unsigned>(M), NORM_THREADS, flags, stream,
                    static_cast<__nv_bfloat16*>(h), static_cast<const __nv_bfloat16*>(delta), static_cast<const __nv_bfloat16*>(weight),
-                   static_cast<__nv_bfloat16*>(y), static_cast<int>(K), eps));
+                   static_cast<__nv_bfloat16*>(y), static_cast<int>(K), eps, static_cast<int8_t*>(nullptr), static_cast<float*>(nullptr), 0.f));
+    return WF_OK;
+}
+
+extern "C" int wf_add_rmsnorm_quant_bf16(void* h, const void* delta, const void* weight, void* y, int8_t* q, float* q_scale, int64_t M,
+                                         int64_t K, float eps, float quant_eps, unsigned flags, void* stream) {
+    WF_REQUIRE(h && weight && q && q_scale, "wf_add_rmsnorm_quant_bf16: null pointer");
+    auto al16 = [](const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15) == 0; };
+    WF_REQUIRE(M > 0 && M < (1LL << 31) && K > 0 && K % 8 == 0 && K <= static_cast<int64_t>(NORM_THREADS) * NORM_CHUNKS * 8,
+               "wf_add_rmsnorm_quant_bf16: K must be a multiple of 8, at most %d", NORM_THREADS * NORM_CHUNKS * 8);
+    WF_REQUIRE(al16(h) && al16(weight) && (!y || al16(y)) && (!delta || al16(delta)) && (reinterpret_cast<uintptr_t>(q) & 7) == 0,
+               "wf_add_rmsnorm_quant_bf16: tensors must be 16-byte aligned (q: 8)");
+    if (int rc = require_device()) return rc;
+    WF_CUDA(launch(add_rmsnorm_kernel<true>, static_cast<unsigned>(M), NORM_THREADS, flags, stream, static_cast<__nv_bfloat16*>(h),
+                   static_cast<const __nv_bfloat16*>(delta), static_cast<const __nv_bfloat16*>(weight), static_cast<__nv_bfloat16*>(y),
+                   static_cast<int>(K), eps, q, q_scale, quant_eps));
+    return WF_OK;
+}
+
+extern "C" int wf_act_mul_quant_bf16(const void* gate, const void* up, void* out, int8_t* q, float* q_scale, int64_t M, int64_t I, int mode,
+                                     float quant_eps, unsigned flags, void* stream) {
+    WF_REQUIRE(gate && up && q && q_scale, "wf_act_mul_quant_bf16: null pointer");
+    WF_REQUIRE(M > 0 && M < (1LL << 31) && I > 0 && I % 8 == 0 && I <= static_cast<int64_t>(AMQ_THREADS) * AMQ_CHUNKS * 8 && (mode == 0 || mode == 1),
+               "wf_act_mul_quant_bf16: rows of a multiple of 8 elements, at most %d; mode 0 or 1", AMQ_THREADS * AMQ_CHUNKS * 8);
+    auto al16 = [](const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15) == 0; };
+    WF_REQUIRE(al16(gate) && al16(up) && (!out || al16(out)) && (reinterpret_cast<uintptr_t>(q) & 7) == 0,
+               "wf_act_mul_quant_bf16: tensors must be 16-byte aligned (q: 8)");
+    if (int rc = require_device()) return rc;
+    WF_CUDA(launch(act_mul_quant_kernel, static_cast<unsigned>(M), static_cast<unsigned>(AMQ_THREADS), flags, stream,
+                   static_cast<const __nv_bfloat16*>(gate), static_cast<const __nv_bfloat16*>(up), static_cast<__nv_bfloat16*>(out), q, q_scale,
+                   static_cast<int>(I), mode, quant_eps));
     return WF_OK;
 }
 

@@ -210,6 +210,12 @@ class TernaryDecoder:
             self.fuse_exchange = (wanted and dt == torch.bfloat16 and not self.big and not self.fused and cfg.hidden % 8 == 0
                                   and cfg.hidden <= 16384 and B * cfg.hidden * 2 <= self._oneshot.max_bytes
                                   and self._oneshot.xchg_ptr() is not None)
+        # The norms in front of q/k/v and gate/up, and the activation (or its sub-norm) in front of down, quantize their
+        # result to int8 themselves where the projection would otherwise run a quantization kernel of its own.
+        i_loc = self.i_hi - self.i_lo
+        self.qnorm = (dt == torch.bfloat16 and not self.fused and not self.fuse_exchange and cfg.hidden % 8 == 0 and cfg.hidden <= 16384
+                      and ops._prequant(B, cfg.hidden, 2))
+        self.qact = (dt == torch.bfloat16 and not self.fused and i_loc % 8 == 0 and i_loc <= 16384 and ops._prequant(B, i_loc, 1))
         mode = "silu" if cfg.act == "silu" else "relu2"
         prev_down = None
         for li, L in enumerate(self.layers):
@@ -225,6 +231,13 @@ class TernaryDecoder:
                 L["actn"] = torch.empty(B, self.i_hi - self.i_lo, dtype=dt, device=dev)
             L["ob"] = torch.empty(B, cfg.hidden, dtype=dt, device=dev)
             L["db"] = torch.empty(B, cfg.hidden, dtype=dt, device=dev)
+            if self.qnorm:
+                for nm in ("xn", "hn"):
+                    L[nm + "_q"] = torch.empty(B, cfg.hidden, dtype=torch.int8, device=dev)
+                    L[nm + "_s"] = torch.empty(B, dtype=torch.float32, device=dev)
+            if self.qact:
+                L["act_q"] = torch.empty(B, i_loc, dtype=torch.int8, device=dev)
+                L["act_s"] = torch.empty(B, dtype=torch.float32, device=dev)
             if self.fused:
                 # q/k/v: rmsnorm(h + previous down output) -> h2;  gate/up: rmsnorm(h2 + o output) -> h
                 first = dict(x_mode="norm", x2=prev_down, norm_w=L["n1"], norm_eps=cfg.eps)
@@ -242,15 +255,17 @@ class TernaryDecoder:
                 nxt = self.layers[li + 1] if li + 1 < len(self.layers) else None
                 pf1 = {"q": L["o"][0], "k": L["gate"][0], "v": L["up"][0]} if self.prefetch else {}
                 pf2 = {"gate": L["down"][0], "up": nxt["q"][0] if nxt else None} if self.prefetch else {}
-                L["g_qkv"] = ops.DecodeGroup([dict(x=L["xn"], codes=L[n][0], w_scale=L[n][1], out=o, prefetch=pf1.get(n))
+                xin = dict(x=L["xn_q"], x_scale=L["xn_s"]) if self.qnorm else dict(x=L["xn"])
+                hin = dict(x=L["hn_q"], x_scale=L["hn_s"]) if self.qnorm else dict(x=L["hn"])
+                L["g_qkv"] = ops.DecodeGroup([dict(codes=L[n][0], w_scale=L[n][1], out=o, prefetch=pf1.get(n), **xin)
                                               for n, o in zip(("q", "k", "v"), L["qkv"])])
-                L["g_gu"] = ops.DecodeGroup([dict(x=L["hn"], codes=L[n][0], w_scale=L[n][1], out=o, prefetch=pf2.get(n))
+                L["g_gu"] = ops.DecodeGroup([dict(codes=L[n][0], w_scale=L[n][1], out=o, prefetch=pf2.get(n), **hin)
                                              for n, o in zip(("gate", "up"), L["gu"])])
                 if self.fuse_exchange:
                     xp = self._oneshot.xchg_ptr()
                     L["g_o"] = ops.DecodeGroup([dict(x=L["an"] if cfg.subln else L["attn"], codes=L["o"][0], w_scale=L["o"][1], out=L["ob"], xchg=xp)])
-                    L["g_down"] = ops.DecodeGroup([dict(x=L["actn"] if cfg.subln else L["act"], codes=L["down"][0], w_scale=L["down"][1],
-                                                        out=L["db"], xchg=xp)])
+                    din = dict(x=L["act_q"], x_scale=L["act_s"]) if self.qact else dict(x=L["actn"] if cfg.subln else L["act"])
+                    L["g_down"] = ops.DecodeGroup([dict(codes=L["down"][0], w_scale=L["down"][1], out=L["db"], xchg=xp, **din)])
 
     def _act(self, g, u):
         return (F.silu(g) if self.cfg.act == "silu" else F.relu(g).pow(2)) * u
@@ -280,6 +295,8 @@ class TernaryDecoder:
         for L in self.layers:
             if fx and delta is not None:  # the previous layer's down projection has pushed its partial outputs
                 self._oneshot.reduce_add_rmsnorm_(self.h, L["n1"], L["xn"], cfg.eps, pdl=True)
+            elif self.qnorm:
+                ops.add_rmsnorm_quant_(self.h, delta, L["n1"], L["xn_q"], L["xn_s"], cfg.eps, pdl=True)
             else:
                 ops.add_rmsnorm_(self.h, delta, L["n1"], L["xn"], cfg.eps, pdl=True)
             q, k, v = L["g_qkv"].run(pdl=True)
@@ -302,20 +319,32 @@ class TernaryDecoder:
                 self._oneshot.reduce_add_rmsnorm_(self.h, L["n2"], L["hn"], cfg.eps, pdl=True)
             else:
                 o = self._allreduce(ops.bitlinear(a, L["o"][0], L["o"][1], out=L["ob"], path=path, pdl=True))
-                ops.add_rmsnorm_(self.h, o, L["n2"], L["hn"], cfg.eps, pdl=True)
+                if self.qnorm:
+                    ops.add_rmsnorm_quant_(self.h, o, L["n2"], L["hn_q"], L["hn_s"], cfg.eps, pdl=True)
+                else:
+                    ops.add_rmsnorm_(self.h, o, L["n2"], L["hn"], cfg.eps, pdl=True)
             if big:
-                hq, hs = ops.act_quant_i8(L["hn"], eps=1e-5)  # one quantization for gate and up
+                # one quantization for gate and up
+                hq, hs = (L["hn_q"], L["hn_s"]) if self.qnorm else ops.act_quant_i8(L["hn"], eps=1e-5)
                 g, u = (ops.bitlinear(hq, L[n][0], L[n][1], x_scale=hs, out=o_, path="prefill")
                         for n, o_ in zip(("gate", "up"), L["gu"]))
             else:
                 g, u = L["g_gu"].run(pdl=True)
-            act = ops.act_mul(g, u, L["act"], self.cfg.act, pdl=True)
+            act_s = None
             if cfg.subln:
-                act = ops.add_rmsnorm_(act, None, L["sf"], L["actn"], cfg.subln_eps, pdl=True)
+                act = ops.act_mul(g, u, L["act"], self.cfg.act, pdl=True)
+                if self.qact:
+                    act, act_s = ops.add_rmsnorm_quant_(act, None, L["sf"], L["act_q"], L["act_s"], cfg.subln_eps, pdl=True)
+                else:
+                    act = ops.add_rmsnorm_(act, None, L["sf"], L["actn"], cfg.subln_eps, pdl=True)
+            elif self.qact:
+                act, act_s = ops.act_mul_quant(g, u, L["act_q"], L["act_s"], self.cfg.act, pdl=True)
+            else:
+                act = ops.act_mul(g, u, L["act"], self.cfg.act, pdl=True)
             if fx:
                 delta = L["g_down"].run(pdl=True)[0]
             else:
-                delta = self._allreduce(ops.bitlinear(act, L["down"][0], L["down"][1], out=L["db"], path=path, pdl=True))
+                delta = self._allreduce(ops.bitlinear(act, L["down"][0], L["down"][1], x_scale=act_s, out=L["db"], path=path, pdl=True))
         if fx:
             self._oneshot.reduce_add_rmsnorm_(self.h, self.norm_f, self.xf, cfg.eps, pdl=True)
         else:

@@ -441,6 +441,32 @@ def attn_decode(q: torch.Tensor, kcache: torch.Tensor, vcache: torch.Tensor, pos
     return out
 
 
+def add_rmsnorm_quant_(h: torch.Tensor, delta: Optional[torch.Tensor], weight: torch.Tensor, q: torch.Tensor, q_scale: torch.Tensor,
+                       eps: float, out: Optional[torch.Tensor] = None, quant_eps: float = 1e-5, pdl: bool = False):
+    """h += delta (when given); the normalised row rmsnorm(h) * weight is quantized to int8 per token straight into
+    `q` [M, K] / `q_scale` [M] (the bits of act_quant_i8 on the bf16 result) and written as bf16 into `out` when given."""
+    _need_cuda(h, delta, weight, q, q_scale, out)
+    m, k = h.shape
+    with torch.cuda.device(h.device):
+        L.check(L.lib().wf_add_rmsnorm_quant_bf16(h.data_ptr(), _ptr(delta), weight.data_ptr(), _ptr(out), q.data_ptr(), q_scale.data_ptr(),
+                                                  m, k, float(eps), float(quant_eps), L.FLAG_PDL if pdl else 0, _stream()),
+                "wf_add_rmsnorm_quant_bf16")
+    return q, q_scale
+
+
+def act_mul_quant(gate: torch.Tensor, up: torch.Tensor, q: torch.Tensor, q_scale: torch.Tensor, mode: str = "silu",
+                  out: Optional[torch.Tensor] = None, quant_eps: float = 1e-5, pdl: bool = False):
+    """act(gate) * up per token row [M, I], quantized to int8 per token into `q` / `q_scale` (and written as bf16 into
+    `out` when given): the activation in front of down_proj with that projection's quantization."""
+    _need_cuda(gate, up, q, q_scale, out)
+    m, i = gate.shape
+    with torch.cuda.device(gate.device):
+        L.check(L.lib().wf_act_mul_quant_bf16(gate.data_ptr(), up.data_ptr(), _ptr(out), q.data_ptr(), q_scale.data_ptr(), m, i,
+                                              0 if mode == "silu" else 1, float(quant_eps), L.FLAG_PDL if pdl else 0, _stream()),
+                "wf_act_mul_quant_bf16")
+    return q, q_scale
+
+
 def linear_bf16(x: torch.Tensor, weight: torch.Tensor, out: Optional[torch.Tensor] = None, out_dtype: Optional[torch.dtype] = None,
                 pdl: bool = False) -> torch.Tensor:
     """y = x @ weight.T for bf16 x [..., K] and weight [N, K] (fp32 accumulation on the tensor cores): the output head of
