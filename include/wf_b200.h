@@ -382,6 +382,9 @@ int wf_ar_set_step(void* ctx, unsigned step);
 int wf_ar_xchg(void* ctx, const void** dev_desc_out);
 int wf_ar_reduce_add_rmsnorm(void* ctx, void* h, const void* weight, void* y, int64_t M, int64_t K, float eps, unsigned flags,
                              void* stream);
+/* ... with the per-token int8 quantization of the projections that follow fused in, as wf_add_rmsnorm_quant_bf16 (y may be NULL) */
+int wf_ar_reduce_add_rmsnorm_quant(void* ctx, void* h, const void* weight, void* y, int8_t* q, float* q_scale, int64_t M, int64_t K,
+                                   float eps, float quant_eps, unsigned flags, void* stream);
 int wf_ar_destroy(void* ctx);
 
 #ifdef __cplusplus

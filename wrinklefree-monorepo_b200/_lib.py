@@ -86,6 +86,7 @@ _SIGNATURES = {
     "wf_ar_status": (_int, [_p, C.POINTER(C.c_int)]),
     "wf_ar_xchg": (_int, [_p, C.POINTER(C.c_void_p)]),
     "wf_ar_reduce_add_rmsnorm": (_int, [_p, _p, _p, _p, _i64, _i64, _f32, _u32, _p]),
+    "wf_ar_reduce_add_rmsnorm_quant": (_int, [_p, _p, _p, _p, _p, _p, _i64, _i64, _f32, _f32, _u32, _p]),
     "wf_ar_step": (_int, [_p, C.POINTER(C.c_uint)]),
     "wf_ar_set_step": (_int, [_p, _u32]),
     "wf_ar_destroy": (_int, [_p]),

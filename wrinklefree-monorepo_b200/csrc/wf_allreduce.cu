@@ -18,6 +18,7 @@
 
 #include "wf_common.cuh"
 #include "wf_xchg.cuh"
+#include "wf_rowquant.cuh"
 
 namespace wf {
 
@@ -160,7 +161,8 @@ __device__ __forceinline__ float xr_round(float v) { return __bfloat162float(__f
 
 __global__ void __launch_bounds__(XR_THREADS) reduce_add_rmsnorm_kernel(const wf_xchg x, __nv_bfloat16* __restrict__ h,
                                                                         const __nv_bfloat16* __restrict__ w, __nv_bfloat16* __restrict__ y,
-                                                                        int K, float eps) {
+                                                                        int K, float eps, int8_t* __restrict__ q, float* __restrict__ q_scale,
+                                                                        float q_eps) {
     __shared__ float sh[XR_THREADS / 32];
     asm volatile("griddepcontrol.launch_dependents;\n" ::: "memory");
     const int64_t m = blockIdx.x;
@@ -227,20 +229,25 @@ __global__ void __launch_bounds__(XR_THREADS) reduce_add_rmsnorm_kernel(const wf
 #pragma unroll
     for (int i = 0; i < XR_THREADS / 32; ++i) tot += sh[i];
     const float rn = rsqrtf(tot / static_cast<float>(K) + eps);
-    uint4* yrow = reinterpret_cast<uint4*>(y + m * K);
+    uint4* yrow = y ? reinterpret_cast<uint4*>(y + m * K) : nullptr;
+    uint32_t o[XR_CHUNKS][4];
+    float mx = 0.f;
 #pragma unroll
     for (int c = 0; c < XR_CHUNKS; ++c) {
         const int i = tid + c * XR_THREADS;
         if (i < chunks) {
             const uint32_t a[4] = {hv[c].x, hv[c].y, hv[c].z, hv[c].w};
             const uint32_t g[4] = {wv[c].x, wv[c].y, wv[c].z, wv[c].w};
-            uint32_t o[4];
 #pragma unroll
-            for (int e = 0; e < 4; ++e)
-                o[e] = xr_pack(xr_round(xr_lo(a[e]) * rn) * xr_lo(g[e]), xr_round(xr_hi(a[e]) * rn) * xr_hi(g[e]));
-            yrow[i] = make_uint4(o[0], o[1], o[2], o[3]);
+            for (int e = 0; e < 4; ++e) {
+                o[c][e] = xr_pack(xr_round(xr_lo(a[e]) * rn) * xr_lo(g[e]), xr_round(xr_hi(a[e]) * rn) * xr_hi(g[e]));
+                mx = fmaxf(mx, fmaxf(fabsf(xr_lo(o[c][e])), fabsf(xr_hi(o[c][e]))));
+            }
+            if (y) yrow[i] = make_uint4(o[c][0], o[c][1], o[c][2], o[c][3]);
         }
     }
+    // the per-token int8 quantization of the projections that follow, as in the residual add + RMSNorm kernel
+    if (q) quantize_row_bf16<XR_THREADS, XR_CHUNKS>(o, mx, chunks, tid, sh, q + m * K, q_scale + m, q_eps);
     // the last block to finish advances this rank's count of consumed exchanges
     __syncthreads();
     if (tid == 0) {
@@ -326,17 +333,27 @@ extern "C" int wf_ar_xchg(void* ctx, const void** dev_desc_out) {
     return WF_OK;
 }
 
+extern "C" int wf_ar_reduce_add_rmsnorm_quant(void* ctx, void* h, const void* weight, void* y, int8_t* q, float* q_scale, int64_t M, int64_t K,
+                                              float eps, float quant_eps, unsigned flags, void* stream);
+
 extern "C" int wf_ar_reduce_add_rmsnorm(void* ctx, void* h, const void* weight, void* y, int64_t M, int64_t K, float eps, unsigned flags,
                                         void* stream) {
+    WF_REQUIRE(y, "wf_ar_reduce_add_rmsnorm: null pointer");
+    return wf_ar_reduce_add_rmsnorm_quant(ctx, h, weight, y, nullptr, nullptr, M, K, eps, 0.f, flags, stream);
+}
+
+extern "C" int wf_ar_reduce_add_rmsnorm_quant(void* ctx, void* h, const void* weight, void* y, int8_t* q, float* q_scale, int64_t M, int64_t K,
+                                              float eps, float quant_eps, unsigned flags, void* stream) {
     ArCtx* c = static_cast<ArCtx*>(ctx);
-    WF_REQUIRE(c && h && weight && y, "wf_ar_reduce_add_rmsnorm: null pointer");
+    WF_REQUIRE(c && h && weight && (y || q) && (!q || q_scale), "wf_ar_reduce_add_rmsnorm: null pointer");
+    WF_REQUIRE(!q || (reinterpret_cast<uintptr_t>(q) & 7) == 0, "wf_ar_reduce_add_rmsnorm: q must be 8-byte aligned");
     WF_REQUIRE(c->connected, "wf_ar_reduce_add_rmsnorm: wf_ar_connect has not run");
     WF_REQUIRE(M >= 1 && K >= 8 && K % 8 == 0 && K <= XR_THREADS * XR_CHUNKS * 8, "wf_ar_reduce_add_rmsnorm: K must be a multiple of 8, at most %d",
                XR_THREADS * XR_CHUNKS * 8);
     WF_REQUIRE(static_cast<size_t>(M) * K * 2 <= c->max_bytes, "wf_ar_reduce_add_rmsnorm: %lld x %lld exceeds the exchange's %zu bytes",
                (long long)M, (long long)K, c->max_bytes);
     WF_REQUIRE((reinterpret_cast<uintptr_t>(h) | reinterpret_cast<uintptr_t>(weight) | reinterpret_cast<uintptr_t>(y)) % 16 == 0,
-               "wf_ar_reduce_add_rmsnorm: tensors must be 16-byte aligned");
+               "wf_ar_reduce_add_rmsnorm: tensors must be 16-byte aligned");  // a null y passes
     cudaLaunchConfig_t lc = {};
     lc.gridDim = dim3(static_cast<unsigned>(M));
     lc.blockDim = dim3(XR_THREADS);
@@ -355,7 +372,7 @@ extern "C" int wf_ar_reduce_add_rmsnorm(void* ctx, void* h, const void* weight, 
     desc.push_off = AR_HEADER + 2 * c->max_bytes;
     for (int r = 0; r < c->world; ++r) desc.peer[r] = c->peers.base[r];
     WF_CUDA(cudaLaunchKernelEx(&lc, reduce_add_rmsnorm_kernel, desc, static_cast<__nv_bfloat16*>(h), static_cast<const __nv_bfloat16*>(weight),
-                               static_cast<__nv_bfloat16*>(y), static_cast<int>(K), eps));
+                               static_cast<__nv_bfloat16*>(y), static_cast<int>(K), eps, q, q_scale, quant_eps));
     return WF_OK;
 }
 

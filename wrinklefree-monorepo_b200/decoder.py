@@ -213,7 +213,7 @@ class TernaryDecoder:
         # The norms in front of q/k/v and gate/up, and the activation (or its sub-norm) in front of down, quantize their
         # result to int8 themselves where the projection would otherwise run a quantization kernel of its own.
         i_loc = self.i_hi - self.i_lo
-        self.qnorm = (dt == torch.bfloat16 and not self.fused and not self.fuse_exchange and cfg.hidden % 8 == 0 and cfg.hidden <= 16384
+        self.qnorm = (dt == torch.bfloat16 and not self.fused and cfg.hidden % 8 == 0 and cfg.hidden <= 16384
                       and ops._prequant(B, cfg.hidden, 2))
         self.qact = (dt == torch.bfloat16 and not self.fused and i_loc % 8 == 0 and i_loc <= 16384 and ops._prequant(B, i_loc, 1))
         mode = "silu" if cfg.act == "silu" else "relu2"
@@ -294,7 +294,10 @@ class TernaryDecoder:
         fx = self.fuse_exchange
         for L in self.layers:
             if fx and delta is not None:  # the previous layer's down projection has pushed its partial outputs
-                self._oneshot.reduce_add_rmsnorm_(self.h, L["n1"], L["xn"], cfg.eps, pdl=True)
+                if self.qnorm:
+                    self._oneshot.reduce_add_rmsnorm_(self.h, L["n1"], None, cfg.eps, pdl=True, q=L["xn_q"], q_scale=L["xn_s"])
+                else:
+                    self._oneshot.reduce_add_rmsnorm_(self.h, L["n1"], L["xn"], cfg.eps, pdl=True)
             elif self.qnorm:
                 ops.add_rmsnorm_quant_(self.h, delta, L["n1"], L["xn_q"], L["xn_s"], cfg.eps, pdl=True)
             else:
@@ -316,7 +319,10 @@ class TernaryDecoder:
                 if a.data_ptr() != L["g_o"].x_ptr:
                     L["attn"].copy_(a)  # the comparison attention writes its own tensor
                 L["g_o"].run(pdl=True)
-                self._oneshot.reduce_add_rmsnorm_(self.h, L["n2"], L["hn"], cfg.eps, pdl=True)
+                if self.qnorm:
+                    self._oneshot.reduce_add_rmsnorm_(self.h, L["n2"], None, cfg.eps, pdl=True, q=L["hn_q"], q_scale=L["hn_s"])
+                else:
+                    self._oneshot.reduce_add_rmsnorm_(self.h, L["n2"], L["hn"], cfg.eps, pdl=True)
             else:
                 o = self._allreduce(ops.bitlinear(a, L["o"][0], L["o"][1], out=L["ob"], path=path, pdl=True))
                 if self.qnorm:

@@ -89,17 +89,20 @@ class OneShotAllReduce:
         L.check(L.lib().wf_ar_xchg(self._ctx, C.byref(p)), "wf_ar_xchg")
         return p.value
 
-    def reduce_add_rmsnorm_(self, h: torch.Tensor, weight: torch.Tensor, y: torch.Tensor, eps: float, pdl: bool = False) -> torch.Tensor:
+    def reduce_add_rmsnorm_(self, h: torch.Tensor, weight: torch.Tensor, y: Optional[torch.Tensor], eps: float, pdl: bool = False,
+                            q: Optional[torch.Tensor] = None, q_scale: Optional[torch.Tensor] = None, quant_eps: float = 1e-5):
         """Consumer of a fused exchange, on every rank after the pushing launch: h += sum over the ranks of the pushed
-        partial outputs (fp32 in rank order, rounded to bf16: the bits of the stand-alone all-reduce), y = rmsnorm(h) * weight."""
+        partial outputs (fp32 in rank order, rounded to bf16: the bits of the stand-alone all-reduce), y = rmsnorm(h) * weight.
+        With `q` / `q_scale` the normalised row is also quantized to int8 per token (the bits of act_quant_i8); y may then be None."""
         if self._ctx is None:
             raise RuntimeError("the peer-memory exchange is not available on this group")
         m, k = h.shape
+        ptr = lambda t: None if t is None else t.data_ptr()
         with torch.cuda.device(h.device):
-            L.check(L.lib().wf_ar_reduce_add_rmsnorm(self._ctx, h.data_ptr(), weight.data_ptr(), y.data_ptr(), m, k, float(eps),
-                                                     L.FLAG_PDL if pdl else 0, torch.cuda.current_stream().cuda_stream),
-                    "wf_ar_reduce_add_rmsnorm")
-        return y
+            L.check(L.lib().wf_ar_reduce_add_rmsnorm_quant(self._ctx, h.data_ptr(), weight.data_ptr(), ptr(y), ptr(q), ptr(q_scale), m, k,
+                                                           float(eps), float(quant_eps), L.FLAG_PDL if pdl else 0,
+                                                           torch.cuda.current_stream().cuda_stream), "wf_ar_reduce_add_rmsnorm")
+        return y if q is None else (q, q_scale)
 
     def status(self) -> None:
         """Raises if a bounded wait for a peer ran out since the last call."""
