@@ -628,6 +628,57 @@ def decoder_section(wf, torch, device, world, full: bool):
     return out
 
 
+def step_kernels_section(wf, torch, device):
+    """The two kernels of the decode step that are not BitLinear, timed alone on the 8B shape (CUDA graph of four calls on
+    distinct tensors, median of three): the bf16 output head (128,256 x 4096, read once per token batch) and the decode
+    attention over a 2048-token bf16 KV cache (32 query / 8 KV heads of 128), with their algorithmic GB/s."""
+    hbm = measured_peaks()[0]["hbm_gbs"]
+    out = {"output_head": [], "decode_attention": []}
+
+    def timed(fn):
+        graph = capture(torch, fn)
+        for _ in range(2):
+            graph.replay()
+        torch.cuda.synchronize()
+        a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        samples = []
+        for _ in range(3):
+            a.record()
+            for _ in range(5):
+                graph.replay()
+            b.record()
+            torch.cuda.synchronize()
+            samples.append(a.elapsed_time(b) * 1e3 / 5)
+        return statistics.median(samples)
+
+    vocab, hidden = 128256, 4096
+    g = torch.Generator(device=device).manual_seed(11)
+    heads = [(torch.randn(vocab, hidden, generator=g, device=device) * 0.02).bfloat16() for _ in range(2)]  # 2.1 GB: larger than L2
+    for batch in (1, 32, 256):
+        x = torch.randn(batch, hidden, generator=g, device=device).bfloat16()
+        y = torch.empty(batch, vocab, dtype=torch.bfloat16, device=device)
+        us = timed(lambda: [wf.linear_bf16(x, w_, out=y) for w_ in heads]) / len(heads)
+        byts = vocab * hidden * 2 + batch * hidden * 2 + batch * vocab * 2
+        out["output_head"].append({"batch": batch, "us": round(us, 1), "GBps": round(byts / us / 1e3, 1), "frac_hbm": round(byts / us / 1e3 / hbm, 4)})
+    del heads
+    torch.cuda.empty_cache()
+    nq, nkv, d, t = 32, 8, 128, 2048 + 32
+    for batch in (1, 32, 256):
+        n = 4 if batch < 256 else 2  # distinct caches, so that a small batch does not sit in L2
+        q = torch.randn(batch, nq * d, generator=g, device=device).bfloat16()
+        caches = [(torch.randn(batch, nkv, t, d, generator=g, device=device).bfloat16(), torch.randn(batch, nkv, t, d, generator=g, device=device).bfloat16())
+                  for _ in range(n)]
+        o = torch.empty(batch, nq * d, dtype=torch.bfloat16, device=device)
+        pos = torch.tensor(2047, dtype=torch.long, device=device)
+        us = timed(lambda: [wf.ops.attn_decode(q, kc, vc, pos, o) for kc, vc in caches]) / n
+        byts = 2 * batch * nkv * 2048 * d * 2
+        out["decode_attention"].append({"batch": batch, "context": 2048, "us": round(us, 1), "GBps": round(byts / us / 1e3, 1),
+                                        "frac_hbm": round(byts / us / 1e3 / hbm, 4)})
+        del caches
+        torch.cuda.empty_cache()
+    return out
+
+
 # ------------------------------------------------------------------ main
 def finish(dist, torch, rank):
     """Multi-rank exit.  The CUDA graphs of this run captured NCCL kernels, and tearing a communicator down while
@@ -658,6 +709,7 @@ def main():
     ap.add_argument("--no-decoder", action="store_true", help="skip the decoder tokens/s section")
     ap.add_argument("--decoder-only", action="store_true", help="run only the decoder tokens/s section (profiling)")
     ap.add_argument("--decoder-quick", action="store_true", help="skip batch 256 of the 8B shape")
+    ap.add_argument("--kernels-only", action="store_true", help="run only the output-head / decode-attention timings (profiling)")
     ap.add_argument("--only-m", type=int, default=0, help="restrict the sweep to one token batch (profiling)")
     ap.add_argument("--only-shape", type=int, default=-1, help="restrict the sweep to one shape index (profiling)")
     ap.add_argument("--no-cpu-baseline", action="store_true")
@@ -714,6 +766,9 @@ def main():
         res = decoder_section(wf, torch, device, world, not args.decoder_quick)
         if rank == 0:
             print(json.dumps({"decode_tok_s": res}))
+        return
+    if args.kernels_only:
+        print(json.dumps({"step_kernels": step_kernels_section(wf, torch, device)}))
         return
     if args.prefill_only:
         peaks, _ = measured_peaks()
@@ -982,9 +1037,14 @@ def main():
                                  "peak_kind": "measured tcgen05.mma.kind::i8 rate (M128 N256 K32, operands resident)" if i8 else "nominal",
                                  "frac": tops / peak_tops, "frac_of_nominal_4500": tops / 4500.0, "ms": ms_gemm,
                                  "note": "useful ops 2*M*N*K; at M = 16 / 64 these stacks are bound by weight streaming and the "
-                                         "instruction issue rate, not by the tensor rate"}
+                                         "expansion of the packed weights, not by the tensor rate"}
     if decoder is not None:
         line["decode_tok_s"] = decoder
+        if world == 1:
+            try:
+                line["step_kernels"] = step_kernels_section(wf, torch, device)
+            except Exception as e:  # a secondary figure must not cost the line
+                line["step_kernels"] = {"error": repr(e)[:200]}
     if not args.only_m and args.only_shape < 0:
         note(rank, "prefill GEMM section")
         line["prefill_gemm"] = prefill_section(wf, torch, device, peak_tops)
