@@ -143,8 +143,10 @@ def build_workload(wf, torch, device, rank: int, world: int, layers_scale: float
             y = torch.empty(nl, m, n_loc, dtype=torch.bfloat16, device=device)
             batched = m >= GEMM_MIN_M
             grp = None if batched else wf.DecodeGroup([dict(x=xd[li], codes=c, w_scale=s, out=y[li]) for li, (c, s) in enumerate(lay)])
+            # a workspace per contraction stack: the step quantizes the tokens of all of them before the first contraction
+            ws = wf.prefill_workspace(nl * m, k_hi - k_lo, device) if batched else None
             groups.append(dict(n=n, k=k, m=m, layers=lay, x_host=x.pin_memory(), x=xd, y=y, group=grp, reduce=row_parallel,
-                               batched=batched, codes_stack=codes_stack, scales_stack=scales_stack))
+                               batched=batched, codes_stack=codes_stack, scales_stack=scales_stack, ws=ws))
     # the stacks are independent: those on the streaming kernel go first, so that their launches chain (each starts
     # while its predecessor drains), then those on the tensor-core contraction
     groups.sort(key=lambda g_: g_["batched"])
@@ -185,6 +187,7 @@ def run_group(wf, g, pdl: bool, reduce: bool = True):
 
 
 _SIDE = {}
+CHAIN_CONTRACTIONS = True  # --no-chain: every contraction stack quantizes in front of its own launch and waits for its predecessor
 
 
 def run_step(wf, groups, pdl: bool):
@@ -214,6 +217,16 @@ def run_step(wf, groups, pdl: bool):
             for m in members:
                 dist.all_reduce(m["y"])
 
+    # The contraction stacks: the tokens of all of them are quantized first (each stack into its own workspace), then
+    # the contractions follow one another; all but the first are launched as independent of what runs ahead of them
+    # (they are: own tokens, own workspace, own output), so each fills the SMs that the tail of its predecessor leaves.
+    batched = [g for g in groups if g["batched"]]
+    split = pdl and len(batched) > 1 and CHAIN_CONTRACTIONS
+    if split:
+        for g in batched:
+            wf.prefill_quantize(g["x"], g["ws"])
+            launches += 1
+    first = True
     for g in groups:
         mg = g.get("merged")
         if mg is not None and all(id(m) in present for m in mg["members"]):
@@ -223,8 +236,14 @@ def run_step(wf, groups, pdl: bool):
                 launches += 1
                 exchange(mg["members"])
             continue
-        run_group(wf, g, pdl, reduce=False)
-        launches += 2 if g["batched"] else 1  # batched = quantization kernel + contraction
+        if g["batched"] and split:
+            wf.bitlinear_batched(g["x"], g["codes_stack"], g["scales_stack"], out=g["y"], workspace=g["ws"], quantized=True,
+                                 independent=not first)
+            first = False
+            launches += 1
+        else:
+            run_group(wf, g, pdl, reduce=False)
+            launches += 2 if g["batched"] else 1  # batched = quantization kernel + contraction
         exchange([g])
     if side is not None:
         main.wait_stream(side)
@@ -713,6 +732,7 @@ def main():
     ap.add_argument("--only-m", type=int, default=0, help="restrict the sweep to one token batch (profiling)")
     ap.add_argument("--only-shape", type=int, default=-1, help="restrict the sweep to one shape index (profiling)")
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--no-chain", action="store_true", help="contraction stacks as quantization + launch pairs that wait for one another")
     ap.add_argument("--no-merge", action="store_true", help="one grouped launch per (shape, M) stack instead of one per (K, M)")
     args = ap.parse_args()
     rank = int(os.environ.get("RANK", "0"))
@@ -782,6 +802,9 @@ def main():
         SHAPES[:] = [SHAPES[args.only_shape]]
     note(rank, "building workload")
     groups = build_workload(wf, torch, device, rank, world, args.layers_scale)
+    if args.no_chain:
+        global CHAIN_CONTRACTIONS
+        CHAIN_CONTRACTIONS = False
     if not args.no_merge:
         merge_streaming(wf, groups)
     note(rank, "capturing step graph")

@@ -63,8 +63,23 @@ extern "C" {
 #define WF_FLAG_X_READY 2u /* with WF_FLAG_PDL, grouped streaming launches only: the caller states that x was NOT
                               written by the previous kernel of the stream (independent layers, experts, replicas).
                               The kernel then reads x without waiting and only its stores wait for that kernel.
-                              Ignored by the other forms.  No counterpart in the reference (its CPU operators are
-                              synchronous calls). */
+                              The tensor-core contraction takes it together with WF_FLAG_WS_READY (below); the other
+                              forms ignore it.  No counterpart in the reference (its CPU operators are synchronous
+                              calls). */
+
+#define WF_FLAG_WS_READY 16u /* wf_bitlinear_prefill(_batched): the workspace already holds the quantized tokens of this x
+                                (wf_prefill_quantize earlier in the stream); x is not read.  One quantization then serves
+                                every projection of the same tokens (q/k/v, gate/up), as the shared act-quant of
+                                bitnet_qkv_forward_cpu / bitnet_mlp_forward_cpu does
+                                (packages/inference/extern/sglang-bitnet/sgl-kernel/csrc/cpu/bitnet_fused_layer.cpp:150-375).
+                                With WF_FLAG_X_READY in addition (only directly behind another wf_bitlinear_prefill(_batched)
+                                launch in the stream, flagged or not) the caller states that the workspace was filled, and y
+                                / acc_out last touched, before the most recent UNFLAGGED one of those launches -- in
+                                practice: the quantizations go first, then one contraction without the flag, then the
+                                flagged ones, each with a workspace and an output of its own.  An unflagged contraction
+                                lets the launches behind it start only once everything ahead of it has completed; a flagged
+                                one waits for nothing before its loads and stores, so it fills the SMs that the tail of the
+                                previous contraction leaves idle.  Its grid still ends after its predecessor. */
 
 #define WF_FLAG_PREFILL_PAIR 4u   /* wf_bitlinear_prefill, more than 64 tokens: use the form in which two CTAs (a cluster of two
                                      SMs, tcgen05 cta_group::2) share each 256-row x 192-token tile (half the token bytes from
@@ -280,7 +295,14 @@ int wf_bitlinear_prefill(const void* x, int x_dtype, int64_t ldx, const float* x
 int wf_bitlinear_prefill_batched(const void* x, int x_dtype, int64_t ldx, const uint8_t* codes, int layout,
                                  const float* w_scale, int64_t w_scale_stride, void* y, int y_dtype, int64_t ldy,
                                  int32_t* acc_out, int64_t batch, int64_t M, int64_t N, int64_t K, float eps,
-                                 void* workspace, size_t workspace_bytes, void* stream);
+                                 void* workspace, size_t workspace_bytes, unsigned flags, void* stream);
+
+/* The quantization step of wf_bitlinear_prefill(_batched) on its own: per-token absmax int8 codes, scales and row sums
+ * of x [M, K] (M = batch * tokens for a batched call) into `workspace` (wf_prefill_workspace_bytes(M, K) bytes), for
+ * later calls with WF_FLAG_WS_READY on the same workspace.  Same arithmetic as wf_act_quant_i8 in per-token mode
+ * (quantize_activations_i8, packages/inference/extern/sglang-bitnet/sgl-kernel/csrc/bitnet/bitnet_gemv.cpp). */
+int wf_prefill_quantize(const void* x, int x_dtype, int64_t ldx, int64_t M, int64_t K, float eps, void* workspace,
+                        size_t workspace_bytes, void* stream);
 
 /*
  * Fused elementwise kernels around the projections of a decoder layer (bf16 tensors, contiguous rows).

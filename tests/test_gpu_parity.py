@@ -645,3 +645,51 @@ def test_few_token_contraction_stage_counts(wf, k, m):
         for i in range(layers):
             assert torch.equal(wf.bitlinear(x[i], codes[i], scales[i], out_dtype=torch.float32, path="decode"), y[i]), (layers, i)
     wf.device_status()
+
+
+@pytest.mark.parametrize("m", [16, 64, 200])
+def test_contraction_on_a_quantized_workspace(wf, m):
+    """Quantize once, contract later: `prefill_quantize` + `bitlinear_batched(workspace=, quantized=True)` equals the
+    one-call form bit for bit; one quantization serves several projections of the same tokens (q/k/v like); and a
+    chain of stacks launched as independent of one another (each with its own workspace, the first one unmarked)
+    gives every stack's one-call result."""
+    g = torch.Generator(device=DEV).manual_seed(77 + m)
+    k = 1024
+
+    def stack(layers, n):
+        codes = torch.empty(layers, n, k // 4, dtype=torch.uint8, device=DEV)
+        scales = torch.empty(layers, 2, device=DEV)
+        for i in range(layers):
+            c, s = wf.pack_ternary(torch.randn(n, k, generator=g, device=DEV) * 0.02)
+            codes[i].copy_(c)
+            scales[i].copy_(s)
+        return codes, scales
+
+    layers = 3
+    x = torch.randn(layers, m, k, generator=g, device=DEV).bfloat16()
+    projs = [stack(layers, n) for n in (384, 128, 256)]
+    want = [wf.bitlinear_batched(x, c, s, out_dtype=torch.float32, want_acc=True) for c, s in projs]
+    ws = wf.prefill_workspace(layers * m, k, DEV)
+    wf.prefill_quantize(x, ws)
+    for (c, s), (y0, a0) in zip(projs, want):
+        y, a = wf.bitlinear_batched(torch.zeros_like(x), c, s, out_dtype=torch.float32, want_acc=True, workspace=ws, quantized=True)
+        assert torch.equal(a, a0) and torch.equal(y, y0)  # x itself is not read again
+
+    # a chain of independent stacks, as a step over many layer stacks issues them
+    chain = []
+    for i in range(5):
+        xi = torch.randn(layers + i, m, k, generator=g, device=DEV).bfloat16()
+        ci, si = stack(layers + i, 640 if i % 2 else 256)
+        chain.append((xi, ci, si, wf.bitlinear_batched(xi, ci, si), wf.prefill_workspace((layers + i) * m, k, DEV)))
+    torch.cuda.synchronize()
+    outs = [torch.empty_like(w) for _, _, _, w, _ in chain]
+    for xi, _, _, _, wsi in chain:
+        wf.prefill_quantize(xi, wsi)
+    for j, (xi, ci, si, _, wsi) in enumerate(chain):
+        wf.bitlinear_batched(xi, ci, si, out=outs[j], workspace=wsi, quantized=True, independent=j > 0)
+    torch.cuda.synchronize()
+    for j, (_, _, _, w, _) in enumerate(chain):
+        assert torch.equal(outs[j], w), j
+    with pytest.raises(ValueError):
+        wf.bitlinear_batched(x, *projs[0], quantized=True)
+    wf.device_status()

@@ -40,6 +40,8 @@ from .ops import (  # noqa: F401
     linear_bf16,
     pack_codes,
     pack_ternary,
+    prefill_quantize,
+    prefill_workspace,
     quantize_activations_i8,
     quantize_maxabs,
     repack,

@@ -21,6 +21,7 @@ X_PLAIN, X_SILU, X_RELU2, X_NORM = 0, 1, 2, 3
 FLAG_PDL = 1
 FLAG_X_READY = 2
 FLAG_PREFILL_PAIR, FLAG_PREFILL_SINGLE = 4, 8
+FLAG_WS_READY = 16
 
 _i64, _int, _f32, _p, _sz, _u32 = C.c_int64, C.c_int, C.c_float, C.c_void_p, C.c_size_t, C.c_uint
 
@@ -91,7 +92,8 @@ _SIGNATURES = {
     "wf_ar_set_step": (_int, [_p, _u32]),
     "wf_ar_destroy": (_int, [_p]),
     "wf_bitlinear_prefill_batched": (_int, [_p, _int, _i64, _p, _int, _p, _i64, _p, _int, _i64, _p, _i64, _i64, _i64, _i64, _f32,
-                                            _p, _sz, _p]),
+                                            _p, _sz, _u32, _p]),
+    "wf_prefill_quantize": (_int, [_p, _int, _i64, _i64, _i64, _f32, _p, _sz, _p]),
 }
 
 _lib = None

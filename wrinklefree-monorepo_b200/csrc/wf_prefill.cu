@@ -49,6 +49,8 @@ struct PrefillParams {
     int batch;            // independent problems stacked along rows: tokens [batch*M, K], weights [batch*N, K/4]
     int w_scale_stride;   // floats between the weight scales of consecutive problems
     int tiles_m, tiles_n; // per problem: token blocks of NTOK, row blocks of 128
+    int x_ready;          // the tokens, their constants and y have nothing to do with the kernels still running ahead of this
+                          // one: no load or store waits for them, only the end of the grid does
 };
 
 __device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory"); }
@@ -229,8 +231,11 @@ __global__ void __launch_bounds__(sm_threads<NTOK>(), 1)
     float* s_inv = reinterpret_cast<float*>(s_rowsum + 128);  // [NTOK]
 
     // chained with a programmatic dependency: the packed weights never depend on the previous kernel (normally the
-    // quantization of the tokens) and are requested at once; the token tiles and the per-token constants wait for it
-    asm volatile("griddepcontrol.launch_dependents;\n" ::: "memory");
+    // quantization of the tokens) and are requested at once; the token tiles and the per-token constants wait for it.
+    // The kernel lets its own dependents go only when that wait is over (in the thread that loads the token tiles):
+    // whatever is launched behind this grid then starts after everything ahead of it has completed, which is what a
+    // following launch that waits for nothing (x_ready) relies on.  Such a launch lets its dependents go at once.
+    if (p.x_ready) asm volatile("griddepcontrol.launch_dependents;\n" ::: "memory");
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     // K is walked in stages of 512: one barrier round trip, one commit and sixteen MMAs per stage.  A last stage
     // that reaches past K is zero-filled by the TMA unit on both operands (code 0 times activation 0).
@@ -284,7 +289,10 @@ __global__ void __launch_bounds__(sm_threads<NTOK>(), 1)
         }
     } else if (warp == 14) {
         if (lane == 0) {
-            asm volatile("griddepcontrol.wait;\n" ::: "memory");
+            if (!p.x_ready) {
+                asm volatile("griddepcontrol.wait;\n" ::: "memory");
+                asm volatile("griddepcontrol.launch_dependents;\n" ::: "memory");
+            }
             int sit = 0;
             for (int t = blockIdx.x; t < total_tiles; t += gridDim.x) {
                 const int row_x = (t / tiles_per_problem) * p.M + ((t % tiles_per_problem) / p.tiles_n) * NTOK;
@@ -428,7 +436,7 @@ __global__ void __launch_bounds__(sm_threads<NTOK>(), 1)
         const int egrp = warp >= 15 ? 1 : 0;
         const int et = egrp * 128 + (warp - (egrp ? 15 : 10)) * 32 + lane;  // 0 .. 128 * EPI_GROUPS - 1
         const int col0 = egrp * EPI_COLS;  // this group's first token column
-        asm volatile("griddepcontrol.wait;\n" ::: "memory");
+        if (!p.x_ready) asm volatile("griddepcontrol.wait;\n" ::: "memory");
         int nt = 0, cur_zb = -1;
         for (int t = blockIdx.x; t < total_tiles; t += gridDim.x, ++nt) {
             const int z = t / tiles_per_problem, zb = t / p.tiles_n, tb = (t % tiles_per_problem) / p.tiles_n, rb = t % p.tiles_n;
@@ -502,6 +510,9 @@ __global__ void __launch_bounds__(sm_threads<NTOK>(), 1)
                 }
             }
         }
+        // a grid that waited for nothing still ends after its predecessor: whoever waits for this grid may rely on
+        // everything ahead of it in the stream
+        if (p.x_ready) asm volatile("griddepcontrol.wait;\n" ::: "memory");
     }
     tc_fence_before();
     __syncthreads();
@@ -607,7 +618,7 @@ __global__ void __launch_bounds__(SM_THREADS, 1)
     int* s_rowsum = reinterpret_cast<int*>((reinterpret_cast<uintptr_t>(tmem_slot + 2) + 15) & ~static_cast<uintptr_t>(15));
     float* s_inv = reinterpret_cast<float*>(s_rowsum + 256);  // [PR_N]
 
-    asm volatile("griddepcontrol.launch_dependents;\n" ::: "memory");
+    // its dependents go when this grid's own wait is over (see the single form)
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     const uint32_t rank = cluster_rank();     // 0: leader (issues the MMAs), 1: peer
     const int cluster_id = blockIdx.x >> 1, n_clusters = gridDim.x >> 1;
@@ -667,6 +678,7 @@ __global__ void __launch_bounds__(SM_THREADS, 1)
     } else if (warp == 14) {
         if (lane == 0) {  // this CTA's half of the token tile; the bytes are counted on the leader's barrier
             asm volatile("griddepcontrol.wait;\n" ::: "memory");
+            asm volatile("griddepcontrol.launch_dependents;\n" ::: "memory");
             int xsit = 0;
             for (int t = cluster_id; t < total_tiles; t += n_clusters) {
                 const int row_x = (t / tiles_per_problem) * p.M + ((t % tiles_per_problem) / p.tiles_n) * PR_N + static_cast<int>(rank) * PR_HALF;
@@ -930,7 +942,10 @@ static int prefill_impl(const char* who, const void* x, int x_dtype, int64_t ldx
     const int8_t* q = nullptr;
     const float* qs = nullptr;
     int64_t ldq = K;
-    if (x_dtype != WF_I8) {
+    if (flags & WF_FLAG_WS_READY) {  // wf_prefill_quantize filled the workspace earlier in the stream
+        q = wq;
+        qs = wscale;
+    } else if (x_dtype != WF_I8) {
         if (int rc = wf_act_quant_i8(x, x_dtype, M, K, ldx, WF_ACT_PER_TOKEN, eps, wq, wscale, wsum, stream)) return rc;
         q = wq;
         qs = wscale;
@@ -979,6 +994,7 @@ static int prefill_impl(const char* who, const void* x, int x_dtype, int64_t ldx
     pp.batch = static_cast<int>(batch); pp.w_scale_stride = static_cast<int>(w_scale_stride);
     pp.tiles_m = static_cast<int>(pair ? (M_one + PR_N - 1) / PR_N : (M_one + ntok - 1) / ntok);
     pp.tiles_n = static_cast<int>(pair ? (N + 255) / 256 : (N + SM_BM - 1) / SM_BM);
+    pp.x_ready = ((flags & WF_FLAG_WS_READY) && (flags & WF_FLAG_X_READY) && !pair) ? 1 : 0;
     static PerDeviceOnce configured;  // the attribute is a per-device setting
     const int dev_now = current_device();
     if (configured.needs(dev_now)) {
@@ -1039,9 +1055,24 @@ extern "C" int wf_bitlinear_prefill(const void* x, int x_dtype, int64_t ldx, con
 extern "C" int wf_bitlinear_prefill_batched(const void* x, int x_dtype, int64_t ldx, const uint8_t* codes, int layout,
                                             const float* w_scale, int64_t w_scale_stride, void* y, int y_dtype, int64_t ldy,
                                             int32_t* acc_out, int64_t batch, int64_t M, int64_t N, int64_t K, float eps,
-                                            void* workspace, size_t workspace_bytes, void* stream) {
+                                            void* workspace, size_t workspace_bytes, unsigned flags, void* stream) {
     WF_REQUIRE(w_scale, "wf_bitlinear_prefill_batched: w_scale must point to the per-problem scales");
     WF_REQUIRE(x_dtype != WF_I8, "wf_bitlinear_prefill_batched: takes floating-point activations");
     return prefill_impl("wf_bitlinear_prefill_batched", x, x_dtype, ldx, nullptr, codes, layout, w_scale, w_scale_stride, 0.f,
-                        nullptr, 0, y, y_dtype, ldy, acc_out, batch, M, N, K, eps, workspace, workspace_bytes, 0u, stream);
+                        nullptr, 0, y, y_dtype, ldy, acc_out, batch, M, N, K, eps, workspace, workspace_bytes,
+                        flags & (WF_FLAG_WS_READY | WF_FLAG_X_READY), stream);
+}
+
+extern "C" int wf_prefill_quantize(const void* x, int x_dtype, int64_t ldx, int64_t M, int64_t K, float eps, void* workspace,
+                                   size_t workspace_bytes, void* stream) {
+    WF_REQUIRE(x && x_dtype != WF_I8, "wf_prefill_quantize: takes floating-point activations");
+    WF_REQUIRE(M > 0 && K > 0 && K % 4 == 0 && ldx >= K, "wf_prefill_quantize: bad shape");
+    WF_REQUIRE(workspace && reinterpret_cast<uintptr_t>(workspace) % 256 == 0, "wf_prefill_quantize: workspace must be 256-byte aligned");
+    if (workspace_bytes < wf_prefill_workspace_bytes(M, K))
+        return wf::fail(WF_E_SCRATCH, "wf_prefill_quantize: workspace of %zu bytes, need %zu", workspace_bytes,
+                        wf_prefill_workspace_bytes(M, K));
+    uint8_t* ws = static_cast<uint8_t*>(workspace);
+    const size_t qb = wf::align_up(static_cast<size_t>(M) * K, 256), sb = wf::align_up(static_cast<size_t>(M) * 4, 256);
+    return wf_act_quant_i8(x, x_dtype, M, K, ldx, WF_ACT_PER_TOKEN, eps, reinterpret_cast<int8_t*>(ws),
+                           reinterpret_cast<float*>(ws + qb), reinterpret_cast<int32_t*>(ws + qb + sb), stream);
 }

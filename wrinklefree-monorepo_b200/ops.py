@@ -246,13 +246,38 @@ def bitlinear(x: torch.Tensor, codes: torch.Tensor, w_scale, bias: Optional[torc
     return (y, acc) if want_acc else y
 
 
+def prefill_workspace(m_rows: int, k: int, device) -> torch.Tensor:
+    """A workspace of its own for `m_rows` tokens of width `k` (see `prefill_quantize`)."""
+    return torch.empty(L.lib().wf_prefill_workspace_bytes(m_rows, k), dtype=torch.uint8, device=device)
+
+
+def prefill_quantize(x: torch.Tensor, workspace: torch.Tensor, eps: float = 1e-5) -> None:
+    """Quantizes the tokens x [..., K] (per-token absmax int8, scales, row sums) into `workspace`
+    (`prefill_workspace(tokens, K, device)`): the first half of `bitlinear_batched`, for calls with `workspace=` and
+    `quantized=True`.  One quantization serves every projection of the same tokens."""
+    _need_cuda(x, workspace)
+    k = x.shape[-1]
+    x2 = x.reshape(-1, k)
+    if x2.stride(1) != 1:
+        raise ValueError("prefill_quantize needs x with unit inner stride")
+    with torch.cuda.device(x.device):
+        L.check(L.lib().wf_prefill_quantize(x2.data_ptr(), _DT[x.dtype], x2.stride(0), x2.shape[0], k, eps, workspace.data_ptr(),
+                                            workspace.numel(), _stream()), "wf_prefill_quantize")
+
+
 def bitlinear_batched(x: torch.Tensor, codes: torch.Tensor, w_scales: torch.Tensor, out: Optional[torch.Tensor] = None,
                       out_dtype: Optional[torch.dtype] = None, layout: int = L.LAYOUT_WF16, eps: float = 1e-5,
-                      want_acc: bool = False):
+                      want_acc: bool = False, workspace: Optional[torch.Tensor] = None, quantized: bool = False,
+                      independent: bool = False):
     """A stack of `B` independent BitLinear layers of one shape in one tensor-core launch.
 
     x [B, M, K] (contiguous), codes uint8 [B, N, K/4] (contiguous), w_scales float32 [B] or [B, 2] (first column used).
     Returns y [B, M, N] (and the int32 accumulators when want_acc).
+
+    `workspace` (default: one shared per device) with `quantized=True`: `prefill_quantize(x, workspace)` ran earlier in
+    the stream and x is not read again.  `independent=True` in addition: the workspace and the output have nothing to do
+    with the launches since the last contraction that was not marked so (the quantizations went first, then one
+    unmarked contraction): the launch does not wait for its predecessor and fills the SMs its tail leaves idle.
     """
     _need_cuda(x, codes, w_scales)
     b, m, k = x.shape
@@ -261,17 +286,22 @@ def bitlinear_batched(x: torch.Tensor, codes: torch.Tensor, w_scales: torch.Tens
         raise ValueError("bitlinear_batched needs contiguous x [B, M, K] and codes [B, N, K/4]")
     if w_scales.dtype != torch.float32 or w_scales.shape[0] != b:
         raise ValueError("w_scales must be float32 with one row per layer")
+    if (quantized or independent) and workspace is None:
+        raise ValueError("quantized / independent need the workspace that prefill_quantize filled")
+    if independent and not quantized:
+        raise ValueError("independent=True needs quantized=True")
     y = out if out is not None else torch.empty((b, m, n), dtype=out_dtype or x.dtype, device=x.device)
     if not y.is_contiguous():
         raise ValueError("out must be contiguous")
     acc = torch.empty((b * m, n), dtype=torch.int32, device=x.device) if want_acc else None
     lib = L.lib()
     nbytes = lib.wf_prefill_workspace_bytes(b * m, k)
-    ws = _workspace(x.device, nbytes)
+    ws = workspace if workspace is not None else _workspace(x.device, nbytes)
+    flags = (L.FLAG_WS_READY if quantized else 0) | (L.FLAG_X_READY if independent else 0)
     with torch.cuda.device(x.device):
         L.check(lib.wf_bitlinear_prefill_batched(x.data_ptr(), _DT[x.dtype], k, codes.data_ptr(), layout, w_scales.data_ptr(),
                                                  w_scales.stride(0), y.data_ptr(), _DT[y.dtype], n, _ptr(acc), b, m, n, k, eps,
-                                                 ws.data_ptr(), ws.numel(), _stream()), "wf_bitlinear_prefill_batched")
+                                                 ws.data_ptr(), ws.numel(), flags, _stream()), "wf_bitlinear_prefill_batched")
     return (y, acc.view(b, m, n)) if want_acc else y
 
 
