@@ -224,7 +224,7 @@ def run_step(wf, groups, pdl: bool):
     split = pdl and len(batched) > 1 and CHAIN_CONTRACTIONS
     if split:
         for g in batched:
-            wf.prefill_quantize(g["x"], g["ws"])
+            wf.prefill_quantize(g["x"], g["ws"], independent=True)
             launches += 1
     first = True
     for g in groups:

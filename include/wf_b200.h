@@ -300,9 +300,12 @@ int wf_bitlinear_prefill_batched(const void* x, int x_dtype, int64_t ldx, const 
 /* The quantization step of wf_bitlinear_prefill(_batched) on its own: per-token absmax int8 codes, scales and row sums
  * of x [M, K] (M = batch * tokens for a batched call) into `workspace` (wf_prefill_workspace_bytes(M, K) bytes), for
  * later calls with WF_FLAG_WS_READY on the same workspace.  Same arithmetic as wf_act_quant_i8 in per-token mode
- * (quantize_activations_i8, packages/inference/extern/sglang-bitnet/sgl-kernel/csrc/bitnet/bitnet_gemv.cpp). */
+ * (quantize_activations_i8, packages/inference/extern/sglang-bitnet/sgl-kernel/csrc/bitnet/bitnet_gemv.cpp).
+ * flags: WF_FLAG_X_READY -- the caller states that no kernel that may still be running (the previous one of the stream
+ * and, while those were launched with this flag too, the ones before it) writes x or uses the workspace: the kernel
+ * starts at once instead of behind its predecessor (its grid still ends after it). */
 int wf_prefill_quantize(const void* x, int x_dtype, int64_t ldx, int64_t M, int64_t K, float eps, void* workspace,
-                        size_t workspace_bytes, void* stream);
+                        size_t workspace_bytes, unsigned flags, void* stream);
 
 /*
  * Fused elementwise kernels around the projections of a decoder layer (bf16 tensors, contiguous rows).

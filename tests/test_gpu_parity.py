@@ -684,7 +684,7 @@ def test_contraction_on_a_quantized_workspace(wf, m):
     torch.cuda.synchronize()
     outs = [torch.empty_like(w) for _, _, _, w, _ in chain]
     for xi, _, _, _, wsi in chain:
-        wf.prefill_quantize(xi, wsi)
+        wf.prefill_quantize(xi, wsi, independent=True)  # nothing ahead of them touches x or the workspaces
     for j, (xi, ci, si, _, wsi) in enumerate(chain):
         wf.bitlinear_batched(xi, ci, si, out=outs[j], workspace=wsi, quantized=True, independent=j > 0)
     torch.cuda.synchronize()

@@ -93,7 +93,7 @@ _SIGNATURES = {
     "wf_ar_destroy": (_int, [_p]),
     "wf_bitlinear_prefill_batched": (_int, [_p, _int, _i64, _p, _int, _p, _i64, _p, _int, _i64, _p, _i64, _i64, _i64, _i64, _f32,
                                             _p, _sz, _u32, _p]),
-    "wf_prefill_quantize": (_int, [_p, _int, _i64, _i64, _i64, _f32, _p, _sz, _p]),
+    "wf_prefill_quantize": (_int, [_p, _int, _i64, _i64, _i64, _f32, _p, _sz, _u32, _p]),
 }
 
 _lib = None

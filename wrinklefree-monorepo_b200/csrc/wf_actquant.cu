@@ -36,13 +36,15 @@ __device__ __forceinline__ int block_sum_int(int v, int* sh) {
 template <int DT>
 __global__ void __launch_bounds__(AQ_THREADS)
     act_quant_token_kernel(const void* __restrict__ x, int64_t K, int64_t ldx, float eps, int8_t* __restrict__ q,
-                           float* __restrict__ scale, int32_t* __restrict__ rowsum) {
+                           float* __restrict__ scale, int32_t* __restrict__ rowsum, int x_ready) {
     __shared__ float shf[AQ_THREADS / 32];
     __shared__ int shi[AQ_THREADS / 32];
     // chained with a programmatic dependency: the next kernel may start (the contraction fetches its first weights
     // meanwhile); x may come from the previous kernel and q may still be read by it, so everything else waits for it
+    // -- unless the caller states that neither is the case (x_ready): then only the end of the grid waits, so that
+    // whoever waits for this grid may still rely on everything ahead of it in the stream
     asm volatile("griddepcontrol.launch_dependents;\n" ::: "memory");
-    asm volatile("griddepcontrol.wait;\n" ::: "memory");
+    if (!x_ready) asm volatile("griddepcontrol.wait;\n" ::: "memory");
     const int64_t m = blockIdx.x;
     float mx = 0.f;
     for (int64_t k = threadIdx.x * 8; k < K; k += AQ_THREADS * 8) {
@@ -72,6 +74,7 @@ __global__ void __launch_bounds__(AQ_THREADS)
         scale[m] = s;
         if (rowsum) rowsum[m] = sum;
     }
+    if (x_ready) asm volatile("griddepcontrol.wait;\n" ::: "memory");
 }
 
 // Per-tensor absmax: pass 1 reduces |x| into a float kept as ordered uint bits.
@@ -122,8 +125,23 @@ __global__ void publish_tensor_scale(float* scale) {
 
 using namespace wf;
 
+static int act_quant_impl(const void* x, int x_dtype, int64_t M, int64_t K, int64_t ldx, int mode, float eps, int8_t* q, float* scale,
+                          int32_t* rowsum, int x_ready, void* stream);
+
 extern "C" int wf_act_quant_i8(const void* x, int x_dtype, int64_t M, int64_t K, int64_t ldx, int mode, float eps, int8_t* q,
                                float* scale, int32_t* rowsum, void* stream) {
+    return act_quant_impl(x, x_dtype, M, K, ldx, mode, eps, q, scale, rowsum, 0, stream);
+}
+
+// Per-token quantization whose launch neither reads nor overwrites anything the kernels still running ahead of it use
+// (x_ready != 0): see wf_prefill_quantize.
+int wf_act_quant_token_ready(const void* x, int x_dtype, int64_t M, int64_t K, int64_t ldx, float eps, int8_t* q, float* scale,
+                             int32_t* rowsum, int x_ready, void* stream) {
+    return act_quant_impl(x, x_dtype, M, K, ldx, WF_ACT_PER_TOKEN, eps, q, scale, rowsum, x_ready, stream);
+}
+
+static int act_quant_impl(const void* x, int x_dtype, int64_t M, int64_t K, int64_t ldx, int mode, float eps, int8_t* q, float* scale,
+                          int32_t* rowsum, int x_ready, void* stream) {
     WF_REQUIRE(x && q && scale, "wf_act_quant_i8: null pointer");
     WF_REQUIRE(M > 0 && K > 0 && K % 8 == 0, "wf_act_quant_i8: need M > 0 and K a positive multiple of 8 (M=%lld K=%lld)",
                (long long)M, (long long)K);
@@ -145,9 +163,9 @@ extern "C" int wf_act_quant_i8(const void* x, int x_dtype, int64_t M, int64_t K,
         lc.attrs = attr;
         lc.numAttrs = 1;
         switch (x_dtype) {
-            case WF_F32: WF_CUDA(cudaLaunchKernelEx(&lc, act_quant_token_kernel<WF_F32>, x, K, ldx, eps, q, scale, rowsum)); break;
-            case WF_BF16: WF_CUDA(cudaLaunchKernelEx(&lc, act_quant_token_kernel<WF_BF16>, x, K, ldx, eps, q, scale, rowsum)); break;
-            default: WF_CUDA(cudaLaunchKernelEx(&lc, act_quant_token_kernel<WF_F16>, x, K, ldx, eps, q, scale, rowsum)); break;
+            case WF_F32: WF_CUDA(cudaLaunchKernelEx(&lc, act_quant_token_kernel<WF_F32>, x, K, ldx, eps, q, scale, rowsum, x_ready)); break;
+            case WF_BF16: WF_CUDA(cudaLaunchKernelEx(&lc, act_quant_token_kernel<WF_BF16>, x, K, ldx, eps, q, scale, rowsum, x_ready)); break;
+            default: WF_CUDA(cudaLaunchKernelEx(&lc, act_quant_token_kernel<WF_F16>, x, K, ldx, eps, q, scale, rowsum, x_ready)); break;
         }
     } else if (mode == WF_ACT_PER_TENSOR) {
         WF_REQUIRE(x_dtype == WF_F32, "wf_act_quant_i8: per-tensor mode takes fp32 input (as the operator it replaces)");

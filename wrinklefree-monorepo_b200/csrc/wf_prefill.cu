@@ -1063,8 +1063,11 @@ extern "C" int wf_bitlinear_prefill_batched(const void* x, int x_dtype, int64_t 
                         flags & (WF_FLAG_WS_READY | WF_FLAG_X_READY), stream);
 }
 
+int wf_act_quant_token_ready(const void* x, int x_dtype, int64_t M, int64_t K, int64_t ldx, float eps, int8_t* q, float* scale,
+                             int32_t* rowsum, int x_ready, void* stream);
+
 extern "C" int wf_prefill_quantize(const void* x, int x_dtype, int64_t ldx, int64_t M, int64_t K, float eps, void* workspace,
-                                   size_t workspace_bytes, void* stream) {
+                                   size_t workspace_bytes, unsigned flags, void* stream) {
     WF_REQUIRE(x && x_dtype != WF_I8, "wf_prefill_quantize: takes floating-point activations");
     WF_REQUIRE(M > 0 && K > 0 && K % 4 == 0 && ldx >= K, "wf_prefill_quantize: bad shape");
     WF_REQUIRE(workspace && reinterpret_cast<uintptr_t>(workspace) % 256 == 0, "wf_prefill_quantize: workspace must be 256-byte aligned");
@@ -1073,6 +1076,6 @@ extern "C" int wf_prefill_quantize(const void* x, int x_dtype, int64_t ldx, int6
                         wf_prefill_workspace_bytes(M, K));
     uint8_t* ws = static_cast<uint8_t*>(workspace);
     const size_t qb = wf::align_up(static_cast<size_t>(M) * K, 256), sb = wf::align_up(static_cast<size_t>(M) * 4, 256);
-    return wf_act_quant_i8(x, x_dtype, M, K, ldx, WF_ACT_PER_TOKEN, eps, reinterpret_cast<int8_t*>(ws),
-                           reinterpret_cast<float*>(ws + qb), reinterpret_cast<int32_t*>(ws + qb + sb), stream);
+    return wf_act_quant_token_ready(x, x_dtype, M, K, ldx, eps, reinterpret_cast<int8_t*>(ws), reinterpret_cast<float*>(ws + qb),
+                                    reinterpret_cast<int32_t*>(ws + qb + sb), (flags & WF_FLAG_X_READY) ? 1 : 0, stream);
 }

@@ -251,10 +251,11 @@ def prefill_workspace(m_rows: int, k: int, device) -> torch.Tensor:
     return torch.empty(L.lib().wf_prefill_workspace_bytes(m_rows, k), dtype=torch.uint8, device=device)
 
 
-def prefill_quantize(x: torch.Tensor, workspace: torch.Tensor, eps: float = 1e-5) -> None:
+def prefill_quantize(x: torch.Tensor, workspace: torch.Tensor, eps: float = 1e-5, independent: bool = False) -> None:
     """Quantizes the tokens x [..., K] (per-token absmax int8, scales, row sums) into `workspace`
     (`prefill_workspace(tokens, K, device)`): the first half of `bitlinear_batched`, for calls with `workspace=` and
-    `quantized=True`.  One quantization serves every projection of the same tokens."""
+    `quantized=True`.  One quantization serves every projection of the same tokens.  `independent=True`: no kernel that
+    may still be running writes x or uses the workspace, so the launch need not wait for its predecessor."""
     _need_cuda(x, workspace)
     k = x.shape[-1]
     x2 = x.reshape(-1, k)
@@ -262,7 +263,8 @@ def prefill_quantize(x: torch.Tensor, workspace: torch.Tensor, eps: float = 1e-5
         raise ValueError("prefill_quantize needs x with unit inner stride")
     with torch.cuda.device(x.device):
         L.check(L.lib().wf_prefill_quantize(x2.data_ptr(), _DT[x.dtype], x2.stride(0), x2.shape[0], k, eps, workspace.data_ptr(),
-                                            workspace.numel(), _stream()), "wf_prefill_quantize")
+                                            workspace.numel(), L.FLAG_X_READY if independent else 0, _stream()),
+                "wf_prefill_quantize")
 
 
 def bitlinear_batched(x: torch.Tensor, codes: torch.Tensor, w_scales: torch.Tensor, out: Optional[torch.Tensor] = None,
