@@ -128,6 +128,69 @@ using namespace wf;
 static int act_quant_impl(const void* x, int x_dtype, int64_t M, int64_t K, int64_t ldx, int mode, float eps, int8_t* q, float* scale,
                           int32_t* rowsum, int x_ready, void* stream);
 
+// The same with the row held in registers between the two passes (K <= 8 * AQ_THREADS * CHUNKS): x is read once, and all
+// of a thread's loads are in flight together.
+template <int DT, int CHUNKS>
+__global__ void __launch_bounds__(AQ_THREADS)
+    act_quant_token_reg_kernel(const void* __restrict__ x, int64_t K, int64_t ldx, float eps, int8_t* __restrict__ q,
+                               float* __restrict__ scale, int32_t* __restrict__ rowsum, int x_ready) {
+    __shared__ float shf[AQ_THREADS / 32];
+    __shared__ int shi[AQ_THREADS / 32];
+    asm volatile("griddepcontrol.launch_dependents;\n" ::: "memory");
+    if (!x_ready) asm volatile("griddepcontrol.wait;\n" ::: "memory");
+    const int64_t m = blockIdx.x;
+    const int chunks = static_cast<int>(K >> 3);
+    float f[CHUNKS][8];
+#pragma unroll
+    for (int c = 0; c < CHUNKS; ++c) {
+        const int i = threadIdx.x + c * AQ_THREADS;
+        if (i < chunks) {
+            load8<DT>(x, m * ldx + 8 * static_cast<int64_t>(i), f[c]);
+        } else {
+#pragma unroll
+            for (int e = 0; e < 8; ++e) f[c][e] = 0.f;
+        }
+    }
+    float mx = 0.f;
+#pragma unroll
+    for (int c = 0; c < CHUNKS; ++c)
+#pragma unroll
+        for (int e = 0; e < 8; ++e) mx = fmaxf(mx, fabsf(f[c][e]));
+    mx = block_max(mx, shf);
+    const float s = act_scale_from_absmax<DT>(mx, eps);
+    int sum = 0;
+#pragma unroll
+    for (int c = 0; c < CHUNKS; ++c) {
+        const int i = threadIdx.x + c * AQ_THREADS;
+        if (i < chunks) {
+            uint32_t w0 = 0, w1 = 0;
+#pragma unroll
+            for (int e = 0; e < 4; ++e) {
+                const int a = quantize_one<DT>(f[c][e], s), b = quantize_one<DT>(f[c][4 + e], s);
+                sum += a + b;
+                w0 |= static_cast<uint32_t>(a & 0xff) << (8 * e);
+                w1 |= static_cast<uint32_t>(b & 0xff) << (8 * e);
+            }
+            *reinterpret_cast<uint2*>(q + m * K + 8 * static_cast<int64_t>(i)) = make_uint2(w0, w1);
+        }
+    }
+    sum = block_sum_int(sum, shi);
+    if (threadIdx.x == 0) {
+        scale[m] = s;
+        if (rowsum) rowsum[m] = sum;
+    }
+    if (x_ready) asm volatile("griddepcontrol.wait;\n" ::: "memory");
+}
+
+template <int DT>
+static cudaError_t launch_token_quant(const cudaLaunchConfig_t& lc, const void* x, int64_t K, int64_t ldx, float eps, int8_t* q,
+                                      float* scale, int32_t* rowsum, int x_ready) {
+    const int64_t per_thread = ((K >> 3) + AQ_THREADS - 1) / AQ_THREADS;
+    if (per_thread <= 2) return cudaLaunchKernelEx(&lc, act_quant_token_reg_kernel<DT, 2>, x, K, ldx, eps, q, scale, rowsum, x_ready);
+    if (per_thread <= 4) return cudaLaunchKernelEx(&lc, act_quant_token_reg_kernel<DT, 4>, x, K, ldx, eps, q, scale, rowsum, x_ready);
+    return cudaLaunchKernelEx(&lc, act_quant_token_kernel<DT>, x, K, ldx, eps, q, scale, rowsum, x_ready);
+}
+
 extern "C" int wf_act_quant_i8(const void* x, int x_dtype, int64_t M, int64_t K, int64_t ldx, int mode, float eps, int8_t* q,
                                float* scale, int32_t* rowsum, void* stream) {
     return act_quant_impl(x, x_dtype, M, K, ldx, mode, eps, q, scale, rowsum, 0, stream);
@@ -163,9 +226,9 @@ static int act_quant_impl(const void* x, int x_dtype, int64_t M, int64_t K, int6
         lc.attrs = attr;
         lc.numAttrs = 1;
         switch (x_dtype) {
-            case WF_F32: WF_CUDA(cudaLaunchKernelEx(&lc, act_quant_token_kernel<WF_F32>, x, K, ldx, eps, q, scale, rowsum, x_ready)); break;
-            case WF_BF16: WF_CUDA(cudaLaunchKernelEx(&lc, act_quant_token_kernel<WF_BF16>, x, K, ldx, eps, q, scale, rowsum, x_ready)); break;
-            default: WF_CUDA(cudaLaunchKernelEx(&lc, act_quant_token_kernel<WF_F16>, x, K, ldx, eps, q, scale, rowsum, x_ready)); break;
+            case WF_F32: WF_CUDA(launch_token_quant<WF_F32>(lc, x, K, ldx, eps, q, scale, rowsum, x_ready)); break;
+            case WF_BF16: WF_CUDA(launch_token_quant<WF_BF16>(lc, x, K, ldx, eps, q, scale, rowsum, x_ready)); break;
+            default: WF_CUDA(launch_token_quant<WF_F16>(lc, x, K, ldx, eps, q, scale, rowsum, x_ready)); break;
         }
     } else if (mode == WF_ACT_PER_TENSOR) {
         WF_REQUIRE(x_dtype == WF_F32, "wf_act_quant_i8: per-tensor mode takes fp32 input (as the operator it replaces)");
