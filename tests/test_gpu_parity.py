@@ -625,7 +625,7 @@ def test_training_step_on_packed_weights(wf, dt, tol):
 
 
 @pytest.mark.parametrize("k", [64, 512, 1024, 1536, 2560])
-@pytest.mark.parametrize("m", [16, 33, 64])
+@pytest.mark.parametrize("m", [16, 24, 32, 33, 64])
 def test_few_token_contraction_stage_counts(wf, k, m):
     """The few-token forms of the contraction share the K stages out among two or three issuing threads with partial
     accumulators: every count of stages per tile (fewer than issuing threads, equal, more, not a multiple), one layer
