@@ -37,7 +37,8 @@ BATCHES = [1, 4, 16, 64]
 # (4 attention-sized, 2 gate/up, 1 down per layer): 594 MB of packed weights
 LAYERS = {(2560, 2560): 120, (6912, 2560): 60, (2560, 6912): 30}
 METRIC = "ternary_decode_gemv_GBps"
-GEMM_MIN_M = 16  # token batches from here on run on the tensor-core contraction (one batched launch per layer stack)
+GEMM_MIN_M = 16  # token batches from here on always run on the tensor-core contraction (one batched launch per layer stack);
+                 # below it the library's measured rule decides per stack (ops.stack_uses_contraction: from 4 tokens on for K >= 4096)
 REPEATS = 5      # the --steps region is timed this many times; the median is reported, with min and max
 # DRAM bytes (ncu dram__bytes_read.sum + dram__bytes_write.sum of the streaming kernel's four launches of the step, one
 # capture of the bench command itself) over the algorithmic bytes of the same launch: (shape index, M) -> the ratio of
@@ -141,7 +142,7 @@ def build_workload(wf, torch, device, rank: int, world: int, layers_scale: float
             x = gi.with_outliers(x, seed=1000 * si + m).to(torch.bfloat16)[..., k_lo:k_hi].contiguous()
             xd = x.to(device)
             y = torch.empty(nl, m, n_loc, dtype=torch.bfloat16, device=device)
-            batched = m >= GEMM_MIN_M
+            batched = m >= GEMM_MIN_M or (STACK_RULE and wf.stack_uses_contraction(m, k_hi - k_lo))
             grp = None if batched else wf.DecodeGroup([dict(x=xd[li], codes=c, w_scale=s, out=y[li]) for li, (c, s) in enumerate(lay)])
             # a workspace per contraction stack: the step quantizes the tokens of all of them before the first contraction
             ws = wf.prefill_workspace(nl * m, k_hi - k_lo, device) if batched else None
@@ -187,6 +188,7 @@ def run_group(wf, g, pdl: bool, reduce: bool = True):
 
 
 _SIDE = {}
+STACK_RULE = True  # --min-m-only: stacks below GEMM_MIN_M tokens all run on the streaming kernel
 CHAIN_CONTRACTIONS = True  # --no-chain: every contraction stack quantizes in front of its own launch and waits for its predecessor
 
 
@@ -732,6 +734,7 @@ def main():
     ap.add_argument("--only-m", type=int, default=0, help="restrict the sweep to one token batch (profiling)")
     ap.add_argument("--only-shape", type=int, default=-1, help="restrict the sweep to one shape index (profiling)")
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--min-m-only", action="store_true", help="every stack below 16 tokens on the streaming kernel (ablation of the dispatch rule)")
     ap.add_argument("--no-chain", action="store_true", help="contraction stacks as quantization + launch pairs that wait for one another")
     ap.add_argument("--no-merge", action="store_true", help="one grouped launch per (shape, M) stack instead of one per (K, M)")
     args = ap.parse_args()
@@ -800,6 +803,9 @@ def main():
         BATCHES[:] = [args.only_m]
     if args.only_shape >= 0:
         SHAPES[:] = [SHAPES[args.only_shape]]
+    if args.min_m_only:
+        global STACK_RULE
+        STACK_RULE = False
     note(rank, "building workload")
     groups = build_workload(wf, torch, device, rank, world, args.layers_scale)
     if args.no_chain:
@@ -1033,7 +1039,7 @@ def main():
                                            "algorithmic bytes: " + ", ".join(f"shape {k_[0]} M={k_[1]}: {v_:.3f}" for k_, v_ in sorted(NCU_TRAFFIC_RATIO.items())) +
                                            "; other stacks: their mean",
                          "peak_kind": peak_kind + " copy bandwidth",
-                         "kernel": "decode_stream_kernel", "launches": f"the {dec_launches} grouped launches of the step that hold its {len(dec_groups)} stacks with M < {GEMM_MIN_M}"
+                         "kernel": "decode_stream_kernel", "launches": f"the {dec_launches} grouped launches of the step that hold its {len(dec_groups)} stacks on the streaming kernel: " + ", ".join(f"{g_['n']}x{g_['k']} M={g_['m']}" for g_ in dec_groups)
                                      + (" (stacks of equal K and M share a launch)" if dec_launches < len(dec_groups) else ""),
                          "bytes_per_launch": per_launch_bytes, "us_per_launch": per_launch_us},
             "e2e": {"value": full_bytes / (ms_e2e * 1e-3) / 1e9, "unit": "GB/s", "h2d_bytes_per_step": h2d,
@@ -1055,7 +1061,7 @@ def main():
     if n_gemm_groups and ms_gemm:
         tops = gemm_ops / (ms_gemm * 1e-3) / 1e12
         line["roofline_gemm"] = {"bound": "tensor", "kernel": "prefill_kernel (batched over each layer stack)",
-                                 "launches": f"the {n_gemm_groups} stacks with M >= {GEMM_MIN_M}", "achieved": tops,
+                                 "launches": f"the {n_gemm_groups} stacks on the contraction: " + ", ".join(f"{g_['n']}x{g_['k']} M={g_['m']}" for g_ in gemm_groups), "achieved": tops,
                                  "unit": "TOPS", "peak": peak_tops,
                                  "peak_kind": "measured tcgen05.mma.kind::i8 rate (M128 N256 K32, operands resident)" if i8 else "nominal",
                                  "frac": tops / peak_tops, "frac_of_nominal_4500": tops / 4500.0, "ms": ms_gemm,

@@ -45,6 +45,7 @@ from .ops import (  # noqa: F401
     quantize_activations_i8,
     quantize_maxabs,
     repack,
+    stack_uses_contraction,
     unpack_codes,
 )
 from . import torch_ops  # noqa: F401,E402  (registers torch.ops.wf_b200.*)

@@ -19,6 +19,16 @@ _PACK_MODE = {torch.float32: L.PACK_FP32, torch.bfloat16: L.PACK_CAST_BF16, torc
 DECODE_MAX_TOKENS = 64  # token counts above this go to the prefill entry point
 
 
+def stack_uses_contraction(m: int, k: int) -> bool:
+    """Which kernel a STACK of independent same-shape layers with `m` tokens each should run on: the batched tensor-core
+    contraction (`bitlinear_batched`) or the grouped streaming launch (`DecodeGroup`).  Measured on B200 on stacks of
+    16 to 120 layers (2560x2560, 6912x2560, 2560x6912, 4096x4096, 4096x14336; the contraction timed with its
+    quantization kernel): the contraction's time does not depend on m up to 16 tokens, the streaming kernel's grows
+    with m (its legacy MMA covers 8 tokens per instruction, and activations of long rows crowd its stages out of
+    shared memory); they cross at 2 to 4 tokens for K >= 4096 and between 4 and 8 tokens for K = 2560."""
+    return m >= 8 or (m >= 4 and k >= 4096)
+
+
 def _stream() -> int:
     return torch.cuda.current_stream().cuda_stream
 
