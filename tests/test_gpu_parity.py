@@ -693,3 +693,31 @@ def test_contraction_on_a_quantized_workspace(wf, m):
     with pytest.raises(ValueError):
         wf.bitlinear_batched(x, *projs[0], quantized=True)
     wf.device_status()
+
+
+@pytest.mark.parametrize("m", [16, 32, 64, 128])
+def test_contraction_forms_on_a_long_stack(wf, m):
+    """Every form of the contraction on a stack with some twenty tiles per CTA (30 layers of 6912 x 2560), launched
+    several times back to back on one quantized workspace, alternately as independent launches: the persistent
+    pipeline (ring slots, issuing threads, accumulator buffers) keeps its bookkeeping over many tiles and from one
+    launch into the next.  Three layers are compared with the per-layer kernels bit for bit."""
+    g = torch.Generator(device=DEV).manual_seed(900 + m)
+    n, k, layers = 6912, 2560, 30
+    codes = torch.empty(layers, n, k // 4, dtype=torch.uint8, device=DEV)
+    scales = torch.empty(layers, 2, device=DEV)
+    for i in range(layers):
+        c, s = wf.pack_ternary(torch.randn(n, k, generator=g, device=DEV) * 0.02)
+        codes[i].copy_(c)
+        scales[i].copy_(s)
+    x = torch.randn(layers, m, k, generator=g, device=DEV).bfloat16()
+    y = torch.empty(layers, m, n, dtype=torch.bfloat16, device=DEV)
+    picks = (0, layers // 2, layers - 1)
+    ref = {i: wf.bitlinear(x[i], codes[i], scales[i], path="decode" if m <= 64 else "prefill") for i in picks}
+    ws = wf.prefill_workspace(layers * m, k, DEV)
+    wf.prefill_quantize(x, ws)
+    for rep in range(6):
+        wf.bitlinear_batched(x, codes, scales, out=y, workspace=ws, quantized=True, independent=rep % 2 == 1)
+    torch.cuda.synchronize()
+    wf.device_status()
+    for i in picks:
+        assert torch.equal(ref[i], y[i]), i

@@ -104,9 +104,12 @@ __host__ __device__ constexpr int sm_acc_bufs() { return NTOK == 64 ? 1 : 2; }
 template <int NTOK>
 __host__ __device__ constexpr int sm_acc_cols() { return sm_acc_bufs<NTOK>() * sm_issuers<NTOK>() * NTOK <= 128 ? 128 : 256; }  // one accumulator per issuer and buffer
 constexpr int SM_A_COLS = SM_PK * SM_BK / 4;  // 128 columns of 4 int8 per stage
-// token-tile stages = tensor-memory stages of expanded weights: what the accumulators leave
+// token-tile stages = tensor-memory stages of expanded weights: what the accumulators leave -- except for 32 tokens, which
+// keeps two (one per issuer): with three, launches of that form on 60 stacked 6912x2560 layers ended in a launch failure
+// whose cause reading the kernel did not show, so the combination (two issuers, three stages, two accumulator buffers)
+// is not used.
 template <int NTOK>
-__host__ __device__ constexpr int sm_xs() { return (512 - sm_acc_cols<NTOK>()) / SM_A_COLS; }
+__host__ __device__ constexpr int sm_xs() { return NTOK == 32 ? 2 : (512 - sm_acc_cols<NTOK>()) / SM_A_COLS; }
 constexpr int SM_P_BYTES = SM_BM * SM_PK * SM_BK / 4;  // 16 KB
 constexpr int SM_THREADS = 19 * 32;
 // the second issuer of the two-issuer forms is a warp of its own behind the others; the three-issuer form (16 tokens)
@@ -120,7 +123,7 @@ constexpr size_t sm_smem() {  // more than half of an SM's shared memory: two of
 static_assert(sm_smem<16>() > 114 * 1024 && sm_smem<64>() <= 227 * 1024 && sm_smem<128>() <= 227 * 1024, "shared memory");
 static_assert(sm_acc_cols<16>() + sm_xs<16>() * SM_A_COLS <= 512 && sm_acc_cols<32>() + sm_xs<32>() * SM_A_COLS <= 512 &&
                   sm_acc_cols<64>() + sm_xs<64>() * SM_A_COLS <= 512 && sm_acc_cols<128>() + sm_xs<128>() * SM_A_COLS <= 512 &&
-                  sm_xs<16>() == 3 && sm_xs<32>() == 3 && sm_xs<64>() == 3 && sm_xs<128>() == 2,
+                  sm_xs<16>() == 3 && sm_xs<32>() == 2 && sm_xs<64>() == 3 && sm_xs<128>() == 2,
               "tensor memory");
 
 // The four MMAs of one 128-byte swizzle atom of K in one block of PTX: A advances by 8 tensor-memory columns, B by 32
