@@ -966,6 +966,8 @@ def main():
     note(rank, "breakdown")
     gemm_ops = sum(2.0 * g["m"] * g["n"] * g["k"] * len(g["layers"]) for g in gemm_groups)
     n_gemm_groups = len(gemm_groups)
+    dec_names = ", ".join(f"{g_['n']}x{g_['k']} M={g_['m']}" for g_ in dec_groups)  # (the groups are emptied before the decoder section)
+    gemm_names = ", ".join(f"{g_['n']}x{g_['k']} M={g_['m']}" for g_ in gemm_groups)
     dec_launches = max(1, counted.get(id(dec_groups), len(dec_groups)))
     per_launch_bytes = step_bytes(dec_groups) / dec_launches / world if dec_groups else 0.0  # what one rank's kernel moves
     per_launch_us = (ms_dec or 0.0) * 1e3 / dec_launches
@@ -1039,7 +1041,7 @@ def main():
                                            "algorithmic bytes: " + ", ".join(f"shape {k_[0]} M={k_[1]}: {v_:.3f}" for k_, v_ in sorted(NCU_TRAFFIC_RATIO.items())) +
                                            "; other stacks: their mean",
                          "peak_kind": peak_kind + " copy bandwidth",
-                         "kernel": "decode_stream_kernel", "launches": f"the {dec_launches} grouped launches of the step that hold its {len(dec_groups)} stacks on the streaming kernel: " + ", ".join(f"{g_['n']}x{g_['k']} M={g_['m']}" for g_ in dec_groups)
+                         "kernel": "decode_stream_kernel", "launches": f"the {dec_launches} grouped launches of the step that hold its {len(dec_groups)} stacks on the streaming kernel: " + dec_names
                                      + (" (stacks of equal K and M share a launch)" if dec_launches < len(dec_groups) else ""),
                          "bytes_per_launch": per_launch_bytes, "us_per_launch": per_launch_us},
             "e2e": {"value": full_bytes / (ms_e2e * 1e-3) / 1e9, "unit": "GB/s", "h2d_bytes_per_step": h2d,
@@ -1061,7 +1063,7 @@ def main():
     if n_gemm_groups and ms_gemm:
         tops = gemm_ops / (ms_gemm * 1e-3) / 1e12
         line["roofline_gemm"] = {"bound": "tensor", "kernel": "prefill_kernel (batched over each layer stack)",
-                                 "launches": f"the {n_gemm_groups} stacks on the contraction: " + ", ".join(f"{g_['n']}x{g_['k']} M={g_['m']}" for g_ in gemm_groups), "achieved": tops,
+                                 "launches": f"the {n_gemm_groups} stacks on the contraction: " + gemm_names, "achieved": tops,
                                  "unit": "TOPS", "peak": peak_tops,
                                  "peak_kind": "measured tcgen05.mma.kind::i8 rate (M128 N256 K32, operands resident)" if i8 else "nominal",
                                  "frac": tops / peak_tops, "frac_of_nominal_4500": tops / 4500.0, "ms": ms_gemm,
