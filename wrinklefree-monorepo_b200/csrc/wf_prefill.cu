@@ -95,21 +95,12 @@ constexpr int SM_PS = 6;     // packed-weight stages
 // per-stage bookkeeping, and a single thread's instruction stream is what limits it.)
 template <int NTOK>
 __host__ __device__ constexpr int sm_issuers() { return NTOK <= 16 ? 3 : (NTOK <= 64 ? 2 : 1); }
-// Accumulator buffers: two, so that a tile's epilogue runs under the next tile's MMAs -- except for 64 tokens with two
-// issuers, where a second buffer would leave tensor memory for only two stages of expanded weights and the expansion
-// warps then wait for a free stage a quarter of their time; with one buffer the MMAs of the next tile wait only until
-// the epilogue has the accumulator in registers (it hands the buffer back before it rescales and stores).
 template <int NTOK>
-__host__ __device__ constexpr int sm_acc_bufs() { return NTOK == 64 ? 1 : 2; }
-template <int NTOK>
-__host__ __device__ constexpr int sm_acc_cols() { return sm_acc_bufs<NTOK>() * sm_issuers<NTOK>() * NTOK <= 128 ? 128 : 256; }  // one accumulator per issuer and buffer
+__host__ __device__ constexpr int sm_acc_cols() { return 2 * sm_issuers<NTOK>() * NTOK <= 128 ? 128 : 256; }  // two buffers of one accumulator per issuer
 constexpr int SM_A_COLS = SM_PK * SM_BK / 4;  // 128 columns of 4 int8 per stage
-// token-tile stages = tensor-memory stages of expanded weights: what the accumulators leave -- except for 32 tokens, which
-// keeps two (one per issuer): with three, launches of that form on 60 stacked 6912x2560 layers ended in a launch failure
-// whose cause reading the kernel did not show, so the combination (two issuers, three stages, two accumulator buffers)
-// is not used.
+// token-tile stages = tensor-memory stages of expanded weights; with several issuers one ring slot per issuer
 template <int NTOK>
-__host__ __device__ constexpr int sm_xs() { return NTOK == 32 ? 2 : (512 - sm_acc_cols<NTOK>()) / SM_A_COLS; }
+__host__ __device__ constexpr int sm_xs() { return sm_issuers<NTOK>() > 1 ? sm_issuers<NTOK>() : (512 - sm_acc_cols<NTOK>()) / SM_A_COLS; }
 constexpr int SM_P_BYTES = SM_BM * SM_PK * SM_BK / 4;  // 16 KB
 constexpr int SM_THREADS = 19 * 32;
 // the second issuer of the two-issuer forms is a warp of its own behind the others; the three-issuer form (16 tokens)
@@ -123,7 +114,7 @@ constexpr size_t sm_smem() {  // more than half of an SM's shared memory: two of
 static_assert(sm_smem<16>() > 114 * 1024 && sm_smem<64>() <= 227 * 1024 && sm_smem<128>() <= 227 * 1024, "shared memory");
 static_assert(sm_acc_cols<16>() + sm_xs<16>() * SM_A_COLS <= 512 && sm_acc_cols<32>() + sm_xs<32>() * SM_A_COLS <= 512 &&
                   sm_acc_cols<64>() + sm_xs<64>() * SM_A_COLS <= 512 && sm_acc_cols<128>() + sm_xs<128>() * SM_A_COLS <= 512 &&
-                  sm_xs<16>() == 3 && sm_xs<32>() == 2 && sm_xs<64>() == 3 && sm_xs<128>() == 2,
+                  sm_xs<16>() == 3 && sm_xs<32>() == 2 && sm_xs<64>() == 2 && sm_xs<128>() == 2,
               "tensor memory");
 
 // The four MMAs of one 128-byte swizzle atom of K in one block of PTX: A advances by 8 tensor-memory columns, B by 32
@@ -220,7 +211,7 @@ __global__ void __launch_bounds__(sm_threads<NTOK>(), 1)
     constexpr int SM_ACC_COLS = sm_acc_cols<NTOK>();
     constexpr int NI = sm_issuers<NTOK>();   // issuing threads; with several, issuer i takes the stages of ring slot i
     constexpr int ACC_BUF = NI * NTOK;       // columns of one accumulator buffer: one partial accumulator per issuer
-    constexpr int ACC_BUFS = sm_acc_bufs<NTOK>();
+    static_assert(NI == 1 || NI == SM_XS, "one ring slot per issuer");
     constexpr int X_ATOM = NTOK * SM_BK;        // one 128-byte swizzle atom of the token tile
     constexpr int X_BYTES = SM_PK * X_ATOM;     // a stage: 512 values of K for every token
     extern __shared__ uint8_t smem_raw[];
@@ -321,19 +312,20 @@ __global__ void __launch_bounds__(sm_threads<NTOK>(), 1)
             const uint32_t idesc = (2u << 4) | (0u << 7) | (1u << 10) | (static_cast<uint32_t>(NTOK >> 3) << 17) |
                                    (static_cast<uint32_t>(SM_BM >> 4) << 24);
             if constexpr (NI > 1) {
-                // Issuer i takes the stages whose running number is i modulo NI, sixteen MMAs and one commit each, into a
-                // partial accumulator of its own; the stage's ring slot follows from the running number.
-                uint64_t bdesc[SM_XS][SM_PK];
+                // This thread's stages are those of ring slot `issuer`: operands, barriers and the accumulator column are fixed.
+                uint64_t bdesc[SM_PK];
 #pragma unroll
-                for (int s = 0; s < SM_XS; ++s)
-#pragma unroll
-                    for (int j = 0; j < SM_PK; ++j) bdesc[s][j] = smem_desc_sw128(smem_u32(x_ring + s * X_BYTES + j * X_ATOM));
+                for (int j = 0; j < SM_PK; ++j) bdesc[j] = smem_desc_sw128(smem_u32(x_ring + issuer * X_BYTES + j * X_ATOM));
+                const uint32_t a_stage = tmem_a + issuer * SM_A_COLS;
+                uint64_t* const my_full = &a_full[issuer];
+                uint64_t* const my_free = &st_free[issuer];
+                unsigned par = 0;  // parity of the next wait on my_full
                 int nt = 0, sit0 = 0;
                 for (int t = blockIdx.x; t < total_tiles; t += gridDim.x, ++nt, sit0 += stages) {
-                    const int a = nt % ACC_BUFS;
+                    const int a = nt & 1;
                     const int r0 = sit0 % NI;
                     const int g0 = issuer >= r0 ? issuer - r0 : issuer - r0 + NI;  // this thread's first stage of the tile
-                    if (nt >= ACC_BUFS) mbar_wait(&acc_empty[a], ((nt / ACC_BUFS) - 1) & 1, poisoned);
+                    if (nt >= 2) mbar_wait(&acc_empty[a], ((nt >> 1) - 1) & 1, poisoned);
                     if (g0 >= stages) {  // a tile of fewer stages than issuers: nothing of it is this thread's
                         mbar_arrive(&acc_full[a]);
                         continue;
@@ -341,19 +333,12 @@ __global__ void __launch_bounds__(sm_threads<NTOK>(), 1)
                     tc_fence_after();
                     const uint32_t d_tmem = tmem_base + a * ACC_BUF + issuer * NTOK;
                     for (int g = g0; g < stages; g += NI) {
-                        const int sit = sit0 + g, s = sit % SM_XS;
-                        mbar_wait(&a_full[s], (sit / SM_XS) & 1, poisoned);
+                        mbar_wait(my_full, par, poisoned);
+                        par ^= 1;
                         tc_fence_after();
-                        const uint32_t a_stage = tmem_a + s * SM_A_COLS;
 #pragma unroll
-                        for (int ss = 0; ss < SM_XS; ++ss) {  // a switch, so that the descriptors stay in registers
-                            if (ss == s) {
-#pragma unroll
-                                for (int j = 0; j < SM_PK; ++j)
-                                    mma_i8_ts_x4(d_tmem, a_stage + j * 32, bdesc[ss][j], idesc, (g != g0 || j) ? 1u : 0u);
-                            }
-                        }
-                        tc_commit(&st_free[s]);
+                        for (int j = 0; j < SM_PK; ++j) mma_i8_ts_x4(d_tmem, a_stage + j * 32, bdesc[j], idesc, (g != g0 || j) ? 1u : 0u);
+                        tc_commit(my_free);
                     }
                     tc_commit(&acc_full[a]);
                 }
@@ -366,8 +351,8 @@ __global__ void __launch_bounds__(sm_threads<NTOK>(), 1)
                     for (int j = 0; j < SM_PK; ++j) bdesc[s][j] = smem_desc_sw128(smem_u32(x_ring + s * X_BYTES + j * X_ATOM));
                 int sit = 0, nt = 0;
                 for (int t = blockIdx.x; t < total_tiles; t += gridDim.x, ++nt) {
-                    const int a = nt % ACC_BUFS;
-                    if (nt >= ACC_BUFS) mbar_wait(&acc_empty[a], ((nt / ACC_BUFS) - 1) & 1, poisoned);
+                    const int a = nt & 1;
+                    if (nt >= 2) mbar_wait(&acc_empty[a], ((nt >> 1) - 1) & 1, poisoned);
                     tc_fence_after();
                     const uint32_t d_tmem = tmem_base + a * ACC_BUF;
                     for (int g = 0; g < stages; ++g, ++sit) {
@@ -455,7 +440,7 @@ __global__ void __launch_bounds__(sm_threads<NTOK>(), 1)
         int nt = 0, cur_zb = -1;
         for (int t = blockIdx.x; t < total_tiles; t += gridDim.x, ++nt) {
             const int z = t / tiles_per_problem, zb = t / p.tiles_n, tb = (t % tiles_per_problem) / p.tiles_n, rb = t % p.tiles_n;
-            const int a = nt % ACC_BUFS;
+            const int a = nt & 1;
             const int nrow = rb * SM_BM + r;
             const bool row_ok = nrow < p.N;
             const int tok_base = tb * NTOK;                 // first token of the block inside its problem
@@ -479,13 +464,14 @@ __global__ void __launch_bounds__(sm_threads<NTOK>(), 1)
             const bool fast16 = (p.y_dtype == WF_BF16 || p.y_dtype == WF_F16) && p.acc_out == nullptr;
             uint16_t* y16 = static_cast<uint16_t*>(p.y) + tok0 * p.ldy + nrow;
             const bool is_bf16 = p.y_dtype == WF_BF16;
-            mbar_wait(&acc_full[a], (nt / ACC_BUFS) & 1, poisoned);
+            mbar_wait(&acc_full[a], (nt >> 1) & 1, poisoned);
             tc_fence_after();
-            // sixteen token columns of this thread's row: the sum of the issuers' partial accumulators
-            auto load_chunk = [&](int c0, uint32_t (&v)[16]) {
+#pragma unroll
+            for (int c0 = col0; c0 < col0 + EPI_COLS; c0 += 16) {
+                uint32_t v[16];
                 if constexpr (NI == 1) {
                     tmem_ldn<16>(tmem_base + (static_cast<uint32_t>(quarter * 32) << 16) + a * ACC_BUF + c0, v);
-                } else {  // an issuer without a stage in this tile wrote none
+                } else {  // the sum of the issuers' partial accumulators (an issuer without a stage in this tile wrote none)
 #pragma unroll
                     for (int jt = 0; jt < 16; ++jt) v[jt] = 0;
                     const int r0 = static_cast<int>((static_cast<long long>(nt) * stages) % NI);
@@ -500,14 +486,12 @@ __global__ void __launch_bounds__(sm_threads<NTOK>(), 1)
                         }
                     }
                 }
-            };
-            auto release = [&]() {  // this group's columns are in registers: hand the buffer back to the issuing threads
-                tc_fence_before();
-                __syncwarp();
-                if (lane == 0) mbar_arrive(&acc_empty[a]);
-            };
-            auto store_chunk = [&](int c0, const uint32_t (&v)[16]) {
-                if (!row_ok) return;
+                if (c0 + 16 == col0 + EPI_COLS) {  // this group's columns are in registers: hand them back to the MMA warp
+                    tc_fence_before();
+                    __syncwarp();
+                    if (lane == 0) mbar_arrive(&acc_empty[a]);
+                }
+                if (!row_ok) continue;
                 if (fast16) {
                     epilogue16(v, s_rowsum + c0, s_inv + c0, s_w, has_bias, bias, is_bf16, y16 + static_cast<int64_t>(c0) * p.ldy, p.ldy, mtok - c0);
                 } else {
@@ -523,23 +507,6 @@ __global__ void __launch_bounds__(sm_threads<NTOK>(), 1)
                             if (p.acc_out) p.acc_out[tok * p.N + nrow] = acc;
                         }
                     }
-                }
-            };
-            if constexpr (ACC_BUFS == 1) {
-                // the next tile's MMAs wait for this buffer: every column goes to registers first, then the buffer is free
-                uint32_t vv[EPI_COLS / 16][16];
-#pragma unroll
-                for (int ci = 0; ci < EPI_COLS / 16; ++ci) load_chunk(col0 + 16 * ci, vv[ci]);
-                release();
-#pragma unroll
-                for (int ci = 0; ci < EPI_COLS / 16; ++ci) store_chunk(col0 + 16 * ci, vv[ci]);
-            } else {
-#pragma unroll
-                for (int c0 = col0; c0 < col0 + EPI_COLS; c0 += 16) {
-                    uint32_t v[16];
-                    load_chunk(c0, v);
-                    if (c0 + 16 == col0 + EPI_COLS) release();
-                    store_chunk(c0, v);
                 }
             }
         }
