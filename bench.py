@@ -40,7 +40,7 @@ METRIC = "ternary_decode_gemv_GBps"
 GEMM_MIN_M = 16  # token batches from here on always run on the tensor-core contraction (one batched launch per layer stack);
                  # below it the library's measured rule decides per stack (ops.stack_uses_contraction: from 4 tokens on for K >= 4096)
 REPEATS = 5      # the --steps region is timed this many times; the median is reported, with min and max
-# DRAM bytes (ncu dram__bytes_read.sum + dram__bytes_write.sum of the streaming kernel's four launches of the step, one
+# DRAM bytes (ncu dram__bytes_read.sum + dram__bytes_write.sum of the streaming kernel's launches of the step, one
 # capture of the bench command itself) over the algorithmic bytes of the same launch: (shape index, M) -> the ratio of
 # the launch that holds the stack.  Stacks without a capture of their own use the mean of the measured ones.
 NCU_TRAFFIC_RATIO = {(0, 1): 1.016, (1, 1): 1.016, (0, 4): 1.007, (1, 4): 1.007, (2, 1): 1.018, (2, 4): 1.018}
