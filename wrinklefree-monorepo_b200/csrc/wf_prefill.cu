@@ -275,13 +275,17 @@ __global__ void __launch_bounds__(sm_threads<NTOK>(), 1)
 
     if (warp == 0) {
         if (lane == 0) {
+            // A wait that ran out ends this thread's requests (also below: token tiles, MMAs): nothing new goes into flight
+            // in a CTA that has given up; the expansion and epilogue warps run on without waiting, for their barriers' sake.
             int sit = 0;
-            for (int t = blockIdx.x; t < total_tiles; t += gridDim.x) {
+            bool live = true;
+            for (int t = blockIdx.x; live && t < total_tiles; t += gridDim.x) {
                 const int z = t / tiles_per_problem, rb = t % p.tiles_n;
                 const int row_w = z * p.N + rb * SM_BM;
                 for (int g = 0; g < stages; ++g, ++sit) {
                     const int s = sit % SM_PS;
-                    if (sit >= SM_PS) mbar_wait(&p_empty[s], ((sit / SM_PS) - 1) & 1, poisoned);
+                    if (sit >= SM_PS) live = mbar_wait(&p_empty[s], ((sit / SM_PS) - 1) & 1, poisoned);
+                    if (!live) break;
                     mbar_expect_tx(&p_full[s], SM_P_BYTES);
                     tma_load_2d(p_ring + s * SM_P_BYTES, &tmap_p, g * (SM_PK * SM_BK / 4), row_w, &p_full[s]);
                 }
@@ -294,11 +298,13 @@ __global__ void __launch_bounds__(sm_threads<NTOK>(), 1)
                 asm volatile("griddepcontrol.launch_dependents;\n" ::: "memory");
             }
             int sit = 0;
-            for (int t = blockIdx.x; t < total_tiles; t += gridDim.x) {
+            bool live = true;
+            for (int t = blockIdx.x; live && t < total_tiles; t += gridDim.x) {
                 const int row_x = (t / tiles_per_problem) * p.M + ((t % tiles_per_problem) / p.tiles_n) * NTOK;
                 for (int g = 0; g < stages; ++g, ++sit) {
                     const int s = sit % SM_XS;
-                    if (sit >= SM_XS) mbar_wait(&st_free[s], ((sit / SM_XS) - 1) & 1, poisoned);
+                    if (sit >= SM_XS) live = mbar_wait(&st_free[s], ((sit / SM_XS) - 1) & 1, poisoned);
+                    if (!live) break;
                     mbar_expect_tx(&a_full[s], X_BYTES);
 #pragma unroll
                     for (int j = 0; j < SM_PK; ++j)  // an atom that lies past K arrives as zeros
@@ -321,11 +327,13 @@ __global__ void __launch_bounds__(sm_threads<NTOK>(), 1)
                 uint64_t* const my_free = &st_free[issuer];
                 unsigned par = 0;  // parity of the next wait on my_full
                 int nt = 0, sit0 = 0;
-                for (int t = blockIdx.x; t < total_tiles; t += gridDim.x, ++nt, sit0 += stages) {
+                bool live = true;
+                for (int t = blockIdx.x; live && t < total_tiles; t += gridDim.x, ++nt, sit0 += stages) {
                     const int a = nt & 1;
                     const int r0 = sit0 % NI;
                     const int g0 = issuer >= r0 ? issuer - r0 : issuer - r0 + NI;  // this thread's first stage of the tile
-                    if (nt >= 2) mbar_wait(&acc_empty[a], ((nt >> 1) - 1) & 1, poisoned);
+                    if (nt >= 2) live = mbar_wait(&acc_empty[a], ((nt >> 1) - 1) & 1, poisoned);
+                    if (!live) break;
                     if (g0 >= stages) {  // a tile of fewer stages than issuers: nothing of it is this thread's
                         mbar_arrive(&acc_full[a]);
                         continue;
@@ -333,14 +341,15 @@ __global__ void __launch_bounds__(sm_threads<NTOK>(), 1)
                     tc_fence_after();
                     const uint32_t d_tmem = tmem_base + a * ACC_BUF + issuer * NTOK;
                     for (int g = g0; g < stages; g += NI) {
-                        mbar_wait(my_full, par, poisoned);
+                        live = mbar_wait(my_full, par, poisoned);
+                        if (!live) break;
                         par ^= 1;
                         tc_fence_after();
 #pragma unroll
                         for (int j = 0; j < SM_PK; ++j) mma_i8_ts_x4(d_tmem, a_stage + j * 32, bdesc[j], idesc, (g != g0 || j) ? 1u : 0u);
                         tc_commit(my_free);
                     }
-                    tc_commit(&acc_full[a]);
+                    if (live) tc_commit(&acc_full[a]);
                 }
             } else {
                 // operand descriptors of every (stage, atom), fixed for the whole kernel
@@ -350,14 +359,17 @@ __global__ void __launch_bounds__(sm_threads<NTOK>(), 1)
 #pragma unroll
                     for (int j = 0; j < SM_PK; ++j) bdesc[s][j] = smem_desc_sw128(smem_u32(x_ring + s * X_BYTES + j * X_ATOM));
                 int sit = 0, nt = 0;
-                for (int t = blockIdx.x; t < total_tiles; t += gridDim.x, ++nt) {
+                bool live = true;
+                for (int t = blockIdx.x; live && t < total_tiles; t += gridDim.x, ++nt) {
                     const int a = nt & 1;
-                    if (nt >= 2) mbar_wait(&acc_empty[a], ((nt >> 1) - 1) & 1, poisoned);
+                    if (nt >= 2) live = mbar_wait(&acc_empty[a], ((nt >> 1) - 1) & 1, poisoned);
+                    if (!live) break;
                     tc_fence_after();
                     const uint32_t d_tmem = tmem_base + a * ACC_BUF;
                     for (int g = 0; g < stages; ++g, ++sit) {
                         const int s = sit % SM_XS;
-                        mbar_wait(&a_full[s], (sit / SM_XS) & 1, poisoned);
+                        live = mbar_wait(&a_full[s], (sit / SM_XS) & 1, poisoned);
+                        if (!live) break;
                         tc_fence_after();
                         const uint32_t a_stage = tmem_a + s * SM_A_COLS;
                         // sixteen MMAs of 32 values of K: four per swizzle atom (the ring index is resolved by a switch so
@@ -372,7 +384,7 @@ __global__ void __launch_bounds__(sm_threads<NTOK>(), 1)
                         }
                         tc_commit(&st_free[s]);
                     }
-                    tc_commit(&acc_full[a]);
+                    if (live) tc_commit(&acc_full[a]);
                 }
             }
         }
@@ -516,6 +528,12 @@ __global__ void __launch_bounds__(sm_threads<NTOK>(), 1)
     }
     tc_fence_before();
     __syncthreads();
+    if (*poisoned) {
+        // A CTA that gave up: nothing new was requested since, but copies and MMAs issued before may still be on their
+        // way into this CTA's shared and tensor memory.  They take microseconds; the CTA keeps both for half a millisecond.
+        for (int i = 0; i < 256; ++i) __nanosleep(2000);
+        __syncthreads();
+    }
     if (warp == 1) {
         tc_fence_after();
         asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;\n" ::"r"(tmem_base), "r"(512));
