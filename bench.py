@@ -1034,7 +1034,10 @@ def main():
     line = {"metric": METRIC, "value": value, "unit": "GB/s", "n_gpus": world, "steps": args.steps, "warmup": warmup,
             "ms_per_step": ms, "ms_per_step_repeats": med(ms_all), "higher_is_better": True, "scaling": "strong", "vs_baseline": None,
             "dtype": "u8xs8->s32", "data": "synthetic", "config": config,
-            "launch": {"pdl": pdl, "graph": True, "parallelism": f"tp{world}" if world > 1 else "single"},
+            "launch": {"pdl": pdl, "graph": True, "parallelism": f"tp{world}" if world > 1 else "single",
+                       "streaming_kernel_stacks": dec_names, "contraction_stacks": gemm_names,
+                       "contractions_chained": bool(pdl and CHAIN_CONTRACTIONS and n_gemm_groups > 1),
+                       "streaming_stacks_merged_by_K_and_M": not args.no_merge},
             "roofline": {"bound": "hbm", "achieved": achieved, "peak": peaks["hbm_gbs"], "unit": "GB/s",
                          "frac": achieved / peaks["hbm_gbs"], "frac_of_nominal_8000": achieved / 8000.0, "traffic": traffic,
                          "traffic_source": "ncu dram__bytes_read.sum + dram__bytes_write.sum of the step's streaming launches, as a ratio to the "
