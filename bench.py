@@ -148,9 +148,11 @@ def build_workload(wf, torch, device, rank: int, world: int, layers_scale: float
             ws = wf.prefill_workspace(nl * m, k_hi - k_lo, device) if batched else None
             groups.append(dict(n=n, k=k, m=m, layers=lay, x_host=x.pin_memory(), x=xd, y=y, group=grp, reduce=row_parallel,
                                batched=batched, codes_stack=codes_stack, scales_stack=scales_stack, ws=ws))
-    # the stacks are independent: those on the streaming kernel go first, so that their launches chain (each starts
-    # while its predecessor drains), then those on the tensor-core contraction
-    groups.sort(key=lambda g_: g_["batched"])
+    # The stacks are independent.  Those on the tensor-core contraction go first: a contraction ends with a last wave of
+    # tiles that leaves most SMs idle (600 tiles on 148 SMs are 4.05 waves), which the launch behind it fills -- the next
+    # contraction, and behind the last one the first streaming launch, whose own tail is short (its CTAs claim small items
+    # from a shared counter).  STREAMING_FIRST (--streaming-first) is the other order.
+    groups.sort(key=lambda g_: g_["batched"] if STREAMING_FIRST else not g_["batched"])
     return groups
 
 
@@ -188,6 +190,7 @@ def run_group(wf, g, pdl: bool, reduce: bool = True):
 
 
 _SIDE = {}
+STREAMING_FIRST = False
 STACK_RULE = True  # --min-m-only: stacks below GEMM_MIN_M tokens all run on the streaming kernel
 CHAIN_CONTRACTIONS = True  # --no-chain: every contraction stack quantizes in front of its own launch and waits for its predecessor
 
@@ -734,6 +737,7 @@ def main():
     ap.add_argument("--only-m", type=int, default=0, help="restrict the sweep to one token batch (profiling)")
     ap.add_argument("--only-shape", type=int, default=-1, help="restrict the sweep to one shape index (profiling)")
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--streaming-first", action="store_true", help="the streaming launches of a step before its contractions (ablation of the order)")
     ap.add_argument("--min-m-only", action="store_true", help="every stack below 16 tokens on the streaming kernel (ablation of the dispatch rule)")
     ap.add_argument("--no-chain", action="store_true", help="contraction stacks as quantization + launch pairs that wait for one another")
     ap.add_argument("--no-merge", action="store_true", help="one grouped launch per (shape, M) stack instead of one per (K, M)")
@@ -806,6 +810,9 @@ def main():
     if args.min_m_only:
         global STACK_RULE
         STACK_RULE = False
+    if args.streaming_first:
+        global STREAMING_FIRST
+        STREAMING_FIRST = True
     note(rank, "building workload")
     groups = build_workload(wf, torch, device, rank, world, args.layers_scale)
     if args.no_chain:
