@@ -74,7 +74,8 @@ __global__ void __launch_bounds__(AQ_THREADS)
         scale[m] = s;
         if (rowsum) rowsum[m] = sum;
     }
-    if (x_ready) asm volatile("griddepcontrol.wait;\n" ::: "memory");
+    // one block stays until the predecessor has completed, so that this grid does not end before it; the others leave
+    if (x_ready && blockIdx.x == 0) asm volatile("griddepcontrol.wait;\n" ::: "memory");
 }
 
 // Per-tensor absmax: pass 1 reduces |x| into a float kept as ordered uint bits.
@@ -179,7 +180,8 @@ __global__ void __launch_bounds__(AQ_THREADS)
         scale[m] = s;
         if (rowsum) rowsum[m] = sum;
     }
-    if (x_ready) asm volatile("griddepcontrol.wait;\n" ::: "memory");
+    // one block stays until the predecessor has completed, so that this grid does not end before it; the others leave
+    if (x_ready && blockIdx.x == 0) asm volatile("griddepcontrol.wait;\n" ::: "memory");
 }
 
 template <int DT>
