@@ -266,3 +266,23 @@ def test_packed_weight_cache_invalidation(wf):
     layer._packed[torch.float32] = ("stale",)
     layer.invalidate_packed()
     assert not layer._packed
+
+
+def test_flags_match_the_header_and_the_stack_rule(wf):
+    """The flag values of the Python binding are those of include/wf_b200.h, wf_prefill_quantize validates its
+    arguments without a GPU, and the rule that sends a stack of layers to the contraction is monotonic in the token
+    count."""
+    text = open(os.path.join(ROOT, "include", "wf_b200.h")).read()
+    defs = {k: int(v) for k, v in re.findall(r"#define\s+(WF_FLAG_[A-Z_]+)\s+(\d+)u", text)}
+    L = wf._lib
+    assert defs["WF_FLAG_PDL"] == L.FLAG_PDL and defs["WF_FLAG_X_READY"] == L.FLAG_X_READY
+    assert defs["WF_FLAG_WS_READY"] == L.FLAG_WS_READY
+    assert defs["WF_FLAG_PREFILL_PAIR"] == L.FLAG_PREFILL_PAIR and defs["WF_FLAG_PREFILL_SINGLE"] == L.FLAG_PREFILL_SINGLE
+    assert len(set(defs.values())) == len(defs)  # distinct bits
+    lib = L.lib()
+    assert lib.wf_prefill_quantize(None, 2, 64, 4, 64, 1e-5, None, 0, 0, None) == 1
+    assert b"wf_prefill_quantize" in lib.wf_last_error()
+    for k in (2560, 4096, 6912, 14336):
+        uses = [wf.stack_uses_contraction(m, k) for m in range(1, 65)]
+        assert uses == sorted(uses) and uses[-1] and not uses[0]  # once on the contraction, always from there on
+    assert wf.stack_uses_contraction(4, 6912) and not wf.stack_uses_contraction(4, 2560) and wf.stack_uses_contraction(8, 2560)
